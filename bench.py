@@ -1,0 +1,306 @@
+"""Headline benchmark: ELSA two-pass attention forward + backward, fp16, B=1 H=8 N=16384 d=64.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload headline|...]
+
+One "step" = one forward + backward of the attention operator on one batch of synthetic Q, K, V, dO.
+Multi-GPU (torchrun, one rank per GPU): every rank runs its own batch element (batch x heads shards
+with no data-path collective), so scaling is "weak" and `value` is the whole-job TFLOP/s.
+
+Prints ONE JSON line (rank 0).  `value` is kernel throughput with inputs resident in HBM; `e2e` is
+the same metric through the public PyTorch API with pinned HOST buffers (H2D of q,k,v,dO and D2H of
+out,dq,dk,dv inside the timed region).  `--impl reference` times the CPU restatement of the
+reference's algorithm (the reference itself has no CPU path and its device code is Triton) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "ELSA attn fwd+bwd TFLOP/s (% of B200 peak), d=64 N=16K; scaling at 1/2/4/8 GPU"
+WORKLOADS = {
+    # name: (B, H, N, D, dtype, causal)
+    "headline": (1, 8, 16384, 64, "float16", False),
+    "causal_bf16": (1, 8, 16384, 64, "bfloat16", True),
+    "fp32_4k": (1, 8, 4096, 64, "float32", False),
+    "small": (1, 8, 2048, 64, "float16", False),
+}
+
+
+def flops(b, h, n, d, causal):
+    pairs = n * (n + 1) // 2 if causal else n * n
+    fwd = 4 * b * h * pairs * d
+    return fwd, int(2.5 * fwd)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) > 8:
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(b, h, n, d, dtype, causal, rows, threads):
+    """One bounded CPU step of the oracle: 1 head, `rows` query rows against all N keys, fwd + bwd."""
+    from oracle import elsa_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1234)
+    q, k, v, do = (torch.randn(1, 1, n, d, generator=g).to(dtype) for _ in range(4))
+    rows = min(rows, n)
+    bh, scale = 1, 1.0 / (d ** 0.5)
+    t0 = time.perf_counter()
+    m, z, s = O.phase1_generic(q[0], k[0], v[0], is_causal=causal, block_n=2048, summary_dtype=dtype, q_start=0, q_len=rows)
+    out, rm, rz = O.final_reduce(m, z, s)
+    out = out.to(dtype)
+    # backward for the same rows: dQ for those rows, and their contribution to dK, dV
+    q3, k3, v3, do3 = q[0, :, :rows].float(), k[0].float(), v[0].float(), do[0, :, :rows].float()
+    d_row, lse = O.bwd_preprocess(out, do3, rm, rz)
+    sc = (q3 @ k3.transpose(-1, -2)) * (scale * O.LOG2E)
+    if causal:
+        idx = torch.arange(n)
+        sc = torch.where(idx[:rows, None] >= idx[None, :], sc, torch.full((), float("-inf")))
+    p = torch.exp2(sc - lse[..., None])
+    dp = do3 @ v3.transpose(-1, -2)
+    ds = (p * (dp - d_row[..., None])).to(dtype).float()
+    dq = (ds @ k3) * scale
+    dk = (ds.transpose(-1, -2) @ q3) * scale
+    dv = p.to(dtype).float().transpose(-1, -2) @ do3
+    dt = time.perf_counter() - t0
+    pairs = (rows * (rows + 1) // 2 + 0) if (causal and rows == n) else rows * n
+    if causal and rows < n:
+        pairs = rows * (rows + 1) // 2
+    return 14 * bh * pairs * d, dt, float(dq.abs().sum() + dk.abs().sum() + dv.abs().sum())
+
+
+def run_reference(args, wl):
+    b, h, n, d, dt_name, causal = wl
+    dtype = getattr(torch, dt_name)
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 1024
+    for _ in range(max(args.warmup, 1)):
+        cpu_sample(b, h, n, d, dtype, causal, rows, threads)
+    tot_f, tot_t = 0, 0.0
+    for _ in range(args.steps):
+        f, t, _ = cpu_sample(b, h, n, d, dtype, causal, rows, threads)
+        tot_f += f
+        tot_t += t
+    val = tot_f / tot_t / 1e12
+    sample = f"per step: 1 of {b*h} heads, first {rows} of {n} query rows against all keys, fwd+bwd"
+    line = {"metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 arithmetic on " + dt_name + " inputs", "data": "synthetic", "impl": "reference",
+            "config": {"workload": args.workload, "shape": [b, h, n, d], "causal": causal},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, wl)
+
+    import elsa_b200 as E
+    from elsa_b200 import _lib
+    from elsa_b200.attention_bwd import _backward_impl
+    lib = _lib.load()   # raises if the CUDA library is missing: there is no fallback
+
+    b, h, n, d, dt_name, causal = wl
+    dtype = getattr(torch, dt_name)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # synthetic inputs: iid N(0,1), CPU generator seeded per rank; ROT input sets are rotated so that a
+    # step never finds its operands in L2 (one set = 8 tensors of B*H*N*D elements)
+    ROT = 3
+    g = torch.Generator().manual_seed(1234 + rank)
+    host = [[torch.randn(b, h, n, d, generator=g).to(dtype).pin_memory() for _ in range(4)] for _ in range(ROT)]
+    sets = [[t.to(dev) for t in s] for s in host]
+    fwd_f, bwd_f = flops(b, h, n, d, causal)
+
+    def step(i, ev=None):
+        q, k, v, do = sets[i % ROT]
+        if ev:
+            ev[0].record()
+        out, rm, rz, qc, kc, vc = E.attention._forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=dtype,
+                                                            part_width=0, q_chunk=0, want_state=True)
+        if ev:
+            ev[1].record()
+        res = _backward_impl(qc, kc, vc, out, do, bias=None, is_causal=causal, row_m=rm, row_z=rz, want_dbias=False)
+        if ev:
+            ev[2].record()
+        return out, res
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    l0 = lib.elsa_kernel_launches()
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        step(i, evs[i])
+    t_end.record()
+    barrier()
+    launches = lib.elsa_kernel_launches() - l0
+    total_ms = t_start.elapsed_time(t_end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * (fwd_f + bwd_f) / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the public API with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        outs_host = [torch.empty(b, h, n, d, dtype=dtype).pin_memory() for _ in range(4)]
+
+        def e2e_step(i):
+            q, k, v, do = (t.to(dev, non_blocking=True) for t in host[i % ROT])
+            q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+            out = E.twopass_attention_train(q, k, v, is_causal=causal)
+            out.backward(do)
+            for dst, src in zip(outs_host, (out.detach(), q.grad, k.grad, v.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        for i in range(2):
+            e2e_step(i)
+        barrier()
+        k_e2e = max(3, min(args.steps, 10))
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(k_e2e):
+            e2e_step(i)
+        t1.record()
+        barrier()
+        e_ms = t0.elapsed_time(t1)
+        if dist is not None:
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        nbytes = b * h * n * d * torch.empty((), dtype=dtype).element_size() * 4
+        e2e = {"value": world * (fwd_f + bwd_f) / (e_ms / k_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": k_e2e}
+
+    if rank == 0:
+        pk = peaks()
+        uses_tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(dtype), d, n, 0, int(causal), 1))
+        achieved = bwd_f / (bwd_ms * 1e-3) / 1e12
+        roofline = {"kernel": "backward (dQ, dK, dV recompute)" + (" tcgen05" if uses_tc else " fp32-fma"),
+                    "bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["tflops"], "peak_source": pk["source"] + " bf16 dense burst", "traffic": None,
+                    "ms_per_launch": bwd_ms, "forward": {"achieved": fwd_f / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms}}
+        cpu = None
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            rows, tot_f, tot_t = 1024, 0, 0.0
+            cpu_sample(b, h, n, d, dtype, causal, 256, threads)
+            t_lim = time.perf_counter() + 20.0
+            while time.perf_counter() < t_lim and tot_t < 12.0:
+                f, t, _ = cpu_sample(b, h, n, d, dtype, causal, rows, threads)
+                tot_f += f; tot_t += t
+            cpu = {"value": tot_f / tot_t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                   "sample": f"1 of {b*h} heads, first {rows} of {n} query rows against all keys, fwd+bwd, repeated for {tot_t:.1f} s"}
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16" if dtype == torch.float16 else dt_name, "data": "synthetic",
+                "config": {"workload": args.workload, "shape_per_gpu": [b, h, n, d], "causal": causal, "global_batch": b * world,
+                           "sharding": "batch x heads, no collective", "l2": f"{ROT} rotating input sets (>{ROT*134} MB), inputs larger than L2",
+                           "tensor_cores": uses_tc},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+                "pct_of_peak": 100.0 * value / world / pk["tflops"]}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,216 @@
+"""Training side of the two-pass attention: forward that keeps the per-row state, the exact
+recompute backward, and the autograd wrapper.
+
+Mirrors src/elsa_twopass_clean/attention_bwd.py of the reference: `twopass_attention_with_state`
+(:77-185), `twopass_attention_backward` (:661-839), `_TwopassAttentionAutograd` (:842-905),
+`_dense_bias_backward` (:908-1000) and `twopass_attention_train` (:1003-1030).  Differences that are
+deliberate: the bias gradient is produced by the same backward launch (no second pass, no
+materialised score matrix, any broadcast shape), and rows whose keys are all masked get zero
+gradients instead of NaN.
+"""
+from __future__ import annotations
+
+from typing import Literal, Optional
+
+import torch
+
+from . import _lib
+from .attention import _aligned, _canonical_bias, _check_qkv, _forward_impl, _resolve_common, _validate_warps
+
+
+def twopass_attention_with_state(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    block_m: Optional[int] = None,
+    block_n: Optional[int] = None,
+    q_chunk_size: Optional[int] = None,
+    summary_dtype: Optional[torch.dtype] = None,
+    phase1_warps: Optional[int] = None,
+    phase2_warps: Optional[int] = None,
+    phase1_stages: Optional[int] = None,
+    phase2_stages: Optional[int] = None,
+    input_precision: Literal["auto", "ieee", "tf32", "tf32x3"] = "auto",
+    algorithm: Literal["auto", "paper_scan"] = "auto",
+    return_contiguous_inputs: bool = False,
+) -> tuple[torch.Tensor, ...]:
+    """Forward that also returns the row statistics the backward needs.
+
+    Returns (out, row_m, row_z) or, with return_contiguous_inputs, (out, row_m, row_z, q_c, k_c, v_c);
+    row_m (log2 domain, -inf for a row without admissible keys) and row_z are fp32 [B*H, N]."""
+    _check_qkv(q, k, v, "twopass_attention_with_state")
+    batch, heads, seq_len, head_dim = map(int, q.shape)
+    if seq_len <= 0:
+        empty_state = torch.empty((batch * heads, 0), device=q.device, dtype=torch.float32)
+        out_empty = torch.empty_like(q)
+        if return_contiguous_inputs:
+            return out_empty, empty_state, empty_state, q.contiguous(), k.contiguous(), v.contiguous()
+        return out_empty, empty_state, empty_state
+    if head_dim > 128:
+        raise ValueError("head_dim > 128 is not supported by the current kernels")
+    summary_dtype, part_width, q_chunk = _resolve_common(
+        q, algorithm=algorithm, input_precision=input_precision, summary_dtype=summary_dtype, block_m=block_m,
+        block_n=block_n, q_chunk_size=q_chunk_size, phase1_warps=phase1_warps, phase2_warps=phase2_warps,
+        phase1_stages=phase1_stages, phase2_stages=phase2_stages)
+    out, row_m, row_z, q_c, k_c, v_c = _forward_impl(
+        q, k, v, bias=bias, is_causal=is_causal, summary_dtype=summary_dtype, part_width=part_width,
+        q_chunk=q_chunk, want_state=True)
+    if return_contiguous_inputs:
+        return out, row_m, row_z, q_c, k_c, v_c
+    return out, row_m, row_z
+
+
+def _row_stats(q_c, k_c, meta, is_causal):
+    lib = _lib.load()
+    batch, heads, seq_len, head_dim = map(int, q_c.shape)
+    dt = _lib.dtype_code(q_c.dtype)
+    row_m = torch.empty((batch * heads, seq_len), device=q_c.device, dtype=torch.float32)
+    row_z = torch.empty_like(row_m)
+    nbytes = lib.elsa_row_stats_workspace_bytes(dt, batch, heads, seq_len, head_dim, int(meta.has_bias),
+                                                int(bool(is_causal)))
+    if nbytes < 0:
+        raise ValueError("elsa_b200: unsupported problem size for row statistics")
+    with torch.cuda.device(q_c.device):
+        ws = torch.empty((max(int(nbytes), 256),), device=q_c.device, dtype=torch.uint8)
+        rc = lib.elsa_row_stats(q_c.data_ptr(), k_c.data_ptr(), *meta.c_args(), row_m.data_ptr(), row_z.data_ptr(),
+                                ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len, head_dim,
+                                int(bool(is_causal)), torch.cuda.current_stream(q_c.device).cuda_stream)
+    _lib.check(rc, "elsa_row_stats")
+    return row_m, row_z
+
+
+def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, want_dbias, flags=0):
+    lib = _lib.load()
+    batch, heads, seq_len, head_dim = map(int, q.shape)
+    q_c, k_c, v_c, out_c, go_c = (_aligned(t) for t in (q, k, v, out, grad_out))
+    meta = _canonical_bias(bias, batch=batch, heads=heads, seq_len=seq_len, device=q.device)
+    if row_m is None or row_z is None:
+        row_m, row_z = _row_stats(q_c, k_c, meta, is_causal)
+    else:
+        if tuple(row_m.shape) != (batch * heads, seq_len) or tuple(row_z.shape) != (batch * heads, seq_len):
+            raise ValueError("row_m and row_z must have shape [B*H,N]")
+        row_m = row_m.to(torch.float32).contiguous()
+        row_z = row_z.to(torch.float32).contiguous()
+    dq, dk, dv = torch.empty_like(q_c), torch.empty_like(k_c), torch.empty_like(v_c)
+    dbias = None
+    dargs = (None, 0, 0, 0, 0)
+    if want_dbias:
+        if not meta.has_bias:
+            raise ValueError("a bias gradient was requested without a bias")
+        # same broadcast layout as the bias itself: contributions of broadcast axes are summed
+        dbias = torch.zeros_like(meta.tensor)
+        dargs = (dbias.data_ptr(), meta.stride_b, meta.stride_h, meta.stride_q, meta.stride_k)
+    dt = _lib.dtype_code(q.dtype)
+    nbytes = lib.elsa_backward_workspace_bytes(dt, batch, heads, seq_len, head_dim, int(meta.has_bias),
+                                               int(bool(is_causal)), flags)
+    if nbytes < 0:
+        raise ValueError("elsa_b200: unsupported problem size for the backward")
+    with torch.cuda.device(q.device):
+        ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
+        rc = lib.elsa_twopass_backward(
+            q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), out_c.data_ptr(), go_c.data_ptr(),
+            row_m.data_ptr(), row_z.data_ptr(), *meta.c_args(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            *dargs, ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len, head_dim, int(bool(is_causal)), flags,
+            torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "elsa_twopass_backward")
+    if dbias is not None:
+        dbias = dbias.view(bias.shape).to(bias.dtype)
+    return dq, dk, dv, dbias
+
+
+def twopass_attention_backward(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    grad_out: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    block_m: Optional[int] = None,
+    block_n: Optional[int] = None,
+    num_warps: Optional[int] = None,
+    num_stages: Optional[int] = None,
+    input_precision: Literal["auto", "ieee", "tf32", "tf32x3"] = "auto",
+    row_m: Optional[torch.Tensor] = None,
+    row_z: Optional[torch.Tensor] = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """dq, dk, dv by exact recompute; the score matrix is never materialised.  A dense bias takes
+    part in the softmax when given; its gradient is only produced through `twopass_attention_train`.
+    Without (row_m, row_z) the row statistics are recomputed first."""
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must have shape [B,H,N,D]")
+    if q.shape != k.shape or q.shape != v.shape or q.shape != out.shape or q.shape != grad_out.shape:
+        raise ValueError("q, k, v, out, and grad_out must have identical shapes")
+    if q.device.type != "cuda":
+        raise ValueError("twopass_attention_backward currently requires CUDA tensors")
+    if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError("supported dtypes are fp16, bf16, and fp32")
+    if int(q.shape[3]) > 128:
+        raise ValueError("head_dim > 128 is not supported by the current kernels")
+    if int(q.shape[2]) <= 0:
+        return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if input_precision not in ("auto", "ieee", "tf32", "tf32x3"):
+        raise ValueError("input_precision must be 'auto', 'ieee', 'tf32', or 'tf32x3'")
+    if num_warps is not None:
+        _validate_warps("num_warps", num_warps)
+    for val in (block_m, block_n, num_stages):
+        if val is not None:
+            int(val)
+    grad_out = grad_out.to(q.dtype)
+    dq, dk, dv, _ = _backward_impl(q, k, v, out.to(q.dtype), grad_out, bias=bias, is_causal=is_causal, row_m=row_m,
+                                   row_z=row_z, want_dbias=False)
+    return dq, dk, dv
+
+
+class _TwopassAttentionAutograd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, bias, is_causal, fwd_kwargs, bwd_kwargs):
+        out, row_m, row_z, q_s, k_s, v_s = twopass_attention_with_state(
+            q, k, v, bias=bias, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
+        has_bias = bias is not None
+        ctx.save_for_backward(q_s, k_s, v_s, out, bias if has_bias else q_s.new_empty(1, dtype=torch.float32),
+                              row_m, row_z)
+        ctx.has_bias = has_bias
+        ctx.bias_requires_grad = bool(has_bias and bias.requires_grad)
+        ctx.is_causal = bool(is_causal)
+        ctx.bwd_kwargs = dict(bwd_kwargs)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, saved_bias, row_m, row_z = ctx.saved_tensors
+        bias = saved_bias if ctx.has_bias else None
+        if q.numel() == 0:
+            return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), None, None, None, None
+        dq, dk, dv, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
+                                           row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad)
+        return dq, dk, dv, dbias, None, None, None
+
+
+def twopass_attention_train(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    bwd_block_m: Optional[int] = None,
+    bwd_block_n: Optional[int] = None,
+    bwd_num_warps: Optional[int] = None,
+    bwd_num_stages: Optional[int] = None,
+    bwd_input_precision: Literal["auto", "ieee", "tf32", "tf32x3"] = "auto",
+    **fwd_kwargs,
+) -> torch.Tensor:
+    """Differentiable `twopass_attention`: two-pass forward with saved (m, z), recompute backward."""
+    if bwd_input_precision not in ("auto", "ieee", "tf32", "tf32x3"):
+        raise ValueError("input_precision must be 'auto', 'ieee', 'tf32', or 'tf32x3'")
+    if bwd_num_warps is not None:
+        _validate_warps("num_warps", bwd_num_warps)
+    bwd_kwargs = {name: val for name, val in (("block_m", bwd_block_m), ("block_n", bwd_block_n),
+                                              ("num_warps", bwd_num_warps), ("num_stages", bwd_num_stages))
+                  if val is not None}
+    return _TwopassAttentionAutograd.apply(q, k, v, bias, is_causal, dict(fwd_kwargs), bwd_kwargs)

@@ -1,0 +1,315 @@
+// C-ABI layer: argument validation, work planning (partition width, query chunking), host
+// orchestration of the two passes and of the backward.  Everything is stream-ordered; nothing
+// here allocates device memory or synchronises.
+#include <algorithm>
+#include <cmath>
+
+#include "kernels.cuh"
+
+namespace elsa {
+
+thread_local int g_last_cuda_error = 0;
+std::atomic<long long> g_kernel_launches{0};
+
+static int g_sm_count_cache[64] = {0};
+
+static int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (g_sm_count_cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count_cache[dev] = n;
+  }
+  return g_sm_count_cache[dev];
+}
+
+struct ForwardPlan {
+  int part_width, n_parts, q_chunk, tile_m, tile_n;
+  bool tensor_cores;
+  int64_t mz_bytes, s_bytes;  // one summary set: m (== z) and s, 256-byte aligned
+  int sets;                   // 1, or 2 when a ping-pong pass (scan steps / tree) was requested
+};
+
+static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  (void)dtype; (void)head_dim; (void)n_ctx; (void)has_bias; (void)flags;
+  return false;  // no tcgen05 kernel linked into this build yet
+}
+
+static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal,
+                        bool has_bias, int part_width_in, int q_chunk_in, unsigned flags, ForwardPlan* pl) {
+  if (!dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 || heads < 1 || n_ctx < 1 || head_dim < 1 ||
+      head_dim > 128)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  const int64_t bh = static_cast<int64_t>(batch) * heads;
+  if (bh > 65535) return ELSA_ERR_UNSUPPORTED;
+  pl->tensor_cores = tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->tile_m = pl->tensor_cores ? 128 : 64;
+  pl->tile_n = pl->tensor_cores ? 128 : 64;
+  const int tiles_n = static_cast<int>(cdiv64(n_ctx, pl->tile_n));
+  int n_parts;
+  if (part_width_in > 0) {
+    pl->part_width = static_cast<int>(align_up(part_width_in, pl->tile_n));
+  } else {
+    // enough CTAs for a few waves over the SMs, but no more partitions than that needs:
+    // every extra partition is one more summary to write and to merge.
+    const int64_t q_ctas = cdiv64(n_ctx, pl->tile_m) * bh;
+    const int64_t target = static_cast<int64_t>(sm_count()) * (pl->tensor_cores ? 2 : 6);
+    int64_t want = std::max<int64_t>(1, cdiv64(target, q_ctas));
+    want = std::min<int64_t>(want, tiles_n);
+    const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, want));
+    pl->part_width = tiles_per_part * pl->tile_n;
+  }
+  n_parts = static_cast<int>(cdiv64(n_ctx, pl->part_width));
+  if (n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
+  pl->n_parts = n_parts;
+  pl->sets = (flags & (ELSA_FLAG_SCAN_STEPS | ELSA_FLAG_TREE_MERGE)) ? 2 : 1;
+  const int64_t row_bytes = static_cast<int64_t>(n_parts) * bh * (static_cast<int64_t>(head_dim) * dtype_size(summary_dtype) + 8);
+  int q_chunk;
+  if (q_chunk_in > 0) {
+    q_chunk = static_cast<int>(std::min<int64_t>(n_ctx, align_up(q_chunk_in, pl->tile_m)));
+  } else {
+    const int64_t cap = static_cast<int64_t>(1) << 30;  // keep one summary set under 1 GiB
+    int64_t rows = std::max<int64_t>(pl->tile_m, (cap / row_bytes) / pl->tile_m * pl->tile_m);
+    q_chunk = static_cast<int>(std::min<int64_t>(n_ctx, rows));
+  }
+  pl->q_chunk = q_chunk;
+  const int64_t rows_total = static_cast<int64_t>(n_parts) * bh * q_chunk;
+  pl->mz_bytes = align_up(rows_total * 4, 256);
+  pl->s_bytes = align_up(rows_total * head_dim * dtype_size(summary_dtype), 256);
+  return ELSA_OK;
+}
+
+static int64_t plan_bytes(const ForwardPlan& pl) { return pl.sets * (2 * pl.mz_bytes + pl.s_bytes); }
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int phase1_dispatch(const void* q, const void* k, const void* v, const float* bias, int64_t bsb, int64_t bsh,
+                           int64_t bsq, int64_t bsk, float* m_buf, float* z_buf, void* s_buf, int dtype,
+                           int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int q_start, int q_len,
+                           int part_width, int n_parts, int is_causal, unsigned flags, cudaStream_t st) {
+  if (!q || !k || !v || !m_buf || !z_buf || !s_buf || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
+      heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || q_start < 0 || q_len < 0 ||
+      q_start + q_len > n_ctx || part_width < 1 || n_parts < 1 ||
+      static_cast<int64_t>(n_parts) * part_width < n_ctx)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(s_buf)) return ELSA_ERR_INVALID_ARGUMENT;
+  if (static_cast<int64_t>(batch) * heads > 65535 || n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
+  if (q_len == 0) return ELSA_OK;
+  (void)flags;
+  if (part_width % 64 != 0) return ELSA_ERR_INVALID_ARGUMENT;
+  FoldParams p;
+  p.q = q; p.k = k; p.v = v;
+  p.bias = bias; p.bsb = bsb; p.bsh = bsh; p.bsq = bsq; p.bsk = bsk;
+  p.m = m_buf; p.z = z_buf; p.s = s_buf;
+  p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.q_start = q_start; p.q_len = q_len;
+  p.part_width = part_width; p.n_parts = n_parts; p.bh = batch * heads;
+  p.is_causal = is_causal ? 1 : 0;
+  p.summary_dtype = summary_dtype;
+  // reference rounding point: P is cast to fp16 before P.V only for fp16 inputs whose summaries are
+  // not fp32 (attention_parallel_scan.py:701, attention.py:96-99); bf16 and fp32 keep P in fp32.
+  p.round_p = (dtype == ELSA_F16 && summary_dtype != ELSA_F32) ? 1 : 0;
+  p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  return fold_simt(p, dtype, st);
+}
+
+}  // namespace elsa
+
+using namespace elsa;
+
+extern "C" int elsa_abi_version(void) { return ELSA_B200_ABI_VERSION; }
+
+extern "C" const char* elsa_strerror(int status) {
+  switch (status) {
+    case ELSA_OK: return "ok";
+    case ELSA_ERR_INVALID_ARGUMENT: return "invalid argument (size, pointer, dtype or alignment)";
+    case ELSA_ERR_UNSUPPORTED: return "unsupported problem for this build";
+    case ELSA_ERR_CUDA: return "CUDA call failed (see elsa_last_cuda_error)";
+    case ELSA_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case ELSA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int elsa_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
+
+extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
+  (void)is_causal; (void)backward;
+  return tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
+}
+
+extern "C" int elsa_phase1_fold(const void* q, const void* k, const void* v, const float* bias, int64_t bias_stride_b,
+                                int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k, float* m_buf,
+                                float* z_buf, void* s_buf, int dtype, int summary_dtype, int batch, int heads,
+                                int n_ctx, int head_dim, int q_start, int q_len, int part_width, int n_parts,
+                                int is_causal, unsigned flags, void* stream) {
+  return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_buf, z_buf, s_buf,
+                         dtype, summary_dtype, batch, heads, n_ctx, head_dim, q_start, q_len, part_width, n_parts,
+                         is_causal, flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
+                                 int has_bias, int is_causal, int part_width_in, int q_chunk_in, unsigned flags,
+                                 int* part_width, int* n_parts, int* q_chunk) {
+  ForwardPlan pl;
+  int rc = plan_forward(dtype, summary_dtype, batch, heads, n_ctx, head_dim, is_causal, has_bias != 0, part_width_in,
+                        q_chunk_in, flags, &pl);
+  if (rc != ELSA_OK) return rc;
+  if (part_width) *part_width = pl.part_width;
+  if (n_parts) *n_parts = pl.n_parts;
+  if (q_chunk) *q_chunk = pl.q_chunk;
+  return ELSA_OK;
+}
+
+extern "C" int64_t elsa_forward_workspace_bytes(int dtype, int summary_dtype, int batch, int heads, int n_ctx,
+                                                int head_dim, int has_bias, int is_causal, int part_width,
+                                                int q_chunk, unsigned flags) {
+  if (n_ctx == 0) return 0;
+  ForwardPlan pl;
+  if (plan_forward(dtype, summary_dtype, batch, heads, n_ctx, head_dim, is_causal, has_bias != 0, part_width, q_chunk, flags,
+                   &pl) != ELSA_OK)
+    return -1;
+  return plan_bytes(pl);
+}
+
+extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v, const float* bias,
+                                    int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q,
+                                    int64_t bias_stride_k, void* out, float* row_m, float* row_z, void* workspace,
+                                    int64_t workspace_bytes, int dtype, int summary_dtype, int batch, int heads,
+                                    int n_ctx, int head_dim, int is_causal, int part_width, int q_chunk, unsigned flags,
+                                    void* stream) {
+  if (n_ctx == 0) return ELSA_OK;
+  if (!q || !k || !v || !out) return ELSA_ERR_INVALID_ARGUMENT;
+  if ((row_m == nullptr) != (row_z == nullptr)) return ELSA_ERR_INVALID_ARGUMENT;
+  ForwardPlan pl;
+  int rc = plan_forward(dtype, summary_dtype, batch, heads, n_ctx, head_dim, is_causal, bias != nullptr, part_width,
+                        q_chunk, flags, &pl);
+  if (rc != ELSA_OK) return rc;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < plan_bytes(pl))
+    return ELSA_ERR_WORKSPACE;
+  if (!aligned16(out)) return ELSA_ERR_INVALID_ARGUMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  float* m_a = reinterpret_cast<float*>(ws);
+  float* z_a = reinterpret_cast<float*>(ws + pl.mz_bytes);
+  void* s_a = ws + 2 * pl.mz_bytes;
+  char* ws_b = ws + 2 * pl.mz_bytes + pl.s_bytes;
+  float* m_b = reinterpret_cast<float*>(ws_b);
+  float* z_b = reinterpret_cast<float*>(ws_b + pl.mz_bytes);
+  void* s_b = ws_b + 2 * pl.mz_bytes;
+  const int bh = batch * heads;
+  const int store_state = row_m != nullptr;
+
+  for (int q_start = 0; q_start < n_ctx; q_start += pl.q_chunk) {
+    const int q_len = std::min(pl.q_chunk, n_ctx - q_start);
+    rc = phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_a, z_a, s_a, dtype,
+                         summary_dtype, batch, heads, n_ctx, head_dim, q_start, q_len, pl.part_width, pl.n_parts,
+                         is_causal, flags, st);
+    if (rc != ELSA_OK) return rc;
+    if (is_causal && (flags & ELSA_FLAG_SCAN_STEPS)) {
+      // log-depth Hillis-Steele inclusive scan, ping-pong between the two summary sets; the last
+      // prefix is the row's answer (future partitions hold the identity).
+      float *sm = m_a, *sz = z_a, *dm = m_b, *dz = z_b;
+      void *ss = s_a, *ds = s_b;
+      for (int step = 1; step < pl.n_parts; step *= 2) {
+        rc = elsa_scan_step(sm, sz, ss, dm, dz, ds, summary_dtype, pl.n_parts, bh, q_len, head_dim, step, stream);
+        if (rc != ELSA_OK) return rc;
+        std::swap(sm, dm); std::swap(sz, dz); std::swap(ss, ds);
+      }
+      rc = merge_final_any(sm, sz, ss, out, row_m, row_z, summary_dtype, dtype, 1, bh, q_start, q_len, n_ctx, head_dim,
+                           pl.n_parts - 1, store_state, st);
+    } else if (!is_causal && (flags & ELSA_FLAG_TREE_MERGE)) {
+      float *sm = m_a, *sz = z_a, *dm = m_b, *dz = z_b;
+      void *ss = s_a, *ds = s_b;
+      for (int n_in = pl.n_parts; n_in > 1; n_in = (n_in + 1) / 2) {
+        rc = elsa_upsweep_level(sm, sz, ss, dm, dz, ds, summary_dtype, n_in, bh, q_len, head_dim, stream);
+        if (rc != ELSA_OK) return rc;
+        std::swap(sm, dm); std::swap(sz, dz); std::swap(ss, ds);
+      }
+      rc = merge_final_any(sm, sz, ss, out, row_m, row_z, summary_dtype, dtype, 1, bh, q_start, q_len, n_ctx, head_dim, 0,
+                           store_state, st);
+    } else {
+      rc = merge_final_any(m_a, z_a, s_a, out, row_m, row_z, summary_dtype, dtype, pl.n_parts, bh, q_start, q_len, n_ctx,
+                           head_dim, 0, store_state, st);
+    }
+    if (rc != ELSA_OK) return rc;
+  }
+  return ELSA_OK;
+}
+
+// ---- backward -------------------------------------------------------------------------------
+static int64_t bwd_state_bytes(int batch, int heads, int n_ctx) {
+  return align_up(static_cast<int64_t>(batch) * heads * n_ctx * 4, 256);
+}
+
+extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                                 int has_bias, int is_causal, unsigned flags) {
+  (void)has_bias; (void)is_causal; (void)flags;
+  if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128) return -1;
+  return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
+}
+
+extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                     const float* row_m, const float* row_z, const float* bias, int64_t bias_stride_b,
+                                     int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k, void* dq,
+                                     void* dk, void* dv, float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
+                                     int64_t dbias_stride_q, int64_t dbias_stride_k, void* workspace,
+                                     int64_t workspace_bytes, int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                     int is_causal, unsigned flags, void* stream) {
+  if (n_ctx == 0) return ELSA_OK;
+  if (!q || !k || !v || !out || !dout || !row_m || !row_z || !dq || !dk || !dv || !dtype_ok(dtype) || batch < 1 ||
+      heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(dout) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (static_cast<int64_t>(batch) * heads > 65535) return ELSA_ERR_UNSUPPORTED;
+  const int64_t need = elsa_backward_workspace_bytes(dtype, batch, heads, n_ctx, head_dim, bias != nullptr, is_causal, flags);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < need) return ELSA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  float* row_d = reinterpret_cast<float*>(ws);
+  float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
+  int rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
+  if (rc != ELSA_OK) return rc;
+  BwdParams p;
+  p.q = q; p.k = k; p.v = v; p.dout = dout;
+  p.lse = row_lse; p.drow = row_d;
+  p.bias = bias; p.bsb = bias_stride_b; p.bsh = bias_stride_h; p.bsq = bias_stride_q; p.bsk = bias_stride_k;
+  p.dq = dq; p.dk = dk; p.dv = dv;
+  p.dbias = dbias; p.dsb = dbias_stride_b; p.dsh = dbias_stride_h; p.dsq = dbias_stride_q; p.dsk = dbias_stride_k;
+  p.dbias_atomic = (dbias && ((dbias_stride_b == 0 && batch > 1) || (dbias_stride_h == 0 && heads > 1))) ? 1 : 0;
+  p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.bh = batch * heads; p.is_causal = is_causal ? 1 : 0;
+  p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int elsa_row_stats(const void* q, const void* k, const float* bias, int64_t bias_stride_b,
+                              int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k, float* row_m,
+                              float* row_z, void* workspace, int64_t workspace_bytes, int dtype, int batch, int heads,
+                              int n_ctx, int head_dim, int is_causal, void* stream) {
+  // (m, z) do not depend on V: run the forward with V := K into a scratch output placed behind the
+  // summaries in the workspace, and keep only the state.
+  if (n_ctx == 0) return ELSA_OK;
+  if (!row_m || !row_z) return ELSA_ERR_INVALID_ARGUMENT;
+  const int64_t fwd = elsa_forward_workspace_bytes(dtype, dtype, batch, heads, n_ctx, head_dim, bias != nullptr,
+                                                   is_causal, 0, 0, 0u);
+  if (fwd < 0) return ELSA_ERR_INVALID_ARGUMENT;
+  const int64_t out_bytes = align_up(static_cast<int64_t>(batch) * heads * n_ctx * head_dim * dtype_size(dtype), 256);
+  if (!workspace || workspace_bytes < fwd + out_bytes) return ELSA_ERR_WORKSPACE;
+  void* scratch_out = static_cast<char*>(workspace) + fwd;
+  return elsa_twopass_forward(q, k, k, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, scratch_out,
+                              row_m, row_z, workspace, fwd, dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, 0, 0,
+                              0u, stream);
+}
+
+extern "C" int64_t elsa_row_stats_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                                  int has_bias, int is_causal) {
+  const int64_t fwd = elsa_forward_workspace_bytes(dtype, dtype, batch, heads, n_ctx, head_dim, has_bias, is_causal,
+                                                   0, 0, 0u);
+  if (fwd < 0) return -1;
+  return fwd + align_up(static_cast<int64_t>(batch) * heads * n_ctx * head_dim * dtype_size(dtype), 256);
+}

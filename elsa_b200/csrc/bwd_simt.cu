@@ -1,0 +1,240 @@
+// Backward on the FP32-FMA pipe: exact recompute from the saved row statistics.
+//
+//   bwd_preprocess   D = sum_d out*dout, LSE = m + log2(max(z, 1e-30))        (HBM pass)
+//   bwd_simt<MODE 0> one CTA per 64 query rows, streams key tiles:  dQ (+ dbias)
+//   bwd_simt<MODE 1> one CTA per 64 key rows,   streams query tiles: dK, dV
+//
+// Both modes are the same register-tiled code with the operand roles swapped: the "row" operands
+// stay in shared memory for the whole CTA, the "column" operands are streamed in 64-row tiles.
+// MODE 1 computes the transposed tiles S^T = K Q^T and dP^T = V dO^T directly, so P^T and dS^T are
+// produced in the layout the dV / dK contractions consume.  No atomics on dQ/dK/dV: results are
+// bit-reproducible from run to run.
+#include "kernels.cuh"
+#include "simt_tile.cuh"
+
+namespace elsa {
+
+template <typename T, int DP, int MODE>
+__global__ void __launch_bounds__(256)
+bwd_simt_kernel(const BwdParams prm) {
+  constexpr int LD = DP + 4;
+  constexpr int CPT = DP / 16;
+  extern __shared__ __align__(16) float smem[];
+  float* RA = smem;             // MODE 0: Q rows     MODE 1: K rows
+  float* RB = RA + 64 * LD;     // MODE 0: dO rows    MODE 1: V rows
+  float* CA = RB + 64 * LD;     // MODE 0: K tile     MODE 1: Q tile
+  float* CB = CA + 64 * LD;     // MODE 0: V tile     MODE 1: dO tile
+  float* Ps = CB + 64 * LD;     // MODE 0: dS         MODE 1: P^T
+  float* Ss = Ps + 64 * 68;     //                    MODE 1: dS^T
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y;
+  const int D = prm.head_dim, N = prm.n_ctx;
+  const int r0 = blockIdx.x * 64;
+  const int rows_valid = min(64, N - r0);
+  const int64_t base = static_cast<int64_t>(bh) * N * D;
+  const T* qb = static_cast<const T*>(prm.q) + base;
+  const T* kb = static_cast<const T*>(prm.k) + base;
+  const T* vb = static_cast<const T*>(prm.v) + base;
+  const T* gb = static_cast<const T*>(prm.dout) + base;
+  const float* lse = prm.lse + static_cast<int64_t>(bh) * N;
+  const float* drow = prm.drow + static_cast<int64_t>(bh) * N;
+  const bool vec_ok = (D % 4) == 0;
+  const int b = bh / prm.heads, h = bh - b * prm.heads;
+  const float* bias_bh = prm.bias ? prm.bias + b * prm.bsb + h * prm.bsh : nullptr;
+  float* dbias_bh = (MODE == 0 && prm.dbias) ? prm.dbias + b * prm.dsb + h * prm.dsh : nullptr;
+
+  load_tile<T, DP>(RA, LD, (MODE == 0 ? qb : kb) + static_cast<int64_t>(r0) * D, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(RB, LD, (MODE == 0 ? gb : vb) + static_cast<int64_t>(r0) * D, rows_valid, D, vec_ok, tid);
+
+  float lse_r[4], d_r[4];
+  if (MODE == 0) {
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+      const int r = r0 + ty * 4 + ii;
+      lse_r[ii] = r < N ? lse[r] : -CUDART_INF_F;
+      d_r[ii] = r < N ? drow[r] : 0.f;
+    }
+  }
+  float acc1[4][CPT], acc2[4][CPT];  // MODE 0: acc1 = dQ; MODE 1: acc1 = dV, acc2 = dK
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) { acc1[i][c] = 0.f; acc2[i][c] = 0.f; }
+
+  int c_begin = 0, c_end = N;
+  if (prm.is_causal) {
+    if (MODE == 0) c_end = min(N, r0 + rows_valid);  // keys <= last query row of the tile
+    else c_begin = r0;                               // queries >= first key row of the tile
+  }
+
+  for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+    __syncthreads();
+    const int cv = min(64, N - c0);
+    load_tile<T, DP>(CA, LD, (MODE == 0 ? kb : qb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
+    load_tile<T, DP>(CB, LD, (MODE == 0 ? vb : gb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
+    __syncthreads();
+
+    float S[4][4], dP[4][4];
+    tile_dot<DP>(RA, CA, LD, ty, tx, S);
+    tile_dot<DP>(RB, CB, LD, ty, tx, dP);
+
+    float lse_c[4], d_c[4];
+    if (MODE == 1) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int c = c0 + tx + 16 * jj;
+        lse_c[jj] = c < N ? lse[c] : -CUDART_INF_F;
+        d_c[jj] = c < N ? drow[c] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int rr = r0 + ty * 4 + ii, cc = c0 + tx + 16 * jj;
+        const int qi = MODE == 0 ? rr : cc;
+        const int kj = MODE == 0 ? cc : rr;
+        bool valid = rr < N && cc < N;
+        if (prm.is_causal) valid = valid && (qi >= kj);
+        const float l = MODE == 0 ? lse_r[ii] : lse_c[jj];
+        const float dd = MODE == 0 ? d_r[ii] : d_c[jj];
+        float sc;
+        if (bias_bh) {
+          const float bv = valid ? bias_bh[static_cast<int64_t>(qi) * prm.bsq + static_cast<int64_t>(kj) * prm.bsk] : 0.f;
+          sc = (S[ii][jj] * prm.scale + bv) * kLog2e;
+        } else {
+          sc = S[ii][jj] * prm.scale_log2;
+        }
+        // a row with no admissible key has LSE = -inf: its probabilities are defined as 0
+        const float p = (valid && l > -CUDART_INF_F) ? exp2f(sc - l) : 0.f;
+        const float ds = p * (dP[ii][jj] - dd);
+        if (MODE == 0 && dbias_bh && valid) {
+          float* dst = dbias_bh + static_cast<int64_t>(qi) * prm.dsq + static_cast<int64_t>(kj) * prm.dsk;
+          if (prm.dbias_atomic) atomicAdd(dst, ds); else *dst = ds;
+        }
+        const int so = (ty * 4 + ii) * 68 + tx + 16 * jj;
+        if (MODE == 0) {
+          Ps[so] = round_to<T>(ds);
+        } else {
+          Ps[so] = round_to<T>(p);
+          Ss[so] = round_to<T>(ds);
+        }
+      }
+    }
+    __syncthreads();
+    if (MODE == 0) {
+      tile_pv<DP>(Ps, CA, LD, ty, tx, acc1);   // dQ += dS K
+    } else {
+      tile_pv<DP>(Ps, CB, LD, ty, tx, acc1);   // dV += P^T dO
+      tile_pv<DP>(Ss, CA, LD, ty, tx, acc2);   // dK += dS^T Q
+    }
+  }
+
+#pragma unroll
+  for (int ii = 0; ii < 4; ++ii) {
+    const int r = r0 + ty * 4 + ii;
+    if (r >= N) continue;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int col = tile_col<DP>(tx, c);
+      if (col >= D) continue;
+      const int64_t o = base + static_cast<int64_t>(r) * D + col;
+      if (MODE == 0) {
+        static_cast<T*>(prm.dq)[o] = from_f32<T>(acc1[ii][c] * prm.scale);
+      } else {
+        static_cast<T*>(prm.dv)[o] = from_f32<T>(acc1[ii][c]);
+        static_cast<T*>(prm.dk)[o] = from_f32<T>(acc2[ii][c] * prm.scale);
+      }
+    }
+  }
+}
+
+template <typename T, int DP, int MODE>
+static int launch_bwd(const BwdParams& p, cudaStream_t st) {
+  constexpr size_t smem = sizeof(float) * (4 * 64 * (DP + 4) + (MODE == 0 ? 1 : 2) * 64 * 68);
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_simt_kernel<T, DP, MODE>), smem);
+  if (rc != ELSA_OK) return rc;
+  dim3 grid(static_cast<unsigned>((p.n_ctx + 63) / 64), static_cast<unsigned>(p.bh));
+  bwd_simt_kernel<T, DP, MODE><<<grid, 256, smem, st>>>(p);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+template <typename T>
+static int bwd_simt_t(const BwdParams& p, cudaStream_t st) {
+  const int dp = p.head_dim <= 32 ? 32 : (p.head_dim <= 64 ? 64 : 128);
+  int rc;
+  if (dp == 32) { rc = launch_bwd<T, 32, 0>(p, st); if (rc) return rc; return launch_bwd<T, 32, 1>(p, st); }
+  if (dp == 64) { rc = launch_bwd<T, 64, 0>(p, st); if (rc) return rc; return launch_bwd<T, 64, 1>(p, st); }
+  rc = launch_bwd<T, 128, 0>(p, st); if (rc) return rc; return launch_bwd<T, 128, 1>(p, st);
+}
+
+int bwd_simt(const BwdParams& p, int dtype, cudaStream_t st) {
+  if (dtype == ELSA_F32) return bwd_simt_t<float>(p, st);
+  if (dtype == ELSA_F16) return bwd_simt_t<__half>(p, st);
+  return bwd_simt_t<__nv_bfloat16>(p, st);
+}
+
+// ---- preprocess --------------------------------------------------------------------------
+// 8 lanes per row; each lane strides over the row in 4-element vectors.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bwd_preprocess_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
+                      const float* __restrict__ row_z, float* __restrict__ row_d, float* __restrict__ row_lse,
+                      int64_t rows, int D, int vec_ok) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t row = gid >> 3;
+  const int lane = static_cast<int>(gid & 7);
+  float part = 0.f;
+  if (row < rows) {
+    const T* o = out + row * D;
+    const T* g = dout + row * D;
+    if (vec_ok) {
+      for (int c = lane * 4; c < D; c += 32) {
+        float a[4], b[4];
+        Vec4<T>::load(o + c, a);
+        Vec4<T>::load(g + c, b);
+        part += a[0] * b[0] + a[1] * b[1] + a[2] * b[2] + a[3] * b[3];
+      }
+    } else {
+      for (int c = lane; c < D; c += 8) part += to_f32<T>(o[c]) * to_f32<T>(g[c]);
+    }
+  }
+  part += __shfl_xor_sync(0xffffffffu, part, 4);
+  part += __shfl_xor_sync(0xffffffffu, part, 2);
+  part += __shfl_xor_sync(0xffffffffu, part, 1);
+  if (row < rows && lane == 0) {
+    row_d[row] = part;
+    row_lse[row] = row_m[row] + log2f(fmaxf(row_z[row], 1.0e-30f));
+  }
+}
+
+}  // namespace elsa
+
+using namespace elsa;
+
+extern "C" int elsa_bwd_preprocess(const void* out, const void* dout, const float* row_m, const float* row_z,
+                                   float* row_d, float* row_lse, int dtype, int bh, int n_ctx, int head_dim,
+                                   void* stream) {
+  if (!out || !dout || !row_m || !row_z || !row_d || !row_lse || !dtype_ok(dtype) || bh < 1 || n_ctx < 0 ||
+      head_dim < 1 || head_dim > 128)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (n_ctx == 0) return ELSA_OK;
+  const int64_t rows = static_cast<int64_t>(bh) * n_ctx;
+  const unsigned blocks = static_cast<unsigned>(cdiv64(rows * 8, 256));
+  const int vec_ok = head_dim % 4 == 0;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == ELSA_F32)
+    bwd_preprocess_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(dout),
+                                                         row_m, row_z, row_d, row_lse, rows, head_dim, vec_ok);
+  else if (dtype == ELSA_F16)
+    bwd_preprocess_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(out), static_cast<const __half*>(dout),
+                                                          row_m, row_z, row_d, row_lse, rows, head_dim, vec_ok);
+  else
+    bwd_preprocess_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(out),
+                                                                 static_cast<const __nv_bfloat16*>(dout), row_m, row_z,
+                                                                 row_d, row_lse, rows, head_dim, vec_ok);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}

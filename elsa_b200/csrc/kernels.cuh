@@ -1,0 +1,36 @@
+// Internal interface between the C-ABI layer (api.cu) and the kernel translation units.
+#pragma once
+
+#include "common.cuh"
+
+namespace elsa {
+
+struct FoldParams {
+  const void* q; const void* k; const void* v;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;
+  float* m; float* z; void* s;
+  int heads, n_ctx, head_dim, q_start, q_len, part_width, n_parts, bh;
+  int is_causal, summary_dtype, round_p;  // round_p: 0 keep P in fp32, 1 round to fp16, 2 to bf16
+  float scale, scale_log2;
+};
+
+struct BwdParams {
+  const void* q; const void* k; const void* v; const void* dout;
+  const float* lse; const float* drow;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;
+  void* dq; void* dk; void* dv;
+  float* dbias; int64_t dsb, dsh, dsq, dsk; int dbias_atomic;
+  int heads, n_ctx, head_dim, bh, is_causal;
+  float scale, scale_log2;
+};
+
+// FP32-FMA kernels (fold_simt.cu, bwd_simt.cu)
+int fold_simt(const FoldParams& p, int dtype, cudaStream_t st);
+int bwd_simt(const BwdParams& p, int dtype, cudaStream_t st);
+
+// phase 2 (phase2.cu)
+int merge_final_any(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
+                    int summary_dtype, int out_dtype, int n_parts, int bh, int q_start, int q_len, int n_ctx,
+                    int head_dim, int first_part, int store_state, cudaStream_t st);
+
+}  // namespace elsa

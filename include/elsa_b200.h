@@ -1,0 +1,188 @@
+/*
+ * elsa_b200 -- C ABI of the B200-native two-pass monoid attention.
+ *
+ * Every entry point takes raw device pointers, explicit sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), launches on that
+ * stream and returns immediately with 0 or one of the ELSA_ERR_* codes.  Nothing here
+ * allocates or frees device memory, synchronises the device or throws: buffers belong to
+ * the caller and are borrowed for the duration of the stream-ordered launch.
+ *
+ * The citations name the interface of the reference project (ming053l/ELSA, paths relative
+ * to its root) that each entry point replaces.
+ *
+ * Tensor conventions
+ *   q, k, v, out, dout, dq, dk, dv ... [B*H, N, D] contiguous, element type `dtype`
+ *   row_m, row_z, row_d, row_lse ..... [B*H, N] fp32; row_m and row_lse in the log2 domain
+ *   bias ............................. fp32, addressed as
+ *                                      bias[b*stride_b + h*stride_h + q*stride_q + k*stride_k]
+ *                                      (a zero stride broadcasts), NULL = no bias
+ *   summaries ........................ m, z: [P, B*H, q_len] fp32; s: [P, B*H, q_len, D] in
+ *                                      `summary_dtype`; P = number of K partitions; the rows
+ *                                      are the queries q_start .. q_start+q_len-1
+ */
+#ifndef ELSA_B200_H_
+#define ELSA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ELSA_B200_ABI_VERSION 1
+
+enum elsa_dtype { ELSA_F32 = 0, ELSA_F16 = 1, ELSA_BF16 = 2 };
+
+enum elsa_status {
+  ELSA_OK = 0,
+  ELSA_ERR_INVALID_ARGUMENT = 1, /* a size, pointer, dtype or alignment the ABI does not accept */
+  ELSA_ERR_UNSUPPORTED = 2,      /* valid request that no kernel in this build covers */
+  ELSA_ERR_CUDA = 3,             /* a CUDA runtime/driver call failed; see elsa_last_cuda_error */
+  ELSA_ERR_WORKSPACE = 4,        /* workspace pointer missing, misaligned or too small */
+  ELSA_ERR_DEVICE_TIMEOUT = 5    /* a bounded device-side wait gave up (status word set) */
+};
+
+/* flags for the forward / backward entry points */
+#define ELSA_FLAG_FORCE_SIMT 1u   /* never take the tcgen05 kernels (debug / A-B checks) */
+#define ELSA_FLAG_SCAN_STEPS 2u   /* causal: run the log-depth Hillis-Steele steps instead of the one-pass merge */
+#define ELSA_FLAG_TREE_MERGE 4u   /* non-causal: run the Blelloch up-sweep levels instead of the one-pass merge */
+
+int elsa_abi_version(void);
+const char* elsa_strerror(int status);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread */
+int elsa_last_cuda_error(void);
+/* number of kernels this library has launched in this process so far (all threads, all streams) */
+int64_t elsa_kernel_launches(void);
+/* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run */
+int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward);
+
+/* ---------------------------------------------------------------------------------------
+ * Phase 1: per-K-partition (m, z, s) fold.
+ * Replaces the Triton launches `_phase1_summary_kernel` (src/elsa_twopass_clean/attention.py:22-106),
+ * `_phase1_d64_{fp16,fp32}_nomask_kernel` (attention_parallel_scan.py:123-224) and
+ * `_phase1_d64_tiled_{fp16,fp32}_nomask_kernel` (attention_parallel_scan.py:227-372) together
+ * with their grid set-up (attention_parallel_scan.py:486-563, 680-708, 881-909).
+ * Partition p covers keys [p*part_width, min(N, (p+1)*part_width)).  Keys >= N never contribute
+ * (the NEEDS_MASK rule, attention_parallel_scan.py:472); a partition with no valid key for a row
+ * yields the identity (-inf, 0, 0).
+ * ------------------------------------------------------------------------------------- */
+int elsa_phase1_fold(const void* q, const void* k, const void* v,
+                     const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                     int64_t bias_stride_q, int64_t bias_stride_k,
+                     float* m_buf, float* z_buf, void* s_buf,
+                     int dtype, int summary_dtype,
+                     int batch, int heads, int n_ctx, int head_dim,
+                     int q_start, int q_len, int part_width, int n_parts,
+                     int is_causal, unsigned flags, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Phase 2, one pass: merge all partition summaries of each row, out = s / z, optional state.
+ * Replaces pybind `final_reduce(m, z, s, out, row_m, row_z, q_start, n_ctx, k_blocks, q_blocks,
+ * bh, block_m, store_state)` (src/elsa_twopass_clean/cuda/paper_scan_d64.cpp:3-20, kernel
+ * cuda/paper_scan_d64_kernel.cu:9-96), generalised to any D <= 128 and to bf16.
+ * out is [B*H, N, D] in `out_dtype`; rows q_start .. q_start+q_len-1 are written.
+ * ------------------------------------------------------------------------------------- */
+int elsa_merge_final(const float* m_buf, const float* z_buf, const void* s_buf,
+                     void* out, float* row_m, float* row_z,
+                     int summary_dtype, int out_dtype,
+                     int n_parts, int bh, int q_start, int q_len, int n_ctx, int head_dim,
+                     int store_state, void* stream);
+
+/* One Hillis-Steele step out[p] = in[p-step] (+) in[p]; replaces `_summary_scan_step_kernel`
+ * (attention_parallel_scan.py:13-64) and one iteration of the host loop at :713-733. */
+int elsa_scan_step(const float* m_in, const float* z_in, const void* s_in,
+                   float* m_out, float* z_out, void* s_out,
+                   int summary_dtype, int n_parts, int bh, int q_len, int head_dim,
+                   int step, void* stream);
+
+/* One Blelloch up-sweep level out[i] = in[2i] (+) in[2i+1] (odd tail merges with the identity);
+ * replaces `_summary_blelloch_upsweep_kernel` (attention_parallel_scan.py:67-120) and one
+ * iteration of the host loop at :914-935.  Writes ceil(n_in/2) partitions. */
+int elsa_upsweep_level(const float* m_in, const float* z_in, const void* s_in,
+                       float* m_out, float* z_out, void* s_out,
+                       int summary_dtype, int n_in, int bh, int q_len, int head_dim, void* stream);
+
+/* Inclusive prefix scan over the partitions in ONE read + ONE write pass (each row's P
+ * summaries are folded left to right in registers).  Same result as running elsa_scan_step for
+ * step = 1, 2, 4, ... (attention_parallel_scan.py:710-733) with 1/log2(P) of the HBM traffic.
+ * The output buffers must not alias the inputs. */
+int elsa_prefix_scan(const float* m_in, const float* z_in, const void* s_in,
+                     float* m_out, float* z_out, void* s_out,
+                     int summary_dtype, int n_parts, int bh, int q_len, int head_dim, void* stream);
+
+/* out = s / z from partition `final_part`, optional state; replaces `_scan_last_to_out_kernel`
+ * (attention_parallel_scan.py:375-415). */
+int elsa_finalize(const float* m_buf, const float* z_buf, const void* s_buf,
+                  void* out, float* row_m, float* row_z,
+                  int summary_dtype, int out_dtype,
+                  int final_part, int bh, int q_start, int q_len, int n_ctx, int head_dim,
+                  int store_state, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Whole forward = host orchestration of both passes, one call.
+ * Replaces `twopass_attention_paper_scan` and the three host drivers under it
+ * (attention_parallel_scan.py:443-584, 587-759, 762-961, 964-1018).
+ * part_width / q_chunk <= 0 let the library choose.  row_m / row_z may be NULL.
+ * ------------------------------------------------------------------------------------- */
+int64_t elsa_forward_workspace_bytes(int dtype, int summary_dtype, int batch, int heads, int n_ctx,
+                                     int head_dim, int has_bias, int is_causal, int part_width,
+                                     int q_chunk, unsigned flags);
+int elsa_twopass_forward(const void* q, const void* k, const void* v,
+                         const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                         int64_t bias_stride_q, int64_t bias_stride_k,
+                         void* out, float* row_m, float* row_z,
+                         void* workspace, int64_t workspace_bytes,
+                         int dtype, int summary_dtype,
+                         int batch, int heads, int n_ctx, int head_dim,
+                         int is_causal, int part_width, int q_chunk, unsigned flags, void* stream);
+/* how the forward above splits the work: fills part_width, n_parts, q_chunk (all may be NULL) */
+int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
+                      int has_bias, int is_causal, int part_width_in, int q_chunk_in, unsigned flags,
+                      int* part_width, int* n_parts, int* q_chunk);
+
+/* ---------------------------------------------------------------------------------------
+ * Backward.
+ * ------------------------------------------------------------------------------------- */
+/* D = sum_d out*dout, LSE = m + log2(max(z, 1e-30)); replaces `_bwd_preprocess_kernel`
+ * (src/elsa_twopass_clean/attention_bwd.py:188-224). */
+int elsa_bwd_preprocess(const void* out, const void* dout, const float* row_m, const float* row_z,
+                        float* row_d, float* row_lse, int dtype, int bh, int n_ctx, int head_dim,
+                        void* stream);
+
+/* Row statistics (m, z) recomputed from q, k (and bias); replaces `_row_stats_kernel`
+ * (attention_bwd.py:227-306).  workspace: elsa_row_stats_workspace_bytes. */
+int64_t elsa_row_stats_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                       int has_bias, int is_causal);
+int elsa_row_stats(const void* q, const void* k,
+                   const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                   int64_t bias_stride_q, int64_t bias_stride_k,
+                   float* row_m, float* row_z, void* workspace, int64_t workspace_bytes,
+                   int dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal,
+                   void* stream);
+
+/* dQ, dK, dV (and, when dbias != NULL, the bias gradient accumulated in fp32) by exact
+ * recompute from the saved forward state (out, row_m, row_z).  Replaces the launches of
+ * `_bwd_preprocess_kernel`, `_bwd_dq_kernel`, `_bwd_dkdv_kernel` and `_dbias_dense_kernel`
+ * (attention_bwd.py:188-224, 309-412, 415-527, 529-624) made by `twopass_attention_backward`
+ * and `_dense_bias_backward` (attention_bwd.py:765-838, 939-970).
+ * dbias is fp32, addressed with the dbias_stride_* like bias; where a stride is 0 the
+ * contributions of that axis are summed (atomically) -- the caller zeroes dbias first.
+ * workspace: elsa_backward_workspace_bytes (row_d, row_lse, and the fp32 dQ accumulator of the
+ * tensor-core path). */
+int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                      int has_bias, int is_causal, unsigned flags);
+int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                          const float* row_m, const float* row_z,
+                          const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                          int64_t bias_stride_q, int64_t bias_stride_k,
+                          void* dq, void* dk, void* dv,
+                          float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
+                          int64_t dbias_stride_q, int64_t dbias_stride_k,
+                          void* workspace, int64_t workspace_bytes,
+                          int dtype, int batch, int heads, int n_ctx, int head_dim,
+                          int is_causal, unsigned flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELSA_B200_H_ */

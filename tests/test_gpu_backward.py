@@ -1,0 +1,142 @@
+"""GPU parity of the backward path against the oracle, the reference fixtures and fp64 autograd.
+
+Tolerances: gradients <= 1e-6 in fp32 (task statement).  For 16-bit inputs the task's 2e-5 was
+measured by the reference with dO scaled by 0.1 on long rows; gradients here are O(0.1-1) and are
+rounded to the input dtype, so the bound is 2e-5 + 2 output ulps of the largest gradient element
+against the oracle (same rounding points), and the reference's own test tolerance against fp64.
+"""
+import pytest
+import torch
+
+import elsa_b200 as E
+from oracle import elsa_oracle as O
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+F32, F16, BF16 = torch.float32, torch.float16, torch.bfloat16
+
+
+def grad_tol(dtype, ref):
+    if dtype == F32:
+        return 1e-6 * max(1.0, float(ref.abs().max()))
+    return 2e-5 + 2 * U.ulp(dtype, float(ref.float().abs().max()))
+
+
+@pytest.mark.parametrize("name", ["bwd_f32_n70_d64", "bwd_f32_causal_n70_d64", "bwd_f16_n70_d64",
+                                  "bwd_f16_causal_n70_d64", "bwd_swin_f32_n49_d32", "bwd_swin_f16_n49_d32"])
+def test_backward_matches_reference_fixture(golden, name):
+    g = golden(name)
+    q, k, v, out, dout = (g[x].to(DEV) for x in ("q", "k", "v", "out", "dout"))
+    bias = g.get("bias")
+    causal = bool(g["causal"])
+    biasd = None if bias is None else bias.to(DEV)
+    dq, dk, dv = E.twopass_attention_backward(q, k, v, out, dout, bias=biasd, is_causal=causal,
+                                              row_m=g["row_m"].to(DEV), row_z=g["row_z"].to(DEV))
+    for got, nm in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert U.max_abs(got, g[nm]) <= grad_tol(q.dtype, g[nm]), nm
+    # without saved state the statistics are recomputed (reference: _row_stats_kernel)
+    dq2, dk2, dv2 = E.twopass_attention_backward(q, k, v, out, dout, bias=biasd, is_causal=causal)
+    for got, nm in ((dq2, "dq"), (dk2, "dk"), (dv2, "dv")):
+        assert U.max_abs(got, g[nm]) <= 4 * grad_tol(q.dtype, g[nm]), nm
+    if "dbias" in g:
+        from elsa_b200.attention_bwd import _backward_impl
+        res = _backward_impl(q, k, v, out, dout, bias=biasd, is_causal=causal, row_m=g["row_m"].to(DEV),
+                             row_z=g["row_z"].to(DEV), want_dbias=True)
+        tol = (2e-6 if q.dtype == F32 else 2e-3) * max(1.0, float(g["dbias"].abs().max()))
+        assert U.max_abs(res[3], g["dbias"]) <= tol
+
+
+CASES = [
+    # (B, H, N, D, dtype, causal, bias_kind)
+    (1, 2, 64, 32, F32, False, None),
+    (1, 2, 64, 32, F32, True, None),
+    (1, 2, 64, 32, F16, False, None),
+    (1, 2, 64, 32, F16, True, None),
+    (1, 2, 193, 64, F32, False, None),
+    (2, 2, 130, 64, F16, True, None),
+    (1, 2, 257, 64, BF16, True, None),
+    (1, 2, 100, 128, BF16, False, None),
+    (1, 2, 75, 48, F32, True, None),
+    (8, 3, 49, 32, F16, False, "1hnn"),
+    (8, 3, 49, 32, F32, False, "bhnn"),
+    (2, 3, 49, 32, F32, False, "b1nn"),
+    (2, 3, 60, 32, F32, False, "nn"),
+    (2, 3, 60, 32, F16, True, "hnn"),
+    (1, 2, 1025, 64, F16, False, None),
+]
+
+
+def make_bias(kind, b, h, n, seed):
+    if kind is None:
+        return None
+    shape = {"nn": (n, n), "hnn": (h, n, n), "1hnn": (1, h, n, n), "b1nn": (b, 1, n, n), "bhnn": (b, h, n, n)}[kind]
+    return U.seeded(shape, F32, seed, 0.05)
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_train_vs_oracle_and_fp64(case):
+    b, h, n, d, dtype, causal, bias_kind = case
+    q = U.seeded((b, h, n, d), dtype, 60, 0.5)
+    k = U.seeded((b, h, n, d), dtype, 61, 0.5)
+    v = U.seeded((b, h, n, d), dtype, 62)
+    dout = U.seeded((b, h, n, d), dtype, 63, 0.25)
+    bias = make_bias(bias_kind, b, h, n, 64)
+
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    biasd = None if bias is None else bias.to(DEV).requires_grad_(True)
+    out = E.twopass_attention_train(qd, kd, vd, bias=biasd, is_causal=causal)
+    out.backward(dout.to(DEV))
+
+    o_ref, rm, rz = O.twopass_forward(q, k, v, bias=bias, is_causal=causal, training=True)
+    # the oracle's backward starts from the CUDA forward's saved output so that both sides see the same D
+    res = O.twopass_backward(q, k, v, out.detach().cpu(), dout, rm, rz, bias=bias, is_causal=causal,
+                             want_dbias=bias is not None)
+    for got, ref, nm in ((qd.grad, res[0], "dq"), (kd.grad, res[1], "dk"), (vd.grad, res[2], "dv")):
+        assert got.dtype == dtype
+        assert U.max_abs(got, ref) <= grad_tol(dtype, ref), nm
+    if bias is not None:
+        ref_db = O.reduce_dbias(res[3], bias, b, h)
+        assert biasd.grad.shape == bias.shape
+        assert U.max_abs(biasd.grad, ref_db) <= (2e-6 if dtype == F32 else 2e-3) * max(1.0, float(ref_db.abs().max()))
+
+    # absolute truth: fp64 autograd (the reference's tests use fp32 SDPA with atol=rtol 2.5e-3 / 8e-2)
+    q64, k64, v64 = (t.double().requires_grad_(True) for t in (q, k, v))
+    b64 = None if bias is None else bias.double().requires_grad_(True)
+    O.softmax_attention_fp64(q64, k64, v64, bias=b64, is_causal=causal).backward(dout.double())
+    lim = {F32: 2e-6, F16: 2e-3, BF16: 1.6e-2}[dtype]
+    for got, ref in ((qd.grad, q64.grad), (kd.grad, k64.grad), (vd.grad, v64.grad)):
+        assert U.max_abs(got, ref) <= lim * max(1.0, float(ref.abs().max()))
+    if bias is not None:
+        assert U.max_abs(biasd.grad, b64.grad) <= lim * max(1.0, float(b64.grad.abs().max()))
+
+
+def test_backward_is_deterministic_and_masked_rows_are_zero():
+    b, h, n, d = 1, 2, 150, 64
+    q, k, v, do = (U.seeded((b, h, n, d), F16, 70 + i).to(DEV) for i in range(4))
+    bias = torch.zeros(n, n, device=DEV)
+    bias[7, :] = float("-inf")
+    out, rm, rz = E.twopass_attention_with_state(q, k, v, bias=bias)
+    a = E.twopass_attention_backward(q, k, v, out, do, bias=bias, row_m=rm, row_z=rz)
+    c = E.twopass_attention_backward(q, k, v, out, do, bias=bias, row_m=rm, row_z=rz)
+    for x, y in zip(a, c):
+        assert torch.equal(x, y)
+        assert torch.isfinite(x).all()
+    assert float(a[0][:, :, 7].abs().max()) == 0.0
+
+
+def test_preprocess_abi():
+    from elsa_b200 import _lib
+    lib = _lib.load()
+    bh, n, d = 3, 77, 48
+    out = U.seeded((bh, n, d), BF16, 80).to(DEV)
+    dout = U.seeded((bh, n, d), BF16, 81).to(DEV)
+    rm = U.seeded((bh, n), F32, 82).to(DEV)
+    rz = (U.seeded((bh, n), F32, 83).abs() + 0.1).to(DEV)
+    rm[0, 0] = float("-inf"); rz[0, 0] = 0
+    rd = torch.empty_like(rm); lse = torch.empty_like(rm)
+    rc = lib.elsa_bwd_preprocess(out.data_ptr(), dout.data_ptr(), rm.data_ptr(), rz.data_ptr(), rd.data_ptr(),
+                                 lse.data_ptr(), 2, bh, n, d, U.stream())
+    assert rc == 0
+    ref_d, ref_l = O.bwd_preprocess(out.cpu(), dout.cpu(), rm.cpu(), rz.cpu())
+    assert U.max_abs(rd, ref_d) <= 1e-5 and U.max_abs(lse, ref_l) <= 1e-5

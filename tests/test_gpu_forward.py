@@ -1,0 +1,250 @@
+"""GPU parity of the forward path: CUDA (through the C ABI / the Python mirror) against the CPU
+oracle, the golden fixtures produced by the reference's own kernels, and fp64 math softmax.
+
+Tolerances (stated by the task): forward max_abs <= 1e-6 in fp32 and <= 5e-4 in fp16.  bf16 has
+8 mantissa bits, so its bound is one output ulp + 5e-4.  Row state: m is compared at 2e-5 absolute
+(log2 domain), z at 1e-5 relative for fp32 inputs and 2e-3 for 16-bit inputs.
+"""
+import math
+
+import pytest
+import torch
+
+import elsa_b200 as E
+from oracle import elsa_oracle as O
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+F32, F16, BF16 = torch.float32, torch.float16, torch.bfloat16
+
+
+def out_tol(dtype, ref):
+    if dtype == F32:
+        return 1e-6
+    if dtype == F16:
+        return 5e-4
+    return 5e-4 + U.ulp(BF16, float(ref.abs().max()))
+
+
+def check_state(rm, rz, rm_ref, rz_ref, dtype):
+    assert U.max_abs(rm, rm_ref) <= (2e-5 if dtype == F32 else 2e-3)
+    fin = rz_ref > 0
+    rel = ((rz.cpu()[fin] - rz_ref[fin]).abs() / rz_ref[fin]).max().item() if fin.any() else 0.0
+    assert rel <= (1e-5 if dtype == F32 else 2e-3)
+    assert torch.equal(rz.cpu() == 0, rz_ref == 0)
+
+
+FWD_GOLDEN = ["fwd_generic_f32_n96_d64", "fwd_generic_f16_n100_d32", "fwd_causal_f32_n129_d32",
+              "fwd_causal_f16_n129_d32", "fwd_swin_f32_n49_d32", "fwd_swin_f16_n49_d32",
+              "fwd_swinshift_f16_n49_d32", "fwd_generic_f32_n70_d128"]
+
+
+@pytest.mark.parametrize("name", FWD_GOLDEN)
+def test_forward_matches_reference_fixture(golden, name):
+    g = golden(name)
+    q, k, v = (g[x].to(DEV) for x in "qkv")
+    bias = g.get("bias")
+    causal = bool(g["causal"])
+    out, rm, rz = E.twopass_attention_with_state(q, k, v, bias=None if bias is None else bias.to(DEV),
+                                                 is_causal=causal, block_n=g["block_n"])
+    ref = g["out"]
+    assert U.max_abs(out, ref) <= out_tol(q.dtype, ref.float())
+    check_state(rm, rz, g["row_m"], g["row_z"], q.dtype)
+    # the fixture's per-partition summaries, where its partition width is a multiple of the kernel tile
+    if g["block_n"] % 64 == 0:
+        b, h, n, d = q.shape
+        meta = E.attention._canonical_bias(None if bias is None else bias.to(DEV), batch=b, heads=h, seq_len=n,
+                                           device=q.device)
+        m, z, s = U.phase1(q, k, v, part_width=g["block_n"], bias=meta.tensor,
+                           bias_strides=(meta.stride_b, meta.stride_h, meta.stride_q, meta.stride_k), is_causal=causal)
+        assert U.max_abs(m, g["p1_m"]) <= 2e-5
+        assert U.max_abs(z, g["p1_z"]) <= 1e-4 * float(g["p1_z"].max())
+        assert U.max_abs(s, g["p1_s"]) <= (2e-5 if q.dtype == F32 else 4e-3) * max(1.0, float(g["p1_s"].float().abs().max()))
+
+
+@pytest.mark.parametrize("name", ["fwd_d64tiled_f32_n200", "fwd_d64tiled_f16_n200", "fwd_d64tiled_f32_n700",
+                                  "fwd_d64_f32_n130", "fwd_d64_f16_n130"])
+def test_phase1_matches_reference_d64_fixture(golden, name):
+    g = golden(name)
+    q, k, v = (g[x].to(DEV) for x in "qkv")
+    m, z, s = U.phase1(q, k, v, part_width=g["block_n"])
+    f32 = q.dtype == F32
+    # fp16 fixtures carry the reference's fp16-rounded softmax scale (0.18030 vs 0.18034): the maxima
+    # differ by 2e-4 relative, which is the reference's own deviation from exact arithmetic.
+    assert U.max_abs(m, g["p1_m"]) <= (2e-5 if f32 else 6e-3)
+    assert U.max_abs(z, g["p1_z"]) <= (1e-5 if f32 else 4e-3) * float(g["p1_z"].max())
+    assert U.max_abs(s, g["p1_s"]) <= (2e-5 if f32 else 6e-3) * max(1.0, float(g["p1_s"].float().abs().max()))
+    out, rm, rz = U.merge_final(m, z, s, q.dtype, q.shape[2])
+    ref_out, ref_m, ref_z = O.final_reduce(g["p1_m"], g["p1_z"], g["p1_s"].float())
+    assert U.max_abs(out, ref_out.to(q.dtype)) <= out_tol(q.dtype, ref_out)
+
+
+CASES = [
+    # (B, H, N, D, dtype, causal, bias_kind, block_n, q_chunk)
+    (1, 2, 64, 32, F32, False, None, None, None),
+    (1, 3, 196, 64, F32, False, None, None, None),
+    (2, 4, 257, 32, F32, False, None, None, None),
+    (1, 2, 64, 32, F16, False, None, None, None),
+    (1, 3, 196, 64, F16, False, None, None, None),
+    (2, 4, 257, 32, F16, False, None, None, None),
+    (2, 3, 128, 32, F32, False, "1hnn", None, None),
+    (2, 3, 128, 32, F16, False, "1hnn", None, None),
+    (1, 2, 129, 32, F32, True, None, None, None),
+    (1, 2, 129, 32, F16, True, None, None, None),
+    (1, 2, 513, 64, F32, False, None, None, 128),
+    (1, 2, 513, 64, F16, False, None, None, 128),
+    (1, 2, 1, 64, F32, False, None, None, None),
+    (1, 1, 63, 64, F16, True, None, 64, None),
+    (1, 2, 65, 48, F32, False, None, 64, None),
+    (1, 2, 200, 96, F16, False, None, 128, None),
+    (1, 2, 130, 128, BF16, False, None, 64, None),
+    (1, 2, 1000, 64, BF16, True, None, 256, 512),
+    (2, 2, 300, 64, BF16, False, "bhnn", 128, None),
+    (3, 2, 49, 32, F16, False, "nn", 64, 49),
+    (3, 2, 49, 32, F32, False, "b1nn", 64, 49),
+    (2, 3, 77, 40, F32, True, "hnn", None, None),
+    (1, 8, 1024, 64, F32, False, None, None, None),       # BASELINE config 1
+    (1, 2, 2048, 64, F16, False, None, 2048, None),
+    (1, 2, 2048, 64, F16, False, None, 256, 1024),
+]
+
+
+def make_bias(kind, b, h, n, seed):
+    if kind is None:
+        return None
+    shape = {"nn": (n, n), "hnn": (h, n, n), "1hnn": (1, h, n, n), "b1nn": (b, 1, n, n), "bhnn": (b, h, n, n)}[kind]
+    return U.seeded(shape, F32, seed, 0.05)
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_forward_vs_oracle(case):
+    b, h, n, d, dtype, causal, bias_kind, block_n, q_chunk = case
+    q, k, v = (U.seeded((b, h, n, d), dtype, 10 + i) for i in range(3))
+    bias = make_bias(bias_kind, b, h, n, 99)
+    ref_out, ref_m, ref_z = O.twopass_forward(q, k, v, bias=bias, is_causal=causal, block_n=block_n,
+                                              q_chunk_size=q_chunk)
+    out, rm, rz = E.twopass_attention_with_state(q.to(DEV), k.to(DEV), v.to(DEV),
+                                                 bias=None if bias is None else bias.to(DEV), is_causal=causal,
+                                                 block_n=block_n, q_chunk_size=q_chunk)
+    assert out.dtype == dtype and out.shape == q.shape
+    assert U.max_abs(out, ref_out) <= out_tol(dtype, ref_out.float())
+    check_state(rm, rz, ref_m, ref_z, dtype)
+    truth = O.softmax_attention_fp64(q, k, v, bias=bias, is_causal=causal)
+    assert U.max_abs(out, truth) <= {F32: 1e-6, F16: 5e-4}.get(dtype, 5e-4 + U.ulp(BF16, float(truth.abs().max())))
+    out2 = E.twopass_attention(q.to(DEV), k.to(DEV), v.to(DEV), bias=None if bias is None else bias.to(DEV),
+                               is_causal=causal, block_n=block_n, q_chunk_size=q_chunk)
+    assert torch.equal(out2, out), "inference and training forward disagree / not deterministic"
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+@pytest.mark.parametrize("flag", ["scan_steps", "tree"])
+def test_log_depth_phase2_variants(dtype, flag):
+    """Hillis-Steele steps (causal) and Blelloch up-sweep levels (non-causal) give the same answer as
+    the one-pass merge and as the oracle's restatement of those loops."""
+    from elsa_b200 import _lib
+    from elsa_b200.attention import _forward_impl
+    causal = flag == "scan_steps"
+    b, h, n, d = 1, 2, 450, 64
+    q, k, v = (U.seeded((b, h, n, d), dtype, 20 + i).to(DEV) for i in range(3))
+    fl = _lib.FLAG_SCAN_STEPS if causal else _lib.FLAG_TREE_MERGE
+    a = _forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=dtype, part_width=64, q_chunk=0,
+                      want_state=True, flags=fl)
+    c = _forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=dtype, part_width=64, q_chunk=0,
+                      want_state=True, flags=0)
+    ref_out, ref_m, ref_z = O.twopass_forward(q.cpu(), k.cpu(), v.cpu(), is_causal=causal, block_n=64)
+    for res in (a, c):
+        assert U.max_abs(res[0], ref_out) <= out_tol(dtype, ref_out.float())
+        check_state(res[1], res[2], ref_m, ref_z, dtype)
+
+
+@pytest.mark.parametrize("sdt", [F32, F16, BF16])
+def test_phase2_kernels_vs_oracle(sdt):
+    g = torch.Generator().manual_seed(5)
+    parts, bh, rows, d = 7, 3, 37, 64
+    m = torch.randn(parts, bh, rows, generator=g) * 3
+    z = torch.rand(parts, bh, rows, generator=g) + 0.5
+    s = torch.randn(parts, bh, rows, d, generator=g)
+    dead = torch.rand(parts, bh, rows, generator=g) < 0.25
+    dead[:, 0, 0] = True                       # a row that is empty in every partition
+    m[dead] = float("-inf"); z[dead] = 0; s[dead] = 0
+    s = s.to(sdt)
+    md, zd, sd = m.to(DEV), z.to(DEV), s.to(DEV)
+    tol = 1e-5 if sdt == F32 else (2e-3 if sdt == F16 else 1.6e-2)
+
+    def cmp(got, ref):
+        assert U.max_abs(got[0], ref[0]) <= 2e-5
+        assert U.max_abs(got[1], ref[1]) <= 1e-5 * float(ref[1].max())
+        assert U.max_abs(got[2], ref[2]) <= tol * max(1.0, float(ref[2].abs().max()))
+
+    for step in (1, 2, 4):
+        cmp(U.scan_step(md, zd, sd, step), O.hillis_steele_step(m, z, s.float(), step, sdt))
+    cmp(U.upsweep(md, zd, sd), O.upsweep_level(m, z, s.float(), sdt))
+    # one-pass prefix scan == the log-depth scan (same prefixes, different association order)
+    cmp(U.prefix_scan(md, zd, sd), O.hillis_steele_scan(m, z, s.float(), sdt))
+    ref = O.final_reduce(m, z, s.float())
+    out, rm, rz = U.merge_final(md, zd, sd, F32, rows)
+    assert U.max_abs(out, ref[0]) <= tol
+    assert U.max_abs(rm, ref[1]) <= 2e-5 and U.max_abs(rz, ref[2]) <= 1e-5 * float(ref[2].max())
+    ref = O.finalize(m[3], z[3], s[3].float())
+    out, rm, rz = U.finalize(md, zd, sd, F32, rows, 3)
+    assert U.max_abs(out, ref[0]) <= 1e-6 and U.max_abs(rm, ref[1]) == 0 and U.max_abs(rz, ref[2]) == 0
+    assert float(out[0, 0].abs().max()) == 0.0
+
+
+def test_summaries_round_trip_global_memory():
+    """Structural check of the two-pass design: phase 1 leaves one (m, z, s) per (partition, row) in
+    global memory, and phase 2 alone (fed those buffers) produces the operator's output."""
+    b, h, n, d = 1, 2, 700, 64
+    q, k, v = (U.seeded((b, h, n, d), F32, 30 + i).to(DEV) for i in range(3))
+    m, z, s = U.phase1(q, k, v, part_width=256)
+    assert m.shape == (3, 2, 700) and s.shape == (3, 2, 700, 64)
+    assert torch.isfinite(m).all() and (z > 0).all() and torch.isfinite(s).all()
+    rm_, rz_, rs_ = O.phase1_generic(q.cpu().reshape(2, n, d), k.cpu().reshape(2, n, d), v.cpu().reshape(2, n, d),
+                                     block_n=256, summary_dtype=F32)
+    assert U.max_abs(m, rm_) <= 2e-5 and U.max_abs(s, rs_) <= 2e-5 * float(rs_.abs().max())
+    out, _, _ = U.merge_final(m, z, s, F32, n)
+    full = E.twopass_attention(q, k, v, block_n=256)
+    assert torch.equal(out.view(b, h, n, d), full)
+
+
+def test_masked_rows_and_empty():
+    b, h, n, d = 1, 2, 70, 32
+    q, k, v = (U.seeded((b, h, n, d), F32, 40 + i).to(DEV) for i in range(3))
+    bias = torch.zeros(n, n, device=DEV)
+    bias[5, :] = float("-inf")           # a row with no admissible key
+    bias[:, 9] = float("-inf")           # a key nobody may see
+    bias[11, 3:] = -100.0                # Swin-style large negative
+    out, rm, rz = E.twopass_attention_with_state(q, k, v, bias=bias)
+    assert torch.isfinite(out).all()
+    assert float(out[:, :, 5].abs().max()) == 0.0
+    assert (rm[:, 5] == float("-inf")).all() and (rz[:, 5] == 0).all()
+    ref = O.softmax_attention_fp64(q.cpu(), k.cpu(), v.cpu(), bias=bias.cpu())
+    assert U.max_abs(out, ref) <= 1e-6
+    e = torch.empty(1, 2, 0, 32, device=DEV)
+    assert E.twopass_attention(e, e, e).shape == (1, 2, 0, 32)
+    o, m0, z0 = E.twopass_attention_with_state(e, e, e)
+    assert m0.shape == (2, 0) and z0.shape == (2, 0)
+
+
+def test_non_contiguous_inputs_and_errors():
+    b, h, n, d = 2, 3, 50, 64
+    qkv = U.seeded((b, n, 3, h, d), F16, 50).to(DEV)
+    q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)      # the ViT drop-in's strided views
+    assert not q.is_contiguous()
+    out = E.twopass_attention(q, k, v)
+    ref = O.softmax_attention_fp64(q.cpu(), k.cpu(), v.cpu())
+    assert U.max_abs(out, ref) <= 5e-4
+    with pytest.raises(ValueError, match="paper_scan"):
+        E.twopass_attention(q, k, v, algorithm="not_available")
+    with pytest.raises(ValueError, match="phase1_warps"):
+        E.twopass_attention(q, k, v, phase1_warps=3)
+    with pytest.raises(ValueError, match="input_precision"):
+        E.twopass_attention(q, k, v, input_precision="fp8")
+    with pytest.raises(ValueError, match="head_dim"):
+        x = torch.zeros(1, 1, 4, 256, device=DEV)
+        E.twopass_attention(x, x, x)
+    with pytest.raises(ValueError, match="bias"):
+        E.twopass_attention(q, k, v, bias=torch.zeros(n, n + 1, device=DEV))
+    with pytest.raises(ValueError, match="3D bias"):
+        E.twopass_attention(q, k, v, bias=torch.zeros(2, n, n, device=DEV))
