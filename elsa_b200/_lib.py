@@ -24,6 +24,7 @@ SIGNATURES = {
     "elsa_strerror": (c_char_p, [c_int]),
     "elsa_last_cuda_error": (c_int, []),
     "elsa_kernel_launches": (c_int64, []),
+    "elsa_device_status": (c_int, [c_int]),
     "elsa_uses_tensor_cores": (c_int, [c_int] * 6),
     "elsa_phase1_fold": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_uint, _P]),

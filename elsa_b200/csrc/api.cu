@@ -32,8 +32,10 @@ struct ForwardPlan {
 };
 
 static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
-  (void)dtype; (void)head_dim; (void)n_ctx; (void)has_bias; (void)flags;
-  return false;  // no tcgen05 kernel linked into this build yet
+  // tcgen05 fold: 16-bit inputs, head dim 64, no bias; short sequences stay on the FP32-FMA kernel
+  // (one 64-row CTA per tile keeps more SMs busy than a 256-row CTA does when N is a few hundred).
+  if (flags & ELSA_FLAG_FORCE_SIMT) return false;
+  return n_ctx >= 512 && fold_tc_supported(dtype, head_dim, has_bias);
 }
 
 static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal,
@@ -44,21 +46,29 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
   const int64_t bh = static_cast<int64_t>(batch) * heads;
   if (bh > 65535) return ELSA_ERR_UNSUPPORTED;
   pl->tensor_cores = tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  pl->tile_m = pl->tensor_cores ? 128 : 64;
-  pl->tile_n = pl->tensor_cores ? 128 : 64;
+  pl->tile_m = pl->tensor_cores ? 256 : 64;   // query rows per CTA
+  pl->tile_n = pl->tensor_cores ? 128 : 64;   // keys per tile
   const int tiles_n = static_cast<int>(cdiv64(n_ctx, pl->tile_n));
   int n_parts;
   if (part_width_in > 0) {
     pl->part_width = static_cast<int>(align_up(part_width_in, pl->tile_n));
   } else {
-    // enough CTAs for a few waves over the SMs, but no more partitions than that needs:
-    // every extra partition is one more summary to write and to merge.
+    // Every extra partition is one more summary to write and merge, so take the smallest partition
+    // count whose CTA count fills the SMs in whole waves to >= 92 % (or the best seen).
     const int64_t q_ctas = cdiv64(n_ctx, pl->tile_m) * bh;
-    const int64_t target = static_cast<int64_t>(sm_count()) * (pl->tensor_cores ? 2 : 6);
-    int64_t want = std::max<int64_t>(1, cdiv64(target, q_ctas));
-    want = std::min<int64_t>(want, tiles_n);
-    const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, want));
-    pl->part_width = tiles_per_part * pl->tile_n;
+    const int64_t slots = static_cast<int64_t>(sm_count()) * (pl->tensor_cores ? 1 : 3);
+    const int max_parts = static_cast<int>(std::min<int64_t>(tiles_n, pl->tensor_cores ? 8 : 16));
+    int best = 1;
+    double best_eff = 0.0;
+    for (int cand = 1; cand <= max_parts; ++cand) {
+      const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, cand));
+      const int64_t real_parts = cdiv64(tiles_n, tiles_per_part);
+      const int64_t ctas = q_ctas * real_parts;
+      const double eff = static_cast<double>(ctas) / static_cast<double>(cdiv64(ctas, slots) * slots);
+      if (eff > best_eff + 1e-9) { best_eff = eff; best = cand; }
+      if (eff >= 0.92) { best = cand; break; }
+    }
+    pl->part_width = static_cast<int>(cdiv64(tiles_n, best)) * pl->tile_n;
   }
   n_parts = static_cast<int>(cdiv64(n_ctx, pl->part_width));
   if (n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
@@ -96,7 +106,6 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(s_buf)) return ELSA_ERR_INVALID_ARGUMENT;
   if (static_cast<int64_t>(batch) * heads > 65535 || n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
   if (q_len == 0) return ELSA_OK;
-  (void)flags;
   if (part_width % 64 != 0) return ELSA_ERR_INVALID_ARGUMENT;
   FoldParams p;
   p.q = q; p.k = k; p.v = v;
@@ -111,6 +120,7 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.round_p = (dtype == ELSA_F16 && summary_dtype != ELSA_F32) ? 1 : 0;
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) return fold_tc(p, dtype, st);
   return fold_simt(p, dtype, st);
 }
 
@@ -133,6 +143,12 @@ extern "C" const char* elsa_strerror(int status) {
 }
 
 extern "C" int elsa_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int elsa_device_status(int clear) {
+  int v = 0;
+  if (fold_tc_status(&v, clear) != ELSA_OK) return -1;
+  return v;
+}
 
 extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
 

@@ -1,0 +1,387 @@
+// Phase 1 on the 5th-generation tensor cores (tcgen05 + TMEM + TMA): the per-K-partition
+// (m, z, s) fold for fp16 / bf16 inputs with head dim 64, causal or not.
+//
+// One CTA (1 per SM: 160 KB of shared memory, 384 TMEM columns) owns TWO 128-row query tiles of one
+// (batch*head) and one K partition, walked in 128-key tiles:
+//
+//   warp 8      TMA producer   Q tiles once; K and V tiles into a 4-stage ring (128-byte swizzle)
+//   warp 9      MMA issuer     S_t = Q_t K^T   (4 x tcgen05.mma 128x128x16, both operands in smem)
+//                              O_t += P_t V    (8 x tcgen05.mma 128x64x16, P from TMEM, V MN-major)
+//   warps 0-3   fold of tile 0 one thread per query row: S row from TMEM, running max, exp2, row sum,
+//   warps 4-7   fold of tile 1 P (16-bit) written back over S in TMEM, exp-rescale of O when the max moved
+//
+// The two tiles ping-pong on the tensor pipe: while one tile's rows are in the exp2 phase the
+// other tile's MMAs run.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384); P_t
+// overlays the first 64 columns of S_t.
+//
+// Exp-rescale merge: the fold keeps a reference max m_ref per row and only moves it (rescaling z
+// and the O accumulator in TMEM) when the tile max exceeds it by more than 2^8; the true running
+// max is tracked separately and the summary is renormalised to it in the epilogue, so the stored
+// (m, z, s) is the same monoid element the FP32-FMA kernel produces.
+#include <type_traits>
+
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace elsa {
+
+using namespace tc;
+
+static __device__ int g_fold_status = 0;
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kTileBytes = 128 * 64 * 2;                          // one 128 x 64 16-bit tile
+constexpr int kFoldSmem = (2 + 2 * kStages) * kTileBytes + 1024;  // + alignment slack
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;
+
+enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6 };
+
+struct FoldTcParams {
+  float* m; float* z; void* s;
+  int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
+  float scale_log2;
+};
+
+template <typename TS>
+__device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64]) {
+  if constexpr (sizeof(TS) == 4) {
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; i += 8) {
+      uint4 t;
+      t.x = pack2<TS>(v[i], v[i + 1]); t.y = pack2<TS>(v[i + 2], v[i + 3]);
+      t.z = pack2<TS>(v[i + 4], v[i + 5]); t.w = pack2<TS>(v[i + 6], v[i + 7]);
+      *reinterpret_cast<uint4*>(dst + i) = t;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const FoldTcParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 6];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.z, part = blockIdx.y;
+  const int q0 = prm.q_start + blockIdx.x * 256;           // first query row of tile 0
+  const int q_end = prm.q_start + prm.q_len;
+  const int k_begin = part * prm.part_width;
+  const int k_end = min(prm.n_ctx, k_begin + prm.part_width);
+
+  // number of 128-key tiles each query tile has to visit
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt0 = q0 + t * 128;
+    int ke = k_end;
+    if (prm.is_causal) ke = min(ke, min(qt0 + 128, q_end));  // keys above the tile's last row are never admissible
+    n_t[t] = (qt0 < q_end && ke > k_begin) ? (ke - k_begin + 127) / 128 : 0;
+  }
+  const int n_max = max(n_t[0], n_t[1]);
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ[2] = {smem_base, smem_base + kTileBytes};
+  auto sK = [&](int st) { return smem_base + (2 + 2 * st) * kTileBytes; };
+  auto sV = [&](int st) { return smem_base + (3 + 2 * st) * kTileBytes; };
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_q = bar0;
+  auto bar_kv_full = [&](int st) { return bar0 + 8 * (1 + st); };
+  auto bar_kv_free = [&](int st) { return bar0 + 8 * (1 + kStages + st); };
+  auto bar_s = [&](int t) { return bar0 + 8 * (1 + 2 * kStages + t); };
+  auto bar_p = [&](int t) { return bar0 + 8 * (3 + 2 * kStages + t); };
+  const uint32_t bar_o = bar0 + 8 * (5 + 2 * kStages);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_q, 1);
+    for (int st = 0; st < kStages; ++st) { mbar_init(bar_kv_full(st), 1); mbar_init(bar_kv_free(st), 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(bar_s(t), 1); mbar_init(bar_p(t), 128); }
+    mbar_init(bar_o, 1);
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO[2] = {tmem_base + 256, tmem_base + 320};
+
+  if (n_max > 0) {
+    if (warp == 8) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+        mbar_arrive_expect_tx(bar_q, 2 * kTileBytes);
+        tma_load_3d(sQ[0], &tmap_q, bar_q, 0, q0, bh);
+        tma_load_3d(sQ[1], &tmap_q, bar_q, 0, q0 + 128, bh);
+        for (int j = 0; j < n_max; ++j) {
+          const int st = j % kStages;
+          if (j >= kStages && !mbar_wait(bar_kv_free(st), ((j / kStages) - 1) & 1, &abort_flag, &g_fold_status, BAR_KV_FREE)) break;
+          mbar_arrive_expect_tx(bar_kv_full(st), 2 * kTileBytes);
+          tma_load_3d(sK(st), &tmap_k, bar_kv_full(st), 0, k_begin + j * 128, bh);
+          tma_load_3d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, bh);
+        }
+      }
+    } else if (warp == 9) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+        constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+        constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // S = Q K^T : A, B K-major
+        constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // O += P V  : A in TMEM, B (V) MN-major
+        auto issue_s = [&](int t, int st) {
+          const uint64_t a = make_sdesc(sQ[t], 16, 1024), b = make_sdesc(sK(st), 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) mma_ss(tS[t], a + 2 * kk, b + 2 * kk, idesc_s, kk > 0);
+          mma_commit(bar_s(t));
+        };
+        auto issue_pv = [&](int t, int st, int j) {
+          const uint64_t b = make_sdesc(sV(st), 128 * 128, 1024);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) mma_ts(tO[t], tS[t] + 8 * kk, b + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        };
+        bool ok = mbar_wait(bar_q, 0, &abort_flag, &g_fold_status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, &g_fold_status, BAR_KV_FULL);
+        if (ok) {
+          tc_fence_after();
+          for (int t = 0; t < 2; ++t)
+            if (n_t[t] > 0) issue_s(t, 0);
+        }
+        for (int j = 0; ok && j < n_max; ++j) {
+          const int st = j % kStages;
+          for (int t = 0; ok && t < 2; ++t) {
+            if (j < n_t[t]) {
+              ok = mbar_wait(bar_p(t), j & 1, &abort_flag, &g_fold_status, BAR_P);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv(t, st, j);
+            }
+            if (t == 1) mma_commit(bar_kv_free(st));   // K(j), V(j) are no longer read once these MMAs retire
+            if (j + 1 < n_t[t]) {
+              const int sn = (j + 1) % kStages;
+              ok = mbar_wait(bar_kv_full(sn), ((j + 1) / kStages) & 1, &abort_flag, &g_fold_status, BAR_KV_FULL);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s(t, sn);
+            }
+          }
+        }
+        if (ok) mma_commit(bar_o);
+      }
+    }
+  }
+
+  if (warp < 8) {
+    // ---------------- fold warps: one thread per query row ----------------
+    const int t = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;                 // row within the tile == TMEM lane
+    const int qi = q0 + t * 128 + row;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const float c = prm.scale_log2;
+    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;
+    bool alive = true;
+
+    for (int j = 0; j < n_t[t]; ++j) {
+      if (!mbar_wait(bar_s(t), j & 1, &abort_flag, &g_fold_status, BAR_S)) { alive = false; break; }
+      tc_fence_after();
+      float sv[128];
+#pragma unroll
+      for (int cchunk = 0; cchunk < 4; ++cchunk) {
+        uint32_t r[32];
+        tmem_ld32(tS[t] + lane_off + 32 * cchunk, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[32 * cchunk + i] = __uint_as_float(r[i]);
+      }
+      tmem_wait_ld();
+      const int k0 = k_begin + j * 128;
+      const bool tail = k0 + 128 > k_end;
+      const bool diag = prm.is_causal && (k0 + 127 > q0 + t * 128);
+      if (tail || diag) {
+        const int lim = prm.is_causal ? min(k_end - 1, qi) : k_end - 1;   // last admissible key of this row
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > lim) sv[i] = -CUDART_INF_F;
+      }
+      float tmax = sv[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) tmax = fmaxf(tmax, sv[i]);
+      tmax *= c;
+      m_true = fmaxf(m_true, tmax);
+      const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
+      if (__any_sync(0xffffffffu, move)) {
+        const float m_new = fmaxf(m_ref, tmax);
+        const float alpha = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_ref - m_new);
+        zsum *= alpha;
+        if (j > 0) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld32(tO[t] + lane_off + 32 * h, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(tO[t] + lane_off + 32 * h, r);
+          }
+        }
+        m_ref = m_new;
+      }
+      const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+      float psum = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(sv[64 * h + 2 * i], c, -m_use));
+          const float p1 = fast_exp2(fmaf(sv[64 * h + 2 * i + 1], c, -m_use));
+          psum += p0 + p1;
+          pk[i] = pack2<T>(p0, p1);
+        }
+        tmem_st32(tS[t] + lane_off + 32 * h, pk);
+      }
+      zsum += psum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p(t));
+    }
+
+    // epilogue: renormalise to the true max and write the summary row
+    const int r_chunk = blockIdx.x * 256 + t * 128 + row;   // row within the query chunk
+    const bool row_ok = r_chunk < prm.q_len;
+    if (n_t[t] > 0) {
+      if (alive && !mbar_wait(bar_o, 0, &abort_flag, &g_fold_status, BAR_O)) alive = false;
+      if (alive) {
+        tc_fence_after();
+        float ov[64];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(tO[t] + lane_off + 32 * h, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[32 * h + i] = __uint_as_float(r[i]);
+        }
+        tmem_wait_ld();
+        const float f = (m_true == -CUDART_INF_F) ? 0.f : fast_exp2(m_ref - m_true);
+        const float zo = zsum * f;
+        if (row_ok) {
+          const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
+          prm.m[ro] = zo > 0.f ? m_true : -CUDART_INF_F;
+          prm.z[ro] = zo;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) ov[i] = zo > 0.f ? ov[i] * f : 0.f;
+          if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
+          else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
+          else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+        }
+      }
+    } else if (row_ok) {
+      // nothing admissible in this partition for this tile: the identity
+      const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
+      prm.m[ro] = -CUDART_INF_F;
+      prm.z[ro] = 0.f;
+      float ov[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) ov[i] = 0.f;
+      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
+      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
+      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+// ---- host ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int64_t n_mats, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return ELSA_ERR_UNSUPPORTED;
+  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(n_mats)};
+  const cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(n_rows) * 128};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == ELSA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return ELSA_ERR_CUDA;
+  }
+  return ELSA_OK;
+}
+
+bool fold_tc_supported(int dtype, int head_dim, bool has_bias) {
+  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim == 64 && !has_bias && encode_tiled_fn() != nullptr;
+}
+
+int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
+  if (!fold_tc_supported(dtype, p.head_dim, p.bias != nullptr) || p.part_width % 128 != 0) return ELSA_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
+  FoldTcParams prm;
+  prm.m = p.m; prm.z = p.z; prm.s = p.s;
+  prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
+  prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
+  prm.scale_log2 = p.scale_log2;
+  dim3 grid(static_cast<unsigned>((p.q_len + 255) / 256), static_cast<unsigned>(p.n_parts), static_cast<unsigned>(p.bh));
+  if (dtype == ELSA_F16) {
+    rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tc_kernel<__half>), kFoldSmem);
+    if (rc != ELSA_OK) return rc;
+    fold_tc_kernel<__half><<<grid, kThreads, kFoldSmem, st>>>(mq, mk, mv, prm);
+  } else {
+    rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tc_kernel<__nv_bfloat16>), kFoldSmem);
+    if (rc != ELSA_OK) return rc;
+    fold_tc_kernel<__nv_bfloat16><<<grid, kThreads, kFoldSmem, st>>>(mq, mk, mv, prm);
+  }
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+int fold_tc_status(int* status_out, int clear) {
+  int v = 0;
+  ELSA_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_fold_status, sizeof(int)));
+  if (clear && v != 0) {
+    int zero = 0;
+    ELSA_CUDA_CHECK(cudaMemcpyToSymbol(g_fold_status, &zero, sizeof(int)));
+  }
+  *status_out = v;
+  return ELSA_OK;
+}
+
+}  // namespace elsa

@@ -1,6 +1,10 @@
 // Internal interface between the C-ABI layer (api.cu) and the kernel translation units.
 #pragma once
 
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "common.cuh"
 
 namespace elsa {
@@ -23,6 +27,24 @@ struct BwdParams {
   int heads, n_ctx, head_dim, bh, is_causal;
   float scale, scale_log2;
 };
+
+// opt-in to > 48 KB dynamic shared memory once per (function, device)
+inline int ensure_dynamic_smem(const void* func, size_t bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  ELSA_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({func, dev})) return ELSA_OK;
+  ELSA_CUDA_CHECK(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+  done.insert({func, dev});
+  return ELSA_OK;
+}
+
+// tcgen05 kernels (fold_tc.cu)
+bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
+int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
+int fold_tc_status(int* status_out, int clear);
 
 // FP32-FMA kernels (fold_simt.cu, bwd_simt.cu)
 int fold_simt(const FoldParams& p, int dtype, cudaStream_t st);

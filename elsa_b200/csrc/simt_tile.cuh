@@ -3,26 +3,9 @@
 // tx+16*{0..3}, in an output tile [64][DP] it owns the columns given by tile_col().
 #pragma once
 
-#include <mutex>
-#include <set>
-#include <utility>
-
-#include "common.cuh"
+#include "kernels.cuh"
 
 namespace elsa {
-
-// opt-in to > 48 KB dynamic shared memory once per (function, device)
-inline int ensure_dynamic_smem(const void* func, size_t bytes) {
-  static std::mutex mu;
-  static std::set<std::pair<const void*, int>> done;
-  int dev = 0;
-  ELSA_CUDA_CHECK(cudaGetDevice(&dev));
-  std::lock_guard<std::mutex> lock(mu);
-  if (done.count({func, dev})) return ELSA_OK;
-  ELSA_CUDA_CHECK(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
-  done.insert({func, dev});
-  return ELSA_OK;
-}
 
 // global [rows][D] of T  ->  shared fp32 [64][ld], zero-filled beyond rows_valid and beyond D
 template <typename T, int DP>

@@ -51,6 +51,10 @@ int elsa_abi_version(void);
 const char* elsa_strerror(int status);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread */
 int elsa_last_cuda_error(void);
+/* Status word written by bounded device-side waits of the tensor-core kernels: 0 = no wait ever
+ * gave up; otherwise (1 << 8) | id of the barrier.  Synchronous (copies one int from the device);
+ * clear != 0 resets it.  Returns -1 when the copy itself fails. */
+int elsa_device_status(int clear);
 /* number of kernels this library has launched in this process so far (all threads, all streams) */
 int64_t elsa_kernel_launches(void);
 /* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run */

@@ -102,3 +102,20 @@ def ulp(dtype, magnitude=1.0):
     """spacing of `dtype` just below `magnitude`"""
     bits = {torch.float16: 10, torch.bfloat16: 7, torch.float32: 23}[dtype]
     return 2.0 ** (math.floor(math.log2(max(magnitude, 1e-30))) - bits)
+
+
+def out_close(got, ref, dtype):
+    """Forward-output criterion, elementwise: fp32 <= 1e-6; fp16 <= 5e-4 or, where |ref| >= 1 so that
+    one fp16 spacing already exceeds 5e-4, one spacing of the reference value; bf16 <= 5e-4 + one bf16
+    spacing of the reference value.  Returns the worst ratio err/limit (<= 1 passes)."""
+    a = got.detach().double().cpu()
+    b = ref.detach().double().cpu()
+    assert torch.isfinite(a).all() and torch.isfinite(b).all()
+    err = (a - b).abs()
+    if dtype == torch.float32:
+        lim = torch.full_like(err, 1e-6)
+    else:
+        bits = 10 if dtype == torch.float16 else 7
+        spacing = torch.exp2(torch.floor(torch.log2(b.abs().clamp_min(1e-30))) - bits)
+        lim = torch.maximum(torch.full_like(err, 5e-4), spacing) if dtype == torch.float16 else 5e-4 + spacing
+    return (err / lim).max().item()
