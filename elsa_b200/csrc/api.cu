@@ -146,14 +146,18 @@ extern "C" int elsa_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int elsa_device_status(int clear) {
   int v = 0;
-  if (fold_tc_status(&v, clear) != ELSA_OK) return -1;
-  return v;
+  int w = 0;
+  if (fold_tc_status(&v, clear) != ELSA_OK || bwd_tc_status(&w, clear) != ELSA_OK) return -1;
+  return v != 0 ? v : w;
 }
 
 extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
 
+static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
+
 extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
-  (void)is_causal; (void)backward;
+  (void)is_causal;
+  if (backward) return tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
   return tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
 }
 
@@ -257,14 +261,20 @@ extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v,
 }
 
 // ---- backward -------------------------------------------------------------------------------
+static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  if (flags & ELSA_FLAG_FORCE_SIMT) return false;
+  return n_ctx >= 512 && bwd_tc_supported(dtype, head_dim, has_bias);
+}
+
 static int64_t bwd_state_bytes(int batch, int heads, int n_ctx) {
   return align_up(static_cast<int64_t>(batch) * heads * n_ctx * 4, 256);
 }
 
 extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                                  int has_bias, int is_causal, unsigned flags) {
-  (void)has_bias; (void)is_causal; (void)flags;
+  (void)is_causal;
   if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128) return -1;
+  if (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags)) return bwd_tc_workspace_bytes(batch * heads, n_ctx);
   return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
 }
 
@@ -288,7 +298,9 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   char* ws = static_cast<char*>(workspace);
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
-  int rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
+  const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  int rc = ELSA_OK;
+  if (!use_tc) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
   if (rc != ELSA_OK) return rc;
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.dout = dout;
@@ -300,6 +312,7 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.bh = batch * heads; p.is_causal = is_causal ? 1 : 0;
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  if (use_tc) return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }
 

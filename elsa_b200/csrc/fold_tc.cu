@@ -194,7 +194,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
-      if (!mbar_wait(bar_s(t), j & 1, &abort_flag, &g_fold_status, BAR_S)) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(t), j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -261,7 +261,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int r_chunk = blockIdx.x * 256 + t * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     if (n_t[t] > 0) {
-      if (alive && !mbar_wait(bar_o, 0, &abort_flag, &g_fold_status, BAR_O)) alive = false;
+      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, &g_fold_status, BAR_O))) alive = false;
       if (alive) {
         tc_fence_after();
         float ov[64];
