@@ -35,6 +35,7 @@ WORKLOADS = {
     "causal_bf16": (1, 8, 16384, 64, "bfloat16", True),
     "fp32_4k": (1, 8, 4096, 64, "float32", False),
     "small": (1, 8, 2048, 64, "float16", False),
+    "prof4k": (1, 8, 4096, 64, "float16", False),      # ncu capture size: same kernels, a few hundred MB on the device
 }
 
 
@@ -55,7 +56,7 @@ def peaks():
 
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -72,19 +73,26 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")][1:]))
 
-    def stop(self):
+    def mark(self):
+        """host time stamp; samples between two marks are the ones taken under load"""
+        return time.time()
+
+    def stop(self, t0=None, t1=None):
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
-        sm = sorted(float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit())
-        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        rows = [r for (ts, r) in self.rows if (t0 is None or ts >= t0) and (t1 is None or ts <= t1 + 0.15)]
+        if not rows:
+            rows = [r for (_, r) in self.rows]
+        sm = sorted(float(r[1]) for r in rows if len(r) > 8 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
         reasons = set()
-        for r in self.rows:
+        for r in rows:
             if len(r) > 8:
                 for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
                     if val.lower().startswith("active"):
@@ -210,15 +218,22 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    # keep the GPU busy for at least ~0.5 s before the timed region so that the clock samples (100 ms
+    # period) taken during it describe a loaded, settled GPU; these extra steps are untimed warm-up
+    t_busy = time.time()
+    while time.time() - t_busy < 0.5:
+        step(0)
+        torch.cuda.synchronize()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     l0 = lib.elsa_kernel_launches()
     barrier()
+    mark0 = sampler.mark()
     t_start = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
     t_start.record()
@@ -230,7 +245,8 @@ def main():
     total_ms = t_start.elapsed_time(t_end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    mark1 = sampler.mark()
+    clock_marks = (mark0, mark1)
     if dist is not None:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -270,6 +286,11 @@ def main():
         e2e = {"value": world * (fwd_f + bwd_f) / (e_ms / k_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": k_e2e}
 
+    clocks = None
+    if rank == 0:
+        # the e2e region that follows is load of the same kind: widen the window to it when the timed region
+        # was shorter than two sampling periods
+        clocks = sampler.stop(clock_marks[0], clock_marks[1] if (clock_marks[1] - clock_marks[0]) > 0.25 else None)
     if rank == 0:
         pk = peaks()
         uses_tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(dtype), d, n, 0, int(causal), 1))
