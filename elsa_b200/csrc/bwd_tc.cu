@@ -2,26 +2,36 @@
 // fp16 / bf16 inputs, head dim 64, causal or not, no bias.  Five contractions per (key tile, query
 // tile) pair -- the algorithmic minimum -- all as tcgen05.mma with TMEM accumulators:
 //
-//   S^T  = K Q^T          [128 keys x 128 queries]   smem x smem          -> TMEM tS
-//   dP^T = V dO^T         [128 x 128]                smem x smem          -> TMEM tdP
-//   dV  += P^T dO         [128 keys x 64]            TMEM (P^T over tS)  x smem (dO, MN-major)
-//   dK  += dS^T Q         [128 keys x 64]            TMEM (dS^T over tdP) x smem (Q, MN-major)
-//   dQ   = dS K           [128 queries x 64]         smem (dS^T, MN-major A) x smem (K, MN-major)
+//   S^T  = K Q^T          [128 keys x 128 queries]   smem x smem            -> TMEM
+//   dP^T = V dO^T         [128 x 128]                smem x smem            -> TMEM
+//   dV  += P^T dO         [128 keys x 64]            TMEM (P^T over S^T)   x smem (dO, MN-major)
+//   dK  += dS^T Q         [128 keys x 64]            TMEM (dS^T over dP^T) x smem (Q, MN-major)
+//   dQ   = dS K           [128 queries x 64]         smem (dS^T, M-major A) x smem (K, MN-major)
 //
-// One CTA (1 per SM) owns one 128-key tile of one (batch*head) and streams the query tiles.  Working
-// on the transposed score tile puts one KEY per TMEM lane, so P^T and dS^T come out in exactly the
-// layout the dV / dK contractions take as their TMEM A operand; dS^T is also written to shared
+// One CTA (1 per SM, 512 threads) owns one 128-key tile of one (batch*head) and streams the query
+// tiles.  Working on the transposed score tile puts one KEY per TMEM lane, so P^T and dS^T come out
+// in the layout the dV / dK contractions take as their TMEM A operand; dS^T also goes to shared
 // memory (16-bit, 128-byte swizzle) where the dQ contraction reads it as an M-major A operand.
-// dK and dV stay in TMEM for the whole CTA.  dQ of each pair is added into an fp32 accumulator in
-// global memory with vector reductions (red.global.add.v4.f32); a last pass scales and rounds it.
+// dK and dV stay in TMEM for the whole CTA; dQ of each pair is added into an fp32 accumulator in
+// global memory by a TMA reduce-add (cp.reduce.async.bulk.tensor) of the staged tile, and a last
+// pass scales and rounds it.
 //
-//   warp 8      TMA producer   K, V once; Q_i, dO_i, LSE_i, D_i into a 2-stage ring
-//   warp 9      MMA issuer
-//   warps 0-7   256 threads: thread = (key row, half of the 128 query columns): exp2, dS, packing,
-//               then (query row, half of the 64 dQ columns) for the reductions
+// Each 128-query tile is processed as two 64-query halves that are half an iteration apart: while
+// the warps of half a are in their exp2 / dS phase the tensor pipe runs the contractions of half b
+// and vice versa.
 //
-// LSE and D are read from a padded [BH][ceil(N/128)*128] layout whose padding holds LSE = +inf,
-// D = 0, so that query rows beyond N produce P = 0 without a branch.
+//   warps 0-3   half a (query columns 0-63): one thread per key row: exp2, dS, packing
+//   warps 4-7   half b (query columns 64-127)
+//   warps 8-11  dQ drain: one thread per query row: TMEM -> registers -> swizzled smem -> TMA reduce-add
+//   warp 12     TMA producer: K, V once; Q_i, dO_i, -LSE_i, -D_i into a 2-stage ring
+//   warp 13     MMA issuer
+//   (register budget re-balanced with setmaxnreg: 184 / 184 / 104 / 40 per thread)
+//
+// TMEM columns: S^T_a [0,64) S^T_b [64,128) dP^T_a [128,192) dP^T_b [192,256) dV [256,320)
+// dK [320,384) dQ [384,448).  The 16-bit P^T_h / dS^T_h overlay the first 32 columns of S^T_h / dP^T_h.
+//
+// -LSE and -D are read from a padded [BH][ceil(N/128)*128] layout whose padding holds -LSE = -inf,
+// -D = 0, so that query rows beyond N produce P = 0 without a branch.
 #include <type_traits>
 
 #include "kernels.cuh"
@@ -33,23 +43,34 @@ using namespace tc;
 
 static __device__ int g_bwd_status = 0;
 
+// Optional per-phase timestamps of CTA (0,0) for tuning builds (-DELSA_TRACE); compiled out otherwise.
+#ifdef ELSA_TRACE
+__device__ long long g_bwd_trace[5][256][4];
+#define ELSA_TR(role, it, slot)                                                              \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 256) g_bwd_trace[role][it][slot] = clock64(); \
+  } while (0)
+#else
+#define ELSA_TR(role, it, slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kQStages = 2;
 constexpr int kTile = 128 * 64 * 2;     // 16 KB: one 128 x 64 16-bit tile
 constexpr int kVecBytes = 128 * 4;      // 128 fp32 row statistics
-// smem: K, V | ring of (Q, dO, LSE, D) | dS^T (two 64-query blocks)
+// smem: K, V | ring of (Q, dO, -LSE, -D) | dS^T double buffer (each two 64-query blocks) | dQ staging (fp32, 2 x 16 KB)
 constexpr int kStageBytes = 2 * kTile + 2 * kVecBytes;
-constexpr int kBwdSmem = 2 * kTile + kQStages * kStageBytes + 2 * kTile + 1024;
-constexpr int kThreads = 320;
+constexpr int kBwdSmem = 2 * kTile + kQStages * kStageBytes + 4 * kTile + 2 * kTile + 1024;
+constexpr int kThreads = 512;
 constexpr uint32_t kTmemCols = 512;
 
 enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS = 15, BAR_DQ_FULL = 16, BAR_DQ_FREE = 17, BAR_DONE = 18 };
 
 struct BwdTcParams {
-  const float* lse_pad; const float* d_pad;   // [BH][n_pad]
-  float* dq_acc;                              // [BH][N][64] fp32, zeroed by the caller
-  void* dk; void* dv;                         // [BH][N][64] T
+  const float* nlse_pad; const float* nd_pad;  // [BH][n_pad]: -LSE, -D
+  float* dq_acc;                               // [BH][N][64] fp32, zeroed by the caller
+  void* dk; void* dv;                          // [BH][N][64] T
   int n_ctx, n_pad, bh, is_causal;
   float scale, scale_log2;
 };
@@ -63,13 +84,23 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&w)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]),
+        "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+}
+
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-              const BwdTcParams prm) {
+              const __grid_constant__ CUtensorMap tmap_dq, const BwdTcParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kQStages + 6];
+  __shared__ __align__(8) uint64_t bars[2 * kQStages + 9];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -78,37 +109,39 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   const int k0 = blockIdx.x * 128;                  // first key row of this CTA
   const int N = prm.n_ctx;
   const int n_qtiles = (N + 127) / 128;
-  const int it_begin = prm.is_causal ? blockIdx.x : 0;   // query tiles below the diagonal tile see none of these keys
+  const int it_begin = prm.is_causal ? blockIdx.x : 0;   // query tiles above the diagonal tile see none of these keys
   const int n_it = n_qtiles - it_begin;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sK = smem_base, sV = smem_base + kTile;
   auto sQ = [&](int st) { return smem_base + 2 * kTile + st * kStageBytes; };
   auto sDO = [&](int st) { return sQ(st) + kTile; };
-  auto sLSE = [&](int st) { return sQ(st) + 2 * kTile; };
-  auto sD = [&](int st) { return sQ(st) + 2 * kTile + kVecBytes; };
-  const uint32_t sDS = smem_base + 2 * kTile + kQStages * kStageBytes;   // 2 x 16 KB
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));        // generic pointer to smem_base
+  auto sNL = [&](int st) { return sQ(st) + 2 * kTile; };
+  auto sND = [&](int st) { return sQ(st) + 2 * kTile + kVecBytes; };
+  const uint32_t sDS0 = smem_base + 2 * kTile + kQStages * kStageBytes;   // buffer b at + b * 2 * kTile
+  const uint32_t sDQ = sDS0 + 4 * kTile;                                   // dQ staging: two [128][32] fp32 blocks
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));         // generic pointer to smem_base
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_kv = bar0;
   auto bar_q_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_q_free = [&](int st) { return bar0 + 8 * (1 + kQStages + st); };
-  const uint32_t bar_sp = bar0 + 8 * (1 + 2 * kQStages);
-  const uint32_t bar_pds = bar_sp + 8, bar_dq_full = bar_sp + 16, bar_dq_free = bar_sp + 24, bar_done = bar_sp + 32;
+  const uint32_t barx = bar0 + 8 * (1 + 2 * kQStages);
+  auto bar_sp = [&](int h) { return barx + 8 * h; };
+  auto bar_pds = [&](int h) { return barx + 16 + 8 * h; };
+  const uint32_t bar_dq_full = barx + 32, bar_dq_free = barx + 40, bar_done = barx + 48;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_kv, 1);
     for (int st = 0; st < kQStages; ++st) { mbar_init(bar_q_full(st), 1); mbar_init(bar_q_free(st), 1); }
-    mbar_init(bar_sp, 1);
-    mbar_init(bar_pds, 256);
+    for (int h = 0; h < 2; ++h) { mbar_init(bar_sp(h), 1); mbar_init(bar_pds(h), 128); }
     mbar_init(bar_dq_full, 1);
-    mbar_init(bar_dq_free, 256);
+    mbar_init(bar_dq_free, 128);
     mbar_init(bar_done, 1);
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == 12) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -116,11 +149,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 320, tdQ = tmem_base + 384;
+  const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 320, tdQ = tmem_base + 384;
+  auto tS = [&](int h) { return tmem_base + 64 * h; };
+  auto tdP = [&](int h) { return tmem_base + 128 + 64 * h; };
 
-  if (warp == 8) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
+  if (warp >= 12) {
+    reg_dec<40>();
+    if (warp == 12 && lane == 0) {
+      // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       mbar_arrive_expect_tx(bar_kv, 2 * kTile);
       tma_load_3d(sK, &tmap_k, bar_kv, 0, k0, bh);
@@ -132,152 +168,206 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mbar_arrive_expect_tx(bar_q_full(st), kStageBytes);
         tma_load_3d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, bh);
         tma_load_3d(sDO(st), &tmap_do, bar_q_full(st), 0, qrow, bh);
-        bulk_load_1d(sLSE(st), prm.lse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
-        bulk_load_1d(sD(st), prm.d_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
+        bulk_load_1d(sNL(st), prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
+        bulk_load_1d(sND(st), prm.nd_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
       }
-    }
-  } else if (warp == 9) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    } else if (warp == 13 && lane == 0) {
+      // ---------------- MMA issuer ----------------
       constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-      constexpr uint32_t idesc_st = make_idesc(fmt, 0, 0, 128, 128);  // S^T, dP^T: A, B K-major
+      constexpr uint32_t idesc_st = make_idesc(fmt, 0, 0, 128, 64);   // S^T_h, dP^T_h: A, B K-major, N = 64 queries
       constexpr uint32_t idesc_kv = make_idesc(fmt, 0, 1, 128, 64);   // dV, dK: A in TMEM, B MN-major
       constexpr uint32_t idesc_dq = make_idesc(fmt, 1, 1, 128, 64);   // dQ: A (dS^T) M-major, B (K) MN-major
-      bool ok = mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV);
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % kQStages;
-        ok = mbar_wait(bar_q_full(st), (it / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL);
-        if (!ok) break;
+      const uint64_t ak = make_sdesc(sK, 16, 1024), av = make_sdesc(sV, 16, 1024);
+      const uint64_t bk_mn = make_sdesc(sK, 128 * 128, 1024);
+      // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for the 64 queries of half h of ring stage st
+      auto issue_sp = [&](int st, int h) {
+        const uint64_t bq = make_sdesc(sQ(st) + h * 8192, 16, 1024), bdo = make_sdesc(sDO(st) + h * 8192, 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ss(tS(h), ak + 2 * kk, bq + 2 * kk, idesc_st, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ss(tdP(h), av + 2 * kk, bdo + 2 * kk, idesc_st, kk > 0);
+        mma_commit(bar_sp(h));
+      };
+      // dV += P^T_h dO_h, dK += dS^T_h Q_h (contraction over the 64 queries of half h)
+      auto issue_dkv = [&](int st, int h, bool first) {
+        const uint64_t bdo = make_sdesc(sDO(st) + h * 8192, 128 * 128, 1024), bq = make_sdesc(sQ(st) + h * 8192, 128 * 128, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ts(tdV, tS(h) + 8 * kk, bdo + 128 * kk, idesc_kv, (first && kk == 0) ? 0u : 1u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_ts(tdK, tdP(h) + 8 * kk, bq + 128 * kk, idesc_kv, (first && kk == 0) ? 0u : 1u);
+      };
+      bool ok = mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV) &&
+                (n_it == 0 || mbar_wait(bar_q_full(0), 0, &abort_flag, &g_bwd_status, BAR_Q_FULL));
+      if (ok && n_it > 0) {
         tc_fence_after();
-        {
-          const uint64_t ak = make_sdesc(sK, 16, 1024), av = make_sdesc(sV, 16, 1024);
-          const uint64_t bq = make_sdesc(sQ(st), 16, 1024), bdo = make_sdesc(sDO(st), 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_ss(tS, ak + 2 * kk, bq + 2 * kk, idesc_st, kk > 0);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_ss(tdP, av + 2 * kk, bdo + 2 * kk, idesc_st, kk > 0);
-          mma_commit(bar_sp);
+        issue_sp(0, 0);
+        issue_sp(0, 1);
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % kQStages, sn = (it + 1) % kQStages;
+        const bool more = it + 1 < n_it;
+        // half a of this iteration, then S/dP of half a of the next one
+        ok = mbar_wait(bar_pds(0), it & 1, &abort_flag, &g_bwd_status, BAR_PDS);
+        if (!ok) break;
+        ELSA_TR(0, it, 0);
+        tc_fence_after();
+        issue_dkv(st, 0, it == 0);
+        ELSA_TR(4, it, 0);
+        if (more) {
+          ok = mbar_wait(bar_q_full(sn), ((it + 1) / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sp(sn, 0);
         }
-        ok = mbar_wait(bar_pds, it & 1, &abort_flag, &g_bwd_status, BAR_PDS);
+        ELSA_TR(0, it, 1);
+        // half b, then dQ of the whole tile, then S/dP of half b of the next one
+        ok = mbar_wait(bar_pds(1), it & 1, &abort_flag, &g_bwd_status, BAR_PDS);
         if (ok && it > 0) ok = mbar_wait(bar_dq_free, (it - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE);
         if (!ok) break;
+        ELSA_TR(0, it, 2);
         tc_fence_after();
+        issue_dkv(st, 1, false);
+        ELSA_TR(4, it, 1);
         {
-          const uint64_t bdo = make_sdesc(sDO(st), 128 * 128, 1024), bq = make_sdesc(sQ(st), 128 * 128, 1024);
-          const uint64_t ads = make_sdesc(sDS, 128 * 128, 1024), bk = make_sdesc(sK, 128 * 128, 1024);
+          const uint64_t ads = make_sdesc(sDS0 + (it & 1) * 2 * kTile, 128 * 128, 1024);
 #pragma unroll
-          // 16 queries per step; queries 0-63 sit in columns [0,32), queries 64-127 in columns [64,96)
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tdV, tS + (kk < 4 ? 8 * kk : 32 + 8 * kk), bdo + 128 * kk, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tdK, tdP + (kk < 4 ? 8 * kk : 32 + 8 * kk), bq + 128 * kk, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) mma_ss(tdQ, ads + 128 * kk, bk + 128 * kk, idesc_dq, kk > 0);
-          mma_commit(bar_dq_full);
-          mma_commit(bar_q_free(st));
+          for (int kk = 0; kk < 8; ++kk) mma_ss(tdQ, ads + 128 * kk, bk_mn + 128 * kk, idesc_dq, kk > 0);
         }
+        ELSA_TR(4, it, 2);
+        mma_commit(bar_dq_full);
+        mma_commit(bar_q_free(st));
+        ELSA_TR(4, it, 3);
+        if (more) issue_sp(sn, 1);
+        ELSA_TR(0, it, 3);
       }
       if (ok) mma_commit(bar_done);
     }
+  } else if (warp >= 8) {
+    // ---------------- dQ drain warps: one thread per query row ----------------
+    reg_dec<104>();
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int it = 0; it < n_it; ++it) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dq_full, it & 1, &abort_flag, &g_bwd_status, BAR_DQ_FULL))) break;
+      if (tid == 256) ELSA_TR(3, it, 0);
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tdQ + lane_off, r0);
+      tmem_ld32(tdQ + lane_off + 32, r1);
+      tmem_wait_ld();
+      if (tid == 256) ELSA_TR(3, it, 1);
+      tc_fence_before();
+      mbar_arrive(bar_dq_free);
+      // Stage the 128 x 64 fp32 tile in shared memory (two 32-column blocks, 128-byte swizzle) and let the TMA
+      // unit add it into the global accumulator: whole 128-byte lines per reduction instead of one 16-byte
+      // piece per lane, and no LSU traffic that would delay the MMA issue slots of this scheduler.
+      if (tid == 256) bulk_wait_group_read<0>();          // the previous tile has been read out of the staging buffer
+      named_barrier_sync(1, 128);
+      {
+        uint8_t* stg = smem_gen + (sDQ - smem_base) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          *reinterpret_cast<uint4*>(stg + ((c ^ (row & 7)) << 4)) = make_uint4(r0[4 * c], r0[4 * c + 1], r0[4 * c + 2], r0[4 * c + 3]);
+          *reinterpret_cast<uint4*>(stg + kTile + ((c ^ (row & 7)) << 4)) = make_uint4(r1[4 * c], r1[4 * c + 1], r1[4 * c + 2], r1[4 * c + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      named_barrier_sync(1, 128);
+      if (tid == 256) {
+        const int qrow0 = (it_begin + it) * 128;
+        tma_reduce_add_3d(&tmap_dq, sDQ, 0, qrow0, bh);           // rows beyond N are clipped by the tensor map
+        tma_reduce_add_3d(&tmap_dq, sDQ + kTile, 32, qrow0, bh);
+        bulk_commit_group();
+      }
+      if (tid == 256) ELSA_TR(3, it, 2);
+    }
+    if (tid == 256) bulk_wait_group<0>();                 // reductions must have left shared memory before the CTA exits
   } else {
-    // ---------------- compute warps ----------------
-    const int half = warp >> 2;                               // which 64 query columns / 32 dQ columns
-    const int row = (warp & 3) * 32 + lane;                   // key row in phase A, query row in phase B
+    // ---------------- compute warps: thread = (key row, query half) ----------------
+    reg_inc<184>();
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int key = k0 + row;
     const bool key_ok = key < N;
-    const float c = prm.scale_log2;
+    const bool cta_tail = k0 + 128 > N;        // some key rows of this CTA do not exist
+    const float2 c2 = make_float2(prm.scale_log2, prm.scale_log2);
     bool alive = true;
 
     for (int it = 0; it < n_it; ++it) {
       const int st = it % kQStages;
       const int q_tile0 = (it_begin + it) * 128;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_sp, it & 1, &abort_flag, &g_bwd_status, BAR_SP))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_sp(half), it & 1, &abort_flag, &g_bwd_status, BAR_SP))) { alive = false; break; }
+      // the row statistics of this stage were written by the bulk copies that complete on q_full: observe that
+      // barrier directly (it completed before the MMAs behind bar_sp were issued, so this never spins)
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_q_full(st), (it / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL))) { alive = false; break; }
+      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 0);
       tc_fence_after();
-      const float* lse_s = reinterpret_cast<const float*>(smem_gen + (sLSE(st) - smem_base));
-      const float* d_s = reinterpret_cast<const float*>(smem_gen + (sD(st) - smem_base));
-      const bool diag = prm.is_causal && (q_tile0 < k0 + 128);   // only the first visited tile crosses the diagonal
+      const float4* nl4 =reinterpret_cast<const float4*>(smem_gen + (sNL(st) - smem_base)) + half * 16;
+      const float4* nd4 = reinterpret_cast<const float4*>(smem_gen + (sND(st) - smem_base)) + half * 16;
+      const bool masked = cta_tail || (prm.is_causal && q_tile0 < k0 + 128);   // only the diagonal tile / the last key tile
+      uint8_t* ds_row = smem_gen + (sDS0 - smem_base) + (it & 1) * 2 * kTile + half * kTile + row * 128;
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
-        const int col0 = half * 64 + ch * 32;                 // first query column of this chunk
         uint32_t rs[32], rp[32];
-        tmem_ld32(tS + lane_off + col0, rs);
-        tmem_ld32(tdP + lane_off + col0, rp);
+        tmem_ld32(tS(half) + lane_off + 32 * ch, rs);
+        tmem_ld32(tdP(half) + lane_off + 32 * ch, rp);
         tmem_wait_ld();
-        uint32_t pk[16], dk_[16];
+        if (ch == 0 && lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
+        uint32_t pk[16], dsk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float pv[2], dv_[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = col0 + 2 * i + e;
-            const float l = lse_s[col], dd = d_s[col];
-            float p = fast_exp2(fmaf(__uint_as_float(rs[2 * i + e]), c, -l));
-            bool valid = key_ok;
-            if (diag) valid = valid && (q_tile0 + col >= key);
-            p = valid ? p : 0.f;
-            pv[e] = p;
-            dv_[e] = p * (__uint_as_float(rp[2 * i + e]) - dd);
+        for (int g = 0; g < 8; ++g) {
+          const float4 nl = nl4[ch * 8 + g], nd = nd4[ch * 8 + g];   // -LSE, -D of 4 queries (warp-wide broadcast reads)
+          float2 x0 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g]), __uint_as_float(rs[4 * g + 1])), c2, make_float2(nl.x, nl.y));
+          float2 x1 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g + 2]), __uint_as_float(rs[4 * g + 3])), c2, make_float2(nl.z, nl.w));
+#ifdef ELSA_VAR_NOEXP
+          float2 p0 = x0, p1 = x1;
+#else
+          float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+          float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+#endif
+          if (masked) {
+            const int qc = q_tile0 + half * 64 + ch * 32 + 4 * g;     // first query of this group of 4
+            const bool causal = prm.is_causal;
+            p0.x = (key_ok && (!causal || qc + 0 >= key)) ? p0.x : 0.f;
+            p0.y = (key_ok && (!causal || qc + 1 >= key)) ? p0.y : 0.f;
+            p1.x = (key_ok && (!causal || qc + 2 >= key)) ? p1.x : 0.f;
+            p1.y = (key_ok && (!causal || qc + 3 >= key)) ? p1.y : 0.f;
           }
-          pk[i] = pack2<T>(pv[0], pv[1]);
-          dk_[i] = pack2<T>(dv_[0], dv_[1]);
+          const float2 t0 = __fadd2_rn(make_float2(__uint_as_float(rp[4 * g]), __uint_as_float(rp[4 * g + 1])), make_float2(nd.x, nd.y));
+          const float2 t1 = __fadd2_rn(make_float2(__uint_as_float(rp[4 * g + 2]), __uint_as_float(rp[4 * g + 3])), make_float2(nd.z, nd.w));
+          const float2 d0 = __fmul2_rn(p0, t0), d1 = __fmul2_rn(p1, t1);
+          pk[2 * g] = pack2<T>(p0.x, p0.y);
+          pk[2 * g + 1] = pack2<T>(p1.x, p1.y);
+          dsk[2 * g] = pack2<T>(d0.x, d0.y);
+          dsk[2 * g + 1] = pack2<T>(d1.x, d1.y);
         }
-        // P^T over S^T, dS^T over dP^T (16-bit pairs: 16 columns hold 32 query columns).  Each thread
-        // overwrites only fp32 columns it has already consumed: the packed values of query half h go to
-        // columns [64h + 16*ch, +16), inside this thread's own 64-column region.
-        {
-          uint32_t w[32];
+        // 16-bit P^T_h over S^T_h and dS^T_h over dP^T_h: chunk ch lands in columns [16*ch, +16), which this
+        // thread has already consumed (it loaded columns [32*ch, +32) above).
+        tmem_st16(tS(half) + lane_off + 16 * ch, pk);
+        tmem_st16(tdP(half) + lane_off + 16 * ch, dsk);
+        // dS^T to shared memory: block `half`, row = key, 16-byte chunk (8 queries) index XOR (key & 7)
+#ifndef ELSA_VAR_NODS
 #pragma unroll
-          for (int i = 0; i < 16; ++i) { w[i] = pk[i]; w[16 + i] = dk_[i]; }
-          const uint32_t pcol = static_cast<uint32_t>(half * 64 + ch * 16);
-          asm volatile(
-              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-              ::"r"(tS + lane_off + pcol), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]),
-                "r"(w[7]), "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
-          asm volatile(
-              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-              ::"r"(tdP + lane_off + pcol), "r"(w[16]), "r"(w[17]), "r"(w[18]), "r"(w[19]), "r"(w[20]), "r"(w[21]),
-                "r"(w[22]), "r"(w[23]), "r"(w[24]), "r"(w[25]), "r"(w[26]), "r"(w[27]), "r"(w[28]), "r"(w[29]), "r"(w[30]),
-                "r"(w[31]) : "memory");
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ch * 4 + g;
+          *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(dsk[4 * g], dsk[4 * g + 1], dsk[4 * g + 2], dsk[4 * g + 3]);
         }
-        // dS^T to shared memory: block `half` (64 queries), row = key, 16-byte chunk index XOR (key & 7)
-        {
-          uint8_t* blk = smem_gen + (sDS - smem_base) + half * kTile + row * 128;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int chunk = ch * 4 + g;                      // 8 queries per 16-byte chunk
-            uint4 val = make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
-            *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = val;
-          }
-        }
+#endif
       }
+      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 2);
+#ifndef ELSA_VAR_NOFENCE
       fence_proxy_async_smem();
+#endif
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_pds);
-
-      // ---- dQ of this pair: TMEM -> registers -> global fp32 reductions ----
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_dq_full, it & 1, &abort_flag, &g_bwd_status, BAR_DQ_FULL))) { alive = false; break; }
-      tc_fence_after();
-      uint32_t rq[32];
-      tmem_ld32(tdQ + lane_off + half * 32, rq);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar_dq_free);
-      const int qrow = q_tile0 + row;
-      if (qrow < N) {
-        float* dst = prm.dq_acc + (static_cast<int64_t>(bh) * N + qrow) * 64 + half * 32;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          red_add_v4(dst + 4 * i, __uint_as_float(rq[4 * i]), __uint_as_float(rq[4 * i + 1]), __uint_as_float(rq[4 * i + 2]),
-                     __uint_as_float(rq[4 * i + 3]));
-      }
+      mbar_arrive(bar_pds(half));
+      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 3);
     }
 
-    // ---- epilogue: dK, dV of this key tile ----
+    // ---- epilogue: dK, dV of this key tile (tcgen05.ld is warp-collective: only the stores are predicated) ----
     if (alive && n_it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_done, 0, &abort_flag, &g_bwd_status, BAR_DONE))) alive = false;
-    // tcgen05.ld is warp-collective (.sync.aligned): every lane executes it, only the stores are predicated
     if (alive) {
       uint32_t rk[32], rv[32];
       if (n_it > 0) {
@@ -312,14 +402,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 12) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-// D = sum_d out*dout, LSE = m + log2(max(z, 1e-30)) into the padded layout; padding: D = 0, LSE = +inf
+// -D = -sum_d out*dout, -LSE = -(m + log2(max(z, 1e-30))) into the padded layout; padding: -D = 0, -LSE = -inf
 template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
-                          const float* __restrict__ row_z, float* __restrict__ d_pad, float* __restrict__ lse_pad,
+                          const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
                           int bh, int n_ctx, int n_pad) {
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t prow = gid >> 3;                  // padded row index
@@ -343,11 +433,11 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   part += __shfl_xor_sync(0xffffffffu, part, 1);
   if (prow < total && lane == 0) {
     if (real) {
-      d_pad[prow] = part;
-      lse_pad[prow] = row_m[b * n_ctx + r] + log2f(fmaxf(row_z[b * n_ctx + r], 1.0e-30f));
+      nd_pad[prow] = -part;
+      nlse_pad[prow] = -(row_m[b * n_ctx + r] + log2f(fmaxf(row_z[b * n_ctx + r], 1.0e-30f)));
     } else {
-      d_pad[prow] = 0.f;
-      lse_pad[prow] = CUDART_INF_F;
+      nd_pad[prow] = 0.f;
+      nlse_pad[prow] = -CUDART_INF_F;
     }
   }
 }
@@ -382,33 +472,34 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   const int n_pad = static_cast<int>(align_up(N, 128));
   const int64_t vec_bytes = align_up(static_cast<int64_t>(bh) * n_pad * 4, 256);
   char* ws = static_cast<char*>(workspace);
-  float* d_pad = reinterpret_cast<float*>(ws);
-  float* lse_pad = reinterpret_cast<float*>(ws + vec_bytes);
+  float* nd_pad = reinterpret_cast<float*>(ws);
+  float* nlse_pad = reinterpret_cast<float*>(ws + vec_bytes);
   float* dq_acc = reinterpret_cast<float*>(ws + 2 * vec_bytes);
   const int64_t acc_elems = static_cast<int64_t>(bh) * N * 64;
 
   {
     const int64_t threads = static_cast<int64_t>(bh) * n_pad * 8;
     bwd_preprocess_pad_kernel<T><<<static_cast<unsigned>(cdiv64(threads, 256)), 256, 0, st>>>(
-        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, d_pad, lse_pad, bh, N, n_pad);
+        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, bh, N, n_pad);
     ELSA_LAUNCH_CHECK();
   }
   ELSA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, acc_elems * 4, st));
 
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   int rc;
+  if ((rc = make_tmap_f32_rows64(&mdq, dq_acc, N, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mk, p.k, dtype, N, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mv, p.v, dtype, N, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, bh, 128)) != ELSA_OK) return rc;
   BwdTcParams prm;
-  prm.lse_pad = lse_pad; prm.d_pad = d_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
+  prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.is_causal = p.is_causal;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_tc_kernel<T>), kBwdSmem);
   if (rc != ELSA_OK) return rc;
   dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
-  bwd_tc_kernel<T><<<grid, kThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, prm);
+  bwd_tc_kernel<T><<<grid, kThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, prm);
   ELSA_LAUNCH_CHECK();
   dq_convert_kernel<T><<<static_cast<unsigned>(cdiv64(acc_elems / 8, 256)), 256, 0, st>>>(
       dq_acc, static_cast<T*>(p.dq), acc_elems / 8, p.scale);
@@ -422,6 +513,12 @@ int bwd_tc(const BwdParams& p, const void* out, const float* row_m, const float*
   if (dtype == ELSA_F16) return bwd_tc_t<__half>(p, out, row_m, row_z, workspace, dtype, st);
   return bwd_tc_t<__nv_bfloat16>(p, out, row_m, row_z, workspace, dtype, st);
 }
+
+#ifdef ELSA_TRACE
+extern "C" int elsa_debug_bwd_trace(long long* host_buf) {
+  return cudaMemcpyFromSymbol(host_buf, g_bwd_trace, sizeof(long long) * 5 * 256 * 4) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 int bwd_tc_status(int* status_out, int clear) {
   int v = 0;

@@ -343,6 +343,23 @@ int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_ro
   return ELSA_OK;
 }
 
+int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int64_t n_mats, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return ELSA_ERR_UNSUPPORTED;
+  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(n_mats)};
+  const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(n_rows) * 256};
+  const cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};   // 32 floats = one 128-byte swizzle row
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return ELSA_ERR_CUDA;
+  }
+  return ELSA_OK;
+}
+
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias) {
   return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim == 64 && !has_bias && encode_tiled_fn() != nullptr;
 }

@@ -78,6 +78,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// 3-D tiled reduction shared -> global: global[tile] += smem tile (element type and add come from the tensor
+// map / the .add qualifier); tracked by the thread's bulk async-group.  Coordinates out of range are skipped.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest `N` groups of this thread have finished READING their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- tcgen05 ----------------------------------------------------------------------------------
@@ -183,5 +201,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 // [BH][N][64] 16-bit tensor seen as a 3-D map (innermost first: 64, N, BH), box 64 x box_rows x 1,
 // 128-byte swizzle, out-of-range rows read as zeros.
 int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int64_t n_mats, int box_rows);
+// [n_mats][n_rows][64] fp32 tensor, box 32 x box_rows x 1 (two boxes cover the 64 columns), 128-byte swizzle
+int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int64_t n_mats, int box_rows);
 
 }  // namespace elsa
