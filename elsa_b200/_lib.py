@@ -28,6 +28,8 @@ SIGNATURES = {
     "elsa_uses_tensor_cores": (c_int, [c_int] * 6),
     "elsa_phase1_fold": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_uint, _P]),
+    "elsa_phase1_fold_shard": (c_int, [_P, _P, _P, _P, _P, _P] + [c_int] * 11 + [c_uint, _P]),
+    "elsa_merge_partial": (c_int, [_P] * 6 + [c_int] * 5 + [_P]),
     "elsa_merge_final": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "elsa_scan_step": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
     "elsa_upsweep_level": (c_int, [_P] * 6 + [c_int] * 5 + [_P]),

@@ -97,11 +97,13 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int phase1_dispatch(const void* q, const void* k, const void* v, const float* bias, int64_t bsb, int64_t bsh,
                            int64_t bsq, int64_t bsk, float* m_buf, float* z_buf, void* s_buf, int dtype,
                            int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int q_start, int q_len,
-                           int part_width, int n_parts, int is_causal, unsigned flags, cudaStream_t st) {
+                           int part_width, int n_parts, int is_causal, unsigned flags, cudaStream_t st,
+                           int n_keys = -1, int key_offset = 0) {
+  if (n_keys < 0) n_keys = n_ctx;
   if (!q || !k || !v || !m_buf || !z_buf || !s_buf || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
       heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || q_start < 0 || q_len < 0 ||
       q_start + q_len > n_ctx || part_width < 1 || n_parts < 1 ||
-      static_cast<int64_t>(n_parts) * part_width < n_ctx)
+      static_cast<int64_t>(n_parts) * part_width < n_keys || n_keys < 1 || key_offset < 0)
     return ELSA_ERR_INVALID_ARGUMENT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(s_buf)) return ELSA_ERR_INVALID_ARGUMENT;
   if (static_cast<int64_t>(batch) * heads > 65535 || n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
@@ -113,6 +115,7 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.m = m_buf; p.z = z_buf; p.s = s_buf;
   p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.q_start = q_start; p.q_len = q_len;
   p.part_width = part_width; p.n_parts = n_parts; p.bh = batch * heads;
+  p.n_keys = n_keys; p.key_offset = key_offset;
   p.is_causal = is_causal ? 1 : 0;
   p.summary_dtype = summary_dtype;
   // reference rounding point: P is cast to fp16 before P.V only for fp16 inputs whose summaries are
@@ -169,6 +172,15 @@ extern "C" int elsa_phase1_fold(const void* q, const void* k, const void* v, con
   return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_buf, z_buf, s_buf,
                          dtype, summary_dtype, batch, heads, n_ctx, head_dim, q_start, q_len, part_width, n_parts,
                          is_causal, flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int elsa_phase1_fold_shard(const void* q, const void* k, const void* v, float* m_buf, float* z_buf,
+                                      void* s_buf, int dtype, int summary_dtype, int batch, int heads, int n_ctx,
+                                      int head_dim, int n_keys, int key_offset, int part_width, int n_parts,
+                                      int is_causal, unsigned flags, void* stream) {
+  return phase1_dispatch(q, k, v, nullptr, 0, 0, 0, 0, m_buf, z_buf, s_buf, dtype, summary_dtype, batch, heads, n_ctx,
+                         head_dim, 0, n_ctx, part_width, n_parts, is_causal, flags, static_cast<cudaStream_t>(stream),
+                         n_keys, key_offset);
 }
 
 extern "C" int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,

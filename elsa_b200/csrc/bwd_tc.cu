@@ -91,8 +91,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&w)[16
         "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
 }
 
-template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)

@@ -31,12 +31,13 @@ fold_simt_kernel(const FoldParams prm) {
   const int q_end = prm.q_start + prm.q_len;
   const int rows_valid = min(64, q_end - q0);
   const int k_begin = part * prm.part_width;
-  int k_end = min(N, k_begin + prm.part_width);
-  if (prm.is_causal) k_end = min(k_end, q0 + rows_valid);  // keys beyond the tile's last row are masked for every row
+  const int koff = prm.key_offset;       // global index of local key 0
+  int k_end = min(prm.n_keys, k_begin + prm.part_width);
+  if (prm.is_causal) k_end = min(k_end, q0 + rows_valid - koff);  // keys beyond the tile's last row are masked for every row
 
   const T* qb = static_cast<const T*>(prm.q) + static_cast<int64_t>(bh) * N * D;
-  const T* kb = static_cast<const T*>(prm.k) + static_cast<int64_t>(bh) * N * D;
-  const T* vb = static_cast<const T*>(prm.v) + static_cast<int64_t>(bh) * N * D;
+  const T* kb = static_cast<const T*>(prm.k) + static_cast<int64_t>(bh) * prm.n_keys * D;
+  const T* vb = static_cast<const T*>(prm.v) + static_cast<int64_t>(bh) * prm.n_keys * D;
   const bool vec_ok = (D % 4) == 0;
   const float* bias_bh = nullptr;
   if (prm.bias) {
@@ -74,10 +75,10 @@ fold_simt_kernel(const FoldParams prm) {
       for (int jj = 0; jj < 4; ++jj) {
         const int kj = k0 + tx + 16 * jj;
         bool valid = kj < k_end && qi < q_end;
-        if (prm.is_causal) valid = valid && (qi >= kj);
+        if (prm.is_causal) valid = valid && (qi >= kj + koff);
         float sc;
         if (bias_bh) {
-          float bv = valid ? bias_bh[static_cast<int64_t>(qi) * prm.bsq + static_cast<int64_t>(kj) * prm.bsk] : 0.f;
+          float bv = valid ? bias_bh[static_cast<int64_t>(qi) * prm.bsq + static_cast<int64_t>(kj + koff) * prm.bsk] : 0.f;
           sc = (S[ii][jj] * prm.scale + bv) * kLog2e;
         } else {
           sc = S[ii][jj] * prm.scale_log2;

@@ -34,7 +34,7 @@ namespace {
 constexpr int kStages = 4;
 constexpr int kTileBytes = 128 * 64 * 2;                          // one 128 x 64 16-bit tile
 constexpr int kFoldSmem = (2 + 2 * kStages) * kTileBytes + 1024;  // + alignment slack
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MMA issuer, 2 idle warps)
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -43,6 +43,7 @@ enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, 
 struct FoldTcParams {
   float* m; float* z; void* s;
   int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
+  int n_keys, key_offset;
   float scale_log2;
 };
 
@@ -76,7 +77,8 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int q0 = prm.q_start + blockIdx.x * 256;           // first query row of tile 0
   const int q_end = prm.q_start + prm.q_len;
   const int k_begin = part * prm.part_width;
-  const int k_end = min(prm.n_ctx, k_begin + prm.part_width);
+  const int k_end = min(prm.n_keys, k_begin + prm.part_width);   // local key indices
+  const int koff = prm.key_offset;
 
   // number of 128-key tiles each query tile has to visit
   int n_t[2];
@@ -84,7 +86,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   for (int t = 0; t < 2; ++t) {
     const int qt0 = q0 + t * 128;
     int ke = k_end;
-    if (prm.is_causal) ke = min(ke, min(qt0 + 128, q_end));  // keys above the tile's last row are never admissible
+    if (prm.is_causal) ke = min(ke, min(qt0 + 128, q_end) - koff);  // keys above the tile's last row are never admissible
     n_t[t] = (qt0 < q_end && ke > k_begin) ? (ke - k_begin + 127) / 128 : 0;
   }
   const int n_max = max(n_t[0], n_t[1]);
@@ -120,8 +122,13 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t tS[2] = {tmem_base, tmem_base + 128};
   const uint32_t tO[2] = {tmem_base + 256, tmem_base + 320};
 
-  if (n_max > 0) {
-    if (warp == 8) {
+  // register budget: the fold warps hold a whole 128-column score row per thread; the producer / issuer
+  // warpgroup needs almost nothing (3 x 128 threads: 232 + 232 + 40 registers per thread <= 64 K).  Each role
+  // branch starts with its setmaxnreg and runs to the common exit, so the allocator sees one budget per branch.
+
+  if (warp >= 8) {
+    reg_dec<40>();
+    if (n_max > 0 && warp == 8) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
         prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -136,7 +143,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           tma_load_3d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, bh);
         }
       }
-    } else if (warp == 9) {
+    } else if (n_max > 0 && warp == 9) {
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
         constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
@@ -181,9 +188,8 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (ok) mma_commit(bar_o);
       }
     }
-  }
-
-  if (warp < 8) {
+  } else {
+    reg_inc<232>();
     // ---------------- fold warps: one thread per query row ----------------
     const int t = warp >> 2;
     const int row = (warp & 3) * 32 + lane;                 // row within the tile == TMEM lane
@@ -207,16 +213,21 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tmem_wait_ld();
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
-      const bool diag = prm.is_causal && (k0 + 127 > q0 + t * 128);
+      const bool diag = prm.is_causal && (k0 + koff + 127 > q0 + t * 128);
       if (tail || diag) {
-        const int lim = prm.is_causal ? min(k_end - 1, qi) : k_end - 1;   // last admissible key of this row
+        const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (k0 + i > lim) sv[i] = -CUDART_INF_F;
       }
-      float tmax = sv[0];
+      // row max with four independent chains (a single 128-deep fmax chain costs ~500 cycles of latency)
+      float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int i = 1; i < 128; ++i) tmax = fmaxf(tmax, sv[i]);
+      for (int i = 4; i < 128; i += 4) {
+        mx[0] = fmaxf(mx[0], sv[i]); mx[1] = fmaxf(mx[1], sv[i + 1]);
+        mx[2] = fmaxf(mx[2], sv[i + 2]); mx[3] = fmaxf(mx[3], sv[i + 3]);
+      }
+      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
@@ -238,20 +249,26 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         m_ref = m_new;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      float psum = 0.f;
+      // p = 2^(s*c - m) on packed pairs (fma.f32x2 / add.f32x2), row sum in four independent pair accumulators
+      const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_use, -m_use);
+      float2 ps[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(sv[64 * h + 2 * i], c, -m_use));
-          const float p1 = fast_exp2(fmaf(sv[64 * h + 2 * i + 1], c, -m_use));
-          psum += p0 + p1;
-          pk[i] = pack2<T>(p0, p1);
+          const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
+          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
+          pk[i] = pack2<T>(pp.x, pp.y);
         }
         tmem_st32(tS[t] + lane_off + 32 * h, pk);
       }
-      zsum += psum;
+      {
+        const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
+        const float2 s = __fadd2_rn(s01, s23);
+        zsum += s.x + s.y;
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p(t));
@@ -369,9 +386,10 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   int rc;
   if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_keys, p.bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_keys, p.bh, 128)) != ELSA_OK) return rc;
   FoldTcParams prm;
+  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;

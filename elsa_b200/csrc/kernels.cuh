@@ -14,6 +14,7 @@ struct FoldParams {
   const float* bias; int64_t bsb, bsh, bsq, bsk;
   float* m; float* z; void* s;
   int heads, n_ctx, head_dim, q_start, q_len, part_width, n_parts, bh;
+  int n_keys, key_offset;   // rows of k/v per (batch*head) and the global index of their first row (sequence shards)
   int is_causal, summary_dtype, round_p;  // round_p: 0 keep P in fp32, 1 round to fp16, 2 to bf16
   float scale, scale_log2;
 };
@@ -59,6 +60,6 @@ int bwd_simt(const BwdParams& p, int dtype, cudaStream_t st);
 // phase 2 (phase2.cu)
 int merge_final_any(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                     int summary_dtype, int out_dtype, int n_parts, int bh, int q_start, int q_len, int n_ctx,
-                    int head_dim, int first_part, int store_state, cudaStream_t st);
+                    int head_dim, int first_part, int store_state, cudaStream_t st, int normalize = 1);
 
 }  // namespace elsa

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256)
 merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, const TS* __restrict__ s,
                    TO* __restrict__ out, float* __restrict__ row_m, float* __restrict__ row_z,
                    int n_parts, int64_t rows, int q_len, int q_start, int n_ctx, int head_dim,
-                   int chunks, int first_part, int store_state) {
+                   int chunks, int first_part, int store_state, int normalize) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * chunks) return;
   const int64_t row = idx / chunks;
@@ -83,7 +83,7 @@ merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, con
   const int64_t bh_idx = row / q_len;
   const int r = static_cast<int>(row - bh_idx * q_len);
   const int64_t orow = bh_idx * n_ctx + q_start + r;
-  const float inv = Z > 0.f ? 1.0f / Z : 0.f;
+  const float inv = normalize ? (Z > 0.f ? 1.0f / Z : 0.f) : 1.0f;   // normalize == 0: emit the merged, un-normalised s
   float o[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) o[i] = Z > 0.f ? acc[i] * inv : 0.f;
@@ -172,7 +172,7 @@ static inline int pick_nv(int head_dim, int elem_bytes_a, int elem_bytes_b) {
 template <typename TS, typename TO>
 static int launch_merge_final(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                               int n_parts, int bh, int q_start, int q_len, int n_ctx, int head_dim,
-                              int first_part, int store_state, cudaStream_t st) {
+                              int first_part, int store_state, cudaStream_t st, int normalize) {
   const int64_t rows = static_cast<int64_t>(bh) * q_len;
   const int nv = pick_nv(head_dim, sizeof(TS), sizeof(TO));
   const int chunks = head_dim / nv;
@@ -181,7 +181,7 @@ static int launch_merge_final(const float* m, const float* z, const void* s, voi
   auto ts = static_cast<const TS*>(s);
   auto to = static_cast<TO*>(out);
 #define ELSA_MF(NV) merge_final_kernel<TS, TO, NV><<<blocks, 256, 0, st>>>(m, z, ts, to, row_m, row_z, n_parts, rows, \
-                                                   q_len, q_start, n_ctx, head_dim, chunks, first_part, store_state)
+                                                   q_len, q_start, n_ctx, head_dim, chunks, first_part, store_state, normalize)
   if (nv == 8) ELSA_MF(8); else if (nv == 4) ELSA_MF(4); else ELSA_MF(1);
 #undef ELSA_MF
   ELSA_LAUNCH_CHECK();
@@ -190,7 +190,7 @@ static int launch_merge_final(const float* m, const float* z, const void* s, voi
 
 int merge_final_any(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                            int summary_dtype, int out_dtype, int n_parts, int bh, int q_start, int q_len, int n_ctx,
-                           int head_dim, int first_part, int store_state, cudaStream_t st) {
+                           int head_dim, int first_part, int store_state, cudaStream_t st, int normalize) {
   if (!dtype_ok(summary_dtype) || !dtype_ok(out_dtype)) return ELSA_ERR_INVALID_ARGUMENT;
   if (!m || !z || !s || !out || n_parts < 1 || bh < 1 || q_len < 0 || head_dim < 1 || head_dim > 128 ||
       q_start < 0 || q_start + q_len > n_ctx || first_part < 0)
@@ -200,7 +200,7 @@ int merge_final_any(const float* m, const float* z, const void* s, void* out, fl
 #define ELSA_CASE(SD, OD, TS, TO)                 \
   if (summary_dtype == SD && out_dtype == OD)     \
     return launch_merge_final<TS, TO>(m, z, s, out, row_m, row_z, n_parts, bh, q_start, q_len, n_ctx, head_dim, \
-                                      first_part, store_state, st)
+                                      first_part, store_state, st, normalize)
   ELSA_CASE(ELSA_F32, ELSA_F32, float, float);
   ELSA_CASE(ELSA_F16, ELSA_F16, __half, __half);
   ELSA_CASE(ELSA_BF16, ELSA_BF16, __nv_bfloat16, __nv_bfloat16);
@@ -312,4 +312,12 @@ extern "C" int elsa_prefix_scan(const float* m_in, const float* z_in, const void
   if (summary_dtype == ELSA_F32) return launch_prefix<float>(m_in, z_in, s_in, m_out, z_out, s_out, n_parts, bh, q_len, head_dim, st);
   if (summary_dtype == ELSA_F16) return launch_prefix<__half>(m_in, z_in, s_in, m_out, z_out, s_out, n_parts, bh, q_len, head_dim, st);
   return launch_prefix<__nv_bfloat16>(m_in, z_in, s_in, m_out, z_out, s_out, n_parts, bh, q_len, head_dim, st);
+}
+
+extern "C" int elsa_merge_partial(const float* m_buf, const float* z_buf, const void* s_buf, float* s_out, float* m_out,
+                                  float* z_out, int summary_dtype, int n_parts, int bh, int q_len, int head_dim,
+                                  void* stream) {
+  // one un-normalised fp32 summary per row: the state a sequence shard contributes to the cross-GPU merge
+  return merge_final_any(m_buf, z_buf, s_buf, s_out, m_out, z_out, summary_dtype, ELSA_F32, n_parts, bh, 0, q_len, q_len,
+                         head_dim, 0, 1, static_cast<cudaStream_t>(stream), 0);
 }

@@ -1,0 +1,112 @@
+"""Multi-GPU forms of the two-pass attention (one process per GPU, torch.distributed for plumbing).
+
+The reference is single-GPU; these are the two ways its path shards:
+
+* batch x heads: rows of B*H are independent (the reference's grid axis `pid_bh`,
+  src/elsa_twopass_clean/attention.py:51).  `shard_heads` slices q, k, v; no collective is needed.
+
+* sequence (K partitions): the (m, z, s) merge is associative and commutative for the non-causal
+  total, and for causal rows a shard that lies in the future contributes the identity, so every GPU
+  folds its own K/V rows for ALL query rows and the per-GPU summaries are combined with the same
+  operator the single-GPU phase 2 uses (cuda/paper_scan_d64_kernel.cu:39-70):
+      M = max over ranks of m            -> all_reduce(MAX)
+      w = 2^(m - M) (0 where z == 0)     -> local
+      Z, S = sum over ranks of z*w, s*w  -> all_reduce(SUM) of one concatenated [z | s] buffer
+      out = S / Z
+  `merge_summaries_across_ranks` is that exchange on plain tensors (it runs on CPU ranks with gloo
+  as well); `sequence_parallel_attention` is the GPU forward built on it.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .attention import _aligned, _check_qkv
+
+
+def shard_heads(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """[B, H, N, D] -> this rank's contiguous slice of the flattened batch*head axis, as [1, BH/world, N, D]."""
+    b, h, n, d = t.shape
+    bh = b * h
+    if bh % world:
+        raise ValueError("batch*heads must be divisible by the number of ranks")
+    per = bh // world
+    return t.reshape(bh, n, d)[rank * per:(rank + 1) * per].reshape(1, per, n, d)
+
+
+def merge_summaries_across_ranks(m: torch.Tensor, z: torch.Tensor, s: torch.Tensor, group=None
+                                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Combine one (m, z, s) summary per row per rank into the global result.
+
+    m, z: [...]; s: [..., D]; fp32, same shape on every rank.  Returns (out, row_m, row_z) with
+    out = S / Z (0 where Z == 0), row_m = M (-inf where Z == 0), row_z = Z -- the state the backward uses."""
+    m = m.float()
+    big_m = m.clone()
+    dist.all_reduce(big_m, op=dist.ReduceOp.MAX, group=group)
+    w = torch.where(z > 0, torch.exp2(m - big_m), torch.zeros((), device=m.device))
+    buf = torch.cat([(z * w).unsqueeze(-1), s.float() * w.unsqueeze(-1)], dim=-1).contiguous()
+    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+    big_z, big_s = buf[..., 0], buf[..., 1:]
+    out = torch.where(big_z.unsqueeze(-1) > 0, big_s / big_z.unsqueeze(-1), torch.zeros((), device=m.device))
+    row_m = torch.where(big_z > 0, big_m, torch.full((), float("-inf"), device=m.device))
+    return out, row_m, big_z
+
+
+def local_shard_summary(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, *, key_offset: int,
+                        is_causal: bool = False, part_width: int = 2048
+                        ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Phase 1 + local merge of ONE sequence shard on this GPU.
+
+    q: [B, H, N, D] (all query rows); k_shard, v_shard: [B, H, Nk, D] (rows key_offset .. key_offset+Nk-1 of
+    the sequence).  Returns fp32 (m, z, s) with one un-normalised summary per query row: [B*H, N], [B*H, N, D]."""
+    lib = _lib.load()
+    if q.dim() != 4 or k_shard.dim() != 4 or k_shard.shape != v_shard.shape:
+        raise ValueError("q must be [B,H,N,D] and k_shard, v_shard [B,H,Nk,D]")
+    if q.device.type != "cuda":
+        raise ValueError("local_shard_summary currently requires CUDA tensors")
+    b, h, n, d = map(int, q.shape)
+    nk = int(k_shard.shape[2])
+    if tuple(k_shard.shape) != (b, h, nk, d) or k_shard.dtype != q.dtype or v_shard.dtype != q.dtype:
+        raise ValueError("k_shard / v_shard must match q in batch, heads, head_dim and dtype")
+    q_c, k_c, v_c = _aligned(q), _aligned(k_shard), _aligned(v_shard)
+    dt = _lib.dtype_code(q.dtype)
+    pw = max(128, (int(part_width) + 127) // 128 * 128)
+    parts = -(-nk // pw)
+    bh = b * h
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        m_p = torch.empty((parts, bh, n), device=dev, dtype=torch.float32)
+        z_p = torch.empty_like(m_p)
+        s_p = torch.empty((parts, bh, n, d), device=dev, dtype=torch.float32)
+        rc = lib.elsa_phase1_fold_shard(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), m_p.data_ptr(), z_p.data_ptr(),
+                                        s_p.data_ptr(), dt, _lib.ELSA_F32, b, h, n, d, nk, int(key_offset), pw, parts,
+                                        int(bool(is_causal)), 0, stream)
+        _lib.check(rc, "elsa_phase1_fold_shard")
+        m = torch.empty((bh, n), device=dev, dtype=torch.float32)
+        z = torch.empty_like(m)
+        s = torch.empty((bh, n, d), device=dev, dtype=torch.float32)
+        rc = lib.elsa_merge_partial(m_p.data_ptr(), z_p.data_ptr(), s_p.data_ptr(), s.data_ptr(), m.data_ptr(),
+                                    z.data_ptr(), _lib.ELSA_F32, parts, bh, n, d, stream)
+        _lib.check(rc, "elsa_merge_partial")
+    return m, z, s
+
+
+def sequence_parallel_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, *, key_offset: int,
+                                is_causal: bool = False, part_width: int = 2048, group=None,
+                                return_state: bool = False):
+    """Forward of exact attention with K/V sharded along the sequence over the ranks of `group`.
+
+    Every rank passes the full q and its own K/V rows; every rank gets the full output [B, H, N, D] (input dtype)
+    and, with return_state, the global (row_m, row_z)."""
+    _check_qkv(q, q, q, "sequence_parallel_attention")
+    b, h, n, d = map(int, q.shape)
+    m, z, s = local_shard_summary(q, k_shard, v_shard, key_offset=key_offset, is_causal=is_causal, part_width=part_width)
+    out, row_m, row_z = merge_summaries_across_ranks(m, z, s, group=group)
+    out = out.to(q.dtype).reshape(b, h, n, d)
+    if return_state:
+        return out, row_m, row_z
+    return out

@@ -79,6 +79,24 @@ int elsa_phase1_fold(const void* q, const void* k, const void* v,
                      int q_start, int q_len, int part_width, int n_parts,
                      int is_causal, unsigned flags, void* stream);
 
+/* Phase 1 of ONE SEQUENCE SHARD: q holds all n_ctx query rows, k / v hold n_keys rows per
+ * (batch*head) whose first row has global index key_offset (needed only by the causal mask).
+ * Summaries cover all n_ctx rows: m, z [n_parts, B*H, n_ctx]; s [n_parts, B*H, n_ctx, D].
+ * No counterpart in the reference, which is single-GPU: this is the per-GPU half of the
+ * sequence-parallel forward; the partition layout is the reference's (attention.py:102-106). */
+int elsa_phase1_fold_shard(const void* q, const void* k, const void* v,
+                           float* m_buf, float* z_buf, void* s_buf,
+                           int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
+                           int n_keys, int key_offset, int part_width, int n_parts,
+                           int is_causal, unsigned flags, void* stream);
+
+/* Merge the partitions of each row into ONE un-normalised fp32 summary (m_out, z_out [B*H, q_len],
+ * s_out [B*H, q_len, D]): what a shard hands to the cross-GPU merge.  Same arithmetic as
+ * elsa_merge_final (cuda/paper_scan_d64_kernel.cu:39-70) without the final division. */
+int elsa_merge_partial(const float* m_buf, const float* z_buf, const void* s_buf,
+                       float* s_out, float* m_out, float* z_out,
+                       int summary_dtype, int n_parts, int bh, int q_len, int head_dim, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Phase 2, one pass: merge all partition summaries of each row, out = s / z, optional state.
  * Replaces pybind `final_reduce(m, z, s, out, row_m, row_z, q_start, n_ctx, k_blocks, q_blocks,
