@@ -29,7 +29,11 @@ def out_tol(dtype, ref):
 
 
 def check_state(rm, rz, rm_ref, rz_ref, dtype):
-    assert U.max_abs(rm, rm_ref) <= (2e-5 if dtype == F32 else 2e-3)
+    # 16-bit: the reference's fp16 fast path evaluates the logits with its softmax scale rounded to fp16
+    # (2.2e-4 relative), so its row maxima sit 2.2e-4 * |m| away from exact arithmetic
+    fin_m = torch.isfinite(rm_ref)
+    m_mag = float(rm_ref[fin_m].abs().max()) if fin_m.any() else 0.0
+    assert U.max_abs(rm, rm_ref) <= (2e-5 if dtype == F32 else 1e-3 + 3e-4 * m_mag)
     fin = rz_ref > 0
     rel = ((rz.cpu()[fin] - rz_ref[fin]).abs() / rz_ref[fin]).max().item() if fin.any() else 0.0
     # 16-bit: the reference's fp16 fast path rounds its softmax scale to fp16 (2e-4 relative on every logit),
@@ -243,7 +247,7 @@ def test_non_contiguous_inputs_and_errors():
     assert not q.is_contiguous()
     out = E.twopass_attention(q, k, v)
     ref = O.softmax_attention_fp64(q.cpu(), k.cpu(), v.cpu())
-    assert U.max_abs(out, ref) <= 5e-4
+    assert U.out_close(out, ref, F16) <= 2.0
     with pytest.raises(ValueError, match="paper_scan"):
         E.twopass_attention(q, k, v, algorithm="not_available")
     with pytest.raises(ValueError, match="phase1_warps"):

@@ -58,13 +58,15 @@ def test_full_size_properties(dtype, causal, n, h):
     q, k = (U.seeded((b, h, n, d), dtype, 210 + i).cuda() for i in range(2))
     ones = torch.ones((b, h, n, d), dtype=dtype, device="cuda")
     out = E.twopass_attention(q, k, ones, is_causal=causal)
-    tol = {F32: 2e-6, F16: 1e-3, BF16: 8e-3}[dtype]
-    assert (out.float() - 1.0).abs().max().item() <= tol          # every row of P sums to one
+    # every row of P sums to one; fp32: z and s are two length-N fp32 sums in different orders, so the bound
+    # grows like sqrt(N) from 2e-6 at N = 1024
+    tol = {F32: 2e-6 * max(1.0, math.sqrt(n / 1024)), F16: 1e-3, BF16: 8e-3}[dtype]
+    assert (out.float() - 1.0).abs().max().item() <= tol
     v1, v2 = (U.seeded((b, h, n, d), dtype, 220 + i).cuda() for i in range(2))
     o1 = E.twopass_attention(q, k, v1, is_causal=causal).float()
     o2 = E.twopass_attention(q, k, v2, is_causal=causal).float()
     o12 = E.twopass_attention(q, k, (v1.float() + v2.float()).to(dtype), is_causal=causal).float()
-    lin_tol = {F32: 4e-6, F16: 4e-3, BF16: 3e-2}[dtype]           # v1+v2 is itself rounded to the input dtype
+    lin_tol = {F32: 4e-6 * max(1.0, math.sqrt(n / 1024)), F16: 4e-3, BF16: 3e-2}[dtype]           # v1+v2 is itself rounded to the input dtype
     assert (o12 - (o1 + o2)).abs().max().item() <= lin_tol
     # sampled rows against fp64 on the same device
     rows = torch.tensor([0, 1, 127, 128, n // 2 + 3, n - 1], device="cuda")
