@@ -39,6 +39,8 @@ SIGNATURES = {
     "elsa_forward_plan": (c_int, [c_int] * 10 + [c_uint, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "elsa_twopass_forward": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_uint, _P]),
+    "elsa_static_scratch_bytes": (c_int64, []),
+    "elsa_twopass_forward_static": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
     "elsa_bwd_preprocess": (c_int, [_P] * 6 + [c_int] * 4 + [_P]),
     "elsa_row_stats_workspace_bytes": (c_int64, [c_int] * 7),
     "elsa_row_stats": (c_int, [_P, _P, *_BIAS, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

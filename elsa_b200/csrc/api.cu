@@ -354,3 +354,51 @@ extern "C" int64_t elsa_row_stats_workspace_bytes(int dtype, int batch, int head
   if (fwd < 0) return -1;
   return fwd + align_up(static_cast<int64_t>(batch) * heads * n_ctx * head_dim * dtype_size(dtype), 256);
 }
+
+// ---- forward without any caller-supplied or freshly allocated scratch --------------------------
+// Some callers have no way to hand over a workspace: a host runtime that reaches this library through a
+// minimal FFI and owns no device allocator, or a serving process whose device memory was carved up once at
+// start-up and whose request path is forbidden to allocate.  For them the partition summaries of the forward
+// live in one fixed array inside the library image.  The price: a hard size limit, the array is resident on
+// every GPU that loads the library until the process exits, and all calls share it.
+namespace elsa {
+constexpr int64_t kStaticScratchBytes = 64ll << 20;   // 64 MiB: covers the fp16 16K-token, 8-head forward (35.6 MB)
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the CURRENT device (in host code the symbol itself is only a handle,
+// not an address a kernel could use).  Looked up once per device and remembered.
+static int static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  ELSA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ELSA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    ELSA_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (!p || (reinterpret_cast<uintptr_t>(p) & 255u)) return ELSA_ERR_WORKSPACE;
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return ELSA_OK;
+}
+}  // namespace elsa
+
+extern "C" int64_t elsa_static_scratch_bytes(void) { return elsa::kStaticScratchBytes; }
+
+extern "C" int elsa_twopass_forward_static(const void* q, const void* k, const void* v, void* out, float* row_m,
+                                           float* row_z, int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                           int is_causal, void* stream) {
+  if (n_ctx == 0) return ELSA_OK;
+  // same plan as elsa_twopass_forward with library-chosen partitions, no bias, summaries in the input dtype
+  const int64_t need = elsa_forward_workspace_bytes(dtype, dtype, batch, heads, n_ctx, head_dim, 0, is_causal, 0, 0, 0u);
+  if (need < 0) return ELSA_ERR_INVALID_ARGUMENT;
+  if (need > elsa::kStaticScratchBytes) return ELSA_ERR_WORKSPACE;   // problem too large for the built-in scratch
+  void* scratch = nullptr;
+  int rc = elsa::static_scratch_ptr(&scratch);
+  if (rc != ELSA_OK) return rc;
+  // Nothing in the scratch has to start at zero: phase 1 writes every summary that phase 2 reads.
+  return elsa_twopass_forward(q, k, v, nullptr, 0, 0, 0, 0, out, row_m, row_z, scratch, elsa::kStaticScratchBytes, dtype,
+                              dtype, batch, heads, n_ctx, head_dim, is_causal, 0, 0, 0u, stream);
+}

@@ -162,6 +162,26 @@ int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_
                       int has_bias, int is_causal, int part_width_in, int q_chunk_in, unsigned flags,
                       int* part_width, int* n_parts, int* q_chunk);
 
+/* Forward for callers that cannot provide or allocate a workspace (no counterpart in the reference, whose
+ * buffers are always PyTorch allocations).  Meant for hosts that bind this library through a bare FFI and own
+ * no device allocator, and for serving loops whose device memory is fixed at start-up and whose request
+ * path must not allocate: the partition summaries go to a 64 MiB array that is part of the library image
+ * (elsa_static_scratch_bytes) instead of a caller workspace.  No bias, library-chosen partitions, summaries
+ * in the input dtype; out / row_m / row_z as in elsa_twopass_forward (row_m, row_z may both be NULL).
+ *   - A problem whose summaries need more than the array returns ELSA_ERR_WORKSPACE and launches nothing.
+ *   - The array stays resident on every GPU that loads the library, until the process exits.
+ *   - All calls on a device share the array: two calls that overlap on the GPU (different streams, or
+ *     different host threads) race on it.  Calls on one stream are safe back to back; nothing in the array
+ *     needs clearing between calls.
+ *   - The first call on each device looks the array's device address up; make that first call outside any
+ *     stream capture.
+ *   - The call itself never allocates or frees device memory. */
+int64_t elsa_static_scratch_bytes(void);
+int elsa_twopass_forward_static(const void* q, const void* k, const void* v,
+                                void* out, float* row_m, float* row_z,
+                                int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                int is_causal, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Backward.
  * ------------------------------------------------------------------------------------- */
