@@ -151,14 +151,13 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // O += P V  : A in TMEM, B (V) MN-major
         auto issue_s = [&](int t, int st) {
           const uint64_t a = make_sdesc(sQ[t], 16, 1024), b = make_sdesc(sK(st), 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_ss(tS[t], a + 2 * kk, b + 2 * kk, idesc_s, kk > 0);
+          mma_ss_x4<2, 2>(tS[t], a, b, idesc_s, 0u);
           mma_commit(bar_s(t));
         };
         auto issue_pv = [&](int t, int st, int j) {
           const uint64_t b = make_sdesc(sV(st), 128 * 128, 1024);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) mma_ts(tO[t], tS[t] + 8 * kk, b + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_x4<8, 128>(tO[t], tS[t], b, idesc_o, j > 0 ? 1u : 0u);
+          mma_ts_x4<8, 128>(tO[t], tS[t] + 32, b + 512, idesc_o, 1u);
         };
         bool ok = mbar_wait(bar_q, 0, &abort_flag, &g_fold_status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, &g_fold_status, BAR_KV_FULL);
         if (ok) {

@@ -135,6 +135,51 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four consecutive K-steps in ONE asm block.  The issuing thread is blocked by each tcgen05.mma until the pipe
+// accepts it, so every instruction executed between two MMAs is tensor-pipe idle time; here the operand
+// addresses of all four steps are formed first and the four MMAs follow back to back.
+// A_STEP: TMEM columns (TS form) or descriptor units of 16 bytes (SS form) per K-step; B_STEP: descriptor units.
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b1, b2, b3;\n\t.reg .b32 a1, a2, a3;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "add.u32 a1, %1, %5;\n\tadd.u32 a2, %1, %6;\n\tadd.u32 a3, %1, %7;\n\t"
+      "add.u64 b1, %2, %8;\n\tadd.u64 b2, %2, %9;\n\tadd.u64 b3, %2, %10;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, p1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(first_accumulate), "n"(A_STEP), "n"(2 * A_STEP),
+        "n"(3 * A_STEP), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b1;\n\t.reg .b32 a1;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "add.u32 a1, %1, %5;\n\tadd.u64 b1, %2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, p1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(first_accumulate), "n"(A_STEP), "n"(B_STEP)
+      : "memory");
+}
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void mma_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "add.u64 a1, %1, %5;\n\tadd.u64 a2, %1, %6;\n\tadd.u64 a3, %1, %7;\n\t"
+      "add.u64 b1, %2, %8;\n\tadd.u64 b2, %2, %9;\n\tadd.u64 b3, %2, %10;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, p1;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(first_accumulate), "n"(A_STEP), "n"(2 * A_STEP),
+        "n"(3 * A_STEP), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
 // the mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is complete
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
