@@ -29,6 +29,17 @@ using namespace tc;
 
 static __device__ int g_fold_status = 0;
 
+// Optional per-phase timestamps of CTA (0,0,0) for tuning builds (-DELSA_TRACE); compiled out otherwise.
+#ifdef ELSA_TRACE
+__device__ long long g_fold_trace[3][256][4];
+#define ELSA_FTR(role, it, slot)                                                                              \
+  do {                                                                                                        \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_fold_trace[role][it][slot] = clock64(); \
+  } while (0)
+#else
+#define ELSA_FTR(role, it, slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kStages = 4;
@@ -37,6 +48,9 @@ constexpr int kFoldSmem = (2 + 2 * kStages) * kTileBytes + 1024;  // + alignment
 constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MMA issuer, 2 idle warps)
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
+// every kPolyEvery-th pair of exponentials is evaluated on the FMA pipe; 0 = never.  Measured at 2 (half of them):
+// 6 % slower -- the fold warps are bound by instruction issue (two warps per scheduler), not by the ex2 unit.
+constexpr int kPolyEvery = 0;
 
 enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6 };
 
@@ -46,6 +60,29 @@ struct FoldTcParams {
   int n_keys, key_offset;
   float scale_log2;
 };
+
+// 2^x for a packed pair on the FMA pipe instead of the ex2 unit (16 results / clk / SM): round-to-nearest split
+// x = n + f with the 1.5 * 2^23 trick, degree-4 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error
+// 2.7e-6, far below the 16-bit rounding of P), then n is added into the exponent field.  x is clamped at -126.
+__device__ __forceinline__ float2 exp2_fma_pair(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(f, make_float2(0.009570101276040077f, 0.009570101276040077f), make_float2(0.05591785907745361f, 0.05591785907745361f));
+  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
+  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 template <typename TS>
 __device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64]) {
@@ -68,7 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FoldTcParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kStages + 6];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 8];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -100,14 +137,14 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto bar_kv_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_kv_free = [&](int st) { return bar0 + 8 * (1 + kStages + st); };
   auto bar_s = [&](int t) { return bar0 + 8 * (1 + 2 * kStages + t); };
-  auto bar_p = [&](int t) { return bar0 + 8 * (3 + 2 * kStages + t); };
-  const uint32_t bar_o = bar0 + 8 * (5 + 2 * kStages);
+  auto bar_p = [&](int t, int h) { return bar0 + 8 * (3 + 2 * kStages + 2 * t + h); };   // per (tile, 64-key half of P)
+  const uint32_t bar_o = bar0 + 8 * (7 + 2 * kStages);
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int st = 0; st < kStages; ++st) { mbar_init(bar_kv_full(st), 1); mbar_init(bar_kv_free(st), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(bar_s(t), 1); mbar_init(bar_p(t), 128); }
+    for (int t = 0; t < 2; ++t) { mbar_init(bar_s(t), 1); mbar_init(bar_p(t, 0), 128); mbar_init(bar_p(t, 1), 128); }
     mbar_init(bar_o, 1);
     fence_mbar_init();
   }
@@ -154,10 +191,16 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           mma_ss_x4<2, 2>(tS[t], a, b, idesc_s, 0u);
           mma_commit(bar_s(t));
         };
-        auto issue_pv = [&](int t, int st, int j) {
+        // O_t += P_t V, issued per 64-key half of P as soon as the fold warps have delivered it
+        auto issue_pv = [&](int t, int st, int j) -> bool {
           const uint64_t b = make_sdesc(sV(st), 128 * 128, 1024);
+          if (!mbar_wait(bar_p(t, 0), j & 1, &abort_flag, &g_fold_status, BAR_P)) return false;
+          tc_fence_after();
           mma_ts_x4<8, 128>(tO[t], tS[t], b, idesc_o, j > 0 ? 1u : 0u);
+          if (!mbar_wait(bar_p(t, 1), j & 1, &abort_flag, &g_fold_status, BAR_P)) return false;
+          tc_fence_after();
           mma_ts_x4<8, 128>(tO[t], tS[t] + 32, b + 512, idesc_o, 1u);
+          return true;
         };
         bool ok = mbar_wait(bar_q, 0, &abort_flag, &g_fold_status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, &g_fold_status, BAR_KV_FULL);
         if (ok) {
@@ -169,10 +212,10 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const int st = j % kStages;
           for (int t = 0; ok && t < 2; ++t) {
             if (j < n_t[t]) {
-              ok = mbar_wait(bar_p(t), j & 1, &abort_flag, &g_fold_status, BAR_P);
+              ELSA_FTR(2, j, 2 * t);
+              ok = issue_pv(t, st, j);
               if (!ok) break;
-              tc_fence_after();
-              issue_pv(t, st, j);
+              ELSA_FTR(2, j, 2 * t + 1);
             }
             if (t == 1) mma_commit(bar_kv_free(st));   // K(j), V(j) are no longer read once these MMAs retire
             if (j + 1 < n_t[t]) {
@@ -200,6 +243,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
     for (int j = 0; j < n_t[t]; ++j) {
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s(t), j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 0);
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -210,6 +254,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 32; ++i) sv[32 * cchunk + i] = __uint_as_float(r[i]);
       }
       tmem_wait_ld();
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 1);
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0 + t * 128);
@@ -220,15 +265,19 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           if (k0 + i > lim) sv[i] = -CUDART_INF_F;
       }
       // row max with four independent chains (a single 128-deep fmax chain costs ~500 cycles of latency)
+      // (three-input max: 64 instructions instead of 128)
       float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx[0] = fmaxf(mx[0], sv[i]); mx[1] = fmaxf(mx[1], sv[i + 1]);
-        mx[2] = fmaxf(mx[2], sv[i + 2]); mx[3] = fmaxf(mx[3], sv[i + 3]);
+      for (int i = 4; i < 124; i += 8) {
+        mx[0] = max3(mx[0], sv[i], sv[i + 1]); mx[1] = max3(mx[1], sv[i + 2], sv[i + 3]);
+        mx[2] = max3(mx[2], sv[i + 4], sv[i + 5]); mx[3] = max3(mx[3], sv[i + 6], sv[i + 7]);
       }
+      mx[0] = max3(mx[0], sv[124], sv[125]);
+      mx[1] = max3(mx[1], sv[126], sv[127]);
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 2);
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, move)) {
         const float m_new = fmaxf(m_ref, tmax);
@@ -257,20 +306,22 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
-          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          const float2 pp = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) ? exp2_fma_pair(x)
+                                                                                         : make_float2(fast_exp2(x.x), fast_exp2(x.y));
           ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
           pk[i] = pack2<T>(pp.x, pp.y);
         }
         tmem_st32(tS[t] + lane_off + 32 * h, pk);
+        tmem_wait_st();               // (also covers the O rescale stores above)
+        tc_fence_before();
+        mbar_arrive(bar_p(t, h));     // P V can start on this half while the other half's exponentials are computed
       }
       {
         const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
         const float2 s = __fadd2_rn(s01, s23);
         zsum += s.x + s.y;
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p(t));
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 3);
     }
 
     // epilogue: renormalise to the true max and write the summary row
@@ -406,6 +457,12 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }
+
+#ifdef ELSA_TRACE
+extern "C" int elsa_debug_fold_trace(long long* host_buf) {
+  return cudaMemcpyFromSymbol(host_buf, g_fold_trace, sizeof(long long) * 3 * 256 * 4) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 int fold_tc_status(int* status_out, int clear) {
   int v = 0;
