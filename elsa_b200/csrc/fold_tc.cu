@@ -31,7 +31,7 @@ static __device__ int g_fold_status = 0;
 
 // Optional per-phase timestamps of CTA (0,0,0) for tuning builds (-DELSA_TRACE); compiled out otherwise.
 #ifdef ELSA_TRACE
-__device__ long long g_fold_trace[3][256][4];
+__device__ long long g_fold_trace[4][256][8];
 #define ELSA_FTR(role, it, slot)                                                                              \
   do {                                                                                                        \
     if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_fold_trace[role][it][slot] = clock64(); \
@@ -47,12 +47,20 @@ constexpr int kTileBytes = 128 * 64 * 2;                          // one 128 x 6
 constexpr int kFoldSmem = (2 + 2 * kStages) * kTileBytes + 1024;  // + alignment slack
 constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MMA issuer, 2 idle warps)
 constexpr uint32_t kTmemCols = 512;
+#ifdef ELSA_VAR_SWAP
+constexpr int kProducerWarp = 9, kIssuerWarp = 8;
+#else
+constexpr int kProducerWarp = 8, kIssuerWarp = 9;
+#endif
 constexpr float kRescaleThreshold = 8.0f;
 // every kPolyEvery-th pair of exponentials is evaluated on the FMA pipe; 0 = never.  Measured at 2 (half of them):
 // 6 % slower -- the fold warps are bound by instruction issue (two warps per scheduler), not by the ex2 unit.
-constexpr int kPolyEvery = 0;
+#ifndef ELSA_POLY_EVERY
+#define ELSA_POLY_EVERY 0
+#endif
+constexpr int kPolyEvery = ELSA_POLY_EVERY;
 
-enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6 };
+enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6, BAR_SFREE = 7, BAR_PV = 8 };
 
 struct FoldTcParams {
   float* m; float* z; void* s;
@@ -105,7 +113,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FoldTcParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kStages + 8];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 11];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -136,16 +144,21 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t bar_q = bar0;
   auto bar_kv_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_kv_free = [&](int st) { return bar0 + 8 * (1 + kStages + st); };
-  auto bar_s = [&](int t) { return bar0 + 8 * (1 + 2 * kStages + t); };
+  const uint32_t bar_s = bar0 + 8 * (1 + 2 * kStages);   // S(j) of both tiles is in TMEM (slot 2 + 2 * kStages is unused)
   auto bar_p = [&](int t, int h) { return bar0 + 8 * (3 + 2 * kStages + 2 * t + h); };   // per (tile, 64-key half of P)
   const uint32_t bar_o = bar0 + 8 * (7 + 2 * kStages);
+  auto bar_sfree = [&](int t) { return bar0 + 8 * (8 + 2 * kStages + t); };   // the fold warps hold S_t in registers
+  const uint32_t bar_pv0 = bar0 + 8 * (10 + 2 * kStages);                     // P_0 V of the current key tile has retired
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int st = 0; st < kStages; ++st) { mbar_init(bar_kv_full(st), 1); mbar_init(bar_kv_free(st), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(bar_s(t), 1); mbar_init(bar_p(t, 0), 128); mbar_init(bar_p(t, 1), 128); }
+    for (int t = 0; t < 2; ++t) { mbar_init(bar_p(t, 0), 128); mbar_init(bar_p(t, 1), 128); }
     mbar_init(bar_o, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_sfree(0), 128); mbar_init(bar_sfree(1), 128);
+    mbar_init(bar_pv0, 1);
     fence_mbar_init();
   }
   if (warp == 8) {
@@ -158,14 +171,15 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tS[2] = {tmem_base, tmem_base + 128};
   const uint32_t tO[2] = {tmem_base + 256, tmem_base + 320};
+  const uint32_t tP[2] = {tmem_base + 384, tmem_base + 448};
 
   // register budget: the fold warps hold a whole 128-column score row per thread; the producer / issuer
-  // warpgroup needs almost nothing (3 x 128 threads: 232 + 232 + 40 registers per thread <= 64 K).  Each role
+  // warpgroup needs almost nothing (3 x 128 threads: 232 + 232 + 40 = 3 x 168, the launch allocation; setmaxnreg.inc waits, unbounded, until the pool has the registers, so the three budgets must never add up to more).  Each role
   // branch starts with its setmaxnreg and runs to the common exit, so the allocator sees one budget per branch.
 
   if (warp >= 8) {
     reg_dec<40>();
-    if (n_max > 0 && warp == 8) {
+    if (n_max > 0 && warp == kProducerWarp) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
         prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -180,51 +194,62 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           tma_load_3d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, bh);
         }
       }
-    } else if (n_max > 0 && warp == 9) {
+    } else if (n_max > 0 && warp == kIssuerWarp) {
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
         constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
         constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // S = Q K^T : A, B K-major
         constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // O += P V  : A in TMEM, B (V) MN-major
-        auto issue_s = [&](int t, int st) {
-          const uint64_t a = make_sdesc(sQ[t], 16, 1024), b = make_sdesc(sK(st), 16, 1024);
-          mma_ss_x4<2, 2>(tS[t], a, b, idesc_s, 0u);
-          mma_commit(bar_s(t));
-        };
-        // O_t += P_t V, issued per 64-key half of P as soon as the fold warps have delivered it
-        auto issue_pv = [&](int t, int st, int j) -> bool {
-          const uint64_t b = make_sdesc(sV(st), 128 * 128, 1024);
-          if (!mbar_wait(bar_p(t, 0), j & 1, &abort_flag, &g_fold_status, BAR_P)) return false;
-          tc_fence_after();
-          mma_ts_x4<8, 128>(tO[t], tS[t], b, idesc_o, j > 0 ? 1u : 0u);
-          if (!mbar_wait(bar_p(t, 1), j & 1, &abort_flag, &g_fold_status, BAR_P)) return false;
-          tc_fence_after();
-          mma_ts_x4<8, 128>(tO[t], tS[t] + 32, b + 512, idesc_o, 1u);
-          return true;
-        };
+        // shared-memory descriptors are loop invariants: every instruction between two tcgen05.mma idles the pipe
+        const uint64_t dq[2] = {make_sdesc(sQ[0], 16, 1024), make_sdesc(sQ[1], 16, 1024)};
+        const uint64_t dk0 = make_sdesc(sK(0), 16, 1024), dv0 = make_sdesc(sV(0), 128 * 128, 1024);
+        constexpr uint64_t kStageStep = (2 * kTileBytes) >> 4;   // descriptor address field counts 16-byte units
         bool ok = mbar_wait(bar_q, 0, &abort_flag, &g_fold_status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, &g_fold_status, BAR_KV_FULL);
         if (ok) {
           tc_fence_after();
-          for (int t = 0; t < 2; ++t)
-            if (n_t[t] > 0) issue_s(t, 0);
+          if (n_t[0] > 0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0, idesc_s, 0u);
+          if (n_t[1] > 0) mma_ss_x4<2, 2>(tS[1], dq[1], dk0, idesc_s, 0u);
+          mma_commit(bar_s);
         }
-        for (int j = 0; ok && j < n_max; ++j) {
-          const int st = j % kStages;
-          for (int t = 0; ok && t < 2; ++t) {
-            if (j < n_t[t]) {
-              ELSA_FTR(2, j, 2 * t);
-              ok = issue_pv(t, st, j);
-              if (!ok) break;
-              ELSA_FTR(2, j, 2 * t + 1);
-            }
-            if (t == 1) mma_commit(bar_kv_free(st));   // K(j), V(j) are no longer read once these MMAs retire
-            if (j + 1 < n_t[t]) {
-              const int sn = (j + 1) % kStages;
-              ok = mbar_wait(bar_kv_full(sn), ((j + 1) / kStages) & 1, &abort_flag, &g_fold_status, BAR_KV_FULL);
+        for (int jb = 0; ok && jb < n_max; jb += kStages) {
+#pragma unroll
+          for (int u = 0; u < kStages; ++u) {
+            const int j = jb + u;
+            if (j >= n_max || !ok) break;
+            const int un = (u + 1) % kStages;
+            ELSA_FTR(2, j, 4);
+            // S(j+1) of both tiles as soon as the fold warps have pulled S(j) into registers: the next scores
+            // are computed while the current exponentials run, so the fold warps never wait for the tensor pipe
+            const bool s0 = j + 1 < n_t[0], s1 = j + 1 < n_t[1];
+            if (s0 || s1) {
+              ok = mbar_wait(bar_kv_full(un), ((j + 1) / kStages) & 1, &abort_flag, &g_fold_status, BAR_KV_FULL) &&
+                   (!s0 || mbar_wait(bar_sfree(0), j & 1, &abort_flag, &g_fold_status, BAR_SFREE)) &&
+                   (!s1 || mbar_wait(bar_sfree(1), j & 1, &abort_flag, &g_fold_status, BAR_SFREE));
               if (!ok) break;
               tc_fence_after();
-              issue_s(t, sn);
+              ELSA_FTR(2, j, 0);
+              if (s0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0 + un * kStageStep, idesc_s, 0u);
+              if (s1) mma_ss_x4<2, 2>(tS[1], dq[1], dk0 + un * kStageStep, idesc_s, 0u);
+              mma_commit(bar_s);
+              ELSA_FTR(2, j, 1);
             }
+            // O_t += P_t V, issued per 64-key half of P as soon as the fold warps have delivered it
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              if (j < n_t[t]) {
+                if (!(ok = mbar_wait(bar_p(t, 0), j & 1, &abort_flag, &g_fold_status, BAR_P))) break;
+                tc_fence_after();
+                mma_ts_x4<8, 128>(tO[t], tP[t], dv0 + u * kStageStep, idesc_o, j > 0 ? 1u : 0u);
+                if (!(ok = mbar_wait(bar_p(t, 1), j & 1, &abort_flag, &g_fold_status, BAR_P))) break;
+                tc_fence_after();
+                mma_ts_x4<8, 128>(tO[t], tP[t] + 32, dv0 + u * kStageStep + 512, idesc_o, 1u);
+                ELSA_FTR(2, j, 2 + t);
+                if (t == 0) mma_commit(bar_pv0);
+              }
+            }
+            // K(j), V(j) are no longer read once these MMAs retire; for tile 1 the same arrival says that
+            // P_1 V has retired (P_1 may be overwritten, O_1 may be rescaled)
+            if (ok) mma_commit(bar_kv_free(u));
           }
         }
         if (ok) mma_commit(bar_o);
@@ -242,8 +267,10 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(t), j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 6);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 0);
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 0);
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -254,7 +281,10 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 32; ++i) sv[32 * cchunk + i] = __uint_as_float(r[i]);
       }
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_sfree(t));      // S_t may be overwritten with the next tile's scores
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 1);
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 1);
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0 + t * 128);
@@ -274,10 +304,24 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       mx[0] = max3(mx[0], sv[124], sv[125]);
       mx[1] = max3(mx[1], sv[126], sv[127]);
+#ifdef ELSA_VAR_NOMAX
+      float tmax = sv[5] + 30.f;
+#else
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+#endif
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 2);
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 2);
+      if (j > 0) {
+        // P_t V of the previous key tile must have retired before P_t is overwritten or O_t rescaled
+        const uint32_t bpv = t == 0 ? bar_pv0 : bar_kv_free((j - 1) % kStages);
+        const uint32_t par = t == 0 ? ((j - 1) & 1) : (((j - 1) / kStages) & 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(bpv, par, &abort_flag, &g_fold_status, BAR_PV))) { alive = false; break; }
+        tc_fence_after();
+      }
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 3);
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 3);
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, move)) {
         const float m_new = fmaxf(m_ref, tmax);
@@ -305,23 +349,48 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
+#ifdef ELSA_VAR_SCALAR
+          const float2 x = make_float2(fmaf(sv[64 * h + 2 * i], c, -m_use), fmaf(sv[64 * h + 2 * i + 1], c, -m_use));
+#else
           const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
+#endif
+#ifdef ELSA_VAR_NOEX2
+          const float2 pp = x;
+#else
           const float2 pp = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) ? exp2_fma_pair(x)
                                                                                          : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+#endif
+#ifdef ELSA_VAR_SCALAR
+          ps[i & 3].x += pp.x; ps[i & 3].y += pp.y;
+#else
           ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
+#endif
+#ifdef ELSA_VAR_NOCVT
+          pk[i] = __float_as_uint(pp.x) ^ __float_as_uint(pp.y);
+#else
           pk[i] = pack2<T>(pp.x, pp.y);
+#endif
         }
-        tmem_st32(tS[t] + lane_off + 32 * h, pk);
+#ifdef ELSA_VAR_NOPST
+        if (pk[3] == 0x12345678u) tmem_st32(tP[t] + lane_off + 32 * h, pk);
+#else
+        tmem_st32(tP[t] + lane_off + 32 * h, pk);
+#endif
         tmem_wait_st();               // (also covers the O rescale stores above)
         tc_fence_before();
         mbar_arrive(bar_p(t, h));     // P V can start on this half while the other half's exponentials are computed
+        if (h == 0 && (warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 4);
+        if (h == 0 && warp == 1 && lane == 0) ELSA_FTR(3, j, 4);
       }
       {
         const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
         const float2 s = __fadd2_rn(s01, s23);
         zsum += s.x + s.y;
       }
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 3);
+      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 5);
+      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 5);
+      if ((warp & 3) == 1 && lane == 0) ELSA_FTR(t, j, 6);
+      if ((warp & 3) == 3 && lane == 0) ELSA_FTR(t, j, 7);
     }
 
     // epilogue: renormalise to the true max and write the summary row
@@ -460,7 +529,7 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
 
 #ifdef ELSA_TRACE
 extern "C" int elsa_debug_fold_trace(long long* host_buf) {
-  return cudaMemcpyFromSymbol(host_buf, g_fold_trace, sizeof(long long) * 3 * 256 * 4) == cudaSuccess ? 0 : 3;
+  return cudaMemcpyFromSymbol(host_buf, g_fold_trace, sizeof(long long) * 4 * 256 * 8) == cudaSuccess ? 0 : 3;
 }
 #endif
 
