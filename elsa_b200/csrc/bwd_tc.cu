@@ -2,10 +2,10 @@
 // fp16 / bf16 inputs, head dim 64, causal or not, no bias.  Five contractions per (key tile, query
 // tile) pair -- the algorithmic minimum -- all as tcgen05.mma with TMEM accumulators:
 //
-//   S^T  = K Q^T          [128 keys x 128 queries]   smem x smem            -> TMEM
-//   dP^T = V dO^T         [128 x 128]                smem x smem            -> TMEM
-//   dV  += P^T dO         [128 keys x 64]            TMEM (P^T over S^T)   x smem (dO, MN-major)
-//   dK  += dS^T Q         [128 keys x 64]            TMEM (dS^T over dP^T) x smem (Q, MN-major)
+//   S^T  = K Q^T          [128 keys x 128 queries]   TMEM (K) x smem (Q, K-major)          N = 128
+//   dP^T = V dO^T         [128 x 128]                TMEM (V) x smem (dO, K-major)         N = 128
+//   dV  += P^T dO         [128 keys x 64]            TMEM (P^T, in the dP^T columns)  x smem (dO, MN-major)
+//   dK  += dS^T Q         [128 keys x 64]            TMEM (dS^T, in the dP^T columns) x smem (Q, MN-major)
 //   dQ   = dS K           [128 queries x 64]         smem (dS^T, M-major A) x smem (K, MN-major)
 //
 // One CTA (1 per SM, 512 threads) owns one 128-key tile of one (batch*head) and streams the query
@@ -16,24 +16,30 @@
 // global memory by a TMA reduce-add (cp.reduce.async.bulk.tensor) of the staged tile, and a last
 // pass scales and rounds it.
 //
-// Each 128-query tile is processed as two 64-query halves that are half an iteration apart: while
-// the warps of half a are in their exp2 / dS phase the tensor pipe runs the contractions of half b
-// and vice versa.  Each half hands its P^T / dS^T back in two 32-query chunks so that dV / dK start on the
-// first chunk while the second is being computed.  (Producing S^T / dP^T for the whole tile with N = 128
-// instructions was measured slower: both compute warpgroups then run at the same time and share the ex2 unit.)
+// Pipeline.  A compute thread owns one key row and 64 of the 128 query columns and works in two phases:
+//   A  load its S^T columns, release them (bar_lds), P^T = exp2(S^T c - LSE) kept in registers (fp32);
+//   B  wait for dP^T, then per 32-query chunk: load dP^T, dS^T = P^T (dP^T - D), write the 16-bit P^T / dS^T
+//      over the chunk's own dP^T columns (and dS^T to shared memory), hand the chunk to the issuer (bar_pds).
+// Because P^T no longer overlays S^T, the S^T columns are free as soon as phase A has loaded them: the issuer
+// produces S^T of the NEXT query tile at the top of the iteration, so phase A of the next tile never waits
+// and runs while the tensor pipe is busy with dV / dK / dP^T(next) / dQ of this one.  dP^T(next) follows the
+// last dV / dK of this tile (same columns) and arrives during phase A.  The ring stage (Q, dO, -LSE, -D) is
+// handed back to the producer right after dV / dK -- dQ reads only dS^T and K -- so the next-but-one tile's
+// loads have a whole dP^T + dQ + S^T of lead time.
 //
-//   warps 0-3   half a (query columns 0-63): one thread per key row: exp2, dS, packing
-//   warps 4-7   half b (query columns 64-127)
+//   warps 0-3   query columns 0-63  : one thread per key row (phases A and B above)
+//   warps 4-7   query columns 64-127
 //   warps 8-11  dQ drain: one thread per query row: TMEM -> registers -> swizzled smem -> TMA reduce-add
 //   warp 12     TMA producer: K, V once; Q_i, dO_i, -LSE_i, -D_i into a 2-stage ring
 //   warp 13     MMA issuer
-//   (register budget re-balanced with setmaxnreg: 168 / 168 / 96 / 80 per thread)
+//   (register budget re-balanced with setmaxnreg: 168 / 168 / 96 / 80 per thread = 4 x 128, the launch allocation)
 //
-// TMEM columns: S^T_a [0,64) S^T_b [64,128) dP^T_a [128,192) dP^T_b [192,256) dV [256,320)
-// dK [320,384) dQ [384,448) K [448,480) V [480,512).  The 16-bit P^T_h / dS^T_h overlay the first 32 columns of
-// S^T_h / dP^T_h.  K and V are copied once into TMEM (16-bit pairs, one key per lane) so that S^T and dP^T
-// take their A operand from TMEM: the kernel is shared-memory-bandwidth bound and this removes 64 KB of
-// operand reads per 128 x 128 pair.
+// TMEM columns: S^T [0,128) dP^T [128,256) dV [256,320) dK [320,384) dQ [384,448) K [448,480) V [480,512).
+// Within the 64 dP^T columns of a half, chunk ch keeps P^T in [32 ch, +16) and dS^T in [32 ch + 16, +16).
+// K and V are copied once into TMEM (16-bit pairs, one key per lane) so that S^T and dP^T take their A operand
+// from TMEM: the kernel is shared-memory-bandwidth sensitive and this removes 64 KB of operand reads per
+// 128 x 128 pair.  (Measured alternatives at B=1 H=8 N=16384: P^T / dS^T as shared-memory A operands of dV / dK,
+// 2.01 ms; two 64-query halves half an iteration apart with N = 64 S^T / dP^T, 1.80 ms; this design 1.64 ms.)
 //
 // -LSE and -D are read from a padded [BH][ceil(N/128)*128] layout whose padding holds -LSE = -inf,
 // -D = 0, so that query rows beyond N produce P = 0 without a branch.
@@ -69,8 +75,15 @@ constexpr int kStageBytes = 2 * kTile + 2 * kVecBytes;
 constexpr int kBwdSmem = 2 * kTile + kQStages * kStageBytes + 4 * kTile + 2 * kTile + 1024;
 constexpr int kThreads = 512;
 constexpr uint32_t kTmemCols = 512;
+#ifndef ELSA_BWD_POLY_EVERY
+#define ELSA_BWD_POLY_EVERY 0
+#endif
+// in every kPolyEvery-th group of four exponentials two are evaluated on the FMA pipe (0 = none).  Measured at the
+// 16K shape: 1 (half of them) 1.67 ms, 2 (a quarter) 1.62 ms, 0 1.64-1.67 ms, and the causal case 10 % slower
+// with either: no gain, so it stays off.
+constexpr int kPolyEvery = ELSA_BWD_POLY_EVERY;
 
-enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS = 15, BAR_DQ_FULL = 16, BAR_DQ_FREE = 17, BAR_DONE = 18, BAR_KVT = 19 };
+enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS = 15, BAR_DQ_FULL = 16, BAR_DQ_FREE = 17, BAR_DONE = 18, BAR_KVT = 19, BAR_LDS = 20, BAR_DP = 21 };
 
 struct BwdTcParams {
   const float* nlse_pad; const float* nd_pad;  // [BH][n_pad]: -LSE, -D
@@ -83,10 +96,6 @@ struct BwdTcParams {
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&w)[16]) {
@@ -103,7 +112,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
               const __grid_constant__ CUtensorMap tmap_dq, const BwdTcParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kQStages + 10];
+  __shared__ __align__(8) uint64_t bars[2 * kQStages + 13];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -130,15 +139,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   auto bar_q_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_q_free = [&](int st) { return bar0 + 8 * (1 + kQStages + st); };
   const uint32_t barx = bar0 + 8 * (1 + 2 * kQStages);
-  auto bar_sp = [&](int h) { return barx + 8 * h; };
+  const uint32_t bar_s = barx, bar_dp = barx + 8;          // S^T / dP^T of the current query tile are in TMEM
   auto bar_pds = [&](int h, int ch) { return barx + 16 + 8 * (2 * h + ch); };   // per (half, 32-query chunk)
   const uint32_t bar_dq_free = barx + 48, bar_done = barx + 56, bar_kvt = barx + 64;
+  const uint32_t bar_lds = barx + 72;
+  auto bar_stage_free = [&](int st) { return barx + 80 + 8 * st; };   // dV / dK of the tile in ring stage st have retired                      // all 256 compute threads hold their S^T columns in registers
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_kv, 1);
     for (int st = 0; st < kQStages; ++st) { mbar_init(bar_q_full(st), 1); mbar_init(bar_q_free(st), 1); }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar_sp(h), 1); mbar_init(bar_pds(h, 0), 128); mbar_init(bar_pds(h, 1), 128); }
+    mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_lds, 256);
+    mbar_init(bar_stage_free(0), 1); mbar_init(bar_stage_free(1), 1);
+    for (int h = 0; h < 2; ++h) { mbar_init(bar_pds(h, 0), 128); mbar_init(bar_pds(h, 1), 128); }
     mbar_init(bar_dq_free, 128);
     mbar_init(bar_done, 1);
     mbar_init(bar_kvt, 256);
@@ -154,6 +167,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 320, tdQ = tmem_base + 384;
   const uint32_t tK = tmem_base + 448, tV = tmem_base + 480;
+  const uint32_t tS0 = tmem_base, tdP0 = tmem_base + 128;    // 128 query columns each
   auto tS = [&](int h) { return tmem_base + 64 * h; };
   auto tdP = [&](int h) { return tmem_base + 128 + 64 * h; };
 
@@ -167,7 +181,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       tma_load_3d(sV, &tmap_v, bar_kv, 0, k0, bh);
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kQStages;
-        if (it >= kQStages && !mbar_wait(bar_q_free(st), ((it / kQStages) - 1) & 1, &abort_flag, &g_bwd_status, BAR_Q_FREE)) break;
+        if (it >= kQStages && !mbar_wait(bar_stage_free(st), ((it / kQStages) - 1) & 1, &abort_flag, &g_bwd_status, BAR_Q_FREE)) break;
         const int qrow = (it_begin + it) * 128;
         mbar_arrive_expect_tx(bar_q_full(st), kStageBytes);
         tma_load_3d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, bh);
@@ -194,77 +208,74 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         dds[st] = make_sdesc(sDS0 + st * 2 * kTile, 128 * 128, 1024);       // dS^T buffer as M-major A of dQ
       }
       static_assert(kQStages == 2, "the issuer loop is unrolled over the two ring stages");
-      constexpr uint32_t idesc_st = make_idesc(fmt, 0, 0, 128, 64);   // S^T_h, dP^T_h: A (TMEM) and B K-major, N = 64 queries
-      uint64_t dq_k[2][2], ddo_k[2][2];
+      constexpr uint32_t idesc_st = make_idesc(fmt, 0, 0, 128, 128);  // S^T, dP^T: A (TMEM) and B K-major, N = 128 queries
+      uint64_t dq_k[2], ddo_k[2];
 #pragma unroll
       for (int st = 0; st < 2; ++st) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          dq_k[st][h] = make_sdesc(sQ(st) + h * 8192, 16, 1024);     // Q_h as K-major B of S^T_h
-          ddo_k[st][h] = make_sdesc(sDO(st) + h * 8192, 16, 1024);   // dO_h as K-major B of dP^T_h
-        }
+        dq_k[st] = make_sdesc(sQ(st), 16, 1024);     // Q tile as K-major B of S^T
+        ddo_k[st] = make_sdesc(sDO(st), 16, 1024);   // dO tile as K-major B of dP^T
       }
       using I0 = std::integral_constant<int, 0>;
       using I1 = std::integral_constant<int, 1>;
-      // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for the 64 queries of half h of ring stage st
-      auto issue_sp = [&](auto ST, auto H) {
-        constexpr int st = decltype(ST)::value, h = decltype(H)::value;
-        mma_ts_x4<8, 2>(tS(h), tK, dq_k[st][h], idesc_st, 0u);
-        mma_ts_x4<8, 2>(tdP(h), tV, ddo_k[st][h], idesc_st, 0u);
-        mma_commit(bar_sp(h));
-      };
-      // dV += P^T_h dO_h, dK += dS^T_h Q_h (contraction over the 64 queries of half h), issued per 32-query chunk
-      // as soon as the compute warps have delivered that chunk of P^T_h / dS^T_h
-      auto issue_dkv = [&](auto ST, auto H, int it, uint32_t acc) -> bool {
-        constexpr int st = decltype(ST)::value, h = decltype(H)::value;
-        if (!mbar_wait(bar_pds(h, 0), it & 1, &abort_flag, &g_bwd_status, BAR_PDS)) return false;
-        tc_fence_after();
-        mma_ts_x2<8, 128>(tdV, tS(h), ddo_mn[st][h], idesc_kv, acc);
-        mma_ts_x2<8, 128>(tdK, tdP(h), dq_mn[st][h], idesc_kv, acc);
-        if (!mbar_wait(bar_pds(h, 1), it & 1, &abort_flag, &g_bwd_status, BAR_PDS)) return false;
-        tc_fence_after();
-        mma_ts_x2<8, 128>(tdV, tS(h) + 16, ddo_mn[st][h] + 256, idesc_kv, 1u);
-        mma_ts_x2<8, 128>(tdK, tdP(h) + 16, dq_mn[st][h] + 256, idesc_kv, 1u);
-        return true;
+      // dV += P^T_h dO_h, dK += dS^T_h Q_h over the 32 queries of chunk ch of half h (two K-steps each); the 16-bit
+      // P^T / dS^T of chunk ch sit in columns [32 ch, +16) / [32 ch + 16, +16) of the half's dP^T columns
+      auto issue_dkv = [&](auto ST, auto H, auto CH, uint32_t acc) {
+        constexpr int st = decltype(ST)::value, h = decltype(H)::value, ch = decltype(CH)::value;
+        mma_ts_x2<8, 128>(tdV, tdP(h) + 32 * ch, ddo_mn[st][h] + 256 * ch, idesc_kv, acc);
+        mma_ts_x2<8, 128>(tdK, tdP(h) + 32 * ch + 16, dq_mn[st][h] + 256 * ch, idesc_kv, acc);
       };
       bool ok = mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV) &&
                 mbar_wait(bar_kvt, 0, &abort_flag, &g_bwd_status, BAR_KVT) &&
                 (n_it == 0 || mbar_wait(bar_q_full(0), 0, &abort_flag, &g_bwd_status, BAR_Q_FULL));
       if (ok && n_it > 0) {
         tc_fence_after();
-        issue_sp(I0{}, I0{});
-        issue_sp(I0{}, I1{});
+        mma_ts_x4<8, 2>(tS0, tK, dq_k[0], idesc_st, 0u);
+        mma_commit(bar_s);
+        mma_ts_x4<8, 2>(tdP0, tV, ddo_k[0], idesc_st, 0u);
+        mma_commit(bar_dp);
       }
-      // one iteration on ring stage ST (the next one is on the other stage).  The two 64-query halves are half an
-      // iteration apart: while the warps of one half are in their exp2 / dS phase the pipe runs the other half's MMAs.
+      // One iteration on ring stage ST (the next one is on the other stage).  S^T of the NEXT query tile is issued
+      // as soon as the compute warps hold the current S^T in registers (their exp2 phase then overlaps the
+      // contractions below); dP^T of the next tile follows dV / dK of this one, whose A operands live in the
+      // dP^T columns; dQ comes last.
       auto iteration = [&](int it, auto ST) {
         constexpr int st = decltype(ST)::value;
-        using SN = std::integral_constant<int, st ^ 1>;
         const bool more = it + 1 < n_it;
-        // half a of this iteration, then S/dP of half a of the next one
+        const uint32_t pit = it & 1;
         ELSA_TR(0, it, 0);
-        ok = issue_dkv(ST, I0{}, it, it == 0 ? 0u : 1u);
-        if (!ok) return;
-        ELSA_TR(4, it, 0);
         if (more) {
-          ok = mbar_wait(bar_q_full(st ^ 1), ((it + 1) / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL);
+          ok = mbar_wait(bar_q_full(st ^ 1), ((it + 1) / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL) &&
+               mbar_wait(bar_lds, pit, &abort_flag, &g_bwd_status, BAR_LDS);
           if (!ok) return;
           tc_fence_after();
-          issue_sp(SN{}, I0{});
+          mma_ts_x4<8, 2>(tS0, tK, dq_k[st ^ 1], idesc_st, 0u);
+          mma_commit(bar_s);
         }
         ELSA_TR(0, it, 1);
-        // half b, then dQ of the whole tile, then S/dP of half b of the next one
+        if (!(ok = mbar_wait(bar_pds(0, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        tc_fence_after();
+        issue_dkv(ST, I0{}, I0{}, it == 0 ? 0u : 1u);
+        if (!(ok = mbar_wait(bar_pds(1, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        tc_fence_after();
+        issue_dkv(ST, I1{}, I0{}, 1u);
+        if (!(ok = mbar_wait(bar_pds(0, 1), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        tc_fence_after();
+        issue_dkv(ST, I0{}, I1{}, 1u);
+        if (!(ok = mbar_wait(bar_pds(1, 1), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        tc_fence_after();
+        issue_dkv(ST, I1{}, I1{}, 1u);
         ELSA_TR(0, it, 2);
-        ok = issue_dkv(ST, I1{}, it, 1u);
-        if (ok && it > 0) ok = mbar_wait(bar_dq_free, (it - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE);
-        if (!ok) return;
-        ELSA_TR(4, it, 1);
+        // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K): the producer may refill
+        // the ring stage now, a whole dP^T + dQ ahead of the commit that hands dQ to the drain warps
+        mma_commit(bar_stage_free(st));
+        if (more) {
+          mma_ts_x4<8, 2>(tdP0, tV, ddo_k[st ^ 1], idesc_st, 0u);
+          mma_commit(bar_dp);
+        }
+        if (it > 0 && !(ok = mbar_wait(bar_dq_free, (it - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE))) return;
         mma_ss_x4<128, 128>(tdQ, dds[st], bk_mn, idesc_dq, 0u);
         mma_ss_x4<128, 128>(tdQ, dds[st] + 512, bk_mn + 512, idesc_dq, 1u);
-        ELSA_TR(4, it, 2);
-        mma_commit(bar_q_free(st));   // dQ(it) is complete and ring stage st is free: one commit serves the drain warps and the producer
-        ELSA_TR(4, it, 3);
-        if (more) issue_sp(SN{}, I1{});
+        mma_commit(bar_q_free(st));   // dQ(it) is complete: the drain warps may read it
         ELSA_TR(0, it, 3);
       };
       for (int it = 0; ok && it < n_it; it += 2) {
@@ -345,9 +356,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (int it = 0; alive && it < n_it; ++it) {
       const int st = it % kQStages;
       const int q_tile0 = (it_begin + it) * 128;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_sp(half), it & 1, &abort_flag, &g_bwd_status, BAR_SP))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, it & 1, &abort_flag, &g_bwd_status, BAR_SP))) { alive = false; break; }
       // the row statistics of this stage were written by the bulk copies that complete on q_full: observe that
-      // barrier directly (it completed before the MMAs behind bar_sp were issued, so this never spins)
+      // barrier directly (it completed before the MMAs behind bar_s were issued, so this never spins)
       if (!__all_sync(0xffffffffu, mbar_wait(bar_q_full(st), (it / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL))) { alive = false; break; }
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 0);
       tc_fence_after();
@@ -355,42 +366,56 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       const float4* nd4 = reinterpret_cast<const float4*>(smem_gen + (sND(st) - smem_base)) + half * 16;
       const bool masked = cta_tail || (prm.is_causal && q_tile0 < k0 + 128);   // only the diagonal tile / the last key tile
       uint8_t* ds_row = smem_gen + (sDS0 - smem_base) + (it & 1) * 2 * kTile + half * kTile + row * 128;
+
+      // ---- phase A: P^T = exp2(S^T * c - LSE) for this thread's 64 queries, kept in registers as fp32 ----
+      float p[64];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tS(half) + lane_off, r0);
+        tmem_ld32(tS(half) + lane_off + 32, r1);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar_lds);       // the S^T columns may be overwritten with the next query tile's scores
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { p[i] = __uint_as_float(r0[i]); p[32 + i] = __uint_as_float(r1[i]); }
+      }
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        const float4 nl = nl4[g];                                   // -LSE of 4 queries (warp-wide broadcast read)
+        const float2 x0 = __ffma2_rn(make_float2(p[4 * g], p[4 * g + 1]), c2, make_float2(nl.x, nl.y));
+        const float2 x1 = __ffma2_rn(make_float2(p[4 * g + 2], p[4 * g + 3]), c2, make_float2(nl.z, nl.w));
+        p[4 * g] = fast_exp2(x0.x); p[4 * g + 1] = fast_exp2(x0.y);
+        if (kPolyEvery > 0 && g % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
+          const float2 e1 = exp2_fma_pair(x1);                    // FMA pipe instead of the ex2 unit
+          p[4 * g + 2] = e1.x; p[4 * g + 3] = e1.y;
+        } else {
+          p[4 * g + 2] = fast_exp2(x1.x); p[4 * g + 3] = fast_exp2(x1.y);
+        }
+        if (masked) {
+          const int qc = q_tile0 + half * 64 + 4 * g;               // first query of this group of 4
+          const bool causal = prm.is_causal;
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            p[4 * g + e] = (key_ok && (!causal || qc + e >= key)) ? p[4 * g + e] : 0.f;
+        }
+      }
+      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
+
+      // ---- phase B: dS^T = P^T * (dP^T - D); P^T and dS^T (16-bit) handed to dV / dK in two 32-query chunks ----
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dp, it & 1, &abort_flag, &g_bwd_status, BAR_DP))) { alive = false; break; }
+      tc_fence_after();
+      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 2);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
-        uint32_t rs[32], rp[32];
-#ifdef ELSA_VAR_NOTLD
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { rs[i] = 0x3c000000u + i + it; rp[i] = 0x3c100000u + i; }
-#else
-        tmem_ld32(tS(half) + lane_off + 32 * ch, rs);
+        uint32_t rp[32];
         tmem_ld32(tdP(half) + lane_off + 32 * ch, rp);
         tmem_wait_ld();
-#endif
-        if (ch == 0 && lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
         uint32_t pk[16], dsk[16];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-#ifdef ELSA_VAR_NOLDS
-          const float4 nl = make_float4(-1.f, -2.f, -3.f, -4.f), nd = make_float4(0.1f, 0.2f, 0.3f, 0.4f);
-#else
-          const float4 nl = nl4[ch * 8 + g], nd = nd4[ch * 8 + g];   // -LSE, -D of 4 queries (warp-wide broadcast reads)
-#endif
-          float2 x0 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g]), __uint_as_float(rs[4 * g + 1])), c2, make_float2(nl.x, nl.y));
-          float2 x1 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g + 2]), __uint_as_float(rs[4 * g + 3])), c2, make_float2(nl.z, nl.w));
-#ifdef ELSA_VAR_NOEXP
-          float2 p0 = x0, p1 = x1;
-#else
-          float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-          float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
-#endif
-          if (masked) {
-            const int qc = q_tile0 + half * 64 + ch * 32 + 4 * g;     // first query of this group of 4
-            const bool causal = prm.is_causal;
-            p0.x = (key_ok && (!causal || qc + 0 >= key)) ? p0.x : 0.f;
-            p0.y = (key_ok && (!causal || qc + 1 >= key)) ? p0.y : 0.f;
-            p1.x = (key_ok && (!causal || qc + 2 >= key)) ? p1.x : 0.f;
-            p1.y = (key_ok && (!causal || qc + 3 >= key)) ? p1.y : 0.f;
-          }
+          const float4 nd = nd4[ch * 8 + g];                        // -D of 4 queries
+          const float2 p0 = make_float2(p[32 * ch + 4 * g], p[32 * ch + 4 * g + 1]);
+          const float2 p1 = make_float2(p[32 * ch + 4 * g + 2], p[32 * ch + 4 * g + 3]);
           const float2 t0 = __fadd2_rn(make_float2(__uint_as_float(rp[4 * g]), __uint_as_float(rp[4 * g + 1])), make_float2(nd.x, nd.y));
           const float2 t1 = __fadd2_rn(make_float2(__uint_as_float(rp[4 * g + 2]), __uint_as_float(rp[4 * g + 3])), make_float2(nd.z, nd.w));
           const float2 d0 = __fmul2_rn(p0, t0), d1 = __fmul2_rn(p1, t1);
@@ -399,31 +424,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           dsk[2 * g] = pack2<T>(d0.x, d0.y);
           dsk[2 * g + 1] = pack2<T>(d1.x, d1.y);
         }
-        // 16-bit P^T_h over S^T_h and dS^T_h over dP^T_h: chunk ch lands in columns [16*ch, +16), which this
-        // thread has already consumed (it loaded columns [32*ch, +32) above).
-#ifndef ELSA_VAR_NOTST
-        tmem_st16(tS(half) + lane_off + 16 * ch, pk);
-        tmem_st16(tdP(half) + lane_off + 16 * ch, dsk);
-#else
-        if (pk[0] == 0x12345u && dsk[3] == 0x54321u) abort_flag = 2;
-#endif
-        // dS^T to shared memory: block `half`, row = key, 16-byte chunk (8 queries) index XOR (key & 7)
-#ifndef ELSA_VAR_NODS
+        // the 32 dP^T columns of this chunk are in registers: P^T goes over their first 16, dS^T over the other 16
+        tmem_st16(tdP(half) + lane_off + 32 * ch, pk);
+        tmem_st16(tdP(half) + lane_off + 32 * ch + 16, dsk);
+        // dS^T to shared memory for dQ: block `half`, row = key, 16-byte piece (8 queries) index XOR (key & 7)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = ch * 4 + g;
           *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (row & 7)) << 4)) =
               make_uint4(dsk[4 * g], dsk[4 * g + 1], dsk[4 * g + 2], dsk[4 * g + 3]);
         }
-#endif
-        // hand this 32-query chunk to the MMA issuer (dV / dK can start on it while the second chunk is computed)
-#ifndef ELSA_VAR_NOFENCE
+        // hand this 32-query chunk to the MMA issuer (dV / dK start on it while the second chunk is computed)
         fence_proxy_async_smem();
-#endif
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_pds(half, ch));
-        if (ch == 0 && lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 2);
       }
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 3);
     }

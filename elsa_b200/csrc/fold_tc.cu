@@ -69,23 +69,6 @@ struct FoldTcParams {
   float scale_log2;
 };
 
-// 2^x for a packed pair on the FMA pipe instead of the ex2 unit (16 results / clk / SM): round-to-nearest split
-// x = n + f with the 1.5 * 2^23 trick, degree-4 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error
-// 2.7e-6, far below the 16-bit rounding of P), then n is added into the exponent field.  x is clamped at -126.
-__device__ __forceinline__ float2 exp2_fma_pair(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.009570101276040077f, 0.009570101276040077f), make_float2(0.05591785907745361f, 0.05591785907745361f));
-  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
-  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
-  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
-  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
