@@ -1,23 +1,32 @@
 // Phase 1 on the 5th-generation tensor cores (tcgen05 + TMEM + TMA): the per-K-partition
 // (m, z, s) fold for fp16 / bf16 inputs with head dim 64, causal or not.
 //
-// One CTA (1 per SM: 160 KB of shared memory, 384 TMEM columns) owns TWO 128-row query tiles of one
+// One CTA (1 per SM: 160 KB of shared memory, all 512 TMEM columns) owns TWO 128-row query tiles of one
 // (batch*head) and one K partition, walked in 128-key tiles:
 //
 //   warp 8      TMA producer   Q tiles once; K and V tiles into a 4-stage ring (128-byte swizzle)
 //   warp 9      MMA issuer     S_t = Q_t K^T   (4 x tcgen05.mma 128x128x16, both operands in smem)
 //                              O_t += P_t V    (8 x tcgen05.mma 128x64x16, P from TMEM, V MN-major)
-//   warps 0-3   fold of tile 0 one thread per query row: S row from TMEM, running max, exp2, row sum,
-//   warps 4-7   fold of tile 1 P (16-bit) written back over S in TMEM, exp-rescale of O when the max moved
+//   warps 0-3   fold of tile 0 one thread per query row: S row from TMEM into registers, running max, exp2,
+//   warps 4-7   fold of tile 1 row sum, P (16-bit) into its own TMEM columns, exp-rescale of O when the max moved
 //
-// The two tiles ping-pong on the tensor pipe: while one tile's rows are in the exp2 phase the
-// other tile's MMAs run.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384); P_t
-// overlays the first 64 columns of S_t.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).  Because P has
+// its own columns, S_t is free as soon as the fold warps hold the row in registers (bar_sfree): the issuer
+// produces S_t of the NEXT key tile right then, so the fold warps never wait for scores.  P is handed to the
+// issuer in two 64-key halves (bar_p), P V of the first half runs while the second half's exponentials are
+// computed; the fold warps wait for P V of the previous key tile (bar_pv0 / bar_kv_free) only before they
+// overwrite P or rescale O.
 //
 // Exp-rescale merge: the fold keeps a reference max m_ref per row and only moves it (rescaling z
 // and the O accumulator in TMEM) when the tile max exceeds it by more than 2^8; the true running
 // max is tracked separately and the summary is renormalised to it in the epilogue, so the stored
 // (m, z, s) is the same monoid element the FP32-FMA kernel produces.
+//
+// Measured alternatives at B=1 H=8 N=16384 (this design: 0.755 ms): two threads per row (four fold
+// warpgroups of 64 columns each, half-row max exchanged through shared memory) 0.77-0.79 ms; a fixed
+// issue order that keeps the two tiles half a key tile apart 0.805 ms; half of the exponentials on the FMA
+// pipe 0.81 ms; no exponentials at all (timing only) 0.72 ms -- the kernel is bound by the chain
+// issuer -> TMEM -> fold warps -> TMEM -> issuer of each key tile, not by the ex2 unit.
 #include <type_traits>
 
 #include "kernels.cuh"
@@ -47,14 +56,10 @@ constexpr int kTileBytes = 128 * 64 * 2;                          // one 128 x 6
 constexpr int kFoldSmem = (2 + 2 * kStages) * kTileBytes + 1024;  // + alignment slack
 constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MMA issuer, 2 idle warps)
 constexpr uint32_t kTmemCols = 512;
-#ifdef ELSA_VAR_SWAP
-constexpr int kProducerWarp = 9, kIssuerWarp = 8;
-#else
 constexpr int kProducerWarp = 8, kIssuerWarp = 9;
-#endif
 constexpr float kRescaleThreshold = 8.0f;
 // every kPolyEvery-th pair of exponentials is evaluated on the FMA pipe; 0 = never.  Measured at 2 (half of them):
-// 6 % slower -- the fold warps are bound by instruction issue (two warps per scheduler), not by the ex2 unit.
+// 6 % slower -- the ex2 unit is not what bounds this kernel.
 #ifndef ELSA_POLY_EVERY
 #define ELSA_POLY_EVERY 0
 #endif
@@ -250,10 +255,8 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 6);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 0);
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 0);
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -267,7 +270,6 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(bar_sfree(t));      // S_t may be overwritten with the next tile's scores
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 1);
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 1);
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0 + t * 128);
@@ -287,15 +289,10 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       mx[0] = max3(mx[0], sv[124], sv[125]);
       mx[1] = max3(mx[1], sv[126], sv[127]);
-#ifdef ELSA_VAR_NOMAX
-      float tmax = sv[5] + 30.f;
-#else
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-#endif
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 2);
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 2);
       if (j > 0) {
         // P_t V of the previous key tile must have retired before P_t is overwritten or O_t rescaled
         const uint32_t bpv = t == 0 ? bar_pv0 : bar_kv_free((j - 1) % kStages);
@@ -304,7 +301,6 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
       }
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 3);
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 3);
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, move)) {
         const float m_new = fmaxf(m_ref, tmax);
@@ -332,38 +328,17 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-#ifdef ELSA_VAR_SCALAR
-          const float2 x = make_float2(fmaf(sv[64 * h + 2 * i], c, -m_use), fmaf(sv[64 * h + 2 * i + 1], c, -m_use));
-#else
           const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
-#endif
-#ifdef ELSA_VAR_NOEX2
-          const float2 pp = x;
-#else
           const float2 pp = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) ? exp2_fma_pair(x)
                                                                                          : make_float2(fast_exp2(x.x), fast_exp2(x.y));
-#endif
-#ifdef ELSA_VAR_SCALAR
-          ps[i & 3].x += pp.x; ps[i & 3].y += pp.y;
-#else
           ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
-#endif
-#ifdef ELSA_VAR_NOCVT
-          pk[i] = __float_as_uint(pp.x) ^ __float_as_uint(pp.y);
-#else
           pk[i] = pack2<T>(pp.x, pp.y);
-#endif
         }
-#ifdef ELSA_VAR_NOPST
-        if (pk[3] == 0x12345678u) tmem_st32(tP[t] + lane_off + 32 * h, pk);
-#else
         tmem_st32(tP[t] + lane_off + 32 * h, pk);
-#endif
         tmem_wait_st();               // (also covers the O rescale stores above)
         tc_fence_before();
         mbar_arrive(bar_p(t, h));     // P V can start on this half while the other half's exponentials are computed
         if (h == 0 && (warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 4);
-        if (h == 0 && warp == 1 && lane == 0) ELSA_FTR(3, j, 4);
       }
       {
         const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
@@ -371,9 +346,6 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         zsum += s.x + s.y;
       }
       if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 5);
-      if (warp == 1 && lane == 0) ELSA_FTR(3, j, 5);
-      if ((warp & 3) == 1 && lane == 0) ELSA_FTR(t, j, 6);
-      if ((warp & 3) == 3 && lane == 0) ELSA_FTR(t, j, 7);
     }
 
     // epilogue: renormalise to the true max and write the summary row

@@ -41,17 +41,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-#ifdef ELSA_VAR_HINT
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
-#ifdef ELSA_VAR_HINT
-        , "r"(static_cast<uint32_t>(ELSA_VAR_HINT))
-#endif
       : "memory");
   return ok != 0;
 }
@@ -62,9 +55,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef ELSA_VAR_SLEEP
-    __nanosleep(ELSA_VAR_SLEEP);
-#endif
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
