@@ -206,7 +206,8 @@ def main():
 
     # synthetic inputs: iid N(0,1), CPU generator seeded per rank; ROT input sets are rotated so that a
     # step never finds its operands in L2 (one set = 8 tensors of B*H*N*D elements)
-    ROT = 3
+    set_bytes = 4 * b * h * n * d * torch.empty((), dtype=dtype).element_size()
+    ROT = int(min(32, max(3, -(-260_000_000 // set_bytes))))   # enough sets to exceed the 126 MB L2 (at most 32)
     g = torch.Generator().manual_seed(1234 + rank)
     host = [[torch.randn(b, h, n, d, generator=g).to(dtype).pin_memory() for _ in range(4)] for _ in range(ROT)]
     sets = [[t.to(dev) for t in s] for s in host]
@@ -355,7 +356,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16" if dtype == torch.float16 else dt_name, "data": "synthetic",
                 "config": {"workload": args.workload, "shape_per_gpu": [b, h, n, d], "causal": causal, "global_batch": b * world,
-                           "sharding": "batch x heads, no collective", "l2": f"{ROT} rotating input sets (>{ROT*134} MB), inputs larger than L2",
+                           "sharding": "batch x heads, no collective", "l2": f"{ROT} rotating input sets, {ROT * set_bytes / 1e6:.0f} MB in total against 126 MB of L2" + (": a step never finds its operands in L2" if ROT * set_bytes > 1.5 * 126e6 else ": smaller than L2, operands may be L2-resident"),
                            "tensor_cores": uses_tc},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
                 "pct_of_peak": 100.0 * value / world / pk["tflops"]}
