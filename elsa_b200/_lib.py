@@ -46,6 +46,8 @@ SIGNATURES = {
     "elsa_row_stats": (c_int, [_P, _P, *_BIAS, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "elsa_backward_workspace_bytes": (c_int64, [c_int] * 7 + [c_uint]),
     "elsa_twopass_backward": (c_int, [_P] * 7 + _BIAS + [_P, _P, _P] + _BIAS + [_P, c_int64] + [c_int] * 6 + [c_uint, _P]),
+    "elsa_backward_shard_workspace_bytes": (c_int64, [c_int] * 5 + [c_uint]),
+    "elsa_twopass_backward_shard": (c_int, [_P] * 11 + [c_int64] + [c_int] * 8 + [c_uint, _P]),
 }
 
 _lib = None

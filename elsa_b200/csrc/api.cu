@@ -324,6 +324,52 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.bh = batch * heads; p.is_causal = is_causal ? 1 : 0;
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  p.n_keys = n_ctx; p.key_offset = 0; p.dq_f32 = 0;
+  if (use_tc) return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+// ---- backward of one sequence shard ---------------------------------------------------------------
+// k, v hold rows key_offset .. key_offset + n_keys - 1 of the sequence; q, out, dout and the GLOBAL row state
+// (row_m, row_z of the merged forward) cover all n_ctx rows.  dk, dv of the shard are complete; dq is this shard's
+// contribution in fp32, to be summed over the shards by the caller (all_reduce / reduce_scatter) before rounding.
+extern "C" int64_t elsa_backward_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                                       unsigned flags) {
+  return elsa_backward_workspace_bytes(dtype, batch, heads, n_ctx, head_dim, 0, 0, flags);
+}
+
+extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, const void* v_shard, const void* out,
+                                           const void* dout, const float* row_m, const float* row_z, float* dq_partial,
+                                           void* dk_shard, void* dv_shard, void* workspace, int64_t workspace_bytes,
+                                           int dtype, int batch, int heads, int n_ctx, int head_dim, int n_keys,
+                                           int key_offset, int is_causal, unsigned flags, void* stream) {
+  if (n_ctx == 0) return ELSA_OK;
+  if (!q || !out || !dout || !row_m || !row_z || !dq_partial || !dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 ||
+      head_dim < 1 || head_dim > 128 || n_keys < 0 || key_offset < 0 || (n_keys > 0 && (!k_shard || !v_shard || !dk_shard || !dv_shard)))
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q) || !aligned16(k_shard) || !aligned16(v_shard) || !aligned16(out) || !aligned16(dout) ||
+      !aligned16(dq_partial) || !aligned16(dk_shard) || !aligned16(dv_shard))
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (static_cast<int64_t>(batch) * heads > 65535) return ELSA_ERR_UNSUPPORTED;
+  const int64_t need = elsa_backward_shard_workspace_bytes(dtype, batch, heads, n_ctx, head_dim, flags);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < need) return ELSA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  float* row_d = reinterpret_cast<float*>(ws);
+  float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
+  const bool use_tc = n_keys > 0 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
+  int rc = ELSA_OK;
+  if (!use_tc) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
+  if (rc != ELSA_OK) return rc;
+  BwdParams p;
+  p.q = q; p.k = k_shard; p.v = v_shard; p.dout = dout;
+  p.lse = row_lse; p.drow = row_d;
+  p.bias = nullptr; p.bsb = p.bsh = p.bsq = p.bsk = 0;
+  p.dq = dq_partial; p.dk = dk_shard; p.dv = dv_shard;
+  p.dbias = nullptr; p.dsb = p.dsh = p.dsq = p.dsk = 0; p.dbias_atomic = 0;
+  p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.bh = batch * heads; p.is_causal = is_causal ? 1 : 0;
+  p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  p.n_keys = n_keys; p.key_offset = key_offset; p.dq_f32 = 1;
   if (use_tc) return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }

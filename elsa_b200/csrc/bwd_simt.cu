@@ -29,13 +29,16 @@ bwd_simt_kernel(const BwdParams prm) {
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int bh = blockIdx.y;
-  const int D = prm.head_dim, N = prm.n_ctx;
+  const int D = prm.head_dim, N = prm.n_ctx, NK = prm.n_keys, koff = prm.key_offset;
+  const int NR = MODE == 0 ? N : NK;       // rows of this launch: queries (dQ) or local keys (dK, dV)
+  const int NC = MODE == 0 ? NK : N;       // columns walked by the loop
   const int r0 = blockIdx.x * 64;
-  const int rows_valid = min(64, N - r0);
-  const int64_t base = static_cast<int64_t>(bh) * N * D;
+  const int rows_valid = min(64, NR - r0);
+  const int64_t base = static_cast<int64_t>(bh) * N * D;       // q, dO, dQ
+  const int64_t kbase = static_cast<int64_t>(bh) * NK * D;     // k, v, dK, dV
   const T* qb = static_cast<const T*>(prm.q) + base;
-  const T* kb = static_cast<const T*>(prm.k) + base;
-  const T* vb = static_cast<const T*>(prm.v) + base;
+  const T* kb = static_cast<const T*>(prm.k) + kbase;
+  const T* vb = static_cast<const T*>(prm.v) + kbase;
   const T* gb = static_cast<const T*>(prm.dout) + base;
   const float* lse = prm.lse + static_cast<int64_t>(bh) * N;
   const float* drow = prm.drow + static_cast<int64_t>(bh) * N;
@@ -62,15 +65,15 @@ bwd_simt_kernel(const BwdParams prm) {
 #pragma unroll
     for (int c = 0; c < CPT; ++c) { acc1[i][c] = 0.f; acc2[i][c] = 0.f; }
 
-  int c_begin = 0, c_end = N;
+  int c_begin = 0, c_end = NC;
   if (prm.is_causal) {
-    if (MODE == 0) c_end = min(N, r0 + rows_valid);  // keys <= last query row of the tile
-    else c_begin = r0;                               // queries >= first key row of the tile
+    if (MODE == 0) c_end = max(0, min(NK, r0 + rows_valid - koff));  // local keys whose sequence index <= last query row of the tile
+    else c_begin = min(N, r0 + koff);                                // queries >= sequence index of the first key row of the tile
   }
 
   for (int c0 = c_begin; c0 < c_end; c0 += 64) {
     __syncthreads();
-    const int cv = min(64, N - c0);
+    const int cv = min(64, NC - c0);
     load_tile<T, DP>(CA, LD, (MODE == 0 ? kb : qb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
     load_tile<T, DP>(CB, LD, (MODE == 0 ? vb : gb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
     __syncthreads();
@@ -94,8 +97,8 @@ bwd_simt_kernel(const BwdParams prm) {
       for (int jj = 0; jj < 4; ++jj) {
         const int rr = r0 + ty * 4 + ii, cc = c0 + tx + 16 * jj;
         const int qi = MODE == 0 ? rr : cc;
-        const int kj = MODE == 0 ? cc : rr;
-        bool valid = rr < N && cc < N;
+        const int kj = (MODE == 0 ? cc : rr) + koff;       // sequence index of the key
+        bool valid = rr < NR && cc < NC;
         if (prm.is_causal) valid = valid && (qi >= kj);
         const float l = MODE == 0 ? lse_r[ii] : lse_c[jj];
         const float dd = MODE == 0 ? d_r[ii] : d_c[jj];
@@ -134,14 +137,15 @@ bwd_simt_kernel(const BwdParams prm) {
 #pragma unroll
   for (int ii = 0; ii < 4; ++ii) {
     const int r = r0 + ty * 4 + ii;
-    if (r >= N) continue;
+    if (r >= NR) continue;
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
       const int col = tile_col<DP>(tx, c);
       if (col >= D) continue;
-      const int64_t o = base + static_cast<int64_t>(r) * D + col;
+      const int64_t o = (MODE == 0 ? base : kbase) + static_cast<int64_t>(r) * D + col;
       if (MODE == 0) {
-        static_cast<T*>(prm.dq)[o] = from_f32<T>(acc1[ii][c] * prm.scale);
+        if (prm.dq_f32) static_cast<float*>(prm.dq)[o] = acc1[ii][c] * prm.scale;
+        else static_cast<T*>(prm.dq)[o] = from_f32<T>(acc1[ii][c] * prm.scale);
       } else {
         static_cast<T*>(prm.dv)[o] = from_f32<T>(acc1[ii][c]);
         static_cast<T*>(prm.dk)[o] = from_f32<T>(acc2[ii][c] * prm.scale);
@@ -155,7 +159,9 @@ static int launch_bwd(const BwdParams& p, cudaStream_t st) {
   constexpr size_t smem = sizeof(float) * (4 * 64 * (DP + 4) + (MODE == 0 ? 1 : 2) * 64 * 68);
   int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_simt_kernel<T, DP, MODE>), smem);
   if (rc != ELSA_OK) return rc;
-  dim3 grid(static_cast<unsigned>((p.n_ctx + 63) / 64), static_cast<unsigned>(p.bh));
+  const int rows = MODE == 0 ? p.n_ctx : p.n_keys;
+  if (rows == 0) return ELSA_OK;
+  dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>(p.bh));
   bwd_simt_kernel<T, DP, MODE><<<grid, 256, smem, st>>>(p);
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;

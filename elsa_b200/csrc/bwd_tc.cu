@@ -88,8 +88,9 @@ enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS
 struct BwdTcParams {
   const float* nlse_pad; const float* nd_pad;  // [BH][n_pad]: -LSE, -D
   float* dq_acc;                               // [BH][N][64] fp32, zeroed by the caller
-  void* dk; void* dv;                          // [BH][N][64] T
+  void* dk; void* dv;                          // [BH][n_keys][64] T
   int n_ctx, n_pad, bh, is_causal;
+  int n_keys, key_offset;                      // K/V rows of this launch and the sequence index of the first one
   float scale, scale_log2;
 };
 
@@ -118,10 +119,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;
-  const int k0 = blockIdx.x * 128;                  // first key row of this CTA
-  const int N = prm.n_ctx;
+  const int k0 = blockIdx.x * 128;                  // first (local) key row of this CTA
+  const int N = prm.n_ctx, NK = prm.n_keys;
+  const int kseq0 = k0 + prm.key_offset;            // its index in the sequence
   const int n_qtiles = (N + 127) / 128;
-  const int it_begin = prm.is_causal ? blockIdx.x : 0;   // query tiles above the diagonal tile see none of these keys
+  const int it_begin = prm.is_causal ? min(n_qtiles, kseq0 / 128) : 0;   // query tiles above the diagonal see none of these keys
   const int n_it = n_qtiles - it_begin;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -330,9 +332,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const int half = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int key = k0 + row;
-    const bool key_ok = key < N;
-    const bool cta_tail = k0 + 128 > N;        // some key rows of this CTA do not exist
+    const int key = k0 + row;                  // local key row
+    const int key_seq = kseq0 + row;           // its index in the sequence (what the causal rule compares)
+    const bool key_ok = key < NK;
+    const bool cta_tail = k0 + 128 > NK;       // some key rows of this CTA do not exist
     const float2 c2 = make_float2(prm.scale_log2, prm.scale_log2);
     bool alive = true;
 
@@ -364,7 +367,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       tc_fence_after();
       const float4* nl4 =reinterpret_cast<const float4*>(smem_gen + (sNL(st) - smem_base)) + half * 16;
       const float4* nd4 = reinterpret_cast<const float4*>(smem_gen + (sND(st) - smem_base)) + half * 16;
-      const bool masked = cta_tail || (prm.is_causal && q_tile0 < k0 + 128);   // only the diagonal tile / the last key tile
+      const bool masked = cta_tail || (prm.is_causal && q_tile0 < kseq0 + 128);   // only the diagonal tile(s) / the last key tile
       uint8_t* ds_row = smem_gen + (sDS0 - smem_base) + (it & 1) * 2 * kTile + half * kTile + row * 128;
 
       // ---- phase A: P^T = exp2(S^T * c - LSE) for this thread's 64 queries, kept in registers as fp32 ----
@@ -396,7 +399,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const bool causal = prm.is_causal;
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            p[4 * g + e] = (key_ok && (!causal || qc + e >= key)) ? p[4 * g + e] : 0.f;
+            p[4 * g + e] = (key_ok && (!causal || qc + e >= key_seq)) ? p[4 * g + e] : 0.f;
         }
       }
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
@@ -457,8 +460,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         for (int i = 0; i < 32; ++i) { rk[i] = 0u; rv[i] = 0u; }   // no query sees these keys: zero gradients
       }
       if (key_ok) {
-        T* dk_row = static_cast<T*>(prm.dk) + (static_cast<int64_t>(bh) * N + key) * 64 + half * 32;
-        T* dv_row = static_cast<T*>(prm.dv) + (static_cast<int64_t>(bh) * N + key) * 64 + half * 32;
+        T* dk_row = static_cast<T*>(prm.dk) + (static_cast<int64_t>(bh) * NK + key) * 64 + half * 32;
+        T* dv_row = static_cast<T*>(prm.dv) + (static_cast<int64_t>(bh) * NK + key) * 64 + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           uint4 a, b;
@@ -519,6 +522,15 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   }
 }
 
+// acc *= scale (the fp32 dQ of a sequence shard stays fp32: the caller sums the shards before rounding)
+__global__ void __launch_bounds__(256) dq_scale_kernel(float* __restrict__ acc, int64_t n_vec4, float scale) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec4) return;
+  float4 a = *reinterpret_cast<float4*>(acc + i * 4);
+  a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+  *reinterpret_cast<float4*>(acc + i * 4) = a;
+}
+
 // dq = T(acc * scale)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -545,13 +557,14 @@ int64_t bwd_tc_workspace_bytes(int bh, int n_ctx) {
 template <typename T>
 static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, const float* row_z, void* workspace,
                     int dtype, cudaStream_t st) {
-  const int N = p.n_ctx, bh = p.bh;
+  const int N = p.n_ctx, NK = p.n_keys, bh = p.bh;
   const int n_pad = static_cast<int>(align_up(N, 128));
   const int64_t vec_bytes = align_up(static_cast<int64_t>(bh) * n_pad * 4, 256);
   char* ws = static_cast<char*>(workspace);
   float* nd_pad = reinterpret_cast<float*>(ws);
   float* nlse_pad = reinterpret_cast<float*>(ws + vec_bytes);
-  float* dq_acc = reinterpret_cast<float*>(ws + 2 * vec_bytes);
+  // the fp32 accumulator the TMA reductions add into: the caller's fp32 dQ for a sequence shard, else workspace
+  float* dq_acc = p.dq_f32 ? static_cast<float*>(p.dq) : reinterpret_cast<float*>(ws + 2 * vec_bytes);
   const int64_t acc_elems = static_cast<int64_t>(bh) * N * 64;
 
   {
@@ -566,20 +579,27 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   int rc;
   if ((rc = make_tmap_f32_rows64(&mdq, dq_acc, N, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, N, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, N, bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, NK, bh, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, bh, 128)) != ELSA_OK) return rc;
   BwdTcParams prm;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.is_causal = p.is_causal;
+  prm.n_keys = NK; prm.key_offset = p.key_offset;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_tc_kernel<T>), kBwdSmem);
   if (rc != ELSA_OK) return rc;
-  dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
-  bwd_tc_kernel<T><<<grid, kThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, prm);
-  ELSA_LAUNCH_CHECK();
-  dq_convert_kernel<T><<<static_cast<unsigned>(cdiv64(acc_elems / 8, 256)), 256, 0, st>>>(
-      dq_acc, static_cast<T*>(p.dq), acc_elems / 8, p.scale);
+  if (NK > 0) {
+    dim3 grid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
+    bwd_tc_kernel<T><<<grid, kThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, prm);
+    ELSA_LAUNCH_CHECK();
+  }
+  if (p.dq_f32) {
+    dq_scale_kernel<<<static_cast<unsigned>(cdiv64(acc_elems / 4, 256)), 256, 0, st>>>(dq_acc, acc_elems / 4, p.scale);
+  } else {
+    dq_convert_kernel<T><<<static_cast<unsigned>(cdiv64(acc_elems / 8, 256)), 256, 0, st>>>(
+        dq_acc, static_cast<T*>(p.dq), acc_elems / 8, p.scale);
+  }
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }

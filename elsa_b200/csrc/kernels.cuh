@@ -27,6 +27,9 @@ struct BwdParams {
   float* dbias; int64_t dsb, dsh, dsq, dsk; int dbias_atomic;
   int heads, n_ctx, head_dim, bh, is_causal;
   float scale, scale_log2;
+  // sequence shard: k, v, dk, dv hold n_keys rows that are rows key_offset .. key_offset + n_keys - 1 of the
+  // sequence (n_keys = n_ctx, key_offset = 0 for the whole problem); dq_f32: dq is an fp32 [BH, N, D] buffer
+  int n_keys, key_offset, dq_f32;
 };
 
 // opt-in to > 48 KB dynamic shared memory once per (function, device)

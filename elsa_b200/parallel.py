@@ -110,3 +110,86 @@ def sequence_parallel_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard:
     if return_state:
         return out, row_m, row_z
     return out
+
+
+# ---- backward of the sequence-sharded form -------------------------------------------------------
+# dK and dV of a shard need only the global row state (LSE, D) and are complete on the rank that owns the
+# K/V rows; dQ is a sum over the shards: every rank computes its contribution in fp32 and the contributions
+# are added across ranks before rounding to the input dtype.
+
+def reduce_dq_across_ranks(dq_partial: torch.Tensor, *, scatter: bool = False, group=None) -> torch.Tensor:
+    """Sum the per-shard fp32 dQ contributions ([..., N, D], same shape on every rank).
+
+    scatter=False: every rank gets the full sum (all_reduce).  scatter=True: rank r gets rows
+    [r*N/W, (r+1)*N/W) of the sum (reduce_scatter along the sequence axis; N must divide by the world size)."""
+    if not scatter:
+        dist.all_reduce(dq_partial, op=dist.ReduceOp.SUM, group=group)
+        return dq_partial
+    world = dist.get_world_size(group)
+    n = dq_partial.shape[-2]
+    if n % world:
+        raise ValueError("reduce_scatter of dQ needs the sequence length to be divisible by the number of ranks")
+    chunks = [c.contiguous() for c in dq_partial.chunk(world, dim=-2)]
+    out = torch.empty_like(chunks[0])
+    if dq_partial.device.type == "cuda":
+        dist.reduce_scatter(out, chunks, op=dist.ReduceOp.SUM, group=group)
+    else:
+        # gloo has no reduce_scatter: all_reduce and keep this rank's rows
+        dist.all_reduce(dq_partial, op=dist.ReduceOp.SUM, group=group)
+        out = dq_partial.chunk(world, dim=-2)[dist.get_rank(group)].contiguous()
+    return out
+
+
+def local_shard_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
+                         dout: torch.Tensor, row_m: torch.Tensor, row_z: torch.Tensor, *, key_offset: int,
+                         is_causal: bool = False, flags: int = 0
+                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of ONE sequence shard on this GPU.
+
+    q, out, dout: [B, H, N, D]; k_shard, v_shard: [B, H, Nk, D]; row_m, row_z: [B*H, N] fp32, the state of the
+    merged forward.  Returns (dq_partial fp32 [B, H, N, D], dk_shard, dv_shard [B, H, Nk, D] in the input dtype)."""
+    lib = _lib.load()
+    if q.dim() != 4 or k_shard.dim() != 4 or k_shard.shape != v_shard.shape or out.shape != q.shape or dout.shape != q.shape:
+        raise ValueError("q, out, dout must be [B,H,N,D] and k_shard, v_shard [B,H,Nk,D]")
+    if q.device.type != "cuda":
+        raise ValueError("local_shard_backward requires CUDA tensors")
+    b, h, n, d = map(int, q.shape)
+    nk = int(k_shard.shape[2])
+    if tuple(k_shard.shape) != (b, h, nk, d) or any(t.dtype != q.dtype for t in (k_shard, v_shard, out, dout)):
+        raise ValueError("k_shard / v_shard / out / dout must match q in batch, heads, head_dim and dtype")
+    q_c, k_c, v_c, o_c, g_c = (_aligned(t) for t in (q, k_shard, v_shard, out, dout))
+    rm = row_m.reshape(b * h, n).float().contiguous()
+    rz = row_z.reshape(b * h, n).float().contiguous()
+    dt = _lib.dtype_code(q.dtype)
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        dq = torch.empty((b, h, n, d), device=dev, dtype=torch.float32)
+        dk = torch.empty((b, h, nk, d), device=dev, dtype=q.dtype)
+        dv = torch.empty_like(dk)
+        ws_bytes = int(lib.elsa_backward_shard_workspace_bytes(dt, b, h, n, d, flags))
+        if ws_bytes < 0:
+            raise ValueError("local_shard_backward: unsupported problem")
+        ws = torch.empty(max(ws_bytes, 256), device=dev, dtype=torch.uint8)
+        rc = lib.elsa_twopass_backward_shard(q_c.data_ptr(), k_c.data_ptr() if nk else None, v_c.data_ptr() if nk else None,
+                                             o_c.data_ptr(), g_c.data_ptr(), rm.data_ptr(), rz.data_ptr(), dq.data_ptr(),
+                                             dk.data_ptr() if nk else None, dv.data_ptr() if nk else None, ws.data_ptr(),
+                                             ws_bytes, dt, b, h, n, d, nk, int(key_offset), int(bool(is_causal)),
+                                             int(flags), stream)
+        _lib.check(rc, "elsa_twopass_backward_shard")
+    return dq, dk, dv
+
+
+def sequence_parallel_attention_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
+                                         out: torch.Tensor, dout: torch.Tensor, row_m: torch.Tensor,
+                                         row_z: torch.Tensor, *, key_offset: int, is_causal: bool = False,
+                                         scatter_dq: bool = False, group=None):
+    """Backward of `sequence_parallel_attention`: (dq, dk_shard, dv_shard).
+
+    Every rank passes the full q, out, dout, the global (row_m, row_z) returned by the forward with
+    return_state=True, and its own K/V rows.  dk_shard / dv_shard are this rank's rows; dq is the full gradient on
+    every rank (or, with scatter_dq, this rank's N/world rows), rounded to the input dtype after the fp32 sum."""
+    dq_part, dk, dv = local_shard_backward(q, k_shard, v_shard, out, dout, row_m, row_z, key_offset=key_offset,
+                                           is_causal=is_causal)
+    dq = reduce_dq_across_ranks(dq_part, scatter=scatter_dq, group=group)
+    return dq.to(q.dtype), dk, dv

@@ -224,6 +224,21 @@ int elsa_twopass_backward(const void* q, const void* k, const void* v, const voi
                           int dtype, int batch, int heads, int n_ctx, int head_dim,
                           int is_causal, unsigned flags, void* stream);
 
+/* Backward of ONE sequence shard (the K/V partitioning of the two-pass formulation, README.md:27-29,
+ * carried across GPUs; the reference itself is single-GPU and has no counterpart).
+ * k_shard, v_shard, dk_shard, dv_shard: [B*H, n_keys, D], rows key_offset .. key_offset + n_keys - 1
+ * of the sequence; q, out, dout: [B*H, n_ctx, D]; row_m, row_z: the state of the MERGED forward.
+ * dk_shard, dv_shard are complete; dq_partial ([B*H, n_ctx, D], fp32 whatever the input dtype) is this
+ * shard's contribution: the caller sums it over the shards (all_reduce / reduce_scatter) and rounds.
+ * No bias.  workspace: elsa_backward_shard_workspace_bytes. */
+int64_t elsa_backward_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                            unsigned flags);
+int elsa_twopass_backward_shard(const void* q, const void* k_shard, const void* v_shard, const void* out,
+                                const void* dout, const float* row_m, const float* row_z, float* dq_partial,
+                                void* dk_shard, void* dv_shard, void* workspace, int64_t workspace_bytes,
+                                int dtype, int batch, int heads, int n_ctx, int head_dim, int n_keys,
+                                int key_offset, int is_causal, unsigned flags, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

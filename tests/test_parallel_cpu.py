@@ -94,3 +94,55 @@ def test_rank_merge_identity_and_empty_rows():
     ret = mp.Manager().dict()
     mp.spawn(_identity_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret[0] and ret[1]
+
+
+def _bwd_worker(rank, world, port, causal, scatter, ret):
+    """Sequence-sharded backward among CPU ranks: each rank forms its shard's (dq_partial, dk, dv) in plain fp64
+    torch from the GLOBAL row state, the ranks sum dQ; the result must equal the oracle's full backward."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from elsa_b200.parallel import reduce_dq_across_ranks
+        g = torch.Generator().manual_seed(77)
+        b, h, n, d = 1, 2, 96, 16
+        q, k, v, do = (torch.randn(b, h, n, d, generator=g) for _ in range(4))
+        bh = b * h
+        q3, k3, v3, g3 = (t.reshape(bh, n, d).double() for t in (q, k, v, do))
+        out = O.softmax_attention_fp64(q, k, v, is_causal=causal).reshape(bh, n, d)
+        rm, rz = O.row_stats(q3.float(), k3.float(), is_causal=causal)
+        lse = (rm + torch.log2(rz)).double()
+        drow = (out * g3).sum(-1)
+        bounds = [0, 32, 96] if world == 2 else [0, 32, 64, 96]
+        k0, k1 = bounds[rank], bounds[rank + 1]
+        sc = (q3 @ k3[:, k0:k1].transpose(-1, -2)) * (d ** -0.5) * O.LOG2E
+        p = torch.exp2(sc - lse[..., None])
+        if causal:
+            p = p * (torch.arange(n)[:, None] >= torch.arange(k0, k1)[None, :])
+        dp = g3 @ v3[:, k0:k1].transpose(-1, -2)
+        ds = p * (dp - drow[..., None])
+        dq_part = (ds @ k3[:, k0:k1]) * (d ** -0.5)
+        dk = (ds.transpose(-1, -2) @ q3) * (d ** -0.5)
+        dv = p.transpose(-1, -2) @ g3
+        dq = reduce_dq_across_ranks(dq_part.float().contiguous(), scatter=scatter)
+        dq_ref, dk_ref, dv_ref = O.twopass_backward(q, k, v, out.reshape(b, h, n, d).float(), do, rm, rz, is_causal=causal)
+        dq_ref = dq_ref.reshape(bh, n, d)
+        if scatter:
+            dq_ref = dq_ref.chunk(world, dim=-2)[rank]
+        e = [(dq.double() - dq_ref.double()).abs().max().item(),
+             (dk - dk_ref.reshape(bh, n, d)[:, k0:k1].double()).abs().max().item(),
+             (dv - dv_ref.reshape(bh, n, d)[:, k0:k1].double()).abs().max().item()]
+        ret[rank] = e
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,scatter", [(2, False), (3, False), (2, True)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_rank_sum_of_dq_matches_single_process(world, scatter, causal):
+    port = _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_bwd_worker, args=(world, port, causal, scatter, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for rank in range(world):
+        assert max(ret[rank]) < 5e-6, (rank, ret[rank])
