@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_int, c_int64, c_uint, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libelsa_b200.so")
+# ELSA_B200_LIB points the loader at another build of the same library (a tuning build, an installed copy)
+LIB_PATH = os.environ.get("ELSA_B200_LIB") or os.path.join(_HERE, "libelsa_b200.so")
 
 ELSA_F32, ELSA_F16, ELSA_BF16 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_SCAN_STEPS, FLAG_TREE_MERGE = 1, 2, 4
