@@ -68,6 +68,7 @@ __device__ long long g_bwd_trace[5][256][4];
 namespace {
 
 constexpr int kQStages = 2;
+constexpr int kPrefetchAhead = 3;   // query tiles between the ring's load and the L2 prefetch
 constexpr int kTile = 128 * 64 * 2;     // 16 KB: one 128 x 64 16-bit tile
 constexpr int kVecBytes = 128 * 4;      // 128 fp32 row statistics
 // smem: K, V | ring of (Q, dO, -LSE, -D) | dS^T double buffer (each two 64-query blocks) | dQ staging (fp32, 2 x 16 KB)
@@ -190,6 +191,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tma_load_3d(sDO(st), &tmap_do, bar_q_full(st), 0, qrow, bh);
         bulk_load_1d(sNL(st), prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
         bulk_load_1d(sND(st), prm.nd_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
+        // the ring is only one tile ahead of the tensor pipe: pull the tiles after it into L2 now, so that a first
+        // touch (inputs that are not L2-resident) costs an L2 hit instead of a DRAM round trip when its turn comes
+        if (it + kPrefetchAhead < n_it) {
+          tma_prefetch_l2_3d(&tmap_q, 0, qrow + kPrefetchAhead * 128, bh);
+          tma_prefetch_l2_3d(&tmap_do, 0, qrow + kPrefetchAhead * 128, bh);
+        }
       }
     } else if (warp == 13 && lane == 0) {
       // ---------------- MMA issuer ----------------
