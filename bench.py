@@ -77,7 +77,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", os.environ.get("ELSA_BENCH_SAMPLE_MS", "100"), "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
@@ -252,14 +252,20 @@ def main():
     t_end = torch.cuda.Event(enable_timing=True)
     t_start.record()
     for i in range(args.steps):
-        step(i, evs[i])
+        step(i)
     t_end.record()
     barrier()
     launches = lib.elsa_kernel_launches() - l0
     total_ms = t_start.elapsed_time(t_end)
+    mark1 = sampler.mark()
+    # the forward / backward split (and with it the dominant kernel's duration for the roofline) comes from a second
+    # pass over the same steps with events between the two calls: timing events drain the GPU before they take
+    # their time stamp, which costs the timed region above about 0.2 ms per step when they sit inside it
+    for i in range(args.steps):
+        step(i, evs[i])
+    barrier()
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
-    mark1 = sampler.mark()
     clock_marks = (mark0, mark1)
     if dist is not None:
         t = torch.tensor([total_ms], device=dev)
@@ -267,6 +273,26 @@ def main():
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     value = world * (fwd_f + bwd_f) / (ms_per_step * 1e-3) / 1e12
+
+    # The burst figure: MEASURED_PEAKS.json's 1683.8 TFLOP/s is the best of 10 cuBLAS calls on a rested GPU, the timed
+    # region above runs under a settled power cap.  The same protocol for one step of this path (best of 10 single
+    # steps, 50 ms of idle before each, rotating input sets) pairs with that denominator; the sustained value above
+    # pairs with the sustained one.
+    burst_ms = None
+    for i in range(10):
+        torch.cuda.synchronize()
+        time.sleep(0.05)
+        b0 = torch.cuda.Event(enable_timing=True); b1 = torch.cuda.Event(enable_timing=True)
+        b0.record()
+        step(i)
+        b1.record()
+        torch.cuda.synchronize()
+        t = b0.elapsed_time(b1)
+        burst_ms = t if burst_ms is None else min(burst_ms, t)
+    if dist is not None:
+        t = torch.tensor([burst_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        burst_ms = float(t.item())
 
     # the same step replayed from a CUDA graph (the entry points allocate nothing and never synchronise): what is
     # left when launch gaps and host work are taken out; reported beside the eager number, never instead of it
@@ -277,21 +303,25 @@ def main():
         with torch.cuda.stream(gs):
             step(0)
         torch.cuda.current_stream().wait_stream(gs)
-        cg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(cg):
-            step(0)
-        cg.replay()
+        graphs = []
+        for r in range(ROT):                     # one graph per input set: the replays rotate like the eager steps
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                step(r)
+            graphs.append(cg)
+        for cg in graphs:
+            cg.replay()
         barrier()
         g0 = torch.cuda.Event(enable_timing=True); g1 = torch.cuda.Event(enable_timing=True)
         g0.record()
-        for _ in range(args.steps):
-            cg.replay()
+        for i in range(args.steps):
+            graphs[i % ROT].replay()
         g1.record()
         barrier()
         g_ms = g0.elapsed_time(g1) / args.steps
         graph_line = {"ms_per_step": g_ms, "value": world * (fwd_f + bwd_f) / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                      "note": "one input set replayed: operands may be L2-resident"}
-        del cg
+                      "note": f"{ROT} graphs, one per input set, replayed in rotation"}
+        del graphs
     except Exception as exc:  # noqa: BLE001 - a capture failure must not take the bench line down
         graph_line = {"error": str(exc)[:200]}
 
@@ -385,8 +415,12 @@ def main():
                 "config": {"workload": args.workload, "shape_per_gpu": [b, h, n, d], "causal": causal, "global_batch": b * world,
                            "sharding": "batch x heads, no collective", "l2": f"{ROT} rotating input sets, {ROT * set_bytes / 1e6:.0f} MB in total against 126 MB of L2" + (": a step never finds its operands in L2" if ROT * set_bytes > 1.5 * 126e6 else ": smaller than L2, operands may be L2-resident"),
                            "tensor_cores": uses_tc},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "graph_replay": graph_line, "gpu_launches": int(launches), "clocks": clocks,
-                "pct_of_peak": 100.0 * value / world / pk["tflops"]}
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "graph_replay": graph_line,
+                "burst": {"ms_per_step": burst_ms, "value": world * (fwd_f + bwd_f) / (burst_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "protocol": "best of 10 single steps, 50 ms idle before each (the protocol of the burst peak)",
+                          "pct_of_burst_peak": 100.0 * (fwd_f + bwd_f) / (burst_ms * 1e-3) / 1e12 / pk["tflops"]}, "gpu_launches": int(launches), "clocks": clocks,
+                "pct_of_peak": 100.0 * value / world / pk["tflops"],
+                "pct_of_sustained_peak": 100.0 * value / world / pk["tflops_sustained"] if pk["tflops_sustained"] else None}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
