@@ -15,7 +15,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py <checkout of ming053l/ELSA>")
+REF = sys.argv[1]
 sys.path.insert(0, os.path.join(REF, "src"))
 
 import numpy as np  # noqa: E402

@@ -115,7 +115,7 @@ CASES = [
     (3, 2, 49, 32, F16, False, "nn", 64, 49),
     (3, 2, 49, 32, F32, False, "b1nn", 64, 49),
     (2, 3, 77, 40, F32, True, "hnn", None, None),
-    (1, 8, 1024, 64, F32, False, None, None, None),       # BASELINE config 1
+    (1, 8, 1024, 64, F32, False, None, None, None),       # the reference's CPU-runnable fp32 case
     (1, 2, 2048, 64, F16, False, None, 2048, None),
     (1, 2, 2048, 64, F16, False, None, 256, 1024),
 ]
