@@ -19,7 +19,7 @@
 // Pipeline.  A compute thread owns one key row and 64 of the 128 query columns and works in two phases:
 //   A  load its S^T columns, release them (bar_lds), P^T = exp2(S^T c - LSE) kept in registers (fp32);
 //   B  wait for dP^T, then per 32-query chunk: load dP^T, dS^T = P^T (dP^T - D), write the 16-bit P^T / dS^T
-//      over the chunk's own dP^T columns (and dS^T to shared memory), hand the chunk to the issuer (bar_pds).
+//      over the chunk's own dP^T columns (and dS^T to shared memory); one hand-off to the issuer per half (bar_pds).
 // Because P^T no longer overlays S^T, the S^T columns are free as soon as phase A has loaded them: the issuer
 // produces S^T of the NEXT query tile at the top of the iteration, so phase A of the next tile never waits
 // and runs while the tensor pipe is busy with dV / dK / dP^T(next) / dQ of this one.  dP^T(next) follows the
@@ -39,7 +39,8 @@
 // K and V are copied once into TMEM (16-bit pairs, one key per lane) so that S^T and dP^T take their A operand
 // from TMEM: the kernel is shared-memory-bandwidth sensitive and this removes 64 KB of operand reads per
 // 128 x 128 pair.  (Measured alternatives at B=1 H=8 N=16384: P^T / dS^T as shared-memory A operands of dV / dK,
-// 2.01 ms; two 64-query halves half an iteration apart with N = 64 S^T / dP^T, 1.80 ms; this design 1.64 ms.)
+// 2.01 ms; two 64-query halves half an iteration apart with N = 64 S^T / dP^T, 1.80 ms; this design with a
+// hand-off per 32-query chunk 1.64 ms, per half 1.59 ms.)
 //
 // -LSE and -D are read from a padded [BH][ceil(N/128)*128] layout whose padding holds -LSE = -inf,
 // -D = 0, so that query rows beyond N produce P = 0 without a branch.
@@ -246,7 +247,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       // One iteration on ring stage ST (the next one is on the other stage).  S^T of the NEXT query tile is issued
       // as soon as the compute warps hold the current S^T in registers (their exp2 phase then overlaps the
       // contractions below); dP^T of the next tile follows dV / dK of this one, whose A operands live in the
-      // dP^T columns; dQ comes last.
+      // dP^T columns; dQ comes last.  (dQ of the previous tile at the top of the iteration instead, so that only
+      // dV / dK / dP^T stand between the halves' arrival and the next dS phase: measured 1.95 ms against 1.59 ms.)
+      auto issue_dq = [&](int it_q, auto STQ) {       // dQ of tile it_q, whose dS^T sits in buffer STQ
+        constexpr int stq = decltype(STQ)::value;
+        if (it_q > 0 && !(ok = mbar_wait(bar_dq_free, (it_q - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE))) return;
+        mma_ss_x4<128, 128>(tdQ, dds[stq], bk_mn, idesc_dq, 0u);
+        mma_ss_x4<128, 128>(tdQ, dds[stq] + 512, bk_mn + 512, idesc_dq, 1u);
+        mma_commit(bar_q_free(stq));   // dQ(it_q) is complete: the drain warps may read it
+      };
       auto iteration = [&](int it, auto ST) {
         constexpr int st = decltype(ST)::value;
         const bool more = it + 1 < n_it;
@@ -264,27 +273,20 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         if (!(ok = mbar_wait(bar_pds(0, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
         tc_fence_after();
         issue_dkv(ST, I0{}, I0{}, it == 0 ? 0u : 1u);
+        issue_dkv(ST, I0{}, I1{}, 1u);
         if (!(ok = mbar_wait(bar_pds(1, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
         tc_fence_after();
         issue_dkv(ST, I1{}, I0{}, 1u);
-        if (!(ok = mbar_wait(bar_pds(0, 1), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
-        tc_fence_after();
-        issue_dkv(ST, I0{}, I1{}, 1u);
-        if (!(ok = mbar_wait(bar_pds(1, 1), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
-        tc_fence_after();
         issue_dkv(ST, I1{}, I1{}, 1u);
         ELSA_TR(0, it, 2);
         // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K): the producer may refill
-        // the ring stage now, a whole dP^T + dQ ahead of the commit that hands dQ to the drain warps
+        // the ring stage now
         mma_commit(bar_stage_free(st));
         if (more) {
           mma_ts_x4<8, 2>(tdP0, tV, ddo_k[st ^ 1], idesc_st, 0u);
           mma_commit(bar_dp);
         }
-        if (it > 0 && !(ok = mbar_wait(bar_dq_free, (it - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE))) return;
-        mma_ss_x4<128, 128>(tdQ, dds[st], bk_mn, idesc_dq, 0u);
-        mma_ss_x4<128, 128>(tdQ, dds[st] + 512, bk_mn + 512, idesc_dq, 1u);
-        mma_commit(bar_q_free(st));   // dQ(it) is complete: the drain warps may read it
+        issue_dq(it, ST);
         ELSA_TR(0, it, 3);
       };
       for (int it = 0; ok && it < n_it; it += 2) {
@@ -444,12 +446,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (row & 7)) << 4)) =
               make_uint4(dsk[4 * g], dsk[4 * g + 1], dsk[4 * g + 2], dsk[4 * g + 3]);
         }
-        // hand this 32-query chunk to the MMA issuer (dV / dK start on it while the second chunk is computed)
-        fence_proxy_async_smem();
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_pds(half, ch));
       }
+      // hand the half to the MMA issuer: one wait for all four TMEM stores, one fence, one arrival (dP^T of the
+      // next tile is only needed after the next exp2 phase, so dV / dK need not start on the first chunk)
+      fence_proxy_async_smem();
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_pds(half, 0));
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 3);
     }
 
