@@ -227,12 +227,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       }
       using I0 = std::integral_constant<int, 0>;
       using I1 = std::integral_constant<int, 1>;
-      // dV += P^T_h dO_h, dK += dS^T_h Q_h over the 32 queries of chunk ch of half h (two K-steps each); the 16-bit
+      // dV += P^T_h dO_h, dK += dS^T_h Q_h over the 64 queries of half h (four K-steps each); the 16-bit
       // P^T / dS^T of chunk ch sit in columns [32 ch, +16) / [32 ch + 16, +16) of the half's dP^T columns
-      auto issue_dkv = [&](auto ST, auto H, auto CH, uint32_t acc) {
-        constexpr int st = decltype(ST)::value, h = decltype(H)::value, ch = decltype(CH)::value;
-        mma_ts_x2<8, 128>(tdV, tdP(h) + 32 * ch, ddo_mn[st][h] + 256 * ch, idesc_kv, acc);
-        mma_ts_x2<8, 128>(tdK, tdP(h) + 32 * ch + 16, dq_mn[st][h] + 256 * ch, idesc_kv, acc);
+      auto issue_dkv = [&](auto ST, auto H, uint32_t acc) {
+        constexpr int st = decltype(ST)::value, h = decltype(H)::value;
+        // K-steps of 16 queries: P^T at columns 0, 8 (chunk 0) and 32, 40 (chunk 1); dS^T 16 columns further
+        mma_ts_x4_cols<8, 32, 40, 128>(tdV, tdP(h), ddo_mn[st][h], idesc_kv, acc);
+        mma_ts_x4_cols<8, 32, 40, 128>(tdK, tdP(h) + 16, dq_mn[st][h], idesc_kv, acc);
       };
       bool ok = mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV) &&
                 mbar_wait(bar_kvt, 0, &abort_flag, &g_bwd_status, BAR_KVT) &&
@@ -272,12 +273,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         ELSA_TR(0, it, 1);
         if (!(ok = mbar_wait(bar_pds(0, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
         tc_fence_after();
-        issue_dkv(ST, I0{}, I0{}, it == 0 ? 0u : 1u);
-        issue_dkv(ST, I0{}, I1{}, 1u);
+        issue_dkv(ST, I0{}, it == 0 ? 0u : 1u);
         if (!(ok = mbar_wait(bar_pds(1, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
         tc_fence_after();
-        issue_dkv(ST, I1{}, I0{}, 1u);
-        issue_dkv(ST, I1{}, I1{}, 1u);
+        issue_dkv(ST, I1{}, 1u);
         ELSA_TR(0, it, 2);
         // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K): the producer may refill
         // the ring stage now

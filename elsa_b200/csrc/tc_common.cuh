@@ -159,6 +159,22 @@ __device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint
         "n"(3 * A_STEP), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
       : "memory");
 }
+// four MMAs whose TMEM A slices sit at arbitrary column offsets A1..A3 from the first (B advances uniformly)
+template <int A1, int A2, int A3, int B_STEP>
+__device__ __forceinline__ void mma_ts_x4_cols(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b1, b2, b3;\n\t.reg .b32 a1, a2, a3;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "add.u32 a1, %1, %5;\n\tadd.u32 a2, %1, %6;\n\tadd.u32 a3, %1, %7;\n\t"
+      "add.u64 b1, %2, %8;\n\tadd.u64 b2, %2, %9;\n\tadd.u64 b3, %2, %10;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, p1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(first_accumulate), "n"(A1), "n"(A2), "n"(A3),
+        "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
 template <int A_STEP, int B_STEP>
 __device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
   asm volatile(
