@@ -19,13 +19,13 @@
 // Pipeline.  A compute thread owns one key row and 64 of the 128 query columns and works in two phases:
 //   A  load its S^T columns, release them (bar_lds), P^T = exp2(S^T c - LSE) kept in registers (fp32);
 //   B  wait for dP^T, then per 32-query chunk: load dP^T, dS^T = P^T (dP^T - D), write the 16-bit P^T / dS^T
-//      over the chunk's own dP^T columns (and dS^T to shared memory); one hand-off to the issuer per half (bar_pds).
+//      over the chunk's own dP^T columns (and dS^T to shared memory); every thread arrives once per tile on bar_pds.
 // Because P^T no longer overlays S^T, the S^T columns are free as soon as phase A has loaded them: the issuer
 // produces S^T of the NEXT query tile at the top of the iteration, so phase A of the next tile never waits
 // and runs while the tensor pipe is busy with dV / dK / dP^T(next) / dQ of this one.  dP^T(next) follows the
-// last dV / dK of this tile (same columns) and arrives during phase A.  The ring stage (Q, dO, -LSE, -D) is
-// handed back to the producer right after dV / dK -- dQ reads only dS^T and K -- so the next-but-one tile's
-// loads have a whole dP^T + dQ + S^T of lead time.
+// last dV / dK of this tile (same columns) and arrives during phase A.  The commit that announces dP^T(next)
+// also tells the producer that dV / dK of this tile have retired, i.e. that its ring stage (Q, dO, -LSE, -D) may be
+// refilled -- dQ reads only dS^T and K -- so the next-but-one tile's loads have a whole dQ + S^T of lead time.
 //
 //   warps 0-3   query columns 0-63  : one thread per key row (phases A and B above)
 //   warps 4-7   query columns 64-127
@@ -143,19 +143,20 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   auto bar_q_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_q_free = [&](int st) { return bar0 + 8 * (1 + kQStages + st); };
   const uint32_t barx = bar0 + 8 * (1 + 2 * kQStages);
-  const uint32_t bar_s = barx, bar_dp = barx + 8;          // S^T / dP^T of the current query tile are in TMEM
-  auto bar_pds = [&](int h, int ch) { return barx + 16 + 8 * (2 * h + ch); };   // per (half, 32-query chunk)
+  const uint32_t bar_s = barx;                             // S^T of the current query tile is in TMEM
+  // bar_dpx(p): dP^T of a query tile of parity p is in TMEM -- and, the same arrival, dV / dK of the tile before it
+  // have retired, so the ring stage of that tile (also parity-indexed) may be refilled
+  auto bar_dpx = [&](int p) { return barx + 8 + 8 * 9 + 8 * p; };
+  const uint32_t bar_pds = barx + 16;                      // P^T / dS^T of both halves are in TMEM / shared memory
   const uint32_t bar_dq_free = barx + 48, bar_done = barx + 56, bar_kvt = barx + 64;
   const uint32_t bar_lds = barx + 72;
-  auto bar_stage_free = [&](int st) { return barx + 80 + 8 * st; };   // dV / dK of the tile in ring stage st have retired                      // all 256 compute threads hold their S^T columns in registers
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_kv, 1);
     for (int st = 0; st < kQStages; ++st) { mbar_init(bar_q_full(st), 1); mbar_init(bar_q_free(st), 1); }
-    mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_lds, 256);
-    mbar_init(bar_stage_free(0), 1); mbar_init(bar_stage_free(1), 1);
-    for (int h = 0; h < 2; ++h) { mbar_init(bar_pds(h, 0), 128); mbar_init(bar_pds(h, 1), 128); }
+    mbar_init(bar_s, 1); mbar_init(bar_dpx(0), 1); mbar_init(bar_dpx(1), 1); mbar_init(bar_lds, 256);
+    mbar_init(bar_pds, 256);
     mbar_init(bar_dq_free, 128);
     mbar_init(bar_done, 1);
     mbar_init(bar_kvt, 256);
@@ -185,7 +186,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       tma_load_3d(sV, &tmap_v, bar_kv, 0, k0, bh);
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kQStages;
-        if (it >= kQStages && !mbar_wait(bar_stage_free(st), ((it / kQStages) - 1) & 1, &abort_flag, &g_bwd_status, BAR_Q_FREE)) break;
+        // stage st held tile it-2: its dV / dK retired before the commit that announced dP^T of tile it-1
+        if (it >= kQStages && !mbar_wait(bar_dpx((it - 1) & 1), ((it - 1) / 2) & 1, &abort_flag, &g_bwd_status, BAR_Q_FREE)) break;
         const int qrow = (it_begin + it) * 128;
         mbar_arrive_expect_tx(bar_q_full(st), kStageBytes);
         tma_load_3d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, bh);
@@ -243,7 +245,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mma_ts_x4<8, 2>(tS0, tK, dq_k[0], idesc_st, 0u);
         mma_commit(bar_s);
         mma_ts_x4<8, 2>(tdP0, tV, ddo_k[0], idesc_st, 0u);
-        mma_commit(bar_dp);
+        mma_commit(bar_dpx(0));
       }
       // One iteration on ring stage ST (the next one is on the other stage).  S^T of the NEXT query tile is issued
       // as soon as the compute warps hold the current S^T in registers (their exp2 phase then overlaps the
@@ -271,19 +273,17 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           mma_commit(bar_s);
         }
         ELSA_TR(0, it, 1);
-        if (!(ok = mbar_wait(bar_pds(0, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        if (!(ok = mbar_wait(bar_pds, pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
         tc_fence_after();
         issue_dkv(ST, I0{}, it == 0 ? 0u : 1u);
-        if (!(ok = mbar_wait(bar_pds(1, 0), pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
-        tc_fence_after();
         issue_dkv(ST, I1{}, 1u);
         ELSA_TR(0, it, 2);
-        // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K): the producer may refill
-        // the ring stage now
-        mma_commit(bar_stage_free(st));
         if (more) {
+          // one commit for two facts: dP^T of the next tile is in TMEM, and dV / dK of this tile have retired, so
+          // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K) and the producer may
+          // refill the ring stage
           mma_ts_x4<8, 2>(tdP0, tV, ddo_k[st ^ 1], idesc_st, 0u);
-          mma_commit(bar_dp);
+          mma_commit(bar_dpx(st ^ 1));
         }
         issue_dq(it, ST);
         ELSA_TR(0, it, 3);
@@ -413,7 +413,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
 
       // ---- phase B: dS^T = P^T * (dP^T - D); P^T and dS^T (16-bit) handed to dV / dK in two 32-query chunks ----
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_dp, it & 1, &abort_flag, &g_bwd_status, BAR_DP))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dpx(it & 1), (it / 2) & 1, &abort_flag, &g_bwd_status, BAR_DP))) { alive = false; break; }
       tc_fence_after();
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 2);
 #pragma unroll
@@ -451,7 +451,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       fence_proxy_async_smem();
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_pds(half, 0));
+      mbar_arrive(bar_pds);
       if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 3);
     }
 
