@@ -228,8 +228,6 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 if (!(ok = mbar_wait(bar_p(t, 0), j & 1, &abort_flag, &g_fold_status, BAR_P))) break;
                 tc_fence_after();
                 mma_ts_x4<8, 128>(tO[t], tP[t], dv0 + u * kStageStep, idesc_o, j > 0 ? 1u : 0u);
-                if (!(ok = mbar_wait(bar_p(t, 1), j & 1, &abort_flag, &g_fold_status, BAR_P))) break;
-                tc_fence_after();
                 mma_ts_x4<8, 128>(tO[t], tP[t] + 32, dv0 + u * kStageStep + 512, idesc_o, 1u);
                 ELSA_FTR(2, j, 2 + t);
                 if (t == 0) mma_commit(bar_pv0);
@@ -335,11 +333,12 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           pk[i] = pack2<T>(pp.x, pp.y);
         }
         tmem_st32(tP[t] + lane_off + 32 * h, pk);
-        tmem_wait_st();               // (also covers the O rescale stores above)
-        tc_fence_before();
-        mbar_arrive(bar_p(t, h));     // P V can start on this half while the other half's exponentials are computed
         if (h == 0 && (warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 4);
       }
+      // one hand-off per key tile: with the scores produced a tile ahead, P V need not start on the first half
+      tmem_wait_st();               // (also covers the O rescale stores above)
+      tc_fence_before();
+      mbar_arrive(bar_p(t, 0));
       {
         const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
         const float2 s = __fadd2_rn(s01, s23);
