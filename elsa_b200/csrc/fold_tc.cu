@@ -13,8 +13,7 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).  Because P has
 // its own columns, S_t is free as soon as the fold warps hold the row in registers (bar_sfree): the issuer
 // produces S_t of the NEXT key tile right then, so the fold warps never wait for scores.  P is handed to the
-// issuer in two 64-key halves (bar_p), P V of the first half runs while the second half's exponentials are
-// computed; the fold warps wait for P V of the previous key tile (bar_pv0 / bar_kv_free) only before they
+// issuer once per key tile (bar_p); the fold warps wait for P V of the previous key tile (bar_pv0 / bar_kv_free) only before they
 // overwrite P or rescale O.
 //
 // Exp-rescale merge: the fold keeps a reference max m_ref per row and only moves it (rescaling z
@@ -22,7 +21,8 @@
 // max is tracked separately and the summary is renormalised to it in the epilogue, so the stored
 // (m, z, s) is the same monoid element the FP32-FMA kernel produces.
 //
-// Measured alternatives at B=1 H=8 N=16384 (this design: 0.755 ms): two threads per row (four fold
+// Measured alternatives at B=1 H=8 N=16384 (this design: 0.738 ms; with a P hand-off per 64-key half 0.755 ms and
+// the variants below were measured against that): two threads per row (four fold
 // warpgroups of 64 columns each, half-row max exchanged through shared memory) 0.77-0.79 ms; a fixed
 // issue order that keeps the two tiles half a key tile apart 0.805 ms; half of the exponentials on the FMA
 // pipe 0.81 ms; no exponentials at all (timing only) 0.72 ms -- the kernel is bound by the chain
