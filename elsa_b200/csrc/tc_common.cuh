@@ -176,17 +176,6 @@ __device__ __forceinline__ void mma_ts_x4_cols(uint32_t d_tmem, uint32_t a_tmem,
       : "memory");
 }
 template <int A_STEP, int B_STEP>
-__device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b1;\n\t.reg .b32 a1;\n\t"
-      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
-      "add.u32 a1, %1, %5;\n\tadd.u64 b1, %2, %6;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, p1;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(first_accumulate), "n"(A_STEP), "n"(B_STEP)
-      : "memory");
-}
-template <int A_STEP, int B_STEP>
 __device__ __forceinline__ void mma_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t first_accumulate) {
   asm volatile(
       "{\n\t.reg .pred p0, p1;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
