@@ -140,3 +140,29 @@ def test_preprocess_abi():
     assert rc == 0
     ref_d, ref_l = O.bwd_preprocess(out.cpu(), dout.cpu(), rm.cpu(), rz.cpu())
     assert U.max_abs(rd, ref_d) <= 1e-5 and U.max_abs(lse, ref_l) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype,causal", [(torch.float16, False), (torch.bfloat16, True)])
+def test_tensor_core_path_repeats_bit_for_bit(dtype, causal):
+    """The tcgen05 kernels hand tiles between warps through mbarriers and reuse TMEM columns and shared-memory stages:
+    a missing ordering would show up as run-to-run differences.  out, row state, dK and dV have a fixed summation
+    order and must repeat bit for bit; dQ is summed by TMA reduce-adds whose order varies, so it repeats to one spacing of
+    the output type only."""
+    import elsa_b200 as E
+    b, h, n, d = 1, 4, 4096 + 77, 64
+    g = torch.Generator().manual_seed(4242)
+    q, k, v, do = (torch.randn(b, h, n, d, generator=g).to(dtype).cuda() for _ in range(4))
+    ref = None
+    for rep in range(12):
+        out, rm, rz = E.twopass_attention_with_state(q, k, v, is_causal=causal)[:3]
+        dq, dk, dv = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz, is_causal=causal)
+        cur = [t.clone() for t in (out, rm, rz, dk, dv, dq)]
+        if ref is None:
+            ref = cur
+            continue
+        for name, a, r in zip(("out", "row_m", "row_z", "dk", "dv"), cur[:5], ref[:5]):
+            assert torch.equal(a, r), (name, rep)
+        scale = ref[5].float().abs().max().item()
+        # one spacing of the output type at the largest magnitude: a different fp32 summation order can move a
+        # value across a rounding boundary, nothing more
+        assert (cur[5].float() - ref[5].float()).abs().max().item() <= scale * (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7), rep
