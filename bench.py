@@ -4,18 +4,23 @@
 
 One "step" = one forward + backward of the attention operator on one batch of synthetic Q, K, V, dO.
 Multi-GPU (torchrun, one rank per GPU): every rank runs its own batch element (batch x heads shards
-with no data-path collective), so scaling is "weak" and `value` is the whole-job TFLOP/s.
+with no data-path collective), so scaling is "weak" and `value` is the whole-job TFLOP/s; the line also
+carries `seq_sharded`, the sequence-sharded long fp32 case (K/V split over the ranks, summaries merged
+over NCCL), which is the multi-GPU path that has a real exchange step.
 
-Prints ONE JSON line (rank 0).  `value` is kernel throughput with inputs resident in HBM; `e2e` is
-the same metric through the public PyTorch API with pinned HOST buffers (H2D of q,k,v,dO and D2H of
-out,dq,dk,dv inside the timed region).  `--impl reference` times the CPU restatement of the
-reference's algorithm (the reference itself has no CPU path and its device code is Triton) on the
-host cores, on a bounded sample of the same workload.
+Prints ONE JSON line (rank 0).  `value` is kernel throughput with inputs resident in HBM, timed over a region
+of at least two seconds (the --steps block repeated back to back, `timed_steps` in all) so that it is a sustained
+figure under the power cap; `e2e` is the same metric through the public PyTorch API with pinned HOST buffers
+(H2D of q,k,v,dO and D2H of out,dq,dk,dv inside the timed region).  `--impl reference` times the CPU restatement of
+the reference's algorithm (the reference itself has no CPU path and its device code is Triton) on the host cores,
+on a bounded sample of the same workload; `reference_gpu` in the default line is the unmodified reference (its
+Triton kernels compiled for this GPU) timed on the same tensors with the same events.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -31,11 +36,11 @@ import torch  # noqa: E402
 METRIC = "ELSA attn fwd+bwd TFLOP/s (% of B200 peak), d=64 N=16K; scaling at 1/2/4/8 GPU"
 WORKLOADS = {
     # name: (B, H, N, D, dtype, causal)          the headline is the configuration the metric is quoted on; the
-    # others are the remaining benchmark configurations of the reference path, kept for one-off measurements
+    # others are the remaining benchmark configurations of the reference path
     "headline": (1, 8, 16384, 64, "float16", False),
     "causal_bf16": (1, 8, 16384, 64, "bfloat16", True),          # causal prefix path, bf16
     "fp32_1k": (1, 8, 1024, 64, "float32", False),                # the reference's CPU-runnable case
-    "fp32_64k": (1, 8, 65536, 64, "float32", False),              # long non-causal fp32 (one GPU's view)
+    "fp32_64k": (1, 8, 65536, 64, "float32", False),              # long non-causal fp32 (one GPU, unsharded)
     "vit_4097": (8, 3, 4097, 64, "float16", False),               # ViT-Tiny attention at 1024x1024 input, NEEDS_MASK
     "swin_s1": (512, 3, 49, 32, "float16", False, "bias"),        # Swin-T stage-1 windows with relative-position bias
     "swin_s4": (8, 24, 49, 32, "float16", False, "bias"),
@@ -43,6 +48,7 @@ WORKLOADS = {
     "small": (1, 8, 2048, 64, "float16", False),
     "prof4k": (1, 8, 4096, 64, "float16", False),      # ncu capture size: same kernels, a few hundred MB on the device
 }
+MIN_REGION_S = 2.0        # the timed region of the headline number lasts at least this long
 
 
 def flops(b, h, n, d, causal):
@@ -52,7 +58,7 @@ def flops(b, h, n, d, causal):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (the tcgen05 backward), from one
-# ncu capture of this file's own command line at that workload (profiles/bwd_tc_fold_tc_headline_dram.md)
+# ncu capture of this file's own command line at that workload
 NCU_TRAFFIC_BYTES = {"headline": 102034944 + 20017920}
 
 
@@ -90,18 +96,13 @@ class ClockSampler:
         """host time stamp; samples between two marks are the ones taken under load"""
         return time.time()
 
-    def stop(self, t0=None, t1=None):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=2)
-            except Exception:
-                self.proc.kill()
-        rows = [r for (ts, r) in self.rows if (t0 is None or ts >= t0) and (t1 is None or ts <= t1 + 0.15)]
+    def summary(self, t0=None, t1=None):
+        rows = [r for (ts, r) in self.rows if (t0 is None or ts >= t0) and (t1 is None or ts <= t1)]
         if not rows:
             rows = [r for (_, r) in self.rows]
         sm = sorted(float(r[1]) for r in rows if len(r) > 8 and r[1].replace(".", "").isdigit())
         mx = [float(r[2]) for r in rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        pw = sorted(float(r[3]) for r in rows if len(r) > 8 and r[3].replace(".", "").isdigit())
         reasons = set()
         for r in rows:
             if len(r) > 8:
@@ -109,7 +110,15 @@ class ClockSampler:
                     if val.lower().startswith("active"):
                         reasons.add(name)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w": pw[len(pw) // 2] if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
 
 
 def cpu_sample(b, h, n, d, dtype, causal, rows, threads):
@@ -165,9 +174,259 @@ def run_reference(args, wl):
             "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32 arithmetic on " + dt_name + " inputs", "data": "synthetic", "impl": "reference",
             "config": {"workload": args.workload, "shape": [b, h, n, d], "causal": causal},
+            "note": "CPU restatement of the reference's algorithm on the host cores (the reference has no CPU path); "
+                    "the reference's own GPU code on this GPU is the `reference_gpu` object of the default line",
             "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# pieces of the default line
+# ---------------------------------------------------------------------------------------------------------
+def ev_pair():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def timed(fn, n):
+    """mean milliseconds of n back-to-back calls of fn(i), CUDA events on the current stream"""
+    e0, e1 = ev_pair()
+    e0.record()
+    for i in range(n):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+class Workload:
+    """Device-resident rotating input sets of one workload and its fwd+bwd step through the library."""
+
+    def __init__(self, name, dev, rank=0, rot_bytes=260_000_000):
+        import elsa_b200 as E
+        from elsa_b200.attention_bwd import _backward_impl
+        self.E, self._bwd = E, _backward_impl
+        wl = WORKLOADS[name]
+        self.name = name
+        self.b, self.h, self.n, self.d, dt_name, self.causal = wl[:6]
+        self.use_bias = len(wl) > 6
+        self.dtype = getattr(torch, dt_name)
+        self.dt_name = dt_name
+        b, h, n, d = self.b, self.h, self.n, self.d
+        self.set_bytes = 4 * b * h * n * d * torch.empty((), dtype=self.dtype).element_size()
+        # enough input sets to exceed the 126 MB L2 (at most 32), so that a step never finds its operands there
+        self.rot = int(min(32, max(3, -(-rot_bytes // self.set_bytes)))) if self.set_bytes < 400_000_000 else 2
+        g = torch.Generator().manual_seed(1234 + rank)
+        self.host = [[torch.randn(b, h, n, d, generator=g).to(self.dtype).pin_memory() for _ in range(4)] for _ in range(self.rot)]
+        self.sets = [[t.to(dev) for t in s] for s in self.host]
+        self.bias = (torch.randn(1, h, n, n, generator=g) * 0.02).to(dev) if self.use_bias else None
+        self.fwd_f, self.bwd_f = flops(b, h, n, d, self.causal)
+
+    def step(self, i, ev=None):
+        q, k, v, do = self.sets[i % self.rot]
+        if ev:
+            ev[0].record()
+        out, rm, rz, qc, kc, vc = self.E.attention._forward_impl(q, k, v, bias=self.bias, is_causal=self.causal,
+                                                                 summary_dtype=self.dtype, part_width=0, q_chunk=0, want_state=True)
+        if ev:
+            ev[1].record()
+        res = self._bwd(qc, kc, vc, out, do, bias=self.bias, is_causal=self.causal, row_m=rm, row_z=rz, want_dbias=self.use_bias)
+        if ev:
+            ev[2].record()
+        return out, res
+
+    def split(self, steps):
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+        for i in range(steps):
+            self.step(i, evs[i])
+        torch.cuda.synchronize()
+        return (sum(e[0].elapsed_time(e[1]) for e in evs) / steps, sum(e[1].elapsed_time(e[2]) for e in evs) / steps)
+
+
+def measure_fma_peak(lib, dev):
+    """FP32-FMA rate of this GPU from the library's register-resident FMA chain, about half a second per form."""
+    sink = torch.zeros(4, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    blocks = 148 * 8
+    best = {}
+    for packed in (0, 1):
+        iters = 20000
+        lib.elsa_debug_fma_rate(sink.data_ptr(), blocks, iters, packed, stream)
+        torch.cuda.synchronize()
+        ms = timed(lambda i: lib.elsa_debug_fma_rate(sink.data_ptr(), blocks, iters, packed, stream), 2)
+        iters = int(iters * 250.0 / max(ms, 1e-3))           # about 0.25 s per launch
+        ms = timed(lambda i: lib.elsa_debug_fma_rate(sink.data_ptr(), blocks, iters, packed, stream), 2)
+        best["packed_f32x2" if packed else "scalar"] = blocks * 256 * iters * 32 / (ms * 1e-3) / 1e12
+    return {"tflops": max(best.values()), "forms": best, "how": "register-resident FMA chains, 148*8 CTAs x 256 threads, ~0.25 s per launch, CUDA events"}
+
+
+def measure_phase2(lib, dev, hbm_gbs):
+    """Achieved HBM GB/s of the streaming passes (phase-2 merge / scan, backward pre- and post-pass) through the C ABI,
+    at the headline plan (fp16, 2 partitions, 131072 rows; buffers rotated so that nothing is L2-resident) and at the
+    long fp32 case's 32 partitions (one 1 GiB query chunk of summaries)."""
+    from elsa_b200 import _lib
+    stream = torch.cuda.current_stream().cuda_stream
+    out = {}
+
+    def run(tag, fn, nbytes, reps):
+        fn(0)
+        torch.cuda.synchronize()
+        ms = timed(fn, reps)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[tag] = {"ms": ms, "bytes": nbytes, "gbs": gbs, "frac": gbs / hbm_gbs}
+
+    for tag, dtype, parts, bh, rows_q, nset in (("headline_plan_f16_P2", torch.float16, 2, 8, 16384, 6),
+                                                 ("long_fp32_P32_chunk", torch.float32, 32, 8, 1024, 1)):
+        d = 64
+        es = torch.empty((), dtype=dtype).element_size()
+        sdt = _lib.dtype_code(dtype)
+        rows = bh * rows_q
+        sets = []
+        for _ in range(nset):
+            m = torch.randn(parts, rows, device=dev)
+            z = torch.rand(parts, rows, device=dev) + 0.5
+            s = torch.randn(parts, rows, d, device=dev).to(dtype)
+            sets.append((m, z, s, torch.empty_like(m), torch.empty_like(z), torch.empty_like(s),
+                         torch.empty(rows, d, device=dev, dtype=dtype), torch.empty(rows, device=dev), torch.empty(rows, device=dev)))
+        sum_bytes = parts * rows * (d * es + 8)
+        out_bytes = rows * (d * es + 8)
+
+        def merge(i):
+            m, z, s, _, _, _, o, rm, rz = sets[i % nset]
+            lib.elsa_merge_final(m.data_ptr(), z.data_ptr(), s.data_ptr(), o.data_ptr(), rm.data_ptr(), rz.data_ptr(), sdt, sdt,
+                                 parts, bh, 0, rows_q, rows_q, d, 1, stream)
+
+        def scan(i):
+            m, z, s, mo, zo, so = sets[i % nset][:6]
+            lib.elsa_prefix_scan(m.data_ptr(), z.data_ptr(), s.data_ptr(), mo.data_ptr(), zo.data_ptr(), so.data_ptr(), sdt,
+                                 parts, bh, rows_q, d, stream)
+
+        def step1(i):
+            m, z, s, mo, zo, so = sets[i % nset][:6]
+            lib.elsa_scan_step(m.data_ptr(), z.data_ptr(), s.data_ptr(), mo.data_ptr(), zo.data_ptr(), so.data_ptr(), sdt,
+                               parts, bh, rows_q, d, 1, stream)
+
+        def up(i):
+            m, z, s, mo, zo, so = sets[i % nset][:6]
+            lib.elsa_upsweep_level(m.data_ptr(), z.data_ptr(), s.data_ptr(), mo.data_ptr(), zo.data_ptr(), so.data_ptr(), sdt,
+                                   parts, bh, rows_q, d, stream)
+
+        reps = 12 if nset > 1 else 4
+        run(f"{tag}.merge_final", merge, sum_bytes + out_bytes, reps)
+        run(f"{tag}.prefix_scan", scan, 2 * sum_bytes, reps)
+        run(f"{tag}.scan_step", step1, 3 * sum_bytes - (d * es + 8) * rows, reps)     # partition 0 has no left neighbour
+        run(f"{tag}.upsweep_level", up, sum_bytes + (parts + 1) // 2 * rows * (d * es + 8), reps)
+        del sets
+    # backward pre-pass at the headline shape: D and LSE from out, dO and the row state
+    bh, n, d = 8, 16384, 64
+    sets = [(torch.randn(bh, n, d, device=dev).half(), torch.randn(bh, n, d, device=dev).half(), torch.randn(bh, n, device=dev),
+             torch.rand(bh, n, device=dev) + 0.5, torch.empty(bh, n, device=dev), torch.empty(bh, n, device=dev)) for _ in range(6)]
+
+    def pre(i):
+        o, g, rm, rz, rd, rl = sets[i % 6]
+        lib.elsa_bwd_preprocess(o.data_ptr(), g.data_ptr(), rm.data_ptr(), rz.data_ptr(), rd.data_ptr(), rl.data_ptr(), 1, bh, n, d, stream)
+
+    run("headline_f16.bwd_preprocess", pre, 2 * bh * n * d * 2 + 4 * bh * n * 4, 12)
+    return out
+
+
+def measure_reference_gpu(wl: Workload, steps):
+    """The unmodified reference on this GPU, same tensors, same events: ms per forward + backward step."""
+    try:
+        from baseline import reference as R
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"baseline/reference.py does not import: {exc}"[:200]}
+    ok, why = R.available()
+    if not ok:
+        return {"unavailable": why}
+    try:
+        ref = R.load()
+
+        def rstep(i):
+            q, k, v, do = wl.sets[i % wl.rot]
+            qg, kg, vg = (t.detach().requires_grad_(True) for t in (q, k, v))
+            ref.twopass_attention_train(qg, kg, vg, bias=wl.bias, is_causal=wl.causal).backward(do)
+
+        def rfwd(i):
+            q, k, v, _ = wl.sets[i % wl.rot]
+            ref.twopass_attention(q, k, v, bias=wl.bias, is_causal=wl.causal)
+
+        t0 = time.time()
+        for i in range(2):          # includes the Triton JIT of every kernel variant
+            rstep(i)
+            rfwd(i)
+        torch.cuda.synchronize()
+        jit_s = time.time() - t0
+        ms = timed(rstep, steps)
+        fms = timed(rfwd, steps)
+        tf = (wl.fwd_f + wl.bwd_f) / (ms * 1e-3) / 1e12
+        return {"impl": "elsa_twopass_clean (Triton JIT for this GPU + its CUDA phase-2 reduce), twopass_attention_train fwd+bwd",
+                "ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "steps": steps, "forward_only_ms": fms,
+                "forward_only_value": wl.fwd_f / (fms * 1e-3) / 1e12, "warmup_incl_jit_s": jit_s}
+    except Exception as exc:  # noqa: BLE001 - the reference arm must not take the bench line down
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def measure_seq_sharded(dev, rank, world, dist, steps=2):
+    """The long fp32 case (B=1 H=8 N=65536 d=64, non-causal, 2048-wide partitions) with K/V sharded along the sequence
+    over the ranks: forward = local fold + cross-GPU merge, backward = local dK/dV + reduce_scatter of dQ.  With one
+    rank the same problem runs unsharded through the ordinary operator."""
+    from elsa_b200 import parallel as P
+    import elsa_b200 as E
+    from elsa_b200.attention_bwd import _backward_impl
+    b, h, n, d = WORKLOADS["fp32_64k"][:4]
+    g = torch.Generator().manual_seed(4321)
+    q, k, v, do = (torch.randn(b, h, n, d, generator=g).to(dev) for _ in range(4))
+    fwd_f, bwd_f = flops(b, h, n, d, False)
+    per = n // world
+    lo, hi = rank * per, (rank + 1) * per
+    ks, vs = k[:, :, lo:hi].contiguous(), v[:, :, lo:hi].contiguous()
+    marks = {}
+
+    def step(i, split=False):
+        if world == 1:
+            out, rm, rz, qc, kc, vc = E.attention._forward_impl(q, k, v, bias=None, is_causal=False, summary_dtype=torch.float32,
+                                                                part_width=2048, q_chunk=0, want_state=True)
+            _backward_impl(qc, kc, vc, out, do, bias=None, is_causal=False, row_m=rm, row_z=rz, want_dbias=False)
+            return
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if split else None
+        if split:
+            e[0].record()
+        m, z, s = P.local_shard_summary(q, ks, vs, key_offset=lo, is_causal=False, part_width=2048)
+        if split:
+            e[1].record()
+        out, rm, rz = P.merge_shards_on_gpu(m, z, s, q.dtype, gather=True)
+        out = out.reshape(b, h, n, d)
+        if split:
+            e[2].record()
+        dq_p, dk, dv = P.local_shard_backward(q, ks, vs, out, do, rm, rz, key_offset=lo, is_causal=False)
+        if split:
+            e[3].record()
+        P.reduce_dq_across_ranks(dq_p, scatter=True)
+        if split:
+            e[4].record()
+            torch.cuda.synchronize()
+            for name, a, c in (("fold_ms", 0, 1), ("merge_exchange_ms", 1, 2), ("backward_ms", 2, 3), ("dq_exchange_ms", 3, 4)):
+                marks[name] = e[a].elapsed_time(e[c])
+
+    step(0)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = timed(step, steps)
+    step(0, split=True)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    res = {"workload": "fp32 B=1 H=8 N=65536 d=64 non-causal fwd+bwd, K/V sharded along the sequence, 2048-wide partitions",
+           "n_gpus": world, "ms_per_step": ms, "value": (fwd_f + bwd_f) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "scaling": "strong", "steps": steps,
+           "collectives": "none (one rank: unsharded operator)" if world == 1 else
+           "all_reduce(MAX) m 2 MB; reduce_scatter(SUM) [s|z] 136 MB fp32 per rank; all_gather out + state; reduce_scatter(SUM) dQ 134 MB fp32 per rank"}
+    if marks:
+        res["split_rank0_ms"] = marks
+    return res
 
 
 def main():
@@ -179,20 +438,19 @@ def main():
     ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the side measurements (other configurations, phase-2 bandwidth, FMA peak, reference on the GPU, sequence-sharded case)")
+    ap.add_argument("--min-region-s", type=float, default=MIN_REGION_S)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = WORKLOADS[args.workload]
+    wl_def = WORKLOADS[args.workload]
     if args.impl == "reference":
-        return run_reference(args, wl)
+        return run_reference(args, wl_def)
 
     import elsa_b200 as E
     from elsa_b200 import _lib
-    from elsa_b200.attention_bwd import _backward_impl
     lib = _lib.load()   # raises if the CUDA library is missing: there is no fallback
 
-    b, h, n, d, dt_name, causal = wl[:6]
-    use_bias = len(wl) > 6
-    dtype = getattr(torch, dt_name)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -204,33 +462,22 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    # synthetic inputs: iid N(0,1), CPU generator seeded per rank; ROT input sets are rotated so that a
-    # step never finds its operands in L2 (one set = 8 tensors of B*H*N*D elements)
-    set_bytes = 4 * b * h * n * d * torch.empty((), dtype=dtype).element_size()
-    ROT = int(min(32, max(3, -(-260_000_000 // set_bytes))))   # enough sets to exceed the 126 MB L2 (at most 32)
-    g = torch.Generator().manual_seed(1234 + rank)
-    host = [[torch.randn(b, h, n, d, generator=g).to(dtype).pin_memory() for _ in range(4)] for _ in range(ROT)]
-    sets = [[t.to(dev) for t in s] for s in host]
-    fwd_f, bwd_f = flops(b, h, n, d, causal)
-    bias = (torch.randn(1, h, n, n, generator=g) * 0.02).to(dev) if use_bias else None
-
-    def step(i, ev=None):
-        q, k, v, do = sets[i % ROT]
-        if ev:
-            ev[0].record()
-        out, rm, rz, qc, kc, vc = E.attention._forward_impl(q, k, v, bias=bias, is_causal=causal, summary_dtype=dtype,
-                                                            part_width=0, q_chunk=0, want_state=True)
-        if ev:
-            ev[1].record()
-        res = _backward_impl(qc, kc, vc, out, do, bias=bias, is_causal=causal, row_m=rm, row_z=rz, want_dbias=use_bias)
-        if ev:
-            ev[2].record()
-        return out, res
+    # synthetic inputs: iid N(0,1), CPU generator seeded per rank
+    wl = Workload(args.workload, dev, rank)
+    b, h, n, d, dtype, causal, dt_name = wl.b, wl.h, wl.n, wl.d, wl.dtype, wl.causal, wl.dt_name
+    ROT, set_bytes, fwd_f, bwd_f, step = wl.rot, wl.set_bytes, wl.fwd_f, wl.bwd_f, wl.step
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -238,44 +485,35 @@ def main():
     for i in range(args.warmup):
         step(i)
     barrier()
-    # keep the GPU busy for at least ~0.5 s before the timed region so that the clock samples (100 ms
-    # period) taken during it describe a loaded, settled GPU; these extra steps are untimed warm-up
-    t_busy = time.time()
-    mark_load = sampler.mark() + 0.2     # the load of the same kind starts here; skip its first 200 ms (ramp)
-    while time.time() - t_busy < 0.5:
-        step(0)
-        torch.cuda.synchronize()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    # an untimed block of the same steps gives the step time from which the number of repetitions follows: the timed
+    # region is the --steps block repeated `reps` times back to back so that it lasts >= min-region-s (a sustained
+    # figure under the power cap, to be set against the sustained peak); all ranks use the same count
+    est_ms = max_over_ranks(timed(step, args.steps))
+    reps = max(1, min(2000, math.ceil(args.min_region_s * 1e3 / max(est_ms * args.steps, 1e-3))))
+    n_timed = reps * args.steps
     l0 = lib.elsa_kernel_launches()
     barrier()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
+    mark0 = sampler.mark()
+    t_start, t_end = ev_pair()
     t_start.record()
-    for i in range(args.steps):
+    for i in range(n_timed):
         step(i)
     t_end.record()
     barrier()
+    mark1 = sampler.mark()
     launches = lib.elsa_kernel_launches() - l0
-    total_ms = t_start.elapsed_time(t_end)
+    total_ms = max_over_ranks(t_start.elapsed_time(t_end))
+    clocks = sampler.summary(mark0 + 0.3, mark1) if rank == 0 else None
+    ms_per_step = total_ms / n_timed
+    value = world * (fwd_f + bwd_f) / (ms_per_step * 1e-3) / 1e12
     # the forward / backward split (and with it the dominant kernel's duration for the roofline) comes from a second
     # pass over the same steps with events between the two calls: timing events drain the GPU before they take
     # their time stamp, which costs the timed region above about 1.5 % when they sit inside it
-    for i in range(args.steps):
-        step(i, evs[i])
-    barrier()
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
-    # clock samples: from 200 ms into the pre-load (same steps, same load) to the end of the second pass below;
-    # the timed region alone (tens of ms) is shorter than the sampling period
-    clock_marks = (mark_load, sampler.mark())
-    if dist is not None:
-        t = torch.tensor([total_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    value = world * (fwd_f + bwd_f) / (ms_per_step * 1e-3) / 1e12
+    fwd_ms, bwd_ms = wl.split(args.steps)
+    # scale the split to the sustained step time (the split pass itself is short)
+    k_split = ms_per_step / max(fwd_ms + bwd_ms, 1e-9)
 
-    # The burst figure: MEASURED_PEAKS.json's 1683.8 TFLOP/s is the best of 10 cuBLAS calls on a rested GPU, the timed
+    # The burst figure: MEASURED_PEAKS.json's burst TFLOP/s is the best of 10 cuBLAS calls on a rested GPU, the timed
     # region above runs under a settled power cap.  The same protocol for one step of this path (best of 10 single
     # steps, 50 ms of idle before each, rotating input sets) pairs with that denominator; the sustained value above
     # pairs with the sustained one.
@@ -283,17 +521,14 @@ def main():
     for i in range(10):
         torch.cuda.synchronize()
         time.sleep(0.05)
-        b0 = torch.cuda.Event(enable_timing=True); b1 = torch.cuda.Event(enable_timing=True)
+        b0, b1 = ev_pair()
         b0.record()
         step(i)
         b1.record()
         torch.cuda.synchronize()
         t = b0.elapsed_time(b1)
         burst_ms = t if burst_ms is None else min(burst_ms, t)
-    if dist is not None:
-        t = torch.tensor([burst_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        burst_ms = float(t.item())
+    burst_ms = max_over_ranks(burst_ms)
 
     # the same step replayed from a CUDA graph (the entry points allocate nothing and never synchronise): what is
     # left when launch gaps and host work are taken out; reported beside the eager number, never instead of it
@@ -313,15 +548,10 @@ def main():
         for cg in graphs:
             cg.replay()
         barrier()
-        g0 = torch.cuda.Event(enable_timing=True); g1 = torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for i in range(args.steps):
-            graphs[i % ROT].replay()
-        g1.record()
-        barrier()
-        g_ms = g0.elapsed_time(g1) / args.steps
+        g_n = max(args.steps, min(n_timed, int(1000.0 / max(ms_per_step, 1e-3))))     # about one second of replays
+        g_ms = max_over_ranks(timed(lambda i: graphs[i % ROT].replay(), g_n))
         graph_line = {"ms_per_step": g_ms, "value": world * (fwd_f + bwd_f) / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                      "note": f"{ROT} graphs, one per input set, replayed in rotation"}
+                      "steps": g_n, "note": f"{ROT} graphs, one per input set, replayed in rotation"}
         del graphs
     except Exception as exc:  # noqa: BLE001 - a capture failure must not take the bench line down
         graph_line = {"error": str(exc)[:200]}
@@ -329,6 +559,7 @@ def main():
     # end to end through the public API with host buffers (pinned), copies inside the timed region
     e2e = None
     if not args.no_e2e:
+        host, bias = wl.host, wl.bias
         # Double-buffered pipeline over three streams: H2D of step i+1 and D2H of step i-1 overlap the kernels of
         # step i (PCIe is full duplex); every step still moves its own inputs in and its own results out.
         outs_host = [[torch.empty(b, h, n, d, dtype=dtype).pin_memory() for _ in range(4)] for _ in range(2)]
@@ -366,7 +597,7 @@ def main():
         # the host link is shared with the other tenants of the machine: the faster of two repetitions is reported
         e_ms = None
         for _rep in range(2):
-            t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+            t0, t1 = ev_pair()
             t0.record()
             for i in range(k_e2e):
                 e2e_step(i)
@@ -375,30 +606,85 @@ def main():
             t1.record()
             barrier()
             e_ms = t0.elapsed_time(t1) if e_ms is None else min(e_ms, t0.elapsed_time(t1))
-        if dist is not None:
-            t = torch.tensor([e_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
+        e_ms = max_over_ranks(e_ms)
         nbytes = b * h * n * d * torch.empty((), dtype=dtype).element_size() * 4
         e2e = {"value": world * (fwd_f + bwd_f) / (e_ms / k_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": k_e2e}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": k_e2e,
+               "note": "three-stream pipeline (copy in, compute, copy out); bounded by the host link: every rank moves "
+                       f"{2 * nbytes / 1e6:.0f} MB per step over its own PCIe link and the ranks share host DRAM"}
+        del outs_host, dev_in, keep
 
-    clocks = None
+    # ---- side measurements -------------------------------------------------------------------------------
+    pk = peaks()
+    extras = {}
+    if not args.no_extras:
+        seq = None
+        try:
+            del wl.host
+            seq = measure_seq_sharded(dev, rank, world, dist)
+        except Exception as exc:  # noqa: BLE001
+            seq = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        extras["seq_sharded"] = seq
+        if rank == 0 and world == 1:
+            try:
+                extras["fp32_fma_peak"] = measure_fma_peak(lib, dev)
+            except Exception as exc:  # noqa: BLE001
+                extras["fp32_fma_peak"] = {"error": str(exc)[:200]}
+            try:
+                extras["phase2"] = measure_phase2(lib, dev, pk["hbm_gbs"])
+            except Exception as exc:  # noqa: BLE001
+                extras["phase2"] = {"error": str(exc)[:200]}
+            fma = extras["fp32_fma_peak"].get("tflops")
+            others = {}
+            for name in ("causal_bf16", "fp32_1k", "vit_4097", "swin_s1", "swin_s4"):
+                try:
+                    w2 = Workload(name, dev)
+                    for i in range(3):
+                        w2.step(i)
+                    torch.cuda.synchronize()
+                    k2 = max(5, min(200, int(300.0 / max(timed(w2.step, 3), 1e-3))))       # about 0.3 s
+                    ms2 = timed(w2.step, k2)
+                    tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(w2.dtype), w2.d, w2.n, int(w2.use_bias), int(w2.causal), 1))
+                    tf = (w2.fwd_f + w2.bwd_f) / (ms2 * 1e-3) / 1e12
+                    peak = pk["tflops_sustained"] if tc else fma
+                    others[name] = {"shape": [w2.b, w2.h, w2.n, w2.d], "dtype": w2.dt_name, "causal": w2.causal, "bias": w2.use_bias,
+                                    "ms_per_step": ms2, "value": tf, "unit": "TFLOP/s", "steps": k2,
+                                    "bound": "tensor" if tc else "fp32-fma",
+                                    "peak": peak, "frac": (tf / peak) if peak else None,
+                                    "peak_source": "measured bf16 dense, sustained" if tc else "FMA chain measured in this run"}
+                    del w2
+                except Exception as exc:  # noqa: BLE001
+                    others[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            if seq and "value" in seq and fma:
+                others["fp32_64k"] = {"shape": list(WORKLOADS["fp32_64k"][:4]), "dtype": "float32", "ms_per_step": seq["ms_per_step"],
+                                      "value": seq["value"], "unit": "TFLOP/s", "bound": "fp32-fma", "peak": fma, "frac": seq["value"] / fma}
+            extras["other_configs"] = others
+            extras["reference_gpu"] = measure_reference_gpu(wl, max(3, min(args.steps, 10)))
+
     if rank == 0:
-        # the e2e region that follows is load of the same kind: widen the window to it when the timed region
-        # was shorter than two sampling periods
-        clocks = sampler.stop(clock_marks[0], clock_marks[1])
-    if rank == 0:
-        pk = peaks()
-        uses_tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(dtype), d, n, 0, int(causal), 1))
-        achieved = bwd_f / (bwd_ms * 1e-3) / 1e12
+        sampler.stop()
+        uses_tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(dtype), d, n, int(wl.use_bias), int(causal), 1))
+        bwd_sus = bwd_ms * k_split
+        fwd_sus = fwd_ms * k_split
+        achieved = bwd_f / (bwd_sus * 1e-3) / 1e12
+        if uses_tc:
+            peak, peak_src = pk["tflops_sustained"] or pk["tflops"], pk["source"] + " bf16 dense, sustained (seconds-long loop under the power cap: the timed region is one too)"
+            bound = "tensor"
+        else:
+            fma = (extras.get("fp32_fma_peak") or {}).get("tflops")
+            peak, peak_src, bound = fma, "FP32-FMA chain measured in this run", "fp32-fma"
         roofline = {"kernel": "backward (dQ, dK, dV recompute)" + (" tcgen05" if uses_tc else " fp32-fma"),
-                    "bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["tflops"], "peak_source": pk["source"] + " bf16 dense burst",
-                    "peak_sustained": pk["tflops_sustained"],
-                    "frac_of_sustained": achieved / pk["tflops_sustained"] if pk["tflops_sustained"] else None,
+                    "bound": bound, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": (achieved / peak) if peak else None, "peak_source": peak_src,
+                    "peak_burst": pk["tflops"] if uses_tc else None,
+                    "frac_of_burst": achieved / pk["tflops"] if uses_tc else None,
                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "traffic_unit": "bytes per launch (ncu dram read+write)",
-                    "ms_per_launch": bwd_ms, "forward": {"achieved": fwd_f / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms}}
+                    "ms_per_launch": bwd_sus,
+                    "forward": {"achieved": fwd_f / (fwd_sus * 1e-3) / 1e12, "ms": fwd_sus,
+                                "frac": (fwd_f / (fwd_sus * 1e-3) / 1e12 / peak) if peak else None},
+                    "split_note": "forward / backward shares from a separate event-instrumented pass, scaled to the sustained step time"}
+        if "phase2" in extras:
+            roofline["phase2"] = extras.pop("phase2")
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
@@ -413,15 +699,20 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16" if dtype == torch.float16 else dt_name, "data": "synthetic",
+                "timed_steps": n_timed, "timed_region_s": total_ms * 1e-3,
                 "config": {"workload": args.workload, "shape_per_gpu": [b, h, n, d], "causal": causal, "global_batch": b * world,
-                           "sharding": "batch x heads, no collective", "l2": f"{ROT} rotating input sets, {ROT * set_bytes / 1e6:.0f} MB in total against 126 MB of L2" + (": a step never finds its operands in L2" if ROT * set_bytes > 1.5 * 126e6 else ": smaller than L2, operands may be L2-resident"),
+                           "sharding": "batch x heads, no collective (replica scaling; the path with an exchange step is `seq_sharded`)",
+                           "l2": f"{ROT} rotating input sets, {ROT * set_bytes / 1e6:.0f} MB in total against 126 MB of L2" + (": a step never finds its operands in L2" if ROT * set_bytes > 1.5 * 126e6 else ": smaller than L2, operands may be L2-resident"),
+                           "timed_region": f"the --steps block repeated {reps}x back to back between one pair of events (>= {args.min_region_s} s)",
                            "tensor_cores": uses_tc},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "graph_replay": graph_line,
                 "burst": {"ms_per_step": burst_ms, "value": world * (fwd_f + bwd_f) / (burst_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                           "protocol": "best of 10 single steps, 50 ms idle before each (the protocol of the burst peak)",
-                          "pct_of_burst_peak": 100.0 * (fwd_f + bwd_f) / (burst_ms * 1e-3) / 1e12 / pk["tflops"]}, "gpu_launches": int(launches), "clocks": clocks,
-                "pct_of_peak": 100.0 * value / world / pk["tflops"],
-                "pct_of_sustained_peak": 100.0 * value / world / pk["tflops_sustained"] if pk["tflops_sustained"] else None}
+                          "pct_of_burst_peak": 100.0 * (fwd_f + bwd_f) / (burst_ms * 1e-3) / 1e12 / pk["tflops"]},
+                "gpu_launches": int(launches), "clocks": clocks,
+                "pct_of_sustained_peak": 100.0 * value / world / pk["tflops_sustained"] if pk["tflops_sustained"] else None,
+                "pct_of_burst_peak": 100.0 * value / world / pk["tflops"]}
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_uint, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_int64, c_uint, c_uint64, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # ELSA_B200_LIB points the loader at another build of the same library (a tuning build, an installed copy)
@@ -26,11 +26,16 @@ SIGNATURES = {
     "elsa_last_cuda_error": (c_int, []),
     "elsa_kernel_launches": (c_int64, []),
     "elsa_device_status": (c_int, [c_int]),
+    "elsa_debug_wait_timeout": (c_int, [c_uint64, _P]),
+    "elsa_debug_fma_rate": (c_int, [_P, c_int, c_int64, c_int, _P]),
     "elsa_uses_tensor_cores": (c_int, [c_int] * 6),
     "elsa_phase1_fold": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_uint, _P]),
     "elsa_phase1_fold_shard": (c_int, [_P, _P, _P, _P, _P, _P] + [c_int] * 11 + [c_uint, _P]),
     "elsa_merge_partial": (c_int, [_P] * 6 + [c_int] * 5 + [_P]),
+    "elsa_shard_chunk_elems": (c_int64, [c_int] * 4),
+    "elsa_shard_pack": (c_int, [_P] * 5 + [c_int] * 4 + [_P]),
+    "elsa_shard_finalize": (c_int, [_P] * 5 + [c_int] * 6 + [_P]),
     "elsa_merge_final": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "elsa_scan_step": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
     "elsa_upsweep_level": (c_int, [_P] * 6 + [c_int] * 5 + [_P]),

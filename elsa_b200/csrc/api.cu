@@ -1,6 +1,8 @@
 // C-ABI layer: argument validation, work planning (partition width, query chunking), host
 // orchestration of the two passes and of the backward.  Everything is stream-ordered; nothing
-// here allocates device memory or synchronises.
+// here allocates device memory or synchronises.  Two things live inside the library instead of with the
+// caller: the 64 MiB scratch array of elsa_twopass_forward_static, and one block of pinned host memory for
+// the per-device status words (allocated once, at the first call that needs it).
 #include <algorithm>
 #include <cmath>
 
@@ -22,6 +24,43 @@ static int sm_count() {
     g_sm_count_cache[dev] = n;
   }
   return g_sm_count_cache[dev];
+}
+
+// ---- device status word ------------------------------------------------------------------------
+// One int per device in ONE block of mapped, portable pinned host memory, allocated at the first call that needs it
+// (a host allocation, made once per process; it must not fall inside a stream capture).  Kernels store through the
+// device-side alias, the host reads the word directly: no copy, no synchronisation on the call path.
+int device_status_word(int** dev_ptr, volatile int** host_ptr) {
+  static std::mutex mu;
+  static int* host_block = nullptr;
+  static int* dev_alias[64] = {nullptr};
+  int dev = 0;
+  ELSA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ELSA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!host_block) {
+    void* p = nullptr;
+    ELSA_CUDA_CHECK(cudaHostAlloc(&p, 64 * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+    host_block = static_cast<int*>(p);
+    for (int i = 0; i < 64; ++i) host_block[i] = 0;
+  }
+  if (!dev_alias[dev]) {
+    void* d = nullptr;
+    ELSA_CUDA_CHECK(cudaHostGetDevicePointer(&d, host_block + dev, 0));
+    dev_alias[dev] = static_cast<int*>(d);
+  }
+  if (dev_ptr) *dev_ptr = dev_alias[dev];
+  if (host_ptr) *host_ptr = host_block + dev;
+  return ELSA_OK;
+}
+
+// A wait that gave up earlier leaves the word set until elsa_device_status(1) clears it: every later call that
+// would launch a tensor-core kernel reports it instead of launching.
+static int check_device_status() {
+  volatile int* host = nullptr;
+  const int rc = device_status_word(nullptr, &host);
+  if (rc != ELSA_OK) return rc;
+  return *host != 0 ? ELSA_ERR_DEVICE_TIMEOUT : ELSA_OK;
 }
 
 struct ForwardPlan {
@@ -123,7 +162,11 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.round_p = (dtype == ELSA_F16 && summary_dtype != ELSA_F32) ? 1 : 0;
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
-  if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) return fold_tc(p, dtype, st);
+  if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return fold_tc(p, dtype, st);
+  }
   return fold_simt(p, dtype, st);
 }
 
@@ -148,10 +191,16 @@ extern "C" const char* elsa_strerror(int status) {
 extern "C" int elsa_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int elsa_device_status(int clear) {
-  int v = 0;
-  int w = 0;
-  if (fold_tc_status(&v, clear) != ELSA_OK || bwd_tc_status(&w, clear) != ELSA_OK) return -1;
-  return v != 0 ? v : w;
+  volatile int* host = nullptr;
+  if (device_status_word(nullptr, &host) != ELSA_OK) return -1;
+  const int v = *host;
+  if (clear && v != 0) *host = 0;
+  return v;
+}
+
+extern "C" int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return ELSA_ERR_INVALID_ARGUMENT;   // at most one second
+  return debug_wait_timeout(limit_ns, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
@@ -325,7 +374,11 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
   p.n_keys = n_ctx; p.key_offset = 0; p.dq_f32 = 0;
-  if (use_tc) return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  if (use_tc) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -370,7 +423,11 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
   p.n_keys = n_keys; p.key_offset = key_offset; p.dq_f32 = 1;
-  if (use_tc) return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  if (use_tc) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -402,6 +459,7 @@ extern "C" int64_t elsa_row_stats_workspace_bytes(int dtype, int batch, int head
 }
 
 // ---- forward without any caller-supplied or freshly allocated scratch --------------------------
+// (The one exception to "buffers belong to the caller" in this file.)
 // Some callers have no way to hand over a workspace: a host runtime that reaches this library through a
 // minimal FFI and owns no device allocator, or a serving process whose device memory was carved up once at
 // start-up and whose request path is forbidden to allocate.  For them the partition summaries of the forward
@@ -437,14 +495,28 @@ extern "C" int elsa_twopass_forward_static(const void* q, const void* k, const v
                                            float* row_z, int dtype, int batch, int heads, int n_ctx, int head_dim,
                                            int is_causal, void* stream) {
   if (n_ctx == 0) return ELSA_OK;
-  // same plan as elsa_twopass_forward with library-chosen partitions, no bias, summaries in the input dtype
-  const int64_t need = elsa_forward_workspace_bytes(dtype, dtype, batch, heads, n_ctx, head_dim, 0, is_causal, 0, 0, 0u);
-  if (need < 0) return ELSA_ERR_INVALID_ARGUMENT;
-  if (need > elsa::kStaticScratchBytes) return ELSA_ERR_WORKSPACE;   // problem too large for the built-in scratch
+  // same plan as elsa_twopass_forward with library-chosen partitions, no bias, summaries in the input dtype; the
+  // query chunk is the largest multiple of the kernel's query tile whose summaries fit the built-in array, so a
+  // long problem runs as several chunks through the same array instead of being refused
+  ForwardPlan pl;
+  int rc0 = plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, 0, 0u, &pl);
+  if (rc0 != ELSA_OK) return rc0;
+  int q_chunk = 0;   // 0: the automatic chunk already fits
+  if (plan_bytes(pl) > elsa::kStaticScratchBytes) {
+    const int64_t row_bytes = static_cast<int64_t>(pl.n_parts) * batch * heads * (static_cast<int64_t>(head_dim) * dtype_size(dtype) + 8);
+    int64_t rows = (elsa::kStaticScratchBytes / row_bytes) / pl.tile_m * pl.tile_m;
+    for (; rows >= pl.tile_m; rows -= pl.tile_m) {
+      if (plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, static_cast<int>(rows), 0u, &pl) != ELSA_OK)
+        return ELSA_ERR_INVALID_ARGUMENT;
+      if (plan_bytes(pl) <= elsa::kStaticScratchBytes) break;
+    }
+    if (rows < pl.tile_m) return ELSA_ERR_WORKSPACE;   // not even one query tile of summaries fits
+    q_chunk = static_cast<int>(rows);
+  }
   void* scratch = nullptr;
   int rc = elsa::static_scratch_ptr(&scratch);
   if (rc != ELSA_OK) return rc;
   // Nothing in the scratch has to start at zero: phase 1 writes every summary that phase 2 reads.
   return elsa_twopass_forward(q, k, v, nullptr, 0, 0, 0, 0, out, row_m, row_z, scratch, elsa::kStaticScratchBytes, dtype,
-                              dtype, batch, heads, n_ctx, head_dim, is_causal, 0, 0, 0u, stream);
+                              dtype, batch, heads, n_ctx, head_dim, is_causal, 0, q_chunk, 0u, stream);
 }

@@ -53,19 +53,6 @@ namespace elsa {
 
 using namespace tc;
 
-static __device__ int g_bwd_status = 0;
-
-// Optional per-phase timestamps of CTA (0,0) for tuning builds (-DELSA_TRACE); compiled out otherwise.
-#ifdef ELSA_TRACE
-__device__ long long g_bwd_trace[5][256][4];
-#define ELSA_TR(role, it, slot)                                                              \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 256) g_bwd_trace[role][it][slot] = clock64(); \
-  } while (0)
-#else
-#define ELSA_TR(role, it, slot) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kQStages = 2;
@@ -77,13 +64,6 @@ constexpr int kStageBytes = 2 * kTile + 2 * kVecBytes;
 constexpr int kBwdSmem = 2 * kTile + kQStages * kStageBytes + 4 * kTile + 2 * kTile + 1024;
 constexpr int kThreads = 512;
 constexpr uint32_t kTmemCols = 512;
-#ifndef ELSA_BWD_POLY_EVERY
-#define ELSA_BWD_POLY_EVERY 0
-#endif
-// in every kPolyEvery-th group of four exponentials two are evaluated on the FMA pipe (0 = none).  Measured at the
-// 16K shape: 1 (half of them) 1.67 ms, 2 (a quarter) 1.62 ms, 0 1.64-1.67 ms, and the causal case 10 % slower
-// with either: no gain, so it stays off.
-constexpr int kPolyEvery = ELSA_BWD_POLY_EVERY;
 
 enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS = 15, BAR_DQ_FULL = 16, BAR_DQ_FREE = 17, BAR_DONE = 18, BAR_KVT = 19, BAR_LDS = 20, BAR_DP = 21 };
 
@@ -94,6 +74,7 @@ struct BwdTcParams {
   int n_ctx, n_pad, bh, is_causal;
   int n_keys, key_offset;                      // K/V rows of this launch and the sequence index of the first one
   float scale, scale_log2;
+  int* status;   // the device's status word (mapped host memory)
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -187,7 +168,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kQStages;
         // stage st held tile it-2: its dV / dK retired before the commit that announced dP^T of tile it-1
-        if (it >= kQStages && !mbar_wait(bar_dpx((it - 1) & 1), ((it - 1) / 2) & 1, &abort_flag, &g_bwd_status, BAR_Q_FREE)) break;
+        if (it >= kQStages && !mbar_wait(bar_dpx((it - 1) & 1), ((it - 1) / 2) & 1, &abort_flag, prm.status, BAR_Q_FREE)) break;
         const int qrow = (it_begin + it) * 128;
         mbar_arrive_expect_tx(bar_q_full(st), kStageBytes);
         tma_load_3d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, bh);
@@ -237,9 +218,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mma_ts_x4_cols<8, 32, 40, 128>(tdV, tdP(h), ddo_mn[st][h], idesc_kv, acc);
         mma_ts_x4_cols<8, 32, 40, 128>(tdK, tdP(h) + 16, dq_mn[st][h], idesc_kv, acc);
       };
-      bool ok = mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV) &&
-                mbar_wait(bar_kvt, 0, &abort_flag, &g_bwd_status, BAR_KVT) &&
-                (n_it == 0 || mbar_wait(bar_q_full(0), 0, &abort_flag, &g_bwd_status, BAR_Q_FULL));
+      bool ok = mbar_wait(bar_kv, 0, &abort_flag, prm.status, BAR_KV) &&
+                mbar_wait(bar_kvt, 0, &abort_flag, prm.status, BAR_KVT) &&
+                (n_it == 0 || mbar_wait(bar_q_full(0), 0, &abort_flag, prm.status, BAR_Q_FULL));
       if (ok && n_it > 0) {
         tc_fence_after();
         mma_ts_x4<8, 2>(tS0, tK, dq_k[0], idesc_st, 0u);
@@ -254,7 +235,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       // dV / dK / dP^T stand between the halves' arrival and the next dS phase: measured 1.95 ms against 1.59 ms.)
       auto issue_dq = [&](int it_q, auto STQ) {       // dQ of tile it_q, whose dS^T sits in buffer STQ
         constexpr int stq = decltype(STQ)::value;
-        if (it_q > 0 && !(ok = mbar_wait(bar_dq_free, (it_q - 1) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FREE))) return;
+        if (it_q > 0 && !(ok = mbar_wait(bar_dq_free, (it_q - 1) & 1, &abort_flag, prm.status, BAR_DQ_FREE))) return;
         mma_ss_x4<128, 128>(tdQ, dds[stq], bk_mn, idesc_dq, 0u);
         mma_ss_x4<128, 128>(tdQ, dds[stq] + 512, bk_mn + 512, idesc_dq, 1u);
         mma_commit(bar_q_free(stq));   // dQ(it_q) is complete: the drain warps may read it
@@ -263,21 +244,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         constexpr int st = decltype(ST)::value;
         const bool more = it + 1 < n_it;
         const uint32_t pit = it & 1;
-        ELSA_TR(0, it, 0);
         if (more) {
-          ok = mbar_wait(bar_q_full(st ^ 1), ((it + 1) / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL) &&
-               mbar_wait(bar_lds, pit, &abort_flag, &g_bwd_status, BAR_LDS);
+          ok = mbar_wait(bar_q_full(st ^ 1), ((it + 1) / kQStages) & 1, &abort_flag, prm.status, BAR_Q_FULL) &&
+               mbar_wait(bar_lds, pit, &abort_flag, prm.status, BAR_LDS);
           if (!ok) return;
           tc_fence_after();
           mma_ts_x4<8, 2>(tS0, tK, dq_k[st ^ 1], idesc_st, 0u);
           mma_commit(bar_s);
         }
-        ELSA_TR(0, it, 1);
-        if (!(ok = mbar_wait(bar_pds, pit, &abort_flag, &g_bwd_status, BAR_PDS))) return;
+        if (!(ok = mbar_wait(bar_pds, pit, &abort_flag, prm.status, BAR_PDS))) return;
         tc_fence_after();
         issue_dkv(ST, I0{}, it == 0 ? 0u : 1u);
         issue_dkv(ST, I1{}, 1u);
-        ELSA_TR(0, it, 2);
         if (more) {
           // one commit for two facts: dP^T of the next tile is in TMEM, and dV / dK of this tile have retired, so
           // Q, dO and the row statistics of this tile are not read again (dQ takes dS^T and K) and the producer may
@@ -286,7 +264,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           mma_commit(bar_dpx(st ^ 1));
         }
         issue_dq(it, ST);
-        ELSA_TR(0, it, 3);
       };
       for (int it = 0; ok && it < n_it; it += 2) {
         iteration(it, I0{});
@@ -300,14 +277,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int it = 0; it < n_it; ++it) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_q_free(it % kQStages), (it / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_DQ_FULL))) break;
-      if (tid == 256) ELSA_TR(3, it, 0);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_q_free(it % kQStages), (it / kQStages) & 1, &abort_flag, prm.status, BAR_DQ_FULL))) break;
       tc_fence_after();
       uint32_t r0[32], r1[32];
       tmem_ld32(tdQ + lane_off, r0);
       tmem_ld32(tdQ + lane_off + 32, r1);
       tmem_wait_ld();
-      if (tid == 256) ELSA_TR(3, it, 1);
       tc_fence_before();
       mbar_arrive(bar_dq_free);
       // Stage the 128 x 64 fp32 tile in shared memory (two 32-column blocks, 128-byte swizzle) and let the TMA
@@ -331,7 +306,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tma_reduce_add_3d(&tmap_dq, sDQ + kTile, 32, qrow0, bh);
         bulk_commit_group();
       }
-      if (tid == 256) ELSA_TR(3, it, 2);
     }
     if (tid == 256) bulk_wait_group<0>();                 // reductions must have left shared memory before the CTA exits
   } else {
@@ -349,7 +323,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
     // one-time copy of this CTA's K (warps 0-3) / V (warps 4-7) tile from shared memory into TMEM as the A operand
     // of S^T / dP^T: lane = key row, 32 columns of 16-bit pairs; the smem row is un-swizzled on the way
-    if (!__all_sync(0xffffffffu, mbar_wait(bar_kv, 0, &abort_flag, &g_bwd_status, BAR_KV))) alive = false;
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_kv, 0, &abort_flag, prm.status, BAR_KV))) alive = false;
     if (alive) {
       const uint8_t* src = smem_gen + ((half == 0 ? sK : sV) - smem_base) + row * 128;
       uint32_t w[32];
@@ -367,11 +341,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (int it = 0; alive && it < n_it; ++it) {
       const int st = it % kQStages;
       const int q_tile0 = (it_begin + it) * 128;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, it & 1, &abort_flag, &g_bwd_status, BAR_SP))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, it & 1, &abort_flag, prm.status, BAR_SP))) { alive = false; break; }
       // the row statistics of this stage were written by the bulk copies that complete on q_full: observe that
       // barrier directly (it completed before the MMAs behind bar_s were issued, so this never spins)
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_q_full(st), (it / kQStages) & 1, &abort_flag, &g_bwd_status, BAR_Q_FULL))) { alive = false; break; }
-      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 0);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_q_full(st), (it / kQStages) & 1, &abort_flag, prm.status, BAR_Q_FULL))) { alive = false; break; }
       tc_fence_after();
       const float4* nl4 =reinterpret_cast<const float4*>(smem_gen + (sNL(st) - smem_base)) + half * 16;
       const float4* nd4 = reinterpret_cast<const float4*>(smem_gen + (sND(st) - smem_base)) + half * 16;
@@ -396,12 +369,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         const float2 x0 = __ffma2_rn(make_float2(p[4 * g], p[4 * g + 1]), c2, make_float2(nl.x, nl.y));
         const float2 x1 = __ffma2_rn(make_float2(p[4 * g + 2], p[4 * g + 3]), c2, make_float2(nl.z, nl.w));
         p[4 * g] = fast_exp2(x0.x); p[4 * g + 1] = fast_exp2(x0.y);
-        if (kPolyEvery > 0 && g % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
-          const float2 e1 = exp2_fma_pair(x1);                    // FMA pipe instead of the ex2 unit
-          p[4 * g + 2] = e1.x; p[4 * g + 3] = e1.y;
-        } else {
-          p[4 * g + 2] = fast_exp2(x1.x); p[4 * g + 3] = fast_exp2(x1.y);
-        }
+        p[4 * g + 2] = fast_exp2(x1.x); p[4 * g + 3] = fast_exp2(x1.y);
         if (masked) {
           const int qc = q_tile0 + half * 64 + 4 * g;               // first query of this group of 4
           const bool causal = prm.is_causal;
@@ -410,12 +378,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             p[4 * g + e] = (key_ok && (!causal || qc + e >= key_seq)) ? p[4 * g + e] : 0.f;
         }
       }
-      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 1);
 
       // ---- phase B: dS^T = P^T * (dP^T - D); P^T and dS^T (16-bit) handed to dV / dK in two 32-query chunks ----
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_dpx(it & 1), (it / 2) & 1, &abort_flag, &g_bwd_status, BAR_DP))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dpx(it & 1), (it / 2) & 1, &abort_flag, prm.status, BAR_DP))) { alive = false; break; }
       tc_fence_after();
-      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 2);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t rp[32];
@@ -452,11 +418,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_pds);
-      if (lane == 0 && (warp & 3) == 0) ELSA_TR(1 + half, it, 3);
     }
 
     // ---- epilogue: dK, dV of this key tile (tcgen05.ld is warp-collective: only the stores are predicated) ----
-    if (alive && n_it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_done, 0, &abort_flag, &g_bwd_status, BAR_DONE))) alive = false;
+    if (alive && n_it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_done, 0, &abort_flag, prm.status, BAR_DONE))) alive = false;
     if (alive) {
       uint32_t rk[32], rv[32];
       if (n_it > 0) {
@@ -592,6 +557,7 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, bh, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, bh, 128)) != ELSA_OK) return rc;
   BwdTcParams prm;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.is_causal = p.is_causal;
   prm.n_keys = NK; prm.key_offset = p.key_offset;
@@ -620,21 +586,5 @@ int bwd_tc(const BwdParams& p, const void* out, const float* row_m, const float*
   return bwd_tc_t<__nv_bfloat16>(p, out, row_m, row_z, workspace, dtype, st);
 }
 
-#ifdef ELSA_TRACE
-extern "C" int elsa_debug_bwd_trace(long long* host_buf) {
-  return cudaMemcpyFromSymbol(host_buf, g_bwd_trace, sizeof(long long) * 5 * 256 * 4) == cudaSuccess ? 0 : 3;
-}
-#endif
-
-int bwd_tc_status(int* status_out, int clear) {
-  int v = 0;
-  ELSA_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_bwd_status, sizeof(int)));
-  if (clear && v != 0) {
-    int zero = 0;
-    ELSA_CUDA_CHECK(cudaMemcpyToSymbol(g_bwd_status, &zero, sizeof(int)));
-  }
-  *status_out = v;
-  return ELSA_OK;
-}
 
 }  // namespace elsa

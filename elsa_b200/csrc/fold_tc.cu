@@ -36,19 +36,6 @@ namespace elsa {
 
 using namespace tc;
 
-static __device__ int g_fold_status = 0;
-
-// Optional per-phase timestamps of CTA (0,0,0) for tuning builds (-DELSA_TRACE); compiled out otherwise.
-#ifdef ELSA_TRACE
-__device__ long long g_fold_trace[4][256][8];
-#define ELSA_FTR(role, it, slot)                                                                              \
-  do {                                                                                                        \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_fold_trace[role][it][slot] = clock64(); \
-  } while (0)
-#else
-#define ELSA_FTR(role, it, slot) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kStages = 4;
@@ -58,12 +45,6 @@ constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MM
 constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarp = 8, kIssuerWarp = 9;
 constexpr float kRescaleThreshold = 8.0f;
-// every kPolyEvery-th pair of exponentials is evaluated on the FMA pipe; 0 = never.  Measured at 2 (half of them):
-// 6 % slower -- the ex2 unit is not what bounds this kernel.
-#ifndef ELSA_POLY_EVERY
-#define ELSA_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = ELSA_POLY_EVERY;
 
 enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6, BAR_SFREE = 7, BAR_PV = 8 };
 
@@ -72,6 +53,7 @@ struct FoldTcParams {
   int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
   int n_keys, key_offset;
   float scale_log2;
+  int* status;   // the device's status word (mapped host memory)
 };
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -176,7 +158,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tma_load_3d(sQ[1], &tmap_q, bar_q, 0, q0 + 128, bh);
         for (int j = 0; j < n_max; ++j) {
           const int st = j % kStages;
-          if (j >= kStages && !mbar_wait(bar_kv_free(st), ((j / kStages) - 1) & 1, &abort_flag, &g_fold_status, BAR_KV_FREE)) break;
+          if (j >= kStages && !mbar_wait(bar_kv_free(st), ((j / kStages) - 1) & 1, &abort_flag, prm.status, BAR_KV_FREE)) break;
           mbar_arrive_expect_tx(bar_kv_full(st), 2 * kTileBytes);
           tma_load_3d(sK(st), &tmap_k, bar_kv_full(st), 0, k_begin + j * 128, bh);
           tma_load_3d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, bh);
@@ -192,7 +174,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const uint64_t dq[2] = {make_sdesc(sQ[0], 16, 1024), make_sdesc(sQ[1], 16, 1024)};
         const uint64_t dk0 = make_sdesc(sK(0), 16, 1024), dv0 = make_sdesc(sV(0), 128 * 128, 1024);
         constexpr uint64_t kStageStep = (2 * kTileBytes) >> 4;   // descriptor address field counts 16-byte units
-        bool ok = mbar_wait(bar_q, 0, &abort_flag, &g_fold_status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, &g_fold_status, BAR_KV_FULL);
+        bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, prm.status, BAR_KV_FULL);
         if (ok) {
           tc_fence_after();
           if (n_t[0] > 0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0, idesc_s, 0u);
@@ -205,31 +187,30 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             const int j = jb + u;
             if (j >= n_max || !ok) break;
             const int un = (u + 1) % kStages;
-            ELSA_FTR(2, j, 4);
             // S(j+1) of both tiles as soon as the fold warps have pulled S(j) into registers: the next scores
             // are computed while the current exponentials run, so the fold warps never wait for the tensor pipe
             const bool s0 = j + 1 < n_t[0], s1 = j + 1 < n_t[1];
             if (s0 || s1) {
-              ok = mbar_wait(bar_kv_full(un), ((j + 1) / kStages) & 1, &abort_flag, &g_fold_status, BAR_KV_FULL) &&
-                   (!s0 || mbar_wait(bar_sfree(0), j & 1, &abort_flag, &g_fold_status, BAR_SFREE)) &&
-                   (!s1 || mbar_wait(bar_sfree(1), j & 1, &abort_flag, &g_fold_status, BAR_SFREE));
+              // bar_s is shared by both tiles and advances one phase per commit: every tile that consumes S(j)
+              // must have seen phase j (its sfree arrival says so) before phase j+1 completes, also the tile that
+              // gets no S(j+1) of its own (causal diagonal: n_t[1] == n_t[0] + 1), or its parity test would alias
+              ok = mbar_wait(bar_kv_full(un), ((j + 1) / kStages) & 1, &abort_flag, prm.status, BAR_KV_FULL) &&
+                   (j >= n_t[0] || mbar_wait(bar_sfree(0), j & 1, &abort_flag, prm.status, BAR_SFREE)) &&
+                   (j >= n_t[1] || mbar_wait(bar_sfree(1), j & 1, &abort_flag, prm.status, BAR_SFREE));
               if (!ok) break;
               tc_fence_after();
-              ELSA_FTR(2, j, 0);
               if (s0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0 + un * kStageStep, idesc_s, 0u);
               if (s1) mma_ss_x4<2, 2>(tS[1], dq[1], dk0 + un * kStageStep, idesc_s, 0u);
               mma_commit(bar_s);
-              ELSA_FTR(2, j, 1);
             }
             // O_t += P_t V, issued per 64-key half of P as soon as the fold warps have delivered it
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (j < n_t[t]) {
-                if (!(ok = mbar_wait(bar_p(t, 0), j & 1, &abort_flag, &g_fold_status, BAR_P))) break;
+                if (!(ok = mbar_wait(bar_p(t, 0), j & 1, &abort_flag, prm.status, BAR_P))) break;
                 tc_fence_after();
                 mma_ts_x4<8, 128>(tO[t], tP[t], dv0 + u * kStageStep, idesc_o, j > 0 ? 1u : 0u);
                 mma_ts_x4<8, 128>(tO[t], tP[t] + 32, dv0 + u * kStageStep + 512, idesc_o, 1u);
-                ELSA_FTR(2, j, 2 + t);
                 if (t == 0) mma_commit(bar_pv0);
               }
             }
@@ -253,8 +234,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, &g_fold_status, BAR_S))) { alive = false; break; }
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 0);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -267,7 +247,6 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar_sfree(t));      // S_t may be overwritten with the next tile's scores
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 1);
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0 + t * 128);
@@ -290,15 +269,13 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 2);
       if (j > 0) {
         // P_t V of the previous key tile must have retired before P_t is overwritten or O_t rescaled
         const uint32_t bpv = t == 0 ? bar_pv0 : bar_kv_free((j - 1) % kStages);
         const uint32_t par = t == 0 ? ((j - 1) & 1) : (((j - 1) / kStages) & 1);
-        if (!__all_sync(0xffffffffu, mbar_wait(bpv, par, &abort_flag, &g_fold_status, BAR_PV))) { alive = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bpv, par, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
         tc_fence_after();
       }
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 3);
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, move)) {
         const float m_new = fmaxf(m_ref, tmax);
@@ -327,13 +304,11 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
-          const float2 pp = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) ? exp2_fma_pair(x)
-                                                                                         : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
           ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
           pk[i] = pack2<T>(pp.x, pp.y);
         }
         tmem_st32(tP[t] + lane_off + 32 * h, pk);
-        if (h == 0 && (warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 4);
       }
       // one hand-off per key tile: with the scores produced a tile ahead, P V need not start on the first half
       tmem_wait_st();               // (also covers the O rescale stores above)
@@ -344,14 +319,13 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const float2 s = __fadd2_rn(s01, s23);
         zsum += s.x + s.y;
       }
-      if ((warp & 3) == 0 && lane == 0) ELSA_FTR(t, j, 5);
     }
 
     // epilogue: renormalise to the true max and write the summary row
     const int r_chunk = blockIdx.x * 256 + t * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     if (n_t[t] > 0) {
-      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, &g_fold_status, BAR_O))) alive = false;
+      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, prm.status, BAR_O))) alive = false;
       if (alive) {
         tc_fence_after();
         float ov[64];
@@ -395,7 +369,28 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// test hook: a bounded wait that runs out (nothing arrives at the barrier), in the form the product kernels use
+__global__ void wait_timeout_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    (void)mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 99, limit_ns);
+  }
+}
+
 }  // namespace
+
+int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st) {
+  int* status = nullptr;
+  int rc = device_status_word(&status, nullptr);
+  if (rc != ELSA_OK) return rc;
+  wait_timeout_kernel<<<1, 32, 0, st>>>(status, limit_ns);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
 
 // ---- host ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -464,6 +459,7 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   FoldTcParams prm;
   prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
   prm.scale_log2 = p.scale_log2;
@@ -481,21 +477,5 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   return ELSA_OK;
 }
 
-#ifdef ELSA_TRACE
-extern "C" int elsa_debug_fold_trace(long long* host_buf) {
-  return cudaMemcpyFromSymbol(host_buf, g_fold_trace, sizeof(long long) * 4 * 256 * 8) == cudaSuccess ? 0 : 3;
-}
-#endif
-
-int fold_tc_status(int* status_out, int clear) {
-  int v = 0;
-  ELSA_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_fold_status, sizeof(int)));
-  if (clear && v != 0) {
-    int zero = 0;
-    ELSA_CUDA_CHECK(cudaMemcpyToSymbol(g_fold_status, &zero, sizeof(int)));
-  }
-  *status_out = v;
-  return ELSA_OK;
-}
 
 }  // namespace elsa

@@ -45,16 +45,19 @@ inline int ensure_dynamic_smem(const void* func, size_t bytes) {
   return ELSA_OK;
 }
 
+// Status word of the CURRENT device for the bounded device-side waits: one int per device in mapped pinned host
+// memory, allocated on first use (api.cu).  *dev_ptr is what a kernel stores through, *host_ptr what the host reads.
+int device_status_word(int** dev_ptr, volatile int** host_ptr);
+
 // tcgen05 kernels (fold_tc.cu)
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
-int fold_tc_status(int* status_out, int clear);
+int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
 // tcgen05 backward (bwd_tc.cu); workspace = padded D / LSE vectors + fp32 dQ accumulator
 bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc_workspace_bytes(int bh, int n_ctx);
 int bwd_tc(const BwdParams& p, const void* out, const float* row_m, const float* row_z, void* workspace, int dtype,
            cudaStream_t st);
-int bwd_tc_status(int* status_out, int clear);
 
 // FP32-FMA kernels (fold_simt.cu, bwd_simt.cu)
 int fold_simt(const FoldParams& p, int dtype, cudaStream_t st);

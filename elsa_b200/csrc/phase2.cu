@@ -162,6 +162,56 @@ pair_merge_kernel(const float* __restrict__ m_in, const float* __restrict__ z_in
   if (c == 0) { m_out[wo] = M; z_out[wo] = Z; }
 }
 
+// ---- cross-GPU merge of sequence shards: the two local passes around the reduce_scatter ---------
+// pack: w = z > 0 ? 2^(m - m_all) : 0; chunk r of `packed` = rows [r*nl, (r+1)*nl) of every (batch*head):
+// s*w as [BH][nl][D] followed by z*w as [BH][nl].  One thread per float4 of s.
+__global__ void __launch_bounds__(256)
+shard_pack_kernel(const float* __restrict__ m, const float* __restrict__ z, const float* __restrict__ s,
+                  const float* __restrict__ m_all, float* __restrict__ packed, int bh, int n_ctx, int nl,
+                  int head_dim, int chunks, int64_t chunk_elems) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t rows = static_cast<int64_t>(bh) * n_ctx;
+  if (idx >= rows * chunks) return;
+  const int64_t row = idx / chunks;
+  const int c = static_cast<int>(idx - row * chunks);
+  const int64_t b = row / n_ctx;
+  const int i = static_cast<int>(row - b * n_ctx);
+  const int r = i / nl, il = i - r * nl;
+  const float zz = z[row];
+  const float w = zz > 0.f ? exp2f(m[row] - m_all[row]) : 0.f;
+  float4 v = *reinterpret_cast<const float4*>(s + row * head_dim + c * 4);
+  v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+  float* chunk = packed + static_cast<int64_t>(r) * chunk_elems;
+  *reinterpret_cast<float4*>(chunk + (b * nl + il) * head_dim + c * 4) = v;
+  if (c == 0) chunk[static_cast<int64_t>(bh) * nl * head_dim + b * nl + il] = zz * w;
+}
+
+// finalize: out = S / Z (0 where Z == 0), row_m = Z > 0 ? m_all : -inf, row_z = Z for the nl rows of chunk `rank`
+template <typename TO>
+__global__ void __launch_bounds__(256)
+shard_finalize_kernel(const float* __restrict__ chunk, const float* __restrict__ m_all, TO* __restrict__ out,
+                      float* __restrict__ row_m, float* __restrict__ row_z, int bh, int n_ctx, int nl, int rank,
+                      int head_dim, int chunks) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t rows = static_cast<int64_t>(bh) * nl;
+  if (idx >= rows * chunks) return;
+  const int64_t row = idx / chunks;           // b * nl + il
+  const int c = static_cast<int>(idx - row * chunks);
+  const float Z = chunk[rows * head_dim + row];
+  const float inv = Z > 0.f ? 1.0f / Z : 0.f;
+  float sv[4], o[4];
+  Vec4<float>::load(chunk + row * head_dim + c * 4, sv);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = Z > 0.f ? sv[i] * inv : 0.f;
+  Vec4<TO>::store(out + row * head_dim + c * 4, o);
+  if (c == 0) {
+    const int64_t b = row / nl;
+    const int il = static_cast<int>(row - b * nl);
+    row_m[row] = Z > 0.f ? m_all[b * n_ctx + static_cast<int64_t>(rank) * nl + il] : -CUDART_INF_F;
+    row_z[row] = Z;
+  }
+}
+
 // ---- dispatch ----------------------------------------------------------------------------
 static inline int pick_nv(int head_dim, int elem_bytes_a, int elem_bytes_b) {
   if (head_dim % 8 == 0 && elem_bytes_a == 2 && elem_bytes_b == 2) return 8;
@@ -320,4 +370,45 @@ extern "C" int elsa_merge_partial(const float* m_buf, const float* z_buf, const 
   // one un-normalised fp32 summary per row: the state a sequence shard contributes to the cross-GPU merge
   return merge_final_any(m_buf, z_buf, s_buf, s_out, m_out, z_out, summary_dtype, ELSA_F32, n_parts, bh, 0, q_len, q_len,
                          head_dim, 0, 1, static_cast<cudaStream_t>(stream), 0);
+}
+
+extern "C" int64_t elsa_shard_chunk_elems(int bh, int n_ctx, int head_dim, int world) {
+  if (bh < 1 || n_ctx < 1 || head_dim < 1 || world < 1 || n_ctx % world != 0) return -1;
+  return static_cast<int64_t>(bh) * (n_ctx / world) * (head_dim + 1);
+}
+
+extern "C" int elsa_shard_pack(const float* m, const float* z, const float* s, const float* m_all, float* packed, int bh,
+                               int n_ctx, int head_dim, int world, void* stream) {
+  if (!m || !z || !s || !m_all || !packed || bh < 1 || n_ctx < 1 || head_dim < 4 || head_dim > 128 || head_dim % 4 != 0 ||
+      world < 1 || n_ctx % world != 0)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(packed)) & 15u) return ELSA_ERR_INVALID_ARGUMENT;
+  const int nl = n_ctx / world, chunks = head_dim / 4;
+  const int64_t chunk_elems = static_cast<int64_t>(bh) * nl * (head_dim + 1);
+  if (world > 1 && (chunk_elems * 4) % 16 != 0) return ELSA_ERR_INVALID_ARGUMENT;   // chunk bases stay 16-byte aligned
+  const int64_t total = static_cast<int64_t>(bh) * n_ctx * chunks;
+  shard_pack_kernel<<<static_cast<unsigned>(cdiv64(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      m, z, s, m_all, packed, bh, n_ctx, nl, head_dim, chunks, chunk_elems);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+extern "C" int elsa_shard_finalize(const float* chunk, const float* m_all, void* out, float* row_m, float* row_z,
+                                   int out_dtype, int bh, int n_ctx, int head_dim, int world, int rank, void* stream) {
+  if (!chunk || !m_all || !out || !row_m || !row_z || !dtype_ok(out_dtype) || bh < 1 || n_ctx < 1 || head_dim < 4 ||
+      head_dim > 128 || head_dim % 4 != 0 || world < 1 || n_ctx % world != 0 || rank < 0 || rank >= world)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(chunk) | reinterpret_cast<uintptr_t>(out)) & 15u) return ELSA_ERR_INVALID_ARGUMENT;
+  const int nl = n_ctx / world, chunks = head_dim / 4;
+  const int64_t total = static_cast<int64_t>(bh) * nl * chunks;
+  const unsigned blocks = static_cast<unsigned>(cdiv64(total, 256));
+  auto st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == ELSA_F32)
+    shard_finalize_kernel<float><<<blocks, 256, 0, st>>>(chunk, m_all, static_cast<float*>(out), row_m, row_z, bh, n_ctx, nl, rank, head_dim, chunks);
+  else if (out_dtype == ELSA_F16)
+    shard_finalize_kernel<__half><<<blocks, 256, 0, st>>>(chunk, m_all, static_cast<__half*>(out), row_m, row_z, bh, n_ctx, nl, rank, head_dim, chunks);
+  else
+    shard_finalize_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(chunk, m_all, static_cast<__nv_bfloat16*>(out), row_m, row_z, bh, n_ctx, nl, rank, head_dim, chunks);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
 }

@@ -15,7 +15,7 @@ namespace tc {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-// device status word (one per translation unit, passed to the waits by pointer):
+// device status word (one per device, in mapped pinned host memory, passed to the waits by pointer):
 // 0 = ok, otherwise (1 << 8) | id of the barrier whose wait gave up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -48,18 +48,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// bounded wait; `abort_flag` lives in shared memory and is raised by whoever times out first
+// bounded wait; `abort_flag` lives in shared memory and is raised by whoever times out first.  `status` points at
+// the device's status word, which lives in mapped pinned HOST memory (the host reads it without a copy or a
+// synchronisation): a plain store followed by a system-scope fence, no atomics across the host link.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int bar_id) {
+                                          int bar_id, unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
-        atomicCAS(status, 0, (1 << 8) | bar_id);
+        if (status) {
+          *reinterpret_cast<volatile int*>(status) = (1 << 8) | bar_id;
+          __threadfence_system();
+        }
         return false;
       }
     }
@@ -190,23 +195,6 @@ __device__ __forceinline__ void mma_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint
         "n"(3 * A_STEP), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
       : "memory");
 }
-// 2^x for a packed pair on the FMA pipe instead of the ex2 unit (16 results / clk / SM): round-to-nearest split
-// x = n + f with the 1.5 * 2^23 trick, degree-4 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error
-// 2.7e-6, far below the 16-bit rounding of P), then n is added into the exponent field.  x is clamped at -126.
-__device__ __forceinline__ float2 exp2_fma_pair(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.009570101276040077f, 0.009570101276040077f), make_float2(0.05591785907745361f, 0.05591785907745361f));
-  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
-  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
-  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
-  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
-}
-
 // the mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is complete
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -13,8 +13,12 @@ The reference is single-GPU; these are the two ways its path shards:
       w = 2^(m - M) (0 where z == 0)     -> local
       Z, S = sum over ranks of z*w, s*w  -> all_reduce(SUM) of one concatenated [z | s] buffer
       out = S / Z
-  `merge_summaries_across_ranks` is that exchange on plain tensors (it runs on CPU ranks with gloo
-  as well); `sequence_parallel_attention` is the GPU forward built on it.
+  `merge_summaries_across_ranks` is that exchange on plain host or device tensors (the form the CPU
+  ranks of the gloo tests run).  On GPUs `merge_shards_on_gpu` does the same with two kernels of the library
+  around the collectives and a reduce_scatter instead of the all_reduce, so that every rank finalises only
+  N / world rows: all_reduce(MAX) of m (4 B per row), elsa_shard_pack (w, z*w, s*w written chunk-per-rank),
+  reduce_scatter(SUM), elsa_shard_finalize (S / Z, row state), then an all_gather of the finished rows where
+  the caller wants them everywhere.  `sequence_parallel_attention` is the GPU forward built on it.
 """
 from __future__ import annotations
 
@@ -61,7 +65,8 @@ def local_shard_summary(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.T
     """Phase 1 + local merge of ONE sequence shard on this GPU.
 
     q: [B, H, N, D] (all query rows); k_shard, v_shard: [B, H, Nk, D] (rows key_offset .. key_offset+Nk-1 of
-    the sequence).  Returns fp32 (m, z, s) with one un-normalised summary per query row: [B*H, N], [B*H, N, D]."""
+    the sequence).  Returns fp32 (m, z, s) with one un-normalised summary per query row: [B*H, N], [B*H, N, D].
+    The partition summaries are kept in fp32 whatever the input dtype: they are summed across GPUs next."""
     lib = _lib.load()
     if q.dim() != 4 or k_shard.dim() != 4 or k_shard.shape != v_shard.shape:
         raise ValueError("q must be [B,H,N,D] and k_shard, v_shard [B,H,Nk,D]")
@@ -74,25 +79,84 @@ def local_shard_summary(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.T
     q_c, k_c, v_c = _aligned(q), _aligned(k_shard), _aligned(v_shard)
     dt = _lib.dtype_code(q.dtype)
     pw = max(128, (int(part_width) + 127) // 128 * 128)
-    parts = -(-nk // pw)
+    parts = max(1, -(-nk // pw))
     bh = b * h
     dev = q.device
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
-        m_p = torch.empty((parts, bh, n), device=dev, dtype=torch.float32)
-        z_p = torch.empty_like(m_p)
-        s_p = torch.empty((parts, bh, n, d), device=dev, dtype=torch.float32)
+        m = torch.empty((bh, n), device=dev, dtype=torch.float32)
+        z = torch.empty_like(m)
+        s = torch.empty((bh, n, d), device=dev, dtype=torch.float32)
+        if nk == 0:                      # an empty shard contributes the identity
+            m.fill_(float("-inf")); z.zero_(); s.zero_()
+            return m, z, s
+        if parts == 1:                   # one partition: its summary IS the shard's summary
+            m_p, z_p, s_p = m, z, s
+        else:
+            m_p = torch.empty((parts, bh, n), device=dev, dtype=torch.float32)
+            z_p = torch.empty_like(m_p)
+            s_p = torch.empty((parts, bh, n, d), device=dev, dtype=torch.float32)
         rc = lib.elsa_phase1_fold_shard(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), m_p.data_ptr(), z_p.data_ptr(),
                                         s_p.data_ptr(), dt, _lib.ELSA_F32, b, h, n, d, nk, int(key_offset), pw, parts,
                                         int(bool(is_causal)), 0, stream)
         _lib.check(rc, "elsa_phase1_fold_shard")
-        m = torch.empty((bh, n), device=dev, dtype=torch.float32)
-        z = torch.empty_like(m)
-        s = torch.empty((bh, n, d), device=dev, dtype=torch.float32)
-        rc = lib.elsa_merge_partial(m_p.data_ptr(), z_p.data_ptr(), s_p.data_ptr(), s.data_ptr(), m.data_ptr(),
-                                    z.data_ptr(), _lib.ELSA_F32, parts, bh, n, d, stream)
-        _lib.check(rc, "elsa_merge_partial")
+        if parts > 1:
+            rc = lib.elsa_merge_partial(m_p.data_ptr(), z_p.data_ptr(), s_p.data_ptr(), s.data_ptr(), m.data_ptr(),
+                                        z.data_ptr(), _lib.ELSA_F32, parts, bh, n, d, stream)
+            _lib.check(rc, "elsa_merge_partial")
     return m, z, s
+
+
+def merge_shards_on_gpu(m: torch.Tensor, z: torch.Tensor, s: torch.Tensor, out_dtype: torch.dtype, *, group=None,
+                        gather: bool = True):
+    """Cross-GPU merge of one fp32 (m, z, s) summary per row per rank, with the library's kernels around NCCL.
+
+    m, z: [BH, N]; s: [BH, N, D]; CUDA fp32.  Returns (out, row_m, row_z): with gather, the finished rows of all
+    ranks ([BH, N, D] in out_dtype, [BH, N] fp32) on every rank; without, only this rank's rows
+    [rank*N/world, (rank+1)*N/world) as ([BH, N/world, D], [BH, N/world], [BH, N/world]).
+    When N does not divide by the world size every rank sums and finalises all rows (all_reduce form)."""
+    lib = _lib.load()
+    bh, n, d = map(int, s.shape)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    scatter = world > 1 and n % world == 0 and (bh * (n // world) * (d + 1)) % 4 == 0
+    w_eff, r_eff = (world, rank) if scatter else (1, 0)
+    dev = s.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        m_all = m
+        if world > 1:
+            m_all = m.clone()
+            dist.all_reduce(m_all, op=dist.ReduceOp.MAX, group=group)
+        chunk = int(lib.elsa_shard_chunk_elems(bh, n, d, w_eff))
+        packed = torch.empty((w_eff * chunk,), device=dev, dtype=torch.float32)
+        _lib.check(lib.elsa_shard_pack(m.data_ptr(), z.data_ptr(), s.data_ptr(), m_all.data_ptr(), packed.data_ptr(),
+                                       bh, n, d, w_eff, stream), "elsa_shard_pack")
+        if scatter:
+            mine = torch.empty((chunk,), device=dev, dtype=torch.float32)
+            dist.reduce_scatter_tensor(mine, packed, op=dist.ReduceOp.SUM, group=group)
+        else:
+            mine = packed
+            if world > 1:
+                dist.all_reduce(mine, op=dist.ReduceOp.SUM, group=group)
+        nl = n // w_eff
+        out = torch.empty((bh, nl, d), device=dev, dtype=out_dtype)
+        row_m = torch.empty((bh, nl), device=dev, dtype=torch.float32)
+        row_z = torch.empty_like(row_m)
+        _lib.check(lib.elsa_shard_finalize(mine.data_ptr(), m_all.data_ptr(), out.data_ptr(), row_m.data_ptr(),
+                                           row_z.data_ptr(), _lib.dtype_code(out_dtype), bh, n, d, w_eff, r_eff, stream),
+                   "elsa_shard_finalize")
+        if not scatter or not gather:
+            return out, row_m, row_z
+        # the finished rows of every rank: [world, BH, N/world, ...] -> [BH, N, ...]
+        g_out = torch.empty((world, bh, nl, d), device=dev, dtype=out_dtype)
+        dist.all_gather_into_tensor(g_out, out, group=group)
+        state = torch.stack((row_m, row_z))                              # one collective for both vectors
+        g_state = torch.empty((world, 2, bh, nl), device=dev, dtype=torch.float32)
+        dist.all_gather_into_tensor(g_state, state, group=group)
+        out = g_out.permute(1, 0, 2, 3).reshape(bh, n, d)
+        g_state = g_state.permute(1, 2, 0, 3).reshape(2, bh, n)
+        return out, g_state[0].contiguous(), g_state[1].contiguous()
 
 
 def sequence_parallel_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, *, key_offset: int,
@@ -105,8 +169,8 @@ def sequence_parallel_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard:
     _check_qkv(q, q, q, "sequence_parallel_attention")
     b, h, n, d = map(int, q.shape)
     m, z, s = local_shard_summary(q, k_shard, v_shard, key_offset=key_offset, is_causal=is_causal, part_width=part_width)
-    out, row_m, row_z = merge_summaries_across_ranks(m, z, s, group=group)
-    out = out.to(q.dtype).reshape(b, h, n, d)
+    out, row_m, row_z = merge_shards_on_gpu(m, z, s, q.dtype, group=group, gather=True)
+    out = out.reshape(b, h, n, d)
     if return_state:
         return out, row_m, row_z
     return out

@@ -5,7 +5,9 @@
  * (a cudaStream_t passed as void*; NULL = the legacy default stream), launches on that
  * stream and returns immediately with 0 or one of the ELSA_ERR_* codes.  Nothing here
  * allocates or frees device memory, synchronises the device or throws: buffers belong to
- * the caller and are borrowed for the duration of the stream-ordered launch.
+ * the caller and are borrowed for the duration of the stream-ordered launch.  (Exceptions, both stated at
+ * their declarations: elsa_twopass_forward_static keeps its scratch inside the library image, and the first
+ * call of the process that needs the device status word makes one small pinned-host allocation.)
  *
  * The citations name the interface of the reference project (ming053l/ELSA, paths relative
  * to its root) that each entry point replaces.
@@ -39,7 +41,7 @@ enum elsa_status {
   ELSA_ERR_UNSUPPORTED = 2,      /* valid request that no kernel in this build covers */
   ELSA_ERR_CUDA = 3,             /* a CUDA runtime/driver call failed; see elsa_last_cuda_error */
   ELSA_ERR_WORKSPACE = 4,        /* workspace pointer missing, misaligned or too small */
-  ELSA_ERR_DEVICE_TIMEOUT = 5    /* a bounded device-side wait gave up (status word set) */
+  ELSA_ERR_DEVICE_TIMEOUT = 5    /* a bounded device-side wait gave up earlier (elsa_device_status is non-zero) */
 };
 
 /* flags for the forward / backward entry points */
@@ -51,10 +53,23 @@ int elsa_abi_version(void);
 const char* elsa_strerror(int status);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread */
 int elsa_last_cuda_error(void);
-/* Status word written by bounded device-side waits of the tensor-core kernels: 0 = no wait ever
- * gave up; otherwise (1 << 8) | id of the barrier.  Synchronous (copies one int from the device);
- * clear != 0 resets it.  Returns -1 when the copy itself fails. */
+/* Status word of the CURRENT device, written by the bounded device-side waits of the tensor-core kernels:
+ * 0 = no wait gave up; otherwise (1 << 8) | id of the barrier.  The word lives in mapped pinned host memory
+ * (one small host allocation, made by the first call of the process that needs it: make that call outside any
+ * stream capture), so this read costs nothing and synchronises nothing; it describes the kernels that have
+ * finished so far -- synchronise the stream first for a definite answer.  While the word is non-zero every entry
+ * point that would launch a tensor-core kernel returns ELSA_ERR_DEVICE_TIMEOUT instead (the results of the
+ * call whose wait gave up are undefined); clear != 0 resets it.  Returns -1 when the word cannot be set up. */
 int elsa_device_status(int clear);
+/* Test hook for the status path: one CTA waits on an mbarrier that nothing ever arrives at, gives up after
+ * limit_ns nanoseconds, records (1 << 8) | 99 in the status word and returns normally.  It faults nothing and
+ * leaves the context usable.  No counterpart in the reference. */
+int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream);
+/* Measurement helper for benchmarks (no counterpart in the reference, on no product path): `blocks` CTAs of 256
+ * threads each run `iters` rounds of 16 independent register-resident FP32 FMAs (scalar, or packed f32x2 when
+ * packed != 0); the work is blocks * 256 * iters * 32 FLOP.  Timed by the caller with events, it gives the
+ * FP32-FMA rate that bounds the fp32 kernels.  sink: one float of device memory. */
+int elsa_debug_fma_rate(float* sink, int blocks, int64_t iters, int packed, void* stream);
 /* number of kernels this library has launched in this process so far (all threads, all streams) */
 int64_t elsa_kernel_launches(void);
 /* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run */
@@ -96,6 +111,23 @@ int elsa_phase1_fold_shard(const void* q, const void* k, const void* v,
 int elsa_merge_partial(const float* m_buf, const float* z_buf, const void* s_buf,
                        float* s_out, float* m_out, float* z_out,
                        int summary_dtype, int n_parts, int bh, int q_len, int head_dim, void* stream);
+
+/* Cross-GPU merge of sequence shards, the two local passes around the collective.  The reference is
+ * single-GPU and has no counterpart; the arithmetic is that of its phase-2 reduce (weights 2^(m - M), weighted
+ * sums of z and s, out = S / Z: cuda/paper_scan_d64_kernel.cu:54-95) with the partitions living on different GPUs.
+ * Sequence: all_reduce(MAX) of m -> m_all; elsa_shard_pack; reduce_scatter(SUM) of `packed` (world equal chunks);
+ * elsa_shard_finalize on the chunk this rank received.  n_ctx must divide by world; head_dim by 4.
+ *   pack      m, z [B*H, N], s [B*H, N, D] fp32: this shard's merged un-normalised summary (elsa_merge_partial).
+ *             packed: world chunks of elsa_shard_chunk_elems floats; chunk r covers rows [r*N/world, (r+1)*N/world)
+ *             of every (batch*head): s*w as [B*H, N/world, D], then z*w as [B*H, N/world]; w = z > 0 ? 2^(m - m_all) : 0.
+ *   finalize  chunk: the summed chunk `rank`; out [B*H, N/world, D] in out_dtype = S / Z (0 where Z == 0);
+ *             row_m = Z > 0 ? m_all : -inf, row_z = Z, both [B*H, N/world].
+ * world = 1 is the all_reduce form: one chunk with all rows, summed on every rank. */
+int64_t elsa_shard_chunk_elems(int bh, int n_ctx, int head_dim, int world);
+int elsa_shard_pack(const float* m, const float* z, const float* s, const float* m_all, float* packed,
+                    int bh, int n_ctx, int head_dim, int world, void* stream);
+int elsa_shard_finalize(const float* chunk, const float* m_all, void* out, float* row_m, float* row_z,
+                        int out_dtype, int bh, int n_ctx, int head_dim, int world, int rank, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Phase 2, one pass: merge all partition summaries of each row, out = s / z, optional state.
@@ -168,7 +200,9 @@ int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_
  * path must not allocate: the partition summaries go to a 64 MiB array that is part of the library image
  * (elsa_static_scratch_bytes) instead of a caller workspace.  No bias, library-chosen partitions, summaries
  * in the input dtype; out / row_m / row_z as in elsa_twopass_forward (row_m, row_z may both be NULL).
- *   - A problem whose summaries need more than the array returns ELSA_ERR_WORKSPACE and launches nothing.
+ *   - Query rows are processed in chunks whose summaries fit the array; only a problem for which not even one
+ *     query tile (256 rows on the tensor-core path, 64 otherwise) of summaries fits returns ELSA_ERR_WORKSPACE,
+ *     and then nothing is launched.
  *   - The array stays resident on every GPU that loads the library, until the process exits.
  *   - All calls on a device share the array: two calls that overlap on the GPU (different streams, or
  *     different host threads) race on it.  Calls on one stream are safe back to back; nothing in the array

@@ -5,7 +5,8 @@ device allocator of its own, or a server whose device memory is handed out once 
 library keeps the partition summaries in a built-in 64 MiB device array.  This test calls that entry point
 through the C ABI exactly as such a host would (raw pointers, no workspace), twice in a row with different
 inputs because the array is shared between calls, and requires the same bits as the regular entry point,
-which takes a caller-allocated workspace.  It also checks that an oversized problem is refused.
+which takes a caller-allocated workspace.  It also checks a problem that needs several query chunks and that an
+oversized problem is refused.
 
 The file name makes pytest collect it last, so a run that stops at the first failure has already run every
 other test.
@@ -49,12 +50,25 @@ def test_static_scratch_forward_matches_workspace_forward(dtype, n, causal):
     assert lib.elsa_device_status(0) == 0
 
 
+def test_static_scratch_chunks_the_queries_when_the_summaries_exceed_the_array():
+    """fp16, 32 heads, 16384 tokens: the summaries of all query rows (68 MiB) exceed the 64 MiB array, so the entry
+    point walks the query axis in chunks through the same array; same bits as the workspace forward."""
+    lib = _lib.load()
+    b, h, n, d = 1, 32, 16384, 64
+    assert lib.elsa_forward_workspace_bytes(1, 1, b, h, n, d, 0, 0, 0, 0, 0) > lib.elsa_static_scratch_bytes()
+    q, k, v = (U.seeded((b, h, n, d), torch.float16, 330 + i).cuda() for i in range(3))
+    ref = _forward_impl(q, k, v, bias=None, is_causal=False, summary_dtype=torch.float16, part_width=0, q_chunk=0,
+                        want_state=True)
+    rc, out, rm, rz = _static_forward(lib, q, k, v, False)
+    assert rc == 0, lib.elsa_strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref[0]) and torch.equal(rm, ref[1]) and torch.equal(rz, ref[2])
+
+
 def test_static_scratch_rejects_oversized_problem():
     lib = _lib.load()
-    # summaries of this problem need far more than 64 MiB per query chunk: refused before anything is launched
-    b, h, n, d = 64, 16, 4096, 64
-    need = lib.elsa_forward_workspace_bytes(1, 1, b, h, n, d, 0, 0, 0, 0, 0)
-    assert need > lib.elsa_static_scratch_bytes()
+    # 4096 (batch*head) rows: the summaries of even one 256-row query tile exceed 64 MiB: refused before any launch
+    b, h, n, d = 256, 16, 4096, 64
     before = lib.elsa_kernel_launches()
     x = torch.zeros(16, device="cuda", dtype=torch.float16)   # never dereferenced: the size check comes first
     rc = lib.elsa_twopass_forward_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None, None, 1, b, h, n,
