@@ -263,7 +263,7 @@ def measure_fma_peak(lib, dev):
 def measure_phase2(lib, dev, hbm_gbs):
     """Achieved HBM GB/s of the streaming passes (phase-2 merge / scan, backward pre- and post-pass) through the C ABI,
     at the headline plan (fp16, 2 partitions, 131072 rows; buffers rotated so that nothing is L2-resident) and at the
-    long fp32 case's 32 partitions (one 1 GiB query chunk of summaries)."""
+    long fp32 case's 32 partitions (one query chunk of its plan: 15872 rows x 8 heads x 32 partitions, 1.07 GB of summaries)."""
     from elsa_b200 import _lib
     stream = torch.cuda.current_stream().cuda_stream
     out = {}
@@ -276,7 +276,7 @@ def measure_phase2(lib, dev, hbm_gbs):
         out[tag] = {"ms": ms, "bytes": nbytes, "gbs": gbs, "frac": gbs / hbm_gbs}
 
     for tag, dtype, parts, bh, rows_q, nset in (("headline_plan_f16_P2", torch.float16, 2, 8, 16384, 6),
-                                                 ("long_fp32_P32_chunk", torch.float32, 32, 8, 1024, 1)):
+                                                 ("long_fp32_P32_chunk", torch.float32, 32, 8, 15872, 1)):
         d = 64
         es = torch.empty((), dtype=dtype).element_size()
         sdt = _lib.dtype_code(dtype)
@@ -426,6 +426,60 @@ def measure_seq_sharded(dev, rank, world, dist, steps=2):
            "all_reduce(MAX) m 2 MB; reduce_scatter(SUM) [s|z] 136 MB fp32 per rank; all_gather out + state; reduce_scatter(SUM) dQ 134 MB fp32 per rank"}
     if marks:
         res["split_rank0_ms"] = marks
+    return res
+
+
+def measure_models(dev, rank, world, dist, steps=5):
+    """Whole-model training steps through the drop-in hooks, data-parallel over the ranks: ViT-Tiny at 1024 x 1024
+    (4097 tokens per image) and Swin-T at 224 x 224, batch 8 per GPU, fp16 weights and activations, random pixels and
+    labels; a step = forward + cross-entropy + backward + the bucketed all-reduce of the parameter gradients (overlapped
+    with the backward).  With one rank the same, unpatched model (PyTorch SDPA / plain window attention) is timed too."""
+    import copy
+    import torch.nn.functional as F
+    import elsa_b200 as E
+    from elsa_b200 import vision
+    res = {}
+    for name, build, img in (("vit_tiny_1024", lambda: vision.vit_tiny(1024), 1024), ("swin_tiny_224", lambda: vision.swin_tiny(224), 224)):
+        try:
+            torch.manual_seed(17)
+            base = build().to(dev, torch.float16)
+            ours = copy.deepcopy(base)
+            rep = E.patch_timm_attention_train(ours)
+            g = torch.Generator().manual_seed(99 + rank)
+            x = torch.randn(8, 3, img, img, generator=g).to(dev, torch.float16)
+            y = torch.randint(0, 1000, (8,), generator=g).to(dev)
+            sync = vision.BucketedGradientAllReduce(ours)
+
+            def train(model, exchange):
+                def one(i):
+                    model.zero_grad(set_to_none=True)
+                    F.cross_entropy(model(x).float(), y).backward()
+                    if exchange:
+                        sync.finish()
+                return one
+
+            entry = {"batch_per_gpu": 8, "n_gpus": world, "attention_modules_patched": rep.total,
+                     "grad_exchange": "none (one rank)" if world == 1 else f"{len(sync.buckets)} buckets, async all_reduce(SUM) per bucket, overlapped with backward"}
+            for tag, model, exch in (("elsa_b200", ours, True),) + ((("unpatched", base, False),) if world == 1 else ()):
+                f = train(model, exch)
+                for i in range(2):
+                    f(i)
+                torch.cuda.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                ms = timed(f, steps)
+                if dist is not None:
+                    t = torch.tensor([ms], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    ms = float(t.item())
+                entry[tag] = {"ms_per_step": ms, "images_per_s": world * 8 / (ms * 1e-3)}
+            if "unpatched" in entry:
+                entry["lat_ratio_vs_unpatched"] = entry["elsa_b200"]["ms_per_step"] / entry["unpatched"]["ms_per_step"]
+            sync.remove()
+            res[name] = entry
+            del base, ours, x
+        except Exception as exc:  # noqa: BLE001
+            res[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     return res
 
 
@@ -625,6 +679,10 @@ def main():
         except Exception as exc:  # noqa: BLE001
             seq = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         extras["seq_sharded"] = seq
+        try:
+            extras["models"] = measure_models(dev, rank, world, dist)
+        except Exception as exc:  # noqa: BLE001
+            extras["models"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         if rank == 0 and world == 1:
             try:
                 extras["fp32_fma_peak"] = measure_fma_peak(lib, dev)

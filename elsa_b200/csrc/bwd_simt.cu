@@ -196,7 +196,17 @@ bwd_preprocess_kernel(const T* __restrict__ out, const T* __restrict__ dout, con
   if (row < rows) {
     const T* o = out + row * D;
     const T* g = dout + row * D;
-    if (vec_ok) {
+    if (vec_ok == 2) {          // 16-bit elements, D % 8 == 0: 16-byte loads
+      if constexpr (sizeof(T) == 2) {
+        for (int c = lane * 8; c < D; c += 64) {
+          const uint4 ov = *reinterpret_cast<const uint4*>(o + c), gv = *reinterpret_cast<const uint4*>(g + c);
+          const T* oe = reinterpret_cast<const T*>(&ov);
+          const T* ge = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) part += to_f32<T>(oe[i]) * to_f32<T>(ge[i]);
+        }
+      }
+    } else if (vec_ok) {
       for (int c = lane * 4; c < D; c += 32) {
         float a[4], b[4];
         Vec4<T>::load(o + c, a);
@@ -229,7 +239,8 @@ extern "C" int elsa_bwd_preprocess(const void* out, const void* dout, const floa
   if (n_ctx == 0) return ELSA_OK;
   const int64_t rows = static_cast<int64_t>(bh) * n_ctx;
   const unsigned blocks = static_cast<unsigned>(cdiv64(rows * 8, 256));
-  const int vec_ok = head_dim % 4 == 0;
+  const bool al16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
+  const int vec_ok = (dtype != ELSA_F32 && head_dim % 8 == 0 && al16) ? 2 : (head_dim % 4 == 0 ? 1 : 0);
   auto st = static_cast<cudaStream_t>(stream);
   if (dtype == ELSA_F32)
     bwd_preprocess_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(dout),

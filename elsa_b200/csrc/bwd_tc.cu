@@ -465,13 +465,14 @@ __global__ void __launch_bounds__(256)
 bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
                           const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
                           int bh, int n_ctx, int n_pad) {
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t prow = gid >> 3;                  // padded row index
+  // blockIdx.y = (batch*head); x covers the n_pad padded rows, 8 lanes (16 bytes each) per row: no division
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = static_cast<int>(gid >> 3);        // padded row within this (batch*head)
   const int lane = static_cast<int>(gid & 7);
-  const int64_t total = static_cast<int64_t>(bh) * n_pad;
-  const int64_t b = prow / n_pad;
-  const int r = static_cast<int>(prow - b * n_pad);
-  const bool real = prow < total && r < n_ctx;
+  const int64_t b = blockIdx.y;
+  const int64_t prow = b * n_pad + r;
+  const bool in_pad = r < n_pad;
+  const bool real = in_pad && r < n_ctx;
   float part = 0.f;
   if (real) {
     const T* o = out + (b * n_ctx + r) * 64 + lane * 8;
@@ -485,7 +486,7 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   part += __shfl_xor_sync(0xffffffffu, part, 4);
   part += __shfl_xor_sync(0xffffffffu, part, 2);
   part += __shfl_xor_sync(0xffffffffu, part, 1);
-  if (prow < total && lane == 0) {
+  if (in_pad && lane == 0) {
     if (real) {
       nd_pad[prow] = -part;
       nlse_pad[prow] = -(row_m[b * n_ctx + r] + log2f(fmaxf(row_z[b * n_ctx + r], 1.0e-30f)));
@@ -542,8 +543,8 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   const int64_t acc_elems = static_cast<int64_t>(bh) * N * 64;
 
   {
-    const int64_t threads = static_cast<int64_t>(bh) * n_pad * 8;
-    bwd_preprocess_pad_kernel<T><<<static_cast<unsigned>(cdiv64(threads, 256)), 256, 0, st>>>(
+    const dim3 pgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_pad) * 8, 256)), static_cast<unsigned>(bh));
+    bwd_preprocess_pad_kernel<T><<<pgrid, 256, 0, st>>>(
         static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, bh, N, n_pad);
     ELSA_LAUNCH_CHECK();
   }

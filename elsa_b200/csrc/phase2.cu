@@ -57,17 +57,36 @@ __device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&o)[NV
   }
 }
 
+// Thread -> (row, 16-byte chunk of the row).  blockIdx.y is the (batch*head) index and the x dimension covers
+// q_len * chunks work items, so the only division left is a 32-bit one by `chunks` (a shift for power-of-two
+// head dims): 64-bit divisions per thread cost more than the memory traffic of these passes.
+struct RowChunk { int64_t row; int r; int c; bool ok; };
+__device__ __forceinline__ RowChunk row_chunk(int q_len, int chunks, int chunk_shift) {
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+  RowChunk rc;
+  const uint32_t r = chunk_shift >= 0 ? (idx >> chunk_shift) : (idx / static_cast<uint32_t>(chunks));
+  rc.r = static_cast<int>(r);
+  rc.c = static_cast<int>(idx - r * static_cast<uint32_t>(chunks));
+  rc.ok = r < static_cast<uint32_t>(q_len);
+  rc.row = static_cast<int64_t>(blockIdx.y) * q_len + r;
+  return rc;
+}
+static inline int chunk_shift_of(int chunks) {
+  for (int sft = 0; sft < 16; ++sft) if ((1 << sft) == chunks) return sft;
+  return -1;
+}
+
 // ---- merge_final -----------------------------------------------------------------------
 template <typename TS, typename TO, int NV>
 __global__ void __launch_bounds__(256)
 merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, const TS* __restrict__ s,
                    TO* __restrict__ out, float* __restrict__ row_m, float* __restrict__ row_z,
                    int n_parts, int64_t rows, int q_len, int q_start, int n_ctx, int head_dim,
-                   int chunks, int first_part, int store_state, int normalize) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= rows * chunks) return;
-  const int64_t row = idx / chunks;
-  const int c = static_cast<int>(idx - row * chunks);
+                   int chunks, int chunk_shift, int first_part, int store_state, int normalize) {
+  const RowChunk rc = row_chunk(q_len, chunks, chunk_shift);
+  if (!rc.ok) return;
+  const int64_t row = rc.row;
+  const int c = rc.c;
   float M = -CUDART_INF_F, Z = 0.f, acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) acc[i] = 0.f;
@@ -80,9 +99,7 @@ merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, con
     load_vec<TS, NV>(sp + static_cast<int64_t>(p) * rows * head_dim, sv);
     monoid_merge<NV>(M, Z, acc, mp[static_cast<int64_t>(p) * rows], zp[static_cast<int64_t>(p) * rows], sv);
   }
-  const int64_t bh_idx = row / q_len;
-  const int r = static_cast<int>(row - bh_idx * q_len);
-  const int64_t orow = bh_idx * n_ctx + q_start + r;
+  const int64_t orow = static_cast<int64_t>(blockIdx.y) * n_ctx + q_start + rc.r;
   const float inv = normalize ? (Z > 0.f ? 1.0f / Z : 0.f) : 1.0f;   // normalize == 0: emit the merged, un-normalised s
   float o[NV];
 #pragma unroll
@@ -98,11 +115,11 @@ merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, con
 template <typename TS, int NV>
 __global__ void __launch_bounds__(256)
 prefix_scan_kernel(const float* m_in, const float* z_in, const TS* s_in, float* m_out, float* z_out, TS* s_out,
-                   int n_parts, int64_t rows, int head_dim, int chunks) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= rows * chunks) return;
-  const int64_t row = idx / chunks;
-  const int c = static_cast<int>(idx - row * chunks);
+                   int n_parts, int64_t rows, int q_len, int head_dim, int chunks, int chunk_shift) {
+  const RowChunk rc = row_chunk(q_len, chunks, chunk_shift);
+  if (!rc.ok) return;
+  const int64_t row = rc.row;
+  const int c = rc.c;
   float M = -CUDART_INF_F, Z = 0.f, acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) acc[i] = 0.f;
@@ -128,12 +145,12 @@ template <typename TS, int NV, bool UPSWEEP>
 __global__ void __launch_bounds__(256)
 pair_merge_kernel(const float* __restrict__ m_in, const float* __restrict__ z_in, const TS* __restrict__ s_in,
                   float* __restrict__ m_out, float* __restrict__ z_out, TS* __restrict__ s_out,
-                  int n_in, int step, int64_t rows, int head_dim, int chunks) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= rows * chunks) return;
-  const int po = blockIdx.y;
-  const int64_t row = idx / chunks;
-  const int c = static_cast<int>(idx - row * chunks);
+                  int n_in, int step, int64_t rows, int q_len, int head_dim, int chunks, int chunk_shift) {
+  const RowChunk rc = row_chunk(q_len, chunks, chunk_shift);
+  if (!rc.ok) return;
+  const int po = blockIdx.z;
+  const int64_t row = rc.row;
+  const int c = rc.c;
   int pa, pb;
   if (UPSWEEP) { pa = 2 * po; pb = 2 * po + 1; } else { pa = po - step; pb = po; }
   float M = -CUDART_INF_F, Z = 0.f, acc[NV];
@@ -226,12 +243,12 @@ static int launch_merge_final(const float* m, const float* z, const void* s, voi
   const int64_t rows = static_cast<int64_t>(bh) * q_len;
   const int nv = pick_nv(head_dim, sizeof(TS), sizeof(TO));
   const int chunks = head_dim / nv;
-  const int64_t total = rows * chunks;
-  const unsigned blocks = static_cast<unsigned>(cdiv64(total, 256));
+  const dim3 blocks(static_cast<unsigned>(cdiv64(static_cast<int64_t>(q_len) * chunks, 256)), static_cast<unsigned>(bh));
+  const int cs = chunk_shift_of(chunks);
   auto ts = static_cast<const TS*>(s);
   auto to = static_cast<TO*>(out);
 #define ELSA_MF(NV) merge_final_kernel<TS, TO, NV><<<blocks, 256, 0, st>>>(m, z, ts, to, row_m, row_z, n_parts, rows, \
-                                                   q_len, q_start, n_ctx, head_dim, chunks, first_part, store_state, normalize)
+                                                   q_len, q_start, n_ctx, head_dim, chunks, cs, first_part, store_state, normalize)
   if (nv == 8) ELSA_MF(8); else if (nv == 4) ELSA_MF(4); else ELSA_MF(1);
 #undef ELSA_MF
   ELSA_LAUNCH_CHECK();
@@ -270,11 +287,13 @@ static int launch_pair(const float* m_in, const float* z_in, const void* s_in, f
   const int64_t rows = static_cast<int64_t>(bh) * q_len;
   const int nv = pick_nv(head_dim, sizeof(TS), sizeof(TS));
   const int chunks = head_dim / nv;
-  dim3 grid(static_cast<unsigned>(cdiv64(rows * chunks, 256)), static_cast<unsigned>(n_out));
+  dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(q_len) * chunks, 256)), static_cast<unsigned>(bh),
+            static_cast<unsigned>(n_out));
+  const int cs = chunk_shift_of(chunks);
   auto si = static_cast<const TS*>(s_in);
   auto so = static_cast<TS*>(s_out);
 #define ELSA_PM(NV, UP) pair_merge_kernel<TS, NV, UP><<<grid, 256, 0, st>>>(m_in, z_in, si, m_out, z_out, so, n_in, step, \
-                                                                          rows, head_dim, chunks)
+                                                                          rows, q_len, head_dim, chunks, cs)
   if (upsweep) { if (nv == 8) ELSA_PM(8, true); else if (nv == 4) ELSA_PM(4, true); else ELSA_PM(1, true); }
   else         { if (nv == 8) ELSA_PM(8, false); else if (nv == 4) ELSA_PM(4, false); else ELSA_PM(1, false); }
 #undef ELSA_PM
@@ -288,11 +307,12 @@ static int launch_prefix(const float* m_in, const float* z_in, const void* s_in,
   const int64_t rows = static_cast<int64_t>(bh) * q_len;
   const int nv = pick_nv(head_dim, sizeof(TS), sizeof(TS));
   const int chunks = head_dim / nv;
-  const unsigned blocks = static_cast<unsigned>(cdiv64(rows * chunks, 256));
+  const dim3 blocks(static_cast<unsigned>(cdiv64(static_cast<int64_t>(q_len) * chunks, 256)), static_cast<unsigned>(bh));
+  const int cs = chunk_shift_of(chunks);
   auto si = static_cast<const TS*>(s_in);
   auto so = static_cast<TS*>(s_out);
 #define ELSA_PS(NV) prefix_scan_kernel<TS, NV><<<blocks, 256, 0, st>>>(m_in, z_in, si, m_out, z_out, so, n_parts, rows, \
-                                                                     head_dim, chunks)
+                                                                     q_len, head_dim, chunks, cs)
   if (nv == 8) ELSA_PS(8); else if (nv == 4) ELSA_PS(4); else ELSA_PS(1);
 #undef ELSA_PS
   ELSA_LAUNCH_CHECK();

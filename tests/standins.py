@@ -1,72 +1,5 @@
-"""Stand-ins for timm's ViT `Attention` and Swin-v1 `WindowAttention` (timm is not installed
-where these tests run).  They expose exactly the attributes the drop-in detectors look for
-(reference: src/elsa_twopass_clean/timm_dropin.py:153-172) and compute attention the plain way,
-so they also serve as the numerical baseline of the drop-in tests."""
-import torch
-import torch.nn as nn
-import torch.nn.functional as F
-
-
-class VitAttention(nn.Module):
-    def __init__(self, dim, num_heads, qkv_bias=True):
-        super().__init__()
-        self.num_heads = num_heads
-        self.head_dim = dim // num_heads
-        self.scale = self.head_dim ** -0.5
-        self.qkv = nn.Linear(dim, dim * 3, bias=qkv_bias)
-        self.q_norm = nn.Identity()
-        self.k_norm = nn.Identity()
-        self.attn_drop = nn.Dropout(0.0)
-        self.proj = nn.Linear(dim, dim)
-        self.proj_drop = nn.Dropout(0.0)
-
-    def forward(self, x, attn_mask=None):
-        b, n, c = x.shape
-        qkv = self.qkv(x).reshape(b, n, 3, self.num_heads, self.head_dim).permute(2, 0, 3, 1, 4)
-        q, k, v = qkv.unbind(0)
-        q, k = self.q_norm(q), self.k_norm(k)
-        y = F.scaled_dot_product_attention(q, k, v)
-        return self.proj_drop(self.proj(y.transpose(1, 2).reshape(b, n, c)))
-
-
-def relative_position_index(win_h, win_w):
-    coords = torch.stack(torch.meshgrid(torch.arange(win_h), torch.arange(win_w), indexing="ij")).flatten(1)
-    rel = (coords[:, :, None] - coords[:, None, :]).permute(1, 2, 0).contiguous()
-    rel[:, :, 0] += win_h - 1
-    rel[:, :, 1] += win_w - 1
-    rel[:, :, 0] *= 2 * win_w - 1
-    return rel.sum(-1)
-
-
-class SwinWindowAttention(nn.Module):
-    def __init__(self, dim, num_heads, window_size):
-        super().__init__()
-        self.dim = dim
-        self.window_size = window_size
-        self.window_area = window_size[0] * window_size[1]
-        self.num_heads = num_heads
-        head_dim = dim // num_heads
-        self.scale = head_dim ** -0.5
-        self.relative_position_bias_table = nn.Parameter(
-            torch.randn((2 * window_size[0] - 1) * (2 * window_size[1] - 1), num_heads) * 0.02)
-        self.register_buffer("relative_position_index", relative_position_index(*window_size), persistent=False)
-        self.qkv = nn.Linear(dim, dim * 3)
-        self.attn_drop = nn.Dropout(0.0)
-        self.proj = nn.Linear(dim, dim)
-        self.proj_drop = nn.Dropout(0.0)
-        self.softmax = nn.Softmax(dim=-1)
-
-    def forward(self, x, mask=None):
-        bw, n, c = x.shape
-        qkv = self.qkv(x).reshape(bw, n, 3, self.num_heads, -1).permute(2, 0, 3, 1, 4)
-        q, k, v = qkv.unbind(0)
-        attn = (q * self.scale) @ k.transpose(-2, -1)
-        bias = self.relative_position_bias_table[self.relative_position_index.view(-1)].view(n, n, -1)
-        attn = attn + bias.permute(2, 0, 1).unsqueeze(0)
-        if mask is not None:
-            nw = mask.shape[0]
-            attn = attn.view(-1, nw, self.num_heads, n, n) + mask.unsqueeze(1).unsqueeze(0)
-            attn = attn.view(-1, self.num_heads, n, n)
-        attn = self.softmax(attn)
-        y = (attn @ v).transpose(1, 2).reshape(bw, n, c)
-        return self.proj_drop(self.proj(y))
+"""Stand-ins for timm's ViT `Attention` and Swin-v1 `WindowAttention` (timm is not installed where these tests
+run): the package's own timm-shaped attention modules, which expose exactly the attributes the drop-in detectors
+look for (reference: src/elsa_twopass_clean/timm_dropin.py:153-172) and compute attention the plain way, so they
+also serve as the numerical baseline of the drop-in tests."""
+from elsa_b200.vision import SwinWindowAttention, VitAttention, relative_position_index  # noqa: F401
