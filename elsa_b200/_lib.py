@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("ELSA_B200_LIB") or os.path.join(_HERE, "libelsa_b200.so")
 
 ELSA_F32, ELSA_F16, ELSA_BF16 = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_SCAN_STEPS, FLAG_TREE_MERGE = 1, 2, 4
+FLAG_FORCE_SIMT, FLAG_SCAN_STEPS, FLAG_TREE_MERGE, FLAG_REF_ROUNDING = 1, 2, 4, 8
 
 _P = c_void_p
 _BIAS = [_P, c_int64, c_int64, c_int64, c_int64]
@@ -45,6 +45,9 @@ SIGNATURES = {
     "elsa_forward_plan": (c_int, [c_int] * 10 + [c_uint, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "elsa_twopass_forward": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_uint, _P]),
+    "elsa_twopass_forward_strided": (c_int, [_P, _P, _P, _P, _P, _P, *_BIAS, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_int, c_uint, _P]),
+    "elsa_twopass_backward_strided": (c_int, [_P] * 6 + [_P, _P] + _BIAS + [_P, _P, _P] + _BIAS + [_P, c_int64] + [c_int] * 6 + [c_uint, _P]),
     "elsa_static_scratch_bytes": (c_int64, []),
     "elsa_twopass_forward_static": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
     "elsa_bwd_preprocess": (c_int, [_P] * 6 + [c_int] * 4 + [_P]),

@@ -114,12 +114,65 @@ def _aligned(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def _bhnd_strides(t: torch.Tensor):
+    """(batch, head, row) element strides of a [B, H, N, D] view the kernels can read in place, or None when it has
+    to be copied first: the D axis must be contiguous, the other strides multiples of 8 elements (size-1 axes may
+    have any stride) and the first element 16-byte aligned."""
+    if t.dim() != 4 or (t.shape[3] > 1 and t.stride(3) != 1) or t.data_ptr() % 16:
+        return None
+    st = []
+    for ax in (0, 1, 2):
+        s = int(t.stride(ax)) if t.shape[ax] > 1 else int(t.shape[3]) * 8      # any valid value for a size-1 axis
+        if s % 8 or s <= 0:
+            return None
+        st.append(s)
+    if st[2] < int(t.shape[3]):
+        return None
+    return tuple(st)
+
+
+def _in_place_or_copy(t: torch.Tensor):
+    """(tensor, strides): the tensor itself with its strides when the kernels can read it in place, else an aligned
+    contiguous copy."""
+    st = _bhnd_strides(t)
+    if st is not None:
+        return t, st
+    t = _aligned(t)
+    return t, _bhnd_strides(t)
+
+
+def _empty_like_layout(ref: torch.Tensor, like_strides) -> torch.Tensor:
+    """An uninitialised [B, H, N, D] tensor whose axis order in memory follows `ref`: when ref is a row-major
+    [B, N, H, D] view (what the model hooks produce from a packed projection), so is the result, and a later
+    transpose(1, 2).reshape(B, N, H*D) is free; otherwise plain contiguous."""
+    b, h, n, d = ref.shape
+    if like_strides is not None and h > 1 and n > 1 and like_strides[1] < like_strides[2]:
+        return torch.empty((b, n, h, d), device=ref.device, dtype=ref.dtype).permute(0, 2, 1, 3)
+    return torch.empty((b, h, n, d), device=ref.device, dtype=ref.dtype)
+
+
+def _i64x(*triples):
+    import ctypes
+    flat = [int(x) for tr in triples for x in tr]
+    return (ctypes.c_int64 * len(flat))(*flat)
+
+
 def _forward_impl(q, k, v, *, bias, is_causal, summary_dtype, part_width, q_chunk, want_state, flags=0):
-    """Runs the two passes; returns (out, row_m, row_z, q_c, k_c, v_c)."""
+    """Runs the two passes; returns (out, row_m, row_z, q_c, k_c, v_c).  q, k, v are read in place when their layout
+    allows it (any [B, H, N, D] view with a contiguous D axis and 16-byte aligned rows), and `out` follows q's axis
+    order in memory; only other layouts are copied first."""
     lib = _lib.load()
     batch, heads, seq_len, head_dim = map(int, q.shape)
-    q_c, k_c, v_c = _aligned(q), _aligned(k), _aligned(v)
-    out = torch.empty_like(q_c)
+    strided = not (flags & _lib.FLAG_REF_ROUNDING) and head_dim % 8 == 0
+    if strided:
+        (q_c, qs), (k_c, ks), (v_c, vs) = (_in_place_or_copy(t) for t in (q, k, v))
+        strided = any(not t.is_contiguous() for t in (q_c, k_c, v_c))
+    if not strided:
+        q_c, k_c, v_c = _aligned(q), _aligned(k), _aligned(v)
+        out = torch.empty_like(q_c)
+    else:
+        out = _empty_like_layout(q_c, qs)
+        os_ = _bhnd_strides(out)
     bh = batch * heads
     row_m = row_z = None
     if want_state:
@@ -134,11 +187,18 @@ def _forward_impl(q, k, v, *, bias, is_causal, summary_dtype, part_width, q_chun
     with torch.cuda.device(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        rc = lib.elsa_twopass_forward(
-            q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), *meta.c_args(), out.data_ptr(),
-            None if row_m is None else row_m.data_ptr(), None if row_z is None else row_z.data_ptr(),
-            ws.data_ptr(), ws.numel(), dt, sdt, batch, heads, seq_len, head_dim, int(bool(is_causal)),
-            part_width, q_chunk, flags, stream)
+        rm_p = None if row_m is None else row_m.data_ptr()
+        rz_p = None if row_z is None else row_z.data_ptr()
+        if strided:
+            rc = lib.elsa_twopass_forward_strided(
+                q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), _i64x(qs), _i64x(ks), _i64x(vs), *meta.c_args(),
+                out.data_ptr(), _i64x(os_), rm_p, rz_p, ws.data_ptr(), ws.numel(), dt, sdt, batch, heads, seq_len,
+                head_dim, int(bool(is_causal)), part_width, q_chunk, flags, stream)
+        else:
+            rc = lib.elsa_twopass_forward(
+                q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), *meta.c_args(), out.data_ptr(), rm_p, rz_p,
+                ws.data_ptr(), ws.numel(), dt, sdt, batch, heads, seq_len, head_dim, int(bool(is_causal)),
+                part_width, q_chunk, flags, stream)
     _lib.check(rc, "elsa_twopass_forward")
     return out, row_m, row_z, q_c, k_c, v_c
 
@@ -160,12 +220,17 @@ def twopass_attention(
     phase2_stages: Optional[int] = None,
     input_precision: Literal["auto", "ieee", "tf32", "tf32x3"] = "auto",
     algorithm: Literal["auto", "paper_scan"] = "auto",
+    reference_rounding: bool = False,
 ) -> torch.Tensor:
     """Exact softmax attention softmax(q k^T / sqrt(D) + bias) v as a two-pass monoid reduction.
 
     Phase 1 writes one (m, z, s) summary per K partition to global memory; phase 2 merges the
     partition summaries (for causal attention: the last inclusive prefix) and emits s / z.
     q, k, v: [B, H, N, D], one dtype in {fp16, bf16, fp32}, D <= 128, CUDA.  Returns [B, H, N, D].
+
+    `reference_rounding` (not a keyword of the reference) reproduces the rounding points of the reference's fp16
+    head-dim-64 kernels (q scaled by log2(e)/8 in fp16, attention_parallel_scan.py:153-154,160) where the reference
+    would run them (fp16, D = 64, no bias, not causal); by default the scale is applied exactly, in fp32.
     """
     _check_qkv(q, k, v, "twopass_attention")
     if algorithm not in ("auto", "paper_scan"):
@@ -179,4 +244,5 @@ def twopass_attention(
         block_n=block_n, q_chunk_size=q_chunk_size, phase1_warps=phase1_warps, phase2_warps=phase2_warps,
         phase1_stages=phase1_stages, phase2_stages=phase2_stages)
     return _forward_impl(q, k, v, bias=bias, is_causal=is_causal, summary_dtype=summary_dtype,
-                         part_width=part_width, q_chunk=q_chunk, want_state=False)[0]
+                         part_width=part_width, q_chunk=q_chunk, want_state=False,
+                         flags=_lib.FLAG_REF_ROUNDING if reference_rounding else 0)[0]

@@ -15,7 +15,8 @@ from typing import Literal, Optional
 import torch
 
 from . import _lib
-from .attention import _aligned, _canonical_bias, _check_qkv, _forward_impl, _resolve_common, _validate_warps
+from .attention import (_aligned, _bhnd_strides, _canonical_bias, _check_qkv, _empty_like_layout, _forward_impl, _i64x,
+                        _in_place_or_copy, _resolve_common, _validate_warps)
 
 
 def twopass_attention_with_state(
@@ -36,6 +37,7 @@ def twopass_attention_with_state(
     input_precision: Literal["auto", "ieee", "tf32", "tf32x3"] = "auto",
     algorithm: Literal["auto", "paper_scan"] = "auto",
     return_contiguous_inputs: bool = False,
+    reference_rounding: bool = False,
 ) -> tuple[torch.Tensor, ...]:
     """Forward that also returns the row statistics the backward needs.
 
@@ -57,7 +59,7 @@ def twopass_attention_with_state(
         phase1_stages=phase1_stages, phase2_stages=phase2_stages)
     out, row_m, row_z, q_c, k_c, v_c = _forward_impl(
         q, k, v, bias=bias, is_causal=is_causal, summary_dtype=summary_dtype, part_width=part_width,
-        q_chunk=q_chunk, want_state=True)
+        q_chunk=q_chunk, want_state=True, flags=_lib.FLAG_REF_ROUNDING if reference_rounding else 0)
     if return_contiguous_inputs:
         return out, row_m, row_z, q_c, k_c, v_c
     return out, row_m, row_z
@@ -82,19 +84,37 @@ def _row_stats(q_c, k_c, meta, is_causal):
     return row_m, row_z
 
 
-def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, want_dbias, flags=0):
+def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, want_dbias, flags=0, grads_into=None):
+    """dq, dk, dv (and dbias) through the library.  Inputs are read in place where their layout allows it (see
+    `_forward_impl`); `grads_into` = (dq, dk, dv) lets the caller supply the gradient tensors, e.g. the three slices
+    of one packed [B, N, 3, H, D] buffer."""
     lib = _lib.load()
     batch, heads, seq_len, head_dim = map(int, q.shape)
-    q_c, k_c, v_c, out_c, go_c = (_aligned(t) for t in (q, k, v, out, grad_out))
+    strided = head_dim % 8 == 0
+    if strided:
+        pairs = [_in_place_or_copy(t) for t in (q, k, v, out, grad_out)]
+        (q_c, qs), (k_c, ks), (v_c, vs), (out_c, os_), (go_c, gs) = pairs
+        strided = any(not t.is_contiguous() for t, _ in pairs) or grads_into is not None
+    if not strided:
+        q_c, k_c, v_c, out_c, go_c = (_aligned(t) for t in (q, k, v, out, grad_out))
     meta = _canonical_bias(bias, batch=batch, heads=heads, seq_len=seq_len, device=q.device)
     if row_m is None or row_z is None:
-        row_m, row_z = _row_stats(q_c, k_c, meta, is_causal)
+        row_m, row_z = _row_stats(_aligned(q_c), _aligned(k_c), meta, is_causal)
     else:
         if tuple(row_m.shape) != (batch * heads, seq_len) or tuple(row_z.shape) != (batch * heads, seq_len):
             raise ValueError("row_m and row_z must have shape [B*H,N]")
         row_m = row_m.to(torch.float32).contiguous()
         row_z = row_z.to(torch.float32).contiguous()
-    dq, dk, dv = torch.empty_like(q_c), torch.empty_like(k_c), torch.empty_like(v_c)
+    if grads_into is not None:
+        dq, dk, dv = grads_into
+        g_strides = [_bhnd_strides(t) for t in (dq, dk, dv)]
+        if any(st is None for st in g_strides) or not strided:
+            raise ValueError("elsa_b200: the supplied gradient tensors cannot be written in place")
+    elif strided:
+        dq, dk, dv = (_empty_like_layout(t, st) for t, st in ((q_c, qs), (k_c, ks), (v_c, vs)))
+        g_strides = [_bhnd_strides(t) for t in (dq, dk, dv)]
+    else:
+        dq, dk, dv = torch.empty_like(q_c), torch.empty_like(k_c), torch.empty_like(v_c)
     dbias = None
     dargs = (None, 0, 0, 0, 0)
     if want_dbias:
@@ -110,11 +130,18 @@ def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, wan
         raise ValueError("elsa_b200: unsupported problem size for the backward")
     with torch.cuda.device(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
-        rc = lib.elsa_twopass_backward(
-            q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), out_c.data_ptr(), go_c.data_ptr(),
-            row_m.data_ptr(), row_z.data_ptr(), *meta.c_args(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-            *dargs, ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len, head_dim, int(bool(is_causal)), flags,
-            torch.cuda.current_stream(q.device).cuda_stream)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        if strided:
+            rc = lib.elsa_twopass_backward_strided(
+                q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), out_c.data_ptr(), go_c.data_ptr(),
+                _i64x(qs, ks, vs, os_, gs, *g_strides), row_m.data_ptr(), row_z.data_ptr(), *meta.c_args(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), *dargs, ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len,
+                head_dim, int(bool(is_causal)), flags, stream)
+        else:
+            rc = lib.elsa_twopass_backward(
+                q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), out_c.data_ptr(), go_c.data_ptr(),
+                row_m.data_ptr(), row_z.data_ptr(), *meta.c_args(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                *dargs, ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len, head_dim, int(bool(is_causal)), flags, stream)
     _lib.check(rc, "elsa_twopass_backward")
     if dbias is not None:
         dbias = dbias.view(bias.shape).to(bias.dtype)
@@ -189,6 +216,63 @@ class _TwopassAttentionAutograd(torch.autograd.Function):
         dq, dk, dv, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
                                            row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad)
         return dq, dk, dv, dbias, None, None, None
+
+
+class _PackedQkvAttentionAutograd(torch.autograd.Function):
+    """Attention on a packed projection output qkv [B, N, 3, H, D] (what `nn.Linear(dim, 3*dim)` produces, viewed):
+    q, k, v are read in place, the output is written as [B, N, H, D] memory, and the backward writes dq, dk, dv
+    straight into one packed gradient -- no `.contiguous()` copies, no `stack` in autograd."""
+
+    @staticmethod
+    def forward(ctx, qkv, bias, is_causal, fwd_kwargs):
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)           # three [B, H, N, D] views
+        out, row_m, row_z, q_s, k_s, v_s = twopass_attention_with_state(
+            q, k, v, bias=bias, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
+        has_bias = bias is not None
+        ctx.save_for_backward(qkv, out, bias if has_bias else qkv.new_empty(1, dtype=torch.float32), row_m, row_z)
+        ctx.has_bias = has_bias
+        ctx.bias_requires_grad = bool(has_bias and bias.requires_grad)
+        ctx.is_causal = bool(is_causal)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkv, out, saved_bias, row_m, row_z = ctx.saved_tensors
+        bias = saved_bias if ctx.has_bias else None
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+        dqkv = torch.empty_like(qkv, memory_format=torch.contiguous_format)
+        grads = dqkv.permute(2, 0, 3, 1, 4).unbind(0)
+        in_place = all(_bhnd_strides(t) is not None for t in (q, k, v, *grads)) and int(qkv.shape[-1]) % 8 == 0
+        if in_place:
+            _, _, _, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
+                                            row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad, grads_into=grads)
+        else:
+            dq, dk, dv, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
+                                               row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad)
+            for dst, src in zip(grads, (dq, dk, dv)):
+                dst.copy_(src)
+        return dqkv, dbias, None, None
+
+
+def twopass_attention_qkvpacked(qkv: torch.Tensor, *, bias: Optional[torch.Tensor] = None, is_causal: bool = False,
+                                train: bool = True, **fwd_kwargs) -> torch.Tensor:
+    """Attention on a packed qkv [B, N, 3, H, D] (not an entry point of the reference: the form its hooks would need to
+    avoid their per-layer copies, src/elsa_twopass_clean/timm_dropin.py:46-55, timm_dropin_bwd.py:68-73).
+    Returns out as a [B, H, N, D] view of [B, N, H, D] memory, so `out.transpose(1, 2).reshape(B, N, H*D)` is free.
+    train=False skips autograd and the row state."""
+    if qkv.dim() != 5 or qkv.shape[2] != 3:
+        raise ValueError("qkv must have shape [B,N,3,H,D]")
+    # the backward tile hints of twopass_attention_train are validated and advisory, as there
+    if fwd_kwargs.get("bwd_input_precision", "auto") not in ("auto", "ieee", "tf32", "tf32x3"):
+        raise ValueError("input_precision must be 'auto', 'ieee', 'tf32', or 'tf32x3'")
+    if fwd_kwargs.get("bwd_num_warps") is not None:
+        _validate_warps("num_warps", fwd_kwargs["bwd_num_warps"])
+    fwd_kwargs = {name: val for name, val in fwd_kwargs.items() if not name.startswith("bwd_")}
+    if not train:
+        from .attention import twopass_attention
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+        return twopass_attention(q, k, v, bias=bias, is_causal=is_causal, **fwd_kwargs)
+    return _PackedQkvAttentionAutograd.apply(qkv, bias, is_causal, dict(fwd_kwargs))
 
 
 def twopass_attention_train(

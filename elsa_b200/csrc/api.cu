@@ -131,13 +131,25 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
 
 static int64_t plan_bytes(const ForwardPlan& pl) { return pl.sets * (2 * pl.mz_bytes + pl.s_bytes); }
 
+// ELSA_FLAG_REF_ROUNDING reproduces the rounding points of the reference's fp16 head-dim-64 kernels
+// (attention_parallel_scan.py:153-154,160: q is multiplied by log2(e)/8 IN fp16 -- the constant rounded to fp16, the
+// product rounded to fp16 -- and the scores get no further scale).  It applies where the reference takes those
+// kernels: fp16, head dim 64, no bias, not causal; elsewhere the flag changes nothing.
+static bool ref_rounding_applies(unsigned flags, int dtype, int head_dim, bool has_bias, int is_causal) {
+  return (flags & ELSA_FLAG_REF_ROUNDING) && dtype == ELSA_F16 && head_dim == 64 && !has_bias && !is_causal;
+}
+static int64_t ref_rounding_bytes(int batch, int heads, int n_ctx, int head_dim) {
+  return align_up(static_cast<int64_t>(batch) * heads * n_ctx * head_dim * 2, 256);
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int phase1_dispatch(const void* q, const void* k, const void* v, const float* bias, int64_t bsb, int64_t bsh,
                            int64_t bsq, int64_t bsk, float* m_buf, float* z_buf, void* s_buf, int dtype,
                            int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int q_start, int q_len,
                            int part_width, int n_parts, int is_causal, unsigned flags, cudaStream_t st,
-                           int n_keys = -1, int key_offset = 0) {
+                           int n_keys = -1, int key_offset = 0, bool q_prescaled = false,
+                           const Strides* qs = nullptr, const Strides* ks = nullptr, const Strides* vs = nullptr) {
   if (n_keys < 0) n_keys = n_ctx;
   if (!q || !k || !v || !m_buf || !z_buf || !s_buf || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
       heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || q_start < 0 || q_len < 0 ||
@@ -150,6 +162,9 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   if (part_width % 64 != 0) return ELSA_ERR_INVALID_ARGUMENT;
   FoldParams p;
   p.q = q; p.k = k; p.v = v;
+  p.qs = qs ? *qs : contiguous_strides(heads, n_ctx, head_dim);
+  p.ks = ks ? *ks : contiguous_strides(heads, n_keys, head_dim);
+  p.vs = vs ? *vs : contiguous_strides(heads, n_keys, head_dim);
   p.bias = bias; p.bsb = bsb; p.bsh = bsh; p.bsq = bsq; p.bsk = bsk;
   p.m = m_buf; p.z = z_buf; p.s = s_buf;
   p.heads = heads; p.n_ctx = n_ctx; p.head_dim = head_dim; p.q_start = q_start; p.q_len = q_len;
@@ -162,6 +177,7 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.round_p = (dtype == ELSA_F16 && summary_dtype != ELSA_F32) ? 1 : 0;
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+  if (q_prescaled) p.scale_log2 = 1.0f;   // q already carries log2(e)/sqrt(d) (reference-rounding mode, no bias)
   if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
@@ -253,15 +269,22 @@ extern "C" int64_t elsa_forward_workspace_bytes(int dtype, int summary_dtype, in
   if (plan_forward(dtype, summary_dtype, batch, heads, n_ctx, head_dim, is_causal, has_bias != 0, part_width, q_chunk, flags,
                    &pl) != ELSA_OK)
     return -1;
-  return plan_bytes(pl);
+  return plan_bytes(pl) +
+         (ref_rounding_applies(flags, dtype, head_dim, has_bias != 0, is_causal) ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0);
 }
 
-extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v, const float* bias,
-                                    int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q,
-                                    int64_t bias_stride_k, void* out, float* row_m, float* row_z, void* workspace,
-                                    int64_t workspace_bytes, int dtype, int summary_dtype, int batch, int heads,
-                                    int n_ctx, int head_dim, int is_causal, int part_width, int q_chunk, unsigned flags,
-                                    void* stream) {
+// strides given by the caller: every one a multiple of 8 elements, so that rows start on 16-byte boundaries
+static bool strides_ok(const int64_t* st, int head_dim) {
+  return st && st[0] >= 0 && st[1] >= 0 && st[2] >= head_dim && (st[0] | st[1] | st[2]) % 8 == 0;
+}
+static Strides to_strides(const int64_t* st) { return Strides{st[0], st[1], st[2]}; }
+
+static int forward_impl(const void* q, const void* k, const void* v, const Strides* qs, const Strides* ks,
+                        const Strides* vs, const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                        int64_t bias_stride_q, int64_t bias_stride_k, void* out, const Strides* os, float* row_m,
+                        float* row_z, void* workspace, int64_t workspace_bytes, int dtype, int summary_dtype, int batch,
+                        int heads, int n_ctx, int head_dim, int is_causal, int part_width, int q_chunk, unsigned flags,
+                        void* stream) {
   if (n_ctx == 0) return ELSA_OK;
   if (!q || !k || !v || !out) return ELSA_ERR_INVALID_ARGUMENT;
   if ((row_m == nullptr) != (row_z == nullptr)) return ELSA_ERR_INVALID_ARGUMENT;
@@ -269,11 +292,23 @@ extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v,
   int rc = plan_forward(dtype, summary_dtype, batch, heads, n_ctx, head_dim, is_causal, bias != nullptr, part_width,
                         q_chunk, flags, &pl);
   if (rc != ELSA_OK) return rc;
-  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < plan_bytes(pl))
+  const bool ref_round = ref_rounding_applies(flags, dtype, head_dim, bias != nullptr, is_causal);
+  const int64_t need_ws = plan_bytes(pl) + (ref_round ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < need_ws)
     return ELSA_ERR_WORKSPACE;
   if (!aligned16(out)) return ELSA_ERR_INVALID_ARGUMENT;
   auto st = static_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
+  if (ref_round) {
+    // q' = fp16(q * fp16(log2(e) / sqrt(d))) behind the summaries in the workspace; phase 1 then runs on q' unscaled
+    void* q_scaled = ws + plan_bytes(pl);
+    if (!aligned16(q)) return ELSA_ERR_INVALID_ARGUMENT;
+    if (qs) return ELSA_ERR_UNSUPPORTED;   // the pre-scaled copy is made from a contiguous q
+    rc = prescale_q_f16(q, q_scaled, static_cast<int64_t>(batch) * heads * n_ctx * head_dim,
+                        static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634), st);
+    if (rc != ELSA_OK) return rc;
+    q = q_scaled;
+  }
   float* m_a = reinterpret_cast<float*>(ws);
   float* z_a = reinterpret_cast<float*>(ws + pl.mz_bytes);
   void* s_a = ws + 2 * pl.mz_bytes;
@@ -288,7 +323,7 @@ extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v,
     const int q_len = std::min(pl.q_chunk, n_ctx - q_start);
     rc = phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_a, z_a, s_a, dtype,
                          summary_dtype, batch, heads, n_ctx, head_dim, q_start, q_len, pl.part_width, pl.n_parts,
-                         is_causal, flags, st);
+                         is_causal, flags, st, -1, 0, ref_round, qs, ks, vs);
     if (rc != ELSA_OK) return rc;
     if (is_causal && (flags & ELSA_FLAG_SCAN_STEPS)) {
       // log-depth Hillis-Steele inclusive scan, ping-pong between the two summary sets; the last
@@ -301,7 +336,7 @@ extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v,
         std::swap(sm, dm); std::swap(sz, dz); std::swap(ss, ds);
       }
       rc = merge_final_any(sm, sz, ss, out, row_m, row_z, summary_dtype, dtype, 1, bh, q_start, q_len, n_ctx, head_dim,
-                           pl.n_parts - 1, store_state, st);
+                           pl.n_parts - 1, store_state, st, 1, heads, os);
     } else if (!is_causal && (flags & ELSA_FLAG_TREE_MERGE)) {
       float *sm = m_a, *sz = z_a, *dm = m_b, *dz = z_b;
       void *ss = s_a, *ds = s_b;
@@ -311,14 +346,41 @@ extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v,
         std::swap(sm, dm); std::swap(sz, dz); std::swap(ss, ds);
       }
       rc = merge_final_any(sm, sz, ss, out, row_m, row_z, summary_dtype, dtype, 1, bh, q_start, q_len, n_ctx, head_dim, 0,
-                           store_state, st);
+                           store_state, st, 1, heads, os);
     } else {
       rc = merge_final_any(m_a, z_a, s_a, out, row_m, row_z, summary_dtype, dtype, pl.n_parts, bh, q_start, q_len, n_ctx,
-                           head_dim, 0, store_state, st);
+                           head_dim, 0, store_state, st, 1, heads, os);
     }
     if (rc != ELSA_OK) return rc;
   }
   return ELSA_OK;
+}
+
+extern "C" int elsa_twopass_forward(const void* q, const void* k, const void* v, const float* bias,
+                                    int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q,
+                                    int64_t bias_stride_k, void* out, float* row_m, float* row_z, void* workspace,
+                                    int64_t workspace_bytes, int dtype, int summary_dtype, int batch, int heads,
+                                    int n_ctx, int head_dim, int is_causal, int part_width, int q_chunk, unsigned flags,
+                                    void* stream) {
+  return forward_impl(q, k, v, nullptr, nullptr, nullptr, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k,
+                      out, nullptr, row_m, row_z, workspace, workspace_bytes, dtype, summary_dtype, batch, heads, n_ctx,
+                      head_dim, is_causal, part_width, q_chunk, flags, stream);
+}
+
+extern "C" int elsa_twopass_forward_strided(const void* q, const void* k, const void* v, const int64_t* q_strides,
+                                            const int64_t* k_strides, const int64_t* v_strides, const float* bias,
+                                            int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q,
+                                            int64_t bias_stride_k, void* out, const int64_t* out_strides, float* row_m,
+                                            float* row_z, void* workspace, int64_t workspace_bytes, int dtype,
+                                            int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
+                                            int is_causal, int part_width, int q_chunk, unsigned flags, void* stream) {
+  if (!strides_ok(q_strides, head_dim) || !strides_ok(k_strides, head_dim) || !strides_ok(v_strides, head_dim) ||
+      !strides_ok(out_strides, head_dim))
+    return ELSA_ERR_INVALID_ARGUMENT;
+  const Strides qs = to_strides(q_strides), ks = to_strides(k_strides), vs = to_strides(v_strides), os = to_strides(out_strides);
+  return forward_impl(q, k, v, &qs, &ks, &vs, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, out, &os,
+                      row_m, row_z, workspace, workspace_bytes, dtype, summary_dtype, batch, heads, n_ctx, head_dim,
+                      is_causal, part_width, q_chunk, flags, stream);
 }
 
 // ---- backward -------------------------------------------------------------------------------
@@ -339,13 +401,14 @@ extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads
   return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
 }
 
-extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                                     const float* row_m, const float* row_z, const float* bias, int64_t bias_stride_b,
-                                     int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k, void* dq,
-                                     void* dk, void* dv, float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
-                                     int64_t dbias_stride_q, int64_t dbias_stride_k, void* workspace,
-                                     int64_t workspace_bytes, int dtype, int batch, int heads, int n_ctx, int head_dim,
-                                     int is_causal, unsigned flags, void* stream) {
+// st8: strides of q, k, v, out, dout, dq, dk, dv in that order, or nullptr for contiguous [B*H, N, D] tensors
+static int backward_impl(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                         const Strides* st8, const float* row_m, const float* row_z, const float* bias,
+                         int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k,
+                         void* dq, void* dk, void* dv, float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
+                         int64_t dbias_stride_q, int64_t dbias_stride_k, void* workspace, int64_t workspace_bytes,
+                         int dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal, unsigned flags,
+                         void* stream) {
   if (n_ctx == 0) return ELSA_OK;
   if (!q || !k || !v || !out || !dout || !row_m || !row_z || !dq || !dk || !dv || !dtype_ok(dtype) || batch < 1 ||
       heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128)
@@ -360,10 +423,16 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
-  int rc = ELSA_OK;
-  if (!use_tc) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
-  if (rc != ELSA_OK) return rc;
+  const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
+  const Strides os = st8 ? st8[3] : cs;
   BwdParams p;
+  p.qs = st8 ? st8[0] : cs; p.ks = st8 ? st8[1] : cs; p.vs = st8 ? st8[2] : cs; p.gs = st8 ? st8[4] : cs;
+  p.dqs = st8 ? st8[5] : cs; p.dks = st8 ? st8[6] : cs; p.dvs = st8 ? st8[7] : cs;
+  int rc = ELSA_OK;
+  if (!use_tc)
+    rc = bwd_preprocess_any(out, os, dout, p.gs, row_m, row_z, row_d, row_lse, dtype, batch, heads, n_ctx, head_dim,
+                            static_cast<cudaStream_t>(stream));
+  if (rc != ELSA_OK) return rc;
   p.q = q; p.k = k; p.v = v; p.dout = dout;
   p.lse = row_lse; p.drow = row_d;
   p.bias = bias; p.bsb = bias_stride_b; p.bsh = bias_stride_h; p.bsq = bias_stride_q; p.bsk = bias_stride_k;
@@ -377,9 +446,40 @@ extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v
   if (use_tc) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
-    return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+    return bwd_tc(p, out, os, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                     const float* row_m, const float* row_z, const float* bias, int64_t bias_stride_b,
+                                     int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k, void* dq,
+                                     void* dk, void* dv, float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
+                                     int64_t dbias_stride_q, int64_t dbias_stride_k, void* workspace,
+                                     int64_t workspace_bytes, int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                     int is_causal, unsigned flags, void* stream) {
+  return backward_impl(q, k, v, out, dout, nullptr, row_m, row_z, bias, bias_stride_b, bias_stride_h, bias_stride_q,
+                       bias_stride_k, dq, dk, dv, dbias, dbias_stride_b, dbias_stride_h, dbias_stride_q, dbias_stride_k,
+                       workspace, workspace_bytes, dtype, batch, heads, n_ctx, head_dim, is_causal, flags, stream);
+}
+
+extern "C" int elsa_twopass_backward_strided(const void* q, const void* k, const void* v, const void* out,
+                                             const void* dout, const int64_t* strides, const float* row_m,
+                                             const float* row_z, const float* bias, int64_t bias_stride_b,
+                                             int64_t bias_stride_h, int64_t bias_stride_q, int64_t bias_stride_k,
+                                             void* dq, void* dk, void* dv, float* dbias, int64_t dbias_stride_b,
+                                             int64_t dbias_stride_h, int64_t dbias_stride_q, int64_t dbias_stride_k,
+                                             void* workspace, int64_t workspace_bytes, int dtype, int batch, int heads,
+                                             int n_ctx, int head_dim, int is_causal, unsigned flags, void* stream) {
+  if (!strides) return ELSA_ERR_INVALID_ARGUMENT;
+  Strides st8[8];
+  for (int i = 0; i < 8; ++i) {
+    if (!strides_ok(strides + 3 * i, head_dim)) return ELSA_ERR_INVALID_ARGUMENT;
+    st8[i] = to_strides(strides + 3 * i);
+  }
+  return backward_impl(q, k, v, out, dout, st8, row_m, row_z, bias, bias_stride_b, bias_stride_h, bias_stride_q,
+                       bias_stride_k, dq, dk, dv, dbias, dbias_stride_b, dbias_stride_h, dbias_stride_q, dbias_stride_k,
+                       workspace, workspace_bytes, dtype, batch, heads, n_ctx, head_dim, is_causal, flags, stream);
 }
 
 // ---- backward of one sequence shard ---------------------------------------------------------------
@@ -414,6 +514,8 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   if (!use_tc) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
   if (rc != ELSA_OK) return rc;
   BwdParams p;
+  const Strides cs = contiguous_strides(heads, n_ctx, head_dim), cks = contiguous_strides(heads, n_keys, head_dim);
+  p.qs = cs; p.gs = cs; p.dqs = cs; p.ks = cks; p.vs = cks; p.dks = cks; p.dvs = cks;
   p.q = q; p.k = k_shard; p.v = v_shard; p.dout = dout;
   p.lse = row_lse; p.drow = row_d;
   p.bias = nullptr; p.bsb = p.bsh = p.bsq = p.bsk = 0;
@@ -426,7 +528,7 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   if (use_tc) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
-    return bwd_tc(p, out, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+    return bwd_tc(p, out, cs, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }

@@ -34,21 +34,22 @@ bwd_simt_kernel(const BwdParams prm) {
   const int NC = MODE == 0 ? NK : N;       // columns walked by the loop
   const int r0 = blockIdx.x * 64;
   const int rows_valid = min(64, NR - r0);
-  const int64_t base = static_cast<int64_t>(bh) * N * D;       // q, dO, dQ
-  const int64_t kbase = static_cast<int64_t>(bh) * NK * D;     // k, v, dK, dV
-  const T* qb = static_cast<const T*>(prm.q) + base;
-  const T* kb = static_cast<const T*>(prm.k) + kbase;
-  const T* vb = static_cast<const T*>(prm.v) + kbase;
-  const T* gb = static_cast<const T*>(prm.dout) + base;
+  const int b = bh / prm.heads, h = bh - b * prm.heads;
+  const T* qb = static_cast<const T*>(prm.q) + b * prm.qs.b + h * prm.qs.h;
+  const T* kb = static_cast<const T*>(prm.k) + b * prm.ks.b + h * prm.ks.h;
+  const T* vb = static_cast<const T*>(prm.v) + b * prm.vs.b + h * prm.vs.h;
+  const T* gb = static_cast<const T*>(prm.dout) + b * prm.gs.b + h * prm.gs.h;
+  const int64_t ra_ld = MODE == 0 ? prm.qs.r : prm.ks.r, rb_ld = MODE == 0 ? prm.gs.r : prm.vs.r;   // resident operands
+  const int64_t ca_ld = MODE == 0 ? prm.ks.r : prm.qs.r, cb_ld = MODE == 0 ? prm.vs.r : prm.gs.r;   // streamed operands
   const float* lse = prm.lse + static_cast<int64_t>(bh) * N;
   const float* drow = prm.drow + static_cast<int64_t>(bh) * N;
-  const bool vec_ok = (D % 4) == 0;
-  const int b = bh / prm.heads, h = bh - b * prm.heads;
+  const bool vec_ok = (D % 4) == 0 && ((prm.qs.r | prm.ks.r | prm.vs.r | prm.gs.r | prm.qs.h | prm.ks.h | prm.vs.h | prm.gs.h |
+                                        prm.qs.b | prm.ks.b | prm.vs.b | prm.gs.b) % 4) == 0;
   const float* bias_bh = prm.bias ? prm.bias + b * prm.bsb + h * prm.bsh : nullptr;
   float* dbias_bh = (MODE == 0 && prm.dbias) ? prm.dbias + b * prm.dsb + h * prm.dsh : nullptr;
 
-  load_tile<T, DP>(RA, LD, (MODE == 0 ? qb : kb) + static_cast<int64_t>(r0) * D, rows_valid, D, vec_ok, tid);
-  load_tile<T, DP>(RB, LD, (MODE == 0 ? gb : vb) + static_cast<int64_t>(r0) * D, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(RA, LD, (MODE == 0 ? qb : kb) + static_cast<int64_t>(r0) * ra_ld, ra_ld, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(RB, LD, (MODE == 0 ? gb : vb) + static_cast<int64_t>(r0) * rb_ld, rb_ld, rows_valid, D, vec_ok, tid);
 
   float lse_r[4], d_r[4];
   if (MODE == 0) {
@@ -74,8 +75,8 @@ bwd_simt_kernel(const BwdParams prm) {
   for (int c0 = c_begin; c0 < c_end; c0 += 64) {
     __syncthreads();
     const int cv = min(64, NC - c0);
-    load_tile<T, DP>(CA, LD, (MODE == 0 ? kb : qb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
-    load_tile<T, DP>(CB, LD, (MODE == 0 ? vb : gb) + static_cast<int64_t>(c0) * D, cv, D, vec_ok, tid);
+    load_tile<T, DP>(CA, LD, (MODE == 0 ? kb : qb) + static_cast<int64_t>(c0) * ca_ld, ca_ld, cv, D, vec_ok, tid);
+    load_tile<T, DP>(CB, LD, (MODE == 0 ? vb : gb) + static_cast<int64_t>(c0) * cb_ld, cb_ld, cv, D, vec_ok, tid);
     __syncthreads();
 
     float S[4][4], dP[4][4];
@@ -142,13 +143,12 @@ bwd_simt_kernel(const BwdParams prm) {
     for (int c = 0; c < CPT; ++c) {
       const int col = tile_col<DP>(tx, c);
       if (col >= D) continue;
-      const int64_t o = (MODE == 0 ? base : kbase) + static_cast<int64_t>(r) * D + col;
       if (MODE == 0) {
-        if (prm.dq_f32) static_cast<float*>(prm.dq)[o] = acc1[ii][c] * prm.scale;
-        else static_cast<T*>(prm.dq)[o] = from_f32<T>(acc1[ii][c] * prm.scale);
+        if (prm.dq_f32) static_cast<float*>(prm.dq)[(static_cast<int64_t>(bh) * N + r) * D + col] = acc1[ii][c] * prm.scale;
+        else static_cast<T*>(prm.dq)[b * prm.dqs.b + h * prm.dqs.h + r * prm.dqs.r + col] = from_f32<T>(acc1[ii][c] * prm.scale);
       } else {
-        static_cast<T*>(prm.dv)[o] = from_f32<T>(acc1[ii][c]);
-        static_cast<T*>(prm.dk)[o] = from_f32<T>(acc2[ii][c] * prm.scale);
+        static_cast<T*>(prm.dv)[b * prm.dvs.b + h * prm.dvs.h + r * prm.dvs.r + col] = from_f32<T>(acc1[ii][c]);
+        static_cast<T*>(prm.dk)[b * prm.dks.b + h * prm.dks.h + r * prm.dks.r + col] = from_f32<T>(acc2[ii][c] * prm.scale);
       }
     }
   }
@@ -183,20 +183,23 @@ int bwd_simt(const BwdParams& p, int dtype, cudaStream_t st) {
 }
 
 // ---- preprocess --------------------------------------------------------------------------
-// 8 lanes per row; each lane strides over the row in 4-element vectors.
+// 8 lanes per row; blockIdx.y = (batch*head), x covers the rows; out / dout rows are addressed through their strides.
 template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
                       const float* __restrict__ row_z, float* __restrict__ row_d, float* __restrict__ row_lse,
-                      int64_t rows, int D, int vec_ok) {
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t row = gid >> 3;
+                      int heads, int n_ctx, int D, Strides os, Strides gs, int vec_ok) {
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = static_cast<int>(gid >> 3);
   const int lane = static_cast<int>(gid & 7);
+  const int bh = blockIdx.y;
+  const int b = bh / heads, h = bh - b * heads;
+  const bool ok = r < n_ctx;
   float part = 0.f;
-  if (row < rows) {
-    const T* o = out + row * D;
-    const T* g = dout + row * D;
-    if (vec_ok == 2) {          // 16-bit elements, D % 8 == 0: 16-byte loads
+  if (ok) {
+    const T* o = out + b * os.b + h * os.h + static_cast<int64_t>(r) * os.r;
+    const T* g = dout + b * gs.b + h * gs.h + static_cast<int64_t>(r) * gs.r;
+    if (vec_ok == 2) {          // 16-bit elements, D % 8 == 0, rows 16-byte aligned: 16-byte loads
       if constexpr (sizeof(T) == 2) {
         for (int c = lane * 8; c < D; c += 64) {
           const uint4 ov = *reinterpret_cast<const uint4*>(o + c), gv = *reinterpret_cast<const uint4*>(g + c);
@@ -208,10 +211,10 @@ bwd_preprocess_kernel(const T* __restrict__ out, const T* __restrict__ dout, con
       }
     } else if (vec_ok) {
       for (int c = lane * 4; c < D; c += 32) {
-        float a[4], b[4];
+        float a[4], bb[4];
         Vec4<T>::load(o + c, a);
-        Vec4<T>::load(g + c, b);
-        part += a[0] * b[0] + a[1] * b[1] + a[2] * b[2] + a[3] * b[3];
+        Vec4<T>::load(g + c, bb);
+        part += a[0] * bb[0] + a[1] * bb[1] + a[2] * bb[2] + a[3] * bb[3];
       }
     } else {
       for (int c = lane; c < D; c += 8) part += to_f32<T>(o[c]) * to_f32<T>(g[c]);
@@ -220,10 +223,38 @@ bwd_preprocess_kernel(const T* __restrict__ out, const T* __restrict__ dout, con
   part += __shfl_xor_sync(0xffffffffu, part, 4);
   part += __shfl_xor_sync(0xffffffffu, part, 2);
   part += __shfl_xor_sync(0xffffffffu, part, 1);
-  if (row < rows && lane == 0) {
+  if (ok && lane == 0) {
+    const int64_t row = static_cast<int64_t>(bh) * n_ctx + r;
     row_d[row] = part;
     row_lse[row] = row_m[row] + log2f(fmaxf(row_z[row], 1.0e-30f));
   }
+}
+
+int bwd_preprocess_any(const void* out, Strides os, const void* dout, Strides gs, const float* row_m, const float* row_z,
+                       float* row_d, float* row_lse, int dtype, int batch, int heads, int n_ctx, int head_dim,
+                       cudaStream_t st) {
+  if (!out || !dout || !row_m || !row_z || !row_d || !row_lse || !dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 ||
+      head_dim < 1 || head_dim > 128 || static_cast<int64_t>(batch) * heads > 65535)
+    return ELSA_ERR_INVALID_ARGUMENT;
+  if (n_ctx == 0) return ELSA_OK;
+  const int64_t all = os.b | os.h | os.r | gs.b | gs.h | gs.r;
+  const bool al16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
+  int vec_ok = 0;
+  if (dtype != ELSA_F32 && head_dim % 8 == 0 && al16 && all % 8 == 0) vec_ok = 2;
+  else if (head_dim % 4 == 0 && all % 4 == 0 && (dtype != ELSA_F32 || al16)) vec_ok = 1;
+  const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_ctx) * 8, 256)), static_cast<unsigned>(batch * heads));
+  if (dtype == ELSA_F32)
+    bwd_preprocess_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(dout),
+                                                       row_m, row_z, row_d, row_lse, heads, n_ctx, head_dim, os, gs, vec_ok);
+  else if (dtype == ELSA_F16)
+    bwd_preprocess_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(out), static_cast<const __half*>(dout),
+                                                        row_m, row_z, row_d, row_lse, heads, n_ctx, head_dim, os, gs, vec_ok);
+  else
+    bwd_preprocess_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(out),
+                                                               static_cast<const __nv_bfloat16*>(dout), row_m, row_z,
+                                                               row_d, row_lse, heads, n_ctx, head_dim, os, gs, vec_ok);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
 }
 
 }  // namespace elsa
@@ -233,25 +264,8 @@ using namespace elsa;
 extern "C" int elsa_bwd_preprocess(const void* out, const void* dout, const float* row_m, const float* row_z,
                                    float* row_d, float* row_lse, int dtype, int bh, int n_ctx, int head_dim,
                                    void* stream) {
-  if (!out || !dout || !row_m || !row_z || !row_d || !row_lse || !dtype_ok(dtype) || bh < 1 || n_ctx < 0 ||
-      head_dim < 1 || head_dim > 128)
-    return ELSA_ERR_INVALID_ARGUMENT;
-  if (n_ctx == 0) return ELSA_OK;
-  const int64_t rows = static_cast<int64_t>(bh) * n_ctx;
-  const unsigned blocks = static_cast<unsigned>(cdiv64(rows * 8, 256));
-  const bool al16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15u) == 0;
-  const int vec_ok = (dtype != ELSA_F32 && head_dim % 8 == 0 && al16) ? 2 : (head_dim % 4 == 0 ? 1 : 0);
-  auto st = static_cast<cudaStream_t>(stream);
-  if (dtype == ELSA_F32)
-    bwd_preprocess_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(dout),
-                                                         row_m, row_z, row_d, row_lse, rows, head_dim, vec_ok);
-  else if (dtype == ELSA_F16)
-    bwd_preprocess_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(out), static_cast<const __half*>(dout),
-                                                          row_m, row_z, row_d, row_lse, rows, head_dim, vec_ok);
-  else
-    bwd_preprocess_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(out),
-                                                                 static_cast<const __nv_bfloat16*>(dout), row_m, row_z,
-                                                                 row_d, row_lse, rows, head_dim, vec_ok);
-  ELSA_LAUNCH_CHECK();
-  return ELSA_OK;
+  if (bh < 1 || head_dim < 1) return ELSA_ERR_INVALID_ARGUMENT;
+  const Strides cs = contiguous_strides(1, n_ctx, head_dim);      // [bh, 1, n_ctx, head_dim]
+  return bwd_preprocess_any(out, cs, dout, cs, row_m, row_z, row_d, row_lse, dtype, bh, 1, n_ctx, head_dim,
+                            static_cast<cudaStream_t>(stream));
 }

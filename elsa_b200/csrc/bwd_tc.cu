@@ -70,8 +70,9 @@ enum BarId { BAR_KV = 11, BAR_Q_FULL = 12, BAR_Q_FREE = 13, BAR_SP = 14, BAR_PDS
 struct BwdTcParams {
   const float* nlse_pad; const float* nd_pad;  // [BH][n_pad]: -LSE, -D
   float* dq_acc;                               // [BH][N][64] fp32, zeroed by the caller
-  void* dk; void* dv;                          // [BH][n_keys][64] T
-  int n_ctx, n_pad, bh, is_causal;
+  void* dk; void* dv;                          // T, rows addressed through dks / dvs
+  Strides dks, dvs;
+  int n_ctx, n_pad, bh, heads, is_causal;
   int n_keys, key_offset;                      // K/V rows of this launch and the sequence index of the first one
   float scale, scale_log2;
   int* status;   // the device's status word (mapped host memory)
@@ -102,6 +103,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;
+  const int bi = bh / prm.heads, hi = bh - bi * prm.heads;   // tensor-map coordinates of this (batch*head)
   const int k0 = blockIdx.x * 128;                  // first (local) key row of this CTA
   const int N = prm.n_ctx, NK = prm.n_keys;
   const int kseq0 = k0 + prm.key_offset;            // its index in the sequence
@@ -163,23 +165,23 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       mbar_arrive_expect_tx(bar_kv, 2 * kTile);
-      tma_load_3d(sK, &tmap_k, bar_kv, 0, k0, bh);
-      tma_load_3d(sV, &tmap_v, bar_kv, 0, k0, bh);
+      tma_load_4d(sK, &tmap_k, bar_kv, 0, k0, hi, bi);
+      tma_load_4d(sV, &tmap_v, bar_kv, 0, k0, hi, bi);
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kQStages;
         // stage st held tile it-2: its dV / dK retired before the commit that announced dP^T of tile it-1
         if (it >= kQStages && !mbar_wait(bar_dpx((it - 1) & 1), ((it - 1) / 2) & 1, &abort_flag, prm.status, BAR_Q_FREE)) break;
         const int qrow = (it_begin + it) * 128;
         mbar_arrive_expect_tx(bar_q_full(st), kStageBytes);
-        tma_load_3d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, bh);
-        tma_load_3d(sDO(st), &tmap_do, bar_q_full(st), 0, qrow, bh);
+        tma_load_4d(sQ(st), &tmap_q, bar_q_full(st), 0, qrow, hi, bi);
+        tma_load_4d(sDO(st), &tmap_do, bar_q_full(st), 0, qrow, hi, bi);
         bulk_load_1d(sNL(st), prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
         bulk_load_1d(sND(st), prm.nd_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, kVecBytes, bar_q_full(st));
         // the ring is only one tile ahead of the tensor pipe: pull the tiles after it into L2 now, so that a first
         // touch (inputs that are not L2-resident) costs an L2 hit instead of a DRAM round trip when its turn comes
         if (it + kPrefetchAhead < n_it) {
-          tma_prefetch_l2_3d(&tmap_q, 0, qrow + kPrefetchAhead * 128, bh);
-          tma_prefetch_l2_3d(&tmap_do, 0, qrow + kPrefetchAhead * 128, bh);
+          tma_prefetch_l2_4d(&tmap_q, 0, qrow + kPrefetchAhead * 128, hi, bi);
+          tma_prefetch_l2_4d(&tmap_do, 0, qrow + kPrefetchAhead * 128, hi, bi);
         }
       }
     } else if (warp == 13 && lane == 0) {
@@ -434,8 +436,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         for (int i = 0; i < 32; ++i) { rk[i] = 0u; rv[i] = 0u; }   // no query sees these keys: zero gradients
       }
       if (key_ok) {
-        T* dk_row = static_cast<T*>(prm.dk) + (static_cast<int64_t>(bh) * NK + key) * 64 + half * 32;
-        T* dv_row = static_cast<T*>(prm.dv) + (static_cast<int64_t>(bh) * NK + key) * 64 + half * 32;
+        T* dk_row = static_cast<T*>(prm.dk) + bi * prm.dks.b + hi * prm.dks.h + key * prm.dks.r + half * 32;
+        T* dv_row = static_cast<T*>(prm.dv) + bi * prm.dvs.b + hi * prm.dvs.h + key * prm.dvs.r + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           uint4 a, b;
@@ -464,7 +466,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
                           const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
-                          int bh, int n_ctx, int n_pad) {
+                          int heads, int n_ctx, int n_pad, Strides os, Strides gs) {
   // blockIdx.y = (batch*head); x covers the n_pad padded rows, 8 lanes (16 bytes each) per row: no division
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = static_cast<int>(gid >> 3);        // padded row within this (batch*head)
@@ -475,8 +477,9 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   const bool real = in_pad && r < n_ctx;
   float part = 0.f;
   if (real) {
-    const T* o = out + (b * n_ctx + r) * 64 + lane * 8;
-    const T* g = dout + (b * n_ctx + r) * 64 + lane * 8;
+    const int bi = static_cast<int>(b) / heads, hi = static_cast<int>(b) - bi * heads;
+    const T* o = out + bi * os.b + hi * os.h + static_cast<int64_t>(r) * os.r + lane * 8;
+    const T* g = dout + bi * gs.b + hi * gs.h + static_cast<int64_t>(r) * gs.r + lane * 8;
     uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
     const T* oe = reinterpret_cast<const T*>(&ov);
     const T* ge = reinterpret_cast<const T*>(&gv);
@@ -506,18 +509,21 @@ __global__ void __launch_bounds__(256) dq_scale_kernel(float* __restrict__ acc, 
   *reinterpret_cast<float4*>(acc + i * 4) = a;
 }
 
-// dq = T(acc * scale)
+// dq = T(acc * scale); acc is [BH][N][64] fp32, dq rows are addressed through their strides (blockIdx.y = batch*head)
 template <typename T>
 __global__ void __launch_bounds__(256)
-dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int64_t n_vec8, float scale) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= n_vec8) return;
-  const float4 a = *reinterpret_cast<const float4*>(acc + i * 8);
-  const float4 b = *reinterpret_cast<const float4*>(acc + i * 8 + 4);
+dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int n_ctx, int heads, Strides ds, float scale) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;        // 8 elements each: row = i / 8
+  const int r = static_cast<int>(i >> 3), c = static_cast<int>(i & 7) * 8;
+  if (r >= n_ctx) return;
+  const int bh = blockIdx.y, bi = bh / heads, hi = bh - bi * heads;
+  const float* src = acc + (static_cast<int64_t>(bh) * n_ctx + r) * 64 + c;
+  const float4 a = *reinterpret_cast<const float4*>(src);
+  const float4 b = *reinterpret_cast<const float4*>(src + 4);
   uint4 o;
   o.x = pack2<T>(a.x * scale, a.y * scale); o.y = pack2<T>(a.z * scale, a.w * scale);
   o.z = pack2<T>(b.x * scale, b.y * scale); o.w = pack2<T>(b.z * scale, b.w * scale);
-  *reinterpret_cast<uint4*>(dq + i * 8) = o;
+  *reinterpret_cast<uint4*>(dq + bi * ds.b + hi * ds.h + static_cast<int64_t>(r) * ds.r + c) = o;
 }
 
 }  // namespace
@@ -530,8 +536,8 @@ int64_t bwd_tc_workspace_bytes(int bh, int n_ctx) {
 }
 
 template <typename T>
-static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, const float* row_z, void* workspace,
-                    int dtype, cudaStream_t st) {
+static int bwd_tc_t(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z,
+                    void* workspace, int dtype, cudaStream_t st) {
   const int N = p.n_ctx, NK = p.n_keys, bh = p.bh;
   const int n_pad = static_cast<int>(align_up(N, 128));
   const int64_t vec_bytes = align_up(static_cast<int64_t>(bh) * n_pad * 4, 256);
@@ -545,7 +551,7 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   {
     const dim3 pgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_pad) * 8, 256)), static_cast<unsigned>(bh));
     bwd_preprocess_pad_kernel<T><<<pgrid, 256, 0, st>>>(
-        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, bh, N, n_pad);
+        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, p.heads, N, n_pad, os, p.gs);
     ELSA_LAUNCH_CHECK();
   }
   ELSA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, acc_elems * 4, st));
@@ -553,14 +559,16 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   CUtensorMap mq, mk, mv, mdo, mdq;
   int rc;
   if ((rc = make_tmap_f32_rows64(&mdq, dq_acc, N, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, NK, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, bh, 128)) != ELSA_OK) return rc;
+  const int batch = bh / p.heads;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, p.heads, batch, p.qs, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, NK, p.heads, batch, p.ks, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, p.heads, batch, p.vs, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, p.heads, batch, p.gs, 128)) != ELSA_OK) return rc;
   BwdTcParams prm;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
-  prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.is_causal = p.is_causal;
+  prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
+  prm.dks = p.dks; prm.dvs = p.dvs;
   prm.n_keys = NK; prm.key_offset = p.key_offset;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_tc_kernel<T>), kBwdSmem);
@@ -573,18 +581,18 @@ static int bwd_tc_t(const BwdParams& p, const void* out, const float* row_m, con
   if (p.dq_f32) {
     dq_scale_kernel<<<static_cast<unsigned>(cdiv64(acc_elems / 4, 256)), 256, 0, st>>>(dq_acc, acc_elems / 4, p.scale);
   } else {
-    dq_convert_kernel<T><<<static_cast<unsigned>(cdiv64(acc_elems / 8, 256)), 256, 0, st>>>(
-        dq_acc, static_cast<T*>(p.dq), acc_elems / 8, p.scale);
+    const dim3 cgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(N) * 8, 256)), static_cast<unsigned>(bh));
+    dq_convert_kernel<T><<<cgrid, 256, 0, st>>>(dq_acc, static_cast<T*>(p.dq), N, p.heads, p.dqs, p.scale);
   }
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }
 
-int bwd_tc(const BwdParams& p, const void* out, const float* row_m, const float* row_z, void* workspace, int dtype,
-           cudaStream_t st) {
+int bwd_tc(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
+           int dtype, cudaStream_t st) {
   if (!bwd_tc_supported(dtype, p.head_dim, p.bias != nullptr) || p.dbias) return ELSA_ERR_UNSUPPORTED;
-  if (dtype == ELSA_F16) return bwd_tc_t<__half>(p, out, row_m, row_z, workspace, dtype, st);
-  return bwd_tc_t<__nv_bfloat16>(p, out, row_m, row_z, workspace, dtype, st);
+  if (dtype == ELSA_F16) return bwd_tc_t<__half>(p, out, os, row_m, row_z, workspace, dtype, st);
+  return bwd_tc_t<__nv_bfloat16>(p, out, os, row_m, row_z, workspace, dtype, st);
 }
 
 

@@ -35,17 +35,17 @@ fold_simt_kernel(const FoldParams prm) {
   int k_end = min(prm.n_keys, k_begin + prm.part_width);
   if (prm.is_causal) k_end = min(k_end, q0 + rows_valid - koff);  // keys beyond the tile's last row are masked for every row
 
-  const T* qb = static_cast<const T*>(prm.q) + static_cast<int64_t>(bh) * N * D;
-  const T* kb = static_cast<const T*>(prm.k) + static_cast<int64_t>(bh) * prm.n_keys * D;
-  const T* vb = static_cast<const T*>(prm.v) + static_cast<int64_t>(bh) * prm.n_keys * D;
-  const bool vec_ok = (D % 4) == 0;
+  const int b = bh / prm.heads, h = bh - b * prm.heads;
+  const T* qb = static_cast<const T*>(prm.q) + b * prm.qs.b + h * prm.qs.h;
+  const T* kb = static_cast<const T*>(prm.k) + b * prm.ks.b + h * prm.ks.h;
+  const T* vb = static_cast<const T*>(prm.v) + b * prm.vs.b + h * prm.vs.h;
+  // vector loads need every row start on a vector boundary (the host only passes such strides with D % 4 == 0)
+  const bool vec_ok = (D % 4) == 0 && ((prm.qs.r | prm.ks.r | prm.vs.r | prm.qs.h | prm.ks.h | prm.vs.h | prm.qs.b | prm.ks.b | prm.vs.b) % 4) == 0;
   const float* bias_bh = nullptr;
-  if (prm.bias) {
-    const int b = bh / prm.heads, h = bh - b * prm.heads;
-    bias_bh = prm.bias + b * prm.bsb + h * prm.bsh;
-  }
+  if (prm.bias) bias_bh = prm.bias + b * prm.bsb + h * prm.bsh;
+  (void)N;
 
-  load_tile<T, DP>(Qs, LD, qb + static_cast<int64_t>(q0) * D, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(Qs, LD, qb + static_cast<int64_t>(q0) * prm.qs.r, prm.qs.r, rows_valid, D, vec_ok, tid);
 
   float m_run[4], z_part[4], acc[4][CPT];
 #pragma unroll
@@ -59,8 +59,8 @@ fold_simt_kernel(const FoldParams prm) {
   for (int k0 = k_begin; k0 < k_end; k0 += 64) {
     __syncthreads();  // previous tile's PV has finished reading V and P
     const int kv = min(64, k_end - k0);
-    load_tile<T, DP>(Ks, LD, kb + static_cast<int64_t>(k0) * D, kv, D, vec_ok, tid);
-    load_tile<T, DP>(Vs, DP, vb + static_cast<int64_t>(k0) * D, kv, D, vec_ok, tid);
+    load_tile<T, DP>(Ks, LD, kb + static_cast<int64_t>(k0) * prm.ks.r, prm.ks.r, kv, D, vec_ok, tid);
+    load_tile<T, DP>(Vs, DP, vb + static_cast<int64_t>(k0) * prm.vs.r, prm.vs.r, kv, D, vec_ok, tid);
     __syncthreads();
 
     float S[4][4];

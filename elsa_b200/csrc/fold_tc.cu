@@ -50,7 +50,7 @@ enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, 
 
 struct FoldTcParams {
   float* m; float* z; void* s;
-  int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
+  int n_ctx, q_start, q_len, part_width, n_parts, bh, heads, is_causal, summary_dtype;
   int n_keys, key_offset;
   float scale_log2;
   int* status;   // the device's status word (mapped host memory)
@@ -89,6 +89,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.z, part = blockIdx.y;
+  const int bi = bh / prm.heads, hi = bh - bi * prm.heads;  // tensor-map coordinates of this (batch*head)
   const int q0 = prm.q_start + blockIdx.x * 256;           // first query row of tile 0
   const int q_end = prm.q_start + prm.q_len;
   const int k_begin = part * prm.part_width;
@@ -154,14 +155,14 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (lane == 0) {
         prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
         mbar_arrive_expect_tx(bar_q, 2 * kTileBytes);
-        tma_load_3d(sQ[0], &tmap_q, bar_q, 0, q0, bh);
-        tma_load_3d(sQ[1], &tmap_q, bar_q, 0, q0 + 128, bh);
+        tma_load_4d(sQ[0], &tmap_q, bar_q, 0, q0, hi, bi);
+        tma_load_4d(sQ[1], &tmap_q, bar_q, 0, q0 + 128, hi, bi);
         for (int j = 0; j < n_max; ++j) {
           const int st = j % kStages;
           if (j >= kStages && !mbar_wait(bar_kv_free(st), ((j / kStages) - 1) & 1, &abort_flag, prm.status, BAR_KV_FREE)) break;
           mbar_arrive_expect_tx(bar_kv_full(st), 2 * kTileBytes);
-          tma_load_3d(sK(st), &tmap_k, bar_kv_full(st), 0, k_begin + j * 128, bh);
-          tma_load_3d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, bh);
+          tma_load_4d(sK(st), &tmap_k, bar_kv_full(st), 0, k_begin + j * 128, hi, bi);
+          tma_load_4d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, hi, bi);
         }
       }
     } else if (n_max > 0 && warp == kIssuerWarp) {
@@ -411,15 +412,19 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int64_t n_mats, int box_rows) {
+int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
+                     int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ELSA_ERR_UNSUPPORTED;
-  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(n_mats)};
-  const cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(n_rows) * 128};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
+  if ((st.b | st.h | st.r) % 8 != 0 || st.r < 64 || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // a size-1 axis may come with any stride (PyTorch reports arbitrary ones): give it a valid dummy
+  const cuuint64_t sh = heads > 1 ? static_cast<cuuint64_t>(st.h) * 2 : 128, sb = batch > 1 ? static_cast<cuuint64_t>(st.b) * 2 : 128;
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st.r) * 2, sh, sb};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == ELSA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
@@ -453,15 +458,16 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   if (!fold_tc_supported(dtype, p.head_dim, p.bias != nullptr) || p.part_width % 128 != 0) return ELSA_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_keys, p.bh, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_keys, p.bh, 128)) != ELSA_OK) return rc;
+  const int batch = p.bh / p.heads;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.heads, batch, p.qs, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_keys, p.heads, batch, p.ks, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_keys, p.heads, batch, p.vs, 128)) != ELSA_OK) return rc;
   FoldTcParams prm;
   prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
-  prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
+  prm.n_parts = p.n_parts; prm.bh = p.bh; prm.heads = p.heads; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
   prm.scale_log2 = p.scale_log2;
   dim3 grid(static_cast<unsigned>((p.q_len + 255) / 256), static_cast<unsigned>(p.n_parts), static_cast<unsigned>(p.bh));
   if (dtype == ELSA_F16) {

@@ -9,8 +9,15 @@
 
 namespace elsa {
 
+// Element strides of the batch, head and row axes of a [B, H, rows, D] view; the D axis is contiguous.
+struct Strides { int64_t b, h, r; };
+inline Strides contiguous_strides(int heads, int64_t rows, int d) {
+  return Strides{static_cast<int64_t>(heads) * rows * d, rows * d, static_cast<int64_t>(d)};
+}
+
 struct FoldParams {
   const void* q; const void* k; const void* v;
+  Strides qs, ks, vs;
   const float* bias; int64_t bsb, bsh, bsq, bsk;
   float* m; float* z; void* s;
   int heads, n_ctx, head_dim, q_start, q_len, part_width, n_parts, bh;
@@ -21,6 +28,8 @@ struct FoldParams {
 
 struct BwdParams {
   const void* q; const void* k; const void* v; const void* dout;
+  Strides qs, ks, vs, gs;          // q, k, v, dout
+  Strides dqs, dks, dvs;           // dq (ignored when dq_f32: the fp32 partial is always contiguous), dk, dv
   const float* lse; const float* drow;
   const float* bias; int64_t bsb, bsh, bsq, bsk;
   void* dq; void* dk; void* dv;
@@ -56,16 +65,24 @@ int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
 // tcgen05 backward (bwd_tc.cu); workspace = padded D / LSE vectors + fp32 dQ accumulator
 bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc_workspace_bytes(int bh, int n_ctx);
-int bwd_tc(const BwdParams& p, const void* out, const float* row_m, const float* row_z, void* workspace, int dtype,
-           cudaStream_t st);
+int bwd_tc(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
+           int dtype, cudaStream_t st);
+// D, LSE from out, dout (any strides) and the row state (bwd_simt.cu)
+int bwd_preprocess_any(const void* out, Strides os, const void* dout, Strides gs, const float* row_m, const float* row_z,
+                       float* row_d, float* row_lse, int dtype, int batch, int heads, int n_ctx, int head_dim, cudaStream_t st);
 
 // FP32-FMA kernels (fold_simt.cu, bwd_simt.cu)
 int fold_simt(const FoldParams& p, int dtype, cudaStream_t st);
 int bwd_simt(const BwdParams& p, int dtype, cudaStream_t st);
 
+// q' = fp16(q * fp16(c)), the product formed in fp16 (phase2.cu)
+int prescale_q_f16(const void* q, void* q_scaled, int64_t n_elems, float c, cudaStream_t st);
+
 // phase 2 (phase2.cu)
+// out_strides == nullptr: out is [bh, n_ctx, head_dim] contiguous; else `heads` splits bh and out is addressed by strides
 int merge_final_any(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                     int summary_dtype, int out_dtype, int n_parts, int bh, int q_start, int q_len, int n_ctx,
-                    int head_dim, int first_part, int store_state, cudaStream_t st, int normalize = 1);
+                    int head_dim, int first_part, int store_state, cudaStream_t st, int normalize = 1,
+                    int heads = 1, const Strides* out_strides = nullptr);
 
 }  // namespace elsa

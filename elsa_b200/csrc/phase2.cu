@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256)
 merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, const TS* __restrict__ s,
                    TO* __restrict__ out, float* __restrict__ row_m, float* __restrict__ row_z,
                    int n_parts, int64_t rows, int q_len, int q_start, int n_ctx, int head_dim,
-                   int chunks, int chunk_shift, int first_part, int store_state, int normalize) {
+                   int chunks, int chunk_shift, int first_part, int store_state, int normalize, int heads, Strides os) {
   const RowChunk rc = row_chunk(q_len, chunks, chunk_shift);
   if (!rc.ok) return;
   const int64_t row = rc.row;
@@ -93,18 +93,33 @@ merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, con
   const TS* sp = s + (static_cast<int64_t>(first_part) * rows + row) * head_dim + c * NV;
   const float* mp = m + static_cast<int64_t>(first_part) * rows + row;
   const float* zp = z + static_cast<int64_t>(first_part) * rows + row;
-#pragma unroll 4
-  for (int p = 0; p < n_parts; ++p) {
-    float sv[NV];
-    load_vec<TS, NV>(sp + static_cast<int64_t>(p) * rows * head_dim, sv);
-    monoid_merge<NV>(M, Z, acc, mp[static_cast<int64_t>(p) * rows], zp[static_cast<int64_t>(p) * rows], sv);
+  // four partitions per round: all loads of a round are issued before the first merge needs its data, so that a
+  // thread keeps up to 64 bytes of s in flight (short plans have only two or three partitions to hide latency with)
+  for (int p0 = 0; p0 < n_parts; p0 += 4) {
+    float sv[4][NV], mv[4], zv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (p0 + u < n_parts) {
+        const int64_t po = static_cast<int64_t>(p0 + u) * rows;
+        load_vec<TS, NV>(sp + po * head_dim, sv[u]);
+        mv[u] = mp[po];
+        zv[u] = zp[po];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (p0 + u < n_parts) monoid_merge<NV>(M, Z, acc, mv[u], zv[u], sv[u]);
   }
   const int64_t orow = static_cast<int64_t>(blockIdx.y) * n_ctx + q_start + rc.r;
   const float inv = normalize ? (Z > 0.f ? 1.0f / Z : 0.f) : 1.0f;   // normalize == 0: emit the merged, un-normalised s
   float o[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) o[i] = Z > 0.f ? acc[i] * inv : 0.f;
-  store_vec<TO, NV>(out + orow * head_dim + c * NV, o);
+  // heads == 0: out is [BH][n_ctx][head_dim] contiguous; else rows are addressed through the strides
+  const int bh_i = blockIdx.y;
+  const int64_t ooff = heads == 0 ? orow * head_dim
+                                  : (bh_i / heads) * os.b + (bh_i % heads) * os.h + static_cast<int64_t>(q_start + rc.r) * os.r;
+  store_vec<TO, NV>(out + ooff + c * NV, o);
   if (store_state && c == 0) {
     row_m[orow] = Z > 0.f ? M : -CUDART_INF_F;
     row_z[orow] = Z;
@@ -239,7 +254,7 @@ static inline int pick_nv(int head_dim, int elem_bytes_a, int elem_bytes_b) {
 template <typename TS, typename TO>
 static int launch_merge_final(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                               int n_parts, int bh, int q_start, int q_len, int n_ctx, int head_dim,
-                              int first_part, int store_state, cudaStream_t st, int normalize) {
+                              int first_part, int store_state, cudaStream_t st, int normalize, int heads, Strides os) {
   const int64_t rows = static_cast<int64_t>(bh) * q_len;
   const int nv = pick_nv(head_dim, sizeof(TS), sizeof(TO));
   const int chunks = head_dim / nv;
@@ -248,7 +263,7 @@ static int launch_merge_final(const float* m, const float* z, const void* s, voi
   auto ts = static_cast<const TS*>(s);
   auto to = static_cast<TO*>(out);
 #define ELSA_MF(NV) merge_final_kernel<TS, TO, NV><<<blocks, 256, 0, st>>>(m, z, ts, to, row_m, row_z, n_parts, rows, \
-                                                   q_len, q_start, n_ctx, head_dim, chunks, cs, first_part, store_state, normalize)
+                                                   q_len, q_start, n_ctx, head_dim, chunks, cs, first_part, store_state, normalize, heads, os)
   if (nv == 8) ELSA_MF(8); else if (nv == 4) ELSA_MF(4); else ELSA_MF(1);
 #undef ELSA_MF
   ELSA_LAUNCH_CHECK();
@@ -257,7 +272,11 @@ static int launch_merge_final(const float* m, const float* z, const void* s, voi
 
 int merge_final_any(const float* m, const float* z, const void* s, void* out, float* row_m, float* row_z,
                            int summary_dtype, int out_dtype, int n_parts, int bh, int q_start, int q_len, int n_ctx,
-                           int head_dim, int first_part, int store_state, cudaStream_t st, int normalize) {
+                           int head_dim, int first_part, int store_state, cudaStream_t st, int normalize, int heads,
+                           const Strides* out_strides) {
+  const int heads_k = out_strides ? heads : 0;
+  const Strides os = out_strides ? *out_strides : Strides{0, 0, 0};
+  if (out_strides && (heads < 1 || bh % heads != 0)) return ELSA_ERR_INVALID_ARGUMENT;
   if (!dtype_ok(summary_dtype) || !dtype_ok(out_dtype)) return ELSA_ERR_INVALID_ARGUMENT;
   if (!m || !z || !s || !out || n_parts < 1 || bh < 1 || q_len < 0 || head_dim < 1 || head_dim > 128 ||
       q_start < 0 || q_start + q_len > n_ctx || first_part < 0)
@@ -267,7 +286,7 @@ int merge_final_any(const float* m, const float* z, const void* s, void* out, fl
 #define ELSA_CASE(SD, OD, TS, TO)                 \
   if (summary_dtype == SD && out_dtype == OD)     \
     return launch_merge_final<TS, TO>(m, z, s, out, row_m, row_z, n_parts, bh, q_start, q_len, n_ctx, head_dim, \
-                                      first_part, store_state, st, normalize)
+                                      first_part, store_state, st, normalize, heads_k, os)
   ELSA_CASE(ELSA_F32, ELSA_F32, float, float);
   ELSA_CASE(ELSA_F16, ELSA_F16, __half, __half);
   ELSA_CASE(ELSA_BF16, ELSA_BF16, __nv_bfloat16, __nv_bfloat16);
@@ -315,6 +334,27 @@ static int launch_prefix(const float* m_in, const float* z_in, const void* s_in,
                                                                      q_len, head_dim, chunks, cs)
   if (nv == 8) ELSA_PS(8); else if (nv == 4) ELSA_PS(4); else ELSA_PS(1);
 #undef ELSA_PS
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+// q' = q * c with c rounded to fp16 and the product formed and rounded in fp16 (8 elements per thread)
+__global__ void __launch_bounds__(256) prescale_q_f16_kernel(const uint4* __restrict__ q, uint4* __restrict__ o, int64_t n_vec, __half c) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  uint4 v = q[i];
+  __half2* h = reinterpret_cast<__half2*>(&v);
+  const __half2 c2 = __half2half2(c);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __hmul2(h[j], c2);
+  o[i] = v;
+}
+
+int prescale_q_f16(const void* q, void* q_scaled, int64_t n_elems, float c, cudaStream_t st) {
+  if (n_elems % 8 != 0) return ELSA_ERR_INVALID_ARGUMENT;
+  const int64_t n_vec = n_elems / 8;
+  prescale_q_f16_kernel<<<static_cast<unsigned>(cdiv64(n_vec, 256)), 256, 0, st>>>(
+      static_cast<const uint4*>(q), static_cast<uint4*>(q_scaled), n_vec, __float2half_rn(c));
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }

@@ -7,10 +7,11 @@
 
 namespace elsa {
 
-// global [rows][D] of T  ->  shared fp32 [64][ld], zero-filled beyond rows_valid and beyond D
+// global rows of D elements of T, `src_ld` elements apart  ->  shared fp32 [64][ld], zero-filled beyond rows_valid
+// and beyond D
 template <typename T, int DP>
-__device__ __forceinline__ void load_tile(float* __restrict__ dst, int ld, const T* __restrict__ src, int rows_valid,
-                                          int D, bool vec_ok, int tid) {
+__device__ __forceinline__ void load_tile(float* __restrict__ dst, int ld, const T* __restrict__ src, int64_t src_ld,
+                                          int rows_valid, int D, bool vec_ok, int tid) {
   constexpr int C4 = DP / 4;
 #pragma unroll 2
   for (int idx = tid; idx < 64 * C4; idx += 256) {
@@ -18,7 +19,7 @@ __device__ __forceinline__ void load_tile(float* __restrict__ dst, int ld, const
     const int c = (idx - r * C4) * 4;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (r < rows_valid) {
-      const T* p = src + static_cast<int64_t>(r) * D + c;
+      const T* p = src + static_cast<int64_t>(r) * src_ld + c;
       if (vec_ok && c + 3 < D) {
         Vec4<T>::load(p, v);
       } else {

@@ -75,18 +75,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 3-D tiled load global -> shared, completion counted in bytes on `bar`; x is the innermost
-// coordinate and must make x*elem_size a multiple of 16 bytes (always 0 here).
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z) {
+// 4-D tiled load global -> shared, completion counted in bytes on `bar`.  Coordinates, innermost first:
+// x = element within the row (must make x*elem_size a multiple of 16 bytes; always 0 here), row, head, batch.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int row, int h, int b) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(row), "r"(h), "r"(b)
       : "memory");
 }
-// 3-D tiled prefetch global -> L2 (no shared-memory destination, no completion to wait for)
-__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z) : "memory");
+// 4-D tiled prefetch global -> L2 (no shared-memory destination, no completion to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* m, int x, int row, int h, int b) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(row), "r"(h), "r"(b) : "memory");
 }
 // 3-D tiled reduction shared -> global: global[tile] += smem tile (element type and add come from the tensor
 // map / the .add qualifier); tracked by the thread's bulk async-group.  Coordinates out of range are skipped.
@@ -262,9 +262,11 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 }  // namespace tc
 
 // ---- host side: tensor maps -------------------------------------------------------------------
-// [BH][N][64] 16-bit tensor seen as a 3-D map (innermost first: 64, N, BH), box 64 x box_rows x 1,
-// 128-byte swizzle, out-of-range rows read as zeros.
-int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int64_t n_mats, int box_rows);
+// 16-bit [B, H, n_rows, 64] view with element strides `st` (the 64 elements of a row contiguous) as a 4-D map
+// (innermost first: 64, n_rows, H, B), box 64 x box_rows x 1 x 1, 128-byte swizzle, out-of-range rows read as zeros.
+// The strides must be multiples of 8 elements (16 bytes) and the base 16-byte aligned.
+int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
+                     int box_rows);
 // [n_mats][n_rows][64] fp32 tensor, box 32 x box_rows x 1 (two boxes cover the 64 columns), 128-byte swizzle
 int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int64_t n_mats, int box_rows);
 

@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from .attention import twopass_attention
-from .attention_bwd import twopass_attention_train
+from .attention_bwd import twopass_attention_qkvpacked, twopass_attention_train
 
 _VIT_ATTRS = ("qkv", "q_norm", "k_norm", "proj", "num_heads", "head_dim")
 _SWIN_ATTRS = ("qkv", "proj", "relative_position_bias_table", "relative_position_index", "window_area",
@@ -75,10 +75,17 @@ class _VitAttentionBase(nn.Module):
         if self._training_op and self.training and getattr(self.attn_drop, "p", 0.0):
             raise ValueError("ELSA ViT bwd drop-in does not implement attention dropout")
         batch, seq_len, _ = x.shape
-        q, k, v = _split_heads(self.qkv(x), (batch, seq_len), self.num_heads, self.head_dim)
-        q, k = self.q_norm(q), self.k_norm(k)
-        op: Callable = twopass_attention_train if self._training_op else twopass_attention
-        y = op(q, k, v, **self._op_kwargs(seq_len, q.dtype))
+        qkv = self.qkv(x)
+        if isinstance(self.q_norm, nn.Identity) and isinstance(self.k_norm, nn.Identity):
+            # q, k, v are read in place from the projection output and the result comes back in [B, N, H, d] memory:
+            # no per-layer copies on either side of the operator (the reference makes one, timm_dropin.py:46-51)
+            y = twopass_attention_qkvpacked(qkv.view(batch, seq_len, 3, self.num_heads, self.head_dim),
+                                            train=self._training_op, **self._op_kwargs(seq_len, qkv.dtype))
+        else:
+            q, k, v = _split_heads(qkv, (batch, seq_len), self.num_heads, self.head_dim)
+            q, k = self.q_norm(q), self.k_norm(k)
+            op: Callable = twopass_attention_train if self._training_op else twopass_attention
+            y = op(q, k, v, **self._op_kwargs(seq_len, q.dtype))
         y = y.transpose(1, 2).reshape(batch, seq_len, self.attn_dim)
         return self.proj_drop(self.proj(self.norm(y)))
 
@@ -138,9 +145,11 @@ class _SwinWindowAttentionBase(nn.Module):
                              if self._training_op else
                              "ELSA Swin drop-in forward is inference-only when attention dropout is nonzero")
         windows, seq_len, _ = x.shape
-        q, k, v = _split_heads(self.qkv(x), (windows, seq_len), self.num_heads, self.head_dim)
+        qkv = self.qkv(x)
         canonical = self.head_dim ** -0.5
-        if abs(self.scale - canonical) > 1e-12:
+        packed = abs(self.scale - canonical) <= 1e-12
+        if not packed:
+            q, k, v = _split_heads(qkv, (windows, seq_len), self.num_heads, self.head_dim)
             q = q * (self.scale / canonical)
         bias = self._get_rel_pos_bias()
         if mask is not None:
@@ -148,8 +157,12 @@ class _SwinWindowAttentionBase(nn.Module):
             n_win = int(mask.shape[0])
             tiled = mask.view(1, n_win, 1, seq_len, seq_len).expand(windows // n_win, -1, self.num_heads, -1, -1)
             bias = bias + tiled.reshape(-1, self.num_heads, seq_len, seq_len)
-        op: Callable = twopass_attention_train if self._training_op else twopass_attention
-        y = op(q, k, v, bias=bias, **self._elsa_kwargs_for_window(seq_len))
+        if packed:
+            y = twopass_attention_qkvpacked(qkv.view(windows, seq_len, 3, self.num_heads, self.head_dim), bias=bias,
+                                            train=self._training_op, **self._elsa_kwargs_for_window(seq_len))
+        else:
+            op: Callable = twopass_attention_train if self._training_op else twopass_attention
+            y = op(q, k, v, bias=bias, **self._elsa_kwargs_for_window(seq_len))
         y = y.transpose(1, 2).reshape(windows, seq_len, self.attn_dim)
         return self.proj_drop(self.proj(y))
 

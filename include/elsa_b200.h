@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define ELSA_B200_ABI_VERSION 1
+#define ELSA_B200_ABI_VERSION 2
 
 enum elsa_dtype { ELSA_F32 = 0, ELSA_F16 = 1, ELSA_BF16 = 2 };
 
@@ -48,6 +48,10 @@ enum elsa_status {
 #define ELSA_FLAG_FORCE_SIMT 1u   /* never take the tcgen05 kernels (debug / A-B checks) */
 #define ELSA_FLAG_SCAN_STEPS 2u   /* causal: run the log-depth Hillis-Steele steps instead of the one-pass merge */
 #define ELSA_FLAG_TREE_MERGE 4u   /* non-causal: run the Blelloch up-sweep levels instead of the one-pass merge */
+#define ELSA_FLAG_REF_ROUNDING 8u /* forward, fp16 / head dim 64 / no bias / not causal only: reproduce the rounding points of
+                                     the reference's fp16 d=64 kernels (q * log2(e)/8 formed in fp16, scores unscaled:
+                                     attention_parallel_scan.py:153-154,160) instead of the exact fp32 scale; the workspace
+                                     grows by one fp16 copy of q (elsa_forward_workspace_bytes accounts for it) */
 
 int elsa_abi_version(void);
 const char* elsa_strerror(int status);
@@ -189,6 +193,22 @@ int elsa_twopass_forward(const void* q, const void* k, const void* v,
                          int dtype, int summary_dtype,
                          int batch, int heads, int n_ctx, int head_dim,
                          int is_causal, int part_width, int q_chunk, unsigned flags, void* stream);
+/* The same forward on strided [B, H, N, D] VIEWS: every tensor comes with three element strides {batch, head, row}
+ * (the D axis contiguous), e.g. q, k, v read in place from a packed [B, N, 3, H, D] projection output
+ * (strides {3*N*H*D, D, 3*H*D}) and out written as [B, N, H*D] (strides {N*H*D, D, H*D}).  This removes the
+ * `.contiguous()` copies the reference's hooks make before the call and the transpose after it
+ * (src/elsa_twopass_clean/timm_dropin.py:46-55, timm_dropin_bwd.py:68-73).  Every stride must be a multiple of 8
+ * elements and every base pointer 16-byte aligned (ELSA_ERR_INVALID_ARGUMENT otherwise: copy first).
+ * row_m / row_z stay [B*H, N] contiguous.  ELSA_FLAG_REF_ROUNDING is not available here (ELSA_ERR_UNSUPPORTED). */
+int elsa_twopass_forward_strided(const void* q, const void* k, const void* v,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                                 int64_t bias_stride_q, int64_t bias_stride_k,
+                                 void* out, const int64_t* out_strides, float* row_m, float* row_z,
+                                 void* workspace, int64_t workspace_bytes,
+                                 int dtype, int summary_dtype,
+                                 int batch, int heads, int n_ctx, int head_dim,
+                                 int is_causal, int part_width, int q_chunk, unsigned flags, void* stream);
 /* how the forward above splits the work: fills part_width, n_parts, q_chunk (all may be NULL) */
 int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
                       int has_bias, int is_causal, int part_width_in, int q_chunk_in, unsigned flags,
@@ -242,7 +262,8 @@ int elsa_row_stats(const void* q, const void* k,
  * (attention_bwd.py:188-224, 309-412, 415-527, 529-624) made by `twopass_attention_backward`
  * and `_dense_bias_backward` (attention_bwd.py:765-838, 939-970).
  * dbias is fp32, addressed with the dbias_stride_* like bias; where a stride is 0 the
- * contributions of that axis are summed (atomically) -- the caller zeroes dbias first.
+ * contributions of that axis are summed (atomically).  The caller ALWAYS zeroes dbias before the call: besides
+ * the sums, entries of pairs that the causal rule or the sequence length excludes are never written.
  * workspace: elsa_backward_workspace_bytes (row_d, row_lse, and the fp32 dQ accumulator of the
  * tensor-core path). */
 int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
@@ -257,6 +278,21 @@ int elsa_twopass_backward(const void* q, const void* k, const void* v, const voi
                           void* workspace, int64_t workspace_bytes,
                           int dtype, int batch, int heads, int n_ctx, int head_dim,
                           int is_causal, unsigned flags, void* stream);
+
+/* The same backward on strided [B, H, N, D] views.  `strides` holds 8 x 3 element strides {batch, head, row}, in the
+ * order q, k, v, out, dout, dq, dk, dv: dq, dk, dv may be the three slices of one packed [B, N, 3, H, D] gradient,
+ * dout the [B, N, H*D] gradient of the projection input.  Same rules as elsa_twopass_forward_strided. */
+int elsa_twopass_backward_strided(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                  const int64_t* strides,
+                                  const float* row_m, const float* row_z,
+                                  const float* bias, int64_t bias_stride_b, int64_t bias_stride_h,
+                                  int64_t bias_stride_q, int64_t bias_stride_k,
+                                  void* dq, void* dk, void* dv,
+                                  float* dbias, int64_t dbias_stride_b, int64_t dbias_stride_h,
+                                  int64_t dbias_stride_q, int64_t dbias_stride_k,
+                                  void* workspace, int64_t workspace_bytes,
+                                  int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                  int is_causal, unsigned flags, void* stream);
 
 /* Backward of ONE sequence shard (the K/V partitioning of the two-pass formulation, README.md:27-29,
  * carried across GPUs; the reference itself is single-GPU and has no counterpart).

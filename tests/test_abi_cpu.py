@@ -36,7 +36,7 @@ def test_binding_covers_header(lib):
 
 
 def test_version_and_strerror(lib):
-    assert lib.elsa_abi_version() == 1
+    assert lib.elsa_abi_version() == 2
     assert lib.elsa_strerror(0) == b"ok"
     assert b"workspace" in lib.elsa_strerror(4)
     assert b"unknown" in lib.elsa_strerror(99)

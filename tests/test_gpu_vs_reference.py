@@ -196,6 +196,17 @@ def test_same_tensors_reference_and_elsa_b200(ref, name):
     assert torch.isfinite(o_our).all()
     lim = fwd_bound(bound_dtype, t_out) + (e_ref if name in REF_ERR_CASES else 0.0)
     assert rec["fwd"]["ours_vs_ref"] <= lim, rec["fwd"]
+    if dtype == F16 and d == 64 and bias is None and not causal:
+        # The reference's fp16 d=64 kernels round q * log2(e)/8 to fp16; with the same rounding points and the same
+        # partition width (256 below 8192 tokens, 2048 from there on: attention.py:195-222) the two implementations
+        # agree within the plain bound, without the allowance for the reference's own error.
+        kw_r = dict(kw)
+        kw_r.setdefault("block_n", 256 if n < 8192 else 2048)
+        o_ref_r = ref.twopass_attention(q, k, v, is_causal=False, **kw_r)
+        o_our_r = E.twopass_attention(q, k, v, is_causal=False, reference_rounding=True, **kw_r)
+        rec["fwd_reference_rounding"] = {"ours_vs_ref": dist(o_our_r, o_ref_r), "ours_vs_fp64": dist(o_our_r, t_out),
+                                         "ref_vs_fp64": dist(o_ref_r, t_out), "bound": fwd_bound(dtype, t_out)}
+        assert rec["fwd_reference_rounding"]["ours_vs_ref"] <= fwd_bound(dtype, t_out), rec["fwd_reference_rounding"]
     if not do_bwd:
         return
 
