@@ -163,7 +163,8 @@ def _forward_impl(q, k, v, *, bias, is_causal, summary_dtype, part_width, q_chun
     order in memory; only other layouts are copied first."""
     lib = _lib.load()
     batch, heads, seq_len, head_dim = map(int, q.shape)
-    strided = not (flags & _lib.FLAG_REF_ROUNDING) and head_dim % 8 == 0
+    strided = (not (flags & _lib.FLAG_REF_ROUNDING) and head_dim % 8 == 0 and
+               not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()))
     if strided:
         (q_c, qs), (k_c, ks), (v_c, vs) = (_in_place_or_copy(t) for t in (q, k, v))
         strided = any(not t.is_contiguous() for t in (q_c, k_c, v_c))

@@ -90,7 +90,8 @@ def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, wan
     of one packed [B, N, 3, H, D] buffer."""
     lib = _lib.load()
     batch, heads, seq_len, head_dim = map(int, q.shape)
-    strided = head_dim % 8 == 0
+    strided = head_dim % 8 == 0 and (grads_into is not None or
+                                     not all(t.is_contiguous() for t in (q, k, v, out, grad_out)))
     if strided:
         pairs = [_in_place_or_copy(t) for t in (q, k, v, out, grad_out)]
         (q_c, qs), (k_c, ks), (v_c, vs), (out_c, os_), (go_c, gs) = pairs

@@ -5,16 +5,19 @@
 // (batch*head) and one K partition, walked in 128-key tiles:
 //
 //   warp 8      TMA producer   Q tiles once; K and V tiles into a 4-stage ring (128-byte swizzle)
-//   warp 9      MMA issuer     S_t = Q_t K^T   (4 x tcgen05.mma 128x128x16, both operands in smem)
+//   warp 9, 10  MMA issuers    one thread per query tile t:
+//                              S_t = Q_t K^T   (4 x tcgen05.mma 128x128x16, both operands in smem)
 //                              O_t += P_t V    (8 x tcgen05.mma 128x64x16, P from TMEM, V MN-major)
 //   warps 0-3   fold of tile 0 one thread per query row: S row from TMEM into registers, running max, exp2,
 //   warps 4-7   fold of tile 1 row sum, P (16-bit) into its own TMEM columns, exp-rescale of O when the max moved
 //
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).  Because P has
-// its own columns, S_t is free as soon as the fold warps hold the row in registers (bar_sfree): the issuer
+// its own columns, S_t is free as soon as the fold warps hold the row in registers (bar_sfree): the tile's issuer
 // produces S_t of the NEXT key tile right then, so the fold warps never wait for scores.  P is handed to the
-// issuer once per key tile (bar_p); the fold warps wait for P V of the previous key tile (bar_pv0 / bar_kv_free) only before they
-// overwrite P or rescale O.
+// issuer once per key tile (bar_p); the fold warps wait for P V of the previous key tile (bar_pv) only before they
+// overwrite P or rescale O.  The two tiles share nothing but the K/V ring (a stage is refilled when both issuers
+// have released it) and the tensor pipe, so their chains scores -> exponentials -> P V run out of phase: one
+// tile's exponentials overlap the other tile's P V and hand-offs instead of both tiles waiting at the same time.
 //
 // Exp-rescale merge: the fold keeps a reference max m_ref per row and only moves it (rescaling z
 // and the O accumulator in TMEM) when the tile max exceeds it by more than 2^8; the true running
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FoldTcParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kStages + 11];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 11];   // q, kv_full x4, kv_free x4, then 5 pairs
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -115,21 +118,22 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t bar_q = bar0;
   auto bar_kv_full = [&](int st) { return bar0 + 8 * (1 + st); };
   auto bar_kv_free = [&](int st) { return bar0 + 8 * (1 + kStages + st); };
-  const uint32_t bar_s = bar0 + 8 * (1 + 2 * kStages);   // S(j) of both tiles is in TMEM (slot 2 + 2 * kStages is unused)
-  auto bar_p = [&](int t, int h) { return bar0 + 8 * (3 + 2 * kStages + 2 * t + h); };   // per (tile, 64-key half of P)
-  const uint32_t bar_o = bar0 + 8 * (7 + 2 * kStages);
-  auto bar_sfree = [&](int t) { return bar0 + 8 * (8 + 2 * kStages + t); };   // the fold warps hold S_t in registers
-  const uint32_t bar_pv0 = bar0 + 8 * (10 + 2 * kStages);                     // P_0 V of the current key tile has retired
+  auto bar_s = [&](int t) { return bar0 + 8 * (1 + 2 * kStages + t); };          // S_t(j) is in TMEM
+  auto bar_p = [&](int t) { return bar0 + 8 * (3 + 2 * kStages + t); };          // P_t(j) has been delivered by the fold warps
+  auto bar_o = [&](int t) { return bar0 + 8 * (5 + 2 * kStages + t); };          // every MMA of tile t has retired
+  auto bar_sfree = [&](int t) { return bar0 + 8 * (7 + 2 * kStages + t); };      // the fold warps hold S_t in registers
+  auto bar_pv = [&](int t) { return bar0 + 8 * (9 + 2 * kStages + t); };         // P_t V of the current key tile has retired
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
-    for (int st = 0; st < kStages; ++st) { mbar_init(bar_kv_full(st), 1); mbar_init(bar_kv_free(st), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(bar_p(t, 0), 128); mbar_init(bar_p(t, 1), 128); }
-    mbar_init(bar_o, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_sfree(0), 128); mbar_init(bar_sfree(1), 128);
-    mbar_init(bar_pv0, 1);
+    // a K/V stage is free again when BOTH tiles' issuers have released it (a commit after the tile's P V, or a plain
+    // arrival for a key tile that the tile does not visit)
+    for (int st = 0; st < kStages; ++st) { mbar_init(bar_kv_full(st), 1); mbar_init(bar_kv_free(st), 2); }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_s(t), 1); mbar_init(bar_p(t), 128); mbar_init(bar_o(t), 1);
+      mbar_init(bar_sfree(t), 128); mbar_init(bar_pv(t), 1);
+    }
     fence_mbar_init();
   }
   if (warp == 8) {
@@ -165,62 +169,59 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           tma_load_4d(sV(st), &tmap_v, bar_kv_full(st), 0, k_begin + j * 128, hi, bi);
         }
       }
-    } else if (n_max > 0 && warp == kIssuerWarp) {
-      // ---------------- MMA issuer ----------------
+    } else if (n_max > 0 && (warp == kIssuerWarp || warp == kIssuerWarp + 1)) {
+      // ---------------- MMA issuers: one thread per query tile ----------------
+      // Each tile has its own issuing thread, so the two tiles run their chains (scores -> exponentials -> P V)
+      // independently and drift half a period apart by themselves: while one tile's P V and hand-offs are in
+      // flight, the other tile's fold warps have the ex2 unit to themselves.  The only thing the tiles share is
+      // the K/V ring (and the tensor pipe, which executes the MMAs of both threads in the order it receives them).
+      const int t = warp - kIssuerWarp;
       if (lane == 0) {
         constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
         constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // S = Q K^T : A, B K-major
         constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // O += P V  : A in TMEM, B (V) MN-major
         // shared-memory descriptors are loop invariants: every instruction between two tcgen05.mma idles the pipe
-        const uint64_t dq[2] = {make_sdesc(sQ[0], 16, 1024), make_sdesc(sQ[1], 16, 1024)};
+        const uint64_t dq = make_sdesc(sQ[t], 16, 1024);
         const uint64_t dk0 = make_sdesc(sK(0), 16, 1024), dv0 = make_sdesc(sV(0), 128 * 128, 1024);
         constexpr uint64_t kStageStep = (2 * kTileBytes) >> 4;   // descriptor address field counts 16-byte units
-        bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, prm.status, BAR_KV_FULL);
-        if (ok) {
-          tc_fence_after();
-          if (n_t[0] > 0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0, idesc_s, 0u);
-          if (n_t[1] > 0) mma_ss_x4<2, 2>(tS[1], dq[1], dk0, idesc_s, 0u);
-          mma_commit(bar_s);
-        }
-        for (int jb = 0; ok && jb < n_max; jb += kStages) {
-#pragma unroll
-          for (int u = 0; u < kStages; ++u) {
-            const int j = jb + u;
-            if (j >= n_max || !ok) break;
-            const int un = (u + 1) % kStages;
-            // S(j+1) of both tiles as soon as the fold warps have pulled S(j) into registers: the next scores
-            // are computed while the current exponentials run, so the fold warps never wait for the tensor pipe
-            const bool s0 = j + 1 < n_t[0], s1 = j + 1 < n_t[1];
-            if (s0 || s1) {
-              // bar_s is shared by both tiles and advances one phase per commit: every tile that consumes S(j)
-              // must have seen phase j (its sfree arrival says so) before phase j+1 completes, also the tile that
-              // gets no S(j+1) of its own (causal diagonal: n_t[1] == n_t[0] + 1), or its parity test would alias
-              ok = mbar_wait(bar_kv_full(un), ((j + 1) / kStages) & 1, &abort_flag, prm.status, BAR_KV_FULL) &&
-                   (j >= n_t[0] || mbar_wait(bar_sfree(0), j & 1, &abort_flag, prm.status, BAR_SFREE)) &&
-                   (j >= n_t[1] || mbar_wait(bar_sfree(1), j & 1, &abort_flag, prm.status, BAR_SFREE));
-              if (!ok) break;
-              tc_fence_after();
-              if (s0) mma_ss_x4<2, 2>(tS[0], dq[0], dk0 + un * kStageStep, idesc_s, 0u);
-              if (s1) mma_ss_x4<2, 2>(tS[1], dq[1], dk0 + un * kStageStep, idesc_s, 0u);
-              mma_commit(bar_s);
-            }
-            // O_t += P_t V, issued per 64-key half of P as soon as the fold warps have delivered it
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              if (j < n_t[t]) {
-                if (!(ok = mbar_wait(bar_p(t, 0), j & 1, &abort_flag, prm.status, BAR_P))) break;
-                tc_fence_after();
-                mma_ts_x4<8, 128>(tO[t], tP[t], dv0 + u * kStageStep, idesc_o, j > 0 ? 1u : 0u);
-                mma_ts_x4<8, 128>(tO[t], tP[t] + 32, dv0 + u * kStageStep + 512, idesc_o, 1u);
-                if (t == 0) mma_commit(bar_pv0);
-              }
-            }
-            // K(j), V(j) are no longer read once these MMAs retire; for tile 1 the same arrival says that
-            // P_1 V has retired (P_1 may be overwritten, O_1 may be rescaled)
-            if (ok) mma_commit(bar_kv_free(u));
+        const int nt = n_t[t];
+        bool ok = true;
+        if (nt > 0) {
+          ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q) && mbar_wait(bar_kv_full(0), 0, &abort_flag, prm.status, BAR_KV_FULL);
+          if (ok) {
+            tc_fence_after();
+            mma_ss_x4<2, 2>(tS[t], dq, dk0, idesc_s, 0u);
+            mma_commit(bar_s(t));
           }
         }
-        if (ok) mma_commit(bar_o);
+        for (int j = 0; ok && j < nt; ++j) {
+          const int u = j % kStages, un = (j + 1) % kStages;
+          // S(j+1) as soon as the fold warps have pulled S(j) into registers: the next scores are computed while
+          // the current exponentials run, so the fold warps never wait for the tensor pipe
+          if (j + 1 < nt) {
+            ok = mbar_wait(bar_kv_full(un), ((j + 1) / kStages) & 1, &abort_flag, prm.status, BAR_KV_FULL) &&
+                 mbar_wait(bar_sfree(t), j & 1, &abort_flag, prm.status, BAR_SFREE);
+            if (!ok) break;
+            tc_fence_after();
+            mma_ss_x4<2, 2>(tS[t], dq, dk0 + un * kStageStep, idesc_s, 0u);
+            mma_commit(bar_s(t));
+          }
+          // O += P V once the fold warps have delivered P(j)
+          if (!(ok = mbar_wait(bar_p(t), j & 1, &abort_flag, prm.status, BAR_P))) break;
+          tc_fence_after();
+          mma_ts_x4<8, 128>(tO[t], tP[t], dv0 + u * kStageStep, idesc_o, j > 0 ? 1u : 0u);
+          mma_ts_x4<8, 128>(tO[t], tP[t] + 32, dv0 + u * kStageStep + 512, idesc_o, 1u);
+          mma_commit(bar_pv(t));        // P_t may be overwritten, O_t may be rescaled
+          mma_commit(bar_kv_free(u));   // this tile no longer reads K(j), V(j)
+        }
+        if (ok && nt > 0) mma_commit(bar_o(t));
+        // key tiles this query tile does not visit (causal: the other tile reaches one tile further; a tile beyond
+        // the last query row visits none): release their stages in order, each after the stage's previous use is over
+        for (int j = nt; ok && j < n_max; ++j) {
+          const int u = j % kStages;
+          if (j >= kStages && !(ok = mbar_wait(bar_kv_free(u), ((j / kStages) - 1) & 1, &abort_flag, prm.status, BAR_KV_FREE))) break;
+          mbar_arrive(bar_kv_free(u));
+        }
       }
     }
   } else {
@@ -235,7 +236,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(t), j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
       tc_fence_after();
       float sv[128];
 #pragma unroll
@@ -272,9 +273,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       m_true = fmaxf(m_true, tmax);
       if (j > 0) {
         // P_t V of the previous key tile must have retired before P_t is overwritten or O_t rescaled
-        const uint32_t bpv = t == 0 ? bar_pv0 : bar_kv_free((j - 1) % kStages);
-        const uint32_t par = t == 0 ? ((j - 1) & 1) : (((j - 1) / kStages) & 1);
-        if (!__all_sync(0xffffffffu, mbar_wait(bpv, par, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_pv(t), (j - 1) & 1, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
         tc_fence_after();
       }
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
@@ -314,7 +313,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // one hand-off per key tile: with the scores produced a tile ahead, P V need not start on the first half
       tmem_wait_st();               // (also covers the O rescale stores above)
       tc_fence_before();
-      mbar_arrive(bar_p(t, 0));
+      mbar_arrive(bar_p(t));
       {
         const float2 s01 = __fadd2_rn(ps[0], ps[1]), s23 = __fadd2_rn(ps[2], ps[3]);
         const float2 s = __fadd2_rn(s01, s23);
@@ -326,7 +325,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int r_chunk = blockIdx.x * 256 + t * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     if (n_t[t] > 0) {
-      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, prm.status, BAR_O))) alive = false;
+      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o(t), 0, &abort_flag, prm.status, BAR_O))) alive = false;
       if (alive) {
         tc_fence_after();
         float ov[64];

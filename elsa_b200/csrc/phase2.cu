@@ -93,22 +93,21 @@ merge_final_kernel(const float* __restrict__ m, const float* __restrict__ z, con
   const TS* sp = s + (static_cast<int64_t>(first_part) * rows + row) * head_dim + c * NV;
   const float* mp = m + static_cast<int64_t>(first_part) * rows + row;
   const float* zp = z + static_cast<int64_t>(first_part) * rows + row;
-  // four partitions per round: all loads of a round are issued before the first merge needs its data, so that a
-  // thread keeps up to 64 bytes of s in flight (short plans have only two or three partitions to hide latency with)
-  for (int p0 = 0; p0 < n_parts; p0 += 4) {
-    float sv[4][NV], mv[4], zv[4];
+  // the first partition initialises the state (merging it into the identity would only cost two exponentials)
+  {
+    float sv[NV];
+    load_vec<TS, NV>(sp, sv);
+    M = mp[0];
+    Z = zp[0];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (p0 + u < n_parts) {
-        const int64_t po = static_cast<int64_t>(p0 + u) * rows;
-        load_vec<TS, NV>(sp + po * head_dim, sv[u]);
-        mv[u] = mp[po];
-        zv[u] = zp[po];
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (p0 + u < n_parts) monoid_merge<NV>(M, Z, acc, mv[u], zv[u], sv[u]);
+    for (int i = 0; i < NV; ++i) acc[i] = Z > 0.f ? sv[i] : 0.f;
+    M = Z > 0.f ? M : -CUDART_INF_F;
+  }
+#pragma unroll 4
+  for (int p = 1; p < n_parts; ++p) {
+    float sv[NV];
+    load_vec<TS, NV>(sp + static_cast<int64_t>(p) * rows * head_dim, sv);
+    monoid_merge<NV>(M, Z, acc, mp[static_cast<int64_t>(p) * rows], zp[static_cast<int64_t>(p) * rows], sv);
   }
   const int64_t orow = static_cast<int64_t>(blockIdx.y) * n_ctx + q_start + rc.r;
   const float inv = normalize ? (Z > 0.f ? 1.0f / Z : 0.f) : 1.0f;   // normalize == 0: emit the merged, un-normalised s
