@@ -4,15 +4,25 @@
 //   bwd_simt<MODE 0> one CTA per 64 query rows, streams key tiles:  dQ (+ dbias)
 //   bwd_simt<MODE 1> one CTA per 64 key rows,   streams query tiles: dK, dV
 //
-// Both modes are the same register-tiled code with the operand roles swapped: the "row" operands
+//   bwd_simt<MODE 2> MODE 1 plus dQ: the dQ contribution of each (key tile, query tile) pair, dS K, is formed from
+//                    the dS^T tile that is already in shared memory and added into an fp32 dQ with vector
+//                    reductions -- five contractions per pair instead of the seven of MODE 0 + MODE 1 (which
+//                    compute S and dP twice).  Used where dQ is fp32 anyway (fp32 inputs, sequence shards) and no
+//                    bias gradient is wanted; the order of the additions into dQ is then not fixed.
+//
+// All modes are the same register-tiled code with the operand roles swapped: the "row" operands
 // stay in shared memory for the whole CTA, the "column" operands are streamed in 64-row tiles.
-// MODE 1 computes the transposed tiles S^T = K Q^T and dP^T = V dO^T directly, so P^T and dS^T are
-// produced in the layout the dV / dK contractions consume.  No atomics on dQ/dK/dV: results are
-// bit-reproducible from run to run.
+// MODE 1 / 2 compute the transposed tiles S^T = K Q^T and dP^T = V dO^T directly, so P^T and dS^T are
+// produced in the layout the dV / dK contractions consume.  MODE 0 + MODE 1 use no atomics: bit-reproducible.
 #include "kernels.cuh"
 #include "simt_tile.cuh"
 
 namespace elsa {
+
+// global[0..3] += {a, b, c, d} as one 16-byte vector reduction (the address must be 16-byte aligned)
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 template <typename T, int DP, int MODE>
 __global__ void __launch_bounds__(256)
@@ -84,7 +94,7 @@ bwd_simt_kernel(const BwdParams prm) {
     tile_dot<DP>(RB, CB, LD, ty, tx, dP);
 
     float lse_c[4], d_c[4];
-    if (MODE == 1) {
+    if (MODE != 0) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const int c = c0 + tx + 16 * jj;
@@ -133,6 +143,33 @@ bwd_simt_kernel(const BwdParams prm) {
       tile_pv<DP>(Ps, CB, LD, ty, tx, acc1);   // dV += P^T dO
       tile_pv<DP>(Ss, CA, LD, ty, tx, acc2);   // dK += dS^T Q
     }
+    if (MODE == 2) {
+      // dQ[c0 + q][:] += scale * sum_key dS^T[key][q] * K[key][:]   (dS^T in Ss, this CTA's K rows in RA)
+      float dq[4][CPT];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) dq[i][c] = 0.f;
+      tile_ptv<DP>(Ss, RA, LD, ty, tx, dq);
+      float* dq_base = static_cast<float*>(prm.dq) + (static_cast<int64_t>(bh) * N + c0) * D;
+#pragma unroll
+      for (int ii = 0; ii < 4; ++ii) {
+        const int qr = ty * 4 + ii;
+        if (c0 + qr >= N) continue;
+        float* dst = dq_base + static_cast<int64_t>(qr) * D;
+        if constexpr (DP == 64) {
+          if (D == 64) {        // four consecutive columns per thread: one 16-byte vector reduction
+            red_add_v4(dst + tx * 4, dq[ii][0] * prm.scale, dq[ii][1] * prm.scale, dq[ii][2] * prm.scale, dq[ii][3] * prm.scale);
+            continue;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const int col = tile_col<DP>(tx, c);
+          if (col < D) atomicAdd(dst + col, dq[ii][c] * prm.scale);
+        }
+      }
+    }
   }
 
 #pragma unroll
@@ -157,6 +194,7 @@ bwd_simt_kernel(const BwdParams prm) {
 template <typename T, int DP, int MODE>
 static int launch_bwd(const BwdParams& p, cudaStream_t st) {
   constexpr size_t smem = sizeof(float) * (4 * 64 * (DP + 4) + (MODE == 0 ? 1 : 2) * 64 * 68);
+  static_assert(MODE >= 0 && MODE <= 2, "MODE");
   int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_simt_kernel<T, DP, MODE>), smem);
   if (rc != ELSA_OK) return rc;
   const int rows = MODE == 0 ? p.n_ctx : p.n_keys;
@@ -171,6 +209,17 @@ template <typename T>
 static int bwd_simt_t(const BwdParams& p, cudaStream_t st) {
   const int dp = p.head_dim <= 32 ? 32 : (p.head_dim <= 64 ? 64 : 128);
   int rc;
+  // one fused launch where dQ is fp32 (fp32 inputs with a contiguous dq, or the fp32 partial of a sequence shard) and
+  // no bias gradient is wanted: dQ is zeroed and every (key tile, query tile) pair adds its contribution
+  const bool dq_contig = p.dqs.r == p.head_dim && p.dqs.h == static_cast<int64_t>(p.n_ctx) * p.head_dim &&
+                         (p.heads == 1 || p.bh == p.heads || p.dqs.b == p.dqs.h * p.heads);
+  const bool fused = !p.dbias && (p.dq_f32 || (sizeof(T) == 4 && dq_contig)) && p.n_keys > 0;
+  if (fused) {
+    ELSA_CUDA_CHECK(cudaMemsetAsync(p.dq, 0, static_cast<size_t>(p.bh) * p.n_ctx * p.head_dim * sizeof(float), st));
+    if (dp == 32) return launch_bwd<T, 32, 2>(p, st);
+    if (dp == 64) return launch_bwd<T, 64, 2>(p, st);
+    return launch_bwd<T, 128, 2>(p, st);
+  }
   if (dp == 32) { rc = launch_bwd<T, 32, 0>(p, st); if (rc) return rc; return launch_bwd<T, 32, 1>(p, st); }
   if (dp == 64) { rc = launch_bwd<T, 64, 0>(p, st); if (rc) return rc; return launch_bwd<T, 64, 1>(p, st); }
   rc = launch_bwd<T, 128, 0>(p, st); if (rc) return rc; return launch_bwd<T, 128, 1>(p, st);

@@ -101,4 +101,35 @@ __device__ __forceinline__ void tile_pv(const float* __restrict__ P, const float
   }
 }
 
+// acc[ii][c] += sum_j PT[j][ty*4+ii] * V[j][col(c)]: as tile_pv with the left operand stored transposed
+// (PT is [64][68], row = the contraction index), so the four rows of a thread come from one float4
+template <int DP>
+__device__ __forceinline__ void tile_ptv(const float* __restrict__ PT, const float* __restrict__ V, int ldv, int ty,
+                                         int tx, float (&acc)[4][DP / 16]) {
+  constexpr int CPT = DP / 16;
+#pragma unroll 4
+  for (int j = 0; j < 64; ++j) {
+    const float4 p4 = *reinterpret_cast<const float4*>(PT + j * 68 + ty * 4);
+    float vv[CPT];
+    const float* vr = V + j * ldv;
+    if constexpr (DP == 32) {
+      float2 t = *reinterpret_cast<const float2*>(vr + tx * 2);
+      vv[0] = t.x; vv[1] = t.y;
+    } else {
+#pragma unroll
+      for (int g = 0; g < CPT / 4; ++g) {
+        float4 t = *reinterpret_cast<const float4*>(vr + g * 64 + tx * 4);
+        vv[g * 4 + 0] = t.x; vv[g * 4 + 1] = t.y; vv[g * 4 + 2] = t.z; vv[g * 4 + 3] = t.w;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      acc[0][c] = fmaf(p4.x, vv[c], acc[0][c]);
+      acc[1][c] = fmaf(p4.y, vv[c], acc[1][c]);
+      acc[2][c] = fmaf(p4.z, vv[c], acc[2][c]);
+      acc[3][c] = fmaf(p4.w, vv[c], acc[3][c]);
+    }
+  }
+}
+
 }  // namespace elsa

@@ -68,7 +68,9 @@ def test_packed_training_step_matches_the_unpacked_operator(dtype, b, h, n, d, c
     gq, gk, gv = pk.grad.permute(2, 0, 3, 1, 4).unbind(0)
     assert torch.equal(gk, k.grad) and torch.equal(gv, v.grad)
     # dQ of the tensor-core path is accumulated by reductions whose order is not fixed: one output spacing
-    tol = 0.0 if dtype == F32 or n < 512 else U.ulp(dtype, float(q.grad.float().abs().max()))
+    # fp32 with a contiguous dq takes the fused backward, whose dQ is summed by reductions in arrival order as well
+    big = float(q.grad.float().abs().max())
+    tol = 2e-6 * max(1.0, big) if dtype == F32 else (0.0 if n < 512 else U.ulp(dtype, big))
     assert (gq.float() - q.grad.float()).abs().max().item() <= tol
     if bias_t is not None:
         assert torch.allclose(bias_t.grad, dbias_r, rtol=0, atol=2e-6 * max(1.0, float(dbias_r.abs().max())))
