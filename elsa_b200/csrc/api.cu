@@ -149,14 +149,16 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
                            int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int q_start, int q_len,
                            int part_width, int n_parts, int is_causal, unsigned flags, cudaStream_t st,
                            int n_keys = -1, int key_offset = 0, bool q_prescaled = false,
-                           const Strides* qs = nullptr, const Strides* ks = nullptr, const Strides* vs = nullptr) {
+                           const Strides* qs = nullptr, const Strides* ks = nullptr, const Strides* vs = nullptr,
+                           void* direct_out = nullptr, const Strides* os = nullptr, float* row_m = nullptr,
+                           float* row_z = nullptr) {
   if (n_keys < 0) n_keys = n_ctx;
-  if (!q || !k || !v || !m_buf || !z_buf || !s_buf || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
+  if (!q || !k || !v || ((!m_buf || !z_buf || !s_buf) && !direct_out) || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
       heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || q_start < 0 || q_len < 0 ||
       q_start + q_len > n_ctx || part_width < 1 || n_parts < 1 ||
       static_cast<int64_t>(n_parts) * part_width < n_keys || n_keys < 1 || key_offset < 0)
     return ELSA_ERR_INVALID_ARGUMENT;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(s_buf)) return ELSA_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || (!direct_out && !aligned16(s_buf))) return ELSA_ERR_INVALID_ARGUMENT;
   if (static_cast<int64_t>(batch) * heads > 65535 || n_parts > 65535) return ELSA_ERR_UNSUPPORTED;
   if (q_len == 0) return ELSA_OK;
   if (part_width % 64 != 0) return ELSA_ERR_INVALID_ARGUMENT;
@@ -172,6 +174,8 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.n_keys = n_keys; p.key_offset = key_offset;
   p.is_causal = is_causal ? 1 : 0;
   p.summary_dtype = summary_dtype;
+  p.direct = direct_out ? 1 : 0;
+  p.out = direct_out; p.os = os ? *os : contiguous_strides(heads, n_ctx, head_dim); p.row_m = row_m; p.row_z = row_z;
   // reference rounding point: P is cast to fp16 before P.V only for fp16 inputs whose summaries are
   // not fp32 (attention_parallel_scan.py:701, attention.py:96-99); bf16 and fp32 keep P in fp32.
   p.round_p = (dtype == ELSA_F16 && summary_dtype != ELSA_F32) ? 1 : 0;
@@ -319,6 +323,14 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
   const int bh = batch * heads;
   const int store_state = row_m != nullptr;
 
+  // A problem that is a single (query tile, key partition) pair of the FP32-FMA kernel (49-token windows and other
+  // sequences of at most 64 tokens): phase 2 would merge one summary per row, so phase 1 finalises the rows itself,
+  // with the same rounding points, and the summaries never travel through memory.
+  if (!pl.tensor_cores && pl.n_parts == 1 && n_ctx <= 64 && !(flags & (ELSA_FLAG_SCAN_STEPS | ELSA_FLAG_TREE_MERGE))) {
+    return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, nullptr, nullptr,
+                           nullptr, dtype, summary_dtype, batch, heads, n_ctx, head_dim, 0, n_ctx, pl.part_width, 1,
+                           is_causal, flags, st, -1, 0, ref_round, qs, ks, vs, out, os, row_m, row_z);
+  }
   for (int q_start = 0; q_start < n_ctx; q_start += pl.q_chunk) {
     const int q_len = std::min(pl.q_chunk, n_ctx - q_start);
     rc = phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_a, z_a, s_a, dtype,
@@ -429,7 +441,10 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   p.qs = st8 ? st8[0] : cs; p.ks = st8 ? st8[1] : cs; p.vs = st8 ? st8[2] : cs; p.gs = st8 ? st8[4] : cs;
   p.dqs = st8 ? st8[5] : cs; p.dks = st8 ? st8[6] : cs; p.dvs = st8 ? st8[7] : cs;
   int rc = ELSA_OK;
-  if (!use_tc)
+  // a problem of at most 64 tokens is one (query tile, key tile) pair: one launch does the pre-pass and all gradients
+  p.single_tile = (!use_tc && n_ctx <= 64 && head_dim <= 64) ? 1 : 0;
+  p.out = out; p.os = os; p.row_m = row_m; p.row_z = row_z;
+  if (!use_tc && !p.single_tile)
     rc = bwd_preprocess_any(out, os, dout, p.gs, row_m, row_z, row_d, row_lse, dtype, batch, heads, n_ctx, head_dim,
                             static_cast<cudaStream_t>(stream));
   if (rc != ELSA_OK) return rc;
@@ -525,6 +540,7 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
   p.n_keys = n_keys; p.key_offset = key_offset; p.dq_f32 = 1;
+  p.single_tile = 0; p.out = out; p.os = cs; p.row_m = row_m; p.row_z = row_z;
   if (use_tc) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;

@@ -4,6 +4,9 @@
 //   bwd_simt<MODE 0> one CTA per 64 query rows, streams key tiles:  dQ (+ dbias)
 //   bwd_simt<MODE 1> one CTA per 64 key rows,   streams query tiles: dK, dV
 //
+//   bwd_simt<MODE 3> the whole problem is ONE (query tile, key tile) pair (n_ctx <= 64: 49-token windows): one launch
+//                    forms D and LSE from out, dout and the row state, computes S and dP once and all of dQ, dK,
+//                    dV (and dbias) from them -- five contractions, no atomics, no separate pre-pass
 //   bwd_simt<MODE 2> MODE 1 plus dQ: the dQ contribution of each (key tile, query tile) pair, dS K, is formed from
 //                    the dS^T tile that is already in shared memory and added into an fp32 dQ with vector
 //                    reductions -- five contractions per pair instead of the seven of MODE 0 + MODE 1 (which
@@ -25,10 +28,11 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 
 template <typename T, int DP, int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (DP == 32 ? ELSA_BWD_MIN_CTAS_D32 : (DP == 64 ? ELSA_BWD_MIN_CTAS_D64 : 1)))
 bwd_simt_kernel(const BwdParams prm) {
   constexpr int LD = DP + 4;
   constexpr int CPT = DP / 16;
+  constexpr bool QROWS = MODE == 0 || MODE == 3;   // the CTA's resident rows are queries (else keys)
   extern __shared__ __align__(16) float smem[];
   float* RA = smem;             // MODE 0: Q rows     MODE 1: K rows
   float* RB = RA + 64 * LD;     // MODE 0: dO rows    MODE 1: V rows
@@ -40,8 +44,8 @@ bwd_simt_kernel(const BwdParams prm) {
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int bh = blockIdx.y;
   const int D = prm.head_dim, N = prm.n_ctx, NK = prm.n_keys, koff = prm.key_offset;
-  const int NR = MODE == 0 ? N : NK;       // rows of this launch: queries (dQ) or local keys (dK, dV)
-  const int NC = MODE == 0 ? NK : N;       // columns walked by the loop
+  const int NR = QROWS ? N : NK;       // rows of this launch: queries (dQ) or local keys (dK, dV)
+  const int NC = QROWS ? NK : N;       // columns walked by the loop
   const int r0 = blockIdx.x * 64;
   const int rows_valid = min(64, NR - r0);
   const int b = bh / prm.heads, h = bh - b * prm.heads;
@@ -49,17 +53,17 @@ bwd_simt_kernel(const BwdParams prm) {
   const T* kb = static_cast<const T*>(prm.k) + b * prm.ks.b + h * prm.ks.h;
   const T* vb = static_cast<const T*>(prm.v) + b * prm.vs.b + h * prm.vs.h;
   const T* gb = static_cast<const T*>(prm.dout) + b * prm.gs.b + h * prm.gs.h;
-  const int64_t ra_ld = MODE == 0 ? prm.qs.r : prm.ks.r, rb_ld = MODE == 0 ? prm.gs.r : prm.vs.r;   // resident operands
-  const int64_t ca_ld = MODE == 0 ? prm.ks.r : prm.qs.r, cb_ld = MODE == 0 ? prm.vs.r : prm.gs.r;   // streamed operands
+  const int64_t ra_ld = QROWS ? prm.qs.r : prm.ks.r, rb_ld = QROWS ? prm.gs.r : prm.vs.r;   // resident operands
+  const int64_t ca_ld = QROWS ? prm.ks.r : prm.qs.r, cb_ld = QROWS ? prm.vs.r : prm.gs.r;   // streamed operands
   const float* lse = prm.lse + static_cast<int64_t>(bh) * N;
   const float* drow = prm.drow + static_cast<int64_t>(bh) * N;
   const bool vec_ok = (D % 4) == 0 && ((prm.qs.r | prm.ks.r | prm.vs.r | prm.gs.r | prm.qs.h | prm.ks.h | prm.vs.h | prm.gs.h |
                                         prm.qs.b | prm.ks.b | prm.vs.b | prm.gs.b) % 4) == 0;
   const float* bias_bh = prm.bias ? prm.bias + b * prm.bsb + h * prm.bsh : nullptr;
-  float* dbias_bh = (MODE == 0 && prm.dbias) ? prm.dbias + b * prm.dsb + h * prm.dsh : nullptr;
+  float* dbias_bh = (QROWS && prm.dbias) ? prm.dbias + b * prm.dsb + h * prm.dsh : nullptr;
 
-  load_tile<T, DP>(RA, LD, (MODE == 0 ? qb : kb) + static_cast<int64_t>(r0) * ra_ld, ra_ld, rows_valid, D, vec_ok, tid);
-  load_tile<T, DP>(RB, LD, (MODE == 0 ? gb : vb) + static_cast<int64_t>(r0) * rb_ld, rb_ld, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(RA, LD, (QROWS ? qb : kb) + static_cast<int64_t>(r0) * ra_ld, ra_ld, rows_valid, D, vec_ok, tid);
+  load_tile<T, DP>(RB, LD, (QROWS ? gb : vb) + static_cast<int64_t>(r0) * rb_ld, rb_ld, rows_valid, D, vec_ok, tid);
 
   float lse_r[4], d_r[4];
   if (MODE == 0) {
@@ -70,6 +74,35 @@ bwd_simt_kernel(const BwdParams prm) {
       d_r[ii] = r < N ? drow[r] : 0.f;
     }
   }
+  if (MODE == 3) {
+    // the pre-pass, inline: D = sum_d out * dout over the row (out staged in the K tile's buffer, dout already
+    // resident), LSE = m + log2(max(z, 1e-30))
+    const T* ob = static_cast<const T*>(prm.out) + b * prm.os.b + h * prm.os.h;
+    const bool ovec = vec_ok && ((prm.os.r | prm.os.h | prm.os.b) % 4) == 0;
+    load_tile<T, DP>(CA, LD, ob, prm.os.r, rows_valid, D, ovec, tid);
+    __syncthreads();
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+      const int r = ty * 4 + ii;
+      float part = 0.f;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const int col = tile_col<DP>(tx, c);
+        part += CA[r * LD + col] * RB[r * LD + col];     // columns >= D are zero-filled in both tiles
+      }
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      d_r[ii] = r < N ? part : 0.f;
+      const int64_t sr = static_cast<int64_t>(bh) * N + r;
+      lse_r[ii] = r < N ? prm.row_m[sr] + log2f(fmaxf(prm.row_z[sr], 1.0e-30f)) : -CUDART_INF_F;
+    }
+    // (the loop below starts with a barrier before it overwrites the staging buffer)
+  }
+  float acc3[4][CPT];   // MODE 3: dK (unused, and removed by the compiler, in the other modes)
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) acc3[i][c] = 0.f;
   float acc1[4][CPT], acc2[4][CPT];  // MODE 0: acc1 = dQ; MODE 1: acc1 = dV, acc2 = dK
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -78,15 +111,15 @@ bwd_simt_kernel(const BwdParams prm) {
 
   int c_begin = 0, c_end = NC;
   if (prm.is_causal) {
-    if (MODE == 0) c_end = max(0, min(NK, r0 + rows_valid - koff));  // local keys whose sequence index <= last query row of the tile
+    if (QROWS) c_end = max(0, min(NK, r0 + rows_valid - koff));  // local keys whose sequence index <= last query row of the tile
     else c_begin = min(N, r0 + koff);                                // queries >= sequence index of the first key row of the tile
   }
 
   for (int c0 = c_begin; c0 < c_end; c0 += 64) {
     __syncthreads();
     const int cv = min(64, NC - c0);
-    load_tile<T, DP>(CA, LD, (MODE == 0 ? kb : qb) + static_cast<int64_t>(c0) * ca_ld, ca_ld, cv, D, vec_ok, tid);
-    load_tile<T, DP>(CB, LD, (MODE == 0 ? vb : gb) + static_cast<int64_t>(c0) * cb_ld, cb_ld, cv, D, vec_ok, tid);
+    load_tile<T, DP>(CA, LD, (QROWS ? kb : qb) + static_cast<int64_t>(c0) * ca_ld, ca_ld, cv, D, vec_ok, tid);
+    load_tile<T, DP>(CB, LD, (QROWS ? vb : gb) + static_cast<int64_t>(c0) * cb_ld, cb_ld, cv, D, vec_ok, tid);
     __syncthreads();
 
     float S[4][4], dP[4][4];
@@ -94,7 +127,7 @@ bwd_simt_kernel(const BwdParams prm) {
     tile_dot<DP>(RB, CB, LD, ty, tx, dP);
 
     float lse_c[4], d_c[4];
-    if (MODE != 0) {
+    if (!QROWS) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const int c = c0 + tx + 16 * jj;
@@ -107,12 +140,12 @@ bwd_simt_kernel(const BwdParams prm) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const int rr = r0 + ty * 4 + ii, cc = c0 + tx + 16 * jj;
-        const int qi = MODE == 0 ? rr : cc;
-        const int kj = (MODE == 0 ? cc : rr) + koff;       // sequence index of the key
+        const int qi = QROWS ? rr : cc;
+        const int kj = (QROWS ? cc : rr) + koff;       // sequence index of the key
         bool valid = rr < NR && cc < NC;
         if (prm.is_causal) valid = valid && (qi >= kj);
-        const float l = MODE == 0 ? lse_r[ii] : lse_c[jj];
-        const float dd = MODE == 0 ? d_r[ii] : d_c[jj];
+        const float l = QROWS ? lse_r[ii] : lse_c[jj];
+        const float dd = QROWS ? d_r[ii] : d_c[jj];
         float sc;
         if (bias_bh) {
           const float bv = valid ? bias_bh[static_cast<int64_t>(qi) * prm.bsq + static_cast<int64_t>(kj) * prm.bsk] : 0.f;
@@ -123,13 +156,16 @@ bwd_simt_kernel(const BwdParams prm) {
         // a row with no admissible key has LSE = -inf: its probabilities are defined as 0
         const float p = (valid && l > -CUDART_INF_F) ? exp2f(sc - l) : 0.f;
         const float ds = p * (dP[ii][jj] - dd);
-        if (MODE == 0 && dbias_bh && valid) {
+        if (QROWS && dbias_bh && valid) {
           float* dst = dbias_bh + static_cast<int64_t>(qi) * prm.dsq + static_cast<int64_t>(kj) * prm.dsk;
           if (prm.dbias_atomic) atomicAdd(dst, ds); else *dst = ds;
         }
         const int so = (ty * 4 + ii) * 68 + tx + 16 * jj;
         if (MODE == 0) {
           Ps[so] = round_to<T>(ds);
+        } else if (MODE == 3) {
+          Ps[so] = round_to<T>(ds);      // dS [query][key]
+          Ss[so] = round_to<T>(p);       // P  [query][key]
         } else {
           Ps[so] = round_to<T>(p);
           Ss[so] = round_to<T>(ds);
@@ -139,6 +175,10 @@ bwd_simt_kernel(const BwdParams prm) {
     __syncthreads();
     if (MODE == 0) {
       tile_pv<DP>(Ps, CA, LD, ty, tx, acc1);   // dQ += dS K
+    } else if (MODE == 3) {
+      tile_pv<DP>(Ps, CA, LD, ty, tx, acc1);    // dQ = dS K            (rows: queries)
+      tile_ptv<DP>(Ss, RB, LD, ty, tx, acc2);   // dV = P^T dO          (rows: keys; the left operand is read transposed)
+      tile_ptv<DP>(Ps, RA, LD, ty, tx, acc3);   // dK = dS^T Q
     } else {
       tile_pv<DP>(Ps, CB, LD, ty, tx, acc1);   // dV += P^T dO
       tile_pv<DP>(Ss, CA, LD, ty, tx, acc2);   // dK += dS^T Q
@@ -180,9 +220,13 @@ bwd_simt_kernel(const BwdParams prm) {
     for (int c = 0; c < CPT; ++c) {
       const int col = tile_col<DP>(tx, c);
       if (col >= D) continue;
-      if (MODE == 0) {
+      if (QROWS) {
         if (prm.dq_f32) static_cast<float*>(prm.dq)[(static_cast<int64_t>(bh) * N + r) * D + col] = acc1[ii][c] * prm.scale;
         else static_cast<T*>(prm.dq)[b * prm.dqs.b + h * prm.dqs.h + r * prm.dqs.r + col] = from_f32<T>(acc1[ii][c] * prm.scale);
+        if (MODE == 3) {     // single tile: row r is also key r
+          static_cast<T*>(prm.dv)[b * prm.dvs.b + h * prm.dvs.h + r * prm.dvs.r + col] = from_f32<T>(acc2[ii][c]);
+          static_cast<T*>(prm.dk)[b * prm.dks.b + h * prm.dks.h + r * prm.dks.r + col] = from_f32<T>(acc3[ii][c] * prm.scale);
+        }
       } else {
         static_cast<T*>(prm.dv)[b * prm.dvs.b + h * prm.dvs.h + r * prm.dvs.r + col] = from_f32<T>(acc1[ii][c]);
         static_cast<T*>(prm.dk)[b * prm.dks.b + h * prm.dks.h + r * prm.dks.r + col] = from_f32<T>(acc2[ii][c] * prm.scale);
@@ -194,10 +238,10 @@ bwd_simt_kernel(const BwdParams prm) {
 template <typename T, int DP, int MODE>
 static int launch_bwd(const BwdParams& p, cudaStream_t st) {
   constexpr size_t smem = sizeof(float) * (4 * 64 * (DP + 4) + (MODE == 0 ? 1 : 2) * 64 * 68);
-  static_assert(MODE >= 0 && MODE <= 2, "MODE");
+  static_assert(MODE >= 0 && MODE <= 3, "MODE");
   int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_simt_kernel<T, DP, MODE>), smem);
   if (rc != ELSA_OK) return rc;
-  const int rows = MODE == 0 ? p.n_ctx : p.n_keys;
+  const int rows = (MODE == 0 || MODE == 3) ? p.n_ctx : p.n_keys;
   if (rows == 0) return ELSA_OK;
   dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>(p.bh));
   bwd_simt_kernel<T, DP, MODE><<<grid, 256, smem, st>>>(p);
@@ -213,6 +257,10 @@ static int bwd_simt_t(const BwdParams& p, cudaStream_t st) {
   // no bias gradient is wanted: dQ is zeroed and every (key tile, query tile) pair adds its contribution
   const bool dq_contig = p.dqs.r == p.head_dim && p.dqs.h == static_cast<int64_t>(p.n_ctx) * p.head_dim &&
                          (p.heads == 1 || p.bh == p.heads || p.dqs.b == p.dqs.h * p.heads);
+  if (p.single_tile && dp <= 64) {
+    if (dp == 32) return launch_bwd<T, 32, 3>(p, st);
+    return launch_bwd<T, 64, 3>(p, st);
+  }
   const bool fused = !p.dbias && (p.dq_f32 || (sizeof(T) == 4 && dq_contig)) && p.n_keys > 0;
   if (fused) {
     ELSA_CUDA_CHECK(cudaMemsetAsync(p.dq, 0, static_cast<size_t>(p.bh) * p.n_ctx * p.head_dim * sizeof(float), st));

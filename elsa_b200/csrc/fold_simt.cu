@@ -14,7 +14,7 @@
 namespace elsa {
 
 template <typename T, int DP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (DP == 32 ? ELSA_FOLD_MIN_CTAS_D32 : (DP == 64 ? ELSA_FOLD_MIN_CTAS_D64 : 1)))
 fold_simt_kernel(const FoldParams prm) {
   constexpr int LD = DP + 4;
   constexpr int CPT = DP / 16;
@@ -43,7 +43,6 @@ fold_simt_kernel(const FoldParams prm) {
   const bool vec_ok = (D % 4) == 0 && ((prm.qs.r | prm.ks.r | prm.vs.r | prm.qs.h | prm.ks.h | prm.vs.h | prm.qs.b | prm.ks.b | prm.vs.b) % 4) == 0;
   const float* bias_bh = nullptr;
   if (prm.bias) bias_bh = prm.bias + b * prm.bsb + h * prm.bsh;
-  (void)N;
 
   load_tile<T, DP>(Qs, LD, qb + static_cast<int64_t>(q0) * prm.qs.r, prm.qs.r, rows_valid, D, vec_ok, tid);
 
@@ -112,6 +111,35 @@ fold_simt_kernel(const FoldParams prm) {
     }
     __syncthreads();
     tile_pv<DP>(Ps, Vs, DP, ty, tx, acc);
+  }
+
+  if (prm.direct) {
+    // one partition, so (m, z, s) is the row's final state: out = s / z (0 for a row without admissible keys)
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+      float zsum = z_part[ii];
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) zsum += __shfl_xor_sync(0xffffffffu, zsum, o);
+      const int qi = q0 + ty * 4 + ii;
+      if (qi >= q_end) continue;
+      const float inv = zsum > 0.f ? 1.0f / zsum : 0.f;
+      if (tx == 0 && prm.row_m) {
+        prm.row_m[static_cast<int64_t>(bh) * N + qi] = zsum > 0.f ? m_run[ii] : -CUDART_INF_F;
+        prm.row_z[static_cast<int64_t>(bh) * N + qi] = zsum;
+      }
+      T* orow = static_cast<T*>(prm.out) + b * prm.os.b + h * prm.os.h + static_cast<int64_t>(qi) * prm.os.r;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const int col = tile_col<DP>(tx, c);
+        if (col >= D) continue;
+        // same rounding points as the two-pass route: s is rounded to the summary type before the division
+        float sval = acc[ii][c];
+        if (prm.summary_dtype == ELSA_F16) sval = round_to<__half>(sval);
+        else if (prm.summary_dtype == ELSA_BF16) sval = round_to<__nv_bfloat16>(sval);
+        orow[col] = from_f32<T>(zsum > 0.f ? sval * inv : 0.f);
+      }
+    }
+    return;
   }
 
   // write the partition summary

@@ -24,6 +24,11 @@ struct FoldParams {
   int n_keys, key_offset;   // rows of k/v per (batch*head) and the global index of their first row (sequence shards)
   int is_causal, summary_dtype, round_p;  // round_p: 0 keep P in fp32, 1 round to fp16, 2 to bf16
   float scale, scale_log2;
+  // direct != 0 (FP32-FMA kernel, one partition, one query tile): the partition summary is the final state, so the
+  // kernel writes out = s / z (element type = the input type, rows addressed through `os`) and, when row_m is
+  // not null, the row state, instead of a summary -- phase 2 would merge a single element
+  int direct;
+  void* out; Strides os; float* row_m; float* row_z;
 };
 
 struct BwdParams {
@@ -39,6 +44,10 @@ struct BwdParams {
   // sequence shard: k, v, dk, dv hold n_keys rows that are rows key_offset .. key_offset + n_keys - 1 of the
   // sequence (n_keys = n_ctx, key_offset = 0 for the whole problem); dq_f32: dq is an fp32 [BH, N, D] buffer
   int n_keys, key_offset, dq_f32;
+  // single_tile != 0 (FP32-FMA kernels, n_ctx <= 64, whole problem): one launch computes D and LSE from out, dout and
+  // the row state and then dQ, dK, dV (and dbias) of the only (query tile, key tile) pair
+  int single_tile;
+  const void* out; Strides os; const float* row_m; const float* row_z;
 };
 
 // opt-in to > 48 KB dynamic shared memory once per (function, device)

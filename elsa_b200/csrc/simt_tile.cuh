@@ -5,6 +5,23 @@
 
 #include "kernels.cuh"
 
+// Minimum resident CTAs per SM the FP32-FMA kernels are compiled for (this bounds the registers per thread).
+// Measured on B200 (CUDA-graph replays, microseconds): the forward gains from three or four CTAs per SM (fp32
+// N = 4096: 1155 -> 1050 at head dim 64; 49-token windows at head dim 32: 84 -> 47), the head-dim-32 backward from
+// three (246 -> 162), while the head-dim-64 backward loses when squeezed below 128 registers (2710 -> 3360).
+#ifndef ELSA_FOLD_MIN_CTAS_D32
+#define ELSA_FOLD_MIN_CTAS_D32 4
+#endif
+#ifndef ELSA_FOLD_MIN_CTAS_D64
+#define ELSA_FOLD_MIN_CTAS_D64 3
+#endif
+#ifndef ELSA_BWD_MIN_CTAS_D32
+#define ELSA_BWD_MIN_CTAS_D32 3
+#endif
+#ifndef ELSA_BWD_MIN_CTAS_D64
+#define ELSA_BWD_MIN_CTAS_D64 2
+#endif
+
 namespace elsa {
 
 // global rows of D elements of T, `src_ld` elements apart  ->  shared fp32 [64][ld], zero-filled beyond rows_valid

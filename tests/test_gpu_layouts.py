@@ -36,7 +36,8 @@ def test_packed_views_are_read_in_place_and_match_the_contiguous_path(dtype, b, 
     l0 = lib.elsa_kernel_launches()
     names = _cuda_kernel_names(lambda: E.twopass_attention(q, k, v, is_causal=causal))
     out = E.twopass_attention(q, k, v, is_causal=causal)
-    assert lib.elsa_kernel_launches() - l0 == 4            # phase 1 + phase 2, twice (profiled call and this one)
+    # phase 1 + phase 2 per call (one fused launch for a sequence of at most 64 tokens), profiled call and this one
+    assert lib.elsa_kernel_launches() - l0 == (2 if n <= 64 else 4)
     assert not any("copy" in nm.lower() or "elementwise" in nm.lower() for nm in names), names
     assert torch.equal(out, ref)                                     # same kernels, same arithmetic: same bits
     # the result sits in [B, N, H, D] memory: the hooks' transpose + reshape is a view
@@ -66,7 +67,12 @@ def test_packed_training_step_matches_the_unpacked_operator(dtype, b, h, n, d, c
     assert not any("copy" in nm.lower() or "cat" in nm.lower() for nm in names), names
     assert torch.equal(out_p, out_r)
     gq, gk, gv = pk.grad.permute(2, 0, 3, 1, 4).unbind(0)
-    assert torch.equal(gk, k.grad) and torch.equal(gv, v.grad)
+    if dtype == F32:
+        # fp32: the contiguous operator takes the fused backward, the packed one the two-kernel backward
+        for got, ref in ((gk, k.grad), (gv, v.grad)):
+            assert (got - ref).abs().max().item() <= 2e-6 * max(1.0, float(ref.abs().max()))
+    else:
+        assert torch.equal(gk, k.grad) and torch.equal(gv, v.grad)
     # dQ of the tensor-core path is accumulated by reductions whose order is not fixed: one output spacing
     # fp32 with a contiguous dq takes the fused backward, whose dQ is summed by reductions in arrival order as well
     big = float(q.grad.float().abs().max())
