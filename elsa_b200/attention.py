@@ -151,6 +151,37 @@ def _empty_like_layout(ref: torch.Tensor, like_strides) -> torch.Tensor:
     return torch.empty((b, h, n, d), device=ref.device, dtype=ref.dtype)
 
 
+_WS_CACHE: dict = {}
+
+
+def _cached_bytes(fn_name: str, *args) -> int:
+    """Workspace size queries are pure functions of their arguments: remember them (the per-call ctypes round trip is
+    a measurable part of a 49-token window problem)."""
+    key = (fn_name,) + args
+    val = _WS_CACHE.get(key)
+    if val is None:
+        val = int(getattr(_lib.load(), fn_name)(*args))
+        _WS_CACHE[key] = val
+    return val
+
+
+class _DeviceScope:
+    """`torch.cuda.device(dev)` only when dev is not already current (entering the context manager costs several
+    microseconds per call)."""
+
+    def __init__(self, dev):
+        self._ctx = None if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self._ctx is not None:
+            self._ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            self._ctx.__exit__(*exc)
+        return False
+
+
 def _i64x(*triples):
     import ctypes
     flat = [int(x) for tr in triples for x in tr]
@@ -181,11 +212,11 @@ def _forward_impl(q, k, v, *, bias, is_causal, summary_dtype, part_width, q_chun
         row_z = torch.empty_like(row_m)
     meta = _canonical_bias(bias, batch=batch, heads=heads, seq_len=seq_len, device=q.device)
     dt, sdt = _lib.dtype_code(q.dtype), _lib.dtype_code(summary_dtype)
-    nbytes = lib.elsa_forward_workspace_bytes(dt, sdt, batch, heads, seq_len, head_dim, int(meta.has_bias),
-                                              int(bool(is_causal)), part_width, q_chunk, flags)
+    nbytes = _cached_bytes("elsa_forward_workspace_bytes", dt, sdt, batch, heads, seq_len, head_dim, int(meta.has_bias),
+                           int(bool(is_causal)), part_width, q_chunk, flags)
     if nbytes < 0:
         raise ValueError("elsa_b200: unsupported problem size for the forward")
-    with torch.cuda.device(q.device):
+    with _DeviceScope(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
         stream = torch.cuda.current_stream(q.device).cuda_stream
         rm_p = None if row_m is None else row_m.data_ptr()

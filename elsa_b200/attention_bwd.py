@@ -15,7 +15,7 @@ from typing import Literal, Optional
 import torch
 
 from . import _lib
-from .attention import (_aligned, _bhnd_strides, _canonical_bias, _check_qkv, _empty_like_layout, _forward_impl, _i64x,
+from .attention import (_DeviceScope, _aligned, _bhnd_strides, _cached_bytes, _canonical_bias, _check_qkv, _empty_like_layout, _forward_impl, _i64x,
                         _in_place_or_copy, _resolve_common, _validate_warps)
 
 
@@ -125,11 +125,11 @@ def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, wan
         dbias = torch.zeros_like(meta.tensor)
         dargs = (dbias.data_ptr(), meta.stride_b, meta.stride_h, meta.stride_q, meta.stride_k)
     dt = _lib.dtype_code(q.dtype)
-    nbytes = lib.elsa_backward_workspace_bytes(dt, batch, heads, seq_len, head_dim, int(meta.has_bias),
-                                               int(bool(is_causal)), flags)
+    nbytes = _cached_bytes("elsa_backward_workspace_bytes", dt, batch, heads, seq_len, head_dim, int(meta.has_bias),
+                           int(bool(is_causal)), flags)
     if nbytes < 0:
         raise ValueError("elsa_b200: unsupported problem size for the backward")
-    with torch.cuda.device(q.device):
+    with _DeviceScope(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
         stream = torch.cuda.current_stream(q.device).cuda_stream
         if strided:
