@@ -89,6 +89,15 @@ def test_phase1_matches_reference_d64_fixture(golden, name):
     truth = O.softmax_attention_fp64(g["q"], g["k"], g["v"]).reshape(out.shape)
     assert U.out_close(out, truth, q.dtype) <= 1.0
     assert U.out_close(out, ref_out.to(q.dtype), q.dtype) <= (1.0 if f32 else 2.5)
+    if not f32:
+        # With the reference's own rounding points (q * log2(e)/8 formed in fp16, scores unscaled) the stated bound
+        # holds against the fixture itself, and the row state agrees far more closely than with the exact scale.
+        b, h, n, d = q.shape
+        out_r, rm_r, rz_r = E.twopass_attention_with_state(q, k, v, block_n=g["block_n"], reference_rounding=True)
+        assert U.out_close(out_r.reshape(out.shape), ref_out.to(q.dtype), q.dtype) <= 1.0
+        fin = ref_z > 0
+        assert U.max_abs(rm_r.reshape(ref_m.shape), ref_m) <= 1e-4
+        assert ((rz_r.reshape(ref_z.shape).cpu()[fin] - ref_z[fin]).abs() / ref_z[fin]).max().item() <= 1e-3
 
 
 CASES = [
