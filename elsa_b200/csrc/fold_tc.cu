@@ -48,10 +48,6 @@ constexpr int kThreads = 384;   // 3 warpgroups: two fold groups + (producer, MM
 constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarp = 8, kIssuerWarp = 9;
 constexpr float kRescaleThreshold = 8.0f;
-#ifndef ELSA_POLY_EVERY
-#define ELSA_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = ELSA_POLY_EVERY;   // every kPolyEvery-th pair of exponentials on the FMA pipe (0 = none)
 
 enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, BAR_O = 6, BAR_SFREE = 7, BAR_PV = 8 };
 
@@ -308,8 +304,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(sv[64 * h + 2 * i], sv[64 * h + 2 * i + 1]), c2, nm2);
-          const float2 pp = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery > 0 ? kPolyEvery - 1 : 0)) ? exp2_fma_pair(x)
-                                                                                                                     : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
           ps[i & 3] = __fadd2_rn(ps[i & 3], pp);
           pk[i] = pack2<T>(pp.x, pp.y);
         }

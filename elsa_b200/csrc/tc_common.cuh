@@ -195,23 +195,6 @@ __device__ __forceinline__ void mma_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint
         "n"(3 * A_STEP), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
       : "memory");
 }
-// 2^x for a packed pair on the FMA pipe instead of the ex2 unit (16 results / clk / SM): round-to-nearest split
-// x = n + f with the 1.5 * 2^23 trick, degree-4 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error
-// 2.7e-6, far below the 16-bit rounding of P), then n is added into the exponent field.  x is clamped at -126.
-__device__ __forceinline__ float2 exp2_fma_pair(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.009570101276040077f, 0.009570101276040077f), make_float2(0.05591785907745361f, 0.05591785907745361f));
-  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
-  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
-  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
-  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
-}
-
 // the mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is complete
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
