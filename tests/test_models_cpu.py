@@ -93,3 +93,34 @@ def test_bucketed_gradient_exchange_two_cpu_ranks():
     ret = mp.Manager().dict()
     mp.spawn(_dp_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert len(ret) == 4 and all(v <= 1e-6 for v in ret.values()), dict(ret)
+
+
+def test_layout_helpers_decide_in_place_or_copy():
+    """Host logic of the strided entry points: which [B, H, N, D] views the kernels may read in place."""
+    from elsa_b200.attention import _bhnd_strides, _empty_like_layout, _i64x
+    b, n, h, d = 2, 50, 3, 64
+    qkv = torch.zeros(b, n, 3, h, d, dtype=torch.float16)
+    q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+    assert _bhnd_strides(q) == (n * 3 * h * d, d, 3 * h * d) == _bhnd_strides(k) == _bhnd_strides(v)
+    assert k.data_ptr() - q.data_ptr() == h * d * 2
+    assert _bhnd_strides(torch.zeros(b, h, n, d)) == (h * n * d, n * d, d)
+    assert _bhnd_strides(torch.zeros(1, 1, n, d)) == (d * 8, d * 8, d)              # size-1 axes: any valid stride
+    assert _bhnd_strides(torch.zeros(b, h, d, n).transpose(2, 3)) is None            # D axis not contiguous
+    assert _bhnd_strides(torch.zeros(b, h, n, d + 4, dtype=torch.float16)[..., :d]) is None   # row stride 68: not 16-byte rows
+    assert _bhnd_strides(torch.zeros(b, h, n, d + 8, dtype=torch.float16)[..., 4:4 + d]) is None   # first element off a 16-byte boundary
+    assert _bhnd_strides(torch.zeros(1, h, n, d).expand(b, h, n, d)) is None         # broadcast batch axis
+    out = _empty_like_layout(q, _bhnd_strides(q))
+    assert out.shape == q.shape and out.transpose(1, 2).reshape(b, n, h * d).data_ptr() == out.data_ptr()
+    assert _empty_like_layout(torch.zeros(b, h, n, d), (h * n * d, n * d, d)).is_contiguous()
+    arr = _i64x((1, 2, 3), (4, 5, 6))
+    assert list(arr) == [1, 2, 3, 4, 5, 6]
+
+
+def test_packed_operator_validates_its_arguments():
+    from elsa_b200.attention_bwd import twopass_attention_qkvpacked
+    with pytest.raises(ValueError, match=r"\[B,N,3,H,D\]"):
+        twopass_attention_qkvpacked(torch.zeros(2, 5, 2, 3, 8))
+    with pytest.raises(ValueError, match="num_warps"):
+        twopass_attention_qkvpacked(torch.zeros(2, 5, 3, 3, 8), bwd_num_warps=3)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        twopass_attention_qkvpacked(torch.zeros(2, 5, 3, 3, 8))
