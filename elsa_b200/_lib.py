@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("ELSA_B200_LIB") or os.path.join(_HERE, "libelsa_b200.so")
 
 ELSA_F32, ELSA_F16, ELSA_BF16 = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_SCAN_STEPS, FLAG_TREE_MERGE, FLAG_REF_ROUNDING = 1, 2, 4, 8
+FLAG_FORCE_SIMT, FLAG_SCAN_STEPS, FLAG_TREE_MERGE, FLAG_REF_ROUNDING, FLAG_FP32_FMA = 1, 2, 4, 8, 16
 
 _P = c_void_p
 _BIAS = [_P, c_int64, c_int64, c_int64, c_int64]

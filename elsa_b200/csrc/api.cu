@@ -66,6 +66,7 @@ static int check_device_status() {
 struct ForwardPlan {
   int part_width, n_parts, q_chunk, tile_m, tile_n;
   bool tensor_cores;
+  bool split3;                // fp32 inputs on the tensor cores as three bf16 planes (fold_tc3.cu)
   int64_t mz_bytes, s_bytes;  // one summary set: m (== z) and s, 256-byte aligned
   int sets;                   // 1, or 2 when a ping-pong pass (scan steps / tree) was requested
 };
@@ -77,6 +78,13 @@ static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, uns
   return n_ctx >= 512 && fold_tc_supported(dtype, head_dim, has_bias);
 }
 
+// fp32 on the tensor cores: head dim 64, no bias, and long enough that 128-row tiles fill the machine better than the
+// FP32-FMA kernel's 64-row tiles do
+static bool tc3_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
+  return n_ctx >= 512 && fold_tc3_supported(dtype, head_dim, has_bias);
+}
+
 static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal,
                         bool has_bias, int part_width_in, int q_chunk_in, unsigned flags, ForwardPlan* pl) {
   if (!dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 || heads < 1 || n_ctx < 1 || head_dim < 1 ||
@@ -84,9 +92,10 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
     return ELSA_ERR_INVALID_ARGUMENT;
   const int64_t bh = static_cast<int64_t>(batch) * heads;
   if (bh > 65535) return ELSA_ERR_UNSUPPORTED;
-  pl->tensor_cores = tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  pl->tile_m = pl->tensor_cores ? 256 : 64;   // query rows per CTA
-  pl->tile_n = pl->tensor_cores ? 128 : 64;   // keys per tile
+  pl->split3 = tc3_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->tensor_cores = pl->split3 || tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->tile_m = pl->split3 ? 128 : (pl->tensor_cores ? 256 : 64);   // query rows per CTA
+  pl->tile_n = pl->tensor_cores ? 128 : 64;                          // keys per tile
   const int tiles_n = static_cast<int>(cdiv64(n_ctx, pl->tile_n));
   int n_parts;
   if (part_width_in > 0) {
@@ -151,7 +160,8 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
                            int n_keys = -1, int key_offset = 0, bool q_prescaled = false,
                            const Strides* qs = nullptr, const Strides* ks = nullptr, const Strides* vs = nullptr,
                            void* direct_out = nullptr, const Strides* os = nullptr, float* row_m = nullptr,
-                           float* row_z = nullptr) {
+                           float* row_z = nullptr, const void* q3 = nullptr, const void* k3 = nullptr,
+                           const void* v3 = nullptr) {
   if (n_keys < 0) n_keys = n_ctx;
   if (!q || !k || !v || ((!m_buf || !z_buf || !s_buf) && !direct_out) || !dtype_ok(dtype) || !dtype_ok(summary_dtype) || batch < 1 ||
       heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || q_start < 0 || q_len < 0 ||
@@ -174,6 +184,7 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.n_keys = n_keys; p.key_offset = key_offset;
   p.is_causal = is_causal ? 1 : 0;
   p.summary_dtype = summary_dtype;
+  p.q3 = q3; p.k3 = k3; p.v3 = v3;
   p.direct = direct_out ? 1 : 0;
   p.out = direct_out; p.os = os ? *os : contiguous_strides(heads, n_ctx, head_dim); p.row_m = row_m; p.row_z = row_z;
   // reference rounding point: P is cast to fp16 before P.V only for fp16 inputs whose summaries are
@@ -182,6 +193,11 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
   p.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
   if (q_prescaled) p.scale_log2 = 1.0f;   // q already carries log2(e)/sqrt(d) (reference-rounding mode, no bias)
+  if (q3 && part_width % 128 == 0) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return fold_tc3(p, st);
+  }
   if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
@@ -230,7 +246,7 @@ static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, un
 extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
   (void)is_causal;
   if (backward) return tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
-  return tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
+  return (tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
 }
 
 extern "C" int elsa_phase1_fold(const void* q, const void* k, const void* v, const float* bias, int64_t bias_stride_b,
@@ -274,7 +290,8 @@ extern "C" int64_t elsa_forward_workspace_bytes(int dtype, int summary_dtype, in
                    &pl) != ELSA_OK)
     return -1;
   return plan_bytes(pl) +
-         (ref_rounding_applies(flags, dtype, head_dim, has_bias != 0, is_causal) ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0);
+         (ref_rounding_applies(flags, dtype, head_dim, has_bias != 0, is_causal) ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0) +
+         (pl.split3 ? 3 * fold_tc3_plane_bytes(batch * heads, n_ctx) : 0);
 }
 
 // strides given by the caller: every one a multiple of 8 elements, so that rows start on 16-byte boundaries
@@ -297,7 +314,8 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
                         q_chunk, flags, &pl);
   if (rc != ELSA_OK) return rc;
   const bool ref_round = ref_rounding_applies(flags, dtype, head_dim, bias != nullptr, is_causal);
-  const int64_t need_ws = plan_bytes(pl) + (ref_round ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0);
+  const int64_t plane_bytes = pl.split3 ? fold_tc3_plane_bytes(batch * heads, n_ctx) : 0;
+  const int64_t need_ws = plan_bytes(pl) + (ref_round ? ref_rounding_bytes(batch, heads, n_ctx, head_dim) : 0) + 3 * plane_bytes;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < need_ws)
     return ELSA_ERR_WORKSPACE;
   if (!aligned16(out)) return ELSA_ERR_INVALID_ARGUMENT;
@@ -323,6 +341,16 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
   const int bh = batch * heads;
   const int store_state = row_m != nullptr;
 
+  const void *q3 = nullptr, *k3 = nullptr, *v3 = nullptr;
+  if (pl.split3) {
+    // fp32 on the tensor cores: the three bf16 planes of q, k, v, written once behind the summaries
+    char* planes = ws + plan_bytes(pl);
+    const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
+    if ((rc = fold_tc3_split(q, qs ? *qs : cs, planes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(k, ks ? *ks : cs, planes + plane_bytes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(v, vs ? *vs : cs, planes + 2 * plane_bytes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
+    q3 = planes; k3 = planes + plane_bytes; v3 = planes + 2 * plane_bytes;
+  }
   // A problem that is a single (query tile, key partition) pair of the FP32-FMA kernel (49-token windows and other
   // sequences of at most 64 tokens): phase 2 would merge one summary per row, so phase 1 finalises the rows itself,
   // with the same rounding points, and the summaries never travel through memory.
@@ -335,7 +363,7 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
     const int q_len = std::min(pl.q_chunk, n_ctx - q_start);
     rc = phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_a, z_a, s_a, dtype,
                          summary_dtype, batch, heads, n_ctx, head_dim, q_start, q_len, pl.part_width, pl.n_parts,
-                         is_causal, flags, st, -1, 0, ref_round, qs, ks, vs);
+                         is_causal, flags, st, -1, 0, ref_round, qs, ks, vs, nullptr, nullptr, nullptr, nullptr, q3, k3, v3);
     if (rc != ELSA_OK) return rc;
     if (is_causal && (flags & ELSA_FLAG_SCAN_STEPS)) {
       // log-depth Hillis-Steele inclusive scan, ping-pong between the two summary sets; the last
@@ -617,14 +645,15 @@ extern "C" int elsa_twopass_forward_static(const void* q, const void* k, const v
   // query chunk is the largest multiple of the kernel's query tile whose summaries fit the built-in array, so a
   // long problem runs as several chunks through the same array instead of being refused
   ForwardPlan pl;
-  int rc0 = plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, 0, 0u, &pl);
+  const unsigned sflags = ELSA_FLAG_FP32_FMA;   // the bf16 planes of an fp32 problem would not fit the built-in array
+  int rc0 = plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, 0, sflags, &pl);
   if (rc0 != ELSA_OK) return rc0;
   int q_chunk = 0;   // 0: the automatic chunk already fits
   if (plan_bytes(pl) > elsa::kStaticScratchBytes) {
     const int64_t row_bytes = static_cast<int64_t>(pl.n_parts) * batch * heads * (static_cast<int64_t>(head_dim) * dtype_size(dtype) + 8);
     int64_t rows = (elsa::kStaticScratchBytes / row_bytes) / pl.tile_m * pl.tile_m;
     for (; rows >= pl.tile_m; rows -= pl.tile_m) {
-      if (plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, static_cast<int>(rows), 0u, &pl) != ELSA_OK)
+      if (plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, static_cast<int>(rows), sflags, &pl) != ELSA_OK)
         return ELSA_ERR_INVALID_ARGUMENT;
       if (plan_bytes(pl) <= elsa::kStaticScratchBytes) break;
     }
@@ -636,5 +665,5 @@ extern "C" int elsa_twopass_forward_static(const void* q, const void* k, const v
   if (rc != ELSA_OK) return rc;
   // Nothing in the scratch has to start at zero: phase 1 writes every summary that phase 2 reads.
   return elsa_twopass_forward(q, k, v, nullptr, 0, 0, 0, 0, out, row_m, row_z, scratch, elsa::kStaticScratchBytes, dtype,
-                              dtype, batch, heads, n_ctx, head_dim, is_causal, 0, q_chunk, 0u, stream);
+                              dtype, batch, heads, n_ctx, head_dim, is_causal, 0, q_chunk, sflags, stream);
 }

@@ -1,0 +1,412 @@
+// Phase 1 for fp32 inputs on the 5th-generation tensor cores WITHOUT giving up fp32 accuracy: every operand is
+// split into three bf16 terms, x = x0 + x1 + x2 exactly (8 + 8 + 8 mantissa bits), and a product a*b is formed as
+// the six cross terms whose weight is at least 2^-16 of the leading one,
+//     a0 b0 + a0 b1 + a1 b0 + a1 b1 + a0 b2 + a2 b0        (dropped: a1 b2, a2 b1, a2 b2 <= 2^-24 relative),
+// each an exact bf16 x bf16 product accumulated in fp32 by tcgen05.mma (kind::f16, bf16 inputs).  The reference's own
+// route for fp32 is 3xTF32 (src/elsa_twopass_clean/attention.py:280-282, 21 significant bits per operand); this keeps
+// all 24.
+//
+// A pre-pass (split3_kernel) writes the three bf16 planes of q, k, v once per forward call.  One CTA (256 threads,
+// 1 per SM) owns ONE 128-row query tile of one (batch*head) and one K partition, walked in 128-key tiles:
+//
+//   warp 4      TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
+//                              order the issuer consumes them: K planes of key tile j+1, V planes of key tile j
+//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
+//                              into the S buffer the fold warps are not reading (two S buffers);
+//                              O += sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each
+//   warps 0-3   fold           one thread per query row: S row from TMEM, running max, exp2, row sum, P split into
+//                              its three bf16 planes (own TMEM columns), exp-rescale of O when the max moved
+//
+// TMEM columns: S_a [0,128) S_b [128,256) O [256,320) P0 [320,384) P1 [384,448) P2 [448,512).
+// Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3800 cycles), the ex2 unit 1024 cycles: unlike
+// the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate -- roughly ten times the
+// rate of the FP32-FMA kernel.
+#include <type_traits>
+
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace elsa {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kSlots = 8;
+constexpr int kPlaneBytes = 128 * 64 * 2;                      // one 128 x 64 bf16 plane tile
+constexpr int kFold3Smem = (3 + kSlots) * kPlaneBytes + 1024;  // + alignment slack
+constexpr int kThreads = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kProducerWarp = 4, kIssuerWarp = 5;
+constexpr float kRescaleThreshold = 8.0f;
+
+enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, BAR_O = 36, BAR_SFREE = 37, BAR_PV = 38 };
+
+struct Fold3Params {
+  float* m; float* z; void* s;
+  int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
+  int n_keys, key_offset;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&w)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]),
+        "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+}
+
+template <typename TS>
+__device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64]) {
+  if constexpr (sizeof(TS) == 4) {
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; i += 8) {
+      uint4 t;
+      t.x = pack2<TS>(v[i], v[i + 1]); t.y = pack2<TS>(v[i + 2], v[i + 3]);
+      t.z = pack2<TS>(v[i + 4], v[i + 5]); t.w = pack2<TS>(v[i + 6], v[i + 7]);
+      *reinterpret_cast<uint4*>(dst + i) = t;
+    }
+  }
+}
+
+// x (4 consecutive fp32 of a row, any strides) -> three bf16 planes [3][B*H][rows][64], contiguous
+__global__ void __launch_bounds__(256)
+split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ planes, int heads, int rows, Strides st,
+              int64_t plane_elems) {
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
+  const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
+  if (r >= rows) return;
+  const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
+  const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c);
+  const float in[4] = {v.x, v.y, v.z, v.w};
+  __nv_bfloat16 o[3][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat16 b0 = __float2bfloat16_rn(in[i]);
+    const float r1 = in[i] - __bfloat162float(b0);
+    const __nv_bfloat16 b1 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(b1);
+    o[0][i] = b0; o[1][i] = b1; o[2][i] = __float2bfloat16_rn(r2);
+  }
+  const int64_t off = (static_cast<int64_t>(bh) * rows + r) * 64 + c;
+#pragma unroll
+  for (int p = 0; p < 3; ++p) *reinterpret_cast<uint2*>(planes + p * plane_elems + off) = *reinterpret_cast<const uint2*>(o[p]);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const Fold3Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kSlots + 8];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.z, part = blockIdx.y;
+  const int q0 = prm.q_start + blockIdx.x * 128;
+  const int q_end = prm.q_start + prm.q_len;
+  const int k_begin = part * prm.part_width;
+  const int k_end = min(prm.n_keys, k_begin + prm.part_width);   // local key indices
+  const int koff = prm.key_offset;
+  int ke = k_end;
+  if (prm.is_causal) ke = min(ke, min(q0 + 128, q_end) - koff);   // keys above the tile's last row are never admissible
+  const int n_t = (q0 < q_end && ke > k_begin) ? (ke - k_begin + 127) / 128 : 0;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto sQ = [&](int p) { return smem_base + p * kPlaneBytes; };
+  auto sSlot = [&](int i) { return smem_base + (3 + i) * kPlaneBytes; };
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_q = bar0;
+  auto bar_full = [&](int i) { return bar0 + 8 * (1 + i); };
+  auto bar_free = [&](int i) { return bar0 + 8 * (1 + kSlots + i); };
+  auto bar_s = [&](int b) { return bar0 + 8 * (1 + 2 * kSlots + b); };
+  auto bar_sfree = [&](int b) { return bar0 + 8 * (3 + 2 * kSlots + b); };
+  const uint32_t bar_p = bar0 + 8 * (5 + 2 * kSlots), bar_pv = bar0 + 8 * (6 + 2 * kSlots), bar_o = bar0 + 8 * (7 + 2 * kSlots);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < kSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_s(b), 1); mbar_init(bar_sfree(b), 128); }
+    mbar_init(bar_p, 128); mbar_init(bar_pv, 1); mbar_init(bar_o, 1);
+    fence_mbar_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;
+  const uint32_t tP[3] = {tmem_base + 320, tmem_base + 384, tmem_base + 448};
+
+  if (warp == kProducerWarp) {
+    if (n_t > 0 && lane == 0) {
+      // ---------------- TMA producer ----------------
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(bar_q, 3 * kPlaneBytes);
+      for (int p = 0; p < 3; ++p) tma_load_4d(sQ(p), &tmap_q, bar_q, 0, q0, bh, p);
+      int seq = 0;
+      bool ok = true;
+      auto load = [&](const CUtensorMap* map, int tile, int plane) {
+        const int slot = seq % kSlots;
+        if (seq >= kSlots && !mbar_wait(bar_free(slot), ((seq / kSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE)) { ok = false; return; }
+        mbar_arrive_expect_tx(bar_full(slot), kPlaneBytes);
+        tma_load_4d(sSlot(slot), map, bar_full(slot), 0, k_begin + tile * 128, bh, plane);
+        ++seq;
+      };
+      for (int p = 0; p < 3 && ok; ++p) load(&tmap_k, 0, p);
+      for (int j = 0; j < n_t && ok; ++j) {
+        if (j + 1 < n_t)
+          for (int p = 0; p < 3 && ok; ++p) load(&tmap_k, j + 1, p);
+        for (int p = 0; p < 3 && ok; ++p) load(&tmap_v, j, p);
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    if (n_t > 0 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc_s = make_idesc(1u, 0, 0, 128, 128);   // S += Qp Kp^T : bf16, A, B K-major
+      constexpr uint32_t idesc_o = make_idesc(1u, 0, 1, 128, 64);    // O += Pp Vp   : A in TMEM, B (V) MN-major
+      const uint64_t dq[3] = {make_sdesc(sQ(0), 16, 1024), make_sdesc(sQ(1), 16, 1024), make_sdesc(sQ(2), 16, 1024)};
+      const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dv_slot0 = make_sdesc(sSlot(0), 128 * 128, 1024);
+      constexpr uint64_t kSlotStep = kPlaneBytes >> 4;   // descriptor address field counts 16-byte units
+      int seq = 0;
+      bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q);
+      // the six (q plane, k plane) pairs of one key tile into S buffer b; K planes arrive in ring order
+      auto issue_s = [&](int b) {
+        for (int kp = 0; kp < 3 && ok; ++kp) {
+          const int slot = seq % kSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          const uint64_t dk = dk_slot0 + slot * kSlotStep;
+          for (int qp = 0; qp + kp <= 2; ++qp) mma_ss_x4<2, 2>(tS[b], dq[qp], dk, idesc_s, (kp == 0 && qp == 0) ? 0u : 1u);
+          mma_commit(bar_free(slot));     // the plane tile is free again once these MMAs have retired
+          ++seq;
+        }
+        if (ok) mma_commit(bar_s(b));
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; ok && j < n_t; ++j) {
+        if (j + 1 < n_t) {
+          // S buffer (j+1)&1 held S(j-1): the fold warps must have pulled it into registers
+          if (j >= 1 && !(ok = mbar_wait(bar_sfree((j + 1) & 1), ((j - 1) / 2) & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          issue_s((j + 1) & 1);
+          if (!ok) break;
+        }
+        if (!(ok = mbar_wait(bar_p, j & 1, &abort_flag, prm.status, BAR_P))) break;
+        tc_fence_after();
+        for (int vp = 0; vp < 3 && ok; ++vp) {
+          const int slot = seq % kSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) break;
+          tc_fence_after();
+          const uint64_t dv = dv_slot0 + slot * kSlotStep;
+          for (int pp = 0; pp + vp <= 2; ++pp) {
+            mma_ts_x4<8, 128>(tO, tP[pp], dv, idesc_o, (j == 0 && vp == 0 && pp == 0) ? 0u : 1u);
+            mma_ts_x4<8, 128>(tO, tP[pp] + 32, dv + 512, idesc_o, 1u);
+          }
+          mma_commit(bar_free(slot));
+          ++seq;
+        }
+        if (ok) mma_commit(bar_pv);      // the P planes may be overwritten, O may be rescaled
+      }
+      if (ok) mma_commit(bar_o);
+    }
+  } else if (warp < 4) {
+    // ---------------- fold warps: one thread per query row ----------------
+    const int row = warp * 32 + lane;                       // row within the tile == TMEM lane
+    const int qi = q0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const float c = prm.scale_log2;
+    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;
+    bool alive = true;
+
+    for (int j = 0; j < n_t; ++j) {
+      const int b = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(b), (j / 2) & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
+      tc_fence_after();
+      float sv[128];
+#pragma unroll
+      for (int cchunk = 0; cchunk < 4; ++cchunk) {
+        uint32_t r[32];
+        tmem_ld32(tS[b] + lane_off + 32 * cchunk, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[32 * cchunk + i] = __uint_as_float(r[i]);
+      }
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_sfree(b));      // this S buffer may be overwritten with the scores of key tile j + 2
+      const int k0 = k_begin + j * 128;
+      const bool tail = k0 + 128 > k_end;
+      const bool diag = prm.is_causal && (k0 + koff + 127 > q0);
+      if (tail || diag) {
+        const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > lim) sv[i] = -CUDART_INF_F;
+      }
+      float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+      for (int i = 4; i < 124; i += 8) {
+        mx[0] = max3f(mx[0], sv[i], sv[i + 1]); mx[1] = max3f(mx[1], sv[i + 2], sv[i + 3]);
+        mx[2] = max3f(mx[2], sv[i + 4], sv[i + 5]); mx[3] = max3f(mx[3], sv[i + 6], sv[i + 7]);
+      }
+      mx[0] = max3f(mx[0], sv[124], sv[125]);
+      mx[1] = max3f(mx[1], sv[126], sv[127]);
+      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      tmax *= c;
+      m_true = fmaxf(m_true, tmax);
+      if (j > 0) {
+        // P V of the previous key tile must have retired before the P planes are overwritten or O is rescaled
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
+        tc_fence_after();
+      }
+      const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
+      if (__any_sync(0xffffffffu, move)) {
+        const float m_new = fmaxf(m_ref, tmax);
+        const float alpha = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_ref - m_new);
+        zsum *= alpha;
+        if (j > 0) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld32(tO + lane_off + 32 * h, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(tO + lane_off + 32 * h, r);
+          }
+        }
+        m_ref = m_new;
+      }
+      const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+      // p = 2^(s*c - m) (full-precision exp2: this is the fp32 path), row sum in four accumulators, and the split of
+      // p into its three bf16 planes, 32 keys (16 packed pairs per plane) at a time
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[3][16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2f(fmaf(sv[32 * ch + 2 * i], c, -m_use));
+          const float p1 = exp2f(fmaf(sv[32 * ch + 2 * i + 1], c, -m_use));
+          ps[i & 3] += p0 + p1;
+          const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0, p1);
+          const float2 f0 = __bfloat1622float2(a0);
+          const float r0 = p0 - f0.x, r1 = p1 - f0.y;
+          const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
+          const float2 f1 = __bfloat1622float2(a1);
+          const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
+          pk[0][i] = *reinterpret_cast<const uint32_t*>(&a0);
+          pk[1][i] = *reinterpret_cast<const uint32_t*>(&a1);
+          pk[2][i] = *reinterpret_cast<const uint32_t*>(&a2);
+        }
+#pragma unroll
+        for (int p = 0; p < 3; ++p) tmem_st16(tP[p] + lane_off + 16 * ch, pk[p]);
+      }
+      tmem_wait_st();               // (also covers the O rescale stores above)
+      tc_fence_before();
+      mbar_arrive(bar_p);
+      zsum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+    }
+
+    // epilogue: renormalise to the true max and write the summary row
+    const int r_chunk = blockIdx.x * 128 + row;   // row within the query chunk
+    const bool row_ok = r_chunk < prm.q_len;
+    const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
+    float ov[64];
+    float m_out = -CUDART_INF_F, z_out = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) ov[i] = 0.f;
+    if (n_t > 0) {
+      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, prm.status, BAR_O))) alive = false;
+      if (alive) {
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(tO + lane_off + 32 * h, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[32 * h + i] = __uint_as_float(r[i]);
+        }
+        tmem_wait_ld();
+        const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true);
+        z_out = zsum * f;
+        m_out = z_out > 0.f ? m_true : -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) ov[i] = z_out > 0.f ? ov[i] * f : 0.f;
+      }
+    }
+    if (row_ok && (alive || n_t == 0)) {
+      prm.m[ro] = m_out;
+      prm.z[ro] = z_out;
+      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
+      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
+      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+bool fold_tc3_supported(int dtype, int head_dim, bool has_bias) {
+  return dtype == ELSA_F32 && head_dim == 64 && !has_bias && fold_tc_supported(ELSA_BF16, 64, false);
+}
+
+int64_t fold_tc3_plane_bytes(int bh, int rows) { return align_up(static_cast<int64_t>(3) * bh * rows * 64 * 2, 256); }
+
+// planes: [3][bh][rows][64] bf16 of the fp32 tensor x ([B, H, rows, 64] view with strides st)
+int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, cudaStream_t stream) {
+  if (rows <= 0) return ELSA_OK;
+  if ((st.b | st.h | st.r) % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+  const int bh = batch * heads;
+  const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(rows) * 16, 256)), static_cast<unsigned>(bh));
+  split3_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(planes), heads, rows, st,
+                                          static_cast<int64_t>(bh) * rows * 64);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+// p.q3 / p.k3 / p.v3: the plane buffers written by fold_tc3_split for the whole problem (all query rows / this
+// launch's key rows)
+int fold_tc3(const FoldParams& p, cudaStream_t st) {
+  if (!p.q3 || !p.k3 || !p.v3 || p.head_dim != 64 || p.bias || p.part_width % 128 != 0) return ELSA_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  // planes as a [3, B*H, rows, 64] bf16 tensor: the "head" coordinate is (batch*head), the "batch" coordinate the plane
+  const Strides sq = contiguous_strides(p.bh, p.n_ctx, 64), sk = contiguous_strides(p.bh, p.n_keys, 64);
+  if ((rc = make_tmap_rows64(&mq, p.q3, ELSA_BF16, p.n_ctx, p.bh, 3, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k3, ELSA_BF16, p.n_keys, p.bh, 3, sk, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v3, ELSA_BF16, p.n_keys, p.bh, 3, sk, 128)) != ELSA_OK) return rc;
+  Fold3Params prm;
+  prm.m = p.m; prm.z = p.z; prm.s = p.s;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
+  prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
+  prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
+  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
+  prm.scale_log2 = p.scale_log2;
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tc3_kernel), kFold3Smem);
+  if (rc != ELSA_OK) return rc;
+  dim3 grid(static_cast<unsigned>((p.q_len + 127) / 128), static_cast<unsigned>(p.n_parts), static_cast<unsigned>(p.bh));
+  fold_tc3_kernel<<<grid, kThreads, kFold3Smem, st>>>(mq, mk, mv, prm);
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+}  // namespace elsa

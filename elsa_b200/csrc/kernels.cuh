@@ -29,6 +29,8 @@ struct FoldParams {
   // not null, the row state, instead of a summary -- phase 2 would merge a single element
   int direct;
   void* out; Strides os; float* row_m; float* row_z;
+  // fp32 inputs on the tensor cores: the three bf16 planes of q, k, v written by fold_tc3_split (null otherwise)
+  const void* q3; const void* k3; const void* v3;
 };
 
 struct BwdParams {
@@ -71,6 +73,11 @@ int device_status_word(int** dev_ptr, volatile int** host_ptr);
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
 int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
+// tcgen05 fold for fp32 inputs split into three bf16 planes (fold_tc3.cu)
+bool fold_tc3_supported(int dtype, int head_dim, bool has_bias);
+int64_t fold_tc3_plane_bytes(int bh, int rows);
+int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, cudaStream_t stream);
+int fold_tc3(const FoldParams& p, cudaStream_t st);
 // tcgen05 backward (bwd_tc.cu); workspace = padded D / LSE vectors + fp32 dQ accumulator
 bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc_workspace_bytes(int bh, int n_ctx);

@@ -48,6 +48,9 @@ enum elsa_status {
 #define ELSA_FLAG_FORCE_SIMT 1u   /* never take the tcgen05 kernels (debug / A-B checks) */
 #define ELSA_FLAG_SCAN_STEPS 2u   /* causal: run the log-depth Hillis-Steele steps instead of the one-pass merge */
 #define ELSA_FLAG_TREE_MERGE 4u   /* non-causal: run the Blelloch up-sweep levels instead of the one-pass merge */
+#define ELSA_FLAG_FP32_FMA 16u     /* forward, fp32 inputs: stay on the FP32-FMA kernel instead of the tensor-core kernel that
+                                     works on three bf16 planes per operand (same accuracy class; the planes cost
+                                     1.5 x the size of q, k, v in workspace) */
 #define ELSA_FLAG_REF_ROUNDING 8u /* forward, fp16 / head dim 64 / no bias / not causal only: reproduce the rounding points of
                                      the reference's fp16 d=64 kernels (q * log2(e)/8 formed in fp16, scores unscaled:
                                      attention_parallel_scan.py:153-154,160) instead of the exact fp32 scale; the workspace

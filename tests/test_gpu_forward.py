@@ -270,3 +270,28 @@ def test_non_contiguous_inputs_and_errors():
         E.twopass_attention(q, k, v, bias=torch.zeros(n, n + 1, device=DEV))
     with pytest.raises(ValueError, match="3D bias"):
         E.twopass_attention(q, k, v, bias=torch.zeros(2, n, n, device=DEV))
+
+
+@pytest.mark.parametrize("b,h,n,causal,block_n", [(1, 2, 513, False, None), (1, 8, 1024, False, None), (1, 2, 1000, True, None),
+                                                  (2, 2, 4097, False, 2048), (1, 2, 2304, True, 256)])
+def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, block_n):
+    """fp32 inputs with head dim 64 run phase 1 on the tensor cores as three bf16 planes per operand (six cross
+    products per contraction); ELSA_FLAG_FP32_FMA keeps the exact-FMA kernel.  Both must sit within the fp32 bound of
+    fp64 softmax attention, and within it of each other."""
+    from elsa_b200 import _lib
+    from elsa_b200.attention import _forward_impl
+    lib = _lib.load()
+    assert lib.elsa_uses_tensor_cores(0, 64, n, 0, int(causal), 0) == 1
+    q, k, v = (U.seeded((b, h, n, 64), F32, 500 + i).to(DEV) for i in range(3))
+    pw = 0 if block_n is None else block_n
+    tc = _forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=F32, part_width=pw, q_chunk=0, want_state=True)
+    fma = _forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=F32, part_width=pw, q_chunk=0, want_state=True,
+                        flags=_lib.FLAG_FP32_FMA)
+    truth = O.softmax_attention_fp64(q.cpu(), k.cpu(), v.cpu(), is_causal=causal)
+    assert U.out_close(tc[0], truth, F32) <= 1.0
+    assert U.out_close(fma[0], truth, F32) <= 1.0
+    assert U.max_abs(tc[0], fma[0]) <= 1e-6
+    # row state: m in the log2 domain, z relative
+    assert U.max_abs(tc[1], fma[1]) <= 2e-5
+    assert ((tc[2] - fma[2]).abs() / fma[2]).max().item() <= 1e-5
+    assert lib.elsa_device_status(0) == 0
