@@ -11,16 +11,25 @@
 //
 //   warp 4      TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
 //                              order the issuer consumes them: K planes of key tile j+1, V planes of key tile j
-//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
-//                              into the S buffer the fold warps are not reading (two S buffers);
-//                              O += sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each
-//   warps 0-3   fold           one thread per query row: S row from TMEM, running max, exp2, row sum, P split into
-//                              its three bf16 planes (own TMEM columns), exp-rescale of O when the max moved
+//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each;
+//                              O_j = sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each,
+//                              into a FRESH accumulator per key tile (two O buffers)
+//   warps 0-3   fold           one thread per query row: row max from a first pass over the S row in TMEM, then a
+//                              second pass: exp2, row sum, P split into its three bf16 planes (own TMEM columns);
+//                              the row's running output lives in registers and takes in O_{j-1} with ordinary fp32
+//                              additions
 //
-// TMEM columns: S_a [0,128) S_b [128,256) O [256,320) P0 [320,384) P1 [384,448) P2 [448,512).
+// Accuracy.  tcgen05.mma adds into its fp32 accumulator by truncation: every accumulating instruction loses up to one
+// unit in the last place of the accumulator, always towards zero.  Accumulating P V of a whole partition in TMEM (as
+// the 16-bit kernel does: invisible at 16-bit output precision) would cost 48 such losses per key tile -- 1.6e-6 on an
+// output of 0.1 after five key tiles, measured.  Therefore (a) every key tile gets a fresh accumulator and the running
+// sum over key tiles is kept by the fold warps in registers, and (b) within a tile the cross terms are issued in order
+// of increasing weight (x0*y2, x1*y1, x1*y0 ... x0*y0 last), so only the instructions of the leading term work at
+// full magnitude.
+//
+// TMEM columns: S [0,128) O_a [128,192) O_b [192,256) P0 [256,320) P1 [320,384) P2 [384,448).
 // Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3800 cycles), the ex2 unit 1024 cycles: unlike
-// the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate -- roughly ten times the
-// rate of the FP32-FMA kernel.
+// the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate.
 #include <type_traits>
 
 #include "kernels.cuh"
@@ -107,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Fold3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kSlots + 8];
+  __shared__ __align__(8) uint64_t bars[2 * kSlots + 5];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -129,16 +138,15 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar_q = bar0;
   auto bar_full = [&](int i) { return bar0 + 8 * (1 + i); };
   auto bar_free = [&](int i) { return bar0 + 8 * (1 + kSlots + i); };
-  auto bar_s = [&](int b) { return bar0 + 8 * (1 + 2 * kSlots + b); };
-  auto bar_sfree = [&](int b) { return bar0 + 8 * (3 + 2 * kSlots + b); };
-  const uint32_t bar_p = bar0 + 8 * (5 + 2 * kSlots), bar_pv = bar0 + 8 * (6 + 2 * kSlots), bar_o = bar0 + 8 * (7 + 2 * kSlots);
+  const uint32_t bar_s = bar0 + 8 * (1 + 2 * kSlots), bar_sfree = bar0 + 8 * (2 + 2 * kSlots);
+  const uint32_t bar_p = bar0 + 8 * (3 + 2 * kSlots), bar_pv = bar0 + 8 * (4 + 2 * kSlots);
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int i = 0; i < kSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(bar_s(b), 1); mbar_init(bar_sfree(b), 128); }
-    mbar_init(bar_p, 128); mbar_init(bar_pv, 1); mbar_init(bar_o, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_sfree, 128);
+    mbar_init(bar_p, 128); mbar_init(bar_pv, 1);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -149,9 +157,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tO = tmem_base + 256;
-  const uint32_t tP[3] = {tmem_base + 320, tmem_base + 384, tmem_base + 448};
+  const uint32_t tS = tmem_base;
+  const uint32_t tO[2] = {tmem_base + 128, tmem_base + 192};
+  const uint32_t tP[3] = {tmem_base + 256, tmem_base + 320, tmem_base + 384};
 
   if (warp == kProducerWarp) {
     if (n_t > 0 && lane == 0) {
@@ -168,11 +176,11 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tma_load_4d(sSlot(slot), map, bar_full(slot), 0, k_begin + tile * 128, bh, plane);
         ++seq;
       };
-      for (int p = 0; p < 3 && ok; ++p) load(&tmap_k, 0, p);
+      for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, 0, p);       // planes in the order of increasing weight
       for (int j = 0; j < n_t && ok; ++j) {
         if (j + 1 < n_t)
-          for (int p = 0; p < 3 && ok; ++p) load(&tmap_k, j + 1, p);
-        for (int p = 0; p < 3 && ok; ++p) load(&tmap_v, j, p);
+          for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, j + 1, p);
+        for (int p = 2; p >= 0 && ok; --p) load(&tmap_v, j, p);
       }
     }
   } else if (warp == kIssuerWarp) {
@@ -185,44 +193,50 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       constexpr uint64_t kSlotStep = kPlaneBytes >> 4;   // descriptor address field counts 16-byte units
       int seq = 0;
       bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q);
-      // the six (q plane, k plane) pairs of one key tile into S buffer b; K planes arrive in ring order
-      auto issue_s = [&](int b) {
-        for (int kp = 0; kp < 3 && ok; ++kp) {
+      // the six (q plane, k plane) pairs of one key tile; K planes arrive in ring order 2, 1, 0 and within a plane
+      // the q planes go from the lightest admissible one down to q0: the leading term q0 k0 is the last to be added
+      auto issue_s = [&]() {
+        bool first = true;
+        for (int kp = 2; kp >= 0 && ok; --kp) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           const uint64_t dk = dk_slot0 + slot * kSlotStep;
-          for (int qp = 0; qp + kp <= 2; ++qp) mma_ss_x4<2, 2>(tS[b], dq[qp], dk, idesc_s, (kp == 0 && qp == 0) ? 0u : 1u);
+          for (int qp = 2 - kp; qp >= 0; --qp) {
+            mma_ss_x4<2, 2>(tS, dq[qp], dk, idesc_s, first ? 0u : 1u);
+            first = false;
+          }
           mma_commit(bar_free(slot));     // the plane tile is free again once these MMAs have retired
           ++seq;
         }
-        if (ok) mma_commit(bar_s(b));
+        if (ok) mma_commit(bar_s);
       };
-      if (ok) issue_s(0);
+      if (ok) issue_s();
       for (int j = 0; ok && j < n_t; ++j) {
         if (j + 1 < n_t) {
-          // S buffer (j+1)&1 held S(j-1): the fold warps must have pulled it into registers
-          if (j >= 1 && !(ok = mbar_wait(bar_sfree((j + 1) & 1), ((j - 1) / 2) & 1, &abort_flag, prm.status, BAR_SFREE))) break;
-          issue_s((j + 1) & 1);
+          // one S buffer: the fold warps must have finished their second pass over S(j)
+          if (!(ok = mbar_wait(bar_sfree, j & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          issue_s();
           if (!ok) break;
         }
         if (!(ok = mbar_wait(bar_p, j & 1, &abort_flag, prm.status, BAR_P))) break;
         tc_fence_after();
-        for (int vp = 0; vp < 3 && ok; ++vp) {
+        bool first = true;               // O_j starts from zero: a fresh accumulator per key tile
+        for (int vp = 2; vp >= 0 && ok; --vp) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) break;
           tc_fence_after();
           const uint64_t dv = dv_slot0 + slot * kSlotStep;
-          for (int pp = 0; pp + vp <= 2; ++pp) {
-            mma_ts_x4<8, 128>(tO, tP[pp], dv, idesc_o, (j == 0 && vp == 0 && pp == 0) ? 0u : 1u);
-            mma_ts_x4<8, 128>(tO, tP[pp] + 32, dv + 512, idesc_o, 1u);
+          for (int pp = 2 - vp; pp >= 0; --pp) {
+            mma_ts_x4<8, 128>(tO[j & 1], tP[pp], dv, idesc_o, first ? 0u : 1u);
+            mma_ts_x4<8, 128>(tO[j & 1], tP[pp] + 32, dv + 512, idesc_o, 1u);
+            first = false;
           }
           mma_commit(bar_free(slot));
           ++seq;
         }
-        if (ok) mma_commit(bar_pv);      // the P planes may be overwritten, O may be rescaled
+        if (ok) mma_commit(bar_pv);      // O_j is complete; the P planes may be overwritten
       }
-      if (ok) mma_commit(bar_o);
     }
   } else if (warp < 4) {
     // ---------------- fold warps: one thread per query row ----------------
@@ -231,77 +245,87 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
     const float c = prm.scale_log2;
     float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;
+    float o_run[64];                                        // running sum of O over the key tiles, relative to m_ref
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o_run[i] = 0.f;
     bool alive = true;
 
-    for (int j = 0; j < n_t; ++j) {
-      const int b = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(b), (j / 2) & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
-      tc_fence_after();
-      float sv[128];
+    // o_run += O_b (the finished P V of one key tile)
+    auto take_o = [&](int b) {
 #pragma unroll
-      for (int cchunk = 0; cchunk < 4; ++cchunk) {
+      for (int h = 0; h < 2; ++h) {
         uint32_t r[32];
-        tmem_ld32(tS[b] + lane_off + 32 * cchunk, r);
+        tmem_ld32(tO[b] + lane_off + 32 * h, r);
+        tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[32 * cchunk + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) o_run[32 * h + i] += __uint_as_float(r[i]);
       }
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar_sfree(b));      // this S buffer may be overwritten with the scores of key tile j + 2
+    };
+
+    for (int j = 0; j < n_t; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
+      tc_fence_after();
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0);
-      if (tail || diag) {
-        const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
+      const bool masked = tail || diag;
+      const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
+      // ---- pass 1 over the S row: the row max (the row itself stays in TMEM) ----
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (k0 + i > lim) sv[i] = -CUDART_INF_F;
-      }
-      float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + 32 * ch, r);
+        tmem_wait_ld();
 #pragma unroll
-      for (int i = 4; i < 124; i += 8) {
-        mx[0] = max3f(mx[0], sv[i], sv[i + 1]); mx[1] = max3f(mx[1], sv[i + 2], sv[i + 3]);
-        mx[2] = max3f(mx[2], sv[i + 4], sv[i + 5]); mx[3] = max3f(mx[3], sv[i + 6], sv[i + 7]);
+        for (int i = 0; i < 32; i += 8) {
+          float t[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) t[e] = (masked && k0 + 32 * ch + i + e > lim) ? -CUDART_INF_F : __uint_as_float(r[i + e]);
+          mx[0] = max3f(mx[0], t[0], t[1]); mx[1] = max3f(mx[1], t[2], t[3]);
+          mx[2] = max3f(mx[2], t[4], t[5]); mx[3] = max3f(mx[3], t[6], t[7]);
+        }
       }
-      mx[0] = max3f(mx[0], sv[124], sv[125]);
-      mx[1] = max3f(mx[1], sv[126], sv[127]);
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
       if (j > 0) {
-        // P V of the previous key tile must have retired before the P planes are overwritten or O is rescaled
+        // P V of the previous key tile has retired: its O goes into the running sum (both are relative to the m_ref
+        // of that tile), and the P planes may be overwritten
         if (!__all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
         tc_fence_after();
+        take_o((j - 1) & 1);
       }
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
-      if (__any_sync(0xffffffffu, move)) {
+      if (move) {
         const float m_new = fmaxf(m_ref, tmax);
         const float alpha = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_ref - m_new);
         zsum *= alpha;
-        if (j > 0) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            tmem_ld32(tO + lane_off + 32 * h, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO + lane_off + 32 * h, r);
-          }
-        }
+        for (int i = 0; i < 64; ++i) o_run[i] *= alpha;
         m_ref = m_new;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      // p = 2^(s*c - m) (full-precision exp2: this is the fp32 path), row sum in four accumulators, and the split of
-      // p into its three bf16 planes, 32 keys (16 packed pairs per plane) at a time
+      // ---- pass 2: p = 2^(s*c - m) (full-precision exp2: this is the fp32 path), row sum, and the split of p into
+      // its three bf16 planes, 32 keys (16 packed pairs per plane) at a time ----
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + 32 * ch, r);
+        tmem_wait_ld();
+        if (ch == 3) {                  // the whole row has been read twice: S may be overwritten
+          tc_fence_before();
+          mbar_arrive(bar_sfree);
+        }
         uint32_t pk[3][16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = exp2f(fmaf(sv[32 * ch + 2 * i], c, -m_use));
-          const float p1 = exp2f(fmaf(sv[32 * ch + 2 * i + 1], c, -m_use));
+          const int kk = k0 + 32 * ch + 2 * i;
+          const float s0 = (masked && kk > lim) ? -CUDART_INF_F : __uint_as_float(r[2 * i]);
+          const float s1 = (masked && kk + 1 > lim) ? -CUDART_INF_F : __uint_as_float(r[2 * i + 1]);
+          const float p0 = exp2f(fmaf(s0, c, -m_use));
+          const float p1 = exp2f(fmaf(s1, c, -m_use));
           ps[i & 3] += p0 + p1;
           const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0, p1);
           const float2 f0 = __bfloat1622float2(a0);
@@ -316,45 +340,35 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int p = 0; p < 3; ++p) tmem_st16(tP[p] + lane_off + 16 * ch, pk[p]);
       }
-      tmem_wait_st();               // (also covers the O rescale stores above)
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
       zsum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
     }
 
-    // epilogue: renormalise to the true max and write the summary row
+    // epilogue: the last key tile's O, renormalisation to the true max, the summary row
     const int r_chunk = blockIdx.x * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
-    float ov[64];
     float m_out = -CUDART_INF_F, z_out = 0.f;
-#pragma unroll
-    for (int i = 0; i < 64; ++i) ov[i] = 0.f;
     if (n_t > 0) {
-      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, prm.status, BAR_O))) alive = false;
+      if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_pv, (n_t - 1) & 1, &abort_flag, prm.status, BAR_O))) alive = false;
       if (alive) {
         tc_fence_after();
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
-          tmem_ld32(tO + lane_off + 32 * h, r);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ov[32 * h + i] = __uint_as_float(r[i]);
-        }
-        tmem_wait_ld();
+        take_o((n_t - 1) & 1);
         const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true);
         z_out = zsum * f;
         m_out = z_out > 0.f ? m_true : -CUDART_INF_F;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) ov[i] = z_out > 0.f ? ov[i] * f : 0.f;
+        for (int i = 0; i < 64; ++i) o_run[i] = z_out > 0.f ? o_run[i] * f : 0.f;
       }
     }
     if (row_ok && (alive || n_t == 0)) {
       prm.m[ro] = m_out;
       prm.z[ro] = z_out;
-      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
-      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
-      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, o_run);
+      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, o_run);
+      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, o_run);
     }
   }
 
