@@ -32,6 +32,8 @@ SIGNATURES = {
     "elsa_phase1_fold": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_uint, _P]),
     "elsa_phase1_fold_shard": (c_int, [_P, _P, _P, _P, _P, _P] + [c_int] * 11 + [c_uint, _P]),
+    "elsa_phase1_fold_shard_workspace_bytes": (c_int64, [c_int] * 6 + [c_uint]),
+    "elsa_phase1_fold_shard_ws": (c_int, [_P] * 7 + [c_int64] + [c_int] * 11 + [c_uint, _P]),
     "elsa_merge_partial": (c_int, [_P] * 6 + [c_int] * 5 + [_P]),
     "elsa_shard_chunk_elems": (c_int64, [c_int] * 4),
     "elsa_shard_pack": (c_int, [_P] * 5 + [c_int] * 4 + [_P]),

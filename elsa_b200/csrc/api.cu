@@ -268,6 +268,40 @@ extern "C" int elsa_phase1_fold_shard(const void* q, const void* k, const void* 
                          n_keys, key_offset);
 }
 
+// The shard fold with a workspace: fp32 inputs then run on the tensor cores (three bf16 planes per operand, written
+// into the workspace); every other case is the plain shard fold and needs no workspace.
+extern "C" int64_t elsa_phase1_fold_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
+                                                          int n_keys, unsigned flags) {
+  if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || n_keys < 0) return -1;
+  if (n_keys == 0 || !tc3_forward_ok(dtype, head_dim, n_ctx, false, flags)) return 0;
+  return fold_tc3_plane_bytes(batch * heads, n_ctx) + 2 * fold_tc3_plane_bytes(batch * heads, n_keys);
+}
+
+extern "C" int elsa_phase1_fold_shard_ws(const void* q, const void* k, const void* v, float* m_buf, float* z_buf,
+                                         void* s_buf, void* workspace, int64_t workspace_bytes, int dtype,
+                                         int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int n_keys,
+                                         int key_offset, int part_width, int n_parts, int is_causal, unsigned flags,
+                                         void* stream) {
+  const int64_t need = elsa_phase1_fold_shard_workspace_bytes(dtype, batch, heads, n_ctx, head_dim, n_keys, flags);
+  if (need < 0) return ELSA_ERR_INVALID_ARGUMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  const void *q3 = nullptr, *k3 = nullptr, *v3 = nullptr;
+  if (need > 0 && part_width % 128 == 0) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < need) return ELSA_ERR_WORKSPACE;
+    if (!q || !k || !v) return ELSA_ERR_INVALID_ARGUMENT;
+    char* planes = static_cast<char*>(workspace);
+    const int64_t qb = fold_tc3_plane_bytes(batch * heads, n_ctx), kb = fold_tc3_plane_bytes(batch * heads, n_keys);
+    int rc;
+    if ((rc = fold_tc3_split(q, contiguous_strides(heads, n_ctx, head_dim), planes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(k, contiguous_strides(heads, n_keys, head_dim), planes + qb, batch, heads, n_keys, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(v, contiguous_strides(heads, n_keys, head_dim), planes + qb + kb, batch, heads, n_keys, st)) != ELSA_OK) return rc;
+    q3 = planes; k3 = planes + qb; v3 = planes + qb + kb;
+  }
+  return phase1_dispatch(q, k, v, nullptr, 0, 0, 0, 0, m_buf, z_buf, s_buf, dtype, summary_dtype, batch, heads, n_ctx,
+                         head_dim, 0, n_ctx, part_width, n_parts, is_causal, flags, st, n_keys, key_offset, false, nullptr,
+                         nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q3, k3, v3);
+}
+
 extern "C" int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
                                  int has_bias, int is_causal, int part_width_in, int q_chunk_in, unsigned flags,
                                  int* part_width, int* n_parts, int* q_chunk) {

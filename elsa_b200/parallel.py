@@ -96,10 +96,14 @@ def local_shard_summary(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.T
             m_p = torch.empty((parts, bh, n), device=dev, dtype=torch.float32)
             z_p = torch.empty_like(m_p)
             s_p = torch.empty((parts, bh, n, d), device=dev, dtype=torch.float32)
-        rc = lib.elsa_phase1_fold_shard(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), m_p.data_ptr(), z_p.data_ptr(),
-                                        s_p.data_ptr(), dt, _lib.ELSA_F32, b, h, n, d, nk, int(key_offset), pw, parts,
-                                        int(bool(is_causal)), 0, stream)
-        _lib.check(rc, "elsa_phase1_fold_shard")
+        ws_bytes = int(lib.elsa_phase1_fold_shard_workspace_bytes(dt, b, h, n, d, nk, 0))
+        if ws_bytes < 0:
+            raise ValueError("local_shard_summary: unsupported problem")
+        ws = torch.empty((max(ws_bytes, 256),), device=dev, dtype=torch.uint8)
+        rc = lib.elsa_phase1_fold_shard_ws(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), m_p.data_ptr(), z_p.data_ptr(),
+                                           s_p.data_ptr(), ws.data_ptr(), ws.numel(), dt, _lib.ELSA_F32, b, h, n, d, nk,
+                                           int(key_offset), pw, parts, int(bool(is_causal)), 0, stream)
+        _lib.check(rc, "elsa_phase1_fold_shard_ws")
         if parts > 1:
             rc = lib.elsa_merge_partial(m_p.data_ptr(), z_p.data_ptr(), s_p.data_ptr(), s.data_ptr(), m.data_ptr(),
                                         z.data_ptr(), _lib.ELSA_F32, parts, bh, n, d, stream)

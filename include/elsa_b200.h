@@ -112,6 +112,17 @@ int elsa_phase1_fold_shard(const void* q, const void* k, const void* v,
                            int n_keys, int key_offset, int part_width, int n_parts,
                            int is_causal, unsigned flags, void* stream);
 
+/* The same with a workspace (elsa_phase1_fold_shard_workspace_bytes; 0 when none is needed): fp32 shards with head dim 64
+ * then run on the tensor cores, the workspace holding the three bf16 planes of q, k_shard and v_shard.  No counterpart
+ * in the reference. */
+int64_t elsa_phase1_fold_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim, int n_keys,
+                                               unsigned flags);
+int elsa_phase1_fold_shard_ws(const void* q, const void* k, const void* v,
+                              float* m_buf, float* z_buf, void* s_buf, void* workspace, int64_t workspace_bytes,
+                              int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim,
+                              int n_keys, int key_offset, int part_width, int n_parts,
+                              int is_causal, unsigned flags, void* stream);
+
 /* Merge the partitions of each row into ONE un-normalised fp32 summary (m_out, z_out [B*H, q_len],
  * s_out [B*H, q_len, D]): what a shard hands to the cross-GPU merge.  Same arithmetic as
  * elsa_merge_final (cuda/paper_scan_d64_kernel.cu:39-70) without the final division. */
@@ -222,7 +233,8 @@ int elsa_forward_plan(int dtype, int summary_dtype, int batch, int heads, int n_
  * no device allocator, and for serving loops whose device memory is fixed at start-up and whose request
  * path must not allocate: the partition summaries go to a 64 MiB array that is part of the library image
  * (elsa_static_scratch_bytes) instead of a caller workspace.  No bias, library-chosen partitions, summaries
- * in the input dtype; out / row_m / row_z as in elsa_twopass_forward (row_m, row_z may both be NULL).
+ * in the input dtype, fp32 inputs on the FP32-FMA kernel (as with ELSA_FLAG_FP32_FMA); out / row_m / row_z as in
+ * elsa_twopass_forward (row_m, row_z may both be NULL).
  *   - Query rows are processed in chunks whose summaries fit the array; only a problem for which not even one
  *     query tile (256 rows on the tensor-core path, 64 otherwise) of summaries fits returns ELSA_ERR_WORKSPACE,
  *     and then nothing is launched.

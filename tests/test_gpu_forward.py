@@ -226,8 +226,15 @@ def test_summaries_round_trip_global_memory():
                                      block_n=256, summary_dtype=F32)
     assert U.max_abs(m, rm_) <= 2e-5 and U.max_abs(s, rs_) <= 2e-5 * float(rs_.abs().max())
     out, _, _ = U.merge_final(m, z, s, F32, n)
+    # elsa_phase1_fold has no workspace, so fp32 runs its FP32-FMA kernel: the whole operator restricted to that
+    # kernel gives the same bits; the default operator (fp32 phase 1 on the tensor cores) the same values to 1e-6
+    from elsa_b200 import _lib
+    from elsa_b200.attention import _forward_impl
+    fma = _forward_impl(q, k, v, bias=None, is_causal=False, summary_dtype=F32, part_width=256, q_chunk=0, want_state=False,
+                        flags=_lib.FLAG_FP32_FMA)[0]
+    assert torch.equal(out.view(b, h, n, d), fma)
     full = E.twopass_attention(q, k, v, block_n=256)
-    assert torch.equal(out.view(b, h, n, d), full)
+    assert U.max_abs(out.view(b, h, n, d), full) <= 1e-6
 
 
 def test_masked_rows_and_empty():
