@@ -11,9 +11,10 @@
 //
 //   warp 4      TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
 //                              order the issuer consumes them: K planes of key tile j+1, V planes of key tile j
-//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each;
+//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
+//                              into the S buffer the fold warps are not reading (two S buffers);
 //                              O_j = sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each,
-//                              into a FRESH accumulator per key tile (two O buffers)
+//                              into an accumulator that starts from zero for every key tile
 //   warps 0-3   fold           one thread per query row: row max from a first pass over the S row in TMEM, then a
 //                              second pass: exp2, row sum, P split into its three bf16 planes (own TMEM columns);
 //                              the row's running output lives in registers and takes in O_{j-1} with ordinary fp32
@@ -27,7 +28,7 @@
 // of increasing weight (x0*y2, x1*y1, x1*y0 ... x0*y0 last), so only the instructions of the leading term work at
 // full magnitude.
 //
-// TMEM columns: S [0,128) O_a [128,192) O_b [192,256) P0 [256,320) P1 [320,384) P2 [384,448).
+// TMEM columns: S_a [0,128) S_b [128,256) O [256,320) P0 [320,384) P1 [384,448) P2 [448,512).
 // Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3800 cycles), the ex2 unit 1024 cycles: unlike
 // the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate.
 #include <type_traits>
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Fold3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kSlots + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kSlots + 7];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -138,14 +139,15 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar_q = bar0;
   auto bar_full = [&](int i) { return bar0 + 8 * (1 + i); };
   auto bar_free = [&](int i) { return bar0 + 8 * (1 + kSlots + i); };
-  const uint32_t bar_s = bar0 + 8 * (1 + 2 * kSlots), bar_sfree = bar0 + 8 * (2 + 2 * kSlots);
-  const uint32_t bar_p = bar0 + 8 * (3 + 2 * kSlots), bar_pv = bar0 + 8 * (4 + 2 * kSlots);
+  auto bar_s = [&](int b) { return bar0 + 8 * (1 + 2 * kSlots + b); };        // S(j) is in S buffer j & 1
+  auto bar_sfree = [&](int b) { return bar0 + 8 * (3 + 2 * kSlots + b); };    // the fold warps are done with that buffer
+  const uint32_t bar_p = bar0 + 8 * (5 + 2 * kSlots), bar_pv = bar0 + 8 * (6 + 2 * kSlots);
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int i = 0; i < kSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
-    mbar_init(bar_s, 1); mbar_init(bar_sfree, 128);
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_s(b), 1); mbar_init(bar_sfree(b), 128); }
     mbar_init(bar_p, 128); mbar_init(bar_pv, 1);
     fence_mbar_init();
   }
@@ -157,9 +159,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tS = tmem_base;
-  const uint32_t tO[2] = {tmem_base + 128, tmem_base + 192};
-  const uint32_t tP[3] = {tmem_base + 256, tmem_base + 320, tmem_base + 384};
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;
+  const uint32_t tP[3] = {tmem_base + 320, tmem_base + 384, tmem_base + 448};
 
   if (warp == kProducerWarp) {
     if (n_t > 0 && lane == 0) {
@@ -195,7 +197,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q);
       // the six (q plane, k plane) pairs of one key tile; K planes arrive in ring order 2, 1, 0 and within a plane
       // the q planes go from the lightest admissible one down to q0: the leading term q0 k0 is the last to be added
-      auto issue_s = [&]() {
+      auto issue_s = [&](int b) {
         bool first = true;
         for (int kp = 2; kp >= 0 && ok; --kp) {
           const int slot = seq % kSlots;
@@ -203,33 +205,34 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           tc_fence_after();
           const uint64_t dk = dk_slot0 + slot * kSlotStep;
           for (int qp = 2 - kp; qp >= 0; --qp) {
-            mma_ss_x4<2, 2>(tS, dq[qp], dk, idesc_s, first ? 0u : 1u);
+            mma_ss_x4<2, 2>(tS[b], dq[qp], dk, idesc_s, first ? 0u : 1u);
             first = false;
           }
           mma_commit(bar_free(slot));     // the plane tile is free again once these MMAs have retired
           ++seq;
         }
-        if (ok) mma_commit(bar_s);
+        if (ok) mma_commit(bar_s(b));
       };
-      if (ok) issue_s();
+      if (ok) issue_s(0);
       for (int j = 0; ok && j < n_t; ++j) {
         if (j + 1 < n_t) {
-          // one S buffer: the fold warps must have finished their second pass over S(j)
-          if (!(ok = mbar_wait(bar_sfree, j & 1, &abort_flag, prm.status, BAR_SFREE))) break;
-          issue_s();
+          // S buffer (j+1)&1 held S(j-1): the fold warps must have finished their second pass over it
+          if (j >= 1 && !(ok = mbar_wait(bar_sfree((j + 1) & 1), ((j - 1) / 2) & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          issue_s((j + 1) & 1);
           if (!ok) break;
         }
         if (!(ok = mbar_wait(bar_p, j & 1, &abort_flag, prm.status, BAR_P))) break;
         tc_fence_after();
-        bool first = true;               // O_j starts from zero: a fresh accumulator per key tile
+        // O_j starts from zero (the fold warps took O_{j-1} into their registers before they delivered P(j))
+        bool first = true;
         for (int vp = 2; vp >= 0 && ok; --vp) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) break;
           tc_fence_after();
           const uint64_t dv = dv_slot0 + slot * kSlotStep;
           for (int pp = 2 - vp; pp >= 0; --pp) {
-            mma_ts_x4<8, 128>(tO[j & 1], tP[pp], dv, idesc_o, first ? 0u : 1u);
-            mma_ts_x4<8, 128>(tO[j & 1], tP[pp] + 32, dv + 512, idesc_o, 1u);
+            mma_ts_x4<8, 128>(tO, tP[pp], dv, idesc_o, first ? 0u : 1u);
+            mma_ts_x4<8, 128>(tO, tP[pp] + 32, dv + 512, idesc_o, 1u);
             first = false;
           }
           mma_commit(bar_free(slot));
@@ -250,38 +253,38 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 64; ++i) o_run[i] = 0.f;
     bool alive = true;
 
-    // o_run += O_b (the finished P V of one key tile)
-    auto take_o = [&](int b) {
+    // o_run += O (the finished P V of one key tile)
+    auto take_o = [&]() {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tO + lane_off, r0);
+      tmem_ld32(tO + lane_off + 32, r1);
+      tmem_wait_ld();
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t r[32];
-        tmem_ld32(tO[b] + lane_off + 32 * h, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_run[32 * h + i] += __uint_as_float(r[i]);
-      }
+      for (int i = 0; i < 32; ++i) { o_run[i] += __uint_as_float(r0[i]); o_run[32 + i] += __uint_as_float(r1[i]); }
     };
 
     for (int j = 0; j < n_t; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
+      const int b = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(b), (j / 2) & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
       tc_fence_after();
       const int k0 = k_begin + j * 128;
       const bool tail = k0 + 128 > k_end;
       const bool diag = prm.is_causal && (k0 + koff + 127 > q0);
       const bool masked = tail || diag;
       const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
-      // ---- pass 1 over the S row: the row max (the row itself stays in TMEM) ----
+      // ---- pass 1 over the S row: the row max (the row itself stays in TMEM), 64 columns per TMEM round trip ----
       float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_off + 32 * ch, r);
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t r[64];
+        tmem_ld32(tS[b] + lane_off + 64 * hf, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(tS[b] + lane_off + 64 * hf + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
+        for (int i = 0; i < 64; i += 8) {
           float t[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) t[e] = (masked && k0 + 32 * ch + i + e > lim) ? -CUDART_INF_F : __uint_as_float(r[i + e]);
+          for (int e = 0; e < 8; ++e) t[e] = (masked && k0 + 64 * hf + i + e > lim) ? -CUDART_INF_F : __uint_as_float(r[i + e]);
           mx[0] = max3f(mx[0], t[0], t[1]); mx[1] = max3f(mx[1], t[2], t[3]);
           mx[2] = max3f(mx[2], t[4], t[5]); mx[3] = max3f(mx[3], t[6], t[7]);
         }
@@ -291,10 +294,10 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       m_true = fmaxf(m_true, tmax);
       if (j > 0) {
         // P V of the previous key tile has retired: its O goes into the running sum (both are relative to the m_ref
-        // of that tile), and the P planes may be overwritten
+        // of that tile) before P V of this tile starts the accumulator from zero again; the P planes are free
         if (!__all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, &abort_flag, prm.status, BAR_PV))) { alive = false; break; }
         tc_fence_after();
-        take_o((j - 1) & 1);
+        take_o();
       }
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (move) {
@@ -306,39 +309,43 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         m_ref = m_new;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      // ---- pass 2: p = 2^(s*c - m) (full-precision exp2: this is the fp32 path), row sum, and the split of p into
-      // its three bf16 planes, 32 keys (16 packed pairs per plane) at a time ----
+      // ---- pass 2: p = 2^(s*c - m), row sum, and the split of p into its three bf16 planes ----
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_off + 32 * ch, r);
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t r[64];
+        tmem_ld32(tS[b] + lane_off + 64 * hf, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(tS[b] + lane_off + 64 * hf + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         tmem_wait_ld();
-        if (ch == 3) {                  // the whole row has been read twice: S may be overwritten
+        if (hf == 1) {                  // the whole row has been read twice: this S buffer may be overwritten
           tc_fence_before();
-          mbar_arrive(bar_sfree);
-        }
-        uint32_t pk[3][16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int kk = k0 + 32 * ch + 2 * i;
-          const float s0 = (masked && kk > lim) ? -CUDART_INF_F : __uint_as_float(r[2 * i]);
-          const float s1 = (masked && kk + 1 > lim) ? -CUDART_INF_F : __uint_as_float(r[2 * i + 1]);
-          const float p0 = exp2f(fmaf(s0, c, -m_use));
-          const float p1 = exp2f(fmaf(s1, c, -m_use));
-          ps[i & 3] += p0 + p1;
-          const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0, p1);
-          const float2 f0 = __bfloat1622float2(a0);
-          const float r0 = p0 - f0.x, r1 = p1 - f0.y;
-          const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
-          const float2 f1 = __bfloat1622float2(a1);
-          const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
-          pk[0][i] = *reinterpret_cast<const uint32_t*>(&a0);
-          pk[1][i] = *reinterpret_cast<const uint32_t*>(&a1);
-          pk[2][i] = *reinterpret_cast<const uint32_t*>(&a2);
+          mbar_arrive(bar_sfree(b));
         }
 #pragma unroll
-        for (int p = 0; p < 3; ++p) tmem_st16(tP[p] + lane_off + 16 * ch, pk[p]);
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t pk[3][16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int kk = k0 + 64 * hf + 32 * ch + 2 * i;
+            const float s0 = (masked && kk > lim) ? -CUDART_INF_F : __uint_as_float(r[32 * ch + 2 * i]);
+            const float s1 = (masked && kk + 1 > lim) ? -CUDART_INF_F : __uint_as_float(r[32 * ch + 2 * i + 1]);
+            // ex2.approx: 2 units in the last place, i.e. 2.4e-7 relative on a weight
+            const float p0 = fast_exp2(fmaf(s0, c, -m_use));
+            const float p1 = fast_exp2(fmaf(s1, c, -m_use));
+            ps[i & 3] += p0 + p1;
+            const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0, p1);
+            const float2 f0 = __bfloat1622float2(a0);
+            const float r0 = p0 - f0.x, r1 = p1 - f0.y;
+            const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
+            const float2 f1 = __bfloat1622float2(a1);
+            const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
+            pk[0][i] = *reinterpret_cast<const uint32_t*>(&a0);
+            pk[1][i] = *reinterpret_cast<const uint32_t*>(&a1);
+            pk[2][i] = *reinterpret_cast<const uint32_t*>(&a2);
+          }
+#pragma unroll
+          for (int p = 0; p < 3; ++p) tmem_st16(tP[p] + lane_off + 32 * hf + 16 * ch, pk[p]);
+        }
       }
       tmem_wait_st();
       tc_fence_before();
@@ -355,7 +362,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_pv, (n_t - 1) & 1, &abort_flag, prm.status, BAR_O))) alive = false;
       if (alive) {
         tc_fence_after();
-        take_o((n_t - 1) & 1);
+        take_o();
         const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true);
         z_out = zsum * f;
         m_out = z_out > 0.f ? m_true : -CUDART_INF_F;
