@@ -463,6 +463,12 @@ static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, un
   return n_ctx >= 512 && bwd_tc_supported(dtype, head_dim, has_bias);
 }
 
+// fp32 on the tensor cores (three bf16 planes per operand): head dim 64, no bias, no dbias
+static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
+  return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
+}
+
 static int64_t bwd_state_bytes(int batch, int heads, int n_ctx) {
   return align_up(static_cast<int64_t>(batch) * heads * n_ctx * 4, 256);
 }
@@ -472,6 +478,9 @@ extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads
   (void)is_causal;
   if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128) return -1;
   if (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags)) return bwd_tc_workspace_bytes(batch * heads, n_ctx);
+  // (the fp32 tensor-core route is not taken when dbias is asked for: the larger of the two needs covers both)
+  if (tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags))
+    return std::max(bwd_tc3_workspace_bytes(batch * heads, n_ctx, n_ctx), 2 * bwd_state_bytes(batch, heads, n_ctx));
   return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
 }
 
@@ -497,6 +506,7 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  const bool use_tc3 = dbias == nullptr && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
   const Strides os = st8 ? st8[3] : cs;
   BwdParams p;
@@ -506,7 +516,7 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   // a problem of at most 64 tokens is one (query tile, key tile) pair: one launch does the pre-pass and all gradients
   p.single_tile = (!use_tc && n_ctx <= 64 && head_dim <= 64) ? 1 : 0;
   p.out = out; p.os = os; p.row_m = row_m; p.row_z = row_z;
-  if (!use_tc && !p.single_tile)
+  if (!use_tc && !use_tc3 && !p.single_tile)
     rc = bwd_preprocess_any(out, os, dout, p.gs, row_m, row_z, row_d, row_lse, dtype, batch, heads, n_ctx, head_dim,
                             static_cast<cudaStream_t>(stream));
   if (rc != ELSA_OK) return rc;
@@ -524,6 +534,11 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return bwd_tc(p, out, os, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  }
+  if (use_tc3) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tc3(p, out, os, row_m, row_z, workspace, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }
@@ -565,6 +580,7 @@ extern "C" int elsa_twopass_backward_strided(const void* q, const void* k, const
 // contribution in fp32, to be summed over the shards by the caller (all_reduce / reduce_scatter) before rounding.
 extern "C" int64_t elsa_backward_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                                        unsigned flags) {
+  // (for the fp32 tensor-core route this covers a shard of up to n_ctx keys)
   return elsa_backward_workspace_bytes(dtype, batch, heads, n_ctx, head_dim, 0, 0, flags);
 }
 
@@ -587,8 +603,9 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = n_keys > 0 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
+  const bool use_tc3 = n_keys > 0 && n_keys <= n_ctx && tc3_backward_ok(dtype, head_dim, n_ctx, false, flags);
   int rc = ELSA_OK;
-  if (!use_tc) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
+  if (!use_tc && !use_tc3) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
   if (rc != ELSA_OK) return rc;
   BwdParams p;
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim), cks = contiguous_strides(heads, n_keys, head_dim);
@@ -607,6 +624,11 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return bwd_tc(p, out, cs, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  }
+  if (use_tc3) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tc3(p, out, cs, row_m, row_z, workspace, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }

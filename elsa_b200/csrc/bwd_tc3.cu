@@ -1,0 +1,665 @@
+// Backward for fp32 inputs on the 5th-generation tensor cores at fp32 accuracy: exact recompute from the saved row
+// statistics, head dim 64, causal or not, no bias.  Every operand of every contraction is split into three bf16 terms
+// (x = x0 + x1 + x2 exactly) and a product is formed as the six cross terms whose weight is at least 2^-16 of the
+// leading one, exactly as in the forward kernel for fp32 inputs (fold_tc3.cu).
+//
+// tcgen05.mma adds into its fp32 accumulator by truncation, so -- unlike the 16-bit backward -- no gradient is
+// accumulated over tiles in TMEM: every (query tile, key tile) pair gets fresh accumulators, and the running sums live
+// in the registers of the threads that drain them (ordinary round-to-nearest additions).  A resident dK / dV with a
+// streamed dQ (one kernel, five contractions) would need global atomics for dQ and more TMEM than there is, so the
+// work is done by two kernels of the same shape as the forward one, seven contractions per pair in all:
+//
+//   bwd3_dq_kernel    one CTA per 128-row QUERY tile, 64-key tiles streamed:
+//                       S  = Q K^T, dP = dO V^T       A = Q / dO planes (copied once into TMEM), B = K / V planes
+//                       dS = P (dP - D), P = 2^(S c - LSE)          four threads per query row
+//                       dQ_j = dS K                    A = dS planes (TMEM), B = the same K planes, MN-major
+//                     dQ = scale * sum_j dQ_j in registers, written once: no atomics, deterministic
+//   bwd3_dkv_kernel   one CTA per 128-row KEY tile, 64-query tiles streamed:
+//                       S^T = K Q^T, dP^T = V dO^T     A = K / V planes (shared memory), B = Q / dO planes
+//                       P^T, dS^T                      four threads per key row; -LSE, -D of the tile's queries
+//                                                      arrive with the tile (bulk copies into a small ring)
+//                       dV_i = P^T dO, dK_i = dS^T Q   A = P^T / dS^T planes (TMEM), B = the same dO / Q planes, MN-major
+//                     dV = sum_i dV_i, dK = scale * sum_i dK_i in registers
+//
+// Both kernels: 16 fold warps (warp w: TMEM lanes 32 (w % 4) ..., columns 16 (w / 4) ... of the 64-wide tile),
+// a TMA producer warp and an MMA-issuing warp; 8 KB plane tiles through a shared-memory ring in the order the issuer
+// consumes them (planes from the lightest to the leading one: the cross terms are added in order of increasing
+// weight).  The score / dP tiles of pair t+1 are issued as soon as the fold warps hold those of pair t in registers,
+// so the exponentials and the splits of one pair overlap the contractions of its neighbours.
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace elsa {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kSlotBytes = 64 * 64 * 2;      // one 64 x 64 bf16 plane tile (streamed operand)
+constexpr int kPlaneBytes = 128 * 64 * 2;    // one 128 x 64 bf16 plane tile (the CTA's own operand)
+constexpr int kFoldWarps = 16, kFoldThreads = kFoldWarps * 32;
+constexpr int kThreads = kFoldThreads + 64;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint64_t kSlotStep = kSlotBytes >> 4;   // shared-memory descriptors count 16-byte units
+
+// dQ kernel: 24 slots; the six 128-row planes of Q and dO are staged in slots 12..23 and copied into TMEM before the
+// ring's first pass reaches them
+constexpr int kDqSlots = 24;
+constexpr int kDqSmem = kDqSlots * kSlotBytes + 1024;
+// dK/dV kernel: K and V planes resident (96 KB), 15 ring slots, 4 stages of (-LSE, -D) vectors of 64 queries
+constexpr int kKvSlots = 15, kVecStages = 4, kVecBytes = 2 * 64 * 4;
+constexpr int kKvSmem = 6 * kPlaneBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
+
+enum BarId { BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_COPIED = 44, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
+
+struct Bwd3Params {
+  const float* nlse_pad; const float* nd_pad;   // [BH][n_pad]: -LSE, -D; padding rows hold -inf / 0
+  float* dq; float* dk; float* dv;
+  Strides dqs, dks, dvs;
+  int n_ctx, n_pad, bh, heads, is_causal;
+  int n_keys, key_offset;                       // K/V rows of this launch and the sequence index of the first one
+  float scale, scale_log2;
+  int* status;                                  // the device's status word (mapped host memory)
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void store16(float* dst, const float (&v)[16], float f) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i] * f, v[i + 1] * f, v[i + 2] * f, v[i + 3] * f);
+}
+
+// 16 values -> their three bf16 planes, 8 TMEM columns per plane starting at column `col` of plane base tp0 + 32 p
+__device__ __forceinline__ void split_store16(const float (&x)[16], uint32_t tp0, uint32_t col) {
+  uint32_t pk[3][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) split3_pair(x[2 * i], x[2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
+#pragma unroll
+  for (int p = 0; p < 3; ++p) tmem_st8(tp0 + 32 * p + col, pk[p]);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// dQ: one CTA per 128-row query tile
+// TMEM columns: Q planes [0,96) dO planes [96,192) S [192,256) dP [256,320) dQ_j [320,384) dS planes [384,480)
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+               const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+               const Bwd3Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kDqSlots + 6];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int q0 = blockIdx.x * 128;
+  const int N = prm.n_ctx, NK = prm.n_keys, koff = prm.key_offset;
+  int ke = NK;
+  if (prm.is_causal) ke = min(ke, min(q0 + 128, N) - koff);   // keys above the tile's last row are never admissible
+  const int n_t = ke > 0 ? (ke + 63) / 64 : 0;                // 64-key tiles this query tile visits
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto sSlot = [&](int i) { return smem_base + i * kSlotBytes; };
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar_full = [&](int i) { return bar0 + 8 * i; };
+  auto bar_free = [&](int i) { return bar0 + 8 * (kDqSlots + i); };
+  const uint32_t barx = bar0 + 8 * 2 * kDqSlots;
+  const uint32_t bar_stage = barx;            // the Q / dO planes are in shared memory
+  const uint32_t bar_copied = barx + 8;       // ... and have been copied into TMEM: their slots join the ring
+  const uint32_t bar_sdp = barx + 16;         // S(j), dP(j) are in TMEM
+  const uint32_t bar_sfree = barx + 24;       // the fold warps hold them in registers
+  const uint32_t bar_ds = barx + 32;          // the dS planes of tile j have been delivered
+  const uint32_t bar_dq = barx + 40;          // dQ_j is complete
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < kDqSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
+    mbar_init(bar_stage, 1); mbar_init(bar_copied, kFoldThreads);
+    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldThreads);
+    mbar_init(bar_ds, kFoldThreads); mbar_init(bar_dq, 1);
+    fence_mbar_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tA = tmem_base;                 // Q planes at 32 p, dO planes at 96 + 32 p
+  const uint32_t tS = tmem_base + 192, tdP = tmem_base + 256, tdQ = tmem_base + 320, tDS = tmem_base + 384;
+
+  if (warp == kProducerWarp) {
+    if (n_t > 0 && lane == 0) {
+      // ---------------- TMA producer ----------------
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(bar_stage, 6 * kPlaneBytes);
+      for (int p = 0; p < 3; ++p) {
+        tma_load_4d(sSlot(12 + 2 * p), &tmap_q, bar_stage, 0, q0, bh, p);
+        tma_load_4d(sSlot(18 + 2 * p), &tmap_do, bar_stage, 0, q0, bh, p);
+      }
+      int seq = 0;
+      bool ok = true;
+      auto load = [&](const CUtensorMap* map, int tile, int plane) {
+        const int slot = seq % kDqSlots;
+        if (seq >= kDqSlots) ok = mbar_wait(bar_free(slot), ((seq / kDqSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE);
+        else if (slot >= 12) ok = mbar_wait(bar_copied, 0, &abort_flag, prm.status, BAR_COPIED);
+        if (!ok) return;
+        mbar_arrive_expect_tx(bar_full(slot), kSlotBytes);
+        tma_load_4d(sSlot(slot), map, bar_full(slot), 0, tile * 64, bh, plane);
+        ++seq;
+      };
+      for (int j = 0; j < n_t && ok; ++j) {
+        for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, j, p);       // planes in the order of increasing weight
+        for (int p = 2; p >= 0 && ok; --p) load(&tmap_v, j, p);
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    if (n_t > 0 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 64);    // S, dP: A in TMEM, B K-major, N = 64 keys
+      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dQ_j:  A in TMEM, B (K) MN-major, N = 64 = d
+      const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dmn_slot0 = make_sdesc(sSlot(0), 64 * 128, 1024);
+      bool ok = mbar_wait(bar_copied, 0, &abort_flag, prm.status, BAR_COPIED);
+      // ring sequence numbers of key tile j: K planes 2, 1, 0 at 6 j .. 6 j + 2, V planes at 6 j + 3 .. 6 j + 5
+      auto issue_sdp = [&](int j) {
+        bool first = true;
+        for (int kp = 2; kp >= 0 && ok; --kp) {
+          const int seq = 6 * j + 2 - kp, slot = seq % kDqSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kDqSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          for (int qp = 2 - kp; qp >= 0; --qp) {
+            mma_ts_x4<8, 2>(tS, tA + 32 * qp, dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
+            first = false;
+          }                                   // the K planes stay: dQ_j reads them again
+        }
+        first = true;
+        for (int vp = 2; vp >= 0 && ok; --vp) {
+          const int seq = 6 * j + 5 - vp, slot = seq % kDqSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kDqSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          for (int gp = 2 - vp; gp >= 0; --gp) {
+            mma_ts_x4<8, 2>(tdP, tA + 96 + 32 * gp, dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
+            first = false;
+          }
+          mma_commit(bar_free(slot));
+        }
+        if (ok) mma_commit(bar_sdp);
+      };
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      for (int j = 0; ok && j < n_t; ++j) {
+        if (j + 1 < n_t) {
+          if (!(ok = mbar_wait(bar_sfree, j & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          tc_fence_after();
+          issue_sdp(j + 1);
+          if (!ok) break;
+        }
+        if (!(ok = mbar_wait(bar_ds, j & 1, &abort_flag, prm.status, BAR_DS))) break;
+        tc_fence_after();
+        bool first = true;
+        for (int kp = 2; kp >= 0; --kp) {
+          const int slot = (6 * j + 2 - kp) % kDqSlots;
+          for (int sp = 2 - kp; sp >= 0; --sp) {
+            mma_ts_x4<8, 128>(tdQ, tDS + 32 * sp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
+            first = false;
+          }
+          mma_commit(bar_free(slot));
+        }
+        mma_commit(bar_dq);                   // dQ_j is complete; the dS planes may be overwritten
+      }
+    }
+  } else {
+    // ---------------- fold warps: four threads per query row ----------------
+    const int qd = warp & 3, cq = warp >> 2;                // TMEM lane quadrant, column quarter
+    const int row = qd * 32 + lane;
+    const int qi = q0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const float c = prm.scale_log2;
+    const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];   // q0 + 127 < n_pad
+    const float nd = prm.nd_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];
+    float dq_run[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dq_run[i] = 0.f;
+    bool alive = n_t > 0;
+
+    // one-time copy of the Q and dO planes from shared memory into TMEM (the A operands of S and dP): lane = query
+    // row, 32 columns of bf16 pairs per plane; the 128-byte swizzle of the TMA tile is undone on the way.
+    // Column quarter cq copies planes cq and cq + 4 of (Q0, Q1, Q2, dO0, dO1, dO2).
+    if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_stage, 0, &abort_flag, prm.status, BAR_STAGE))) alive = false;
+    if (alive) {
+      for (int idx = cq; idx < 6; idx += 4) {
+        const uint8_t* src = smem_gen + (12 + 2 * idx) * kSlotBytes + row * 128;
+        uint32_t w[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint4 t = *reinterpret_cast<const uint4*>(src + ((g ^ (row & 7)) << 4));
+          w[4 * g] = t.x; w[4 * g + 1] = t.y; w[4 * g + 2] = t.z; w[4 * g + 3] = t.w;
+        }
+        tmem_st32(tA + 32 * idx + lane_off, w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_copied);
+    }
+
+    auto take_dq = [&]() {
+      uint32_t r[16];
+      tmem_ld16(tdQ + lane_off + 16 * cq, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dq_run[i] += __uint_as_float(r[i]);
+    };
+
+    for (int j = 0; alive && j < n_t; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, j & 1, &abort_flag, prm.status, BAR_SDP))) { alive = false; break; }
+      tc_fence_after();
+      float ds[16];
+      {
+        uint32_t rs[16], rp[16];
+        tmem_ld16(tS + lane_off + 16 * cq, rs);
+        tmem_ld16(tdP + lane_off + 16 * cq, rp);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar_sfree);      // S and dP may be overwritten with the next tile's
+        const int kb = j * 64 + 16 * cq;                    // first (local) key of this thread's columns
+        const bool masked = (j * 64 + 64 > NK) || (prm.is_causal && (j * 64 + koff + 63 > q0));
+        const int lim = prm.is_causal ? min(NK - 1, qi - koff) : NK - 1;   // last admissible (local) key of this row
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nlse));
+          if (masked && kb + i > lim) p = 0.f;
+          ds[i] = p * (__uint_as_float(rp[i]) + nd);
+        }
+      }
+      if (j > 0) {
+        // dQ of the previous key tile has retired: it goes into the running sum, and the dS planes are free
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (j - 1) & 1, &abort_flag, prm.status, BAR_ACC))) { alive = false; break; }
+        tc_fence_after();
+        take_dq();
+      }
+      split_store16(ds, tDS + lane_off, 8 * cq);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_ds);
+    }
+    if (alive && n_t > 0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (n_t - 1) & 1, &abort_flag, prm.status, BAR_ACC))) alive = false;
+      if (alive) {
+        tc_fence_after();
+        take_dq();
+      }
+    }
+    if (qi < N && (alive || n_t == 0)) {
+      const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
+      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// dK, dV: one CTA per 128-row key tile
+// TMEM columns: S^T [0,64) dP^T [64,128) P^T planes [128,224) dS^T planes [224,320) dV_i [320,384) dK_i [384,448)
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                const Bwd3Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kKvSlots + 5];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int k0 = blockIdx.x * 128;                  // first (local) key row of this CTA
+  const int N = prm.n_ctx, NK = prm.n_keys;
+  const int kseq0 = k0 + prm.key_offset;            // its index in the sequence
+  const int n_q64 = (N + 63) / 64;
+  const int it_begin = prm.is_causal ? min(n_q64, kseq0 / 64) : 0;   // query tiles above the diagonal see none of these keys
+  const int n_it = n_q64 - it_begin;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto sK = [&](int p) { return smem_base + p * kPlaneBytes; };
+  auto sV = [&](int p) { return smem_base + (3 + p) * kPlaneBytes; };
+  auto sSlot = [&](int i) { return smem_base + 6 * kPlaneBytes + i * kSlotBytes; };
+  const uint32_t vec_off = 6 * kPlaneBytes + kKvSlots * kSlotBytes;    // [stage][-LSE x 64 | -D x 64]
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar_full = [&](int i) { return bar0 + 8 * i; };
+  auto bar_free = [&](int i) { return bar0 + 8 * (kKvSlots + i); };
+  const uint32_t barx = bar0 + 8 * 2 * kKvSlots;
+  const uint32_t bar_kv = barx;               // the K / V planes are in shared memory
+  const uint32_t bar_sdp = barx + 8;          // S^T(i), dP^T(i) are in TMEM
+  const uint32_t bar_sfree = barx + 16;       // the fold warps hold them in registers
+  const uint32_t bar_pl = barx + 24;          // the P^T / dS^T planes of tile i have been delivered
+  const uint32_t bar_acc = barx + 32;         // dV_i, dK_i are complete
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < kKvSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldThreads);
+    mbar_init(bar_pl, kFoldThreads); mbar_init(bar_acc, 1);
+    fence_mbar_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tP = tmem_base + 128, tDS = tmem_base + 224;
+  const uint32_t tdV = tmem_base + 320, tdK = tmem_base + 384;
+
+  if (warp == kProducerWarp) {
+    if (n_it > 0 && lane == 0) {
+      // ---------------- TMA producer ----------------
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(bar_kv, 6 * kPlaneBytes);
+      for (int p = 0; p < 3; ++p) {
+        tma_load_4d(sK(p), &tmap_k, bar_kv, 0, k0, bh, p);
+        tma_load_4d(sV(p), &tmap_v, bar_kv, 0, k0, bh, p);
+      }
+      int seq = 0;
+      bool ok = true;
+      // ring order of query tile i: dO planes 2, 1, 0 (sequence numbers 6 i .. 6 i + 2), then Q planes 2, 1, 0; the
+      // tile's first slot also receives its -LSE / -D vectors
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int qrow = (it_begin + it) * 64;
+        for (int x = 0; x < 6 && ok; ++x) {
+          const int slot = seq % kKvSlots;
+          if (seq >= kKvSlots && !(ok = mbar_wait(bar_free(slot), ((seq / kKvSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
+          mbar_arrive_expect_tx(bar_full(slot), kSlotBytes + (x == 0 ? kVecBytes : 0));
+          tma_load_4d(sSlot(slot), x < 3 ? &tmap_do : &tmap_q, bar_full(slot), 0, qrow, bh, 2 - (x % 3));
+          if (x == 0) {
+            const uint32_t dst = smem_base + vec_off + (it % kVecStages) * kVecBytes;
+            bulk_load_1d(dst, prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, 256, bar_full(slot));
+            bulk_load_1d(dst + 256, prm.nd_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, 256, bar_full(slot));
+          }
+          ++seq;
+        }
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    if (n_it > 0 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 64);    // S^T, dP^T: A, B K-major, N = 64 queries
+      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dV_i, dK_i: A in TMEM, B MN-major, N = 64 = d
+      const uint64_t dKp[3] = {make_sdesc(sK(0), 16, 1024), make_sdesc(sK(1), 16, 1024), make_sdesc(sK(2), 16, 1024)};
+      const uint64_t dVp[3] = {make_sdesc(sV(0), 16, 1024), make_sdesc(sV(1), 16, 1024), make_sdesc(sV(2), 16, 1024)};
+      const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dmn_slot0 = make_sdesc(sSlot(0), 64 * 128, 1024);
+      bool ok = mbar_wait(bar_kv, 0, &abort_flag, prm.status, BAR_STAGE);
+      auto issue_sdp = [&](int it) {
+        bool first = true;
+        for (int gp = 2; gp >= 0 && ok; --gp) {            // dP^T = V dO^T
+          const int seq = 6 * it + 2 - gp, slot = seq % kKvSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          for (int vp = 2 - gp; vp >= 0; --vp) {
+            mma_ss_x4<2, 2>(tdP, dVp[vp], dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
+            first = false;
+          }
+        }
+        first = true;
+        for (int qp = 2; qp >= 0 && ok; --qp) {            // S^T = K Q^T
+          const int seq = 6 * it + 5 - qp, slot = seq % kKvSlots;
+          if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          for (int kp = 2 - qp; kp >= 0; --kp) {
+            mma_ss_x4<2, 2>(tS, dKp[kp], dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
+            first = false;
+          }
+        }
+        if (ok) mma_commit(bar_sdp);
+      };
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (it + 1 < n_it) {
+          if (!(ok = mbar_wait(bar_sfree, it & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          tc_fence_after();
+          issue_sdp(it + 1);
+          if (!ok) break;
+        }
+        if (!(ok = mbar_wait(bar_pl, it & 1, &abort_flag, prm.status, BAR_DS))) break;
+        tc_fence_after();
+        bool first = true;
+        for (int gp = 2; gp >= 0; --gp) {                  // dV_i = P^T dO
+          const int slot = (6 * it + 2 - gp) % kKvSlots;
+          for (int pp = 2 - gp; pp >= 0; --pp) {
+            mma_ts_x4<8, 128>(tdV, tP + 32 * pp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
+            first = false;
+          }
+          mma_commit(bar_free(slot));
+        }
+        first = true;
+        for (int qp = 2; qp >= 0; --qp) {                  // dK_i = dS^T Q
+          const int slot = (6 * it + 5 - qp) % kKvSlots;
+          for (int sp = 2 - qp; sp >= 0; --sp) {
+            mma_ts_x4<8, 128>(tdK, tDS + 32 * sp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
+            first = false;
+          }
+          mma_commit(bar_free(slot));
+        }
+        mma_commit(bar_acc);                  // dV_i, dK_i are complete; the planes may be overwritten
+      }
+    }
+  } else {
+    // ---------------- fold warps: four threads per key row ----------------
+    const int qd = warp & 3, cq = warp >> 2;                // TMEM lane quadrant, column quarter
+    const int row = qd * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const int key = k0 + row;                  // local key row
+    const int key_seq = kseq0 + row;           // its index in the sequence (what the causal rule compares)
+    const bool key_ok = key < NK;
+    const bool cta_tail = k0 + 128 > NK;       // some key rows of this CTA do not exist
+    const float c = prm.scale_log2;
+    float dv_run[16], dk_run[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { dv_run[i] = 0.f; dk_run[i] = 0.f; }
+    bool alive = true;
+
+    auto take_acc = [&]() {
+      uint32_t rv[16], rk[16];
+      tmem_ld16(tdV + lane_off + 16 * cq, rv);
+      tmem_ld16(tdK + lane_off + 16 * cq, rk);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { dv_run[i] += __uint_as_float(rv[i]); dk_run[i] += __uint_as_float(rk[i]); }
+    };
+
+    for (int it = 0; it < n_it; ++it) {
+      const int q_tile0 = (it_begin + it) * 64;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, it & 1, &abort_flag, prm.status, BAR_SDP))) { alive = false; break; }
+      // the tile's row statistics were written by the bulk copies that complete on its first slot's barrier: observe
+      // that barrier directly (it completed before the MMAs behind bar_sdp were issued, so this never spins)
+      {
+        const int seq = 6 * it;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_full(seq % kKvSlots), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) { alive = false; break; }
+      }
+      tc_fence_after();
+      float p[16], ds[16];
+      {
+        uint32_t rs[16], rp[16];
+        tmem_ld16(tS + lane_off + 16 * cq, rs);
+        tmem_ld16(tdP + lane_off + 16 * cq, rp);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar_sfree);      // S^T and dP^T may be overwritten with the next tile's
+        const float4* nl4 = reinterpret_cast<const float4*>(smem_gen + vec_off + (it % kVecStages) * kVecBytes) + 4 * cq;
+        const float4* nd4 = nl4 + 16;
+        const bool masked = cta_tail || (prm.is_causal && q_tile0 < kseq0 + 128);   // only the diagonal tiles / the last key tile
+        const int qc = q_tile0 + 16 * cq;                                           // first query of this thread's columns
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float4 nl = nl4[g], nd = nd4[g];            // -LSE, -D of 4 queries (warp-wide broadcast reads)
+          const float nle[4] = {nl.x, nl.y, nl.z, nl.w}, nde[4] = {nd.x, nd.y, nd.z, nd.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = 4 * g + e;
+            float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nle[e]));
+            if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) pv = 0.f;
+            p[i] = pv;
+            ds[i] = pv * (__uint_as_float(rp[i]) + nde[e]);
+          }
+        }
+      }
+      if (it > 0) {
+        // dV, dK of the previous query tile have retired: they go into the running sums, and the planes are free
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_acc, (it - 1) & 1, &abort_flag, prm.status, BAR_ACC))) { alive = false; break; }
+        tc_fence_after();
+        take_acc();
+      }
+      split_store16(p, tP + lane_off, 8 * cq);
+      split_store16(ds, tDS + lane_off, 8 * cq);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_pl);
+    }
+    if (alive && n_it > 0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_acc, (n_it - 1) & 1, &abort_flag, prm.status, BAR_ACC))) alive = false;
+      if (alive) {
+        tc_fence_after();
+        take_acc();
+      }
+    }
+    if (key_ok && alive) {
+      const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
+      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale);
+      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, 1.f);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// -D = -sum_d out*dout, -LSE = -(m + log2(max(z, 1e-30))) into the padded layout; padding: -D = 0, -LSE = -inf
+__global__ void __launch_bounds__(256)
+bwd3_preprocess_kernel(const float* __restrict__ out, const float* __restrict__ dout, const float* __restrict__ row_m,
+                       const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
+                       int heads, int n_ctx, int n_pad, Strides os, Strides gs) {
+  // blockIdx.y = (batch*head); x covers the n_pad padded rows, 16 lanes (16 bytes each) per row
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = static_cast<int>(gid >> 4);
+  const int lane = static_cast<int>(gid & 15);
+  const int64_t b = blockIdx.y;
+  const bool in_pad = r < n_pad;
+  const bool real = in_pad && r < n_ctx;
+  float part = 0.f;
+  if (real) {
+    const int bi = static_cast<int>(b) / heads, hi = static_cast<int>(b) - bi * heads;
+    const float4 o = *reinterpret_cast<const float4*>(out + bi * os.b + hi * os.h + static_cast<int64_t>(r) * os.r + lane * 4);
+    const float4 g = *reinterpret_cast<const float4*>(dout + bi * gs.b + hi * gs.h + static_cast<int64_t>(r) * gs.r + lane * 4);
+    part = (o.x * g.x + o.y * g.y) + (o.z * g.z + o.w * g.w);
+  }
+  part += __shfl_xor_sync(0xffffffffu, part, 8);
+  part += __shfl_xor_sync(0xffffffffu, part, 4);
+  part += __shfl_xor_sync(0xffffffffu, part, 2);
+  part += __shfl_xor_sync(0xffffffffu, part, 1);
+  if (in_pad && lane == 0) {
+    const int64_t prow = b * n_pad + r;
+    if (real) {
+      nd_pad[prow] = -part;
+      nlse_pad[prow] = -(row_m[b * n_ctx + r] + log2f(fmaxf(row_z[b * n_ctx + r], 1.0e-30f)));
+    } else {
+      nd_pad[prow] = 0.f;
+      nlse_pad[prow] = -CUDART_INF_F;
+    }
+  }
+}
+
+}  // namespace
+
+bool bwd_tc3_supported(int dtype, int head_dim, bool has_bias) { return fold_tc3_supported(dtype, head_dim, has_bias); }
+
+int64_t bwd_tc3_workspace_bytes(int bh, int n_ctx, int n_keys) {
+  const int64_t n_pad = align_up(n_ctx, 128);
+  return 2 * align_up(static_cast<int64_t>(bh) * n_pad * 4, 256) + 2 * fold_tc3_plane_bytes(bh, n_ctx) +
+         2 * fold_tc3_plane_bytes(bh, n_keys);
+}
+
+int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
+            cudaStream_t st) {
+  if (!bwd_tc3_supported(ELSA_F32, p.head_dim, p.bias != nullptr) || p.dbias) return ELSA_ERR_UNSUPPORTED;
+  const int N = p.n_ctx, NK = p.n_keys, bh = p.bh, batch = bh / p.heads;
+  const int n_pad = static_cast<int>(align_up(N, 128));
+  const int64_t vec_bytes = align_up(static_cast<int64_t>(bh) * n_pad * 4, 256);
+  const int64_t qb = fold_tc3_plane_bytes(bh, N), kb = fold_tc3_plane_bytes(bh, NK);
+  char* ws = static_cast<char*>(workspace);
+  float* nd_pad = reinterpret_cast<float*>(ws);
+  float* nlse_pad = reinterpret_cast<float*>(ws + vec_bytes);
+  char* q3 = ws + 2 * vec_bytes;
+  char* do3 = q3 + qb;
+  char* k3 = do3 + qb;
+  char* v3 = k3 + kb;
+  int rc;
+  {
+    const dim3 pgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_pad) * 16, 256)), static_cast<unsigned>(bh));
+    bwd3_preprocess_kernel<<<pgrid, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(p.dout), row_m,
+                                                  row_z, nd_pad, nlse_pad, p.heads, N, n_pad, os, p.gs);
+    ELSA_LAUNCH_CHECK();
+  }
+  if ((rc = fold_tc3_split(p.q, p.qs, q3, batch, p.heads, N, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.dout, p.gs, do3, batch, p.heads, N, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.k, p.ks, k3, batch, p.heads, NK, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.v, p.vs, v3, batch, p.heads, NK, st)) != ELSA_OK) return rc;
+
+  // planes as [3, B*H, rows, 64] bf16 tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
+  const Strides sq = contiguous_strides(bh, N, 64), sk = contiguous_strides(bh, NK, 64);
+  CUtensorMap mq128, mdo128, mk64, mv64, mq64, mdo64, mk128, mv128;
+  if ((rc = make_tmap_rows64(&mq128, q3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo128, do3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq64, q3, ELSA_BF16, N, bh, 3, sq, 64)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo64, do3, ELSA_BF16, N, bh, 3, sq, 64)) != ELSA_OK) return rc;
+  Bwd3Params prm;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
+  prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad;
+  prm.dq = static_cast<float*>(p.dq); prm.dk = static_cast<float*>(p.dk); prm.dv = static_cast<float*>(p.dv);
+  prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
+  prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
+  prm.n_keys = NK; prm.key_offset = p.key_offset;
+  prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
+  if (NK > 0) {
+    if ((rc = make_tmap_rows64(&mk64, k3, ELSA_BF16, NK, bh, 3, sk, 64)) != ELSA_OK) return rc;
+    if ((rc = make_tmap_rows64(&mv64, v3, ELSA_BF16, NK, bh, 3, sk, 64)) != ELSA_OK) return rc;
+    if ((rc = make_tmap_rows64(&mk128, k3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
+    if ((rc = make_tmap_rows64(&mv128, v3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
+  } else {
+    mk64 = mv64 = mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
+  }
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dq_kernel), kDqSmem)) != ELSA_OK) return rc;
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dkv_kernel), kKvSmem)) != ELSA_OK) return rc;
+  {
+    const dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
+    bwd3_dq_kernel<<<grid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk64, mv64, prm);
+    ELSA_LAUNCH_CHECK();
+  }
+  if (NK > 0) {
+    const dim3 grid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
+    bwd3_dkv_kernel<<<grid, kThreads, kKvSmem, st>>>(mq64, mdo64, mk128, mv128, prm);
+    ELSA_LAUNCH_CHECK();
+  }
+  return ELSA_OK;
+}
+
+}  // namespace elsa

@@ -6,19 +6,25 @@
 // route for fp32 is 3xTF32 (src/elsa_twopass_clean/attention.py:280-282, 21 significant bits per operand); this keeps
 // all 24.
 //
-// A pre-pass (split3_kernel) writes the three bf16 planes of q, k, v once per forward call.  One CTA (256 threads,
+// A pre-pass (split3_kernel) writes the three bf16 planes of q, k, v once per forward call.  One CTA (576 threads,
 // 1 per SM) owns ONE 128-row query tile of one (batch*head) and one K partition, walked in 128-key tiles:
 //
-//   warp 4      TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
+//   warp 16     TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
 //                              order the issuer consumes them: K planes of key tile j+1, V planes of key tile j
-//   warp 5      MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
-//                              into the S buffer the fold warps are not reading (two S buffers);
+//   warp 17     MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
+//                              as soon as the fold warps hold S(j) in registers;
 //                              O_j = sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each,
 //                              into an accumulator that starts from zero for every key tile
-//   warps 0-3   fold           one thread per query row: row max from a first pass over the S row in TMEM, then a
-//                              second pass: exp2, row sum, P split into its three bf16 planes (own TMEM columns);
-//                              the row's running output lives in registers and takes in O_{j-1} with ordinary fp32
-//                              additions
+//   warps 0-15  fold           FOUR threads per query row (warp w: rows 32 (w % 4) ..., key columns 32 (w / 4) ...):
+//                              the thread's 32 scores go from TMEM into registers once, the row max is exchanged
+//                              through shared memory, then exp2, row sum and -- after P V of the previous key tile
+//                              has retired -- the split of P into its three bf16 planes (own TMEM columns); the
+//                              row's running output lives in registers (16 columns per thread) and takes in O_{j-1}
+//                              with ordinary fp32 additions
+//
+// The per-element work of the fold (exponential, three roundings and two exact remainders) is about a dozen
+// instructions; with one thread per row (four warps, one per scheduler) every dependent instruction's latency was
+// exposed and a key tile took 11.9 k cycles against 3.1 k of tensor-pipe work.  Four warps per scheduler hide it.
 //
 // Accuracy.  tcgen05.mma adds into its fp32 accumulator by truncation: every accumulating instruction loses up to one
 // unit in the last place of the accumulator, always towards zero.  Accumulating P V of a whole partition in TMEM (as
@@ -28,8 +34,8 @@
 // of increasing weight (x0*y2, x1*y1, x1*y0 ... x0*y0 last), so only the instructions of the leading term work at
 // full magnitude.
 //
-// TMEM columns: S_a [0,128) S_b [128,256) O [256,320) P0 [320,384) P1 [384,448) P2 [448,512).
-// Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3800 cycles), the ex2 unit 1024 cycles: unlike
+// TMEM columns: S [0,128) O [128,192) P0 [192,256) P1 [256,320) P2 [320,384).
+// Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3100 cycles), the ex2 unit 1024 cycles: unlike
 // the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate.
 #include <type_traits>
 
@@ -45,12 +51,13 @@ namespace {
 constexpr int kSlots = 8;
 constexpr int kPlaneBytes = 128 * 64 * 2;                      // one 128 x 64 bf16 plane tile
 constexpr int kFold3Smem = (3 + kSlots) * kPlaneBytes + 1024;  // + alignment slack
-constexpr int kThreads = 256;
+constexpr int kFoldWarps = 16, kFoldThreads = kFoldWarps * 32;
+constexpr int kThreads = kFoldThreads + 64;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kProducerWarp = 4, kIssuerWarp = 5;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17;
 constexpr float kRescaleThreshold = 8.0f;
 
-enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, BAR_O = 36, BAR_SFREE = 37, BAR_PV = 38 };
+enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, BAR_O = 36, BAR_SFREE = 37, BAR_PV = 38, BAR_ROW = 39 };
 
 struct Fold3Params {
   float* m; float* z; void* s;
@@ -66,21 +73,16 @@ __device__ __forceinline__ float max3f(float a, float b, float c) {
   return d;
 }
 
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&w)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]),
-        "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
-}
 
+// 16 consecutive values of a summary row
 template <typename TS>
-__device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64]) {
+__device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16]) {
   if constexpr (sizeof(TS) == 4) {
 #pragma unroll
-    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
   } else {
 #pragma unroll
-    for (int i = 0; i < 64; i += 8) {
+    for (int i = 0; i < 16; i += 8) {
       uint4 t;
       t.x = pack2<TS>(v[i], v[i + 1]); t.y = pack2<TS>(v[i + 2], v[i + 3]);
       t.z = pack2<TS>(v[i + 4], v[i + 5]); t.w = pack2<TS>(v[i + 6], v[i + 7]);
@@ -117,9 +119,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Fold3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kSlots + 7];
+  __shared__ __align__(8) uint64_t bars[2 * kSlots + 9];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float row_max[2][4][128];   // [key-tile parity][column quarter][row]: the quarter-row maxima
+  __shared__ float row_sum[4][128];      // the quarter-row sums, exchanged once in the epilogue
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.z, part = blockIdx.y;
@@ -139,16 +143,19 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar_q = bar0;
   auto bar_full = [&](int i) { return bar0 + 8 * (1 + i); };
   auto bar_free = [&](int i) { return bar0 + 8 * (1 + kSlots + i); };
-  auto bar_s = [&](int b) { return bar0 + 8 * (1 + 2 * kSlots + b); };        // S(j) is in S buffer j & 1
-  auto bar_sfree = [&](int b) { return bar0 + 8 * (3 + 2 * kSlots + b); };    // the fold warps are done with that buffer
-  const uint32_t bar_p = bar0 + 8 * (5 + 2 * kSlots), bar_pv = bar0 + 8 * (6 + 2 * kSlots);
+  const uint32_t bar_s = bar0 + 8 * (1 + 2 * kSlots);        // S(j) is in TMEM
+  const uint32_t bar_sfree = bar0 + 8 * (2 + 2 * kSlots);    // the fold warps hold S(j) in registers
+  const uint32_t bar_p = bar0 + 8 * (3 + 2 * kSlots);        // the P planes of tile j have been delivered
+  const uint32_t bar_pv = bar0 + 8 * (4 + 2 * kSlots);       // O_j is complete
+  auto bar_row = [&](int qd) { return bar0 + 8 * (5 + 2 * kSlots + qd); };   // the four threads of a row have exchanged
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int i = 0; i < kSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(bar_s(b), 1); mbar_init(bar_sfree(b), 128); }
-    mbar_init(bar_p, 128); mbar_init(bar_pv, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_sfree, kFoldThreads);
+    mbar_init(bar_p, kFoldThreads); mbar_init(bar_pv, 1);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar_row(qd), 128);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -159,9 +166,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tO = tmem_base + 256;
-  const uint32_t tP[3] = {tmem_base + 320, tmem_base + 384, tmem_base + 448};
+  const uint32_t tS = tmem_base;
+  const uint32_t tO = tmem_base + 128;
+  const uint32_t tP[3] = {tmem_base + 192, tmem_base + 256, tmem_base + 320};
 
   if (warp == kProducerWarp) {
     if (n_t > 0 && lane == 0) {
@@ -197,7 +204,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q);
       // the six (q plane, k plane) pairs of one key tile; K planes arrive in ring order 2, 1, 0 and within a plane
       // the q planes go from the lightest admissible one down to q0: the leading term q0 k0 is the last to be added
-      auto issue_s = [&](int b) {
+      auto issue_s = [&]() {
         bool first = true;
         for (int kp = 2; kp >= 0 && ok; --kp) {
           const int slot = seq % kSlots;
@@ -205,20 +212,21 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           tc_fence_after();
           const uint64_t dk = dk_slot0 + slot * kSlotStep;
           for (int qp = 2 - kp; qp >= 0; --qp) {
-            mma_ss_x4<2, 2>(tS[b], dq[qp], dk, idesc_s, first ? 0u : 1u);
+            mma_ss_x4<2, 2>(tS, dq[qp], dk, idesc_s, first ? 0u : 1u);
             first = false;
           }
           mma_commit(bar_free(slot));     // the plane tile is free again once these MMAs have retired
           ++seq;
         }
-        if (ok) mma_commit(bar_s(b));
+        if (ok) mma_commit(bar_s);
       };
-      if (ok) issue_s(0);
+      if (ok) issue_s();
       for (int j = 0; ok && j < n_t; ++j) {
         if (j + 1 < n_t) {
-          // S buffer (j+1)&1 held S(j-1): the fold warps must have finished their second pass over it
-          if (j >= 1 && !(ok = mbar_wait(bar_sfree((j + 1) & 1), ((j - 1) / 2) & 1, &abort_flag, prm.status, BAR_SFREE))) break;
-          issue_s((j + 1) & 1);
+          // S(j+1) as soon as the fold warps hold S(j) in registers: it runs while they work on tile j
+          if (!(ok = mbar_wait(bar_sfree, j & 1, &abort_flag, prm.status, BAR_SFREE))) break;
+          tc_fence_after();
+          issue_s();
           if (!ok) break;
         }
         if (!(ok = mbar_wait(bar_p, j & 1, &abort_flag, prm.status, BAR_P))) break;
@@ -241,57 +249,83 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (ok) mma_commit(bar_pv);      // O_j is complete; the P planes may be overwritten
       }
     }
-  } else if (warp < 4) {
-    // ---------------- fold warps: one thread per query row ----------------
-    const int row = warp * 32 + lane;                       // row within the tile == TMEM lane
+  } else {
+    // ---------------- fold warps: four threads per query row ----------------
+    const int qd = warp & 3, cq = warp >> 2;                // TMEM lane quadrant, column quarter
+    const int row = qd * 32 + lane;                         // row within the tile == TMEM lane
     const int qi = q0 + row;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float c = prm.scale_log2;
-    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;
-    float o_run[64];                                        // running sum of O over the key tiles, relative to m_ref
+    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;   // zsum: this thread's 32 columns only
+    float o_run[16];                                        // running sum of O over the key tiles (columns 16 cq ...), relative to m_ref
 #pragma unroll
-    for (int i = 0; i < 64; ++i) o_run[i] = 0.f;
+    for (int i = 0; i < 16; ++i) o_run[i] = 0.f;
     bool alive = true;
 
     // o_run += O (the finished P V of one key tile)
     auto take_o = [&]() {
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tO + lane_off, r0);
-      tmem_ld32(tO + lane_off + 32, r1);
+      uint32_t r[16];
+      tmem_ld16(tO + lane_off + 16 * cq, r);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { o_run[i] += __uint_as_float(r0[i]); o_run[32 + i] += __uint_as_float(r1[i]); }
+      for (int i = 0; i < 16; ++i) o_run[i] += __uint_as_float(r[i]);
     };
 
     for (int j = 0; j < n_t; ++j) {
-      const int b = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s(b), (j / 2) & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
       tc_fence_after();
-      const int k0 = k_begin + j * 128;
-      const bool tail = k0 + 128 > k_end;
-      const bool diag = prm.is_causal && (k0 + koff + 127 > q0);
-      const bool masked = tail || diag;
-      const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
-      // ---- pass 1 over the S row: the row max (the row itself stays in TMEM), 64 columns per TMEM round trip ----
-      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t r[64];
-        tmem_ld32(tS[b] + lane_off + 64 * hf, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-        tmem_ld32(tS[b] + lane_off + 64 * hf + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      float sv[32];
+      {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + 32 * cq, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 64; i += 8) {
-          float t[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) t[e] = (masked && k0 + 64 * hf + i + e > lim) ? -CUDART_INF_F : __uint_as_float(r[i + e]);
-          mx[0] = max3f(mx[0], t[0], t[1]); mx[1] = max3f(mx[1], t[2], t[3]);
-          mx[2] = max3f(mx[2], t[4], t[5]); mx[3] = max3f(mx[3], t[6], t[7]);
-        }
+        for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
       }
-      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      tc_fence_before();
+      mbar_arrive(bar_sfree);        // S may be overwritten with the next tile's scores
+      const int k0 = k_begin + j * 128 + 32 * cq;           // first (local) key of this thread's columns
+      const bool tail = k_begin + j * 128 + 128 > k_end;
+      const bool diag = prm.is_causal && (k_begin + j * 128 + koff + 127 > q0);
+      if (tail || diag) {
+        const int lim = prm.is_causal ? min(k_end - 1, qi - koff) : k_end - 1;   // last admissible (local) key of this row
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (k0 + i > lim) sv[i] = -CUDART_INF_F;
+      }
+      // ---- the row max: this quarter, then the exchange with the three other threads of the row ----
+      float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+      for (int i = 4; i < 28; i += 8) {
+        mx[0] = max3f(mx[0], sv[i], sv[i + 1]); mx[1] = max3f(mx[1], sv[i + 2], sv[i + 3]);
+        mx[2] = max3f(mx[2], sv[i + 4], sv[i + 5]); mx[3] = max3f(mx[3], sv[i + 6], sv[i + 7]);
+      }
+      mx[0] = max3f(mx[0], sv[28], sv[29]); mx[1] = max3f(mx[1], sv[30], sv[31]);
+      row_max[j & 1][cq][row] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      mbar_arrive(bar_row(qd));
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), j & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
+      float tmax = fmaxf(fmaxf(row_max[j & 1][0][row], row_max[j & 1][1][row]), fmaxf(row_max[j & 1][2][row], row_max[j & 1][3][row]));
       tmax *= c;
       m_true = fmaxf(m_true, tmax);
+      // the same decision in all four threads of the row (same tmax, same m_ref)
+      const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
+      float alpha = 1.f;
+      if (move) {
+        const float m_new = fmaxf(m_ref, tmax);
+        alpha = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_ref - m_new);
+        m_ref = m_new;
+      }
+      const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+      // ---- p = 2^(s*c - m) in place of the scores, and the quarter-row sum (all of it overlaps P V of tile j-1) ----
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        // ex2.approx: 2 units in the last place, i.e. 2.4e-7 relative on a weight
+        sv[i] = fast_exp2(fmaf(sv[i], c, -m_use));
+        sv[i + 1] = fast_exp2(fmaf(sv[i + 1], c, -m_use));
+        ps[(i >> 1) & 3] += sv[i] + sv[i + 1];
+      }
+      zsum = zsum * alpha + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
       if (j > 0) {
         // P V of the previous key tile has retired: its O goes into the running sum (both are relative to the m_ref
         // of that tile) before P V of this tile starts the accumulator from zero again; the P planes are free
@@ -299,61 +333,27 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_after();
         take_o();
       }
-      const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
       if (move) {
-        const float m_new = fmaxf(m_ref, tmax);
-        const float alpha = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_ref - m_new);
-        zsum *= alpha;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) o_run[i] *= alpha;
-        m_ref = m_new;
+        for (int i = 0; i < 16; ++i) o_run[i] *= alpha;
       }
-      const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      // ---- pass 2: p = 2^(s*c - m), row sum, and the split of p into its three bf16 planes ----
-      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      // ---- the split of p into its three bf16 planes, 16 keys (8 TMEM columns per plane) at a time ----
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t r[64];
-        tmem_ld32(tS[b] + lane_off + 64 * hf, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-        tmem_ld32(tS[b] + lane_off + 64 * hf + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-        tmem_wait_ld();
-        if (hf == 1) {                  // the whole row has been read twice: this S buffer may be overwritten
-          tc_fence_before();
-          mbar_arrive(bar_sfree(b));
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t pk[3][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          split3_pair(sv[16 * ch + 2 * i], sv[16 * ch + 2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
         }
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t pk[3][16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int kk = k0 + 64 * hf + 32 * ch + 2 * i;
-            const float s0 = (masked && kk > lim) ? -CUDART_INF_F : __uint_as_float(r[32 * ch + 2 * i]);
-            const float s1 = (masked && kk + 1 > lim) ? -CUDART_INF_F : __uint_as_float(r[32 * ch + 2 * i + 1]);
-            // ex2.approx: 2 units in the last place, i.e. 2.4e-7 relative on a weight
-            const float p0 = fast_exp2(fmaf(s0, c, -m_use));
-            const float p1 = fast_exp2(fmaf(s1, c, -m_use));
-            ps[i & 3] += p0 + p1;
-            const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0, p1);
-            const float2 f0 = __bfloat1622float2(a0);
-            const float r0 = p0 - f0.x, r1 = p1 - f0.y;
-            const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
-            const float2 f1 = __bfloat1622float2(a1);
-            const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
-            pk[0][i] = *reinterpret_cast<const uint32_t*>(&a0);
-            pk[1][i] = *reinterpret_cast<const uint32_t*>(&a1);
-            pk[2][i] = *reinterpret_cast<const uint32_t*>(&a2);
-          }
-#pragma unroll
-          for (int p = 0; p < 3; ++p) tmem_st16(tP[p] + lane_off + 32 * hf + 16 * ch, pk[p]);
-        }
+        for (int p = 0; p < 3; ++p) tmem_st8(tP[p] + lane_off + 16 * cq + 8 * ch, pk[p]);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
-      zsum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
     }
 
-    // epilogue: the last key tile's O, renormalisation to the true max, the summary row
+    // epilogue: the last key tile's O, the row sum over the four quarters, renormalisation to the true max, the summary row
     const int r_chunk = blockIdx.x * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
@@ -363,19 +363,27 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (alive) {
         tc_fence_after();
         take_o();
+        row_sum[cq][row] = zsum;
+        mbar_arrive(bar_row(qd));
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), n_t & 1, &abort_flag, prm.status, BAR_ROW))) alive = false;
+      }
+      if (alive) {
+        const float ztot = (row_sum[0][row] + row_sum[1][row]) + (row_sum[2][row] + row_sum[3][row]);
         const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true);
-        z_out = zsum * f;
+        z_out = ztot * f;
         m_out = z_out > 0.f ? m_true : -CUDART_INF_F;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) o_run[i] = z_out > 0.f ? o_run[i] * f : 0.f;
+        for (int i = 0; i < 16; ++i) o_run[i] = z_out > 0.f ? o_run[i] * f : 0.f;
       }
     }
     if (row_ok && (alive || n_t == 0)) {
-      prm.m[ro] = m_out;
-      prm.z[ro] = z_out;
-      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, o_run);
-      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, o_run);
-      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, o_run);
+      if (cq == 0) {
+        prm.m[ro] = m_out;
+        prm.z[ro] = z_out;
+      }
+      if (prm.summary_dtype == ELSA_F32) store_row16<float>(static_cast<float*>(prm.s) + ro * 64 + 16 * cq, o_run);
+      else if (prm.summary_dtype == ELSA_F16) store_row16<__half>(static_cast<__half*>(prm.s) + ro * 64 + 16 * cq, o_run);
+      else store_row16<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64 + 16 * cq, o_run);
     }
   }
 

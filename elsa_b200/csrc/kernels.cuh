@@ -83,6 +83,12 @@ bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc_workspace_bytes(int bh, int n_ctx);
 int bwd_tc(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
            int dtype, cudaStream_t st);
+// tcgen05 backward for fp32 inputs split into three bf16 planes (bwd_tc3.cu); workspace = padded D / LSE vectors +
+// the planes of q, dout (n_ctx rows) and k, v (n_keys rows)
+bool bwd_tc3_supported(int dtype, int head_dim, bool has_bias);
+int64_t bwd_tc3_workspace_bytes(int bh, int n_ctx, int n_keys);
+int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
+            cudaStream_t st);
 // D, LSE from out, dout (any strides) and the row state (bwd_simt.cu)
 int bwd_preprocess_any(const void* out, Strides os, const void* dout, Strides gs, const float* row_m, const float* row_z,
                        float* row_d, float* row_lse, int dtype, int batch, int heads, int n_ctx, int head_dim, cudaStream_t st);

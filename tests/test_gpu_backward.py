@@ -166,3 +166,27 @@ def test_tensor_core_path_repeats_bit_for_bit(dtype, causal):
         # one spacing of the output type at the largest magnitude: a different fp32 summation order can move a
         # value across a rounding boundary, nothing more
         assert (cur[5].float() - ref[5].float()).abs().max().item() <= scale * (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7), rep
+
+
+@pytest.mark.parametrize("n,causal,h", [(512, False, 2), (1000, True, 2), (1153, False, 3), (4097, True, 1)])
+def test_fp32_tensor_core_backward_matches_the_fma_backward_and_fp64(n, causal, h):
+    """fp32 inputs with head dim 64 and at least 512 tokens take the tensor-core backward (three bf16 planes per
+    operand, fresh accumulators per tile pair); ELSA_FLAG_FP32_FMA selects the FP32-FMA kernels.  Both must meet the
+    fp32 gradient bound against fp64, and the tensor-core result must repeat bit for bit (no atomics anywhere)."""
+    from elsa_b200 import _lib
+    from elsa_b200.attention_bwd import _backward_impl
+    g = torch.Generator().manual_seed(900 + n)
+    q, k, v, do = (torch.randn(1, h, n, 64, generator=g).to(DEV) for _ in range(4))
+    out, rm, rz = E.twopass_attention_with_state(q, k, v, is_causal=causal)[:3]
+    tc = _backward_impl(q, k, v, out, do, bias=None, is_causal=causal, row_m=rm, row_z=rz, want_dbias=False)[:3]
+    tc2 = _backward_impl(q, k, v, out, do, bias=None, is_causal=causal, row_m=rm, row_z=rz, want_dbias=False)[:3]
+    fma = _backward_impl(q, k, v, out, do, bias=None, is_causal=causal, row_m=rm, row_z=rz, want_dbias=False,
+                         flags=_lib.FLAG_FP32_FMA)[:3]
+    q64, k64, v64 = (t.cpu().double().requires_grad_(True) for t in (q, k, v))
+    O.softmax_attention_fp64(q64, k64, v64, bias=None, is_causal=causal).backward(do.cpu().double())
+    for name, a, a2, b, ref in zip(("dq", "dk", "dv"), tc, tc2, fma, (q64.grad, k64.grad, v64.grad)):
+        assert torch.equal(a, a2), name
+        bound = 2e-6 * max(1.0, float(ref.abs().max()))
+        assert U.max_abs(a, ref) <= bound, (name, "tensor cores")
+        # (the FP32-FMA kernels sum a row's thousands of terms in one fp32 chain per thread: twice the bound at N = 4097)
+        assert U.max_abs(b, ref) <= 2 * bound, (name, "fma")
