@@ -242,10 +242,12 @@ extern "C" int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream) {
 extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
 
 static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
+static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
 
 extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
   (void)is_causal;
-  if (backward) return tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ? 1 : 0;
+  if (backward)
+    return (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
   return (tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
 }
 

@@ -9,8 +9,8 @@
 // streamed dQ (one kernel, five contractions) would need global atomics for dQ and more TMEM than there is, so the
 // work is done by two kernels of the same shape as the forward one, seven contractions per pair in all:
 //
-//   bwd3_dq_kernel    one CTA per 128-row QUERY tile, 64-key tiles streamed:
-//                       S  = Q K^T, dP = dO V^T       A = Q / dO planes (copied once into TMEM), B = K / V planes
+//   bwd3_dq_kernel    one CTA per 128-row QUERY tile, 128-key tiles streamed:
+//                       S  = Q K^T, dP = dO V^T       A = Q / dO planes (shared memory), B = K / V planes
 //                       dS = P (dP - D), P = 2^(S c - LSE)          four threads per query row
 //                       dQ_j = dS K                    A = dS planes (TMEM), B = the same K planes, MN-major
 //                     dQ = scale * sum_j dQ_j in registers, written once: no atomics, deterministic
@@ -21,8 +21,8 @@
 //                       dV_i = P^T dO, dK_i = dS^T Q   A = P^T / dS^T planes (TMEM), B = the same dO / Q planes, MN-major
 //                     dV = sum_i dV_i, dK = scale * sum_i dK_i in registers
 //
-// Both kernels: 16 fold warps (warp w: TMEM lanes 32 (w % 4) ..., columns 16 (w / 4) ... of the 64-wide tile),
-// a TMA producer warp and an MMA-issuing warp; 8 KB plane tiles through a shared-memory ring in the order the issuer
+// Both kernels: 16 fold warps (warp w: TMEM lanes 32 (w % 4) ..., column quarter w / 4 of the streamed tile),
+// a TMA producer warp and an MMA-issuing warp; plane tiles through shared-memory rings in the order the issuer
 // consumes them (planes from the lightest to the leading one: the cross terms are added in order of increasing
 // weight).  The score / dP tiles of pair t+1 are issued as soon as the fold warps hold those of pair t in registers,
 // so the exponentials and the splits of one pair overlap the contractions of its neighbours.
@@ -43,15 +43,14 @@ constexpr int kProducerWarp = 16, kIssuerWarp = 17;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kSlotStep = kSlotBytes >> 4;   // shared-memory descriptors count 16-byte units
 
-// dQ kernel: 24 slots; the six 128-row planes of Q and dO are staged in slots 12..23 and copied into TMEM before the
-// ring's first pass reaches them
-constexpr int kDqSlots = 24;
-constexpr int kDqSmem = kDqSlots * kSlotBytes + 1024;
+// dQ kernel: Q and dO planes resident (96 KB), a ring of 6 K plane tiles and one of 2 V plane tiles (16 KB each)
+constexpr int kDqKSlots = 6, kDqVSlots = 2;
+constexpr int kDqSmem = (6 + kDqKSlots + kDqVSlots) * kPlaneBytes + 1024;
 // dK/dV kernel: K and V planes resident (96 KB), 15 ring slots, 4 stages of (-LSE, -D) vectors of 64 queries
 constexpr int kKvSlots = 15, kVecStages = 4, kVecBytes = 2 * 64 * 4;
 constexpr int kKvSmem = 6 * kPlaneBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
 
-enum BarId { BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_COPIED = 44, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
+enum BarId { BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
 
 struct Bwd3Params {
   const float* nlse_pad; const float* nd_pad;   // [BH][n_pad]: -LSE, -D; padding rows hold -inf / 0
@@ -83,15 +82,18 @@ __device__ __forceinline__ void split_store16(const float (&x)[16], uint32_t tp0
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// dQ: one CTA per 128-row query tile
-// TMEM columns: Q planes [0,96) dO planes [96,192) S [192,256) dP [256,320) dQ_j [320,384) dS planes [384,480)
+// dQ: one CTA per 128-row query tile, 128-key tiles (N = 128 for S and dP: a tcgen05.mma with N = 64 costs 48-70
+// cycles for 32 cycles of math, one with N = 128 costs 64 for 64)
+// TMEM columns: S [0,128) dP [128,256) dQ_j [256,320) dS planes [320,512) (plane p at 320 + 64 p)
+// Shared memory: Q planes, dO planes (resident, 96 KB) | K ring, 6 slots of 16 KB (the planes of key tile j stay until
+// dQ_j has read them, while S of tile j+1 needs the next three) | V ring, 2 slots
 // ------------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1)
 bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                const Bwd3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kDqSlots + 6];
+  __shared__ __align__(8) uint64_t bars[2 * (kDqKSlots + kDqVSlots) + 5];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -101,28 +103,32 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int N = prm.n_ctx, NK = prm.n_keys, koff = prm.key_offset;
   int ke = NK;
   if (prm.is_causal) ke = min(ke, min(q0 + 128, N) - koff);   // keys above the tile's last row are never admissible
-  const int n_t = ke > 0 ? (ke + 63) / 64 : 0;                // 64-key tiles this query tile visits
+  const int n_t = ke > 0 ? (ke + 127) / 128 : 0;              // 128-key tiles this query tile visits
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  auto sSlot = [&](int i) { return smem_base + i * kSlotBytes; };
+  auto sQ = [&](int p) { return smem_base + p * kPlaneBytes; };
+  auto sDO = [&](int p) { return smem_base + (3 + p) * kPlaneBytes; };
+  auto sKs = [&](int i) { return smem_base + (6 + i) * kPlaneBytes; };
+  auto sVs = [&](int i) { return smem_base + (6 + kDqKSlots + i) * kPlaneBytes; };
   const uint32_t bar0 = smem_u32(bars);
-  auto bar_full = [&](int i) { return bar0 + 8 * i; };
-  auto bar_free = [&](int i) { return bar0 + 8 * (kDqSlots + i); };
-  const uint32_t barx = bar0 + 8 * 2 * kDqSlots;
+  auto bar_kfull = [&](int i) { return bar0 + 8 * i; };
+  auto bar_kfree = [&](int i) { return bar0 + 8 * (kDqKSlots + i); };
+  auto bar_vfull = [&](int i) { return bar0 + 8 * (2 * kDqKSlots + i); };
+  auto bar_vfree = [&](int i) { return bar0 + 8 * (2 * kDqKSlots + kDqVSlots + i); };
+  const uint32_t barx = bar0 + 8 * 2 * (kDqKSlots + kDqVSlots);
   const uint32_t bar_stage = barx;            // the Q / dO planes are in shared memory
-  const uint32_t bar_copied = barx + 8;       // ... and have been copied into TMEM: their slots join the ring
-  const uint32_t bar_sdp = barx + 16;         // S(j), dP(j) are in TMEM
-  const uint32_t bar_sfree = barx + 24;       // the fold warps hold them in registers
-  const uint32_t bar_ds = barx + 32;          // the dS planes of tile j have been delivered
-  const uint32_t bar_dq = barx + 40;          // dQ_j is complete
+  const uint32_t bar_sdp = barx + 8;          // dP(j), S(j) are in TMEM
+  const uint32_t bar_sfree = barx + 16;       // the fold warps hold them in registers
+  const uint32_t bar_ds = barx + 24;          // the dS planes of tile j have been delivered
+  const uint32_t bar_dq = barx + 32;          // dQ_j is complete
 
   if (tid == 0) {
     abort_flag = 0;
-    for (int i = 0; i < kDqSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
-    mbar_init(bar_stage, 1); mbar_init(bar_copied, kFoldThreads);
-    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldThreads);
-    mbar_init(bar_ds, kFoldThreads); mbar_init(bar_dq, 1);
+    for (int i = 0; i < kDqKSlots; ++i) { mbar_init(bar_kfull(i), 1); mbar_init(bar_kfree(i), 1); }
+    for (int i = 0; i < kDqVSlots; ++i) { mbar_init(bar_vfull(i), 1); mbar_init(bar_vfree(i), 1); }
+    mbar_init(bar_stage, 1);
+    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldWarps);
+    mbar_init(bar_ds, kFoldWarps); mbar_init(bar_dq, 1);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -133,8 +139,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tA = tmem_base;                 // Q planes at 32 p, dO planes at 96 + 32 p
-  const uint32_t tS = tmem_base + 192, tdP = tmem_base + 256, tdQ = tmem_base + 320, tDS = tmem_base + 384;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256, tDS = tmem_base + 320;
 
   if (warp == kProducerWarp) {
     if (n_t > 0 && lane == 0) {
@@ -142,54 +147,59 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
       mbar_arrive_expect_tx(bar_stage, 6 * kPlaneBytes);
       for (int p = 0; p < 3; ++p) {
-        tma_load_4d(sSlot(12 + 2 * p), &tmap_q, bar_stage, 0, q0, bh, p);
-        tma_load_4d(sSlot(18 + 2 * p), &tmap_do, bar_stage, 0, q0, bh, p);
+        tma_load_4d(sQ(p), &tmap_q, bar_stage, 0, q0, bh, p);
+        tma_load_4d(sDO(p), &tmap_do, bar_stage, 0, q0, bh, p);
       }
-      int seq = 0;
       bool ok = true;
-      auto load = [&](const CUtensorMap* map, int tile, int plane) {
-        const int slot = seq % kDqSlots;
-        if (seq >= kDqSlots) ok = mbar_wait(bar_free(slot), ((seq / kDqSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE);
-        else if (slot >= 12) ok = mbar_wait(bar_copied, 0, &abort_flag, prm.status, BAR_COPIED);
-        if (!ok) return;
-        mbar_arrive_expect_tx(bar_full(slot), kSlotBytes);
-        tma_load_4d(sSlot(slot), map, bar_full(slot), 0, tile * 64, bh, plane);
-        ++seq;
-      };
+      // per key tile: its K planes (ring sequence numbers 3 j .. 3 j + 2), then its V planes; planes in the order of
+      // increasing weight.  A V slot is released by the dP group that read it, a K slot by the dQ group.
       for (int j = 0; j < n_t && ok; ++j) {
-        for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, j, p);       // planes in the order of increasing weight
-        for (int p = 2; p >= 0 && ok; --p) load(&tmap_v, j, p);
+        for (int x = 0; x < 3 && ok; ++x) {
+          const int seq = 3 * j + x, slot = seq % kDqKSlots;
+          if (seq >= kDqKSlots && !(ok = mbar_wait(bar_kfree(slot), ((seq / kDqKSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
+          mbar_arrive_expect_tx(bar_kfull(slot), kPlaneBytes);
+          tma_load_4d(sKs(slot), &tmap_k, bar_kfull(slot), 0, j * 128, bh, 2 - x);
+        }
+        for (int x = 0; x < 3 && ok; ++x) {
+          const int seq = 3 * j + x, slot = seq % kDqVSlots;
+          if (seq >= kDqVSlots && !(ok = mbar_wait(bar_vfree(slot), ((seq / kDqVSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
+          mbar_arrive_expect_tx(bar_vfull(slot), kPlaneBytes);
+          tma_load_4d(sVs(slot), &tmap_v, bar_vfull(slot), 0, j * 128, bh, 2 - x);
+        }
       }
     }
   } else if (warp == kIssuerWarp) {
     if (n_t > 0 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 64);    // S, dP: A in TMEM, B K-major, N = 64 keys
-      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dQ_j:  A in TMEM, B (K) MN-major, N = 64 = d
-      const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dmn_slot0 = make_sdesc(sSlot(0), 64 * 128, 1024);
-      bool ok = mbar_wait(bar_copied, 0, &abort_flag, prm.status, BAR_COPIED);
-      // ring sequence numbers of key tile j: K planes 2, 1, 0 at 6 j .. 6 j + 2, V planes at 6 j + 3 .. 6 j + 5
+      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 128);   // S, dP: A, B K-major, N = 128 keys
+      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dQ_j: A in TMEM, B (K) MN-major, N = 64 = d
+      const uint64_t dQp[3] = {make_sdesc(sQ(0), 16, 1024), make_sdesc(sQ(1), 16, 1024), make_sdesc(sQ(2), 16, 1024)};
+      const uint64_t dDOp[3] = {make_sdesc(sDO(0), 16, 1024), make_sdesc(sDO(1), 16, 1024), make_sdesc(sDO(2), 16, 1024)};
+      const uint64_t dk_k0 = make_sdesc(sKs(0), 16, 1024), dk_mn0 = make_sdesc(sKs(0), 128 * 128, 1024);
+      const uint64_t dv_k0 = make_sdesc(sVs(0), 16, 1024);
+      constexpr uint64_t kPlaneStep = kPlaneBytes >> 4;
+      bool ok = mbar_wait(bar_stage, 0, &abort_flag, prm.status, BAR_STAGE);
       auto issue_sdp = [&](int j) {
         bool first = true;
-        for (int kp = 2; kp >= 0 && ok; --kp) {
-          const int seq = 6 * j + 2 - kp, slot = seq % kDqSlots;
-          if (!(ok = mbar_wait(bar_full(slot), (seq / kDqSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
-          tc_fence_after();
-          for (int qp = 2 - kp; qp >= 0; --qp) {
-            mma_ts_x4<8, 2>(tS, tA + 32 * qp, dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
-            first = false;
-          }                                   // the K planes stay: dQ_j reads them again
-        }
-        first = true;
-        for (int vp = 2; vp >= 0 && ok; --vp) {
-          const int seq = 6 * j + 5 - vp, slot = seq % kDqSlots;
-          if (!(ok = mbar_wait(bar_full(slot), (seq / kDqSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+        for (int vp = 2; vp >= 0 && ok; --vp) {            // dP = dO V^T
+          const int seq = 3 * j + 2 - vp, slot = seq % kDqVSlots;
+          if (!(ok = mbar_wait(bar_vfull(slot), (seq / kDqVSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           for (int gp = 2 - vp; gp >= 0; --gp) {
-            mma_ts_x4<8, 2>(tdP, tA + 96 + 32 * gp, dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
+            mma_ss_x4<2, 2>(tdP, dDOp[gp], dv_k0 + slot * kPlaneStep, idesc_k, first ? 0u : 1u);
             first = false;
           }
-          mma_commit(bar_free(slot));
+          mma_commit(bar_vfree(slot));
+        }
+        first = true;
+        for (int kp = 2; kp >= 0 && ok; --kp) {            // S = Q K^T
+          const int seq = 3 * j + 2 - kp, slot = seq % kDqKSlots;
+          if (!(ok = mbar_wait(bar_kfull(slot), (seq / kDqKSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
+          tc_fence_after();
+          for (int qp = 2 - kp; qp >= 0; --qp) {
+            mma_ss_x4<2, 2>(tS, dQp[qp], dk_k0 + slot * kPlaneStep, idesc_k, first ? 0u : 1u);
+            first = false;
+          }                                   // the K planes stay: dQ_j reads them again
         }
         if (ok) mma_commit(bar_sdp);
       };
@@ -207,20 +217,21 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!(ok = mbar_wait(bar_ds, j & 1, &abort_flag, prm.status, BAR_DS))) break;
         tc_fence_after();
         bool first = true;
-        for (int kp = 2; kp >= 0; --kp) {
-          const int slot = (6 * j + 2 - kp) % kDqSlots;
+        for (int kp = 2; kp >= 0; --kp) {                  // dQ_j = dS K over the 128 keys (eight K-steps)
+          const int slot = (3 * j + 2 - kp) % kDqKSlots;
           for (int sp = 2 - kp; sp >= 0; --sp) {
-            mma_ts_x4<8, 128>(tdQ, tDS + 32 * sp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
+            mma_ts_x4<8, 128>(tdQ, tDS + 64 * sp, dk_mn0 + slot * kPlaneStep, idesc_mn, first ? 0u : 1u);
+            mma_ts_x4<8, 128>(tdQ, tDS + 64 * sp + 32, dk_mn0 + slot * kPlaneStep + 512, idesc_mn, 1u);
             first = false;
           }
-          mma_commit(bar_free(slot));
+          mma_commit(bar_kfree(slot));
         }
         mma_commit(bar_dq);                   // dQ_j is complete; the dS planes may be overwritten
       }
     }
   } else {
     // ---------------- fold warps: four threads per query row ----------------
-    const int qd = warp & 3, cq = warp >> 2;                // TMEM lane quadrant, column quarter
+    const int qd = warp & 3, cq = warp >> 2;                // TMEM lane quadrant, column quarter (32 keys)
     const int row = qd * 32 + lane;
     const int qi = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
@@ -231,26 +242,6 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
     for (int i = 0; i < 16; ++i) dq_run[i] = 0.f;
     bool alive = n_t > 0;
-
-    // one-time copy of the Q and dO planes from shared memory into TMEM (the A operands of S and dP): lane = query
-    // row, 32 columns of bf16 pairs per plane; the 128-byte swizzle of the TMA tile is undone on the way.
-    // Column quarter cq copies planes cq and cq + 4 of (Q0, Q1, Q2, dO0, dO1, dO2).
-    if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_stage, 0, &abort_flag, prm.status, BAR_STAGE))) alive = false;
-    if (alive) {
-      for (int idx = cq; idx < 6; idx += 4) {
-        const uint8_t* src = smem_gen + (12 + 2 * idx) * kSlotBytes + row * 128;
-        uint32_t w[32];
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint4 t = *reinterpret_cast<const uint4*>(src + ((g ^ (row & 7)) << 4));
-          w[4 * g] = t.x; w[4 * g + 1] = t.y; w[4 * g + 2] = t.z; w[4 * g + 3] = t.w;
-        }
-        tmem_st32(tA + 32 * idx + lane_off, w);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_copied);
-    }
 
     auto take_dq = [&]() {
       uint32_t r[16];
@@ -263,19 +254,19 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     for (int j = 0; alive && j < n_t; ++j) {
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, j & 1, &abort_flag, prm.status, BAR_SDP))) { alive = false; break; }
       tc_fence_after();
-      float ds[16];
+      float ds[32];
       {
-        uint32_t rs[16], rp[16];
-        tmem_ld16(tS + lane_off + 16 * cq, rs);
-        tmem_ld16(tdP + lane_off + 16 * cq, rp);
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_off + 32 * cq, rs);
+        tmem_ld32(tdP + lane_off + 32 * cq, rp);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(bar_sfree);      // S and dP may be overwritten with the next tile's
-        const int kb = j * 64 + 16 * cq;                    // first (local) key of this thread's columns
-        const bool masked = (j * 64 + 64 > NK) || (prm.is_causal && (j * 64 + koff + 63 > q0));
+        mbar_arrive_warp(bar_sfree, lane);      // S and dP may be overwritten with the next tile's
+        const int kb = j * 128 + 32 * cq;                   // first (local) key of this thread's columns
+        const bool masked = (j * 128 + 128 > NK) || (prm.is_causal && (j * 128 + koff + 127 > q0));
         const int lim = prm.is_causal ? min(NK - 1, qi - koff) : NK - 1;   // last admissible (local) key of this row
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 32; ++i) {
           float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nlse));
           if (masked && kb + i > lim) p = 0.f;
           ds[i] = p * (__uint_as_float(rp[i]) + nd);
@@ -287,10 +278,18 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
         take_dq();
       }
-      split_store16(ds, tDS + lane_off, 8 * cq);
+      // the three bf16 planes of dS: 16 keys (8 TMEM columns per plane) at a time
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t pk[3][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) split3_pair(ds[16 * ch + 2 * i], ds[16 * ch + 2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
+#pragma unroll
+        for (int p = 0; p < 3; ++p) tmem_st8(tDS + 64 * p + lane_off + 16 * cq + 8 * ch, pk[p]);
+      }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_ds);
+      mbar_arrive_warp(bar_ds, lane);
     }
     if (alive && n_t > 0) {
       if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (n_t - 1) & 1, &abort_flag, prm.status, BAR_ACC))) alive = false;
@@ -352,8 +351,8 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     abort_flag = 0;
     for (int i = 0; i < kKvSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
     mbar_init(bar_kv, 1);
-    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldThreads);
-    mbar_init(bar_pl, kFoldThreads); mbar_init(bar_acc, 1);
+    mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldWarps);
+    mbar_init(bar_pl, kFoldWarps); mbar_init(bar_acc, 1);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -503,7 +502,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld16(tdP + lane_off + 16 * cq, rp);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(bar_sfree);      // S^T and dP^T may be overwritten with the next tile's
+        mbar_arrive_warp(bar_sfree, lane);      // S^T and dP^T may be overwritten with the next tile's
         const float4* nl4 = reinterpret_cast<const float4*>(smem_gen + vec_off + (it % kVecStages) * kVecBytes) + 4 * cq;
         const float4* nd4 = nl4 + 16;
         const bool masked = cta_tail || (prm.is_causal && q_tile0 < kseq0 + 128);   // only the diagonal tiles / the last key tile
@@ -532,7 +531,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       split_store16(ds, tDS + lane_off, 8 * cq);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_pl);
+      mbar_arrive_warp(bar_pl, lane);
     }
     if (alive && n_it > 0) {
       if (!__all_sync(0xffffffffu, mbar_wait(bar_acc, (n_it - 1) & 1, &abort_flag, prm.status, BAR_ACC))) alive = false;
@@ -626,7 +625,7 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
 
   // planes as [3, B*H, rows, 64] bf16 tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
   const Strides sq = contiguous_strides(bh, N, 64), sk = contiguous_strides(bh, NK, 64);
-  CUtensorMap mq128, mdo128, mk64, mv64, mq64, mdo64, mk128, mv128;
+  CUtensorMap mq128, mdo128, mq64, mdo64, mk128, mv128;
   if ((rc = make_tmap_rows64(&mq128, q3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mdo128, do3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mq64, q3, ELSA_BF16, N, bh, 3, sq, 64)) != ELSA_OK) return rc;
@@ -640,18 +639,16 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   prm.n_keys = NK; prm.key_offset = p.key_offset;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   if (NK > 0) {
-    if ((rc = make_tmap_rows64(&mk64, k3, ELSA_BF16, NK, bh, 3, sk, 64)) != ELSA_OK) return rc;
-    if ((rc = make_tmap_rows64(&mv64, v3, ELSA_BF16, NK, bh, 3, sk, 64)) != ELSA_OK) return rc;
     if ((rc = make_tmap_rows64(&mk128, k3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
     if ((rc = make_tmap_rows64(&mv128, v3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
   } else {
-    mk64 = mv64 = mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
+    mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
   }
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dq_kernel), kDqSmem)) != ELSA_OK) return rc;
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dkv_kernel), kKvSmem)) != ELSA_OK) return rc;
   {
     const dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
-    bwd3_dq_kernel<<<grid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk64, mv64, prm);
+    bwd3_dq_kernel<<<grid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk128, mv128, prm);
     ELSA_LAUNCH_CHECK();
   }
   if (NK > 0) {

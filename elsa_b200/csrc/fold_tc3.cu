@@ -153,9 +153,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int i = 0; i < kSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
-    mbar_init(bar_s, 1); mbar_init(bar_sfree, kFoldThreads);
-    mbar_init(bar_p, kFoldThreads); mbar_init(bar_pv, 1);
-    for (int qd = 0; qd < 4; ++qd) mbar_init(bar_row(qd), 128);
+    mbar_init(bar_s, 1); mbar_init(bar_sfree, kFoldWarps);
+    mbar_init(bar_p, kFoldWarps); mbar_init(bar_pv, 1);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar_row(qd), 4);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -283,7 +283,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
       }
       tc_fence_before();
-      mbar_arrive(bar_sfree);        // S may be overwritten with the next tile's scores
+      mbar_arrive_warp(bar_sfree, lane);        // S may be overwritten with the next tile's scores
       const int k0 = k_begin + j * 128 + 32 * cq;           // first (local) key of this thread's columns
       const bool tail = k_begin + j * 128 + 128 > k_end;
       const bool diag = prm.is_causal && (k_begin + j * 128 + koff + 127 > q0);
@@ -302,7 +302,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       mx[0] = max3f(mx[0], sv[28], sv[29]); mx[1] = max3f(mx[1], sv[30], sv[31]);
       row_max[j & 1][cq][row] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      mbar_arrive(bar_row(qd));
+      mbar_arrive_warp(bar_row(qd), lane);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), j & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
       float tmax = fmaxf(fmaxf(row_max[j & 1][0][row], row_max[j & 1][1][row]), fmaxf(row_max[j & 1][2][row], row_max[j & 1][3][row]));
       tmax *= c;
@@ -350,7 +350,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      mbar_arrive_warp(bar_p, lane);
     }
 
     // epilogue: the last key tile's O, the row sum over the four quarters, renormalisation to the true max, the summary row
@@ -364,7 +364,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_after();
         take_o();
         row_sum[cq][row] = zsum;
-        mbar_arrive(bar_row(qd));
+        mbar_arrive_warp(bar_row(qd), lane);
         if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), n_t & 1, &abort_flag, prm.status, BAR_ROW))) alive = false;
       }
       if (alive) {
