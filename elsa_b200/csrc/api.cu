@@ -294,9 +294,9 @@ extern "C" int elsa_phase1_fold_shard_ws(const void* q, const void* k, const voi
     char* planes = static_cast<char*>(workspace);
     const int64_t qb = fold_tc3_plane_bytes(batch * heads, n_ctx), kb = fold_tc3_plane_bytes(batch * heads, n_keys);
     int rc;
-    if ((rc = fold_tc3_split(q, contiguous_strides(heads, n_ctx, head_dim), planes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(k, contiguous_strides(heads, n_keys, head_dim), planes + qb, batch, heads, n_keys, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(v, contiguous_strides(heads, n_keys, head_dim), planes + qb + kb, batch, heads, n_keys, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(q, contiguous_strides(heads, n_ctx, head_dim), planes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(k, contiguous_strides(heads, n_keys, head_dim), planes + qb, batch, heads, n_keys, head_dim, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(v, contiguous_strides(heads, n_keys, head_dim), planes + qb + kb, batch, heads, n_keys, head_dim, st)) != ELSA_OK) return rc;
     q3 = planes; k3 = planes + qb; v3 = planes + qb + kb;
   }
   return phase1_dispatch(q, k, v, nullptr, 0, 0, 0, 0, m_buf, z_buf, s_buf, dtype, summary_dtype, batch, heads, n_ctx,
@@ -382,9 +382,9 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
     // fp32 on the tensor cores: the three bf16 planes of q, k, v, written once behind the summaries
     char* planes = ws + plan_bytes(pl);
     const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
-    if ((rc = fold_tc3_split(q, qs ? *qs : cs, planes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(k, ks ? *ks : cs, planes + plane_bytes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(v, vs ? *vs : cs, planes + 2 * plane_bytes, batch, heads, n_ctx, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(q, qs ? *qs : cs, planes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(k, ks ? *ks : cs, planes + plane_bytes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
+    if ((rc = fold_tc3_split(v, vs ? *vs : cs, planes + 2 * plane_bytes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
     q3 = planes; k3 = planes + plane_bytes; v3 = planes + 2 * plane_bytes;
   }
   // A problem that is a single (query tile, key partition) pair of the FP32-FMA kernel (49-token windows and other
@@ -604,7 +604,8 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   char* ws = static_cast<char*>(workspace);
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
-  const bool use_tc = n_keys > 0 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
+  // (the tensor-core kernels address the fp32 dQ of a shard as 64-wide rows)
+  const bool use_tc = n_keys > 0 && head_dim == 64 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
   const bool use_tc3 = n_keys > 0 && n_keys <= n_ctx && tc3_backward_ok(dtype, head_dim, n_ctx, false, flags);
   int rc = ELSA_OK;
   if (!use_tc && !use_tc3) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);

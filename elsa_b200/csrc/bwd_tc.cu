@@ -1,5 +1,6 @@
 // Backward on the 5th-generation tensor cores: exact recompute from the saved row statistics,
-// fp16 / bf16 inputs, head dim 64, causal or not, no bias.  Five contractions per (key tile, query
+// fp16 / bf16 inputs, head dim 64 (or a smaller multiple of 8, zero-padded to 64 columns by the TMA box), causal or
+// not, no bias.  Five contractions per (key tile, query
 // tile) pair -- the algorithmic minimum -- all as tcgen05.mma with TMEM accumulators:
 //
 //   S^T  = K Q^T          [128 keys x 128 queries]   TMEM (K) x smem (Q, K-major)          N = 128
@@ -74,6 +75,7 @@ struct BwdTcParams {
   Strides dks, dvs;
   int n_ctx, n_pad, bh, heads, is_causal;
   int n_keys, key_offset;                      // K/V rows of this launch and the sequence index of the first one
+  int head_dim;                                // real columns of q, k, v, dout and the gradients (<= 64)
   float scale, scale_log2;
   int* status;   // the device's status word (mapped host memory)
 };
@@ -433,6 +435,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         T* dv_row = static_cast<T*>(prm.dv) + bi * prm.dvs.b + hi * prm.dvs.h + key * prm.dvs.r + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
+          if (half * 32 + i >= prm.head_dim) continue;
           uint4 a, b;
           a.x = pack2<T>(__uint_as_float(rk[i]) * prm.scale, __uint_as_float(rk[i + 1]) * prm.scale);
           a.y = pack2<T>(__uint_as_float(rk[i + 2]) * prm.scale, __uint_as_float(rk[i + 3]) * prm.scale);
@@ -459,7 +462,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout, const float* __restrict__ row_m,
                           const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
-                          int heads, int n_ctx, int n_pad, Strides os, Strides gs) {
+                          int heads, int n_ctx, int n_pad, int head_dim, Strides os, Strides gs) {
   // blockIdx.y = (batch*head); x covers the n_pad padded rows, 8 lanes (16 bytes each) per row: no division
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = static_cast<int>(gid >> 3);        // padded row within this (batch*head)
@@ -469,7 +472,7 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   const bool in_pad = r < n_pad;
   const bool real = in_pad && r < n_ctx;
   float part = 0.f;
-  if (real) {
+  if (real && lane * 8 < head_dim) {
     const int bi = static_cast<int>(b) / heads, hi = static_cast<int>(b) - bi * heads;
     const T* o = out + bi * os.b + hi * os.h + static_cast<int64_t>(r) * os.r + lane * 8;
     const T* g = dout + bi * gs.b + hi * gs.h + static_cast<int64_t>(r) * gs.r + lane * 8;
@@ -505,10 +508,10 @@ __global__ void __launch_bounds__(256) dq_scale_kernel(float* __restrict__ acc, 
 // dq = T(acc * scale); acc is [BH][N][64] fp32, dq rows are addressed through their strides (blockIdx.y = batch*head)
 template <typename T>
 __global__ void __launch_bounds__(256)
-dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int n_ctx, int heads, Strides ds, float scale) {
+dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int n_ctx, int heads, int head_dim, Strides ds, float scale) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;        // 8 elements each: row = i / 8
   const int r = static_cast<int>(i >> 3), c = static_cast<int>(i & 7) * 8;
-  if (r >= n_ctx) return;
+  if (r >= n_ctx || c >= head_dim) return;
   const int bh = blockIdx.y, bi = bh / heads, hi = bh - bi * heads;
   const float* src = acc + (static_cast<int64_t>(bh) * n_ctx + r) * 64 + c;
   const float4 a = *reinterpret_cast<const float4*>(src);
@@ -544,7 +547,7 @@ static int bwd_tc_t(const BwdParams& p, const void* out, Strides os, const float
   {
     const dim3 pgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_pad) * 8, 256)), static_cast<unsigned>(bh));
     bwd_preprocess_pad_kernel<T><<<pgrid, 256, 0, st>>>(
-        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, p.heads, N, n_pad, os, p.gs);
+        static_cast<const T*>(out), static_cast<const T*>(p.dout), row_m, row_z, nd_pad, nlse_pad, p.heads, N, n_pad, p.head_dim, os, p.gs);
     ELSA_LAUNCH_CHECK();
   }
   ELSA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, acc_elems * 4, st));
@@ -553,16 +556,16 @@ static int bwd_tc_t(const BwdParams& p, const void* out, Strides os, const float
   int rc;
   if ((rc = make_tmap_f32_rows64(&mdq, dq_acc, N, bh, 128)) != ELSA_OK) return rc;
   const int batch = bh / p.heads;
-  if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, p.heads, batch, p.qs, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, NK, p.heads, batch, p.ks, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, p.heads, batch, p.vs, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, p.heads, batch, p.gs, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, N, p.heads, batch, p.qs, 128, p.head_dim)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, NK, p.heads, batch, p.ks, 128, p.head_dim)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, NK, p.heads, batch, p.vs, 128, p.head_dim)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, N, p.heads, batch, p.gs, 128, p.head_dim)) != ELSA_OK) return rc;
   BwdTcParams prm;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad; prm.dq_acc = dq_acc; prm.dk = p.dk; prm.dv = p.dv;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
   prm.dks = p.dks; prm.dvs = p.dvs;
-  prm.n_keys = NK; prm.key_offset = p.key_offset;
+  prm.n_keys = NK; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd_tc_kernel<T>), kBwdSmem);
   if (rc != ELSA_OK) return rc;
@@ -575,7 +578,7 @@ static int bwd_tc_t(const BwdParams& p, const void* out, Strides os, const float
     dq_scale_kernel<<<static_cast<unsigned>(cdiv64(acc_elems / 4, 256)), 256, 0, st>>>(dq_acc, acc_elems / 4, p.scale);
   } else {
     const dim3 cgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(N) * 8, 256)), static_cast<unsigned>(bh));
-    dq_convert_kernel<T><<<cgrid, 256, 0, st>>>(dq_acc, static_cast<T*>(p.dq), N, p.heads, p.dqs, p.scale);
+    dq_convert_kernel<T><<<cgrid, 256, 0, st>>>(dq_acc, static_cast<T*>(p.dq), N, p.heads, p.head_dim, p.dqs, p.scale);
   }
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
@@ -584,6 +587,7 @@ static int bwd_tc_t(const BwdParams& p, const void* out, Strides os, const float
 int bwd_tc(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
            int dtype, cudaStream_t st) {
   if (!bwd_tc_supported(dtype, p.head_dim, p.bias != nullptr) || p.dbias) return ELSA_ERR_UNSUPPORTED;
+  if (p.dq_f32 && p.head_dim != 64) return ELSA_ERR_UNSUPPORTED;   // the caller's fp32 dQ is the accumulator: 64-wide rows
   if (dtype == ELSA_F16) return bwd_tc_t<__half>(p, out, os, row_m, row_z, workspace, dtype, st);
   return bwd_tc_t<__nv_bfloat16>(p, out, os, row_m, row_z, workspace, dtype, st);
 }

@@ -1,5 +1,5 @@
 // Backward for fp32 inputs on the 5th-generation tensor cores at fp32 accuracy: exact recompute from the saved row
-// statistics, head dim 64, causal or not, no bias.  Every operand of every contraction is split into three bf16 terms
+// statistics, head dim 64 (or a smaller multiple of 8: the planes are zero-padded to 64 columns), causal or not, no bias.  Every operand of every contraction is split into three bf16 terms
 // (x = x0 + x1 + x2 exactly) and a product is formed as the six cross terms whose weight is at least 2^-16 of the
 // leading one, exactly as in the forward kernel for fp32 inputs (fold_tc3.cu).
 //
@@ -58,6 +58,7 @@ struct Bwd3Params {
   Strides dqs, dks, dvs;
   int n_ctx, n_pad, bh, heads, is_causal;
   int n_keys, key_offset;                       // K/V rows of this launch and the sequence index of the first one
+  int head_dim;                                 // real columns of the gradients (<= 64; the planes are zero-padded to 64)
   float scale, scale_log2;
   int* status;                                  // the device's status word (mapped host memory)
 };
@@ -67,9 +68,11 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void store16(float* dst, const float (&v)[16], float f) {
+// the first n (a multiple of 4, possibly <= 0) of 16 consecutive values of a gradient row
+__device__ __forceinline__ void store16(float* dst, const float (&v)[16], float f, int n) {
 #pragma unroll
-  for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i] * f, v[i + 1] * f, v[i + 2] * f, v[i + 3] * f);
+  for (int i = 0; i < 16; i += 4)
+    if (i < n) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i] * f, v[i + 1] * f, v[i + 2] * f, v[i + 3] * f);
 }
 
 // 16 values -> their three bf16 planes, 8 TMEM columns per plane starting at column `col` of plane base tp0 + 32 p
@@ -300,7 +303,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
     if (qi < N && (alive || n_t == 0)) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale);
+      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale, prm.head_dim - 16 * cq);
     }
   }
 
@@ -542,8 +545,8 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
     if (key_ok && alive) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale);
-      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, 1.f);
+      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale, prm.head_dim - 16 * cq);
+      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, 1.f, prm.head_dim - 16 * cq);
     }
   }
 
@@ -556,7 +559,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 __global__ void __launch_bounds__(256)
 bwd3_preprocess_kernel(const float* __restrict__ out, const float* __restrict__ dout, const float* __restrict__ row_m,
                        const float* __restrict__ row_z, float* __restrict__ nd_pad, float* __restrict__ nlse_pad,
-                       int heads, int n_ctx, int n_pad, Strides os, Strides gs) {
+                       int heads, int n_ctx, int n_pad, int head_dim, Strides os, Strides gs) {
   // blockIdx.y = (batch*head); x covers the n_pad padded rows, 16 lanes (16 bytes each) per row
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = static_cast<int>(gid >> 4);
@@ -565,7 +568,7 @@ bwd3_preprocess_kernel(const float* __restrict__ out, const float* __restrict__ 
   const bool in_pad = r < n_pad;
   const bool real = in_pad && r < n_ctx;
   float part = 0.f;
-  if (real) {
+  if (real && lane * 4 < head_dim) {
     const int bi = static_cast<int>(b) / heads, hi = static_cast<int>(b) - bi * heads;
     const float4 o = *reinterpret_cast<const float4*>(out + bi * os.b + hi * os.h + static_cast<int64_t>(r) * os.r + lane * 4);
     const float4 g = *reinterpret_cast<const float4*>(dout + bi * gs.b + hi * gs.h + static_cast<int64_t>(r) * gs.r + lane * 4);
@@ -615,13 +618,13 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   {
     const dim3 pgrid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(n_pad) * 16, 256)), static_cast<unsigned>(bh));
     bwd3_preprocess_kernel<<<pgrid, 256, 0, st>>>(static_cast<const float*>(out), static_cast<const float*>(p.dout), row_m,
-                                                  row_z, nd_pad, nlse_pad, p.heads, N, n_pad, os, p.gs);
+                                                  row_z, nd_pad, nlse_pad, p.heads, N, n_pad, p.head_dim, os, p.gs);
     ELSA_LAUNCH_CHECK();
   }
-  if ((rc = fold_tc3_split(p.q, p.qs, q3, batch, p.heads, N, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.dout, p.gs, do3, batch, p.heads, N, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.k, p.ks, k3, batch, p.heads, NK, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.v, p.vs, v3, batch, p.heads, NK, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.q, p.qs, q3, batch, p.heads, N, p.head_dim, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.dout, p.gs, do3, batch, p.heads, N, p.head_dim, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.k, p.ks, k3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
+  if ((rc = fold_tc3_split(p.v, p.vs, v3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
 
   // planes as [3, B*H, rows, 64] bf16 tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
   const Strides sq = contiguous_strides(bh, N, 64), sk = contiguous_strides(bh, NK, 64);
@@ -636,7 +639,7 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   prm.dq = static_cast<float*>(p.dq); prm.dk = static_cast<float*>(p.dk); prm.dv = static_cast<float*>(p.dv);
   prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
-  prm.n_keys = NK; prm.key_offset = p.key_offset;
+  prm.n_keys = NK; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   if (NK > 0) {
     if ((rc = make_tmap_rows64(&mk128, k3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;

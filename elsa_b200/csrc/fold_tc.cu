@@ -1,5 +1,6 @@
 // Phase 1 on the 5th-generation tensor cores (tcgen05 + TMEM + TMA): the per-K-partition
-// (m, z, s) fold for fp16 / bf16 inputs with head dim 64, causal or not.
+// (m, z, s) fold for fp16 / bf16 inputs with head dim 64 (or a smaller multiple of 8: the tensor maps describe the
+// d real columns, the 64-column TMA box reads the rest as zeros, and only d summary columns are stored), causal or not.
 //
 // One CTA (1 per SM: 160 KB of shared memory, all 512 TMEM columns) owns TWO 128-row query tiles of one
 // (batch*head) and one K partition, walked in 128-key tiles:
@@ -54,7 +55,7 @@ enum BarId { BAR_Q = 1, BAR_KV_FULL = 2, BAR_KV_FREE = 3, BAR_S = 4, BAR_P = 5, 
 struct FoldTcParams {
   float* m; float* z; void* s;
   int n_ctx, q_start, q_len, part_width, n_parts, bh, heads, is_causal, summary_dtype;
-  int n_keys, key_offset;
+  int n_keys, key_offset, head_dim;
   float scale_log2;
   int* status;   // the device's status word (mapped host memory)
 };
@@ -65,14 +66,17 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// the first d (a multiple of 8) of the 64 values of a summary row
 template <typename TS>
-__device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64]) {
+__device__ __forceinline__ void store_row64(TS* dst, const float (&v)[64], int d) {
   if constexpr (sizeof(TS) == 4) {
 #pragma unroll
-    for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    for (int i = 0; i < 64; i += 4)
+      if (i < d) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
   } else {
 #pragma unroll
     for (int i = 0; i < 64; i += 8) {
+      if (i >= d) continue;
       uint4 t;
       t.x = pack2<TS>(v[i], v[i + 1]); t.y = pack2<TS>(v[i + 2], v[i + 3]);
       t.z = pack2<TS>(v[i + 4], v[i + 5]); t.w = pack2<TS>(v[i + 6], v[i + 7]);
@@ -345,9 +349,9 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           prm.z[ro] = zo;
 #pragma unroll
           for (int i = 0; i < 64; ++i) ov[i] = zo > 0.f ? ov[i] * f : 0.f;
-          if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
-          else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
-          else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+          if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
+          else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
+          else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
         }
       }
     } else if (row_ok) {
@@ -358,9 +362,9 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       float ov[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) ov[i] = 0.f;
-      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * 64, ov);
-      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * 64, ov);
-      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64, ov);
+      if (prm.summary_dtype == ELSA_F32) store_row64<float>(static_cast<float*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
+      else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
+      else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
     }
   }
 
@@ -412,11 +416,11 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
-                     int box_rows) {
+                     int box_rows, int cols) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ELSA_ERR_UNSUPPORTED;
-  if ((st.b | st.h | st.r) % 8 != 0 || st.r < 64 || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
-  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  if ((st.b | st.h | st.r) % 8 != 0 || cols < 8 || cols > 64 || cols % 8 != 0 || st.r < cols || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
   // a size-1 axis may come with any stride (PyTorch reports arbitrary ones): give it a valid dummy
   const cuuint64_t sh = heads > 1 ? static_cast<cuuint64_t>(st.h) * 2 : 128, sb = batch > 1 ? static_cast<cuuint64_t>(st.b) * 2 : 128;
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st.r) * 2, sh, sb};
@@ -450,7 +454,8 @@ int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int
 }
 
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias) {
-  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim == 64 && !has_bias && encode_tiled_fn() != nullptr;
+  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && !has_bias &&
+         encode_tiled_fn() != nullptr;
 }
 
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
@@ -458,11 +463,11 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   int rc;
   const int batch = p.bh / p.heads;
-  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.heads, batch, p.qs, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_keys, p.heads, batch, p.ks, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_keys, p.heads, batch, p.vs, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.heads, batch, p.qs, 128, p.head_dim)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_keys, p.heads, batch, p.ks, 128, p.head_dim)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_keys, p.heads, batch, p.vs, 128, p.head_dim)) != ELSA_OK) return rc;
   FoldTcParams prm;
-  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
+  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;

@@ -62,7 +62,7 @@ enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, B
 struct Fold3Params {
   float* m; float* z; void* s;
   int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
-  int n_keys, key_offset;
+  int n_keys, key_offset, head_dim;
   float scale_log2;
   int* status;
 };
@@ -74,15 +74,17 @@ __device__ __forceinline__ float max3f(float a, float b, float c) {
 }
 
 
-// 16 consecutive values of a summary row
+// 16 consecutive values of a summary row, of which the first n (a multiple of 8) exist
 template <typename TS>
-__device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16]) {
+__device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16], int n) {
   if constexpr (sizeof(TS) == 4) {
 #pragma unroll
-    for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    for (int i = 0; i < 16; i += 4)
+      if (i < n) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
   } else {
 #pragma unroll
     for (int i = 0; i < 16; i += 8) {
+      if (i >= n) continue;
       uint4 t;
       t.x = pack2<TS>(v[i], v[i + 1]); t.y = pack2<TS>(v[i + 2], v[i + 3]);
       t.z = pack2<TS>(v[i + 4], v[i + 5]); t.w = pack2<TS>(v[i + 6], v[i + 7]);
@@ -91,15 +93,17 @@ __device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16]) {
   }
 }
 
-// x (4 consecutive fp32 of a row, any strides) -> three bf16 planes [3][B*H][rows][64], contiguous
+// x (4 consecutive fp32 of a row of `cols` values, any strides) -> three bf16 planes [3][B*H][rows][64], contiguous;
+// columns beyond `cols` are written as zeros (a head dim below 64 becomes a zero-padded 64-column operand)
 __global__ void __launch_bounds__(256)
-split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ planes, int heads, int rows, Strides st,
+split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ planes, int heads, int rows, int cols, Strides st,
               int64_t plane_elems) {
   const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
   const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
   if (r >= rows) return;
   const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
-  const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c);
+  const float4 v = c < cols ? *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
   const float in[4] = {v.x, v.y, v.z, v.w};
   __nv_bfloat16 o[3][4];
 #pragma unroll
@@ -381,9 +385,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         prm.m[ro] = m_out;
         prm.z[ro] = z_out;
       }
-      if (prm.summary_dtype == ELSA_F32) store_row16<float>(static_cast<float*>(prm.s) + ro * 64 + 16 * cq, o_run);
-      else if (prm.summary_dtype == ELSA_F16) store_row16<__half>(static_cast<__half*>(prm.s) + ro * 64 + 16 * cq, o_run);
-      else store_row16<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * 64 + 16 * cq, o_run);
+      if (prm.summary_dtype == ELSA_F32) store_row16<float>(static_cast<float*>(prm.s) + ro * prm.head_dim + 16 * cq, o_run, prm.head_dim - 16 * cq);
+      else if (prm.summary_dtype == ELSA_F16) store_row16<__half>(static_cast<__half*>(prm.s) + ro * prm.head_dim + 16 * cq, o_run, prm.head_dim - 16 * cq);
+      else store_row16<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * prm.head_dim + 16 * cq, o_run, prm.head_dim - 16 * cq);
     }
   }
 
@@ -395,18 +399,19 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 }  // namespace
 
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias) {
-  return dtype == ELSA_F32 && head_dim == 64 && !has_bias && fold_tc_supported(ELSA_BF16, 64, false);
+  return dtype == ELSA_F32 && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && !has_bias &&
+         fold_tc_supported(ELSA_BF16, 64, false);
 }
 
 int64_t fold_tc3_plane_bytes(int bh, int rows) { return align_up(static_cast<int64_t>(3) * bh * rows * 64 * 2, 256); }
 
 // planes: [3][bh][rows][64] bf16 of the fp32 tensor x ([B, H, rows, 64] view with strides st)
-int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, cudaStream_t stream) {
+int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0) return ELSA_OK;
   if ((st.b | st.h | st.r) % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
   const int bh = batch * heads;
   const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(rows) * 16, 256)), static_cast<unsigned>(bh));
-  split3_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(planes), heads, rows, st,
+  split3_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(planes), heads, rows, cols, st,
                                           static_cast<int64_t>(bh) * rows * 64);
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
@@ -415,7 +420,8 @@ int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads
 // p.q3 / p.k3 / p.v3: the plane buffers written by fold_tc3_split for the whole problem (all query rows / this
 // launch's key rows)
 int fold_tc3(const FoldParams& p, cudaStream_t st) {
-  if (!p.q3 || !p.k3 || !p.v3 || p.head_dim != 64 || p.bias || p.part_width % 128 != 0) return ELSA_ERR_UNSUPPORTED;
+  if (!p.q3 || !p.k3 || !p.v3 || !fold_tc3_supported(ELSA_F32, p.head_dim, p.bias != nullptr) || p.part_width % 128 != 0)
+    return ELSA_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
   int rc;
   // planes as a [3, B*H, rows, 64] bf16 tensor: the "head" coordinate is (batch*head), the "batch" coordinate the plane
@@ -428,7 +434,7 @@ int fold_tc3(const FoldParams& p, cudaStream_t st) {
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
-  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset;
+  prm.n_keys = p.n_keys; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale_log2 = p.scale_log2;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tc3_kernel), kFold3Smem);
   if (rc != ELSA_OK) return rc;

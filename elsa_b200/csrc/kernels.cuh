@@ -76,7 +76,7 @@ int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
 // tcgen05 fold for fp32 inputs split into three bf16 planes (fold_tc3.cu)
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t fold_tc3_plane_bytes(int bh, int rows);
-int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, cudaStream_t stream);
+int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream);
 int fold_tc3(const FoldParams& p, cudaStream_t st);
 // tcgen05 backward (bwd_tc.cu); workspace = padded D / LSE vectors + fp32 dQ accumulator
 bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);

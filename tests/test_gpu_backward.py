@@ -64,6 +64,12 @@ CASES = [
     (2, 3, 60, 32, F32, False, "nn"),
     (2, 3, 60, 32, F16, True, "hnn"),
     (1, 2, 1025, 64, F16, False, None),
+    # head dims below 64 on the tensor cores (N >= 512, no bias)
+    (1, 2, 640, 32, F16, False, None),
+    (1, 2, 777, 32, BF16, True, None),
+    (1, 2, 600, 48, F16, True, None),
+    (1, 2, 640, 32, F32, False, None),
+    (1, 2, 900, 40, F32, True, None),
 ]
 
 

@@ -127,6 +127,13 @@ CASES = [
     (1, 8, 1024, 64, F32, False, None, None, None),       # the reference's CPU-runnable fp32 case
     (1, 2, 2048, 64, F16, False, None, 2048, None),
     (1, 2, 2048, 64, F16, False, None, 256, 1024),
+    # head dims below 64 on the tensor cores (N >= 512, no bias): the 64-column TMA box pads the tiles with zeros
+    (1, 2, 640, 32, F16, False, None, None, None),
+    (1, 2, 777, 32, BF16, True, None, None, None),
+    (2, 2, 600, 48, F16, True, None, None, None),
+    (1, 2, 1030, 8, BF16, False, None, None, None),
+    (1, 2, 640, 32, F32, False, None, None, None),
+    (1, 3, 900, 40, F32, True, None, None, None),
 ]
 
 
@@ -302,3 +309,19 @@ def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, bl
     assert U.max_abs(tc[1], fma[1]) <= 2e-5
     assert ((tc[2] - fma[2]).abs() / fma[2]).max().item() <= 1e-5
     assert lib.elsa_device_status(0) == 0
+
+
+def test_routing_of_small_head_dims_and_fp32():
+    """Head dims below 64 (multiples of 8) and fp32 inputs take the tcgen05 kernels from 512 tokens on, forward and
+    backward; biased problems, head dims above 64 and short sequences stay on the FP32-FMA kernels."""
+    from elsa_b200 import _lib
+    lib = _lib.load()
+    f32, f16, bf16 = (_lib.dtype_code(t) for t in (F32, F16, BF16))
+    for backward in (0, 1):
+        for dt in (f32, f16, bf16):
+            for d in (8, 32, 48, 64):
+                assert lib.elsa_uses_tensor_cores(dt, d, 640, 0, 0, backward) == 1, (dt, d, backward)
+            assert lib.elsa_uses_tensor_cores(dt, 64, 640, 1, 0, backward) == 0      # bias
+            assert lib.elsa_uses_tensor_cores(dt, 96, 640, 0, 0, backward) == 0      # head dim above 64
+            assert lib.elsa_uses_tensor_cores(dt, 36, 640, 0, 0, backward) == 0      # not a multiple of 8
+            assert lib.elsa_uses_tensor_cores(dt, 64, 200, 0, 0, backward) == 0      # short sequence
