@@ -48,9 +48,10 @@ enum elsa_status {
 #define ELSA_FLAG_FORCE_SIMT 1u   /* never take the tcgen05 kernels (debug / A-B checks) */
 #define ELSA_FLAG_SCAN_STEPS 2u   /* causal: run the log-depth Hillis-Steele steps instead of the one-pass merge */
 #define ELSA_FLAG_TREE_MERGE 4u   /* non-causal: run the Blelloch up-sweep levels instead of the one-pass merge */
-#define ELSA_FLAG_FP32_FMA 16u     /* forward, fp32 inputs: stay on the FP32-FMA kernel instead of the tensor-core kernel that
-                                     works on three bf16 planes per operand (same accuracy class; the planes cost
-                                     1.5 x the size of q, k, v in workspace) */
+#define ELSA_FLAG_FP32_FMA 16u     /* forward and backward, fp32 inputs: stay on the FP32-FMA kernels instead of the
+                                     tensor-core kernels that work on three bf16 planes per operand (same accuracy class;
+                                     the planes cost 1.5 x the size of q, k, v in forward workspace and 1.5 x the size of
+                                     q, dout, k, v in backward workspace) */
 #define ELSA_FLAG_REF_ROUNDING 8u /* forward, fp16 / head dim 64 / no bias / not causal only: reproduce the rounding points of
                                      the reference's fp16 d=64 kernels (q * log2(e)/8 formed in fp16, scores unscaled:
                                      attention_parallel_scan.py:153-154,160) instead of the exact fp32 scale; the workspace
@@ -79,7 +80,8 @@ int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream);
 int elsa_debug_fma_rate(float* sink, int blocks, int64_t iters, int packed, void* stream);
 /* number of kernels this library has launched in this process so far (all threads, all streams) */
 int64_t elsa_kernel_launches(void);
-/* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run */
+/* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run.  Covered: fp16, bf16
+ * and fp32 inputs, head dim a multiple of 8 up to 64, at least 512 tokens, no bias (and, backward, no dbias). */
 int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward);
 
 /* ---------------------------------------------------------------------------------------
@@ -279,8 +281,8 @@ int elsa_row_stats(const void* q, const void* k,
  * dbias is fp32, addressed with the dbias_stride_* like bias; where a stride is 0 the
  * contributions of that axis are summed (atomically).  The caller ALWAYS zeroes dbias before the call: besides
  * the sums, entries of pairs that the causal rule or the sequence length excludes are never written.
- * workspace: elsa_backward_workspace_bytes (row_d, row_lse, and the fp32 dQ accumulator of the
- * tensor-core path). */
+ * workspace: elsa_backward_workspace_bytes (row_d, row_lse; on the tensor-core path also the fp32 dQ accumulator
+ * for 16-bit inputs, or the bf16 planes of q, dout, k, v for fp32 inputs). */
 int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                       int has_bias, int is_causal, unsigned flags);
 int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
