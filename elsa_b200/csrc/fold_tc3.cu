@@ -50,12 +50,17 @@ namespace {
 
 constexpr int kSlots = 8;
 constexpr int kPlaneBytes = 128 * 64 * 2;                      // one 128 x 64 bf16 plane tile
-constexpr int kFold3Smem = (3 + kSlots) * kPlaneBytes + 1024;  // + alignment slack
+constexpr int kFold3Smem = (kPlanes + kSlots) * kPlaneBytes + 1024;  // + alignment slack
 constexpr int kFoldWarps = 16, kFoldThreads = kFoldWarps * 32;
 constexpr int kThreads = kFoldThreads + 64;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarp = 16, kIssuerWarp = 17;
-constexpr float kRescaleThreshold = 8.0f;
+// lazy exp-rescale: with bf16 planes a weight may grow to 2^8 before the reference max moves; fp16 planes hold weights
+// times 2^14, so there the reference max follows every tile (weights <= 1)
+constexpr float kRescaleThreshold = kPlanes == 3 ? 8.0f : 0.0f;
+constexpr float kLog2Unit = kPlanes == 3 ? 0.0f : 14.0f;      // log2(kPlaneUnit)
+constexpr int kPlaneHeader = 256;                              // bytes in front of a tensor's planes: its |x| max (bit pattern)
+constexpr uint32_t kPlaneFmt = kPlanes == 3 ? 1u : 0u;         // tcgen05 operand format: bf16 / fp16
 
 enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, BAR_O = 36, BAR_SFREE = 37, BAR_PV = 38, BAR_ROW = 39 };
 
@@ -64,6 +69,7 @@ struct Fold3Params {
   int n_ctx, q_start, q_len, part_width, n_parts, bh, is_causal, summary_dtype;
   int n_keys, key_offset, head_dim;
   float scale_log2;
+  const uint32_t* amax_q; const uint32_t* amax_k; const uint32_t* amax_v;   // the plane headers
   int* status;
 };
 
@@ -93,30 +99,41 @@ __device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16], int n
   }
 }
 
-// x (4 consecutive fp32 of a row of `cols` values, any strides) -> three bf16 planes [3][B*H][rows][64], contiguous;
-// columns beyond `cols` are written as zeros (a head dim below 64 becomes a zero-padded 64-column operand)
+// largest |x| of a [B, H, rows, cols] fp32 view, as a bit pattern (non-negative floats order like integers)
 __global__ void __launch_bounds__(256)
-split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ planes, int heads, int rows, int cols, Strides st,
-              int64_t plane_elems) {
+absmax_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int heads, int rows, int cols, Strides st) {
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
+  const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
+  float m = 0.f;
+  if (r < rows && c < cols) {
+    const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
+    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c);
+    m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f && m <= 3.0e38f) atomicMax(out, __float_as_uint(m));
+}
+
+// x (4 consecutive fp32 of a row of `cols` values, any strides) times the tensor's plane scale -> kPlanes 16-bit
+// planes [kPlanes][B*H][rows][64], contiguous; columns beyond `cols` are written as zeros (a head dim below 64 becomes
+// a zero-padded 64-column operand)
+__global__ void __launch_bounds__(256)
+split_planes_kernel(const float* __restrict__ x, const uint32_t* __restrict__ amax, uint16_t* __restrict__ planes,
+                    int heads, int rows, int cols, Strides st, int64_t plane_elems) {
   const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
   const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
   if (r >= rows) return;
   const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
+  const float sc = plane_scale(*amax);
   const float4 v = c < cols ? *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c)
                             : make_float4(0.f, 0.f, 0.f, 0.f);
-  const float in[4] = {v.x, v.y, v.z, v.w};
-  __nv_bfloat16 o[3][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat16 b0 = __float2bfloat16_rn(in[i]);
-    const float r1 = in[i] - __bfloat162float(b0);
-    const __nv_bfloat16 b1 = __float2bfloat16_rn(r1);
-    const float r2 = r1 - __bfloat162float(b1);
-    o[0][i] = b0; o[1][i] = b1; o[2][i] = __float2bfloat16_rn(r2);
-  }
+  uint32_t w0[kPlanes], w1[kPlanes];
+  split_planes_pair(v.x * sc, v.y * sc, w0);
+  split_planes_pair(v.z * sc, v.w * sc, w1);
   const int64_t off = (static_cast<int64_t>(bh) * rows + r) * 64 + c;
 #pragma unroll
-  for (int p = 0; p < 3; ++p) *reinterpret_cast<uint2*>(planes + p * plane_elems + off) = *reinterpret_cast<const uint2*>(o[p]);
+  for (int p = 0; p < kPlanes; ++p) *reinterpret_cast<uint2*>(planes + p * plane_elems + off) = make_uint2(w0[p], w1[p]);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -142,7 +159,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   auto sQ = [&](int p) { return smem_base + p * kPlaneBytes; };
-  auto sSlot = [&](int i) { return smem_base + (3 + i) * kPlaneBytes; };
+  auto sSlot = [&](int i) { return smem_base + (kPlanes + i) * kPlaneBytes; };
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_q = bar0;
   auto bar_full = [&](int i) { return bar0 + 8 * (1 + i); };
@@ -172,14 +189,14 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tS = tmem_base;
   const uint32_t tO = tmem_base + 128;
-  const uint32_t tP[3] = {tmem_base + 192, tmem_base + 256, tmem_base + 320};
+  const uint32_t tP0 = tmem_base + 192;                  // P plane p at tP0 + 64 p
 
   if (warp == kProducerWarp) {
     if (n_t > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_q, 3 * kPlaneBytes);
-      for (int p = 0; p < 3; ++p) tma_load_4d(sQ(p), &tmap_q, bar_q, 0, q0, bh, p);
+      mbar_arrive_expect_tx(bar_q, kPlanes * kPlaneBytes);
+      for (int p = 0; p < kPlanes; ++p) tma_load_4d(sQ(p), &tmap_q, bar_q, 0, q0, bh, p);
       int seq = 0;
       bool ok = true;
       auto load = [&](const CUtensorMap* map, int tile, int plane) {
@@ -189,19 +206,20 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tma_load_4d(sSlot(slot), map, bar_full(slot), 0, k_begin + tile * 128, bh, plane);
         ++seq;
       };
-      for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, 0, p);       // planes in the order of increasing weight
+      for (int p = kPlanes - 1; p >= 0 && ok; --p) load(&tmap_k, 0, p);       // planes in the order of increasing weight
       for (int j = 0; j < n_t && ok; ++j) {
         if (j + 1 < n_t)
-          for (int p = 2; p >= 0 && ok; --p) load(&tmap_k, j + 1, p);
-        for (int p = 2; p >= 0 && ok; --p) load(&tmap_v, j, p);
+          for (int p = kPlanes - 1; p >= 0 && ok; --p) load(&tmap_k, j + 1, p);
+        for (int p = kPlanes - 1; p >= 0 && ok; --p) load(&tmap_v, j, p);
       }
     }
   } else if (warp == kIssuerWarp) {
     if (n_t > 0 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_s = make_idesc(1u, 0, 0, 128, 128);   // S += Qp Kp^T : bf16, A, B K-major
-      constexpr uint32_t idesc_o = make_idesc(1u, 0, 1, 128, 64);    // O += Pp Vp   : A in TMEM, B (V) MN-major
-      const uint64_t dq[3] = {make_sdesc(sQ(0), 16, 1024), make_sdesc(sQ(1), 16, 1024), make_sdesc(sQ(2), 16, 1024)};
+      constexpr uint32_t idesc_s = make_idesc(kPlaneFmt, 0, 0, 128, 128);   // S += Qp Kp^T : bf16, A, B K-major
+      constexpr uint32_t idesc_o = make_idesc(kPlaneFmt, 0, 1, 128, 64);    // O += Pp Vp   : A in TMEM, B (V) MN-major
+      uint64_t dq[kPlanes];
+      for (int p = 0; p < kPlanes; ++p) dq[p] = make_sdesc(sQ(p), 16, 1024);
       const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dv_slot0 = make_sdesc(sSlot(0), 128 * 128, 1024);
       constexpr uint64_t kSlotStep = kPlaneBytes >> 4;   // descriptor address field counts 16-byte units
       int seq = 0;
@@ -210,12 +228,12 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the q planes go from the lightest admissible one down to q0: the leading term q0 k0 is the last to be added
       auto issue_s = [&]() {
         bool first = true;
-        for (int kp = 2; kp >= 0 && ok; --kp) {
+        for (int kp = kPlanes - 1; kp >= 0 && ok; --kp) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           const uint64_t dk = dk_slot0 + slot * kSlotStep;
-          for (int qp = 2 - kp; qp >= 0; --qp) {
+          for (int qp = kPlanes - 1 - kp; qp >= 0; --qp) {
             mma_ss_x4<2, 2>(tS, dq[qp], dk, idesc_s, first ? 0u : 1u);
             first = false;
           }
@@ -237,14 +255,14 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_after();
         // O_j starts from zero (the fold warps took O_{j-1} into their registers before they delivered P(j))
         bool first = true;
-        for (int vp = 2; vp >= 0 && ok; --vp) {
+        for (int vp = kPlanes - 1; vp >= 0 && ok; --vp) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) break;
           tc_fence_after();
           const uint64_t dv = dv_slot0 + slot * kSlotStep;
-          for (int pp = 2 - vp; pp >= 0; --pp) {
-            mma_ts_x4<8, 128>(tO, tP[pp], dv, idesc_o, first ? 0u : 1u);
-            mma_ts_x4<8, 128>(tO, tP[pp] + 32, dv + 512, idesc_o, 1u);
+          for (int pp = kPlanes - 1 - vp; pp >= 0; --pp) {
+            mma_ts_x4<8, 128>(tO, tP0 + 64 * pp, dv, idesc_o, first ? 0u : 1u);
+            mma_ts_x4<8, 128>(tO, tP0 + 64 * pp + 32, dv + 512, idesc_o, 1u);
             first = false;
           }
           mma_commit(bar_free(slot));

@@ -273,18 +273,50 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-// x = a0 + a1 + a2 with three bf16 terms (round to nearest each time, remainders exact), for a pair of values;
-// the packed pairs hold element 0 in the low half
-__device__ __forceinline__ void split3_pair(float x0, float x1, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
-  const __nv_bfloat162 a0 = __floats2bfloat162_rn(x0, x1);
-  const float2 f0 = __bfloat1622float2(a0);
-  const float r0 = x0 - f0.x, r1 = x1 - f0.y;
-  const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
-  const float2 f1 = __bfloat1622float2(a1);
-  const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
-  w0 = *reinterpret_cast<const uint32_t*>(&a0);
-  w1 = *reinterpret_cast<const uint32_t*>(&a1);
-  w2 = *reinterpret_cast<const uint32_t*>(&a2);
+// ---- fp32 operands as a few 16-bit planes -----------------------------------------------------------------------
+// ELSA_FP32_PLANES == 3: x = a0 + a1 + a2 with three bf16 terms (8 + 8 + 8 significant bits, the full exponent range;
+//   six cross products of weight >= 2^-16 per contraction).
+// ELSA_FP32_PLANES == 2: x * 2^e = h0 + h1 with two fp16 terms (11 + 11 significant bits; three cross products
+//   h0 h0 + h0 h1 + h1 h0 per contraction, the accuracy class of 3xTF32).  fp16 has five exponent bits, so every tensor
+//   is multiplied by a power of two that puts its largest magnitude in [2^13, 2^14): elements down to 2^-16 of the
+//   largest keep all 22 bits, smaller ones lose low bits gradually (absolute error below 2^-38 of the largest).
+#ifndef ELSA_FP32_PLANES
+#define ELSA_FP32_PLANES 2
+#endif
+constexpr int kPlanes = ELSA_FP32_PLANES;
+static_assert(kPlanes == 2 || kPlanes == 3, "fp32 operands are split into two fp16 or three bf16 planes");
+constexpr float kPlaneUnit = kPlanes == 2 ? 16384.f : 1.f;   // what a probability (<= 1) is multiplied by before its split
+
+// the power of two that scales a tensor whose largest magnitude has the bit pattern `absmax_bits` (0 for an all-zero
+// tensor) into [2^13, 2^14); 1 for bf16 planes
+__device__ __forceinline__ float plane_scale(uint32_t absmax_bits) {
+  if (kPlanes == 3) return 1.f;
+  int e = static_cast<int>(absmax_bits >> 23) - 127;         // floor(log2(absmax)) for a normal number
+  if (absmax_bits == 0u) e = 13;
+  e = max(-100, min(100, e));
+  return __uint_as_float(static_cast<uint32_t>(127 + 13 - e) << 23);
+}
+
+// a pair of values -> its kPlanes packed 16-bit pairs (element 0 in the low half), leading plane first: round to
+// nearest each time, remainders exact
+__device__ __forceinline__ void split_planes_pair(float x0, float x1, uint32_t (&w)[kPlanes]) {
+  if constexpr (kPlanes == 3) {
+    const __nv_bfloat162 a0 = __floats2bfloat162_rn(x0, x1);
+    const float2 f0 = __bfloat1622float2(a0);
+    const float r0 = x0 - f0.x, r1 = x1 - f0.y;
+    const __nv_bfloat162 a1 = __floats2bfloat162_rn(r0, r1);
+    const float2 f1 = __bfloat1622float2(a1);
+    const __nv_bfloat162 a2 = __floats2bfloat162_rn(r0 - f1.x, r1 - f1.y);
+    w[0] = *reinterpret_cast<const uint32_t*>(&a0);
+    w[1] = *reinterpret_cast<const uint32_t*>(&a1);
+    w[kPlanes - 1] = *reinterpret_cast<const uint32_t*>(&a2);
+  } else {
+    const __half2 a0 = __floats2half2_rn(x0, x1);
+    const float2 f0 = __half22float2(a0);
+    const __half2 a1 = __floats2half2_rn(x0 - f0.x, x1 - f0.y);
+    w[0] = *reinterpret_cast<const uint32_t*>(&a0);
+    w[1] = *reinterpret_cast<const uint32_t*>(&a1);
+  }
 }
 
 // two fp32 -> one packed pair of T (element 0 in the low half)
