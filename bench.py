@@ -59,8 +59,9 @@ def flops(b, h, n, d, causal):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (the tcgen05 backward), from one
 # ncu capture of this file's own command line at that workload
-FP32_TC_PEAK_NOTE = ("measured bf16 dense (sustained) / 6: an fp32 product on the tensor cores is six bf16 products "
-                     "(three bf16 planes per operand); the backward also runs seven contractions per tile pair for the "
+FP32_TC_MMAS = 3.0   # 16-bit products per fp32 product: x = h0 + h1 in fp16, a*b = h0 h0 + h0 h1 + h1 h0
+FP32_TC_PEAK_NOTE = ("measured bf16 dense (sustained) / 3: an fp32 product on the tensor cores is three fp16 products "
+                     "(two fp16 planes per operand); the backward also runs seven contractions per tile pair for the "
                      "five counted, so its ceiling in these units is 5/7 of this figure")
 NCU_TRAFFIC_BYTES = {"headline": 101780992 + 19949824}
 
@@ -708,7 +709,7 @@ def main():
                     tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(w2.dtype), w2.d, w2.n, int(w2.use_bias), int(w2.causal), 1))
                     tf = (w2.fwd_f + w2.bwd_f) / (ms2 * 1e-3) / 1e12
                     split3 = tc and w2.dtype == torch.float32
-                    peak = (pk["tflops_sustained"] / (6.0 if split3 else 1.0)) if tc else fma
+                    peak = (pk["tflops_sustained"] / (FP32_TC_MMAS if split3 else 1.0)) if tc else fma
                     others[name] = {"shape": [w2.b, w2.h, w2.n, w2.d], "dtype": w2.dt_name, "causal": w2.causal, "bias": w2.use_bias,
                                     "ms_per_step": ms2, "value": tf, "unit": "TFLOP/s", "steps": k2,
                                     "bound": "tensor" if tc else "fp32-fma",
@@ -718,7 +719,7 @@ def main():
                 except Exception as exc:  # noqa: BLE001
                     others[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
             if seq and "value" in seq:
-                p64 = pk["tflops_sustained"] / 6.0
+                p64 = pk["tflops_sustained"] / FP32_TC_MMAS
                 others["fp32_64k"] = {"shape": list(WORKLOADS["fp32_64k"][:4]), "dtype": "float32", "ms_per_step": seq["ms_per_step"],
                                       "value": seq["value"], "unit": "TFLOP/s", "bound": "tensor", "peak": p64, "frac": seq["value"] / p64,
                                       "peak_source": FP32_TC_PEAK_NOTE}
@@ -733,7 +734,7 @@ def main():
         achieved = bwd_f / (bwd_sus * 1e-3) / 1e12
         split3 = uses_tc and dtype == torch.float32
         if split3:
-            peak, peak_src, bound = (pk["tflops_sustained"] or pk["tflops"]) / 6.0, FP32_TC_PEAK_NOTE, "tensor"
+            peak, peak_src, bound = (pk["tflops_sustained"] or pk["tflops"]) / FP32_TC_MMAS, FP32_TC_PEAK_NOTE, "tensor"
         elif uses_tc:
             peak, peak_src = pk["tflops_sustained"] or pk["tflops"], pk["source"] + " bf16 dense, sustained (seconds-long loop under the power cap: the timed region is one too)"
             bound = "tensor"
@@ -743,8 +744,8 @@ def main():
         roofline = {"kernel": "backward (dQ, dK, dV recompute)" + ((" tcgen05, fp32 as three bf16 planes" if split3 else " tcgen05") if uses_tc else " fp32-fma"),
                     "bound": bound, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": (achieved / peak) if peak else None, "peak_source": peak_src,
-                    "peak_burst": (pk["tflops"] / (6.0 if split3 else 1.0)) if uses_tc else None,
-                    "frac_of_burst": (achieved / (pk["tflops"] / (6.0 if split3 else 1.0))) if uses_tc else None,
+                    "peak_burst": (pk["tflops"] / (FP32_TC_MMAS if split3 else 1.0)) if uses_tc else None,
+                    "frac_of_burst": (achieved / (pk["tflops"] / (FP32_TC_MMAS if split3 else 1.0))) if uses_tc else None,
                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "traffic_unit": "bytes per launch (ncu dram read+write)",
                     "ms_per_launch": bwd_sus,
                     "forward": {"achieved": fwd_f / (fwd_sus * 1e-3) / 1e12, "ms": fwd_sus,

@@ -66,7 +66,7 @@ static int check_device_status() {
 struct ForwardPlan {
   int part_width, n_parts, q_chunk, tile_m, tile_n;
   bool tensor_cores;
-  bool split3;                // fp32 inputs on the tensor cores as three bf16 planes (fold_tc3.cu)
+  bool split3;                // fp32 inputs on the tensor cores as 16-bit planes (fold_tc3.cu)
   int64_t mz_bytes, s_bytes;  // one summary set: m (== z) and s, 256-byte aligned
   int sets;                   // 1, or 2 when a ping-pong pass (scan steps / tree) was requested
 };
@@ -270,7 +270,7 @@ extern "C" int elsa_phase1_fold_shard(const void* q, const void* k, const void* 
                          n_keys, key_offset);
 }
 
-// The shard fold with a workspace: fp32 inputs then run on the tensor cores (three bf16 planes per operand, written
+// The shard fold with a workspace: fp32 inputs then run on the tensor cores (16-bit planes per operand, written
 // into the workspace); every other case is the plain shard fold and needs no workspace.
 extern "C" int64_t elsa_phase1_fold_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                                           int n_keys, unsigned flags) {
@@ -379,7 +379,7 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
 
   const void *q3 = nullptr, *k3 = nullptr, *v3 = nullptr;
   if (pl.split3) {
-    // fp32 on the tensor cores: the three bf16 planes of q, k, v, written once behind the summaries
+    // fp32 on the tensor cores: the 16-bit planes of q, k, v, written once behind the summaries
     char* planes = ws + plan_bytes(pl);
     const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
     if ((rc = fold_tc3_split(q, qs ? *qs : cs, planes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
@@ -465,7 +465,7 @@ static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, un
   return n_ctx >= 512 && bwd_tc_supported(dtype, head_dim, has_bias);
 }
 
-// fp32 on the tensor cores (three bf16 planes per operand): head dim 64, no bias, no dbias
+// fp32 on the tensor cores (16-bit planes per operand): head dim up to 64, no bias, no dbias
 static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
   if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
   return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
@@ -704,7 +704,7 @@ extern "C" int elsa_twopass_forward_static(const void* q, const void* k, const v
   // query chunk is the largest multiple of the kernel's query tile whose summaries fit the built-in array, so a
   // long problem runs as several chunks through the same array instead of being refused
   ForwardPlan pl;
-  const unsigned sflags = ELSA_FLAG_FP32_FMA;   // the bf16 planes of an fp32 problem would not fit the built-in array
+  const unsigned sflags = ELSA_FLAG_FP32_FMA;   // the planes of an fp32 problem would not fit the built-in array
   int rc0 = plan_forward(dtype, dtype, batch, heads, n_ctx, head_dim, is_causal, false, 0, 0, sflags, &pl);
   if (rc0 != ELSA_OK) return rc0;
   int q_chunk = 0;   // 0: the automatic chunk already fits

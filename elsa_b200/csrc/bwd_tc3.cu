@@ -1,7 +1,8 @@
-// Backward for fp32 inputs on the 5th-generation tensor cores at fp32 accuracy: exact recompute from the saved row
-// statistics, head dim 64 (or a smaller multiple of 8: the planes are zero-padded to 64 columns), causal or not, no bias.  Every operand of every contraction is split into three bf16 terms
-// (x = x0 + x1 + x2 exactly) and a product is formed as the six cross terms whose weight is at least 2^-16 of the
-// leading one, exactly as in the forward kernel for fp32 inputs (fold_tc3.cu).
+// Backward for fp32 inputs on the 5th-generation tensor cores at fp32-grade accuracy: exact recompute from the saved
+// row statistics, head dim 64 (or a smaller multiple of 8: the planes are zero-padded to 64 columns), causal or not, no
+// bias.  Every operand of every contraction is split into 16-bit planes (two fp16 planes and three cross products, or
+// three bf16 planes and six: ELSA_FP32_PLANES, tc_common.cuh) exactly as in the forward kernel for fp32 inputs
+// (fold_tc3.cu); Q, K, V, dO by the same pre-pass, P and dS inside the kernels.
 //
 // tcgen05.mma adds into its fp32 accumulator by truncation, so -- unlike the 16-bit backward -- no gradient is
 // accumulated over tiles in TMEM: every (query tile, key tile) pair gets fresh accumulators, and the running sums live
@@ -44,16 +45,17 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kSlotStep = kSlotBytes >> 4;   // shared-memory descriptors count 16-byte units
 
 // dQ kernel: Q and dO planes resident (96 KB), a ring of 6 K plane tiles and one of 2 V plane tiles (16 KB each)
-constexpr int kDqKSlots = 6, kDqVSlots = 2;
-constexpr int kDqSmem = (6 + kDqKSlots + kDqVSlots) * kPlaneBytes + 1024;
+constexpr int kDqKSlots = 2 * kPlanes, kDqVSlots = kPlanes == 2 ? 4 : 2;
+constexpr int kDqSmem = (2 * kPlanes + kDqKSlots + kDqVSlots) * kPlaneBytes + 1024;
 // dK/dV kernel: K and V planes resident (96 KB), 15 ring slots, 4 stages of (-LSE, -D) vectors of 64 queries
 constexpr int kKvSlots = 15, kVecStages = 4, kVecBytes = 2 * 64 * 4;
-constexpr int kKvSmem = 6 * kPlaneBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
+constexpr int kKvSmem = 2 * kPlanes * kPlaneBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
 
 enum BarId { BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
 
 struct Bwd3Params {
   const float* nlse_pad; const float* nd_pad;   // [BH][n_pad]: -LSE, -D; padding rows hold -inf / 0
+  const uint32_t* amax_q; const uint32_t* amax_do; const uint32_t* amax_k; const uint32_t* amax_v;   // the plane headers
   float* dq; float* dk; float* dv;
   Strides dqs, dks, dvs;
   int n_ctx, n_pad, bh, heads, is_causal;
@@ -75,14 +77,26 @@ __device__ __forceinline__ void store16(float* dst, const float (&v)[16], float 
     if (i < n) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i] * f, v[i + 1] * f, v[i + 2] * f, v[i + 3] * f);
 }
 
-// 16 values -> their three bf16 planes, 8 TMEM columns per plane starting at column `col` of plane base tp0 + 32 p
-__device__ __forceinline__ void split_store16(const float (&x)[16], uint32_t tp0, uint32_t col) {
-  uint32_t pk[3][8];
+// 16 values -> their planes, 8 TMEM columns per plane starting at column `col` of plane base tp0 + STRIDE p
+template <int STRIDE>
+__device__ __forceinline__ void split_store16(const float* x, uint32_t tp0, uint32_t col) {
+  uint32_t pk[kPlanes][8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) split3_pair(x[2 * i], x[2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
+  for (int i = 0; i < 8; ++i) {
+    uint32_t w[kPlanes];
+    split_planes_pair(x[2 * i], x[2 * i + 1], w);
 #pragma unroll
-  for (int p = 0; p < 3; ++p) tmem_st8(tp0 + 32 * p + col, pk[p]);
+    for (int p = 0; p < kPlanes; ++p) pk[p][i] = w[p];
+  }
+#pragma unroll
+  for (int p = 0; p < kPlanes; ++p) tmem_st8(tp0 + STRIDE * p + col, pk[p]);
 }
+
+// The scaled quantities of the fp16-plane scheme (all factors are powers of two; 1 with bf16 planes):
+//   P'  = P  * 2^kLog2Unit            dS' = dS * s_ds,  s_ds = s_do * s_v * 2^-21  (|dS| <= 128 max|dO| max|V|)
+// where s_x is the plane scale of tensor x.  What the accumulators then hold, and what takes it out at the store:
+//   dP'  = s_do s_v dP      dQ_j' = s_ds s_k dQ_j      dV_i' = 2^kLog2Unit s_do dV_i      dK_i' = s_ds s_q dK_i
+__device__ __forceinline__ float ds_scale(float s_do, float s_v) { return kPlanes == 2 ? s_do * s_v * 4.76837158203125e-7f : 1.f; }
 
 // ------------------------------------------------------------------------------------------------------------------
 // dQ: one CTA per 128-row query tile, 128-key tiles (N = 128 for S and dP: a tcgen05.mma with N = 64 costs 48-70
@@ -110,9 +124,9 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   auto sQ = [&](int p) { return smem_base + p * kPlaneBytes; };
-  auto sDO = [&](int p) { return smem_base + (3 + p) * kPlaneBytes; };
-  auto sKs = [&](int i) { return smem_base + (6 + i) * kPlaneBytes; };
-  auto sVs = [&](int i) { return smem_base + (6 + kDqKSlots + i) * kPlaneBytes; };
+  auto sDO = [&](int p) { return smem_base + (kPlanes + p) * kPlaneBytes; };
+  auto sKs = [&](int i) { return smem_base + (2 * kPlanes + i) * kPlaneBytes; };
+  auto sVs = [&](int i) { return smem_base + (2 * kPlanes + kDqKSlots + i) * kPlaneBytes; };
   const uint32_t bar0 = smem_u32(bars);
   auto bar_kfull = [&](int i) { return bar0 + 8 * i; };
   auto bar_kfree = [&](int i) { return bar0 + 8 * (kDqKSlots + i); };
@@ -148,58 +162,58 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     if (n_t > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_stage, 6 * kPlaneBytes);
-      for (int p = 0; p < 3; ++p) {
+      mbar_arrive_expect_tx(bar_stage, 2 * kPlanes * kPlaneBytes);
+      for (int p = 0; p < kPlanes; ++p) {
         tma_load_4d(sQ(p), &tmap_q, bar_stage, 0, q0, bh, p);
         tma_load_4d(sDO(p), &tmap_do, bar_stage, 0, q0, bh, p);
       }
       bool ok = true;
-      // per key tile: its K planes (ring sequence numbers 3 j .. 3 j + 2), then its V planes; planes in the order of
+      // per key tile: its K planes (ring sequence numbers kPlanes j ...), then its V planes; planes in the order of
       // increasing weight.  A V slot is released by the dP group that read it, a K slot by the dQ group.
       for (int j = 0; j < n_t && ok; ++j) {
-        for (int x = 0; x < 3 && ok; ++x) {
-          const int seq = 3 * j + x, slot = seq % kDqKSlots;
+        for (int x = 0; x < kPlanes && ok; ++x) {
+          const int seq = kPlanes * j + x, slot = seq % kDqKSlots;
           if (seq >= kDqKSlots && !(ok = mbar_wait(bar_kfree(slot), ((seq / kDqKSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_kfull(slot), kPlaneBytes);
-          tma_load_4d(sKs(slot), &tmap_k, bar_kfull(slot), 0, j * 128, bh, 2 - x);
+          tma_load_4d(sKs(slot), &tmap_k, bar_kfull(slot), 0, j * 128, bh, kPlanes - 1 - x);
         }
-        for (int x = 0; x < 3 && ok; ++x) {
-          const int seq = 3 * j + x, slot = seq % kDqVSlots;
+        for (int x = 0; x < kPlanes && ok; ++x) {
+          const int seq = kPlanes * j + x, slot = seq % kDqVSlots;
           if (seq >= kDqVSlots && !(ok = mbar_wait(bar_vfree(slot), ((seq / kDqVSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_vfull(slot), kPlaneBytes);
-          tma_load_4d(sVs(slot), &tmap_v, bar_vfull(slot), 0, j * 128, bh, 2 - x);
+          tma_load_4d(sVs(slot), &tmap_v, bar_vfull(slot), 0, j * 128, bh, kPlanes - 1 - x);
         }
       }
     }
   } else if (warp == kIssuerWarp) {
     if (n_t > 0 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 128);   // S, dP: A, B K-major, N = 128 keys
-      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dQ_j: A in TMEM, B (K) MN-major, N = 64 = d
-      const uint64_t dQp[3] = {make_sdesc(sQ(0), 16, 1024), make_sdesc(sQ(1), 16, 1024), make_sdesc(sQ(2), 16, 1024)};
-      const uint64_t dDOp[3] = {make_sdesc(sDO(0), 16, 1024), make_sdesc(sDO(1), 16, 1024), make_sdesc(sDO(2), 16, 1024)};
+      constexpr uint32_t idesc_k = make_idesc(kPlaneFmt, 0, 0, 128, 128);   // S, dP: A, B K-major, N = 128 keys
+      constexpr uint32_t idesc_mn = make_idesc(kPlaneFmt, 0, 1, 128, 64);   // dQ_j: A in TMEM, B (K) MN-major, N = 64 = d
+      uint64_t dQp[kPlanes], dDOp[kPlanes];
+      for (int p = 0; p < kPlanes; ++p) { dQp[p] = make_sdesc(sQ(p), 16, 1024); dDOp[p] = make_sdesc(sDO(p), 16, 1024); }
       const uint64_t dk_k0 = make_sdesc(sKs(0), 16, 1024), dk_mn0 = make_sdesc(sKs(0), 128 * 128, 1024);
       const uint64_t dv_k0 = make_sdesc(sVs(0), 16, 1024);
       constexpr uint64_t kPlaneStep = kPlaneBytes >> 4;
       bool ok = mbar_wait(bar_stage, 0, &abort_flag, prm.status, BAR_STAGE);
       auto issue_sdp = [&](int j) {
         bool first = true;
-        for (int vp = 2; vp >= 0 && ok; --vp) {            // dP = dO V^T
-          const int seq = 3 * j + 2 - vp, slot = seq % kDqVSlots;
+        for (int vp = kPlanes - 1; vp >= 0 && ok; --vp) {  // dP = dO V^T
+          const int seq = kPlanes * j + kPlanes - 1 - vp, slot = seq % kDqVSlots;
           if (!(ok = mbar_wait(bar_vfull(slot), (seq / kDqVSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
-          for (int gp = 2 - vp; gp >= 0; --gp) {
+          for (int gp = kPlanes - 1 - vp; gp >= 0; --gp) {
             mma_ss_x4<2, 2>(tdP, dDOp[gp], dv_k0 + slot * kPlaneStep, idesc_k, first ? 0u : 1u);
             first = false;
           }
           mma_commit(bar_vfree(slot));
         }
         first = true;
-        for (int kp = 2; kp >= 0 && ok; --kp) {            // S = Q K^T
-          const int seq = 3 * j + 2 - kp, slot = seq % kDqKSlots;
+        for (int kp = kPlanes - 1; kp >= 0 && ok; --kp) {  // S = Q K^T
+          const int seq = kPlanes * j + kPlanes - 1 - kp, slot = seq % kDqKSlots;
           if (!(ok = mbar_wait(bar_kfull(slot), (seq / kDqKSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
-          for (int qp = 2 - kp; qp >= 0; --qp) {
+          for (int qp = kPlanes - 1 - kp; qp >= 0; --qp) {
             mma_ss_x4<2, 2>(tS, dQp[qp], dk_k0 + slot * kPlaneStep, idesc_k, first ? 0u : 1u);
             first = false;
           }                                   // the K planes stay: dQ_j reads them again
@@ -220,9 +234,9 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!(ok = mbar_wait(bar_ds, j & 1, &abort_flag, prm.status, BAR_DS))) break;
         tc_fence_after();
         bool first = true;
-        for (int kp = 2; kp >= 0; --kp) {                  // dQ_j = dS K over the 128 keys (eight K-steps)
-          const int slot = (3 * j + 2 - kp) % kDqKSlots;
-          for (int sp = 2 - kp; sp >= 0; --sp) {
+        for (int kp = kPlanes - 1; kp >= 0; --kp) {        // dQ_j = dS K over the 128 keys (eight K-steps)
+          const int slot = (kPlanes * j + kPlanes - 1 - kp) % kDqKSlots;
+          for (int sp = kPlanes - 1 - kp; sp >= 0; --sp) {
             mma_ts_x4<8, 128>(tdQ, tDS + 64 * sp, dk_mn0 + slot * kPlaneStep, idesc_mn, first ? 0u : 1u);
             mma_ts_x4<8, 128>(tdQ, tDS + 64 * sp + 32, dk_mn0 + slot * kPlaneStep + 512, idesc_mn, 1u);
             first = false;
@@ -238,8 +252,14 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int row = qd * 32 + lane;
     const int qi = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    const float c = prm.scale_log2;
-    const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];   // q0 + 127 < n_pad
+    // plane scales (powers of two; see ds_scale): S arrives times s_q s_k, dP times s_do s_v, dS leaves times s_ds
+    const float s_q = plane_scale(*prm.amax_q), s_do = plane_scale(*prm.amax_do);
+    const float s_k = plane_scale(*prm.amax_k), s_v = plane_scale(*prm.amax_v);
+    const float s_ds = ds_scale(s_do, s_v);
+    const float c = prm.scale_log2 / (s_q * s_k);
+    const float idp = 1.f / (s_do * s_v);
+    // p * s_ds straight from the exponential: the scale rides in the exponent
+    const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi] + log2f(s_ds);   // q0 + 127 < n_pad
     const float nd = prm.nd_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];
     float dq_run[16];
 #pragma unroll
@@ -272,7 +292,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 32; ++i) {
           float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nlse));
           if (masked && kb + i > lim) p = 0.f;
-          ds[i] = p * (__uint_as_float(rp[i]) + nd);
+          ds[i] = p * fmaf(__uint_as_float(rp[i]), idp, nd);
         }
       }
       if (j > 0) {
@@ -281,15 +301,9 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
         take_dq();
       }
-      // the three bf16 planes of dS: 16 keys (8 TMEM columns per plane) at a time
+      // the planes of dS: 16 keys (8 TMEM columns per plane) at a time
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t pk[3][8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) split3_pair(ds[16 * ch + 2 * i], ds[16 * ch + 2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
-#pragma unroll
-        for (int p = 0; p < 3; ++p) tmem_st8(tDS + 64 * p + lane_off + 16 * cq + 8 * ch, pk[p]);
-      }
+      for (int ch = 0; ch < 2; ++ch) split_store16<64>(ds + 16 * ch, tDS + lane_off, 16 * cq + 8 * ch);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(bar_ds, lane);
@@ -303,7 +317,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
     if (qi < N && (alive || n_t == 0)) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale, prm.head_dim - 16 * cq);
+      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale / (s_ds * s_k), prm.head_dim - 16 * cq);
     }
   }
 
@@ -337,9 +351,9 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   auto sK = [&](int p) { return smem_base + p * kPlaneBytes; };
-  auto sV = [&](int p) { return smem_base + (3 + p) * kPlaneBytes; };
-  auto sSlot = [&](int i) { return smem_base + 6 * kPlaneBytes + i * kSlotBytes; };
-  const uint32_t vec_off = 6 * kPlaneBytes + kKvSlots * kSlotBytes;    // [stage][-LSE x 64 | -D x 64]
+  auto sV = [&](int p) { return smem_base + (kPlanes + p) * kPlaneBytes; };
+  auto sSlot = [&](int i) { return smem_base + 2 * kPlanes * kPlaneBytes + i * kSlotBytes; };
+  const uint32_t vec_off = 2 * kPlanes * kPlaneBytes + kKvSlots * kSlotBytes;    // [stage][-LSE x 64 | -D x 64]
   const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int i) { return bar0 + 8 * i; };
   auto bar_free = [&](int i) { return bar0 + 8 * (kKvSlots + i); };
@@ -373,22 +387,22 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (n_it > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_kv, 6 * kPlaneBytes);
-      for (int p = 0; p < 3; ++p) {
+      mbar_arrive_expect_tx(bar_kv, 2 * kPlanes * kPlaneBytes);
+      for (int p = 0; p < kPlanes; ++p) {
         tma_load_4d(sK(p), &tmap_k, bar_kv, 0, k0, bh, p);
         tma_load_4d(sV(p), &tmap_v, bar_kv, 0, k0, bh, p);
       }
       int seq = 0;
       bool ok = true;
-      // ring order of query tile i: dO planes 2, 1, 0 (sequence numbers 6 i .. 6 i + 2), then Q planes 2, 1, 0; the
-      // tile's first slot also receives its -LSE / -D vectors
+      // ring order of query tile i: its dO planes from the lightest to the leading one (sequence numbers
+      // 2 kPlanes i ...), then its Q planes; the tile's first slot also receives its -LSE / -D vectors
       for (int it = 0; it < n_it && ok; ++it) {
         const int qrow = (it_begin + it) * 64;
-        for (int x = 0; x < 6 && ok; ++x) {
+        for (int x = 0; x < 2 * kPlanes && ok; ++x) {
           const int slot = seq % kKvSlots;
           if (seq >= kKvSlots && !(ok = mbar_wait(bar_free(slot), ((seq / kKvSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_full(slot), kSlotBytes + (x == 0 ? kVecBytes : 0));
-          tma_load_4d(sSlot(slot), x < 3 ? &tmap_do : &tmap_q, bar_full(slot), 0, qrow, bh, 2 - (x % 3));
+          tma_load_4d(sSlot(slot), x < kPlanes ? &tmap_do : &tmap_q, bar_full(slot), 0, qrow, bh, kPlanes - 1 - (x % kPlanes));
           if (x == 0) {
             const uint32_t dst = smem_base + vec_off + (it % kVecStages) * kVecBytes;
             bulk_load_1d(dst, prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, 256, bar_full(slot));
@@ -401,29 +415,30 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   } else if (warp == kIssuerWarp) {
     if (n_it > 0 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_k = make_idesc(1u, 0, 0, 128, 64);    // S^T, dP^T: A, B K-major, N = 64 queries
-      constexpr uint32_t idesc_mn = make_idesc(1u, 0, 1, 128, 64);   // dV_i, dK_i: A in TMEM, B MN-major, N = 64 = d
-      const uint64_t dKp[3] = {make_sdesc(sK(0), 16, 1024), make_sdesc(sK(1), 16, 1024), make_sdesc(sK(2), 16, 1024)};
-      const uint64_t dVp[3] = {make_sdesc(sV(0), 16, 1024), make_sdesc(sV(1), 16, 1024), make_sdesc(sV(2), 16, 1024)};
+      constexpr uint32_t idesc_k = make_idesc(kPlaneFmt, 0, 0, 128, 64);    // S^T, dP^T: A, B K-major, N = 64 queries
+      constexpr uint32_t idesc_mn = make_idesc(kPlaneFmt, 0, 1, 128, 64);   // dV_i, dK_i: A in TMEM, B MN-major, N = 64 = d
+      uint64_t dKp[kPlanes], dVp[kPlanes];
+      for (int p = 0; p < kPlanes; ++p) { dKp[p] = make_sdesc(sK(p), 16, 1024); dVp[p] = make_sdesc(sV(p), 16, 1024); }
+      constexpr int kT = 2 * kPlanes;   // ring entries per query tile
       const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dmn_slot0 = make_sdesc(sSlot(0), 64 * 128, 1024);
       bool ok = mbar_wait(bar_kv, 0, &abort_flag, prm.status, BAR_STAGE);
       auto issue_sdp = [&](int it) {
         bool first = true;
-        for (int gp = 2; gp >= 0 && ok; --gp) {            // dP^T = V dO^T
-          const int seq = 6 * it + 2 - gp, slot = seq % kKvSlots;
+        for (int gp = kPlanes - 1; gp >= 0 && ok; --gp) {  // dP^T = V dO^T
+          const int seq = kT * it + kPlanes - 1 - gp, slot = seq % kKvSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
-          for (int vp = 2 - gp; vp >= 0; --vp) {
+          for (int vp = kPlanes - 1 - gp; vp >= 0; --vp) {
             mma_ss_x4<2, 2>(tdP, dVp[vp], dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
             first = false;
           }
         }
         first = true;
-        for (int qp = 2; qp >= 0 && ok; --qp) {            // S^T = K Q^T
-          const int seq = 6 * it + 5 - qp, slot = seq % kKvSlots;
+        for (int qp = kPlanes - 1; qp >= 0 && ok; --qp) {  // S^T = K Q^T
+          const int seq = kT * it + kT - 1 - qp, slot = seq % kKvSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
-          for (int kp = 2 - qp; kp >= 0; --kp) {
+          for (int kp = kPlanes - 1 - qp; kp >= 0; --kp) {
             mma_ss_x4<2, 2>(tS, dKp[kp], dk_slot0 + slot * kSlotStep, idesc_k, first ? 0u : 1u);
             first = false;
           }
@@ -444,18 +459,18 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!(ok = mbar_wait(bar_pl, it & 1, &abort_flag, prm.status, BAR_DS))) break;
         tc_fence_after();
         bool first = true;
-        for (int gp = 2; gp >= 0; --gp) {                  // dV_i = P^T dO
-          const int slot = (6 * it + 2 - gp) % kKvSlots;
-          for (int pp = 2 - gp; pp >= 0; --pp) {
+        for (int gp = kPlanes - 1; gp >= 0; --gp) {        // dV_i = P^T dO
+          const int slot = (kT * it + kPlanes - 1 - gp) % kKvSlots;
+          for (int pp = kPlanes - 1 - gp; pp >= 0; --pp) {
             mma_ts_x4<8, 128>(tdV, tP + 32 * pp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
             first = false;
           }
           mma_commit(bar_free(slot));
         }
         first = true;
-        for (int qp = 2; qp >= 0; --qp) {                  // dK_i = dS^T Q
-          const int slot = (6 * it + 5 - qp) % kKvSlots;
-          for (int sp = 2 - qp; sp >= 0; --sp) {
+        for (int qp = kPlanes - 1; qp >= 0; --qp) {        // dK_i = dS^T Q
+          const int slot = (kT * it + kT - 1 - qp) % kKvSlots;
+          for (int sp = kPlanes - 1 - qp; sp >= 0; --sp) {
             mma_ts_x4<8, 128>(tdK, tDS + 32 * sp, dmn_slot0 + slot * kSlotStep, idesc_mn, first ? 0u : 1u);
             first = false;
           }
@@ -473,7 +488,14 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int key_seq = kseq0 + row;           // its index in the sequence (what the causal rule compares)
     const bool key_ok = key < NK;
     const bool cta_tail = k0 + 128 > NK;       // some key rows of this CTA do not exist
-    const float c = prm.scale_log2;
+    // plane scales (powers of two; see ds_scale): S^T arrives times s_q s_k, dP^T times s_do s_v; P^T leaves times
+    // 2^kLog2Unit (the unit rides in the exponent), dS^T times s_ds
+    const float s_q = plane_scale(*prm.amax_q), s_do = plane_scale(*prm.amax_do);
+    const float s_k = plane_scale(*prm.amax_k), s_v = plane_scale(*prm.amax_v);
+    const float s_ds = ds_scale(s_do, s_v);
+    const float c = prm.scale_log2 / (s_q * s_k);
+    const float k2 = s_ds * exp2f(-kLog2Unit);          // dS' = P' * (dP + nd) * k2
+    const float idp = k2 / (s_do * s_v);
     float dv_run[16], dk_run[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) { dv_run[i] = 0.f; dk_run[i] = 0.f; }
@@ -494,7 +516,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the tile's row statistics were written by the bulk copies that complete on its first slot's barrier: observe
       // that barrier directly (it completed before the MMAs behind bar_sdp were issued, so this never spins)
       {
-        const int seq = 6 * it;
+        const int seq = 2 * kPlanes * it;
         if (!__all_sync(0xffffffffu, mbar_wait(bar_full(seq % kKvSlots), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) { alive = false; break; }
       }
       tc_fence_after();
@@ -517,10 +539,10 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = 4 * g + e;
-            float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nle[e]));
+            float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nle[e] + kLog2Unit));
             if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) pv = 0.f;
             p[i] = pv;
-            ds[i] = pv * (__uint_as_float(rp[i]) + nde[e]);
+            ds[i] = pv * fmaf(__uint_as_float(rp[i]), idp, nde[e] * k2);
           }
         }
       }
@@ -530,8 +552,8 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_after();
         take_acc();
       }
-      split_store16(p, tP + lane_off, 8 * cq);
-      split_store16(ds, tDS + lane_off, 8 * cq);
+      split_store16<32>(p, tP + lane_off, 8 * cq);
+      split_store16<32>(ds, tDS + lane_off, 8 * cq);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(bar_pl, lane);
@@ -545,8 +567,8 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
     if (key_ok && alive) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale, prm.head_dim - 16 * cq);
-      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, 1.f, prm.head_dim - 16 * cq);
+      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale / (s_ds * s_q), prm.head_dim - 16 * cq);
+      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, exp2f(-kLog2Unit) / s_do, prm.head_dim - 16 * cq);
     }
   }
 
@@ -626,24 +648,26 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   if ((rc = fold_tc3_split(p.k, p.ks, k3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
   if ((rc = fold_tc3_split(p.v, p.vs, v3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
 
-  // planes as [3, B*H, rows, 64] bf16 tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
+  // planes as [kPlanes, B*H, rows, 64] 16-bit tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
   const Strides sq = contiguous_strides(bh, N, 64), sk = contiguous_strides(bh, NK, 64);
   CUtensorMap mq128, mdo128, mq64, mdo64, mk128, mv128;
-  if ((rc = make_tmap_rows64(&mq128, q3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mdo128, do3, ELSA_BF16, N, bh, 3, sq, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mq64, q3, ELSA_BF16, N, bh, 3, sq, 64)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mdo64, do3, ELSA_BF16, N, bh, 3, sq, 64)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq128, q3 + kPlaneHeader, kPlaneDtype, N, bh, kPlanes, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo128, do3 + kPlaneHeader, kPlaneDtype, N, bh, kPlanes, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq64, q3 + kPlaneHeader, kPlaneDtype, N, bh, kPlanes, sq, 64)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo64, do3 + kPlaneHeader, kPlaneDtype, N, bh, kPlanes, sq, 64)) != ELSA_OK) return rc;
   Bwd3Params prm;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad;
+  prm.amax_q = reinterpret_cast<const uint32_t*>(q3); prm.amax_do = reinterpret_cast<const uint32_t*>(do3);
+  prm.amax_k = reinterpret_cast<const uint32_t*>(k3); prm.amax_v = reinterpret_cast<const uint32_t*>(v3);
   prm.dq = static_cast<float*>(p.dq); prm.dk = static_cast<float*>(p.dk); prm.dv = static_cast<float*>(p.dv);
   prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
   prm.n_keys = NK; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   if (NK > 0) {
-    if ((rc = make_tmap_rows64(&mk128, k3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
-    if ((rc = make_tmap_rows64(&mv128, v3, ELSA_BF16, NK, bh, 3, sk, 128)) != ELSA_OK) return rc;
+    if ((rc = make_tmap_rows64(&mk128, k3 + kPlaneHeader, kPlaneDtype, NK, bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
+    if ((rc = make_tmap_rows64(&mv128, v3 + kPlaneHeader, kPlaneDtype, NK, bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
   } else {
     mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
   }

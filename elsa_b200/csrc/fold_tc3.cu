@@ -1,42 +1,47 @@
-// Phase 1 for fp32 inputs on the 5th-generation tensor cores WITHOUT giving up fp32 accuracy: every operand is
-// split into three bf16 terms, x = x0 + x1 + x2 exactly (8 + 8 + 8 mantissa bits), and a product a*b is formed as
-// the six cross terms whose weight is at least 2^-16 of the leading one,
-//     a0 b0 + a0 b1 + a1 b0 + a1 b1 + a0 b2 + a2 b0        (dropped: a1 b2, a2 b1, a2 b2 <= 2^-24 relative),
-// each an exact bf16 x bf16 product accumulated in fp32 by tcgen05.mma (kind::f16, bf16 inputs).  The reference's own
-// route for fp32 is 3xTF32 (src/elsa_twopass_clean/attention.py:280-282, 21 significant bits per operand); this keeps
-// all 24.
+// Phase 1 for fp32 inputs on the 5th-generation tensor cores WITHOUT giving up fp32-grade accuracy: every operand is
+// split into a few 16-bit planes and a product a*b is formed from the cross terms of the planes, each an exact
+// 16-bit x 16-bit product accumulated in fp32 by tcgen05.mma (kind::f16).  Two forms, chosen at compile time
+// (ELSA_FP32_PLANES, tc_common.cuh):
+//   2 planes (default): x * 2^e = h0 + h1 in fp16 (11 + 11 significant bits; e puts the tensor's largest magnitude in
+//     [2^13, 2^14)), a*b = h0 h0 + h0 h1 + h1 h0 (dropped: h1 h1 <= 2^-22 relative).  This is the accuracy class of
+//     the reference's own fp32 route, 3xTF32 (src/elsa_twopass_clean/attention.py:280-282, 10 + 11 bits per operand),
+//     at half its tensor-pipe cost: a tf32 instruction covers half the K extent of an fp16 one.
+//   3 planes: x = b0 + b1 + b2 in bf16 (8 + 8 + 8 bits, no scaling needed), six cross terms of weight >= 2^-16
+//     (dropped: <= 2^-24 relative).  Twice the instructions; 2-3 x closer to fp64 on the forward.
 //
-// A pre-pass (split3_kernel) writes the three bf16 planes of q, k, v once per forward call.  One CTA (576 threads,
-// 1 per SM) owns ONE 128-row query tile of one (batch*head) and one K partition, walked in 128-key tiles:
+// A pre-pass (absmax_kernel + split_planes_kernel) writes the planes of q, k, v once per forward call.  One CTA (576
+// threads, 1 per SM) owns ONE 128-row query tile of one (batch*head) and one K partition, walked in 128-key tiles:
 //
-//   warp 16     TMA producer   the 3 planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
+//   warp 16     TMA producer   the planes of the Q tile once; then 16 KB plane tiles through an 8-slot ring in the
 //                              order the issuer consumes them: K planes of key tile j+1, V planes of key tile j
-//   warp 17     MMA issuer     S(j+1) = sum over the six (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
+//   warp 17     MMA issuer     S(j+1) = sum over the (q plane, k plane) pairs, 4 x tcgen05.mma 128x128x16 each,
 //                              as soon as the fold warps hold S(j) in registers;
-//                              O_j = sum over the six (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each,
+//                              O_j = sum over the (p plane, v plane) pairs, 8 x tcgen05.mma 128x64x16 each,
 //                              into an accumulator that starts from zero for every key tile
 //   warps 0-15  fold           FOUR threads per query row (warp w: rows 32 (w % 4) ..., key columns 32 (w / 4) ...):
 //                              the thread's 32 scores go from TMEM into registers once, the row max is exchanged
 //                              through shared memory, then exp2, row sum and -- after P V of the previous key tile
-//                              has retired -- the split of P into its three bf16 planes (own TMEM columns); the
-//                              row's running output lives in registers (16 columns per thread) and takes in O_{j-1}
-//                              with ordinary fp32 additions
+//                              has retired -- the split of P into its planes (own TMEM columns); the row's running
+//                              output lives in registers (16 columns per thread) and takes in O_{j-1} with ordinary
+//                              fp32 additions
 //
-// The per-element work of the fold (exponential, three roundings and two exact remainders) is about a dozen
-// instructions; with one thread per row (four warps, one per scheduler) every dependent instruction's latency was
-// exposed and a key tile took 11.9 k cycles against 3.1 k of tensor-pipe work.  Four warps per scheduler hide it.
+// Scales.  The plane scales of q, k, v are powers of two, so they come out exactly: the scores arrive times s_q s_k
+// (divided out together with the softmax scale), P is produced times 2^14 by adding 14 to the exponent of the
+// exponential (so the row sum and the output carry 2^14, the output also s_v), and the epilogue takes all of it out.
+// With fp16 planes a weight must not exceed 1, so the reference max follows every key tile (no lazy rescale).
+//
+// The per-element work of the fold is about a dozen instructions; with one thread per row (four warps, one per
+// scheduler) every dependent instruction's latency was exposed and a key tile took 11.9 k cycles against 3.1 k of
+// tensor-pipe work.  Four warps per scheduler hide it.
 //
 // Accuracy.  tcgen05.mma adds into its fp32 accumulator by truncation: every accumulating instruction loses up to one
 // unit in the last place of the accumulator, always towards zero.  Accumulating P V of a whole partition in TMEM (as
-// the 16-bit kernel does: invisible at 16-bit output precision) would cost 48 such losses per key tile -- 1.6e-6 on an
-// output of 0.1 after five key tiles, measured.  Therefore (a) every key tile gets a fresh accumulator and the running
-// sum over key tiles is kept by the fold warps in registers, and (b) within a tile the cross terms are issued in order
-// of increasing weight (x0*y2, x1*y1, x1*y0 ... x0*y0 last), so only the instructions of the leading term work at
-// full magnitude.
+// the 16-bit kernel does: invisible at 16-bit output precision) cost 1.6e-6 on an output of 0.1 after five key tiles,
+// measured.  Therefore (a) every key tile gets a fresh accumulator and the running sum over key tiles is kept by the
+// fold warps in registers, and (b) within a tile the cross terms are issued in order of increasing weight (the
+// leading term x0*y0 last), so only its instructions work at full magnitude.
 //
-// TMEM columns: S [0,128) O [128,192) P0 [192,256) P1 [256,320) P2 [320,384).
-// Per 128 x 128 tile the tensor pipe does 24 + 48 instructions (about 3100 cycles), the ex2 unit 1024 cycles: unlike
-// the 16-bit kernel this one is bound by the tensor pipe, at about 1/6 of its 16-bit rate.
+// TMEM columns: S [0,128) O [128,192) P planes [192 + 64 p, +64).
 #include <type_traits>
 
 #include "kernels.cuh"
@@ -58,9 +63,6 @@ constexpr int kProducerWarp = 16, kIssuerWarp = 17;
 // lazy exp-rescale: with bf16 planes a weight may grow to 2^8 before the reference max moves; fp16 planes hold weights
 // times 2^14, so there the reference max follows every tile (weights <= 1)
 constexpr float kRescaleThreshold = kPlanes == 3 ? 8.0f : 0.0f;
-constexpr float kLog2Unit = kPlanes == 3 ? 0.0f : 14.0f;      // log2(kPlaneUnit)
-constexpr int kPlaneHeader = 256;                              // bytes in front of a tensor's planes: its |x| max (bit pattern)
-constexpr uint32_t kPlaneFmt = kPlanes == 3 ? 1u : 0u;         // tcgen05 operand format: bf16 / fp16
 
 enum BarId { BAR_Q = 31, BAR_FULL = 32, BAR_FREE = 33, BAR_S = 34, BAR_P = 35, BAR_O = 36, BAR_SFREE = 37, BAR_PV = 38, BAR_ROW = 39 };
 
@@ -277,8 +279,9 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int row = qd * 32 + lane;                         // row within the tile == TMEM lane
     const int qi = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    const float c = prm.scale_log2;
-    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;   // zsum: this thread's 32 columns only
+    // the scores arrive multiplied by the plane scales of q and k (powers of two): taken out with the softmax scale
+    const float c = prm.scale_log2 / (plane_scale(*prm.amax_q) * plane_scale(*prm.amax_k));
+    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;   // zsum: this thread's 32 columns only, times kPlaneUnit
     float o_run[16];                                        // running sum of O over the key tiles (columns 16 cq ...), relative to m_ref
 #pragma unroll
     for (int i = 0; i < 16; ++i) o_run[i] = 0.f;
@@ -338,13 +341,15 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         m_ref = m_new;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      // ---- p = 2^(s*c - m) in place of the scores, and the quarter-row sum (all of it overlaps P V of tile j-1) ----
+      // ---- p = kPlaneUnit * 2^(s*c - m) in place of the scores (the unit rides in the exponent), and the quarter-row
+      // sum (all of it overlaps P V of tile j-1) ----
+      const float nm = kLog2Unit - m_use;
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         // ex2.approx: 2 units in the last place, i.e. 2.4e-7 relative on a weight
-        sv[i] = fast_exp2(fmaf(sv[i], c, -m_use));
-        sv[i + 1] = fast_exp2(fmaf(sv[i + 1], c, -m_use));
+        sv[i] = fast_exp2(fmaf(sv[i], c, nm));
+        sv[i + 1] = fast_exp2(fmaf(sv[i + 1], c, nm));
         ps[(i >> 1) & 3] += sv[i] + sv[i + 1];
       }
       zsum = zsum * alpha + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
@@ -359,16 +364,19 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 16; ++i) o_run[i] *= alpha;
       }
-      // ---- the split of p into its three bf16 planes, 16 keys (8 TMEM columns per plane) at a time ----
+      // ---- the split of p into its planes, 16 keys (8 TMEM columns per plane) at a time ----
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
-        uint32_t pk[3][8];
+        uint32_t pk[kPlanes][8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          split3_pair(sv[16 * ch + 2 * i], sv[16 * ch + 2 * i + 1], pk[0][i], pk[1][i], pk[2][i]);
+          uint32_t w[kPlanes];
+          split_planes_pair(sv[16 * ch + 2 * i], sv[16 * ch + 2 * i + 1], w);
+#pragma unroll
+          for (int p = 0; p < kPlanes; ++p) pk[p][i] = w[p];
         }
 #pragma unroll
-        for (int p = 0; p < 3; ++p) tmem_st8(tP[p] + lane_off + 16 * cq + 8 * ch, pk[p]);
+        for (int p = 0; p < kPlanes; ++p) tmem_st8(tP0 + 64 * p + lane_off + 16 * cq + 8 * ch, pk[p]);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -391,11 +399,13 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       if (alive) {
         const float ztot = (row_sum[0][row] + row_sum[1][row]) + (row_sum[2][row] + row_sum[3][row]);
-        const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true);
+        // zsum carries kPlaneUnit, o_run kPlaneUnit and the plane scale of v (powers of two: taken out exactly)
+        const float f = (m_true == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_true - kLog2Unit);
+        const float fo = f / plane_scale(*prm.amax_v);
         z_out = ztot * f;
         m_out = z_out > 0.f ? m_true : -CUDART_INF_F;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o_run[i] = z_out > 0.f ? o_run[i] * f : 0.f;
+        for (int i = 0; i < 16; ++i) o_run[i] = z_out > 0.f ? o_run[i] * fo : 0.f;
       }
     }
     if (row_ok && (alive || n_t == 0)) {
@@ -421,16 +431,26 @@ bool fold_tc3_supported(int dtype, int head_dim, bool has_bias) {
          fold_tc_supported(ELSA_BF16, 64, false);
 }
 
-int64_t fold_tc3_plane_bytes(int bh, int rows) { return align_up(static_cast<int64_t>(3) * bh * rows * 64 * 2, 256); }
+// a tensor's plane buffer: a 256-byte header (the bit pattern of its largest magnitude) + [kPlanes][bh][rows][64] 16-bit
+int64_t fold_tc3_plane_bytes(int bh, int rows) {
+  return kPlaneHeader + align_up(static_cast<int64_t>(kPlanes) * bh * rows * 64 * 2, 256);
+}
 
-// planes: [3][bh][rows][64] bf16 of the fp32 tensor x ([B, H, rows, 64] view with strides st)
+// the planes of the fp32 tensor x ([B, H, rows, cols] view with strides st) into `planes` (fold_tc3_plane_bytes)
 int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0) return ELSA_OK;
   if ((st.b | st.h | st.r) % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
   const int bh = batch * heads;
   const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(rows) * 16, 256)), static_cast<unsigned>(bh));
-  split3_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(planes), heads, rows, cols, st,
-                                          static_cast<int64_t>(bh) * rows * 64);
+  uint32_t* amax = static_cast<uint32_t*>(planes);
+  ELSA_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream));
+  if (kPlanes == 2) {
+    absmax_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), amax, heads, rows, cols, st);
+    ELSA_LAUNCH_CHECK();
+  }
+  split_planes_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), amax,
+                                                reinterpret_cast<uint16_t*>(static_cast<char*>(planes) + kPlaneHeader), heads, rows,
+                                                cols, st, static_cast<int64_t>(bh) * rows * 64);
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }
@@ -442,13 +462,15 @@ int fold_tc3(const FoldParams& p, cudaStream_t st) {
     return ELSA_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
   int rc;
-  // planes as a [3, B*H, rows, 64] bf16 tensor: the "head" coordinate is (batch*head), the "batch" coordinate the plane
+  // planes as a [kPlanes, B*H, rows, 64] 16-bit tensor: the "head" coordinate is (batch*head), the "batch" coordinate the plane
   const Strides sq = contiguous_strides(p.bh, p.n_ctx, 64), sk = contiguous_strides(p.bh, p.n_keys, 64);
-  if ((rc = make_tmap_rows64(&mq, p.q3, ELSA_BF16, p.n_ctx, p.bh, 3, sq, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mk, p.k3, ELSA_BF16, p.n_keys, p.bh, 3, sk, 128)) != ELSA_OK) return rc;
-  if ((rc = make_tmap_rows64(&mv, p.v3, ELSA_BF16, p.n_keys, p.bh, 3, sk, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mq, static_cast<const char*>(p.q3) + kPlaneHeader, kPlaneDtype, p.n_ctx, p.bh, kPlanes, sq, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, static_cast<const char*>(p.k3) + kPlaneHeader, kPlaneDtype, p.n_keys, p.bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, static_cast<const char*>(p.v3) + kPlaneHeader, kPlaneDtype, p.n_keys, p.bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
   Fold3Params prm;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
+  prm.amax_q = static_cast<const uint32_t*>(p.q3); prm.amax_k = static_cast<const uint32_t*>(p.k3);
+  prm.amax_v = static_cast<const uint32_t*>(p.v3);
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;

@@ -29,7 +29,7 @@ struct FoldParams {
   // not null, the row state, instead of a summary -- phase 2 would merge a single element
   int direct;
   void* out; Strides os; float* row_m; float* row_z;
-  // fp32 inputs on the tensor cores: the three bf16 planes of q, k, v written by fold_tc3_split (null otherwise)
+  // fp32 inputs on the tensor cores: the 16-bit planes of q, k, v written by fold_tc3_split (null otherwise)
   const void* q3; const void* k3; const void* v3;
 };
 
@@ -73,7 +73,7 @@ int device_status_word(int** dev_ptr, volatile int** host_ptr);
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
 int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
-// tcgen05 fold for fp32 inputs split into three bf16 planes (fold_tc3.cu)
+// tcgen05 fold for fp32 inputs split into 16-bit planes (fold_tc3.cu)
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t fold_tc3_plane_bytes(int bh, int rows);
 int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream);
@@ -83,7 +83,7 @@ bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc_workspace_bytes(int bh, int n_ctx);
 int bwd_tc(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
            int dtype, cudaStream_t st);
-// tcgen05 backward for fp32 inputs split into three bf16 planes (bwd_tc3.cu); workspace = padded D / LSE vectors +
+// tcgen05 backward for fp32 inputs split into 16-bit planes (bwd_tc3.cu); workspace = padded D / LSE vectors +
 // the planes of q, dout (n_ctx rows) and k, v (n_keys rows)
 bool bwd_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc3_workspace_bytes(int bh, int n_ctx, int n_keys);

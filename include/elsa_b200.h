@@ -49,9 +49,10 @@ enum elsa_status {
 #define ELSA_FLAG_SCAN_STEPS 2u   /* causal: run the log-depth Hillis-Steele steps instead of the one-pass merge */
 #define ELSA_FLAG_TREE_MERGE 4u   /* non-causal: run the Blelloch up-sweep levels instead of the one-pass merge */
 #define ELSA_FLAG_FP32_FMA 16u     /* forward and backward, fp32 inputs: stay on the FP32-FMA kernels instead of the
-                                     tensor-core kernels that work on three bf16 planes per operand (same accuracy class;
-                                     the planes cost 1.5 x the size of q, k, v in forward workspace and 1.5 x the size of
-                                     q, dout, k, v in backward workspace) */
+                                     tensor-core kernels that work on two fp16 planes per operand (x * 2^e = h0 + h1,
+                                     three cross products per fp32 product: the accuracy class of 3xTF32; the planes
+                                     cost the size of q, k, v in forward workspace and of q, dout, k, v in backward
+                                     workspace) */
 #define ELSA_FLAG_REF_ROUNDING 8u /* forward, fp16 / head dim 64 / no bias / not causal only: reproduce the rounding points of
                                      the reference's fp16 d=64 kernels (q * log2(e)/8 formed in fp16, scores unscaled:
                                      attention_parallel_scan.py:153-154,160) instead of the exact fp32 scale; the workspace
@@ -115,7 +116,7 @@ int elsa_phase1_fold_shard(const void* q, const void* k, const void* v,
                            int is_causal, unsigned flags, void* stream);
 
 /* The same with a workspace (elsa_phase1_fold_shard_workspace_bytes; 0 when none is needed): fp32 shards with head dim 64
- * then run on the tensor cores, the workspace holding the three bf16 planes of q, k_shard and v_shard.  No counterpart
+ * then run on the tensor cores, the workspace holding the 16-bit planes of q, k_shard and v_shard.  No counterpart
  * in the reference. */
 int64_t elsa_phase1_fold_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim, int n_keys,
                                                unsigned flags);
@@ -282,7 +283,7 @@ int elsa_row_stats(const void* q, const void* k,
  * contributions of that axis are summed (atomically).  The caller ALWAYS zeroes dbias before the call: besides
  * the sums, entries of pairs that the causal rule or the sequence length excludes are never written.
  * workspace: elsa_backward_workspace_bytes (row_d, row_lse; on the tensor-core path also the fp32 dQ accumulator
- * for 16-bit inputs, or the bf16 planes of q, dout, k, v for fp32 inputs). */
+ * for 16-bit inputs, or the 16-bit planes of q, dout, k, v for fp32 inputs). */
 int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                       int has_bias, int is_causal, unsigned flags);
 int elsa_twopass_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,

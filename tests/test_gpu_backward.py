@@ -176,7 +176,7 @@ def test_tensor_core_path_repeats_bit_for_bit(dtype, causal):
 
 @pytest.mark.parametrize("n,causal,h", [(512, False, 2), (1000, True, 2), (1153, False, 3), (4097, True, 1)])
 def test_fp32_tensor_core_backward_matches_the_fma_backward_and_fp64(n, causal, h):
-    """fp32 inputs with head dim 64 and at least 512 tokens take the tensor-core backward (three bf16 planes per
+    """fp32 inputs with head dim 64 and at least 512 tokens take the tensor-core backward (two fp16 planes per
     operand, fresh accumulators per tile pair); ELSA_FLAG_FP32_FMA selects the FP32-FMA kernels.  Both must meet the
     fp32 gradient bound against fp64, and the tensor-core result must repeat bit for bit (no atomics anywhere)."""
     from elsa_b200 import _lib

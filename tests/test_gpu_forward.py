@@ -289,9 +289,9 @@ def test_non_contiguous_inputs_and_errors():
 @pytest.mark.parametrize("b,h,n,causal,block_n", [(1, 2, 513, False, None), (1, 8, 1024, False, None), (1, 2, 1000, True, None),
                                                   (2, 2, 4097, False, 2048), (1, 2, 2304, True, 256)])
 def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, block_n):
-    """fp32 inputs with head dim 64 run phase 1 on the tensor cores as three bf16 planes per operand (six cross
+    """fp32 inputs with head dim 64 run phase 1 on the tensor cores as two fp16 planes per operand (three cross
     products per contraction); ELSA_FLAG_FP32_FMA keeps the exact-FMA kernel.  Both must sit within the fp32 bound of
-    fp64 softmax attention, and within it of each other."""
+    fp64 softmax attention."""
     from elsa_b200 import _lib
     from elsa_b200.attention import _forward_impl
     lib = _lib.load()
@@ -304,7 +304,7 @@ def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, bl
     truth = O.softmax_attention_fp64(q.cpu(), k.cpu(), v.cpu(), is_causal=causal)
     assert U.out_close(tc[0], truth, F32) <= 1.0
     assert U.out_close(fma[0], truth, F32) <= 1.0
-    assert U.max_abs(tc[0], fma[0]) <= 1e-6
+    assert U.max_abs(tc[0], fma[0]) <= 2e-6      # each within 1e-6 of fp64
     # row state: m in the log2 domain, z relative
     assert U.max_abs(tc[1], fma[1]) <= 2e-5
     assert ((tc[2] - fma[2]).abs() / fma[2]).max().item() <= 1e-5

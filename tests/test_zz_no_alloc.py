@@ -39,7 +39,7 @@ def test_static_scratch_forward_matches_workspace_forward(dtype, n, causal):
     assert lib.elsa_static_scratch_bytes() == 64 << 20
     for call in range(2):                      # two calls in a row share the built-in array
         q, k, v = (U.seeded((1, 4, n, 64), dtype, 300 + 10 * call + i).cuda() for i in range(3))
-        # fp32: the allocation-free entry point stays on the FP32-FMA kernel (the bf16 planes of the tensor-core route
+        # fp32: the allocation-free entry point stays on the FP32-FMA kernel (the planes of the tensor-core route
         # would not fit the built-in array), so the workspace forward is held to the same kernel
         ref = _forward_impl(q, k, v, bias=None, is_causal=causal, summary_dtype=dtype, part_width=0, q_chunk=0,
                             want_state=True, flags=_lib.FLAG_FP32_FMA if dtype == torch.float32 else 0)
