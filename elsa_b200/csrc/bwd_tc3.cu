@@ -51,7 +51,7 @@ constexpr int kDqSmem = (2 * kPlanes + kDqKSlots + kDqVSlots) * kPlaneBytes + 10
 constexpr int kKvSlots = 15, kVecStages = 4, kVecBytes = 2 * 64 * 4;
 constexpr int kKvSmem = 2 * kPlanes * kPlaneBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
 
-enum BarId { BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
+enum BarId { BAR_ROW = 40, BAR_STAGE = 41, BAR_FULL = 42, BAR_FREE = 43, BAR_SDP = 45, BAR_SFREE = 46, BAR_DS = 47, BAR_ACC = 48 };
 
 struct Bwd3Params {
   const float* nlse_pad; const float* nd_pad;   // [BH][n_pad]: -LSE, -D; padding rows hold -inf / 0
@@ -92,11 +92,27 @@ __device__ __forceinline__ void split_store16(const float* x, uint32_t tp0, uint
   for (int p = 0; p < kPlanes; ++p) tmem_st8(tp0 + STRIDE * p + col, pk[p]);
 }
 
-// The scaled quantities of the fp16-plane scheme (all factors are powers of two; 1 with bf16 planes):
-//   P'  = P  * 2^kLog2Unit            dS' = dS * s_ds,  s_ds = s_do * s_v * 2^-21  (|dS| <= 128 max|dO| max|V|)
-// where s_x is the plane scale of tensor x.  What the accumulators then hold, and what takes it out at the store:
-//   dP'  = s_do s_v dP      dQ_j' = s_ds s_k dQ_j      dV_i' = 2^kLog2Unit s_do dV_i      dK_i' = s_ds s_q dK_i
-__device__ __forceinline__ float ds_scale(float s_do, float s_v) { return kPlanes == 2 ? s_do * s_v * 4.76837158203125e-7f : 1.f; }
+// The scaled quantities of the fp16-plane scheme (all factors are powers of two; 1 with bf16 planes), s_x being the
+// plane scale of tensor x:
+//   S' = s_q s_k S, dP' = s_do s_v dP        arrive in TMEM; the fold divides the factors out
+//   P' = P * 2^kLog2Unit                     probabilities are at most 1 (the unit rides in the exponent)
+//   dS' = dS * r                             r = the power of two that puts the largest |dS| of this ROW of this tile
+//                                            pair in [2^13, 2^14): dS = P (dP - D) is orders of magnitude below any
+//                                            a-priori bound on long rows (P ~ 1/N), and a fixed scale would push its
+//                                            second fp16 term into the subnormals (measured: dQ 2.5e-5 relative at
+//                                            N = 65536).  The four threads of a row exchange their maxima through
+//                                            shared memory; the accumulator of the tile pair is divided by r (and by
+//                                            the scale of the other operand) when it is taken into the running sum.
+// With bf16 planes r = 1 and no exchange happens.
+__device__ __forceinline__ float abs_max16(const float* x) {
+  float m0 = fmaxf(fabsf(x[0]), fabsf(x[1])), m1 = fmaxf(fabsf(x[2]), fabsf(x[3]));
+#pragma unroll
+  for (int i = 4; i < 16; i += 4) {
+    m0 = fmaxf(m0, fmaxf(fabsf(x[i]), fabsf(x[i + 1])));
+    m1 = fmaxf(m1, fmaxf(fabsf(x[i + 2]), fabsf(x[i + 3])));
+  }
+  return fmaxf(m0, m1);
+}
 
 // ------------------------------------------------------------------------------------------------------------------
 // dQ: one CTA per 128-row query tile, 128-key tiles (N = 128 for S and dP: a tcgen05.mma with N = 64 costs 48-70
@@ -110,9 +126,10 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                const Bwd3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * (kDqKSlots + kDqVSlots) + 5];
+  __shared__ __align__(8) uint64_t bars[2 * (kDqKSlots + kDqVSlots) + 9];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float row_max[2][4][128];   // [tile parity][column quarter][row]: the quarter-row maxima of |dS|
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;
@@ -138,6 +155,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t bar_sfree = barx + 16;       // the fold warps hold them in registers
   const uint32_t bar_ds = barx + 24;          // the dS planes of tile j have been delivered
   const uint32_t bar_dq = barx + 32;          // dQ_j is complete
+  auto bar_row = [&](int qd) { return barx + 40 + 8 * qd; };   // the four threads of a row have exchanged their maxima
 
   if (tid == 0) {
     abort_flag = 0;
@@ -146,6 +164,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(bar_stage, 1);
     mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldWarps);
     mbar_init(bar_ds, kFoldWarps); mbar_init(bar_dq, 1);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar_row(qd), 4);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -252,15 +271,14 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int row = qd * 32 + lane;
     const int qi = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    // plane scales (powers of two; see ds_scale): S arrives times s_q s_k, dP times s_do s_v, dS leaves times s_ds
+    // plane scales (powers of two; see abs_max16): S arrives times s_q s_k, dP times s_do s_v, dS leaves times the row scale of the tile
     const float s_q = plane_scale(*prm.amax_q), s_do = plane_scale(*prm.amax_do);
     const float s_k = plane_scale(*prm.amax_k), s_v = plane_scale(*prm.amax_v);
-    const float s_ds = ds_scale(s_do, s_v);
     const float c = prm.scale_log2 / (s_q * s_k);
     const float idp = 1.f / (s_do * s_v);
-    // p * s_ds straight from the exponential: the scale rides in the exponent
-    const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi] + log2f(s_ds);   // q0 + 127 < n_pad
+    const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];   // q0 + 127 < n_pad
     const float nd = prm.nd_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];
+    float inv_r = 1.f;                         // 1 / (r s_k) of the tile whose dQ_j is in flight
     float dq_run[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) dq_run[i] = 0.f;
@@ -271,7 +289,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tmem_ld16(tdQ + lane_off + 16 * cq, r);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) dq_run[i] += __uint_as_float(r[i]);
+      for (int i = 0; i < 16; ++i) dq_run[i] = fmaf(__uint_as_float(r[i]), inv_r, dq_run[i]);
     };
 
     for (int j = 0; alive && j < n_t; ++j) {
@@ -295,12 +313,24 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           ds[i] = p * fmaf(__uint_as_float(rp[i]), idp, nd);
         }
       }
+      float r_scale = 1.f;
+      if (kPlanes == 2) {
+        // the row's scale for this tile: the largest |dS| over its 128 keys, exchanged between the row's four threads
+        row_max[j & 1][cq][row] = fmaxf(abs_max16(ds), abs_max16(ds + 16));
+        mbar_arrive_warp(bar_row(qd), lane);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), j & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
+        const float mx = fmaxf(fmaxf(row_max[j & 1][0][row], row_max[j & 1][1][row]), fmaxf(row_max[j & 1][2][row], row_max[j & 1][3][row]));
+        r_scale = plane_scale(__float_as_uint(mx));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ds[i] *= r_scale;
+      }
       if (j > 0) {
         // dQ of the previous key tile has retired: it goes into the running sum, and the dS planes are free
         if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (j - 1) & 1, &abort_flag, prm.status, BAR_ACC))) { alive = false; break; }
         tc_fence_after();
         take_dq();
       }
+      inv_r = 1.f / (r_scale * s_k);
       // the planes of dS: 16 keys (8 TMEM columns per plane) at a time
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) split_store16<64>(ds + 16 * ch, tDS + lane_off, 16 * cq + 8 * ch);
@@ -317,7 +347,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
     if (qi < N && (alive || n_t == 0)) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale / (s_ds * s_k), prm.head_dim - 16 * cq);
+      store16(prm.dq + bi * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(qi) * prm.dqs.r + 16 * cq, dq_run, prm.scale, prm.head_dim - 16 * cq);
     }
   }
 
@@ -335,9 +365,10 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                 const Bwd3Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kKvSlots + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kKvSlots + 9];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float row_max[2][4][128];   // [tile parity][column quarter][key row]: the quarter-row maxima of |dS^T|
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;
@@ -363,6 +394,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar_sfree = barx + 16;       // the fold warps hold them in registers
   const uint32_t bar_pl = barx + 24;          // the P^T / dS^T planes of tile i have been delivered
   const uint32_t bar_acc = barx + 32;         // dV_i, dK_i are complete
+  auto bar_row = [&](int qd) { return barx + 40 + 8 * qd; };   // the four threads of a key row have exchanged their maxima
 
   if (tid == 0) {
     abort_flag = 0;
@@ -370,6 +402,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(bar_kv, 1);
     mbar_init(bar_sdp, 1); mbar_init(bar_sfree, kFoldWarps);
     mbar_init(bar_pl, kFoldWarps); mbar_init(bar_acc, 1);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar_row(qd), 4);
     fence_mbar_init();
   }
   if (warp == kProducerWarp) {
@@ -488,14 +521,15 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int key_seq = kseq0 + row;           // its index in the sequence (what the causal rule compares)
     const bool key_ok = key < NK;
     const bool cta_tail = k0 + 128 > NK;       // some key rows of this CTA do not exist
-    // plane scales (powers of two; see ds_scale): S^T arrives times s_q s_k, dP^T times s_do s_v; P^T leaves times
-    // 2^kLog2Unit (the unit rides in the exponent), dS^T times s_ds
+    // plane scales (powers of two; see abs_max16): S^T arrives times s_q s_k, dP^T times s_do s_v; P^T leaves times
+    // 2^kLog2Unit (the unit rides in the exponent), dS^T times this key row's scale for the tile
     const float s_q = plane_scale(*prm.amax_q), s_do = plane_scale(*prm.amax_do);
     const float s_k = plane_scale(*prm.amax_k), s_v = plane_scale(*prm.amax_v);
-    const float s_ds = ds_scale(s_do, s_v);
     const float c = prm.scale_log2 / (s_q * s_k);
-    const float k2 = s_ds * exp2f(-kLog2Unit);          // dS' = P' * (dP + nd) * k2
+    const float k2 = exp2f(-kLog2Unit);                 // dS = P' * (dP + nd) * k2
     const float idp = k2 / (s_do * s_v);
+    const float inv_v = k2 / s_do;                      // dV_i' = 2^kLog2Unit s_do dV_i
+    float inv_r = 1.f;                                  // 1 / (r s_q) of the tile whose dK_i is in flight
     float dv_run[16], dk_run[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) { dv_run[i] = 0.f; dk_run[i] = 0.f; }
@@ -507,7 +541,10 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tmem_ld16(tdK + lane_off + 16 * cq, rk);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) { dv_run[i] += __uint_as_float(rv[i]); dk_run[i] += __uint_as_float(rk[i]); }
+      for (int i = 0; i < 16; ++i) {
+        dv_run[i] = fmaf(__uint_as_float(rv[i]), inv_v, dv_run[i]);
+        dk_run[i] = fmaf(__uint_as_float(rk[i]), inv_r, dk_run[i]);
+      }
     };
 
     for (int it = 0; it < n_it; ++it) {
@@ -546,12 +583,24 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
       }
+      float r_scale = 1.f;
+      if (kPlanes == 2) {
+        // the key row's scale for this tile: the largest |dS^T| over its 64 queries, exchanged between its four threads
+        row_max[it & 1][cq][row] = abs_max16(ds);
+        mbar_arrive_warp(bar_row(qd), lane);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), it & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
+        const float mx = fmaxf(fmaxf(row_max[it & 1][0][row], row_max[it & 1][1][row]), fmaxf(row_max[it & 1][2][row], row_max[it & 1][3][row]));
+        r_scale = plane_scale(__float_as_uint(mx));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ds[i] *= r_scale;
+      }
       if (it > 0) {
         // dV, dK of the previous query tile have retired: they go into the running sums, and the planes are free
         if (!__all_sync(0xffffffffu, mbar_wait(bar_acc, (it - 1) & 1, &abort_flag, prm.status, BAR_ACC))) { alive = false; break; }
         tc_fence_after();
         take_acc();
       }
+      inv_r = 1.f / (r_scale * s_q);
       split_store16<32>(p, tP + lane_off, 8 * cq);
       split_store16<32>(ds, tDS + lane_off, 8 * cq);
       tmem_wait_st();
@@ -567,8 +616,8 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
     if (key_ok && alive) {
       const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
-      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale / (s_ds * s_q), prm.head_dim - 16 * cq);
-      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, exp2f(-kLog2Unit) / s_do, prm.head_dim - 16 * cq);
+      store16(prm.dk + bi * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(key) * prm.dks.r + 16 * cq, dk_run, prm.scale, prm.head_dim - 16 * cq);
+      store16(prm.dv + bi * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(key) * prm.dvs.r + 16 * cq, dv_run, 1.f, prm.head_dim - 16 * cq);
     }
   }
 

@@ -42,6 +42,7 @@
 // leading term x0*y0 last), so only its instructions work at full magnitude.
 //
 // TMEM columns: S [0,128) O [128,192) P planes [192 + 64 p, +64).
+#include <algorithm>
 #include <type_traits>
 
 #include "kernels.cuh"
@@ -101,20 +102,30 @@ __device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16], int n
   }
 }
 
-// largest |x| of a [B, H, rows, cols] fp32 view, as a bit pattern (non-negative floats order like integers)
+// largest |x| of a [B, H, rows, cols] fp32 view, as a bit pattern (non-negative floats order like integers); one
+// atomic per block: grid.x blocks stride over the rows of one (batch*head)
 __global__ void __launch_bounds__(256)
 absmax_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int heads, int rows, int cols, Strides st) {
-  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
-  const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
+  __shared__ float wmax[8];
+  const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
+  const float* base = x + b * st.b + h * st.h;
+  const int c = static_cast<int>(threadIdx.x & 15) * 4;          // 16 threads per row of 64
   float m = 0.f;
-  if (r < rows && c < cols) {
-    const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
-    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c);
-    m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  if (c < cols) {
+    for (int r = blockIdx.x * 16 + static_cast<int>(threadIdx.x >> 4); r < rows; r += gridDim.x * 16) {
+      const float4 v = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(r) * st.r + c);
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0 && m > 0.f && m <= 3.0e38f) atomicMax(out, __float_as_uint(m));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, wmax[w]);
+    if (m > 0.f && m <= 3.0e38f) atomicMax(out, __float_as_uint(m));
+  }
 }
 
 // x (4 consecutive fp32 of a row of `cols` values, any strides) times the tensor's plane scale -> kPlanes 16-bit
@@ -445,7 +456,9 @@ int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads
   uint32_t* amax = static_cast<uint32_t*>(planes);
   ELSA_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream));
   if (kPlanes == 2) {
-    absmax_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), amax, heads, rows, cols, st);
+    // enough blocks to fill the machine a few times over, each with at least 8 rows per thread group
+    const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(cdiv64(rows, 128), cdiv64(1184, bh))));
+    absmax_kernel<<<dim3(gx, static_cast<unsigned>(bh)), 256, 0, stream>>>(static_cast<const float*>(x), amax, heads, rows, cols, st);
     ELSA_LAUNCH_CHECK();
   }
   split_planes_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), amax,
