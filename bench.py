@@ -477,8 +477,27 @@ def measure_models(dev, rank, world, dist, steps=5):
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                     ms = float(t.item())
                 entry[tag] = {"ms_per_step": ms, "images_per_s": world * 8 / (ms * 1e-3)}
+                if world == 1:
+                    # the same step replayed from a CUDA graph: what the GPU needs once the host's per-op overhead
+                    # (which bounds both models at this batch size) is out of the picture
+                    try:
+                        model.zero_grad(set_to_none=True)
+                        cg = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(cg):
+                            F.cross_entropy(model(x).float(), y).backward()
+                        for i in range(3):
+                            cg.replay()
+                        torch.cuda.synchronize()
+                        entry[tag]["graph_replay_ms_per_step"] = timed(lambda i: cg.replay(), 10)
+                        del cg
+                    except Exception as exc:  # noqa: BLE001
+                        entry[tag]["graph_replay_ms_per_step"] = None
+                        entry[tag]["graph_note"] = f"{type(exc).__name__}: {exc}"[:160]
             if "unpatched" in entry:
                 entry["lat_ratio_vs_unpatched"] = entry["elsa_b200"]["ms_per_step"] / entry["unpatched"]["ms_per_step"]
+                ga, gb = entry["elsa_b200"].get("graph_replay_ms_per_step"), entry["unpatched"].get("graph_replay_ms_per_step")
+                if ga and gb:
+                    entry["graph_replay_ratio_vs_unpatched"] = ga / gb
             sync.remove()
             res[name] = entry
             del base, ours, x

@@ -66,7 +66,12 @@ def _canonical_bias(bias: Optional[torch.Tensor], *, batch: int, heads: int, seq
         lead = (int(bias.shape[0]), int(bias.shape[1]))
     else:
         raise ValueError("bias must have shape [N,N], [H,N,N], or [B,H,N,N]")
-    view = bias.detach().to(torch.float32).contiguous().view(lead[0], lead[1], seq_len, seq_len)
+    view = bias.detach()
+    if view.dtype != torch.float32:
+        view = view.to(torch.float32)
+    if not view.is_contiguous():
+        view = view.contiguous()
+    view = view.view(lead[0], lead[1], seq_len, seq_len)
     return _BiasMeta(view,
                      0 if lead[0] == 1 else int(view.stride(0)),
                      0 if lead[1] == 1 else int(view.stride(1)),
@@ -118,17 +123,22 @@ def _bhnd_strides(t: torch.Tensor):
     """(batch, head, row) element strides of a [B, H, N, D] view the kernels can read in place, or None when it has
     to be copied first: the D axis must be contiguous, the other strides multiples of 8 elements (size-1 axes may
     have any stride) and the first element 16-byte aligned."""
-    if t.dim() != 4 or (t.shape[3] > 1 and t.stride(3) != 1) or t.data_ptr() % 16:
+    if t.dim() != 4:
         return None
-    st = []
-    for ax in (0, 1, 2):
-        s = int(t.stride(ax)) if t.shape[ax] > 1 else int(t.shape[3]) * 8      # any valid value for a size-1 axis
-        if s % 8 or s <= 0:
-            return None
-        st.append(s)
-    if st[2] < int(t.shape[3]):
+    b, h, n, d = t.shape
+    s0, s1, s2, s3 = t.stride()
+    if (d > 1 and s3 != 1) or t.data_ptr() % 16:
         return None
-    return tuple(st)
+    pad = d * 8                                  # any valid value for a size-1 axis
+    if b <= 1:
+        s0 = pad
+    if h <= 1:
+        s1 = pad
+    if n <= 1:
+        s2 = pad
+    if (s0 | s1 | s2) % 8 or s0 <= 0 or s1 <= 0 or s2 < d or s2 <= 0:
+        return None
+    return (s0, s1, s2)
 
 
 def _in_place_or_copy(t: torch.Tensor):

@@ -104,8 +104,10 @@ def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, wan
     else:
         if tuple(row_m.shape) != (batch * heads, seq_len) or tuple(row_z.shape) != (batch * heads, seq_len):
             raise ValueError("row_m and row_z must have shape [B*H,N]")
-        row_m = row_m.to(torch.float32).contiguous()
-        row_z = row_z.to(torch.float32).contiguous()
+        if row_m.dtype != torch.float32 or not row_m.is_contiguous():
+            row_m = row_m.to(torch.float32).contiguous()
+        if row_z.dtype != torch.float32 or not row_z.is_contiguous():
+            row_z = row_z.to(torch.float32).contiguous()
     if grads_into is not None:
         dq, dk, dv = grads_into
         g_strides = [_bhnd_strides(t) for t in (dq, dk, dv)]
@@ -227,12 +229,19 @@ class _PackedQkvAttentionAutograd(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, bias, is_causal, fwd_kwargs):
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)           # three [B, H, N, D] views
+        # the kernels read the bias in fp32: convert once, and let the backward reuse the converted tensor
+        bias32 = None
+        if bias is not None:
+            bias32 = bias.detach()
+            if bias32.dtype != torch.float32:
+                bias32 = bias32.to(torch.float32)
         out, row_m, row_z, q_s, k_s, v_s = twopass_attention_with_state(
-            q, k, v, bias=bias, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
+            q, k, v, bias=bias32, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
         has_bias = bias is not None
-        ctx.save_for_backward(qkv, out, bias if has_bias else qkv.new_empty(1, dtype=torch.float32), row_m, row_z)
+        ctx.save_for_backward(qkv, out, bias32 if has_bias else qkv.new_empty(1, dtype=torch.float32), row_m, row_z)
         ctx.has_bias = has_bias
         ctx.bias_requires_grad = bool(has_bias and bias.requires_grad)
+        ctx.bias_dtype = bias.dtype if has_bias else None
         ctx.is_causal = bool(is_causal)
         return out
 
@@ -243,15 +252,20 @@ class _PackedQkvAttentionAutograd(torch.autograd.Function):
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
         dqkv = torch.empty_like(qkv, memory_format=torch.contiguous_format)
         grads = dqkv.permute(2, 0, 3, 1, 4).unbind(0)
-        in_place = all(_bhnd_strides(t) is not None for t in (q, k, v, *grads)) and int(qkv.shape[-1]) % 8 == 0
+        if grad_out.dtype != q.dtype:
+            grad_out = grad_out.to(q.dtype)
+        # (dqkv is freshly allocated and contiguous: its three views are writable in place whenever q's layout is)
+        in_place = int(qkv.shape[-1]) % 8 == 0 and _bhnd_strides(q) is not None and _bhnd_strides(grads[0]) is not None
         if in_place:
-            _, _, _, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
+            _, _, _, dbias = _backward_impl(q, k, v, out, grad_out, bias=bias, is_causal=ctx.is_causal,
                                             row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad, grads_into=grads)
         else:
-            dq, dk, dv, dbias = _backward_impl(q, k, v, out, grad_out.to(q.dtype), bias=bias, is_causal=ctx.is_causal,
+            dq, dk, dv, dbias = _backward_impl(q, k, v, out, grad_out, bias=bias, is_causal=ctx.is_causal,
                                                row_m=row_m, row_z=row_z, want_dbias=ctx.bias_requires_grad)
             for dst, src in zip(grads, (dq, dk, dv)):
                 dst.copy_(src)
+        if dbias is not None and dbias.dtype != ctx.bias_dtype:
+            dbias = dbias.to(ctx.bias_dtype)
         return dqkv, dbias, None, None
 
 
