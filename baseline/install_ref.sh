@@ -6,10 +6,14 @@
 #                                           reference's own loader (torch cpp_extension, sm_100)
 # The reference's loader JIT-builds that extension on first use (about 3.5 minutes of nvcc because of the
 # torch headers); building it here once keeps that out of every GPU run.  Usage:
-#   baseline/install_ref.sh [path-to-reference-checkout]     (default: /root/reference)
+#   baseline/install_ref.sh <path-to-reference-checkout>     (or ELSA_REFERENCE_SRC in the environment)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-src="${1:-/root/reference}"
+src="${1:-${ELSA_REFERENCE_SRC:-}}"
+if [ -z "$src" ] || [ ! -d "$src/src/elsa_twopass_clean" ]; then
+  echo "usage: baseline/install_ref.sh <path-to-reference-checkout>" >&2
+  exit 2
+fi
 dst="$here/_ref"
 mkdir -p "$dst/src"
 rm -rf "$dst/src/elsa_twopass_clean"

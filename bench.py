@@ -537,7 +537,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a rank that fails inside a side measurement must not leave the others waiting for ten minutes (the default)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
 
     # synthetic inputs: iid N(0,1), CPU generator seeded per rank
     wl = Workload(args.workload, dev, rank)
