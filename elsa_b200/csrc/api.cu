@@ -78,6 +78,12 @@ static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, uns
   return n_ctx >= 512 && fold_tc_supported(dtype, head_dim, has_bias);
 }
 
+// 16-bit inputs with 64 < head dim <= 128 on the tensor cores (fold_tcw.cu / bwd_tcw.cu: one 128-row tile per CTA)
+static bool tcw_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  if (flags & ELSA_FLAG_FORCE_SIMT) return false;
+  return n_ctx >= 512 && fold_tcw_supported(dtype, head_dim, has_bias);
+}
+
 // fp32 on the tensor cores: head dim 64, no bias, and long enough that 128-row tiles fill the machine better than the
 // FP32-FMA kernel's 64-row tiles do
 static bool tc3_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
@@ -93,8 +99,9 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
   const int64_t bh = static_cast<int64_t>(batch) * heads;
   if (bh > 65535) return ELSA_ERR_UNSUPPORTED;
   pl->split3 = tc3_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  pl->tensor_cores = pl->split3 || tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  pl->tile_m = pl->split3 ? 128 : (pl->tensor_cores ? 256 : 64);   // query rows per CTA
+  const bool wide = tcw_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->tensor_cores = pl->split3 || wide || tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->tile_m = (pl->split3 || wide) ? 128 : (pl->tensor_cores ? 256 : 64);   // query rows per CTA
   pl->tile_n = pl->tensor_cores ? 128 : 64;                          // keys per tile
   const int tiles_n = static_cast<int>(cdiv64(n_ctx, pl->tile_n));
   int n_parts;
@@ -203,6 +210,11 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
     if (src != ELSA_OK) return src;
     return fold_tc(p, dtype, st);
   }
+  if (part_width % 128 == 0 && tcw_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return fold_tcw(p, dtype, st);
+  }
   return fold_simt(p, dtype, st);
 }
 
@@ -243,12 +255,15 @@ extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_ke
 
 static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
 static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
+static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
 
 extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
   (void)is_causal;
   if (backward)
-    return (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
-  return (tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
+    return (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ||
+            tcw_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
+  return (tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ||
+          tcw_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
 }
 
 extern "C" int elsa_phase1_fold(const void* q, const void* k, const void* v, const float* bias, int64_t bias_stride_b,
@@ -471,6 +486,12 @@ static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, u
   return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
 }
 
+// 16-bit inputs with 64 < head dim <= 128 on the tensor cores (bwd_tcw.cu)
+static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+  if (flags & ELSA_FLAG_FORCE_SIMT) return false;
+  return n_ctx >= 512 && bwd_tcw_supported(dtype, head_dim, has_bias);
+}
+
 static int64_t bwd_state_bytes(int batch, int heads, int n_ctx) {
   return align_up(static_cast<int64_t>(batch) * heads * n_ctx * 4, 256);
 }
@@ -483,6 +504,8 @@ extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads
   // (the fp32 tensor-core route is not taken when dbias is asked for: the larger of the two needs covers both)
   if (tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags))
     return std::max(bwd_tc3_workspace_bytes(batch * heads, n_ctx, n_ctx), 2 * bwd_state_bytes(batch, heads, n_ctx));
+  if (tcw_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags))
+    return std::max(bwd_tcw_workspace_bytes(batch * heads, n_ctx), 2 * bwd_state_bytes(batch, heads, n_ctx));
   return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
 }
 
@@ -509,6 +532,7 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   const bool use_tc3 = dbias == nullptr && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  const bool use_tcw = dbias == nullptr && tcw_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
   const Strides os = st8 ? st8[3] : cs;
   BwdParams p;
@@ -518,7 +542,7 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   // a problem of at most 64 tokens is one (query tile, key tile) pair: one launch does the pre-pass and all gradients
   p.single_tile = (!use_tc && n_ctx <= 64 && head_dim <= 64) ? 1 : 0;
   p.out = out; p.os = os; p.row_m = row_m; p.row_z = row_z;
-  if (!use_tc && !use_tc3 && !p.single_tile)
+  if (!use_tc && !use_tc3 && !use_tcw && !p.single_tile)
     rc = bwd_preprocess_any(out, os, dout, p.gs, row_m, row_z, row_d, row_lse, dtype, batch, heads, n_ctx, head_dim,
                             static_cast<cudaStream_t>(stream));
   if (rc != ELSA_OK) return rc;
@@ -541,6 +565,11 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return bwd_tc3(p, out, os, row_m, row_z, workspace, static_cast<cudaStream_t>(stream));
+  }
+  if (use_tcw) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tcw(p, out, os, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }
@@ -607,8 +636,9 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   // (the tensor-core kernels address the fp32 dQ of a shard as 64-wide rows)
   const bool use_tc = n_keys > 0 && head_dim == 64 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
   const bool use_tc3 = n_keys > 0 && n_keys <= n_ctx && tc3_backward_ok(dtype, head_dim, n_ctx, false, flags);
+  const bool use_tcw = n_keys > 0 && tcw_backward_ok(dtype, head_dim, n_ctx, false, flags);
   int rc = ELSA_OK;
-  if (!use_tc && !use_tc3) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
+  if (!use_tc && !use_tc3 && !use_tcw) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
   if (rc != ELSA_OK) return rc;
   BwdParams p;
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim), cks = contiguous_strides(heads, n_keys, head_dim);
@@ -632,6 +662,11 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return bwd_tc3(p, out, cs, row_m, row_z, workspace, static_cast<cudaStream_t>(stream));
+  }
+  if (use_tcw) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return bwd_tcw(p, out, cs, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
   }
   return bwd_simt(p, dtype, static_cast<cudaStream_t>(stream));
 }

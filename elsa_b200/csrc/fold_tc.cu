@@ -419,7 +419,7 @@ int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_ro
                      int box_rows, int cols) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ELSA_ERR_UNSUPPORTED;
-  if ((st.b | st.h | st.r) % 8 != 0 || cols < 8 || cols > 64 || cols % 8 != 0 || st.r < cols || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+  if ((st.b | st.h | st.r) % 8 != 0 || cols < 8 || cols > 128 || cols % 8 != 0 || st.r < cols || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(n_rows), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
   // a size-1 axis may come with any stride (PyTorch reports arbitrary ones): give it a valid dummy
   const cuuint64_t sh = heads > 1 ? static_cast<cuuint64_t>(st.h) * 2 : 128, sb = batch > 1 ? static_cast<cuuint64_t>(st.b) * 2 : 128;

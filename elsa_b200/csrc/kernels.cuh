@@ -73,6 +73,9 @@ int device_status_word(int** dev_ptr, volatile int** host_ptr);
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
 int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
+// tcgen05 fold for fp16 / bf16 inputs with 64 < head dim <= 128 (fold_tcw.cu)
+bool fold_tcw_supported(int dtype, int head_dim, bool has_bias);
+int fold_tcw(const FoldParams& p, int dtype, cudaStream_t st);
 // tcgen05 fold for fp32 inputs split into 16-bit planes (fold_tc3.cu)
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t fold_tc3_plane_bytes(int bh, int rows);
@@ -89,6 +92,11 @@ bool bwd_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t bwd_tc3_workspace_bytes(int bh, int n_ctx, int n_keys);
 int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
             cudaStream_t st);
+// tcgen05 backward for fp16 / bf16 inputs with 64 < head dim <= 128 (bwd_tcw.cu); workspace = padded D / LSE vectors
+bool bwd_tcw_supported(int dtype, int head_dim, bool has_bias);
+int64_t bwd_tcw_workspace_bytes(int bh, int n_ctx);
+int bwd_tcw(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
+            int dtype, cudaStream_t st);
 // D, LSE from out, dout (any strides) and the row state (bwd_simt.cu)
 int bwd_preprocess_any(const void* out, Strides os, const void* dout, Strides gs, const float* row_m, const float* row_z,
                        float* row_d, float* row_lse, int dtype, int batch, int heads, int n_ctx, int head_dim, cudaStream_t st);

@@ -70,6 +70,10 @@ CASES = [
     (1, 2, 600, 48, F16, True, None),
     (1, 2, 640, 32, F32, False, None),
     (1, 2, 900, 40, F32, True, None),
+    # head dims above 64 on the tensor cores (16-bit inputs)
+    (1, 2, 640, 128, F16, False, None),
+    (1, 2, 777, 96, BF16, True, None),
+    (2, 1, 1030, 72, F16, True, None),
 ]
 
 

@@ -134,6 +134,11 @@ CASES = [
     (1, 2, 1030, 8, BF16, False, None, None, None),
     (1, 2, 640, 32, F32, False, None, None, None),
     (1, 3, 900, 40, F32, True, None, None, None),
+    # head dims above 64 (16-bit inputs): two 64-column halves per operand
+    (1, 2, 640, 128, F16, False, None, None, None),
+    (1, 2, 777, 96, BF16, True, None, None, None),
+    (2, 1, 1030, 72, F16, True, None, 512, None),      # (same partition width in the oracle: same fp16 rounding points)
+    (1, 2, 2048, 128, BF16, False, None, 512, None),
 ]
 
 
@@ -312,8 +317,9 @@ def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, bl
 
 
 def test_routing_of_small_head_dims_and_fp32():
-    """Head dims below 64 (multiples of 8) and fp32 inputs take the tcgen05 kernels from 512 tokens on, forward and
-    backward; biased problems, head dims above 64 and short sequences stay on the FP32-FMA kernels."""
+    """Head dims up to 64 (multiples of 8) in fp16, bf16 and fp32, and head dims up to 128 in fp16 and bf16, take the
+    tcgen05 kernels from 512 tokens on, forward and backward; biased problems, fp32 head dims above 64 and short
+    sequences stay on the FP32-FMA kernels."""
     from elsa_b200 import _lib
     lib = _lib.load()
     f32, f16, bf16 = (_lib.dtype_code(t) for t in (F32, F16, BF16))
@@ -322,6 +328,9 @@ def test_routing_of_small_head_dims_and_fp32():
             for d in (8, 32, 48, 64):
                 assert lib.elsa_uses_tensor_cores(dt, d, 640, 0, 0, backward) == 1, (dt, d, backward)
             assert lib.elsa_uses_tensor_cores(dt, 64, 640, 1, 0, backward) == 0      # bias
-            assert lib.elsa_uses_tensor_cores(dt, 96, 640, 0, 0, backward) == 0      # head dim above 64
+            # head dims above 64: the 16-bit types have kernels for them, fp32 does not
+            for d in (72, 96, 128):
+                assert lib.elsa_uses_tensor_cores(dt, d, 640, 0, 0, backward) == (0 if dt == f32 else 1), (dt, d, backward)
+            assert lib.elsa_uses_tensor_cores(dt, 96, 640, 1, 0, backward) == 0      # bias
             assert lib.elsa_uses_tensor_cores(dt, 36, 640, 0, 0, backward) == 0      # not a multiple of 8
             assert lib.elsa_uses_tensor_cores(dt, 64, 200, 0, 0, backward) == 0      # short sequence

@@ -1,4 +1,4 @@
-"""Randomised sweep over the tensor-core routes (fp16 / bf16 / fp32, head dims 8..64, ragged lengths, causal or not,
+"""Randomised sweep over the tensor-core routes (fp16 / bf16 / fp32, head dims 8..64, and 72..128 for the 16-bit types, ragged lengths, causal or not,
 contiguous or packed-qkv layouts): forward and gradients against fp64 softmax attention evaluated on the same device.
 Seeded, so every run checks the same 36 problems."""
 import random
@@ -19,6 +19,8 @@ def _cases():
     for i in range(36):
         dtype = (torch.float16, torch.bfloat16, torch.float32)[i % 3]
         d = rng.choice((8, 16, 24, 32, 40, 48, 56, 64))
+        if dtype != torch.float32 and i % 2 == 1:
+            d = rng.choice((72, 80, 96, 104, 120, 128))      # the wide-head kernels (16-bit inputs only)
         n = rng.choice((512, 513, 640, 777, 1000, 1024, 1153, 1500, 2049, 2500))
         b, h = rng.choice(((1, 1), (1, 3), (2, 2), (3, 1)))
         out.append((i, dtype, b, h, n, d, rng.random() < 0.5, rng.random() < 0.4))
