@@ -309,9 +309,14 @@ extern "C" int elsa_phase1_fold_shard_ws(const void* q, const void* k, const voi
     char* planes = static_cast<char*>(workspace);
     const int64_t qb = fold_tc3_plane_bytes(batch * heads, n_ctx), kb = fold_tc3_plane_bytes(batch * heads, n_keys);
     int rc;
-    if ((rc = fold_tc3_split(q, contiguous_strides(heads, n_ctx, head_dim), planes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(k, contiguous_strides(heads, n_keys, head_dim), planes + qb, batch, heads, n_keys, head_dim, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(v, contiguous_strides(heads, n_keys, head_dim), planes + qb + kb, batch, heads, n_keys, head_dim, st)) != ELSA_OK) return rc;
+    {
+      const void* xs[3] = {q, k, v};
+      const Strides sts[3] = {contiguous_strides(heads, n_ctx, head_dim), contiguous_strides(heads, n_keys, head_dim),
+                              contiguous_strides(heads, n_keys, head_dim)};
+      void* pls[3] = {planes, planes + qb, planes + qb + kb};
+      const int rws[3] = {n_ctx, n_keys, n_keys};
+      if ((rc = fold_tc3_split_many(3, xs, sts, pls, rws, batch, heads, head_dim, st)) != ELSA_OK) return rc;
+    }
     q3 = planes; k3 = planes + qb; v3 = planes + qb + kb;
   }
   return phase1_dispatch(q, k, v, nullptr, 0, 0, 0, 0, m_buf, z_buf, s_buf, dtype, summary_dtype, batch, heads, n_ctx,
@@ -397,9 +402,13 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
     // fp32 on the tensor cores: the 16-bit planes of q, k, v, written once behind the summaries
     char* planes = ws + plan_bytes(pl);
     const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
-    if ((rc = fold_tc3_split(q, qs ? *qs : cs, planes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(k, ks ? *ks : cs, planes + plane_bytes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
-    if ((rc = fold_tc3_split(v, vs ? *vs : cs, planes + 2 * plane_bytes, batch, heads, n_ctx, head_dim, st)) != ELSA_OK) return rc;
+    {
+      const void* xs[3] = {q, k, v};
+      const Strides sts[3] = {qs ? *qs : cs, ks ? *ks : cs, vs ? *vs : cs};
+      void* pls[3] = {planes, planes + plane_bytes, planes + 2 * plane_bytes};
+      const int rws[3] = {n_ctx, n_ctx, n_ctx};
+      if ((rc = fold_tc3_split_many(3, xs, sts, pls, rws, batch, heads, head_dim, st)) != ELSA_OK) return rc;
+    }
     q3 = planes; k3 = planes + plane_bytes; v3 = planes + 2 * plane_bytes;
   }
   // A problem that is a single (query tile, key partition) pair of the FP32-FMA kernel (49-token windows and other

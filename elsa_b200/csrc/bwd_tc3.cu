@@ -692,10 +692,13 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
                                                   row_z, nd_pad, nlse_pad, p.heads, N, n_pad, p.head_dim, os, p.gs);
     ELSA_LAUNCH_CHECK();
   }
-  if ((rc = fold_tc3_split(p.q, p.qs, q3, batch, p.heads, N, p.head_dim, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.dout, p.gs, do3, batch, p.heads, N, p.head_dim, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.k, p.ks, k3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
-  if ((rc = fold_tc3_split(p.v, p.vs, v3, batch, p.heads, NK, p.head_dim, st)) != ELSA_OK) return rc;
+  {
+    const void* xs[4] = {p.q, p.dout, p.k, p.v};
+    const Strides sts[4] = {p.qs, p.gs, p.ks, p.vs};
+    void* pls[4] = {q3, do3, k3, v3};
+    const int rws[4] = {N, N, NK, NK};
+    if ((rc = fold_tc3_split_many(4, xs, sts, pls, rws, batch, p.heads, p.head_dim, st)) != ELSA_OK) return rc;
+  }
 
   // planes as [kPlanes, B*H, rows, 64] 16-bit tensors: the "head" coordinate is (batch*head), the "batch" coordinate the plane
   const Strides sq = contiguous_strides(bh, N, 64), sk = contiguous_strides(bh, NK, 64);
@@ -707,8 +710,8 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   Bwd3Params prm;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.nlse_pad = nlse_pad; prm.nd_pad = nd_pad;
-  prm.amax_q = reinterpret_cast<const uint32_t*>(q3); prm.amax_do = reinterpret_cast<const uint32_t*>(do3);
-  prm.amax_k = reinterpret_cast<const uint32_t*>(k3); prm.amax_v = reinterpret_cast<const uint32_t*>(v3);
+  prm.amax_q = reinterpret_cast<const uint32_t*>(q3) + kAmaxFinal; prm.amax_do = reinterpret_cast<const uint32_t*>(do3) + kAmaxFinal;
+  prm.amax_k = reinterpret_cast<const uint32_t*>(k3) + kAmaxFinal; prm.amax_v = reinterpret_cast<const uint32_t*>(v3) + kAmaxFinal;
   prm.dq = static_cast<float*>(p.dq); prm.dk = static_cast<float*>(p.dk); prm.dv = static_cast<float*>(p.dv);
   prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;

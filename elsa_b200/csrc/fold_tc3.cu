@@ -102,18 +102,29 @@ __device__ __forceinline__ void store_row16(TS* dst, const float (&v)[16], int n
   }
 }
 
-// largest |x| of a [B, H, rows, cols] fp32 view, as a bit pattern (non-negative floats order like integers); one
-// atomic per block: grid.x blocks stride over the rows of one (batch*head)
+// ---- the plane pre-pass: up to four tensors per launch (blockIdx.z selects the tensor) ----
+struct SplitJobs {
+  const float* x[4]; Strides st[4]; uint32_t* header[4]; int rows[4];
+};
+
+// largest |x| of each [B, H, rows, cols] fp32 view: kAmaxBlocks blocks per tensor stride over its rows and write one
+// partial maximum each into the tensor's plane header (bit patterns: non-negative floats order like integers); no
+// atomics, nothing to zero beforehand
 __global__ void __launch_bounds__(256)
-absmax_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int heads, int rows, int cols, Strides st) {
+absmax_kernel(const __grid_constant__ SplitJobs jobs, int heads, int bh, int cols) {
   __shared__ float wmax[8];
-  const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
-  const float* base = x + b * st.b + h * st.h;
+  const int job = blockIdx.z;
+  const float* x = jobs.x[job];
+  const Strides st = jobs.st[job];
+  const int rows = jobs.rows[job];
   const int c = static_cast<int>(threadIdx.x & 15) * 4;          // 16 threads per row of 64
   float m = 0.f;
   if (c < cols) {
-    for (int r = blockIdx.x * 16 + static_cast<int>(threadIdx.x >> 4); r < rows; r += gridDim.x * 16) {
-      const float4 v = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(r) * st.r + c);
+    const int64_t total = static_cast<int64_t>(bh) * rows;
+    for (int64_t fr = blockIdx.x * 16 + static_cast<int>(threadIdx.x >> 4); fr < total; fr += gridDim.x * 16) {
+      const int g = static_cast<int>(fr / rows), r = static_cast<int>(fr - static_cast<int64_t>(g) * rows);
+      const int b = g / heads, h = g - b * heads;
+      const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c);
       m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
   }
@@ -124,27 +135,48 @@ absmax_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int heads
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int w = 1; w < 8; ++w) m = fmaxf(m, wmax[w]);
-    if (m > 0.f && m <= 3.0e38f) atomicMax(out, __float_as_uint(m));
+    jobs.header[job][blockIdx.x] = (m > 0.f && m <= 3.0e38f) ? __float_as_uint(m) : 0u;
   }
 }
 
 // x (4 consecutive fp32 of a row of `cols` values, any strides) times the tensor's plane scale -> kPlanes 16-bit
-// planes [kPlanes][B*H][rows][64], contiguous; columns beyond `cols` are written as zeros (a head dim below 64 becomes
-// a zero-padded 64-column operand)
+// planes [kPlanes][B*H][rows][64] behind the header, contiguous; columns beyond `cols` are written as zeros (a head dim
+// below 64 becomes a zero-padded 64-column operand).  The tensor's largest magnitude is the maximum of the partial
+// maxima in its header; block (0, 0) also leaves it in header[kAmaxFinal] for the kernels that undo the scale.
 __global__ void __launch_bounds__(256)
-split_planes_kernel(const float* __restrict__ x, const uint32_t* __restrict__ amax, uint16_t* __restrict__ planes,
-                    int heads, int rows, int cols, Strides st, int64_t plane_elems) {
+split_planes_kernel(const __grid_constant__ SplitJobs jobs, int heads, int bh, int cols) {
+  __shared__ uint32_t amax_s;
+  const int job = blockIdx.z;
+  const int rows = jobs.rows[job];
+  uint32_t* header = jobs.header[job];
+  if (kPlanes == 2) {
+    if (threadIdx.x < 32) {
+      uint32_t m = max(header[threadIdx.x], header[threadIdx.x + 32]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (threadIdx.x == 0) {
+        amax_s = m;
+        if (blockIdx.x == 0 && blockIdx.y == 0) header[kAmaxFinal] = m;
+      }
+    }
+    __syncthreads();
+  } else if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+    header[kAmaxFinal] = 0u;
+  }
   const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;    // 16 threads per row of 64
   const int r = static_cast<int>(idx >> 4), c = static_cast<int>(idx & 15) * 4;
   if (r >= rows) return;
-  const int bh = blockIdx.y, b = bh / heads, h = bh - b * heads;
-  const float sc = plane_scale(*amax);
-  const float4 v = c < cols ? *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c)
+  const int g = blockIdx.y, b = g / heads, h = g - b * heads;
+  const Strides st = jobs.st[job];
+  const float sc = kPlanes == 2 ? plane_scale(amax_s) : 1.f;
+  const float4 v = c < cols ? *reinterpret_cast<const float4*>(jobs.x[job] + b * st.b + h * st.h + static_cast<int64_t>(r) * st.r + c)
                             : make_float4(0.f, 0.f, 0.f, 0.f);
   uint32_t w0[kPlanes], w1[kPlanes];
   split_planes_pair(v.x * sc, v.y * sc, w0);
   split_planes_pair(v.z * sc, v.w * sc, w1);
-  const int64_t off = (static_cast<int64_t>(bh) * rows + r) * 64 + c;
+  uint16_t* planes = reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(header) + kPlaneHeader);
+  const int64_t plane_elems = static_cast<int64_t>(bh) * rows * 64;
+  const int64_t off = (static_cast<int64_t>(g) * rows + r) * 64 + c;
 #pragma unroll
   for (int p = 0; p < kPlanes; ++p) *reinterpret_cast<uint2*>(planes + p * plane_elems + off) = make_uint2(w0[p], w1[p]);
 }
@@ -442,30 +474,42 @@ bool fold_tc3_supported(int dtype, int head_dim, bool has_bias) {
          fold_tc_supported(ELSA_BF16, 64, false);
 }
 
-// a tensor's plane buffer: a 256-byte header (the bit pattern of its largest magnitude) + [kPlanes][bh][rows][64] 16-bit
+// a tensor's plane buffer: a header (kAmaxBlocks partial maxima and the final one) + [kPlanes][bh][rows][64] 16-bit
 int64_t fold_tc3_plane_bytes(int bh, int rows) {
   return kPlaneHeader + align_up(static_cast<int64_t>(kPlanes) * bh * rows * 64 * 2, 256);
 }
 
-// the planes of the fp32 tensor x ([B, H, rows, cols] view with strides st) into `planes` (fold_tc3_plane_bytes)
-int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream) {
-  if (rows <= 0) return ELSA_OK;
-  if ((st.b | st.h | st.r) % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+// the planes of up to four fp32 tensors ([B, H, rows[i], cols] views with strides st[i]) into planes[i]
+// (fold_tc3_plane_bytes each): two launches for all of them
+int fold_tc3_split_many(int n, const void* const* x, const Strides* st, void* const* planes, const int* rows, int batch,
+                        int heads, int cols, cudaStream_t stream) {
+  if (n < 1 || n > 4) return ELSA_ERR_INVALID_ARGUMENT;
+  SplitJobs jobs;
+  int n_jobs = 0, max_rows = 0;
+  for (int i = 0; i < n; ++i) {
+    if (rows[i] <= 0) continue;
+    if ((st[i].b | st[i].h | st[i].r) % 4 != 0 || (reinterpret_cast<uintptr_t>(x[i]) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
+    jobs.x[n_jobs] = static_cast<const float*>(x[i]); jobs.st[n_jobs] = st[i];
+    jobs.header[n_jobs] = static_cast<uint32_t*>(planes[i]); jobs.rows[n_jobs] = rows[i];
+    max_rows = std::max(max_rows, rows[i]);
+    ++n_jobs;
+  }
+  if (n_jobs == 0) return ELSA_OK;
+  for (int i = n_jobs; i < 4; ++i) { jobs.x[i] = jobs.x[0]; jobs.st[i] = jobs.st[0]; jobs.header[i] = jobs.header[0]; jobs.rows[i] = 0; }
   const int bh = batch * heads;
-  const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(rows) * 16, 256)), static_cast<unsigned>(bh));
-  uint32_t* amax = static_cast<uint32_t*>(planes);
-  ELSA_CUDA_CHECK(cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream));
   if (kPlanes == 2) {
-    // enough blocks to fill the machine a few times over, each with at least 8 rows per thread group
-    const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(cdiv64(rows, 128), cdiv64(1184, bh))));
-    absmax_kernel<<<dim3(gx, static_cast<unsigned>(bh)), 256, 0, stream>>>(static_cast<const float*>(x), amax, heads, rows, cols, st);
+    absmax_kernel<<<dim3(kAmaxBlocks, 1, static_cast<unsigned>(n_jobs)), 256, 0, stream>>>(jobs, heads, bh, cols);
     ELSA_LAUNCH_CHECK();
   }
-  split_planes_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), amax,
-                                                reinterpret_cast<uint16_t*>(static_cast<char*>(planes) + kPlaneHeader), heads, rows,
-                                                cols, st, static_cast<int64_t>(bh) * rows * 64);
+  const dim3 grid(static_cast<unsigned>(cdiv64(static_cast<int64_t>(max_rows) * 16, 256)), static_cast<unsigned>(bh),
+                  static_cast<unsigned>(n_jobs));
+  split_planes_kernel<<<grid, 256, 0, stream>>>(jobs, heads, bh, cols);
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
+}
+
+int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream) {
+  return fold_tc3_split_many(1, &x, &st, &planes, &rows, batch, heads, cols, stream);
 }
 
 // p.q3 / p.k3 / p.v3: the plane buffers written by fold_tc3_split for the whole problem (all query rows / this
@@ -482,8 +526,8 @@ int fold_tc3(const FoldParams& p, cudaStream_t st) {
   if ((rc = make_tmap_rows64(&mv, static_cast<const char*>(p.v3) + kPlaneHeader, kPlaneDtype, p.n_keys, p.bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
   Fold3Params prm;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
-  prm.amax_q = static_cast<const uint32_t*>(p.q3); prm.amax_k = static_cast<const uint32_t*>(p.k3);
-  prm.amax_v = static_cast<const uint32_t*>(p.v3);
+  prm.amax_q = static_cast<const uint32_t*>(p.q3) + kAmaxFinal; prm.amax_k = static_cast<const uint32_t*>(p.k3) + kAmaxFinal;
+  prm.amax_v = static_cast<const uint32_t*>(p.v3) + kAmaxFinal;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;

@@ -80,6 +80,8 @@ int fold_tcw(const FoldParams& p, int dtype, cudaStream_t st);
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias);
 int64_t fold_tc3_plane_bytes(int bh, int rows);
 int fold_tc3_split(const void* x, Strides st, void* planes, int batch, int heads, int rows, int cols, cudaStream_t stream);
+int fold_tc3_split_many(int n, const void* const* x, const Strides* st, void* const* planes, const int* rows, int batch,
+                        int heads, int cols, cudaStream_t stream);
 int fold_tc3(const FoldParams& p, cudaStream_t st);
 // tcgen05 backward (bwd_tc.cu); workspace = padded D / LSE vectors + fp32 dQ accumulator
 bool bwd_tc_supported(int dtype, int head_dim, bool has_bias);

@@ -286,7 +286,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 constexpr int kPlanes = ELSA_FP32_PLANES;
 static_assert(kPlanes == 2 || kPlanes == 3, "fp32 operands are split into two fp16 or three bf16 planes");
 constexpr float kLog2Unit = kPlanes == 2 ? 14.f : 0.f;        // log2 of what a probability (<= 1) is multiplied by before its split
-constexpr int kPlaneHeader = 256;                              // bytes in front of a tensor's planes: its |x| max (bit pattern)
+constexpr int kAmaxBlocks = 64, kAmaxFinal = 64;               // header words: partial |x| maxima (bit patterns), then the final one
+constexpr int kPlaneHeader = 512;                              // bytes in front of a tensor's planes
 constexpr uint32_t kPlaneFmt = kPlanes == 3 ? 1u : 0u;         // tcgen05 operand format: bf16 / fp16
 constexpr int kPlaneDtype = kPlanes == 3 ? ELSA_BF16 : ELSA_F16;
 
