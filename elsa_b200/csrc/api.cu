@@ -78,7 +78,8 @@ static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, uns
   return n_ctx >= 512 && fold_tc_supported(dtype, head_dim, has_bias);
 }
 
-// 16-bit inputs with 64 < head dim <= 128 on the tensor cores (fold_tcw.cu / bwd_tcw.cu: one 128-row tile per CTA)
+// 16-bit inputs with 64 < head dim <= 128, or with a bias and any head dim up to 128, on the tensor cores
+// (fold_tcw.cu / bwd_tcw.cu: one 128-row tile per CTA)
 static bool tcw_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
   return n_ctx >= 512 && fold_tcw_supported(dtype, head_dim, has_bias);
@@ -495,7 +496,7 @@ static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, u
   return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
 }
 
-// 16-bit inputs with 64 < head dim <= 128 on the tensor cores (bwd_tcw.cu)
+// 16-bit inputs with 64 < head dim <= 128, or with a bias (and its gradient) and any head dim up to 128 (bwd_tcw.cu)
 static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
   return n_ctx >= 512 && bwd_tcw_supported(dtype, head_dim, has_bias);
@@ -541,7 +542,9 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   const bool use_tc3 = dbias == nullptr && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
-  const bool use_tcw = dbias == nullptr && tcw_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  // (the wide-head kernels also take biased problems, with or without a bias gradient)
+  const bool use_tcw = !use_tc && !use_tc3 && (dbias == nullptr || bias != nullptr) &&
+                       tcw_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
   const Strides os = st8 ? st8[3] : cs;
   BwdParams p;

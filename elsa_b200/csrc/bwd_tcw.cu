@@ -1,5 +1,7 @@
 // Backward on the 5th-generation tensor cores for fp16 / bf16 inputs with a WIDE head, 64 < d <= 128 (multiples of 8),
-// causal or not, no bias: exact recompute from the saved row statistics.  The head dim is handled as two 64-column
+// causal or not, and for BIASED problems of any head dim up to 128 (bias and dbias are read / written in global memory
+// by the fold warps of the dQ kernel; with d <= 64 only the first half below exists): exact recompute from the saved
+// row statistics.  The head dim is handled as two 64-column
 // halves of the same tensors (the second half zero-padded by the TMA box when d < 128).
 //
 // The kernel for d <= 64 (bwd_tc.cu) keeps S^T, dP^T, dV, dK and dQ of one key tile in TMEM; with 128 gradient columns
@@ -42,8 +44,8 @@ constexpr uint64_t kTileStep = kTileBytes >> 4;
 // contraction has read them) and one of 4 V tiles
 constexpr int kDqKSlots = 4, kDqVSlots = 4;
 constexpr int kDqSmem = (4 + kDqKSlots + kDqVSlots) * kTileBytes + 1024;
-// dK/dV kernel: K and V halves resident (64 KB), 15 ring slots of 8 KB, 4 stages of (-LSE, -D) vectors of 64 queries
-constexpr int kKvSlots = 15, kVecStages = 4, kVecBytes = 2 * 64 * 4;
+// dK/dV kernel: K and V halves resident (64 KB), 15 ring slots of 8 KB, 8 stages of (-LSE, -D) vectors of 64 queries
+constexpr int kKvSlots = 15, kVecStages = 8, kVecBytes = 2 * 64 * 4;   // (the ring runs up to 7 query tiles ahead when a tile has 2 entries)
 constexpr int kKvSmem = 4 * kTileBytes + kKvSlots * kSlotBytes + kVecStages * kVecBytes + 1024;
 
 enum BarId { BAR_STAGE = 61, BAR_FULL = 62, BAR_FREE = 63, BAR_SDP = 65, BAR_SFREE = 66, BAR_DS = 67, BAR_ACC = 68 };
@@ -55,7 +57,11 @@ struct BwdWParams {
   int n_ctx, n_pad, bh, heads, is_causal;
   int n_keys, key_offset;                       // K/V rows of this launch and the sequence index of the first one
   int head_dim, dq_f32;
+  int n_halves;                                 // 1 when head_dim <= 64 (biased problems), else 2
   float scale, scale_log2;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;      // additive bias [.., N, N] (natural-log units) or null
+  float* dbias; int64_t dsb, dsh, dsq, dsk;           // its gradient (same addressing; zeroed by the caller) or null
+  int dbias_atomic;                                   // a broadcast axis: contributions are added atomically
   int* status;                                  // the device's status word (mapped host memory)
 };
 
@@ -90,7 +96,7 @@ __device__ __forceinline__ void store16(TO* dst, const uint32_t (&r)[16], float 
 // dQ: one CTA per 128-row query tile, 128-key tiles
 // TMEM columns: S [0,128) dP [128,256) dQ_lo [256,320) dQ_hi [320,384) dS [384,448)
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -149,8 +155,9 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     if (n_t > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_stage, 4 * kTileBytes);
-      for (int h = 0; h < 2; ++h) {
+      const int nh = BIAS ? prm.n_halves : 2;
+      mbar_arrive_expect_tx(bar_stage, 2 * nh * kTileBytes);
+      for (int h = 0; h < nh; ++h) {
         tma_load_4d(sQ(h), &tmap_q, bar_stage, 64 * h, q0, hi, bi);
         tma_load_4d(sDO(h), &tmap_do, bar_stage, 64 * h, q0, hi, bi);
       }
@@ -158,13 +165,13 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // per key tile: its K halves (ring sequence numbers 2 j, 2 j + 1), then its V halves.  A V slot is released by
       // the dP contraction that read it, a K slot by the dQ contraction.
       for (int j = 0; j < n_t && ok; ++j) {
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < nh && ok; ++h) {
           const int seq = 2 * j + h, slot = seq % kDqKSlots;
           if (seq >= kDqKSlots && !(ok = mbar_wait(bar_kfree(slot), ((seq / kDqKSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_kfull(slot), kTileBytes);
           tma_load_4d(sKs(slot), &tmap_k, bar_kfull(slot), 64 * h, j * 128, hi, bi);
         }
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < nh && ok; ++h) {
           const int seq = 2 * j + h, slot = seq % kDqVSlots;
           if (seq >= kDqVSlots && !(ok = mbar_wait(bar_vfree(slot), ((seq / kDqVSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_vfull(slot), kTileBytes);
@@ -182,16 +189,17 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const uint64_t dDOh[2] = {make_sdesc(sDO(0), 16, 1024), make_sdesc(sDO(1), 16, 1024)};
       const uint64_t dk_k0 = make_sdesc(sKs(0), 16, 1024), dk_mn0 = make_sdesc(sKs(0), 128 * 128, 1024);
       const uint64_t dv_k0 = make_sdesc(sVs(0), 16, 1024);
+      const int nh = BIAS ? prm.n_halves : 2;
       bool ok = mbar_wait(bar_stage, 0, &abort_flag, prm.status, BAR_STAGE);
       auto issue_sdp = [&](int j) {
-        for (int h = 0; h < 2 && ok; ++h) {                // dP = sum over the halves of dO_h V_h^T
+        for (int h = 0; h < nh && ok; ++h) {               // dP = sum over the halves of dO_h V_h^T
           const int seq = 2 * j + h, slot = seq % kDqVSlots;
           if (!(ok = mbar_wait(bar_vfull(slot), (seq / kDqVSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           mma_ss_x4<2, 2>(tdP, dDOh[h], dv_k0 + slot * kTileStep, idesc_k, h == 0 ? 0u : 1u);
           mma_commit(bar_vfree(slot));
         }
-        for (int h = 0; h < 2 && ok; ++h) {                // S = sum over the halves of Q_h K_h^T
+        for (int h = 0; h < nh && ok; ++h) {               // S = sum over the halves of Q_h K_h^T
           const int seq = 2 * j + h, slot = seq % kDqKSlots;
           if (!(ok = mbar_wait(bar_kfull(slot), (seq / kDqKSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
@@ -212,7 +220,7 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         if (!(ok = mbar_wait(bar_ds, j & 1, &abort_flag, prm.status, BAR_DS))) break;
         tc_fence_after();
-        for (int h = 0; h < 2; ++h) {                      // dQ_h += dS K_h over the 128 keys (eight K-steps)
+        for (int h = 0; h < nh; ++h) {                     // dQ_h += dS K_h over the 128 keys (eight K-steps)
           const int slot = (2 * j + h) % kDqKSlots;
           mma_ts_x4<8, 128>(tdQ + 64 * h, tDS, dk_mn0 + slot * kTileStep, idesc_mn, j == 0 ? 0u : 1u);
           mma_ts_x4<8, 128>(tdQ + 64 * h, tDS + 32, dk_mn0 + slot * kTileStep + 512, idesc_mn, 1u);
@@ -230,6 +238,10 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const float c = prm.scale_log2;
     const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];   // q0 + 127 < n_pad
     const float nd = prm.nd_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];
+    const bool two_halves = BIAS ? prm.n_halves == 2 : true;   // (warp-uniform: tcgen05.ld is collective)
+    const int qrow = min(qi, N - 1);                        // rows beyond N are never stored: any valid address will do
+    const float* bias_row = BIAS ? prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(qrow) * prm.bsq : nullptr;
+    float* dbias_row = (BIAS && prm.dbias) ? prm.dbias + bi * prm.dsb + hi * prm.dsh + static_cast<int64_t>(qrow) * prm.dsq : nullptr;
     bool alive = n_t > 0;
 
     for (int j = 0; alive && j < n_t; ++j) {
@@ -248,11 +260,28 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int lim = prm.is_causal ? min(NK - 1, qi - koff) : NK - 1;   // last admissible (local) key of this row
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nlse));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), c, nlse));
+          float a0 = nlse, a1 = nlse;
+          if constexpr (BIAS) {
+            // bias in natural-log units: s c + b log2(e) - LSE; keys beyond the row's last admissible one are masked below
+            const int64_t ko = static_cast<int64_t>(kb + koff + i) * prm.bsk;
+            if (kb + i < NK) a0 = fmaf(bias_row[ko], 1.4426950408889634f, nlse);
+            if (kb + i + 1 < NK) a1 = fmaf(bias_row[ko + prm.bsk], 1.4426950408889634f, nlse);
+          }
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a0));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), c, a1));
           if (masked && kb + i > lim) p0 = 0.f;
           if (masked && kb + i + 1 > lim) p1 = 0.f;
-          pk[i >> 1] = pack2<T>(p0 * (__uint_as_float(rp[i]) + nd), p1 * (__uint_as_float(rp[i + 1]) + nd));
+          const float d0 = p0 * (__uint_as_float(rp[i]) + nd), d1 = p1 * (__uint_as_float(rp[i + 1]) + nd);
+          pk[i >> 1] = pack2<T>(d0, d1);
+          if constexpr (BIAS) {
+            // dbias = dS (every (query, key) pair is visited exactly once by this kernel); pairs that the causal rule or
+            // the sequence length excludes are left as the caller zeroed them
+            if (dbias_row && qi < N) {
+              const int64_t ko = static_cast<int64_t>(kb + koff + i) * prm.dsk;
+              if (kb + i <= lim) { if (prm.dbias_atomic) atomicAdd(dbias_row + ko, d0); else dbias_row[ko] = d0; }
+              if (kb + i + 1 <= lim) { if (prm.dbias_atomic) atomicAdd(dbias_row + ko + prm.dsk, d1); else dbias_row[ko + prm.dsk] = d1; }
+            }
+          }
         }
       }
       if (j > 0) {
@@ -273,7 +302,7 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (alive) {
         tc_fence_after();
         tmem_ld16(tdQ + lane_off + 16 * cq, r0);
-        tmem_ld16(tdQ + 64 + lane_off + 16 * cq, r1);
+        if (two_halves) tmem_ld16(tdQ + 64 + lane_off + 16 * cq, r1);
         tmem_wait_ld();
       }
     }
@@ -299,7 +328,7 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 // dK, dV: one CTA per 128-row key tile, 64-query tiles
 // TMEM columns: S^T [0,64) dP^T [64,128) P^T [128,160) dS^T [160,192) dV_lo dV_hi [192,320) dK_lo dK_hi [320,448)
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -358,22 +387,23 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (n_it > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_kv, 4 * kTileBytes);
-      for (int h = 0; h < 2; ++h) {
+      const int nh = BIAS ? prm.n_halves : 2;
+      mbar_arrive_expect_tx(bar_kv, 2 * nh * kTileBytes);
+      for (int h = 0; h < nh; ++h) {
         tma_load_4d(sK(h), &tmap_k, bar_kv, 64 * h, k0, hi, bi);
         tma_load_4d(sV(h), &tmap_v, bar_kv, 64 * h, k0, hi, bi);
       }
       int seq = 0;
       bool ok = true;
-      // ring order of query tile i: dO_lo, dO_hi (sequence numbers 4 i, 4 i + 1), then Q_lo, Q_hi; the tile's first
+      // ring order of query tile i: its dO halves (sequence numbers 2 nh i ...), then its Q halves; the tile's first
       // slot also receives its -LSE / -D vectors
       for (int it = 0; it < n_it && ok; ++it) {
         const int qrow = (it_begin + it) * 64;
-        for (int x = 0; x < 4 && ok; ++x) {
+        for (int x = 0; x < 2 * nh && ok; ++x) {
           const int slot = seq % kKvSlots;
           if (seq >= kKvSlots && !(ok = mbar_wait(bar_free(slot), ((seq / kKvSlots) - 1) & 1, &abort_flag, prm.status, BAR_FREE))) break;
           mbar_arrive_expect_tx(bar_full(slot), kSlotBytes + (x == 0 ? kVecBytes : 0));
-          tma_load_4d(sSlot(slot), x < 2 ? &tmap_do : &tmap_q, bar_full(slot), 64 * (x & 1), qrow, hi, bi);
+          tma_load_4d(sSlot(slot), x < nh ? &tmap_do : &tmap_q, bar_full(slot), 64 * (x % nh), qrow, hi, bi);
           if (x == 0) {
             const uint32_t dst = smem_base + vec_off + (it % kVecStages) * kVecBytes;
             bulk_load_1d(dst, prm.nlse_pad + static_cast<int64_t>(bh) * prm.n_pad + qrow, 256, bar_full(slot));
@@ -392,16 +422,17 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint64_t dKh[2] = {make_sdesc(sK(0), 16, 1024), make_sdesc(sK(1), 16, 1024)};
       const uint64_t dVh[2] = {make_sdesc(sV(0), 16, 1024), make_sdesc(sV(1), 16, 1024)};
       const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dmn_slot0 = make_sdesc(sSlot(0), 64 * 128, 1024);
+      const int nh = BIAS ? prm.n_halves : 2;
       bool ok = mbar_wait(bar_kv, 0, &abort_flag, prm.status, BAR_STAGE);
       auto issue_sdp = [&](int it) {
-        for (int h = 0; h < 2 && ok; ++h) {                // dP^T = sum over the halves of V_h dO_h^T
-          const int seq = 4 * it + h, slot = seq % kKvSlots;
+        for (int h = 0; h < nh && ok; ++h) {               // dP^T = sum over the halves of V_h dO_h^T
+          const int seq = 2 * nh * it + h, slot = seq % kKvSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           mma_ss_x4<2, 2>(tdP, dVh[h], dk_slot0 + slot * kSlotStep, idesc_k, h == 0 ? 0u : 1u);
         }
-        for (int h = 0; h < 2 && ok; ++h) {                // S^T = sum over the halves of K_h Q_h^T
-          const int seq = 4 * it + 2 + h, slot = seq % kKvSlots;
+        for (int h = 0; h < nh && ok; ++h) {               // S^T = sum over the halves of K_h Q_h^T
+          const int seq = 2 * nh * it + nh + h, slot = seq % kKvSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
           mma_ss_x4<2, 2>(tS, dKh[h], dk_slot0 + slot * kSlotStep, idesc_k, h == 0 ? 0u : 1u);
@@ -422,13 +453,13 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!(ok = mbar_wait(bar_pl, it & 1, &abort_flag, prm.status, BAR_DS))) break;
         tc_fence_after();
         const uint32_t acc = it == 0 ? 0u : 1u;
-        for (int h = 0; h < 2; ++h) {                      // dV_h += P^T dO_h (64 queries: four K-steps)
-          const int slot = (4 * it + h) % kKvSlots;
+        for (int h = 0; h < nh; ++h) {                     // dV_h += P^T dO_h (64 queries: four K-steps)
+          const int slot = (2 * nh * it + h) % kKvSlots;
           mma_ts_x4<8, 128>(tdV + 64 * h, tP, dmn_slot0 + slot * kSlotStep, idesc_mn, acc);
           mma_commit(bar_free(slot));
         }
-        for (int h = 0; h < 2; ++h) {                      // dK_h += dS^T Q_h
-          const int slot = (4 * it + 2 + h) % kKvSlots;
+        for (int h = 0; h < nh; ++h) {                     // dK_h += dS^T Q_h
+          const int slot = (2 * nh * it + nh + h) % kKvSlots;
           mma_ts_x4<8, 128>(tdK + 64 * h, tDS, dmn_slot0 + slot * kSlotStep, idesc_mn, acc);
           mma_commit(bar_free(slot));
         }
@@ -445,6 +476,9 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const bool key_ok = key < NK;
     const bool cta_tail = k0 + 128 > NK;       // some key rows of this CTA do not exist
     const float c = prm.scale_log2;
+    const int n_halves = BIAS ? prm.n_halves : 2;
+    // bias[query, key] of this thread's key column; the query offset is added per element
+    const float* bias_col = BIAS ? prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(key_seq, N - 1)) * prm.bsk : nullptr;
     bool alive = true;
 
     for (int it = 0; it < n_it; ++it) {
@@ -453,7 +487,7 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the tile's row statistics were written by the bulk copies that complete on its first slot's barrier: observe
       // that barrier directly (it completed before the MMAs behind bar_sdp were issued, so this never spins)
       {
-        const int seq = 4 * it;
+        const int seq = 2 * n_halves * it;
         if (!__all_sync(0xffffffffu, mbar_wait(bar_full(seq % kKvSlots), (seq / kKvSlots) & 1, &abort_flag, prm.status, BAR_FULL))) { alive = false; break; }
       }
       tc_fence_after();
@@ -477,7 +511,11 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = 4 * g + e;
-            float x = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nle[e]));
+            float a = nle[e];
+            if constexpr (BIAS) {
+              if (key_ok && qc + i < N) a = fmaf(bias_col[static_cast<int64_t>(qc + i) * prm.bsq], 1.4426950408889634f, a);
+            }
+            float x = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a));
             if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) x = 0.f;
             pv[e] = x;
             dv[e] = x * (__uint_as_float(rp[i]) + nde[e]);
@@ -502,7 +540,7 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // dK, dV of this key tile (tcgen05.ld is warp-collective: only the stores are predicated)
       const int d = prm.head_dim;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < n_halves; ++h) {
         uint32_t rk[16], rv[16];
         if (n_it > 0) {
           tc_fence_after();
@@ -604,30 +642,34 @@ static int bwd_tcw_t(const BwdParams& p, const void* out, Strides os, const floa
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
   prm.n_keys = NK; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim; prm.dq_f32 = p.dq_f32;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
+  prm.n_halves = p.head_dim > 64 ? 2 : 1;
+  prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk;
+  prm.dbias = p.dbias; prm.dsb = p.dsb; prm.dsh = p.dsh; prm.dsq = p.dsq; prm.dsk = p.dsk; prm.dbias_atomic = p.dbias_atomic;
   if (NK > 0) {
     if ((rc = make_tmap_rows64(&mk128, p.k, dtype, NK, p.heads, batch, p.ks, 128, p.head_dim)) != ELSA_OK) return rc;
     if ((rc = make_tmap_rows64(&mv128, p.v, dtype, NK, p.heads, batch, p.vs, 128, p.head_dim)) != ELSA_OK) return rc;
   } else {
     mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
   }
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwdw_dq_kernel<T>), kDqSmem)) != ELSA_OK) return rc;
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwdw_dkv_kernel<T>), kKvSmem)) != ELSA_OK) return rc;
-  {
-    const dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
-    bwdw_dq_kernel<T><<<grid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk128, mv128, prm);
-    ELSA_LAUNCH_CHECK();
-  }
-  if (NK > 0) {
-    const dim3 grid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
-    bwdw_dkv_kernel<T><<<grid, kThreads, kKvSmem, st>>>(mq64, mdo64, mk128, mv128, prm);
-    ELSA_LAUNCH_CHECK();
-  }
+  const dim3 qgrid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
+  const dim3 kgrid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
+  auto launch = [&](auto dq_kernel, auto dkv_kernel) -> int {
+    int r;
+    if ((r = ensure_dynamic_smem(reinterpret_cast<const void*>(dq_kernel), kDqSmem)) != ELSA_OK) return r;
+    if ((r = ensure_dynamic_smem(reinterpret_cast<const void*>(dkv_kernel), kKvSmem)) != ELSA_OK) return r;
+    dq_kernel<<<qgrid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk128, mv128, prm);
+    if (NK > 0) dkv_kernel<<<kgrid, kThreads, kKvSmem, st>>>(mq64, mdo64, mk128, mv128, prm);
+    return ELSA_OK;
+  };
+  rc = p.bias ? launch(&bwdw_dq_kernel<T, true>, &bwdw_dkv_kernel<T, true>) : launch(&bwdw_dq_kernel<T, false>, &bwdw_dkv_kernel<T, false>);
+  if (rc != ELSA_OK) return rc;
+  ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }
 
 int bwd_tcw(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
             int dtype, cudaStream_t st) {
-  if (!bwd_tcw_supported(dtype, p.head_dim, p.bias != nullptr) || p.dbias) return ELSA_ERR_UNSUPPORTED;
+  if (!bwd_tcw_supported(dtype, p.head_dim, p.bias != nullptr) || (p.dbias && !p.bias)) return ELSA_ERR_UNSUPPORTED;
   if (dtype == ELSA_F16) return bwd_tcw_t<__half>(p, out, os, row_m, row_z, workspace, dtype, st);
   return bwd_tcw_t<__nv_bfloat16>(p, out, os, row_m, row_z, workspace, dtype, st);
 }

@@ -1,4 +1,6 @@
-// Phase 1 on the 5th-generation tensor cores for fp16 / bf16 inputs with a WIDE head: 64 < d <= 128 (multiples of 8).
+// Phase 1 on the 5th-generation tensor cores for fp16 / bf16 inputs with a WIDE head: 64 < d <= 128 (multiples of 8),
+// and for BIASED problems of any head dim up to 128 (the additive bias is read from global memory by the fold warps;
+// with d <= 64 only the first half below exists).
 // The head dim is handled as two 64-column halves of the same tensors (the second half zero-padded by the TMA box
 // when d < 128):
 //     S   = Q_lo K_lo^T + Q_hi K_hi^T          two K = 64 contractions into one accumulator   (N = 128 keys)
@@ -45,7 +47,9 @@ struct FoldWParams {
   float* m; float* z; void* s;
   int n_ctx, q_start, q_len, part_width, n_parts, bh, heads, is_causal, summary_dtype;
   int n_keys, key_offset, head_dim;
+  int n_halves;                                 // 1 when head_dim <= 64 (biased problems), else 2
   float scale_log2;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;  // additive bias [.., N, N] (natural-log units) or null
   int* status;
 };
 
@@ -74,7 +78,7 @@ __device__ __forceinline__ void store_row16(TS* dst, const float* v, int n) {
   }
 }
 
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const FoldWParams prm) {
@@ -135,8 +139,9 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (n_t > 0 && lane == 0) {
       // ---------------- TMA producer ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      mbar_arrive_expect_tx(bar_q, 2 * kTileBytes);
-      for (int h = 0; h < 2; ++h) tma_load_4d(sQ(h), &tmap_q, bar_q, 64 * h, q0, hi, bi);
+      const int nh = BIAS ? prm.n_halves : 2;
+      mbar_arrive_expect_tx(bar_q, nh * kTileBytes);
+      for (int h = 0; h < nh; ++h) tma_load_4d(sQ(h), &tmap_q, bar_q, 64 * h, q0, hi, bi);
       int seq = 0;
       bool ok = true;
       auto load = [&](const CUtensorMap* map, int tile, int half) {
@@ -146,11 +151,11 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tma_load_4d(sSlot(slot), map, bar_full(slot), 64 * half, k_begin + tile * 128, hi, bi);
         ++seq;
       };
-      for (int h = 0; h < 2 && ok; ++h) load(&tmap_k, 0, h);
+      for (int h = 0; h < nh && ok; ++h) load(&tmap_k, 0, h);
       for (int j = 0; j < n_t && ok; ++j) {
         if (j + 1 < n_t)
-          for (int h = 0; h < 2 && ok; ++h) load(&tmap_k, j + 1, h);
-        for (int h = 0; h < 2 && ok; ++h) load(&tmap_v, j, h);
+          for (int h = 0; h < nh && ok; ++h) load(&tmap_k, j + 1, h);
+        for (int h = 0; h < nh && ok; ++h) load(&tmap_v, j, h);
       }
     }
   } else if (warp == kIssuerWarp) {
@@ -163,9 +168,10 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint64_t dk_slot0 = make_sdesc(sSlot(0), 16, 1024), dv_slot0 = make_sdesc(sSlot(0), 128 * 128, 1024);
       constexpr uint64_t kSlotStep = kTileBytes >> 4;   // descriptor address field counts 16-byte units
       int seq = 0;
+      const int nh = BIAS ? prm.n_halves : 2;
       bool ok = mbar_wait(bar_q, 0, &abort_flag, prm.status, BAR_Q);
       auto issue_s = [&]() {
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < nh && ok; ++h) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) return;
           tc_fence_after();
@@ -187,7 +193,7 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!(ok = mbar_wait(bar_p, j & 1, &abort_flag, prm.status, BAR_P))) break;
         tc_fence_after();
         // O_lo, O_hi of this key tile start from zero (the fold warps took the previous ones into their registers)
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < nh && ok; ++h) {
           const int slot = seq % kSlots;
           if (!(ok = mbar_wait(bar_full(slot), (seq / kSlots) & 1, &abort_flag, prm.status, BAR_FULL))) break;
           tc_fence_after();
@@ -207,6 +213,11 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int qi = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float c = prm.scale_log2;
+    const bool two_halves = BIAS ? prm.n_halves == 2 : true;   // (warp-uniform: tcgen05.ld is collective; unbiased problems here are wide)
+    constexpr bool has_bias = BIAS;
+    // with a bias the scores are moved to the log2 domain at once (s c + b log2 e) and the scale below becomes 1
+    const float cc = has_bias ? 1.f : c;
+    const float* bias_row = has_bias ? prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(qi, prm.n_ctx - 1)) * prm.bsq : nullptr;
     float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;   // zsum: this thread's 32 key columns only
     float o_run[32];        // running sums of output columns 16 cq ... (first 16) and 64 + 16 cq ... (last 16), relative to m_ref
 #pragma unroll
@@ -217,10 +228,14 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto take_o = [&]() {
       uint32_t r0[16], r1[16];
       tmem_ld16(tO + lane_off + 16 * cq, r0);
-      tmem_ld16(tO + 64 + lane_off + 16 * cq, r1);
+      if (two_halves) tmem_ld16(tO + 64 + lane_off + 16 * cq, r1);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) { o_run[i] += __uint_as_float(r0[i]); o_run[16 + i] += __uint_as_float(r1[i]); }
+      for (int i = 0; i < 16; ++i) o_run[i] += __uint_as_float(r0[i]);
+      if (two_halves) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o_run[16 + i] += __uint_as_float(r1[i]);
+      }
     };
 
     for (int j = 0; j < n_t; ++j) {
@@ -237,6 +252,14 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_before();
       mbar_arrive_warp(bar_sfree, lane);        // S may be overwritten with the next tile's scores
       const int k0 = k_begin + j * 128 + 32 * cq;           // first (local) key of this thread's columns
+      if constexpr (BIAS) {
+        const float* bp = bias_row + static_cast<int64_t>(k0 + koff) * prm.bsk;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float b = (k0 + i < k_end) ? bp[i * prm.bsk] : 0.f;
+          sv[i] = fmaf(sv[i], c, b * 1.4426950408889634f);
+        }
+      }
       const bool tail = k_begin + j * 128 + 128 > k_end;
       const bool diag = prm.is_causal && (k_begin + j * 128 + koff + 127 > q0);
       if (tail || diag) {
@@ -257,7 +280,7 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_arrive_warp(bar_row(qd), lane);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), j & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
       float tmax = fmaxf(fmaxf(row_max[j & 1][0][row], row_max[j & 1][1][row]), fmaxf(row_max[j & 1][2][row], row_max[j & 1][3][row]));
-      tmax *= c;
+      tmax *= cc;
       m_true = fmaxf(m_true, tmax);
       // the same decision in all four threads of the row (same tmax, same m_ref)
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
@@ -273,8 +296,8 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        const float p0 = fast_exp2(fmaf(sv[i], c, -m_use));
-        const float p1 = fast_exp2(fmaf(sv[i + 1], c, -m_use));
+        const float p0 = fast_exp2(fmaf(sv[i], cc, -m_use));
+        const float p1 = fast_exp2(fmaf(sv[i + 1], cc, -m_use));
         ps[(i >> 1) & 3] += p0 + p1;
         pk[i >> 1] = pack2<T>(p0, p1);
       }
@@ -343,8 +366,9 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 }  // namespace
 
 bool fold_tcw_supported(int dtype, int head_dim, bool has_bias) {
-  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim > 64 && head_dim <= 128 && head_dim % 8 == 0 && !has_bias &&
-         fold_tc_supported(dtype, 64, false);
+  // wide heads, and biased problems of any head dim up to 128 (unbiased ones up to 64 have their own kernel)
+  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0 &&
+         (head_dim > 64 || has_bias) && fold_tc_supported(dtype, 64, false);
 }
 
 int fold_tcw(const FoldParams& p, int dtype, cudaStream_t st) {
@@ -362,14 +386,18 @@ int fold_tcw(const FoldParams& p, int dtype, cudaStream_t st) {
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.heads = p.heads; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
   prm.n_keys = p.n_keys; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale_log2 = p.scale_log2;
+  prm.n_halves = p.head_dim > 64 ? 2 : 1;
+  prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk;
   dim3 grid(static_cast<unsigned>((p.q_len + 127) / 128), static_cast<unsigned>(p.n_parts), static_cast<unsigned>(p.bh));
-  if (dtype == ELSA_F16) {
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tcw_kernel<__half>), kFoldWSmem)) != ELSA_OK) return rc;
-    fold_tcw_kernel<__half><<<grid, kThreads, kFoldWSmem, st>>>(mq, mk, mv, prm);
-  } else {
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tcw_kernel<__nv_bfloat16>), kFoldWSmem)) != ELSA_OK) return rc;
-    fold_tcw_kernel<__nv_bfloat16><<<grid, kThreads, kFoldWSmem, st>>>(mq, mk, mv, prm);
-  }
+  auto launch = [&](auto kernel) -> int {
+    const int r = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kFoldWSmem);
+    if (r != ELSA_OK) return r;
+    kernel<<<grid, kThreads, kFoldWSmem, st>>>(mq, mk, mv, prm);
+    return ELSA_OK;
+  };
+  if (dtype == ELSA_F16) rc = p.bias ? launch(&fold_tcw_kernel<__half, true>) : launch(&fold_tcw_kernel<__half, false>);
+  else rc = p.bias ? launch(&fold_tcw_kernel<__nv_bfloat16, true>) : launch(&fold_tcw_kernel<__nv_bfloat16, false>);
+  if (rc != ELSA_OK) return rc;
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }

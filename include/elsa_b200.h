@@ -81,9 +81,9 @@ int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream);
 int elsa_debug_fma_rate(float* sink, int blocks, int64_t iters, int packed, void* stream);
 /* number of kernels this library has launched in this process so far (all threads, all streams) */
 int64_t elsa_kernel_launches(void);
-/* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run.  Covered: head dim
- * a multiple of 8 up to 128 for fp16 and bf16 inputs, up to 64 for fp32 inputs; at least 512 tokens; no bias (and,
- * backward, no dbias). */
+/* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run.  Covered, from 512
+ * tokens on: fp16 and bf16 inputs with a head dim that is a multiple of 8 up to 128, with or without a bias (and its
+ * gradient); fp32 inputs with a head dim that is a multiple of 8 up to 64 and no bias. */
 int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward);
 
 /* ---------------------------------------------------------------------------------------

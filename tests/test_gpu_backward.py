@@ -74,6 +74,12 @@ CASES = [
     (1, 2, 640, 128, F16, False, None),
     (1, 2, 777, 96, BF16, True, None),
     (2, 1, 1030, 72, F16, True, None),
+    # biased problems on the tensor cores, with the bias gradient (16-bit inputs)
+    (2, 2, 640, 64, F16, False, "bhnn"),
+    (2, 3, 600, 32, BF16, False, "1hnn"),
+    (1, 2, 777, 96, F16, True, "hnn"),
+    (2, 2, 520, 128, BF16, False, "b1nn"),
+    (1, 2, 1030, 64, F16, True, "nn"),
 ]
 
 
