@@ -17,11 +17,13 @@ pytestmark = pytest.mark.gpu
 F32, F16, BF16 = torch.float32, torch.float16, torch.bfloat16
 
 
-@pytest.mark.parametrize("dtype,n,bounds", [(F32, 300, [0, 100, 300]), (F16, 1500, [0, 640, 1100, 1500]),
-                                            (BF16, 1024, [0, 512, 1024]), (F16, 200, [0, 64, 200])])
+@pytest.mark.parametrize("dtype,n,bounds,d", [(F32, 300, [0, 100, 300], 64), (F16, 1500, [0, 640, 1100, 1500], 64),
+                                              (BF16, 1024, [0, 512, 1024], 64), (F16, 200, [0, 64, 200], 64),
+                                              (F16, 1500, [0, 640, 1100, 1500], 128), (BF16, 1024, [0, 512, 1024], 32),
+                                              (F32, 1024, [0, 384, 1024], 32)])
 @pytest.mark.parametrize("causal", [False, True])
-def test_shards_merge_to_full_attention(dtype, n, bounds, causal):
-    b, h, d = 1, 2, 64
+def test_shards_merge_to_full_attention(dtype, n, bounds, d, causal):
+    b, h = 1, 2
     q, k, v = (U.seeded((b, h, n, d), dtype, 90 + i).cuda() for i in range(3))
     state = None
     for k0, k1 in zip(bounds[:-1], bounds[1:]):
@@ -38,16 +40,19 @@ def test_shards_merge_to_full_attention(dtype, n, bounds, causal):
     assert (lse - lse_full).abs().max().item() <= (2e-5 if dtype == F32 else 5e-3)
 
 
-@pytest.mark.parametrize("dtype,n,bounds", [(F32, 300, [0, 100, 300]),            # FP32-FMA kernels, ragged shards
-                                            (F16, 1500, [0, 640, 1100, 1500]),    # tcgen05 kernel, offsets off the 128 grid
-                                            (BF16, 1024, [0, 512, 1024]),
-                                            (F16, 640, [0, 0, 640]),              # an empty shard
-                                            (F16, 200, [0, 64, 200])])            # 16-bit below the tensor-core size
+@pytest.mark.parametrize("dtype,n,bounds,d", [(F32, 300, [0, 100, 300], 64),            # FP32-FMA kernels, ragged shards
+                                              (F16, 1500, [0, 640, 1100, 1500], 64),    # tcgen05 kernel, offsets off the 128 grid
+                                              (BF16, 1024, [0, 512, 1024], 64),
+                                              (F16, 640, [0, 0, 640], 64),              # an empty shard
+                                              (F16, 200, [0, 64, 200], 64),             # 16-bit below the tensor-core size
+                                              (F32, 1024, [0, 384, 1024], 64),          # fp32 on the tensor cores, ragged shards
+                                              (F16, 1500, [0, 640, 1100, 1500], 128),   # wide-head kernels
+                                              (BF16, 1024, [0, 512, 1024], 96)])
 @pytest.mark.parametrize("causal", [False, True])
-def test_shard_backward_sums_to_full_backward(dtype, n, bounds, causal):
+def test_shard_backward_sums_to_full_backward(dtype, n, bounds, d, causal):
     """C ABI elsa_twopass_backward_shard per K/V shard (all on one device): the fp32 dQ contributions add up to the
     unsharded dQ, and the shards' dK / dV are the corresponding rows of the unsharded dK / dV."""
-    b, h, d = 1, 2, 64
+    b, h = 1, 2
     q, k, v, do = (U.seeded((b, h, n, d), dtype, 190 + i).cuda() for i in range(4))
     out, rm, rz = E.twopass_attention_with_state(q, k, v, is_causal=causal)[:3]
     dq_f, dk_f, dv_f = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz, is_causal=causal)[:3]
