@@ -47,6 +47,8 @@ WORKLOADS = {
     "fp32_4k": (1, 8, 4096, 64, "float32", False),
     "small": (1, 8, 2048, 64, "float16", False),
     "prof4k": (1, 8, 4096, 64, "float16", False),      # ncu capture size: same kernels, a few hundred MB on the device
+    "d128_8k": (1, 8, 8192, 128, "float16", False),    # head dim 128: the wide-head tensor-core kernels
+    "bias_4k": (1, 8, 4096, 64, "float16", False, "bias"),   # a long biased problem: the same kernels with bias / dbias
 }
 MIN_REGION_S = 2.0        # the timed region of the headline number lasts at least this long
 
@@ -719,7 +721,7 @@ def main():
                 extras["phase2"] = {"error": str(exc)[:200]}
             fma = extras["fp32_fma_peak"].get("tflops")
             others = {}
-            for name in ("causal_bf16", "fp32_1k", "vit_4097", "swin_s1", "swin_s4"):
+            for name in ("causal_bf16", "fp32_1k", "vit_4097", "swin_s1", "swin_s4", "d128_8k", "bias_4k"):
                 try:
                     w2 = Workload(name, dev)
                     for i in range(3):

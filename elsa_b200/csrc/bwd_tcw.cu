@@ -258,28 +258,56 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int kb = j * 128 + 32 * cq;                   // first (local) key of this thread's columns
         const bool masked = (j * 128 + 128 > NK) || (prm.is_causal && (j * 128 + koff + 127 > q0));
         const int lim = prm.is_causal ? min(NK - 1, qi - koff) : NK - 1;   // last admissible (local) key of this row
+        float ab[32];                                       // bias log2(e) - LSE of this thread's 32 keys
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a0 = nlse, a1 = nlse;
-          if constexpr (BIAS) {
-            // bias in natural-log units: s c + b log2(e) - LSE; keys beyond the row's last admissible one are masked below
-            const int64_t ko = static_cast<int64_t>(kb + koff + i) * prm.bsk;
-            if (kb + i < NK) a0 = fmaf(bias_row[ko], 1.4426950408889634f, nlse);
-            if (kb + i + 1 < NK) a1 = fmaf(bias_row[ko + prm.bsk], 1.4426950408889634f, nlse);
+        for (int i = 0; i < 32; ++i) ab[i] = nlse;
+        bool vec = false;
+        if constexpr (BIAS) {
+          // bias in natural-log units: s c + b log2(e) - LSE; keys beyond the row's last admissible one are masked below
+          const float* bp = bias_row + static_cast<int64_t>(kb + koff) * prm.bsk;
+          vec = prm.bsk == 1 && kb + 32 <= NK && (reinterpret_cast<uintptr_t>(bp) & 31u) == 0;
+          if (vec) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float b8[8];
+              ld_global_v8(bp + 8 * g, b8);      // whole 32-byte sectors: see fold_tcw.cu
+#pragma unroll
+              for (int e = 0; e < 8; ++e) ab[8 * g + e] = fmaf(b8[e], 1.4426950408889634f, nlse);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kb + i < NK) ab[i] = fmaf(bp[i * prm.bsk], 1.4426950408889634f, nlse);
           }
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a0));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), c, a1));
-          if (masked && kb + i > lim) p0 = 0.f;
-          if (masked && kb + i + 1 > lim) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rp[i]) + nd), d1 = p1 * (__uint_as_float(rp[i + 1]) + nd);
-          pk[i >> 1] = pack2<T>(d0, d1);
-          if constexpr (BIAS) {
-            // dbias = dS (every (query, key) pair is visited exactly once by this kernel); pairs that the causal rule or
-            // the sequence length excludes are left as the caller zeroed them
-            if (dbias_row && qi < N) {
-              const int64_t ko = static_cast<int64_t>(kb + koff + i) * prm.dsk;
-              if (kb + i <= lim) { if (prm.dbias_atomic) atomicAdd(dbias_row + ko, d0); else dbias_row[ko] = d0; }
-              if (kb + i + 1 <= lim) { if (prm.dbias_atomic) atomicAdd(dbias_row + ko + prm.dsk, d1); else dbias_row[ko + prm.dsk] = d1; }
+        }
+        float dsv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, ab[i]));
+          if (masked && kb + i > lim) p = 0.f;
+          dsv[i] = p * (__uint_as_float(rp[i]) + nd);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) pk[i >> 1] = pack2<T>(dsv[i], dsv[i + 1]);
+        if constexpr (BIAS) {
+          // dbias = dS (every (query, key) pair is visited exactly once by this kernel); pairs that the causal rule or
+          // the sequence length excludes hold zeros here, as the caller zeroed them
+          if (dbias_row && qi < N) {
+            float* dp = dbias_row + static_cast<int64_t>(kb + koff) * prm.dsk;
+            if (!prm.dbias_atomic && prm.dsk == 1 && kb + 32 <= NK && (reinterpret_cast<uintptr_t>(dp) & 31u) == 0) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                float d8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) d8[e] = dsv[8 * g + e];
+                st_global_v8(dp + 8 * g, d8);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (kb + i > lim) continue;
+                if (prm.dbias_atomic) atomicAdd(dp + i * prm.dsk, dsv[i]); else dp[i * prm.dsk] = dsv[i];
+              }
             }
           }
         }

@@ -254,10 +254,22 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int k0 = k_begin + j * 128 + 32 * cq;           // first (local) key of this thread's columns
       if constexpr (BIAS) {
         const float* bp = bias_row + static_cast<int64_t>(k0 + koff) * prm.bsk;
+        if (prm.bsk == 1 && k0 + 32 <= k_end && (reinterpret_cast<uintptr_t>(bp) & 31u) == 0) {
+          // the thread's 128 bytes of the bias row as four whole sectors (a warp's 32 rows are 32 different lines:
+          // 4-byte loads would fetch every sector eight times)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float b = (k0 + i < k_end) ? bp[i * prm.bsk] : 0.f;
-          sv[i] = fmaf(sv[i], c, b * 1.4426950408889634f);
+          for (int g = 0; g < 4; ++g) {
+            float b8[8];
+            ld_global_v8(bp + 8 * g, b8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[8 * g + e] = fmaf(sv[8 * g + e], c, b8[e] * 1.4426950408889634f);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float b = (k0 + i < k_end) ? bp[i * prm.bsk] : 0.f;
+            sv[i] = fmaf(sv[i], c, b * 1.4426950408889634f);
+          }
         }
       }
       const bool tail = k_begin + j * 128 + 128 > k_end;

@@ -273,6 +273,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
+// 32-byte global loads / stores (one whole sector per thread; the address must be 32-byte aligned)
+__device__ __forceinline__ void ld_global_v8(const float* p, float (&r)[8]) {
+  asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]) : "l"(p));
+}
+__device__ __forceinline__ void st_global_v8(float* p, const float (&r)[8]) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]) : "memory");
+}
+
 // ---- fp32 operands as a few 16-bit planes -----------------------------------------------------------------------
 // ELSA_FP32_PLANES == 3: x = a0 + a1 + a2 with three bf16 terms (8 + 8 + 8 significant bits, the full exponent range;
 //   six cross products of weight >= 2^-16 per contraction).
