@@ -85,7 +85,7 @@ static bool tcw_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, un
   return n_ctx >= 512 && fold_tcw_supported(dtype, head_dim, has_bias);
 }
 
-// fp32 on the tensor cores: head dim 64, no bias, and long enough that 128-row tiles fill the machine better than the
+// fp32 on the tensor cores: head dim up to 64, and long enough that 128-row tiles fill the machine better than the
 // FP32-FMA kernel's 64-row tiles do
 static bool tc3_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
   if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
@@ -490,7 +490,7 @@ static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, un
   return n_ctx >= 512 && bwd_tc_supported(dtype, head_dim, has_bias);
 }
 
-// fp32 on the tensor cores (16-bit planes per operand): head dim up to 64, no bias, no dbias
+// fp32 on the tensor cores (16-bit planes per operand): head dim up to 64, with or without a bias (and its gradient)
 static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
   if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
   return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
@@ -541,7 +541,7 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
-  const bool use_tc3 = dbias == nullptr && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  const bool use_tc3 = (dbias == nullptr || bias != nullptr) && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
   // (the wide-head kernels also take biased problems, with or without a bias gradient)
   const bool use_tcw = !use_tc && !use_tc3 && (dbias == nullptr || bias != nullptr) &&
                        tcw_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);

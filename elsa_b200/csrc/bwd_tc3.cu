@@ -62,6 +62,9 @@ struct Bwd3Params {
   int n_keys, key_offset;                       // K/V rows of this launch and the sequence index of the first one
   int head_dim;                                 // real columns of the gradients (<= 64; the planes are zero-padded to 64)
   float scale, scale_log2;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;      // additive bias [.., N, N] (natural-log units) or null
+  float* dbias; int64_t dsb, dsh, dsq, dsk;           // its gradient (same addressing; zeroed by the caller) or null
+  int dbias_atomic;                                   // a broadcast axis: contributions are added atomically
   int* status;                                  // the device's status word (mapped host memory)
 };
 
@@ -121,6 +124,7 @@ __device__ __forceinline__ float abs_max16(const float* x) {
 // Shared memory: Q planes, dO planes (resident, 96 KB) | K ring, 6 slots of 16 KB (the planes of key tile j stay until
 // dQ_j has read them, while S of tile j+1 needs the next three) | V ring, 2 slots
 // ------------------------------------------------------------------------------------------------------------------
+template <bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -279,6 +283,14 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const float nlse = prm.nlse_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];   // q0 + 127 < n_pad
     const float nd = prm.nd_pad[static_cast<int64_t>(bh) * prm.n_pad + qi];
     float inv_r = 1.f;                         // 1 / (r s_k) of the tile whose dQ_j is in flight
+    const float* bias_row = nullptr;
+    float* dbias_row = nullptr;
+    if constexpr (BIAS) {
+      const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
+      const int qrow = min(qi, N - 1);         // rows beyond N are never stored: any valid address will do
+      bias_row = prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(qrow) * prm.bsq;
+      if (prm.dbias) dbias_row = prm.dbias + bi * prm.dsb + hi * prm.dsh + static_cast<int64_t>(qrow) * prm.dsq;
+    }
     float dq_run[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) dq_run[i] = 0.f;
@@ -306,11 +318,52 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int kb = j * 128 + 32 * cq;                   // first (local) key of this thread's columns
         const bool masked = (j * 128 + 128 > NK) || (prm.is_causal && (j * 128 + koff + 127 > q0));
         const int lim = prm.is_causal ? min(NK - 1, qi - koff) : NK - 1;   // last admissible (local) key of this row
+        float ab[32];                                       // bias log2(e) - LSE of this thread's 32 keys
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ab[i] = nlse;
+        if constexpr (BIAS) {
+          const float* bp = bias_row + static_cast<int64_t>(kb + koff) * prm.bsk;
+          if (prm.bsk == 1 && kb + 32 <= NK && (reinterpret_cast<uintptr_t>(bp) & 31u) == 0) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float b8[8];
+              ld_global_v8(bp + 8 * g, b8);      // whole 32-byte sectors (a warp's 32 rows are 32 different lines)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) ab[8 * g + e] = fmaf(b8[e], 1.4426950408889634f, nlse);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kb + i < NK) ab[i] = fmaf(bp[i * prm.bsk], 1.4426950408889634f, nlse);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nlse));
+          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), c, ab[i]));
           if (masked && kb + i > lim) p = 0.f;
           ds[i] = p * fmaf(__uint_as_float(rp[i]), idp, nd);
+        }
+        if constexpr (BIAS) {
+          // dbias = dS (every (query, key) pair is visited exactly once by this kernel); pairs that the causal rule or
+          // the sequence length excludes hold zeros here, as the caller zeroed them
+          if (dbias_row && qi < N) {
+            float* dp = dbias_row + static_cast<int64_t>(kb + koff) * prm.dsk;
+            if (!prm.dbias_atomic && prm.dsk == 1 && kb + 32 <= NK && (reinterpret_cast<uintptr_t>(dp) & 31u) == 0) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                float d8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) d8[e] = ds[8 * g + e];
+                st_global_v8(dp + 8 * g, d8);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (kb + i > lim) continue;
+                if (prm.dbias_atomic) atomicAdd(dp + i * prm.dsk, ds[i]); else dp[i * prm.dsk] = ds[i];
+              }
+            }
+          }
         }
       }
       float r_scale = 1.f;
@@ -360,6 +413,7 @@ bwd3_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 // dK, dV: one CTA per 128-row key tile
 // TMEM columns: S^T [0,64) dP^T [64,128) P^T planes [128,224) dS^T planes [224,320) dV_i [320,384) dK_i [384,448)
 // ------------------------------------------------------------------------------------------------------------------
+template <bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -530,6 +584,12 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const float idp = k2 / (s_do * s_v);
     const float inv_v = k2 / s_do;                      // dV_i' = 2^kLog2Unit s_do dV_i
     float inv_r = 1.f;                                  // 1 / (r s_q) of the tile whose dK_i is in flight
+    // bias[query, key] of this thread's key column; the query offset is added per element
+    const float* bias_col = nullptr;
+    if constexpr (BIAS) {
+      const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
+      bias_col = prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(key_seq, N - 1)) * prm.bsk;
+    }
     float dv_run[16], dk_run[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) { dv_run[i] = 0.f; dk_run[i] = 0.f; }
@@ -576,7 +636,11 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = 4 * g + e;
-            float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, nle[e] + kLog2Unit));
+            float a = nle[e] + kLog2Unit;
+            if constexpr (BIAS) {
+              if (key_ok && qc + i < N) a = fmaf(bias_col[static_cast<int64_t>(qc + i) * prm.bsq], 1.4426950408889634f, a);
+            }
+            float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a));
             if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) pv = 0.f;
             p[i] = pv;
             ds[i] = pv * fmaf(__uint_as_float(rp[i]), idp, nde[e] * k2);
@@ -673,7 +737,7 @@ int64_t bwd_tc3_workspace_bytes(int bh, int n_ctx, int n_keys) {
 
 int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m, const float* row_z, void* workspace,
             cudaStream_t st) {
-  if (!bwd_tc3_supported(ELSA_F32, p.head_dim, p.bias != nullptr) || p.dbias) return ELSA_ERR_UNSUPPORTED;
+  if (!bwd_tc3_supported(ELSA_F32, p.head_dim, p.bias != nullptr) || (p.dbias && !p.bias)) return ELSA_ERR_UNSUPPORTED;
   const int N = p.n_ctx, NK = p.n_keys, bh = p.bh, batch = bh / p.heads;
   const int n_pad = static_cast<int>(align_up(N, 128));
   const int64_t vec_bytes = align_up(static_cast<int64_t>(bh) * n_pad * 4, 256);
@@ -717,24 +781,27 @@ int bwd_tc3(const BwdParams& p, const void* out, Strides os, const float* row_m,
   prm.n_ctx = N; prm.n_pad = n_pad; prm.bh = bh; prm.heads = p.heads; prm.is_causal = p.is_causal;
   prm.n_keys = NK; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
+  prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk;
+  prm.dbias = p.dbias; prm.dsb = p.dsb; prm.dsh = p.dsh; prm.dsq = p.dsq; prm.dsk = p.dsk; prm.dbias_atomic = p.dbias_atomic;
   if (NK > 0) {
     if ((rc = make_tmap_rows64(&mk128, k3 + kPlaneHeader, kPlaneDtype, NK, bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
     if ((rc = make_tmap_rows64(&mv128, v3 + kPlaneHeader, kPlaneDtype, NK, bh, kPlanes, sk, 128)) != ELSA_OK) return rc;
   } else {
     mk128 = mv128 = mq64;   // never dereferenced: no key tile is visited
   }
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dq_kernel), kDqSmem)) != ELSA_OK) return rc;
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&bwd3_dkv_kernel), kKvSmem)) != ELSA_OK) return rc;
-  {
-    const dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
-    bwd3_dq_kernel<<<grid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk128, mv128, prm);
-    ELSA_LAUNCH_CHECK();
-  }
-  if (NK > 0) {
-    const dim3 grid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
-    bwd3_dkv_kernel<<<grid, kThreads, kKvSmem, st>>>(mq64, mdo64, mk128, mv128, prm);
-    ELSA_LAUNCH_CHECK();
-  }
+  const dim3 qgrid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(bh));
+  const dim3 kgrid(static_cast<unsigned>((NK + 127) / 128), static_cast<unsigned>(bh));
+  auto launch = [&](auto dq_kernel, auto dkv_kernel) -> int {
+    int r;
+    if ((r = ensure_dynamic_smem(reinterpret_cast<const void*>(dq_kernel), kDqSmem)) != ELSA_OK) return r;
+    if ((r = ensure_dynamic_smem(reinterpret_cast<const void*>(dkv_kernel), kKvSmem)) != ELSA_OK) return r;
+    dq_kernel<<<qgrid, kThreads, kDqSmem, st>>>(mq128, mdo128, mk128, mv128, prm);
+    if (NK > 0) dkv_kernel<<<kgrid, kThreads, kKvSmem, st>>>(mq64, mdo64, mk128, mv128, prm);
+    return ELSA_OK;
+  };
+  rc = p.bias ? launch(&bwd3_dq_kernel<true>, &bwd3_dkv_kernel<true>) : launch(&bwd3_dq_kernel<false>, &bwd3_dkv_kernel<false>);
+  if (rc != ELSA_OK) return rc;
+  ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }
 

@@ -73,6 +73,8 @@ struct Fold3Params {
   int n_keys, key_offset, head_dim;
   float scale_log2;
   const uint32_t* amax_q; const uint32_t* amax_k; const uint32_t* amax_v;   // the plane headers
+  const float* bias; int64_t bsb, bsh, bsq, bsk;   // additive bias [.., N, N] (natural-log units) or null
+  int heads;
   int* status;
 };
 
@@ -181,6 +183,7 @@ split_planes_kernel(const __grid_constant__ SplitJobs jobs, int heads, int bh, i
   for (int p = 0; p < kPlanes; ++p) *reinterpret_cast<uint2*>(planes + p * plane_elems + off) = make_uint2(w0[p], w1[p]);
 }
 
+template <bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Fold3Params prm) {
@@ -324,6 +327,13 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     // the scores arrive multiplied by the plane scales of q and k (powers of two): taken out with the softmax scale
     const float c = prm.scale_log2 / (plane_scale(*prm.amax_q) * plane_scale(*prm.amax_k));
+    // with a bias the scores are moved to the log2 domain at once (s c + b log2 e) and the scale below becomes 1
+    const float cc = BIAS ? 1.f : c;
+    const float* bias_row = nullptr;
+    if constexpr (BIAS) {
+      const int bi = bh / prm.heads, hi = bh - bi * prm.heads;
+      bias_row = prm.bias + bi * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(qi, prm.n_ctx - 1)) * prm.bsq;
+    }
     float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, zsum = 0.f;   // zsum: this thread's 32 columns only, times kPlaneUnit
     float o_run[16];                                        // running sum of O over the key tiles (columns 16 cq ...), relative to m_ref
 #pragma unroll
@@ -353,6 +363,25 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_before();
       mbar_arrive_warp(bar_sfree, lane);        // S may be overwritten with the next tile's scores
       const int k0 = k_begin + j * 128 + 32 * cq;           // first (local) key of this thread's columns
+      if constexpr (BIAS) {
+        const float* bp = bias_row + static_cast<int64_t>(k0 + koff) * prm.bsk;
+        if (prm.bsk == 1 && k0 + 32 <= k_end && (reinterpret_cast<uintptr_t>(bp) & 31u) == 0) {
+          // the thread's 128 bytes of the bias row as four whole sectors (a warp's 32 rows are 32 different lines)
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float b8[8];
+            ld_global_v8(bp + 8 * g, b8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[8 * g + e] = fmaf(sv[8 * g + e], c, b8[e] * 1.4426950408889634f);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float b = (k0 + i < k_end) ? bp[i * prm.bsk] : 0.f;
+            sv[i] = fmaf(sv[i], c, b * 1.4426950408889634f);
+          }
+        }
+      }
       const bool tail = k_begin + j * 128 + 128 > k_end;
       const bool diag = prm.is_causal && (k_begin + j * 128 + koff + 127 > q0);
       if (tail || diag) {
@@ -373,7 +402,7 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_arrive_warp(bar_row(qd), lane);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_row(qd), j & 1, &abort_flag, prm.status, BAR_ROW))) { alive = false; break; }
       float tmax = fmaxf(fmaxf(row_max[j & 1][0][row], row_max[j & 1][1][row]), fmaxf(row_max[j & 1][2][row], row_max[j & 1][3][row]));
-      tmax *= c;
+      tmax *= cc;
       m_true = fmaxf(m_true, tmax);
       // the same decision in all four threads of the row (same tmax, same m_ref)
       const bool move = tmax > m_ref + kRescaleThreshold;   // also true for the first admissible tile (m_ref = -inf)
@@ -391,8 +420,8 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         // ex2.approx: 2 units in the last place, i.e. 2.4e-7 relative on a weight
-        sv[i] = fast_exp2(fmaf(sv[i], c, nm));
-        sv[i + 1] = fast_exp2(fmaf(sv[i + 1], c, nm));
+        sv[i] = fast_exp2(fmaf(sv[i], cc, nm));
+        sv[i + 1] = fast_exp2(fmaf(sv[i + 1], cc, nm));
         ps[(i >> 1) & 3] += sv[i] + sv[i + 1];
       }
       zsum = zsum * alpha + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
@@ -470,8 +499,8 @@ fold_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 }  // namespace
 
 bool fold_tc3_supported(int dtype, int head_dim, bool has_bias) {
-  return dtype == ELSA_F32 && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && !has_bias &&
-         fold_tc_supported(ELSA_BF16, 64, false);
+  (void)has_bias;   // the fold warps read an additive bias from global memory (BIAS variant of the kernel)
+  return dtype == ELSA_F32 && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && fold_tc_supported(ELSA_BF16, 64, false);
 }
 
 // a tensor's plane buffer: a header (kAmaxBlocks partial maxima and the final one) + [kPlanes][bh][rows][64] 16-bit
@@ -533,10 +562,12 @@ int fold_tc3(const FoldParams& p, cudaStream_t st) {
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
   prm.n_keys = p.n_keys; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.scale_log2 = p.scale_log2;
-  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&fold_tc3_kernel), kFold3Smem);
+  prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk; prm.heads = p.heads;
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(p.bias ? &fold_tc3_kernel<true> : &fold_tc3_kernel<false>), kFold3Smem);
   if (rc != ELSA_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.q_len + 127) / 128), static_cast<unsigned>(p.n_parts), static_cast<unsigned>(p.bh));
-  fold_tc3_kernel<<<grid, kThreads, kFold3Smem, st>>>(mq, mk, mv, prm);
+  if (p.bias) fold_tc3_kernel<true><<<grid, kThreads, kFold3Smem, st>>>(mq, mk, mv, prm);
+  else fold_tc3_kernel<false><<<grid, kThreads, kFold3Smem, st>>>(mq, mk, mv, prm);
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
 }

@@ -80,6 +80,9 @@ CASES = [
     (1, 2, 777, 96, F16, True, "hnn"),
     (2, 2, 520, 128, BF16, False, "b1nn"),
     (1, 2, 1030, 64, F16, True, "nn"),
+    (2, 2, 640, 64, F32, False, "bhnn"),
+    (1, 3, 900, 40, F32, True, "hnn"),
+    (2, 2, 1024, 32, F32, False, "b1nn"),
 ]
 
 

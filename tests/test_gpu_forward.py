@@ -145,6 +145,9 @@ CASES = [
     (1, 2, 777, 96, F16, True, "hnn", 512, None),
     (2, 2, 520, 128, BF16, False, "b1nn", None, None),
     (1, 2, 1030, 64, F16, True, "nn", 512, None),
+    (2, 2, 640, 64, F32, False, "bhnn", None, None),
+    (1, 3, 900, 40, F32, True, "hnn", None, None),
+    (2, 2, 1024, 32, F32, False, "b1nn", None, None),
 ]
 
 
@@ -324,8 +327,8 @@ def test_fp32_tensor_core_fold_matches_the_fma_fold_and_fp64(b, h, n, causal, bl
 
 def test_routing_of_small_head_dims_and_fp32():
     """Head dims up to 64 (multiples of 8) in fp16, bf16 and fp32, and head dims up to 128 in fp16 and bf16, take the
-    tcgen05 kernels from 512 tokens on, forward and backward, the 16-bit types also with a bias; biased fp32 problems,
-    fp32 head dims above 64 and short sequences stay on the FP32-FMA kernels."""
+    tcgen05 kernels from 512 tokens on, forward and backward, with or without a bias; fp32 head dims above 64 and short
+    sequences stay on the FP32-FMA kernels."""
     from elsa_b200 import _lib
     lib = _lib.load()
     f32, f16, bf16 = (_lib.dtype_code(t) for t in (F32, F16, BF16))
@@ -333,10 +336,11 @@ def test_routing_of_small_head_dims_and_fp32():
         for dt in (f32, f16, bf16):
             for d in (8, 32, 48, 64):
                 assert lib.elsa_uses_tensor_cores(dt, d, 640, 0, 0, backward) == 1, (dt, d, backward)
-            # head dims above 64 and biased problems: the 16-bit types have kernels for them, fp32 does not
-            for d in (72, 96, 128):
-                assert lib.elsa_uses_tensor_cores(dt, d, 640, 0, 0, backward) == (0 if dt == f32 else 1), (dt, d, backward)
-            for d in (32, 64, 96):
-                assert lib.elsa_uses_tensor_cores(dt, d, 640, 1, 0, backward) == (0 if dt == f32 else 1), (dt, d, backward)
+            # head dims above 64: the 16-bit types have kernels for them, fp32 does not; a bias changes nothing
+            for bias in (0, 1):
+                for d in (72, 96, 128):
+                    assert lib.elsa_uses_tensor_cores(dt, d, 640, bias, 0, backward) == (0 if dt == f32 else 1), (dt, d, backward)
+                for d in (32, 64):
+                    assert lib.elsa_uses_tensor_cores(dt, d, 640, bias, 0, backward) == 1, (dt, d, backward)
             assert lib.elsa_uses_tensor_cores(dt, 36, 640, 0, 0, backward) == 0      # not a multiple of 8
             assert lib.elsa_uses_tensor_cores(dt, 64, 200, 0, 0, backward) == 0      # short sequence
