@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(HERE, "libelsa_b200.so")
-SOURCES = ["api.cu", "phase2.cu", "fold_simt.cu", "bwd_simt.cu", "fold_tc.cu", "fold_tc3.cu", "fold_tcw.cu", "bwd_tc.cu", "bwd_tc3.cu", "bwd_tcw.cu", "peaks.cu"]
+SOURCES = ["api.cu", "phase2.cu", "fold_simt.cu", "bwd_simt.cu", "fold_tc.cu", "fold_tc3.cu", "fold_tcw.cu", "bwd_tc.cu", "bwd_tc3.cu", "bwd_tcw.cu", "win_tc.cu", "peaks.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

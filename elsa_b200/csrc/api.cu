@@ -416,6 +416,16 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
   // sequences of at most 64 tokens): phase 2 would merge one summary per row, so phase 1 finalises the rows itself,
   // with the same rounding points, and the summaries never travel through memory.
   if (!pl.tensor_cores && pl.n_parts == 1 && n_ctx <= 64 && !(flags & (ELSA_FLAG_SCAN_STEPS | ELSA_FLAG_TREE_MERGE))) {
+    // 16-bit inputs: two sequences per 128-row tensor-core tile, one launch (win_tc.cu)
+    if (!(flags & ELSA_FLAG_FORCE_SIMT) && !ref_round && win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) {
+      const Strides cs0 = contiguous_strides(heads, n_ctx, head_dim);
+      const int src = check_device_status();
+      if (src != ELSA_OK) return src;
+      const float sl2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
+      return win_tc_fwd(q, qs ? *qs : cs0, k, ks ? *ks : cs0, v, vs ? *vs : cs0, bias, bias_stride_b, bias_stride_h,
+                        bias_stride_q, bias_stride_k, out, os ? *os : cs0, row_m, row_z, dtype, summary_dtype, batch, heads,
+                        n_ctx, head_dim, sl2, st);
+    }
     return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, nullptr, nullptr,
                            nullptr, dtype, summary_dtype, batch, heads, n_ctx, head_dim, 0, n_ctx, pl.part_width, 1,
                            is_causal, flags, st, -1, 0, ref_round, qs, ks, vs, out, os, row_m, row_z);

@@ -416,7 +416,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
-                     int box_rows, int cols) {
+                     int box_rows, int cols, int box_batch) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ELSA_ERR_UNSUPPORTED;
   if ((st.b | st.h | st.r) % 8 != 0 || cols < 8 || cols > 128 || cols % 8 != 0 || st.r < cols || (reinterpret_cast<uintptr_t>(base) & 15u)) return ELSA_ERR_INVALID_ARGUMENT;
@@ -424,7 +424,7 @@ int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_ro
   // a size-1 axis may come with any stride (PyTorch reports arbitrary ones): give it a valid dummy
   const cuuint64_t sh = heads > 1 ? static_cast<cuuint64_t>(st.h) * 2 : 128, sb = batch > 1 ? static_cast<cuuint64_t>(st.b) * 2 : 128;
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st.r) * 2, sh, sb};
-  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, static_cast<cuuint32_t>(box_batch)};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == ELSA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

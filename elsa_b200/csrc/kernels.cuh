@@ -73,6 +73,12 @@ int device_status_word(int** dev_ptr, volatile int** host_ptr);
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);
 int fold_tc(const FoldParams& p, int dtype, cudaStream_t st);
 int debug_wait_timeout(unsigned long long limit_ns, cudaStream_t st);
+// sequences of at most 64 tokens (Swin windows), fp16 / bf16, on the tensor cores: two per tile, one launch (win_tc.cu)
+bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal);
+int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void* v, Strides vs, const float* bias,
+               int64_t bsb, int64_t bsh, int64_t bsq, int64_t bsk, void* out, Strides os, float* row_m, float* row_z,
+               int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, float scale_log2,
+               cudaStream_t st);
 // tcgen05 fold for fp16 / bf16 inputs with 64 < head dim <= 128 (fold_tcw.cu)
 bool fold_tcw_supported(int dtype, int head_dim, bool has_bias);
 int fold_tcw(const FoldParams& p, int dtype, cudaStream_t st);

@@ -350,9 +350,10 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 // 16-bit [B, H, n_rows, cols] view with element strides `st` (the elements of a row contiguous; cols a multiple of 8,
 // at most 128) as a 4-D map (innermost first: cols, n_rows, H, B), box 64 x box_rows x 1 x 1, 128-byte swizzle:
 // columns beyond `cols` and rows beyond n_rows read as zeros, so a narrower head dim lands in shared memory as a
-// zero-padded 64-column tile; a head dim above 64 is loaded as two such tiles (x = 0 and x = 64).  The strides must be multiples of 8 elements (16 bytes) and the base 16-byte aligned.
+// zero-padded 64-column tile; a head dim above 64 is loaded as two such tiles (x = 0 and x = 64).  box_batch = 2 takes
+// two batch entries of one head in one box (short sequences: two of them fill a 128-row tile).  The strides must be multiples of 8 elements (16 bytes) and the base 16-byte aligned.
 int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
-                     int box_rows, int cols = 64);
+                     int box_rows, int cols = 64, int box_batch = 1);
 // [n_mats][n_rows][64] fp32 tensor, box 32 x box_rows x 1 (two boxes cover the 64 columns), 128-byte swizzle
 int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int64_t n_mats, int box_rows);
 

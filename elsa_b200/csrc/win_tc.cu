@@ -1,0 +1,237 @@
+// Short sequences (49-token Swin windows and anything else of at most 64 tokens) on the 5th-generation tensor cores,
+// fp16 / bf16, head dim <= 64 (multiples of 8), optional additive bias, not causal: ONE launch, no partition summaries.
+//
+// A 128-row tcgen05 tile holds TWO sequences of the same head: one 4-D TMA box (64 columns x 64 rows x 1 head x 2
+// batch entries) lands both in shared memory, each zero-padded to 64 rows and 64 columns by the box, as one 128 x 64
+// operand tile.  One CTA (160 threads) per (pair of sequences, head):
+//
+//   warp 4 lane 0   TMA loads of the Q, K, V tiles; S = Q K^T (tcgen05.mma 128x128x16, only the two diagonal
+//                   64 x 64 blocks are meaningful); after the fold warps have delivered P: O = P V (128x64x16 x 8)
+//   warps 0-3       one thread per query row (rows 0-63: first sequence, 64-127: second): the row's own 64 scores from
+//                   TMEM, scale + bias (read from global memory), softmax in registers, P (16-bit) into TMEM with
+//                   zeros in the other sequence's columns, and after P V the row's output = O / z
+//
+// TMEM columns: S [0,128) O [128,192) P [192,256): two CTAs fit an SM.
+#include <type_traits>
+
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace elsa {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kTileBytes = 128 * 64 * 2;          // two 64 x 64 16-bit sequences
+constexpr int kWinSmem = 3 * kTileBytes + 1024;   // Q, K, V + alignment slack
+constexpr int kThreads = 160;
+constexpr uint32_t kTmemCols = 256;
+
+enum BarId { BAR_LOAD = 71, BAR_S = 72, BAR_P = 73, BAR_O = 74 };
+
+struct WinParams {
+  void* out; Strides os;
+  float* row_m; float* row_z;                   // [B*H, N] row state (log2 domain), or null
+  const float* bias; int64_t bsb, bsh, bsq, bsk;
+  int batch, heads, n_ctx, head_dim, summary_dtype;
+  float scale_log2;
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2)
+win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const WinParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b0 = blockIdx.x * 2, hi = blockIdx.y;
+  const int N = prm.n_ctx, d = prm.head_dim;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base, sK = smem_base + kTileBytes, sV = smem_base + 2 * kTileBytes;
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_load = bar0, bar_s = bar0 + 8, bar_p = bar0 + 16, bar_o = bar0 + 24;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tS = tmem_base, tO = tmem_base + 128, tP = tmem_base + 192;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------- loads and MMAs ----------------
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(bar_load, 3 * kTileBytes);
+      tma_load_4d(sQ, &tmap_q, bar_load, 0, 0, hi, b0);     // rows beyond N, columns beyond d, a batch entry beyond B: zeros
+      tma_load_4d(sK, &tmap_k, bar_load, 0, 0, hi, b0);
+      tma_load_4d(sV, &tmap_v, bar_load, 0, 0, hi, b0);
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // S = Q K^T : A, B K-major
+      constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // O = P V   : A in TMEM, B (V) MN-major
+      bool ok = mbar_wait(bar_load, 0, &abort_flag, prm.status, BAR_LOAD);
+      if (ok) {
+        tc_fence_after();
+        const uint64_t dq = make_sdesc(sQ, 16, 1024), dk = make_sdesc(sK, 16, 1024);
+        const int ksteps = (d + 15) / 16;                     // the columns beyond d are zeros: their K-steps add nothing
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tS, dq + 2 * ks, dk + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        mma_commit(bar_s);
+        ok = mbar_wait(bar_p, 0, &abort_flag, prm.status, BAR_P);
+      }
+      if (ok) {
+        tc_fence_after();
+        const uint64_t dv = make_sdesc(sV, 128 * 128, 1024);
+        mma_ts_x4<8, 128>(tO, tP, dv, idesc_o, 0u);
+        mma_ts_x4<8, 128>(tO, tP + 32, dv + 512, idesc_o, 1u);
+        mma_commit(bar_o);
+      }
+    }
+  } else {
+    // ---------------- fold warps: one thread per query row ----------------
+    const int row = warp * 32 + lane;                       // row of the tile == TMEM lane
+    const int seq = row >> 6, qi = row & 63;                // which of the two sequences, and the query index in it
+    const int b = b0 + seq;
+    const bool row_ok = b < prm.batch && qi < N;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const float c = prm.scale_log2;
+    bool alive = __all_sync(0xffffffffu, mbar_wait(bar_s, 0, &abort_flag, prm.status, BAR_S));
+    float z = 0.f, m = -CUDART_INF_F;
+    if (alive) {
+      tc_fence_after();
+      float sv[64];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tS + lane_off + 64 * seq, r0);            // the row's own sequence: the diagonal block
+        tmem_ld32(tS + lane_off + 64 * seq + 32, r1);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(r0[i]) * c; sv[32 + i] = __uint_as_float(r1[i]) * c; }
+      }
+      if (prm.bias && row_ok) {
+        const float* bp = prm.bias + static_cast<int64_t>(b) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(qi) * prm.bsq;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < N) sv[i] = fmaf(bp[i * prm.bsk], 1.4426950408889634f, sv[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        if (i >= N) sv[i] = -CUDART_INF_F;
+      float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+      for (int i = 4; i < 64; i += 4) {
+        mx[0] = fmaxf(mx[0], sv[i]); mx[1] = fmaxf(mx[1], sv[i + 1]);
+        mx[2] = fmaxf(mx[2], sv[i + 2]); mx[3] = fmaxf(mx[3], sv[i + 3]);
+      }
+      m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_use = (m == -CUDART_INF_F) ? 0.f : m;   // a row whose keys are all masked by the bias: p = 0 everywhere
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32], zero[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        const float p0 = fast_exp2(sv[i] - m_use), p1 = fast_exp2(sv[i + 1] - m_use);
+        ps[(i >> 1) & 3] += p0 + p1;
+        pk[i >> 1] = pack2<T>(p0, p1);
+      }
+      z = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) zero[i] = 0u;
+      // P of this row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other sequence's
+      tmem_st32(tP + lane_off + 32 * seq, pk);
+      tmem_st32(tP + lane_off + 32 * (1 - seq), zero);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(bar_p, lane);
+      alive = __all_sync(0xffffffffu, mbar_wait(bar_o, 0, &abort_flag, prm.status, BAR_O));
+    }
+    if (alive) {
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tO + lane_off, r0);
+      tmem_ld32(tO + lane_off + 32, r1);
+      tmem_wait_ld();
+      if (row_ok) {
+        const float inv = z > 0.f ? 1.f / z : 0.f;
+        T* dst = static_cast<T*>(prm.out) + static_cast<int64_t>(b) * prm.os.b + hi * prm.os.h + static_cast<int64_t>(qi) * prm.os.r;
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          if (i >= d) continue;
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float x = __uint_as_float(i + e < 32 ? r0[(i + e) & 31] : r1[(i + e) & 31]);
+            // the two-pass path stores the partition summary in the summary type before dividing: same rounding points
+            if (prm.summary_dtype == ELSA_F16) x = round_to<__half>(x);
+            else if (prm.summary_dtype == ELSA_BF16) x = round_to<__nv_bfloat16>(x);
+            o[e] = x * inv;
+          }
+          uint4 t;
+          t.x = pack2<T>(o[0], o[1]); t.y = pack2<T>(o[2], o[3]); t.z = pack2<T>(o[4], o[5]); t.w = pack2<T>(o[6], o[7]);
+          *reinterpret_cast<uint4*>(dst + i) = t;
+        }
+        if (prm.row_m) {
+          const int64_t ro = (static_cast<int64_t>(b) * prm.heads + hi) * N + qi;
+          prm.row_m[ro] = z > 0.f ? m : -CUDART_INF_F;
+          prm.row_z[ro] = z;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal) {
+  return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && n_ctx >= 1 &&
+         n_ctx <= 64 && !is_causal && fold_tc_supported(dtype, 64, false);
+}
+
+// q, k, v, out: [B, H, N <= 64, D <= 64] views with element strides; bias (fp32, may be null) with its four strides;
+// row_m / row_z may be null
+int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void* v, Strides vs, const float* bias,
+               int64_t bsb, int64_t bsh, int64_t bsq, int64_t bsk, void* out, Strides os, float* row_m, float* row_z,
+               int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, float scale_log2,
+               cudaStream_t st) {
+  if (!win_tc_supported(dtype, head_dim, n_ctx, false)) return ELSA_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  // one box = 64 columns x 64 rows x 1 head x 2 batch entries: two sequences, each padded to 64 x 64 by the fill
+  if ((rc = make_tmap_rows64(&mq, q, dtype, n_ctx, heads, batch, qs, 64, head_dim, 2)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, k, dtype, n_ctx, heads, batch, ks, 64, head_dim, 2)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, v, dtype, n_ctx, heads, batch, vs, 64, head_dim, 2)) != ELSA_OK) return rc;
+  WinParams prm;
+  prm.out = out; prm.os = os; prm.row_m = row_m; prm.row_z = row_z;
+  prm.bias = bias; prm.bsb = bsb; prm.bsh = bsh; prm.bsq = bsq; prm.bsk = bsk;
+  prm.batch = batch; prm.heads = heads; prm.n_ctx = n_ctx; prm.head_dim = head_dim; prm.summary_dtype = summary_dtype;
+  prm.scale_log2 = scale_log2;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
+  const dim3 grid(static_cast<unsigned>((batch + 1) / 2), static_cast<unsigned>(heads));
+  if (dtype == ELSA_F16) {
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_fwd_kernel<__half>), kWinSmem)) != ELSA_OK) return rc;
+    win_tc_fwd_kernel<__half><<<grid, kThreads, kWinSmem, st>>>(mq, mk, mv, prm);
+  } else {
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_fwd_kernel<__nv_bfloat16>), kWinSmem)) != ELSA_OK) return rc;
+    win_tc_fwd_kernel<__nv_bfloat16><<<grid, kThreads, kWinSmem, st>>>(mq, mk, mv, prm);
+  }
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+}  // namespace elsa
