@@ -259,7 +259,8 @@ static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, u
 static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
 
 extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
-  (void)is_causal;
+  // sequences of at most 64 tokens, 16-bit, not causal: two per tensor-core tile, forward and backward (win_tc.cu)
+  if (n_ctx >= 1 && n_ctx <= 64 && win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) return 1;
   if (backward)
     return (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ||
             tcw_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
@@ -582,6 +583,13 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return bwd_tc(p, out, os, row_m, row_z, workspace, dtype, static_cast<cudaStream_t>(stream));
+  }
+  // 16-bit sequences of at most 64 tokens: two per 128-row tensor-core tile, one launch (win_tc.cu)
+  if (p.single_tile && !(flags & ELSA_FLAG_FORCE_SIMT) && (dbias == nullptr || bias != nullptr) &&
+      win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) {
+    const int src = check_device_status();
+    if (src != ELSA_OK) return src;
+    return win_tc_bwd(p, dtype, static_cast<cudaStream_t>(stream));
   }
   if (use_tc3) {
     const int src = check_device_status();

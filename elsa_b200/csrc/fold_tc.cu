@@ -415,6 +415,11 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// The driver's encode call wants a context current on the calling thread.  A thread that has made no runtime call yet
+// (an autograd worker whose first CUDA work is this library's) has none: a null cudaFree binds the primary context of
+// the thread's current device, after which the encode is repeated.
+static bool bind_primary_context() { return cudaFree(nullptr) == cudaSuccess; }
+
 int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_rows, int heads, int batch, Strides st,
                      int box_rows, int cols, int box_batch) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -427,8 +432,12 @@ int make_tmap_rows64(CUtensorMap* map, const void* base, int dtype, int64_t n_ro
   const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, static_cast<cuuint32_t>(box_batch)};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == ELSA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT || !bind_primary_context()) break;
+  }
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
     return ELSA_ERR_CUDA;
@@ -443,9 +452,13 @@ int make_tmap_f32_rows64(CUtensorMap* map, const void* base, int64_t n_rows, int
   const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(n_rows) * 256};
   const cuuint32_t box[3] = {32, static_cast<cuuint32_t>(box_rows), 1};   // 32 floats = one 128-byte swizzle row
   const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT || !bind_primary_context()) break;
+  }
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
     return ELSA_ERR_CUDA;

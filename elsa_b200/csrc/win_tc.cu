@@ -196,6 +196,248 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Backward of the same problems, one launch: dQ, dK, dV (and dbias) of two sequences of one head per CTA.
+//
+//   round 1 (issuer)   S = Q K^T, dP = dO V^T, S^T = K Q^T, dP^T = V dO^T          four 128 x 128 tiles = all 512 TMEM columns
+//   phase 1 (row r as a QUERY)   P = 2^(S c + bias - LSE), dS = P (dP - D) over the row's own sequence;
+//                      dS (16-bit) written over the row's S columns; -LSE and -D of the row published in shared memory
+//   phase 2 (row r as a KEY)     P^T, dS^T from S^T, dP^T with the queries' -LSE / -D; written over the S^T columns;
+//                      dbias += dS^T (the lanes of a warp hold consecutive keys: coalesced)
+//   round 2 (issuer)   dQ = dS K -> the dP columns, dV = P^T dO, dK = dS^T Q -> the dP^T columns
+//   epilogue           every thread stores its dQ row (as a query) and its dK, dV rows (as a key)
+//
+// TMEM columns: S [0,128) (later dS in [0,64)), dP [128,256) (later dQ in [128,192)), S^T [256,384) (later P^T in
+// [256,320), dS^T in [320,384)), dP^T [384,512) (later dV in [384,448), dK in [448,512)).  A thread only ever touches its
+// own TMEM lane, and it has read everything it needs from a column range before it writes there.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kWinBwdSmem = 4 * kTileBytes + 1024;   // Q, K, V, dO
+
+enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PH = 77, BAR_R2 = 78 };
+
+struct WinBwdParams {
+  const void* out; Strides os; const void* dout; Strides gs;
+  const float* row_m; const float* row_z;
+  const float* bias; int64_t bsb, bsh, bsq, bsk;
+  float* dbias; int64_t dsb, dsh, dsq, dsk; int dbias_atomic;
+  void* dq; void* dk; void* dv; Strides dqs, dks, dvs;
+  int batch, heads, n_ctx, head_dim;
+  float scale, scale_log2;
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                  const WinBwdParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ float nlse_s[128], nd_s[128];       // -LSE and -D of the tile's 128 query rows
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b0 = blockIdx.x * 2, hi = blockIdx.y;
+  const int N = prm.n_ctx, d = prm.head_dim;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base, sK = smem_base + kTileBytes, sV = smem_base + 2 * kTileBytes, sDO = smem_base + 3 * kTileBytes;
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_load = bar0, bar_r1 = bar0 + 8, bar_ph = bar0 + 16, bar_r2 = bar0 + 24;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_load, 1); mbar_init(bar_r1, 1); mbar_init(bar_ph, 4); mbar_init(bar_r2, 1);
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tST = tmem_base + 256, tdPT = tmem_base + 384;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------- loads and MMAs ----------------
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+      mbar_arrive_expect_tx(bar_load, 4 * kTileBytes);
+      tma_load_4d(sQ, &tmap_q, bar_load, 0, 0, hi, b0);
+      tma_load_4d(sK, &tmap_k, bar_load, 0, 0, hi, b0);
+      tma_load_4d(sV, &tmap_v, bar_load, 0, 0, hi, b0);
+      tma_load_4d(sDO, &tmap_do, bar_load, 0, 0, hi, b0);
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // A, B K-major, N = 128
+      constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // A in TMEM, B MN-major, N = 64
+      bool ok = mbar_wait(bar_load, 0, &abort_flag, prm.status, BAR_BLOAD);
+      if (ok) {
+        tc_fence_after();
+        const uint64_t dq = make_sdesc(sQ, 16, 1024), dk = make_sdesc(sK, 16, 1024);
+        const uint64_t dv = make_sdesc(sV, 16, 1024), ddo = make_sdesc(sDO, 16, 1024);
+        const int ksteps = (d + 15) / 16;                     // the columns beyond d are zeros
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tS, dq + 2 * ks, dk + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdP, ddo + 2 * ks, dv + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tST, dk + 2 * ks, dq + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdPT, dv + 2 * ks, ddo + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        mma_commit(bar_r1);
+        ok = mbar_wait(bar_ph, 0, &abort_flag, prm.status, BAR_PH);
+      }
+      if (ok) {
+        tc_fence_after();
+        const uint64_t k_mn = make_sdesc(sK, 128 * 128, 1024), q_mn = make_sdesc(sQ, 128 * 128, 1024);
+        const uint64_t do_mn = make_sdesc(sDO, 128 * 128, 1024);
+        mma_ts_x4<8, 128>(tdP, tS, k_mn, idesc_o, 0u);                 // dQ = dS K
+        mma_ts_x4<8, 128>(tdP, tS + 32, k_mn + 512, idesc_o, 1u);
+        mma_ts_x4<8, 128>(tdPT, tST, do_mn, idesc_o, 0u);              // dV = P^T dO
+        mma_ts_x4<8, 128>(tdPT, tST + 32, do_mn + 512, idesc_o, 1u);
+        mma_ts_x4<8, 128>(tdPT + 64, tST + 64, q_mn, idesc_o, 0u);     // dK = dS^T Q
+        mma_ts_x4<8, 128>(tdPT + 64, tST + 96, q_mn + 512, idesc_o, 1u);
+        mma_commit(bar_r2);
+      }
+    }
+  } else {
+    // ---------------- fold warps: thread = row r of the tile, a query in phase 1 and a key in phase 2 ----------------
+    const int row = warp * 32 + lane;
+    const int seq = row >> 6, ri = row & 63;                // which of the two sequences, and the row's index in it
+    const int b = b0 + seq;
+    const bool row_ok = b < prm.batch && ri < N;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const float c = prm.scale_log2;
+    // -LSE and -D of this row as a query
+    float nlse = -CUDART_INF_F, nd = 0.f;
+    if (row_ok) {
+      const int64_t ro = (static_cast<int64_t>(b) * prm.heads + hi) * N + ri;
+      const float m = prm.row_m[ro], z = prm.row_z[ro];
+      if (z > 0.f && m > -CUDART_INF_F) nlse = -(m + log2f(z));   // (a row whose keys are all masked keeps P = 0)
+      const T* o = static_cast<const T*>(prm.out) + static_cast<int64_t>(b) * prm.os.b + hi * prm.os.h + static_cast<int64_t>(ri) * prm.os.r;
+      const T* g = static_cast<const T*>(prm.dout) + static_cast<int64_t>(b) * prm.gs.b + hi * prm.gs.h + static_cast<int64_t>(ri) * prm.gs.r;
+      float acc = 0.f;
+      for (int i = 0; i < d; i += 8) {
+        const uint4 ov = *reinterpret_cast<const uint4*>(o + i), gv = *reinterpret_cast<const uint4*>(g + i);
+        const T* oe = reinterpret_cast<const T*>(&ov);
+        const T* ge = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += to_f32<T>(oe[e]) * to_f32<T>(ge[e]);
+      }
+      nd = -acc;
+    }
+    nlse_s[row] = nlse; nd_s[row] = nd;
+    named_barrier_sync(1, 128);
+    bool alive = __all_sync(0xffffffffu, mbar_wait(bar_r1, 0, &abort_flag, prm.status, BAR_R1));
+    if (alive) {
+      tc_fence_after();
+      uint32_t zero[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) zero[i] = 0u;
+      // ---- phase 1: the row as a query ----
+      {
+        uint32_t rs[64], rp[64];
+        tmem_ld32(tS + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+        tmem_ld32(tS + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
+        tmem_ld32(tdP + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
+        tmem_ld32(tdP + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
+        tmem_wait_ld();
+        const float* bp = prm.bias ? prm.bias + static_cast<int64_t>(min(b, prm.batch - 1)) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(ri, N - 1)) * prm.bsq : nullptr;
+        uint32_t dsk[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          float dsv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kk = i + e;
+            float a = nlse;
+            if (bp && kk < N) a = fmaf(bp[kk * prm.bsk], 1.4426950408889634f, nlse);
+            float p = fast_exp2(fmaf(__uint_as_float(rs[kk]), c, a));
+            if (kk >= N) p = 0.f;
+            dsv[e] = p * (__uint_as_float(rp[kk]) + nd);
+          }
+          dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
+        }
+        // dS of this query row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other's
+        tmem_st32(tS + lane_off + 32 * seq, dsk);
+        tmem_st32(tS + lane_off + 32 * (1 - seq), zero);
+      }
+      // ---- phase 2: the row as a key ----
+      {
+        uint32_t rs[64], rp[64];
+        tmem_ld32(tST + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+        tmem_ld32(tST + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
+        tmem_ld32(tdPT + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
+        tmem_ld32(tdPT + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
+        tmem_wait_ld();
+        // bias[query, key] of this key column
+        const float* bc = prm.bias ? prm.bias + static_cast<int64_t>(min(b, prm.batch - 1)) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(ri, N - 1)) * prm.bsk : nullptr;
+        // dbias[query, key] is written here, where the lanes of a warp hold consecutive keys of one query: one
+        // coalesced store (or reduction) per query instead of 32 scattered ones
+        float* dbc = (prm.dbias && row_ok) ? prm.dbias + static_cast<int64_t>(b) * prm.dsb + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk : nullptr;
+        uint32_t pk[32], dsk[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          float pv[2], dv2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qq = i + e;                            // query index within the sequence
+            float a = nlse_s[64 * seq + qq];                 // -inf for queries that do not exist
+            if (bc && qq < N) a = fmaf(bc[static_cast<int64_t>(qq) * prm.bsq], 1.4426950408889634f, a);
+            float p = fast_exp2(fmaf(__uint_as_float(rs[qq]), c, a));
+            if (!row_ok) p = 0.f;                            // a key that does not exist
+            pv[e] = p;
+            dv2[e] = p * (__uint_as_float(rp[qq]) + nd_s[64 * seq + qq]);
+            if (dbc && qq < N) {
+              if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]); else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
+            }
+          }
+          pk[i >> 1] = pack2<T>(pv[0], pv[1]);
+          dsk[i >> 1] = pack2<T>(dv2[0], dv2[1]);
+        }
+        tmem_st32(tST + lane_off + 32 * seq, pk);                  // P^T over the tile's 128 queries
+        tmem_st32(tST + lane_off + 32 * (1 - seq), zero);
+        tmem_st32(tST + 64 + lane_off + 32 * seq, dsk);            // dS^T
+        tmem_st32(tST + 64 + lane_off + 32 * (1 - seq), zero);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(bar_ph, lane);
+      alive = __all_sync(0xffffffffu, mbar_wait(bar_r2, 0, &abort_flag, prm.status, BAR_R2));
+    }
+    if (alive) {
+      tc_fence_after();
+      // dQ of this row as a query, dV and dK of this row as a key
+#pragma unroll
+      for (int which = 0; which < 3; ++which) {
+        uint32_t r0[32], r1[32];
+        const uint32_t src = which == 0 ? tdP : (which == 1 ? tdPT : tdPT + 64);
+        tmem_ld32(src + lane_off, r0);
+        tmem_ld32(src + lane_off + 32, r1);
+        tmem_wait_ld();
+        if (!row_ok) continue;
+        const Strides st = which == 0 ? prm.dqs : (which == 1 ? prm.dvs : prm.dks);
+        T* dst = static_cast<T*>(which == 0 ? prm.dq : (which == 1 ? prm.dv : prm.dk)) + static_cast<int64_t>(b) * st.b + hi * st.h + static_cast<int64_t>(ri) * st.r;
+        const float f = which == 1 ? 1.f : prm.scale;
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          if (i >= d) continue;
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(i + e < 32 ? r0[(i + e) & 31] : r1[(i + e) & 31]) * f;
+          uint4 t;
+          t.x = pack2<T>(o[0], o[1]); t.y = pack2<T>(o[2], o[3]); t.z = pack2<T>(o[4], o[5]); t.w = pack2<T>(o[6], o[7]);
+          *reinterpret_cast<uint4*>(dst + i) = t;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, 512);
+}
+
 }  // namespace
 
 bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal) {
@@ -229,6 +471,38 @@ int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void*
   } else {
     if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_fwd_kernel<__nv_bfloat16>), kWinSmem)) != ELSA_OK) return rc;
     win_tc_fwd_kernel<__nv_bfloat16><<<grid, kThreads, kWinSmem, st>>>(mq, mk, mv, prm);
+  }
+  ELSA_LAUNCH_CHECK();
+  return ELSA_OK;
+}
+
+int win_tc_bwd(const BwdParams& p, int dtype, cudaStream_t st) {
+  if (!win_tc_supported(dtype, p.head_dim, p.n_ctx, p.is_causal != 0) || p.n_keys != p.n_ctx || p.key_offset != 0 || p.dq_f32 ||
+      !p.out || !p.row_m || !p.row_z || (p.dbias && !p.bias))
+    return ELSA_ERR_UNSUPPORTED;
+  const int batch = p.bh / p.heads;
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.heads, batch, p.qs, 64, p.head_dim, 2)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_ctx, p.heads, batch, p.ks, 64, p.head_dim, 2)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_ctx, p.heads, batch, p.vs, 64, p.head_dim, 2)) != ELSA_OK) return rc;
+  if ((rc = make_tmap_rows64(&mdo, p.dout, dtype, p.n_ctx, p.heads, batch, p.gs, 64, p.head_dim, 2)) != ELSA_OK) return rc;
+  WinBwdParams prm;
+  prm.out = p.out; prm.os = p.os; prm.dout = p.dout; prm.gs = p.gs;
+  prm.row_m = p.row_m; prm.row_z = p.row_z;
+  prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk;
+  prm.dbias = p.dbias; prm.dsb = p.dsb; prm.dsh = p.dsh; prm.dsq = p.dsq; prm.dsk = p.dsk; prm.dbias_atomic = p.dbias_atomic;
+  prm.dq = p.dq; prm.dk = p.dk; prm.dv = p.dv; prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
+  prm.batch = batch; prm.heads = p.heads; prm.n_ctx = p.n_ctx; prm.head_dim = p.head_dim;
+  prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
+  if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
+  const dim3 grid(static_cast<unsigned>((batch + 1) / 2), static_cast<unsigned>(p.heads));
+  if (dtype == ELSA_F16) {
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_bwd_kernel<__half>), kWinBwdSmem)) != ELSA_OK) return rc;
+    win_tc_bwd_kernel<__half><<<grid, kThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, prm);
+  } else {
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_bwd_kernel<__nv_bfloat16>), kWinBwdSmem)) != ELSA_OK) return rc;
+    win_tc_bwd_kernel<__nv_bfloat16><<<grid, kThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, prm);
   }
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;

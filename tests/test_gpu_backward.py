@@ -83,6 +83,14 @@ CASES = [
     (2, 2, 640, 64, F32, False, "bhnn"),
     (1, 3, 900, 40, F32, True, "hnn"),
     (2, 2, 1024, 32, F32, False, "b1nn"),
+    # sequences of at most 64 tokens, 16-bit: two per tensor-core tile (odd batch: the last tile is half empty)
+    (5, 3, 49, 32, BF16, False, "1hnn"),
+    (3, 2, 64, 64, F16, False, "bhnn"),
+    (4, 3, 49, 32, F16, False, "b1nn"),
+    (6, 4, 16, 64, BF16, False, "hnn"),
+    (2, 2, 7, 24, F16, False, None),
+    (1, 1, 1, 8, BF16, False, None),
+    (7, 2, 33, 40, F16, False, "nn"),
 ]
 
 
@@ -130,8 +138,9 @@ def test_train_vs_oracle_and_fp64(case):
         assert U.max_abs(biasd.grad, b64.grad) <= lim * max(1.0, float(b64.grad.abs().max()))
 
 
-def test_backward_is_deterministic_and_masked_rows_are_zero():
-    b, h, n, d = 1, 2, 150, 64
+@pytest.mark.parametrize("b,n,d", [(1, 150, 64), (3, 49, 32)])
+def test_backward_is_deterministic_and_masked_rows_are_zero(b, n, d):
+    h = 2
     q, k, v, do = (U.seeded((b, h, n, d), F16, 70 + i).to(DEV) for i in range(4))
     bias = torch.zeros(n, n, device=DEV)
     bias[7, :] = float("-inf")
@@ -229,3 +238,29 @@ def test_fp32_tensor_core_backward_keeps_its_accuracy_on_long_rows():
         assert U.max_abs(a, b) <= 1.5e-6 * max(1.0, float(b.abs().max())), name
         # relative to the gradient's own size: the fixed-scale version failed this by a factor of five
         assert U.max_abs(a, b) <= 1e-5 * float(b.abs().max()), name
+
+
+def test_first_cuda_call_of_a_thread_may_be_the_backward():
+    """An autograd worker thread whose first CUDA work is this library's has no driver context bound yet; the
+    tensor-map encode of the tensor-core kernels needs one.  Everything is allocated beforehand so that the library
+    call is the thread's first CUDA call."""
+    import threading
+    b, h, n, d = 6, 3, 49, 32
+    q, k, v, do = (U.seeded((b, h, n, d), F16, 90 + i).to(DEV) for i in range(4))
+    out, rm, rz = E.twopass_attention_with_state(q, k, v)
+    ref = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz)
+    del ref                                        # (its blocks go back to the caching allocator for the thread's call)
+    res = {}
+
+    def work():
+        try:
+            res["g"] = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz)
+        except Exception as exc:  # noqa: BLE001
+            res["err"] = exc
+
+    t = threading.Thread(target=work)
+    t.start(); t.join()
+    assert "err" not in res, res.get("err")
+    again = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz)
+    for x, y in zip(res["g"], again):
+        assert torch.equal(x, y)
