@@ -15,7 +15,7 @@ std::atomic<long long> g_kernel_launches{0};
 
 static int g_sm_count_cache[64] = {0};
 
-static int sm_count() {
+int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
   if (g_sm_count_cache[dev] == 0) {

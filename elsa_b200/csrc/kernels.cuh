@@ -68,6 +68,8 @@ inline int ensure_dynamic_smem(const void* func, size_t bytes) {
 // Status word of the CURRENT device for the bounded device-side waits: one int per device in mapped pinned host
 // memory, allocated on first use (api.cu).  *dev_ptr is what a kernel stores through, *host_ptr what the host reads.
 int device_status_word(int** dev_ptr, volatile int** host_ptr);
+// number of SMs of the current device (cached per device; api.cu)
+int sm_count();
 
 // tcgen05 kernels (fold_tc.cu)
 bool fold_tc_supported(int dtype, int head_dim, bool has_bias);

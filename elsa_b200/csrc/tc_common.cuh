@@ -112,6 +112,10 @@ template <int N> __device__ __forceinline__ void bulk_wait_group() {
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// arrive without waiting: the writes made before it are visible to the threads that `named_barrier_sync` on the same id
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // register re-balancing between warpgroups (every warp of the 128-thread warpgroup must execute it)

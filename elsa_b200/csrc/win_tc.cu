@@ -24,11 +24,40 @@ using namespace tc;
 namespace {
 
 constexpr int kTileBytes = 128 * 64 * 2;          // two 64 x 64 16-bit sequences
-constexpr int kWinSmem = 3 * kTileBytes + 1024;   // Q, K, V + alignment slack
+constexpr int kBiasStride = 65;                   // floats per staged bias row: lanes that hold consecutive rows hit distinct banks
+constexpr int kBiasBytes = 2 * 64 * kBiasStride * 4;   // the bias tiles of the two sequences
+constexpr int kWinSmem = 3 * kTileBytes + kBiasBytes + 1024;   // Q, K, V, bias + alignment slack
 constexpr int kThreads = 160;
 constexpr uint32_t kTmemCols = 256;
 
 enum BarId { BAR_LOAD = 71, BAR_S = 72, BAR_P = 73, BAR_O = 74 };
+
+// The bias tiles [query][key] of the CTA's two sequences, copied into shared memory by `n_warps` warps (w = this warp's
+// index among them): the lanes of a warp read consecutive keys of one query (coalesced when the key stride is 1), and
+// afterwards a thread walks its own query row, or its own key column, without bank conflicts.
+__device__ __forceinline__ void stage_bias(float* sb, const float* bias, int64_t bsb, int64_t bsh, int64_t bsq, int64_t bsk,
+                                           int b0, int n_tiles, int batch, int hi, int N, int w, int n_warps, int lane) {
+  for (int s2 = 0; s2 < n_tiles; ++s2) {
+    if (b0 + s2 >= batch) break;
+    const float* src = bias + static_cast<int64_t>(b0 + s2) * bsb + hi * bsh;
+    float* dst = sb + s2 * 64 * kBiasStride;
+    // eight rows of loads in flight per warp before the first store (N <= 64: two loads per row)
+    for (int r0 = w; r0 < N; r0 += 8 * n_warps) {
+      float t[8][2];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = r0 + j * n_warps;
+        t[j][0] = (r < N && lane < N) ? src[static_cast<int64_t>(r) * bsq + lane * bsk] : 0.f;
+        t[j][1] = (r < N && lane + 32 < N) ? src[static_cast<int64_t>(r) * bsq + (lane + 32) * bsk] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = r0 + j * n_warps;
+        if (r < N) { dst[r * kBiasStride + lane] = t[j][0]; dst[r * kBiasStride + lane + 32] = t[j][1]; }
+      }
+    }
+  }
+}
 
 struct WinParams {
   void* out; Strides os;
@@ -108,6 +137,11 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     const bool row_ok = b < prm.batch && qi < N;
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
     const float c = prm.scale_log2;
+    float* sb = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + 3 * kTileBytes);
+    if (prm.bias) {                                         // (while the loads and the S MMA are in flight)
+      stage_bias(sb, prm.bias, prm.bsb, prm.bsh, prm.bsq, prm.bsk, b0, prm.bsb != 0 ? 2 : 1, prm.batch, hi, N, warp, 4, lane);
+      named_barrier_sync(1, 128);
+    }
     bool alive = __all_sync(0xffffffffu, mbar_wait(bar_s, 0, &abort_flag, prm.status, BAR_S));
     float z = 0.f, m = -CUDART_INF_F;
     if (alive) {
@@ -122,10 +156,10 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(r0[i]) * c; sv[32 + i] = __uint_as_float(r1[i]) * c; }
       }
       if (prm.bias && row_ok) {
-        const float* bp = prm.bias + static_cast<int64_t>(b) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(qi) * prm.bsq;
+        const float* bp = sb + ((prm.bsb != 0 ? seq * 64 : 0) + qi) * kBiasStride;   // (one tile when the bias ignores the batch index)
 #pragma unroll
         for (int i = 0; i < 64; ++i)
-          if (i < N) sv[i] = fmaf(bp[i * prm.bsk], 1.4426950408889634f, sv[i]);
+          if (i < N) sv[i] = fmaf(bp[i], 1.4426950408889634f, sv[i]);
       }
 #pragma unroll
       for (int i = 0; i < 64; ++i)
@@ -201,20 +235,24 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // Backward of the same problems, one launch: dQ, dK, dV (and dbias) of two sequences of one head per CTA.
 //
 //   round 1 (issuer)   S = Q K^T, dP = dO V^T, S^T = K Q^T, dP^T = V dO^T          four 128 x 128 tiles = all 512 TMEM columns
-//   phase 1 (row r as a QUERY)   P = 2^(S c + bias - LSE), dS = P (dP - D) over the row's own sequence;
-//                      dS (16-bit) written over the row's S columns; -LSE and -D of the row published in shared memory
-//   phase 2 (row r as a KEY)     P^T, dS^T from S^T, dP^T with the queries' -LSE / -D; written over the S^T columns;
-//                      dbias += dS^T (the lanes of a warp hold consecutive keys: coalesced)
-//   round 2 (issuer)   dQ = dS K -> the dP columns, dV = P^T dO, dK = dS^T Q -> the dP^T columns
-//   epilogue           every thread stores its dQ row (as a query) and its dK, dV rows (as a key)
+//   query side (warps 0-3, thread = query row)   -LSE and -D of the row, published in shared memory;
+//                      P = 2^(S c + bias - LSE), dS = P (dP - D) over the row's own sequence; dS (16-bit) written over
+//                      the row's S columns
+//   key side (warps 4-7, thread = key row, at the same time)   P^T, dS^T from S^T, dP^T with the queries' -LSE / -D;
+//                      written over the S^T columns; dbias += dS^T (the lanes of a warp hold consecutive keys: coalesced)
+//   round 2 (issuer)   dQ = dS K -> the dP columns as soon as the query side is done; dV = P^T dO, dK = dS^T Q -> the
+//                      dP^T columns as soon as the key side is done
+//   epilogue           the query side stores dQ, the key side dV and dK
 //
 // TMEM columns: S [0,128) (later dS in [0,64)), dP [128,256) (later dQ in [128,192)), S^T [256,384) (later P^T in
 // [256,320), dS^T in [320,384)), dP^T [384,512) (later dV in [384,448), dK in [448,512)).  A thread only ever touches its
 // own TMEM lane, and it has read everything it needs from a column range before it writes there.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int kWinBwdSmem = 4 * kTileBytes + 1024;   // Q, K, V, dO
+constexpr int kBwdStageBytes = 5 * kTileBytes;       // Q, K, V, dO, out of one pair of sequences
+constexpr int kWinBwdSmem = 2 * kBwdStageBytes + kBiasBytes + 1024;   // two stages, bias, alignment slack
+constexpr int kBwdThreads = 288;                     // 4 query-side warps, 4 key-side warps, 1 issuing warp
 
-enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PH = 77, BAR_R2 = 78 };
+enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PHQ = 77, BAR_PHK = 78, BAR_R2Q = 79, BAR_R2K = 80, BAR_EPI = 81, BAR_PUB = 82, BAR_BIAS = 83 };
 
 struct WinBwdParams {
   const void* out; Strides os; const void* dout; Strides gs;
@@ -227,32 +265,78 @@ struct WinBwdParams {
   int* status;
 };
 
+// one accumulator row (64 fp32 columns at `src`) scaled by f and stored as d elements of T
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ void store_acc_row(uint32_t src, T* dst, int d, float f) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(src, r0);
+  tmem_ld32(src + 32, r1);
+  tmem_wait_ld();
+  if (!dst) return;
+#pragma unroll
+  for (int i = 0; i < 64; i += 8) {
+    if (i >= d) continue;
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(i + e < 32 ? r0[(i + e) & 31] : r1[(i + e) & 31]) * f;
+    uint4 t;
+    t.x = pack2<T>(o[0], o[1]); t.y = pack2<T>(o[2], o[3]); t.z = pack2<T>(o[4], o[5]); t.w = pack2<T>(o[6], o[7]);
+    *reinterpret_cast<uint4*>(dst + i) = t;
+  }
+}
+
+// -D of a row = -sum(out * dout) over the row's 128 bytes in two 128-byte-swizzled tiles (chunk c of row r sits at
+// chunk c ^ (r & 7)); columns beyond the head dim are zeros
+template <typename T>
+__device__ __forceinline__ float neg_row_dot(const uint8_t* t_out, const uint8_t* t_do, int r, int d) {
+  float acc = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    if (ch * 8 >= d) continue;
+    const int off = r * 128 + ((ch ^ (r & 7)) << 4);
+    const uint4 ov = *reinterpret_cast<const uint4*>(t_out + off), gv = *reinterpret_cast<const uint4*>(t_do + off);
+    const T* oe = reinterpret_cast<const T*>(&ov);
+    const T* ge = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = fmaf(to_f32<T>(oe[e]), to_f32<T>(ge[e]), acc);
+  }
+  return -acc;
+}
+
+// Persistent: CTA c works on head c % heads and on the pairs of sequences c / heads, c / heads + G, ... (G = gridDim.x /
+// heads).  The five tiles of the next pair are in flight while this one is computed (two stages of shared memory); a
+// bias that does not depend on the batch index is staged once.
+template <typename T>
+__global__ void __launch_bounds__(kBwdThreads, 1)
 win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                  const WinBwdParams prm) {
+                  const __grid_constant__ CUtensorMap tmap_o, const WinBwdParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[4];
+  __shared__ __align__(8) uint64_t bars[10];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float nlse_s[128], nd_s[128];       // -LSE and -D of the tile's 128 query rows
+  __shared__ float nlse_s[2][128], nd_s[2][128];   // -LSE and -D of the tile's 128 query rows, per iteration parity
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b0 = blockIdx.x * 2, hi = blockIdx.y;
+  const int hi = blockIdx.x % prm.heads;
+  const int pair0 = blockIdx.x / prm.heads, pair_step = gridDim.x / prm.heads;
+  const int n_pairs = (prm.batch + 1) / 2;
   const int N = prm.n_ctx, d = prm.head_dim;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = smem_base, sK = smem_base + kTileBytes, sV = smem_base + 2 * kTileBytes, sDO = smem_base + 3 * kTileBytes;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  // stage s: Q, K, V, dO, out at smem_base + s * kBwdStageBytes + {0..4} * kTileBytes
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t bar_load = bar0, bar_r1 = bar0 + 8, bar_ph = bar0 + 16, bar_r2 = bar0 + 24;
+  const uint32_t bar_load = bar0 /* [2] */, bar_r1 = bar0 + 16, bar_phq = bar0 + 24, bar_phk = bar0 + 32, bar_r2q = bar0 + 40,
+                 bar_r2k = bar0 + 48, bar_epi = bar0 + 56, bar_pub = bar0 + 64, bar_bias = bar0 + 72;
 
   if (tid == 0) {
     abort_flag = 0;
-    mbar_init(bar_load, 1); mbar_init(bar_r1, 1); mbar_init(bar_ph, 4); mbar_init(bar_r2, 1);
+    mbar_init(bar_load, 1); mbar_init(bar_load + 8, 1); mbar_init(bar_r1, 1); mbar_init(bar_phq, 4); mbar_init(bar_phk, 4);
+    mbar_init(bar_r2q, 1); mbar_init(bar_r2k, 1); mbar_init(bar_epi, 8); mbar_init(bar_pub, 4); mbar_init(bar_bias, 4);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(smem_u32(&tmem_base_slot), 512);
     tmem_relinquish();
   }
@@ -262,79 +346,96 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tS = tmem_base, tdP = tmem_base + 128, tST = tmem_base + 256, tdPT = tmem_base + 384;
 
-  if (warp == 4) {
-    if (lane == 0) {
+  // row of the tile this thread owns (a query for warps 0-3, a key for warps 4-7) == its TMEM lane
+  const int row = (warp & 3) * 32 + lane;
+  const int seq = row >> 6, ri = row & 63;                // which of the two sequences, and the row's index in it
+  const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const float c = prm.scale_log2;
+  float* sb = reinterpret_cast<float*>(smem_al + 2 * kBwdStageBytes);
+  const bool bias_per_batch = prm.bias && prm.bsb != 0;   // else one tile serves every pair of this head
+  const float* sb_seq = sb + (bias_per_batch ? seq * 64 * kBiasStride : 0);
+
+  if (warp == 8) {
+    if (lane == 0 && pair0 < n_pairs) {
       // ---------------- loads and MMAs ----------------
-      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
-      mbar_arrive_expect_tx(bar_load, 4 * kTileBytes);
-      tma_load_4d(sQ, &tmap_q, bar_load, 0, 0, hi, b0);
-      tma_load_4d(sK, &tmap_k, bar_load, 0, 0, hi, b0);
-      tma_load_4d(sV, &tmap_v, bar_load, 0, 0, hi, b0);
-      tma_load_4d(sDO, &tmap_do, bar_load, 0, 0, hi, b0);
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_o);
       constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       constexpr uint32_t idesc_s = make_idesc(fmt, 0, 0, 128, 128);   // A, B K-major, N = 128
       constexpr uint32_t idesc_o = make_idesc(fmt, 0, 1, 128, 64);    // A in TMEM, B MN-major, N = 64
-      bool ok = mbar_wait(bar_load, 0, &abort_flag, prm.status, BAR_BLOAD);
-      if (ok) {
+      const int ksteps = (d + 15) / 16;                     // the columns beyond d are zeros: their K-steps add nothing
+      auto issue_loads = [&](int pair, int stage) {         // rows beyond N, columns beyond d, a batch entry beyond B: zeros
+        const uint32_t base = smem_base + stage * kBwdStageBytes, bar = bar_load + 8 * stage;
+        mbar_arrive_expect_tx(bar, 5 * kTileBytes);
+        tma_load_4d(base, &tmap_q, bar, 0, 0, hi, 2 * pair);
+        tma_load_4d(base + kTileBytes, &tmap_k, bar, 0, 0, hi, 2 * pair);
+        tma_load_4d(base + 2 * kTileBytes, &tmap_v, bar, 0, 0, hi, 2 * pair);
+        tma_load_4d(base + 3 * kTileBytes, &tmap_do, bar, 0, 0, hi, 2 * pair);
+        tma_load_4d(base + 4 * kTileBytes, &tmap_o, bar, 0, 0, hi, 2 * pair);
+      };
+      issue_loads(pair0, 0);
+      int it = 0;
+      for (int pair = pair0; pair < n_pairs; pair += pair_step, ++it) {
+        const int stage = it & 1;
+        const uint32_t ph = it & 1;
+        const uint32_t sQ = smem_base + stage * kBwdStageBytes, sK = sQ + kTileBytes, sV = sQ + 2 * kTileBytes, sDO = sQ + 3 * kTileBytes;
+        if (!mbar_wait(bar_load + 8 * stage, (it >> 1) & 1, &abort_flag, prm.status, BAR_BLOAD)) break;
+        // the fold warps have read the gradients of the previous pair out of TMEM (and its tiles out of the other stage)
+        if (it > 0 && !mbar_wait(bar_epi, (it - 1) & 1, &abort_flag, prm.status, BAR_EPI)) break;
         tc_fence_after();
         const uint64_t dq = make_sdesc(sQ, 16, 1024), dk = make_sdesc(sK, 16, 1024);
         const uint64_t dv = make_sdesc(sV, 16, 1024), ddo = make_sdesc(sDO, 16, 1024);
-        const int ksteps = (d + 15) / 16;                     // the columns beyond d are zeros
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tS, dq + 2 * ks, dk + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdP, ddo + 2 * ks, dv + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tST, dk + 2 * ks, dq + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdPT, dv + 2 * ks, ddo + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         mma_commit(bar_r1);
-        ok = mbar_wait(bar_ph, 0, &abort_flag, prm.status, BAR_PH);
-      }
-      if (ok) {
-        tc_fence_after();
+        if (pair + pair_step < n_pairs) issue_loads(pair + pair_step, stage ^ 1);
         const uint64_t k_mn = make_sdesc(sK, 128 * 128, 1024), q_mn = make_sdesc(sQ, 128 * 128, 1024);
         const uint64_t do_mn = make_sdesc(sDO, 128 * 128, 1024);
+        if (!mbar_wait(bar_phq, ph, &abort_flag, prm.status, BAR_PHQ)) break;
+        tc_fence_after();
         mma_ts_x4<8, 128>(tdP, tS, k_mn, idesc_o, 0u);                 // dQ = dS K
         mma_ts_x4<8, 128>(tdP, tS + 32, k_mn + 512, idesc_o, 1u);
+        mma_commit(bar_r2q);
+        if (!mbar_wait(bar_phk, ph, &abort_flag, prm.status, BAR_PHK)) break;
+        tc_fence_after();
         mma_ts_x4<8, 128>(tdPT, tST, do_mn, idesc_o, 0u);              // dV = P^T dO
         mma_ts_x4<8, 128>(tdPT, tST + 32, do_mn + 512, idesc_o, 1u);
         mma_ts_x4<8, 128>(tdPT + 64, tST + 64, q_mn, idesc_o, 0u);     // dK = dS^T Q
         mma_ts_x4<8, 128>(tdPT + 64, tST + 96, q_mn + 512, idesc_o, 1u);
-        mma_commit(bar_r2);
+        mma_commit(bar_r2k);
       }
     }
-  } else {
-    // ---------------- fold warps: thread = row r of the tile, a query in phase 1 and a key in phase 2 ----------------
-    const int row = warp * 32 + lane;
-    const int seq = row >> 6, ri = row & 63;                // which of the two sequences, and the row's index in it
-    const int b = b0 + seq;
-    const bool row_ok = b < prm.batch && ri < N;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const float c = prm.scale_log2;
-    // -LSE and -D of this row as a query
-    float nlse = -CUDART_INF_F, nd = 0.f;
-    if (row_ok) {
-      const int64_t ro = (static_cast<int64_t>(b) * prm.heads + hi) * N + ri;
-      const float m = prm.row_m[ro], z = prm.row_z[ro];
-      if (z > 0.f && m > -CUDART_INF_F) nlse = -(m + log2f(z));   // (a row whose keys are all masked keeps P = 0)
-      const T* o = static_cast<const T*>(prm.out) + static_cast<int64_t>(b) * prm.os.b + hi * prm.os.h + static_cast<int64_t>(ri) * prm.os.r;
-      const T* g = static_cast<const T*>(prm.dout) + static_cast<int64_t>(b) * prm.gs.b + hi * prm.gs.h + static_cast<int64_t>(ri) * prm.gs.r;
-      float acc = 0.f;
-      for (int i = 0; i < d; i += 8) {
-        const uint4 ov = *reinterpret_cast<const uint4*>(o + i), gv = *reinterpret_cast<const uint4*>(g + i);
-        const T* oe = reinterpret_cast<const T*>(&ov);
-        const T* ge = reinterpret_cast<const T*>(&gv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc += to_f32<T>(oe[e]) * to_f32<T>(ge[e]);
+  } else if (warp < 4) {
+    // ---------------- query-side warps: thread = query row ----------------
+    auto load_state = [&](int pair, float& m, float& z) {
+      const int bb = 2 * pair + seq;
+      m = -CUDART_INF_F; z = 0.f;
+      if (pair < n_pairs && bb < prm.batch && ri < N) {
+        const int64_t ro = (static_cast<int64_t>(bb) * prm.heads + hi) * N + ri;
+        m = prm.row_m[ro]; z = prm.row_z[ro];
       }
-      nd = -acc;
-    }
-    nlse_s[row] = nlse; nd_s[row] = nd;
-    named_barrier_sync(1, 128);
-    bool alive = __all_sync(0xffffffffu, mbar_wait(bar_r1, 0, &abort_flag, prm.status, BAR_R1));
-    if (alive) {
+    };
+    float m_next, z_next;
+    load_state(pair0, m_next, z_next);
+    int it = 0;
+    for (int pair = pair0; pair < n_pairs; pair += pair_step, ++it) {
+      const int stage = it & 1;
+      const uint32_t ph = it & 1;
+      const int b = 2 * pair + seq;
+      const bool row_ok = b < prm.batch && ri < N;
+      const uint8_t* tiles = smem_al + stage * kBwdStageBytes;
+      // -LSE and -D of this row, published for the key-side warps
+      float nlse = -CUDART_INF_F;
+      if (z_next > 0.f && m_next > -CUDART_INF_F) nlse = -(m_next + log2f(z_next));   // (a row whose keys are all masked keeps P = 0)
+      load_state(pair + pair_step, m_next, z_next);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_load + 8 * stage, (it >> 1) & 1, &abort_flag, prm.status, BAR_BLOAD))) break;
+      const float nd = neg_row_dot<T>(tiles + 4 * kTileBytes, tiles + 3 * kTileBytes, row, d);
+      nlse_s[ph][row] = nlse; nd_s[ph][row] = nd;
+      mbar_arrive_warp(bar_pub, lane);
+      if (prm.bias && !__all_sync(0xffffffffu, mbar_wait(bar_bias, ph, &abort_flag, prm.status, BAR_BIAS))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
       tc_fence_after();
-      uint32_t zero[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) zero[i] = 0u;
-      // ---- phase 1: the row as a query ----
       {
         uint32_t rs[64], rp[64];
         tmem_ld32(tS + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
@@ -342,8 +443,8 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_ld32(tdP + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
         tmem_ld32(tdP + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
         tmem_wait_ld();
-        const float* bp = prm.bias ? prm.bias + static_cast<int64_t>(min(b, prm.batch - 1)) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(ri, N - 1)) * prm.bsq : nullptr;
-        uint32_t dsk[32];
+        const float* bp = (prm.bias && row_ok) ? sb_seq + ri * kBiasStride : nullptr;
+        uint32_t dsk[32], zero[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           float dsv[2];
@@ -351,18 +452,48 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int e = 0; e < 2; ++e) {
             const int kk = i + e;
             float a = nlse;
-            if (bp && kk < N) a = fmaf(bp[kk * prm.bsk], 1.4426950408889634f, nlse);
+            if (bp && kk < N) a = fmaf(bp[kk], 1.4426950408889634f, nlse);
             float p = fast_exp2(fmaf(__uint_as_float(rs[kk]), c, a));
             if (kk >= N) p = 0.f;
             dsv[e] = p * (__uint_as_float(rp[kk]) + nd);
           }
           dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) zero[i] = 0u;
         // dS of this query row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other's
         tmem_st32(tS + lane_off + 32 * seq, dsk);
         tmem_st32(tS + lane_off + 32 * (1 - seq), zero);
+        tmem_wait_st();
       }
-      // ---- phase 2: the row as a key ----
+      tc_fence_before();
+      mbar_arrive_warp(bar_phq, lane);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r2q, ph, &abort_flag, prm.status, BAR_R2Q))) break;
+      tc_fence_after();
+      T* dst = row_ok ? static_cast<T*>(prm.dq) + static_cast<int64_t>(b) * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(ri) * prm.dqs.r : nullptr;
+      store_acc_row<T>(tdP + lane_off, dst, d, prm.scale);
+      tc_fence_before();
+      mbar_arrive_warp(bar_epi, lane);
+      // the key side has consumed this pair's -LSE / -D (and the barrier phase that published them) before the next
+      // pair's are published
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r2k, ph, &abort_flag, prm.status, BAR_R2K))) break;
+    }
+  } else {
+    // ---------------- key-side warps: thread = key row ----------------
+    int it = 0;
+    for (int pair = pair0; pair < n_pairs; pair += pair_step, ++it) {
+      const uint32_t ph = it & 1;
+      const int b = 2 * pair + seq;
+      const bool row_ok = b < prm.batch && ri < N;
+      if (prm.bias) {
+        // (the query side has finished with the tiles of the previous pair: its dS was an input of that pair's last MMAs)
+        if (bias_per_batch) stage_bias(sb, prm.bias, prm.bsb, prm.bsh, prm.bsq, prm.bsk, 2 * pair, 2, prm.batch, hi, N, warp & 3, 4, lane);
+        else if (it == 0) stage_bias(sb, prm.bias, 0, prm.bsh, prm.bsq, prm.bsk, 0, 1, prm.batch, hi, N, warp & 3, 4, lane);
+        mbar_arrive_warp(bar_bias, lane);
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_pub, ph, &abort_flag, prm.status, BAR_PUB))) break;   // -LSE, -D of the 128 queries
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
+      tc_fence_after();
       {
         uint32_t rs[64], rp[64];
         tmem_ld32(tST + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
@@ -370,24 +501,25 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_ld32(tdPT + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
         tmem_ld32(tdPT + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
         tmem_wait_ld();
-        // bias[query, key] of this key column
-        const float* bc = prm.bias ? prm.bias + static_cast<int64_t>(min(b, prm.batch - 1)) * prm.bsb + hi * prm.bsh + static_cast<int64_t>(min(ri, N - 1)) * prm.bsk : nullptr;
-        // dbias[query, key] is written here, where the lanes of a warp hold consecutive keys of one query: one
-        // coalesced store (or reduction) per query instead of 32 scattered ones
+        // bias[query, key] and dbias[query, key] of this key column: the lanes of a warp hold consecutive keys of one
+        // query, so that every store or reduction of a warp is one coalesced access
+        const float* bc = (prm.bias && row_ok) ? sb_seq + ri : nullptr;
         float* dbc = (prm.dbias && row_ok) ? prm.dbias + static_cast<int64_t>(b) * prm.dsb + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk : nullptr;
-        uint32_t pk[32], dsk[32];
+        const float* nl = nlse_s[ph] + 64 * seq;
+        const float* ndp = nd_s[ph] + 64 * seq;
+        uint32_t pk[32], dsk[32], zero[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           float pv[2], dv2[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int qq = i + e;                            // query index within the sequence
-            float a = nlse_s[64 * seq + qq];                 // -inf for queries that do not exist
-            if (bc && qq < N) a = fmaf(bc[static_cast<int64_t>(qq) * prm.bsq], 1.4426950408889634f, a);
+            float a = nl[qq];                                // -inf for queries that do not exist
+            if (bc && qq < N) a = fmaf(bc[qq * kBiasStride], 1.4426950408889634f, a);
             float p = fast_exp2(fmaf(__uint_as_float(rs[qq]), c, a));
             if (!row_ok) p = 0.f;                            // a key that does not exist
             pv[e] = p;
-            dv2[e] = p * (__uint_as_float(rp[qq]) + nd_s[64 * seq + qq]);
+            dv2[e] = p * (__uint_as_float(rp[qq]) + ndp[qq]);
             if (dbc && qq < N) {
               if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]); else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
             }
@@ -395,47 +527,30 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           pk[i >> 1] = pack2<T>(pv[0], pv[1]);
           dsk[i >> 1] = pack2<T>(dv2[0], dv2[1]);
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) zero[i] = 0u;
         tmem_st32(tST + lane_off + 32 * seq, pk);                  // P^T over the tile's 128 queries
         tmem_st32(tST + lane_off + 32 * (1 - seq), zero);
         tmem_st32(tST + 64 + lane_off + 32 * seq, dsk);            // dS^T
         tmem_st32(tST + 64 + lane_off + 32 * (1 - seq), zero);
+        tmem_wait_st();
       }
-      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive_warp(bar_ph, lane);
-      alive = __all_sync(0xffffffffu, mbar_wait(bar_r2, 0, &abort_flag, prm.status, BAR_R2));
-    }
-    if (alive) {
+      mbar_arrive_warp(bar_phk, lane);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r2k, ph, &abort_flag, prm.status, BAR_R2K))) break;
       tc_fence_after();
-      // dQ of this row as a query, dV and dK of this row as a key
-#pragma unroll
-      for (int which = 0; which < 3; ++which) {
-        uint32_t r0[32], r1[32];
-        const uint32_t src = which == 0 ? tdP : (which == 1 ? tdPT : tdPT + 64);
-        tmem_ld32(src + lane_off, r0);
-        tmem_ld32(src + lane_off + 32, r1);
-        tmem_wait_ld();
-        if (!row_ok) continue;
-        const Strides st = which == 0 ? prm.dqs : (which == 1 ? prm.dvs : prm.dks);
-        T* dst = static_cast<T*>(which == 0 ? prm.dq : (which == 1 ? prm.dv : prm.dk)) + static_cast<int64_t>(b) * st.b + hi * st.h + static_cast<int64_t>(ri) * st.r;
-        const float f = which == 1 ? 1.f : prm.scale;
-#pragma unroll
-        for (int i = 0; i < 64; i += 8) {
-          if (i >= d) continue;
-          float o[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(i + e < 32 ? r0[(i + e) & 31] : r1[(i + e) & 31]) * f;
-          uint4 t;
-          t.x = pack2<T>(o[0], o[1]); t.y = pack2<T>(o[2], o[3]); t.z = pack2<T>(o[4], o[5]); t.w = pack2<T>(o[6], o[7]);
-          *reinterpret_cast<uint4*>(dst + i) = t;
-        }
-      }
+      T* dvp = row_ok ? static_cast<T*>(prm.dv) + static_cast<int64_t>(b) * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(ri) * prm.dvs.r : nullptr;
+      T* dkp = row_ok ? static_cast<T*>(prm.dk) + static_cast<int64_t>(b) * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(ri) * prm.dks.r : nullptr;
+      store_acc_row<T>(tdPT + lane_off, dvp, d, 1.f);
+      store_acc_row<T>(tdPT + 64 + lane_off, dkp, d, prm.scale);
+      tc_fence_before();
+      mbar_arrive_warp(bar_epi, lane);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, 512);
+  if (warp == 8) tmem_dealloc(tmem_base, 512);
 }
 
 }  // namespace
@@ -481,8 +596,9 @@ int win_tc_bwd(const BwdParams& p, int dtype, cudaStream_t st) {
       !p.out || !p.row_m || !p.row_z || (p.dbias && !p.bias))
     return ELSA_ERR_UNSUPPORTED;
   const int batch = p.bh / p.heads;
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mo;
   int rc;
+  if ((rc = make_tmap_rows64(&mo, p.out, dtype, p.n_ctx, p.heads, batch, p.os, 64, p.head_dim, 2)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mq, p.q, dtype, p.n_ctx, p.heads, batch, p.qs, 64, p.head_dim, 2)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mk, p.k, dtype, p.n_ctx, p.heads, batch, p.ks, 64, p.head_dim, 2)) != ELSA_OK) return rc;
   if ((rc = make_tmap_rows64(&mv, p.v, dtype, p.n_ctx, p.heads, batch, p.vs, 64, p.head_dim, 2)) != ELSA_OK) return rc;
@@ -496,13 +612,17 @@ int win_tc_bwd(const BwdParams& p, int dtype, cudaStream_t st) {
   prm.batch = batch; prm.heads = p.heads; prm.n_ctx = p.n_ctx; prm.head_dim = p.head_dim;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
-  const dim3 grid(static_cast<unsigned>((batch + 1) / 2), static_cast<unsigned>(p.heads));
+  // persistent: one CTA per SM at most, a multiple of the head count (a CTA stays with one head)
+  const int sms = sm_count();
+  const int n_pairs = (batch + 1) / 2;
+  const int groups = std::max(1, std::min(sms / p.heads, n_pairs));
+  const dim3 grid(static_cast<unsigned>(groups * p.heads));
   if (dtype == ELSA_F16) {
     if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_bwd_kernel<__half>), kWinBwdSmem)) != ELSA_OK) return rc;
-    win_tc_bwd_kernel<__half><<<grid, kThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, prm);
+    win_tc_bwd_kernel<__half><<<grid, kBwdThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, mo, prm);
   } else {
     if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&win_tc_bwd_kernel<__nv_bfloat16>), kWinBwdSmem)) != ELSA_OK) return rc;
-    win_tc_bwd_kernel<__nv_bfloat16><<<grid, kThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, prm);
+    win_tc_bwd_kernel<__nv_bfloat16><<<grid, kBwdThreads, kWinBwdSmem, st>>>(mq, mk, mv, mdo, mo, prm);
   }
   ELSA_LAUNCH_CHECK();
   return ELSA_OK;
