@@ -249,7 +249,9 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // own TMEM lane, and it has read everything it needs from a column range before it writes there.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int kBwdStageBytes = 5 * kTileBytes;       // Q, K, V, dO, out of one pair of sequences
-constexpr int kWinBwdSmem = 2 * kBwdStageBytes + kBiasBytes + 1024;   // two stages, bias, alignment slack
+constexpr int kBiasTile = 64 * kBiasStride;          // floats of one staged bias (or dbias) tile
+// two stages, three tiles (bias of the two sequences; or one bias tile and a dbias sum per sequence), alignment slack
+constexpr int kWinBwdSmem = 2 * kBwdStageBytes + 3 * kBiasTile * 4 + 1024;
 constexpr int kBwdThreads = 288;                     // 4 query-side warps, 4 key-side warps, 1 issuing warp
 
 enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PHQ = 77, BAR_PHK = 78, BAR_R2Q = 79, BAR_R2K = 80, BAR_EPI = 81, BAR_PUB = 82, BAR_BIAS = 83 };
@@ -307,7 +309,7 @@ __device__ __forceinline__ float neg_row_dot(const uint8_t* t_out, const uint8_t
 // heads).  The five tiles of the next pair are in flight while this one is computed (two stages of shared memory); a
 // bias that does not depend on the batch index is staged once.
 template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)     // (registers are granted as for 12 warps: 168 per thread)
 win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                   const __grid_constant__ CUtensorMap tmap_o, const WinBwdParams prm) {
@@ -353,7 +355,7 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const float c = prm.scale_log2;
   float* sb = reinterpret_cast<float*>(smem_al + 2 * kBwdStageBytes);
   const bool bias_per_batch = prm.bias && prm.bsb != 0;   // else one tile serves every pair of this head
-  const float* sb_seq = sb + (bias_per_batch ? seq * 64 * kBiasStride : 0);
+  const float* sb_seq = sb + (bias_per_batch ? seq * kBiasTile : 0);
 
   if (warp == 8) {
     if (lane == 0 && pair0 < n_pairs) {
@@ -480,8 +482,18 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   } else {
     // ---------------- key-side warps: thread = key row ----------------
+    // A bias gradient shared by the batch (with a bias that is, so that two tiles of the bias buffer are free) is summed
+    // over all the CTA's pairs in shared memory, one tile per sequence of the pair and every element by one thread only,
+    // and added to global memory once, at the end.
+    const bool dbias_local = prm.dbias && prm.dbias_atomic && prm.dsb == 0 && !bias_per_batch;
+    float* dacc = sb + (1 + seq) * kBiasTile + ri;         // this thread's column of its sequence's tile
+    if (dbias_local) {
+      for (int qq = 0; qq < 64; ++qq) dacc[qq * kBiasStride] = 0.f;
+    }
+    bool completed = true;
     int it = 0;
     for (int pair = pair0; pair < n_pairs; pair += pair_step, ++it) {
+      completed = false;
       const uint32_t ph = it & 1;
       const int b = 2 * pair + seq;
       const bool row_ok = b < prm.batch && ri < N;
@@ -521,7 +533,9 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             pv[e] = p;
             dv2[e] = p * (__uint_as_float(rp[qq]) + ndp[qq]);
             if (dbc && qq < N) {
-              if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]); else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
+              if (dbias_local) dacc[qq * kBiasStride] += dv2[e];
+              else if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]);
+              else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
             }
           }
           pk[i >> 1] = pack2<T>(pv[0], pv[1]);
@@ -545,6 +559,11 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       store_acc_row<T>(tdPT + 64 + lane_off, dkp, d, prm.scale);
       tc_fence_before();
       mbar_arrive_warp(bar_epi, lane);
+      completed = true;
+    }
+    if (dbias_local && completed && ri < N) {                // (nothing is added after a wait that gave up)
+      float* dst = prm.dbias + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk;
+      for (int qq = 0; qq < N; ++qq) atomicAdd(dst + static_cast<int64_t>(qq) * prm.dsq, dacc[qq * kBiasStride]);
     }
   }
 

@@ -264,3 +264,45 @@ def test_first_cuda_call_of_a_thread_may_be_the_backward():
     again = E.twopass_attention_backward(q, k, v, out, do, row_m=rm, row_z=rz)
     for x, y in zip(res["g"], again):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("b,h,n,d,dtype,bias_kind", [
+    (301, 3, 49, 32, F16, "1hnn"),      # odd batch, a bias shared by the batch (staged once per CTA), dbias by reduction
+    (77, 2, 64, 64, BF16, "bhnn"),      # a bias per sequence (staged for every pair), dbias by plain stores
+    (150, 4, 49, 32, F16, None),
+    (333, 5, 16, 24, BF16, "hnn"),
+])
+def test_many_windows_per_cta_vs_fp64_and_fma(b, h, n, d, dtype, bias_kind):
+    """More pairs of sequences than CTAs: the persistent backward walks several pairs per CTA through its two stages
+    of shared memory and its barrier phases.  Checked against fp64 autograd on the GPU and against the FP32-FMA
+    kernels of the same library."""
+    from elsa_b200 import _lib
+    from elsa_b200.attention import _forward_impl
+    from elsa_b200.attention_bwd import _backward_impl
+    q = U.seeded((b, h, n, d), dtype, 110, 0.5).to(DEV)
+    k = U.seeded((b, h, n, d), dtype, 111, 0.5).to(DEV)
+    v = U.seeded((b, h, n, d), dtype, 112).to(DEV)
+    do = U.seeded((b, h, n, d), dtype, 113, 0.25).to(DEV)
+    bias = make_bias(bias_kind, b, h, n, 114)
+    bias = None if bias is None else bias.to(DEV)
+    res = {}
+    for tag, fl in (("tc", 0), ("fma", _lib.FLAG_FORCE_SIMT)):
+        o, rm, rz = _forward_impl(q, k, v, bias=bias, is_causal=False, summary_dtype=dtype, part_width=0, q_chunk=0,
+                                  want_state=True, flags=fl)[:3]
+        g = _backward_impl(q, k, v, o, do, bias=bias, is_causal=False, row_m=rm, row_z=rz, want_dbias=bias is not None,
+                           flags=fl)
+        res[tag] = (o,) + tuple(g)
+    q64, k64, v64 = (t.double().requires_grad_(True) for t in (q, k, v))
+    b64 = None if bias is None else bias.double().requires_grad_(True)
+    s64 = q64 @ k64.transpose(-1, -2) / d ** 0.5
+    if b64 is not None:
+        s64 = s64 + b64
+    o64 = torch.softmax(s64, dim=-1) @ v64
+    o64.backward(do.double())
+    refs = [o64.detach(), q64.grad, k64.grad, v64.grad] + ([] if b64 is None else [b64.grad])
+    lim = {F16: 2e-3, BF16: 1.6e-2}[dtype]
+    for i, ref in enumerate(refs):
+        scale = max(1.0, float(ref.abs().max()))
+        assert U.max_abs(res["tc"][i].double().cpu(), ref.cpu()) <= lim * scale, i
+        # the two kernel families round P and dS at different points: a few output ulps apart
+        assert U.max_abs(res["tc"][i].double().cpu(), res["fma"][i].double().cpu()) <= lim * scale, i
