@@ -729,7 +729,7 @@ def main():
                     torch.cuda.synchronize()
                     k2 = max(5, min(200, int(300.0 / max(timed(w2.step, 3), 1e-3))))       # about 0.3 s
                     ms2 = timed(w2.step, k2)
-                    tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(w2.dtype), w2.d, w2.n, int(w2.use_bias), int(w2.causal), 1))
+                    tc = bool(lib.elsa_uses_tensor_cores_for(_lib.dtype_code(w2.dtype), w2.d, w2.n, int(w2.use_bias), int(w2.causal), 1, w2.b, w2.h))
                     tf = (w2.fwd_f + w2.bwd_f) / (ms2 * 1e-3) / 1e12
                     split3 = tc and w2.dtype == torch.float32
                     peak = (pk["tflops_sustained"] / (FP32_TC_MMAS if split3 else 1.0)) if tc else fma
@@ -751,7 +751,7 @@ def main():
 
     if rank == 0:
         sampler.stop()
-        uses_tc = bool(lib.elsa_uses_tensor_cores(_lib.dtype_code(dtype), d, n, int(wl.use_bias), int(causal), 1))
+        uses_tc = bool(lib.elsa_uses_tensor_cores_for(_lib.dtype_code(dtype), d, n, int(wl.use_bias), int(causal), 1, b, h))
         bwd_sus = bwd_ms * k_split
         fwd_sus = fwd_ms * k_split
         achieved = bwd_f / (bwd_sus * 1e-3) / 1e12

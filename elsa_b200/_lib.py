@@ -29,6 +29,7 @@ SIGNATURES = {
     "elsa_debug_wait_timeout": (c_int, [c_uint64, _P]),
     "elsa_debug_fma_rate": (c_int, [_P, c_int, c_int64, c_int, _P]),
     "elsa_uses_tensor_cores": (c_int, [c_int] * 6),
+    "elsa_uses_tensor_cores_for": (c_int, [c_int] * 8),
     "elsa_phase1_fold": (c_int, [_P, _P, _P, *_BIAS, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_uint, _P]),
     "elsa_phase1_fold_shard": (c_int, [_P, _P, _P, _P, _P, _P] + [c_int] * 11 + [c_uint, _P]),

@@ -13,6 +13,21 @@ namespace elsa {
 thread_local int g_last_cuda_error = 0;
 std::atomic<long long> g_kernel_launches{0};
 
+// sequences shorter than this run on the FP32-FMA kernels (the tensor-core kernels work on 128-row tiles)
+#ifndef ELSA_TC_MIN_TOKENS
+#define ELSA_TC_MIN_TOKENS 512
+#endif
+constexpr int kTcMinTokens = ELSA_TC_MIN_TOKENS;
+// ... unless the problem has at least this many rows in total (batch * heads * tokens): from there on the 128-row tiles
+// fill the machine, and the tensor-core kernels are 3-10 times faster from 65 tokens on (the window kernels take the
+// 16-bit sequences of at most 64).  Below it both families are bound by the launch path.
+#ifndef ELSA_TC_MIN_ROWS
+#define ELSA_TC_MIN_ROWS 4096
+#endif
+static bool tc_tokens_ok(int n_ctx, int bh) {
+  return n_ctx >= kTcMinTokens || (n_ctx > 64 && static_cast<int64_t>(bh) * n_ctx >= ELSA_TC_MIN_ROWS);
+}
+
 static int g_sm_count_cache[64] = {0};
 
 int sm_count() {
@@ -71,25 +86,25 @@ struct ForwardPlan {
   int sets;                   // 1, or 2 when a ping-pong pass (scan steps / tree) was requested
 };
 
-static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tc_forward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   // tcgen05 fold: 16-bit inputs, head dim 64, no bias; short sequences stay on the FP32-FMA kernel
   // (one 64-row CTA per tile keeps more SMs busy than a 256-row CTA does when N is a few hundred).
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
-  return n_ctx >= 512 && fold_tc_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && fold_tc_supported(dtype, head_dim, has_bias);
 }
 
 // 16-bit inputs with 64 < head dim <= 128, or with a bias and any head dim up to 128, on the tensor cores
 // (fold_tcw.cu / bwd_tcw.cu: one 128-row tile per CTA)
-static bool tcw_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tcw_forward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
-  return n_ctx >= 512 && fold_tcw_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && fold_tcw_supported(dtype, head_dim, has_bias);
 }
 
 // fp32 on the tensor cores: head dim up to 64, and long enough that 128-row tiles fill the machine better than the
 // FP32-FMA kernel's 64-row tiles do
-static bool tc3_forward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tc3_forward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
-  return n_ctx >= 512 && fold_tc3_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && fold_tc3_supported(dtype, head_dim, has_bias);
 }
 
 static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, int is_causal,
@@ -99,9 +114,9 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
     return ELSA_ERR_INVALID_ARGUMENT;
   const int64_t bh = static_cast<int64_t>(batch) * heads;
   if (bh > 65535) return ELSA_ERR_UNSUPPORTED;
-  pl->split3 = tc3_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  const bool wide = tcw_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
-  pl->tensor_cores = pl->split3 || wide || tc_forward_ok(dtype, head_dim, n_ctx, has_bias, flags);
+  pl->split3 = tc3_forward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias, flags);
+  const bool wide = tcw_forward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias, flags);
+  pl->tensor_cores = pl->split3 || wide || tc_forward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias, flags);
   pl->tile_m = (pl->split3 || wide) ? 128 : (pl->tensor_cores ? 256 : 64);   // query rows per CTA
   pl->tile_n = pl->tensor_cores ? 128 : 64;                          // keys per tile
   const int tiles_n = static_cast<int>(cdiv64(n_ctx, pl->tile_n));
@@ -206,12 +221,12 @@ static int phase1_dispatch(const void* q, const void* k, const void* v, const fl
     if (src != ELSA_OK) return src;
     return fold_tc3(p, st);
   }
-  if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
+  if (part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags)) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return fold_tc(p, dtype, st);
   }
-  if (part_width % 128 == 0 && tcw_forward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags)) {
+  if (part_width % 128 == 0 && tcw_forward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags)) {
     const int src = check_device_status();
     if (src != ELSA_OK) return src;
     return fold_tcw(p, dtype, st);
@@ -254,18 +269,26 @@ extern "C" int elsa_debug_wait_timeout(uint64_t limit_ns, void* stream) {
 
 extern "C" int64_t elsa_kernel_launches(void) { return static_cast<int64_t>(g_kernel_launches.load()); }
 
-static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
-static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
-static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags);
+static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags);
+static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags);
+static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags);
 
-extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
+extern "C" int elsa_uses_tensor_cores_for(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward,
+                                          int batch, int heads) {
+  if (batch < 1 || heads < 1) return 0;
   // sequences of at most 64 tokens, 16-bit, not causal: two per tensor-core tile, forward and backward (win_tc.cu)
   if (n_ctx >= 1 && n_ctx <= 64 && win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) return 1;
+  const int bh = static_cast<int>(std::min<int64_t>(static_cast<int64_t>(batch) * heads, 1 << 30));
   if (backward)
-    return (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ||
-            tcw_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
-  return (tc_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u) ||
-          tcw_forward_ok(dtype, head_dim, n_ctx, has_bias != 0, 0u)) ? 1 : 0;
+    return (tc_backward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u) || tc3_backward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u) ||
+            tcw_backward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u)) ? 1 : 0;
+  return (tc_forward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u) || tc3_forward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u) ||
+          tcw_forward_ok(dtype, head_dim, n_ctx, bh, has_bias != 0, 0u)) ? 1 : 0;
+}
+
+// the answer for a single (batch, head): what holds whatever the batch size
+extern "C" int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward) {
+  return elsa_uses_tensor_cores_for(dtype, head_dim, n_ctx, has_bias, is_causal, backward, 1, 1);
 }
 
 extern "C" int elsa_phase1_fold(const void* q, const void* k, const void* v, const float* bias, int64_t bias_stride_b,
@@ -292,7 +315,7 @@ extern "C" int elsa_phase1_fold_shard(const void* q, const void* k, const void* 
 extern "C" int64_t elsa_phase1_fold_shard_workspace_bytes(int dtype, int batch, int heads, int n_ctx, int head_dim,
                                                           int n_keys, unsigned flags) {
   if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 1 || head_dim < 1 || head_dim > 128 || n_keys < 0) return -1;
-  if (n_keys == 0 || !tc3_forward_ok(dtype, head_dim, n_ctx, false, flags)) return 0;
+  if (n_keys == 0 || !tc3_forward_ok(dtype, head_dim, n_ctx, batch * heads, false, flags)) return 0;
   return fold_tc3_plane_bytes(batch * heads, n_ctx) + 2 * fold_tc3_plane_bytes(batch * heads, n_keys);
 }
 
@@ -496,21 +519,21 @@ extern "C" int elsa_twopass_forward_strided(const void* q, const void* k, const 
 }
 
 // ---- backward -------------------------------------------------------------------------------
-static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tc_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
-  return n_ctx >= 512 && bwd_tc_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && bwd_tc_supported(dtype, head_dim, has_bias);
 }
 
 // fp32 on the tensor cores (16-bit planes per operand): head dim up to 64, with or without a bias (and its gradient)
-static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tc3_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   if (flags & (ELSA_FLAG_FORCE_SIMT | ELSA_FLAG_FP32_FMA)) return false;
-  return n_ctx >= 512 && bwd_tc3_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && bwd_tc3_supported(dtype, head_dim, has_bias);
 }
 
 // 16-bit inputs with 64 < head dim <= 128, or with a bias (and its gradient) and any head dim up to 128 (bwd_tcw.cu)
-static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, bool has_bias, unsigned flags) {
+static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has_bias, unsigned flags) {
   if (flags & ELSA_FLAG_FORCE_SIMT) return false;
-  return n_ctx >= 512 && bwd_tcw_supported(dtype, head_dim, has_bias);
+  return tc_tokens_ok(n_ctx, bh) && bwd_tcw_supported(dtype, head_dim, has_bias);
 }
 
 static int64_t bwd_state_bytes(int batch, int heads, int n_ctx) {
@@ -521,11 +544,11 @@ extern "C" int64_t elsa_backward_workspace_bytes(int dtype, int batch, int heads
                                                  int has_bias, int is_causal, unsigned flags) {
   (void)is_causal;
   if (!dtype_ok(dtype) || batch < 1 || heads < 1 || n_ctx < 0 || head_dim < 1 || head_dim > 128) return -1;
-  if (tc_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags)) return bwd_tc_workspace_bytes(batch * heads, n_ctx);
+  if (tc_backward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias != 0, flags)) return bwd_tc_workspace_bytes(batch * heads, n_ctx);
   // (the fp32 tensor-core route is not taken when dbias is asked for: the larger of the two needs covers both)
-  if (tc3_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags))
+  if (tc3_backward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias != 0, flags))
     return std::max(bwd_tc3_workspace_bytes(batch * heads, n_ctx, n_ctx), 2 * bwd_state_bytes(batch, heads, n_ctx));
-  if (tcw_backward_ok(dtype, head_dim, n_ctx, has_bias != 0, flags))
+  if (tcw_backward_ok(dtype, head_dim, n_ctx, batch * heads, has_bias != 0, flags))
     return std::max(bwd_tcw_workspace_bytes(batch * heads, n_ctx), 2 * bwd_state_bytes(batch, heads, n_ctx));
   return 2 * bwd_state_bytes(batch, heads, n_ctx);  // row_d, row_lse
 }
@@ -551,11 +574,11 @@ static int backward_impl(const void* q, const void* k, const void* v, const void
   char* ws = static_cast<char*>(workspace);
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
-  const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
-  const bool use_tc3 = (dbias == nullptr || bias != nullptr) && tc3_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+  const bool use_tc = dbias == nullptr && tc_backward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags);
+  const bool use_tc3 = (dbias == nullptr || bias != nullptr) && tc3_backward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags);
   // (the wide-head kernels also take biased problems, with or without a bias gradient)
   const bool use_tcw = !use_tc && !use_tc3 && (dbias == nullptr || bias != nullptr) &&
-                       tcw_backward_ok(dtype, head_dim, n_ctx, bias != nullptr, flags);
+                       tcw_backward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags);
   const Strides cs = contiguous_strides(heads, n_ctx, head_dim);
   const Strides os = st8 ? st8[3] : cs;
   BwdParams p;
@@ -664,9 +687,9 @@ extern "C" int elsa_twopass_backward_shard(const void* q, const void* k_shard, c
   float* row_d = reinterpret_cast<float*>(ws);
   float* row_lse = reinterpret_cast<float*>(ws + bwd_state_bytes(batch, heads, n_ctx));
   // (the tensor-core kernels address the fp32 dQ of a shard as 64-wide rows)
-  const bool use_tc = n_keys > 0 && head_dim == 64 && tc_backward_ok(dtype, head_dim, n_ctx, false, flags);
-  const bool use_tc3 = n_keys > 0 && n_keys <= n_ctx && tc3_backward_ok(dtype, head_dim, n_ctx, false, flags);
-  const bool use_tcw = n_keys > 0 && tcw_backward_ok(dtype, head_dim, n_ctx, false, flags);
+  const bool use_tc = n_keys > 0 && head_dim == 64 && tc_backward_ok(dtype, head_dim, n_ctx, batch * heads, false, flags);
+  const bool use_tc3 = n_keys > 0 && n_keys <= n_ctx && tc3_backward_ok(dtype, head_dim, n_ctx, batch * heads, false, flags);
+  const bool use_tcw = n_keys > 0 && tcw_backward_ok(dtype, head_dim, n_ctx, batch * heads, false, flags);
   int rc = ELSA_OK;
   if (!use_tc && !use_tc3 && !use_tcw) rc = elsa_bwd_preprocess(out, dout, row_m, row_z, row_d, row_lse, dtype, batch * heads, n_ctx, head_dim, stream);
   if (rc != ELSA_OK) return rc;

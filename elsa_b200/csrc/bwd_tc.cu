@@ -488,7 +488,9 @@ bwd_preprocess_pad_kernel(const T* __restrict__ out, const T* __restrict__ dout,
   if (in_pad && lane == 0) {
     if (real) {
       nd_pad[prow] = -part;
-      nlse_pad[prow] = -(row_m[b * n_ctx + r] + log2f(fmaxf(row_z[b * n_ctx + r], 1.0e-30f)));
+      // (a row whose keys are all masked by the bias has m = -inf, z = 0: -LSE = -inf keeps its P at 0)
+      const float rm = row_m[b * n_ctx + r], rz = row_z[b * n_ctx + r];
+      nlse_pad[prow] = (rz > 0.f && rm > -CUDART_INF_F) ? -(rm + log2f(rz)) : -CUDART_INF_F;
     } else {
       nd_pad[prow] = 0.f;
       nlse_pad[prow] = -CUDART_INF_F;

@@ -83,6 +83,13 @@ CASES = [
     (2, 2, 640, 64, F32, False, "bhnn"),
     (1, 3, 900, 40, F32, True, "hnn"),
     (2, 2, 1024, 32, F32, False, "b1nn"),
+    # 65 to 511 tokens with at least 4096 rows in total: the tensor-core kernels
+    (24, 3, 197, 64, F16, False, None),
+    (6, 4, 257, 64, BF16, True, None),
+    (12, 3, 197, 32, F32, False, None),
+    (12, 3, 150, 64, F16, False, "1hnn"),
+    (8, 3, 197, 96, BF16, False, None),
+    (10, 3, 160, 40, F32, True, "bhnn"),
     # sequences of at most 64 tokens, 16-bit: two per tensor-core tile (odd batch: the last tile is half empty)
     (5, 3, 49, 32, BF16, False, "1hnn"),
     (3, 2, 64, 64, F16, False, "bhnn"),
@@ -138,7 +145,7 @@ def test_train_vs_oracle_and_fp64(case):
         assert U.max_abs(biasd.grad, b64.grad) <= lim * max(1.0, float(b64.grad.abs().max()))
 
 
-@pytest.mark.parametrize("b,n,d", [(1, 150, 64), (3, 49, 32)])
+@pytest.mark.parametrize("b,n,d", [(1, 150, 64), (3, 49, 32), (28, 150, 64), (4, 640, 64)])
 def test_backward_is_deterministic_and_masked_rows_are_zero(b, n, d):
     h = 2
     q, k, v, do = (U.seeded((b, h, n, d), F16, 70 + i).to(DEV) for i in range(4))

@@ -148,6 +148,13 @@ CASES = [
     (2, 2, 640, 64, F32, False, "bhnn", None, None),
     (1, 3, 900, 40, F32, True, "hnn", None, None),
     (2, 2, 1024, 32, F32, False, "b1nn", None, None),
+    # 65 to 511 tokens with at least 4096 rows in total: tensor cores as well (ViT at 224 x 224: 197 tokens)
+    (24, 3, 197, 64, F16, False, None, 256, None),
+    (8, 4, 300, 128, BF16, False, None, 384, None),
+    (16, 2, 145, 32, F32, True, None, None, None),
+    (12, 3, 197, 64, F16, False, "1hnn", 256, None),
+    (40, 2, 70, 64, BF16, True, None, 128, None),
+    (12, 3, 197, 48, F32, False, "hnn", None, None),
 ]
 
 
@@ -169,7 +176,12 @@ def test_forward_vs_oracle(case):
                                                  bias=None if bias is None else bias.to(DEV), is_causal=causal,
                                                  block_n=block_n, q_chunk_size=q_chunk)
     assert out.dtype == dtype and out.shape == q.shape
-    assert U.out_close(out, ref_out, dtype) <= 1.0
+    # The d <= 64 tensor-core fold rounds P to fp16 relative to a reference maximum that may lag the true one by up to
+    # 2^8 (lazy rescale), the oracle relative to the true one: the two summaries can round to neighbouring fp16 values,
+    # and on top of the final rounding an output in [0.5, 1) may then sit two spacings (9.8e-4) from the oracle's.  With
+    # a few hundred keys per row outputs that large exist among the 900 000 of this case.
+    worst = 2.0 if (dtype == F16 and bias_kind is None and 64 < n < 512 and b * h * n >= 4096) else 1.0
+    assert U.out_close(out, ref_out, dtype) <= worst
     check_state(rm, rz, ref_m, ref_z, dtype)
     truth = O.softmax_attention_fp64(q, k, v, bias=bias, is_causal=causal)
     # exact arithmetic: fp32 at the stated bound; 16-bit paths carry the rounding of P and of s that the
@@ -343,4 +355,7 @@ def test_routing_of_small_head_dims_and_fp32():
                 for d in (32, 64):
                     assert lib.elsa_uses_tensor_cores(dt, d, 640, bias, 0, backward) == 1, (dt, d, backward)
             assert lib.elsa_uses_tensor_cores(dt, 36, 640, 0, 0, backward) == 0      # not a multiple of 8
-            assert lib.elsa_uses_tensor_cores(dt, 64, 200, 0, 0, backward) == 0      # short sequence
+            assert lib.elsa_uses_tensor_cores(dt, 64, 200, 0, 0, backward) == 0      # short sequence, any batch
+            assert lib.elsa_uses_tensor_cores_for(dt, 64, 200, 0, 0, backward, 1, 3) == 0
+            assert lib.elsa_uses_tensor_cores_for(dt, 64, 200, 0, 0, backward, 8, 3) == 1   # 4800 rows in total
+            assert lib.elsa_uses_tensor_cores_for(dt, 64, 640, 0, 0, backward, 1, 1) == 1
