@@ -82,7 +82,7 @@ int elsa_debug_fma_rate(float* sink, int blocks, int64_t iters, int packed, void
 /* number of kernels this library has launched in this process so far (all threads, all streams) */
 int64_t elsa_kernel_launches(void);
 /* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run.  Covered, from 512
- * tokens on, with or without a bias (and its gradient): fp16 and bf16 inputs with a head dim that is a multiple of 8 up
+ * tokens on (see elsa_uses_tensor_cores_for for shorter sequences), with or without a bias (and its gradient): fp16 and bf16 inputs with a head dim that is a multiple of 8 up
  * to 128; fp32 inputs with a head dim that is a multiple of 8 up to 64.  Also covered: fp16 and bf16 sequences of at
  * most 64 tokens (attention windows) with a head dim that is a multiple of 8 up to 64, not causal, with or without a bias
  * (and its gradient), two sequences per 128-row tile. */
