@@ -437,7 +437,8 @@ def measure_seq_sharded(dev, rank, world, dist, steps=2):
 
 def measure_models(dev, rank, world, dist, steps=5):
     """Whole-model training steps through the drop-in hooks, data-parallel over the ranks: ViT-Tiny at 1024 x 1024
-    (4097 tokens per image) and Swin-T at 224 x 224, batch 8 per GPU, fp16 weights and activations, random pixels and
+    (4097 tokens per image) and Swin-T at 224 x 224, batch 8 per GPU, and ViT-Tiny at 224 x 224 (197 tokens per image),
+    batch 64 per GPU; fp16 weights and activations, random pixels and
     labels; a step = forward + cross-entropy + backward + the bucketed all-reduce of the parameter gradients (overlapped
     with the backward).  With one rank the same, unpatched model (PyTorch SDPA / plain window attention) is timed too."""
     import copy
@@ -445,15 +446,17 @@ def measure_models(dev, rank, world, dist, steps=5):
     import elsa_b200 as E
     from elsa_b200 import vision
     res = {}
-    for name, build, img in (("vit_tiny_1024", lambda: vision.vit_tiny(1024), 1024), ("swin_tiny_224", lambda: vision.swin_tiny(224), 224)):
+    for name, build, img, bsz in (("vit_tiny_1024", lambda: vision.vit_tiny(1024), 1024, 8),
+                                  ("swin_tiny_224", lambda: vision.swin_tiny(224), 224, 8),
+                                  ("vit_tiny_224", lambda: vision.vit_tiny(224), 224, 64)):
         try:
             torch.manual_seed(17)
             base = build().to(dev, torch.float16)
             ours = copy.deepcopy(base)
             rep = E.patch_timm_attention_train(ours)
             g = torch.Generator().manual_seed(99 + rank)
-            x = torch.randn(8, 3, img, img, generator=g).to(dev, torch.float16)
-            y = torch.randint(0, 1000, (8,), generator=g).to(dev)
+            x = torch.randn(bsz, 3, img, img, generator=g).to(dev, torch.float16)
+            y = torch.randint(0, 1000, (bsz,), generator=g).to(dev)
             sync = vision.BucketedGradientAllReduce(ours)
 
             def train(model, exchange):
@@ -464,7 +467,7 @@ def measure_models(dev, rank, world, dist, steps=5):
                         sync.finish()
                 return one
 
-            entry = {"batch_per_gpu": 8, "n_gpus": world, "attention_modules_patched": rep.total,
+            entry = {"batch_per_gpu": bsz, "n_gpus": world, "attention_modules_patched": rep.total,
                      "grad_exchange": "none (one rank)" if world == 1 else f"{len(sync.buckets)} buckets, async all_reduce(SUM) per bucket, overlapped with backward"}
             for tag, model, exch in (("elsa_b200", ours, True),) + ((("unpatched", base, False),) if world == 1 else ()):
                 f = train(model, exch)
@@ -478,7 +481,7 @@ def measure_models(dev, rank, world, dist, steps=5):
                     t = torch.tensor([ms], device=dev)
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                     ms = float(t.item())
-                entry[tag] = {"ms_per_step": ms, "images_per_s": world * 8 / (ms * 1e-3)}
+                entry[tag] = {"ms_per_step": ms, "images_per_s": world * bsz / (ms * 1e-3)}
                 if world == 1:
                     # the same step replayed from a CUDA graph: what the GPU needs once the host's per-op overhead
                     # (which bounds both models at this batch size) is out of the picture

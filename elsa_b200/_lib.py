@@ -103,3 +103,14 @@ def dtype_code(dtype) -> int:
     if dtype == torch.bfloat16:
         return ELSA_BF16
     raise ValueError("supported dtypes are fp16, bf16, and fp32")
+
+
+def raw_stream(device) -> int:
+    """cudaStream_t of torch's current stream on `device` as an integer (the private raw getter when this torch has
+    it: an order of magnitude cheaper than building a Stream object per call)."""
+    import torch
+    getter = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if getter is not None:
+        idx = device.index
+        return int(getter(torch.cuda.current_device() if idx is None else idx))
+    return int(torch.cuda.current_stream(device).cuda_stream)

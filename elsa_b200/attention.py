@@ -228,7 +228,7 @@ def _forward_impl(q, k, v, *, bias, is_causal, summary_dtype, part_width, q_chun
         raise ValueError("elsa_b200: unsupported problem size for the forward")
     with _DeviceScope(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
-        stream = torch.cuda.current_stream(q.device).cuda_stream
+        stream = _lib.raw_stream(q.device)
         rm_p = None if row_m is None else row_m.data_ptr()
         rz_p = None if row_z is None else row_z.data_ptr()
         if strided:

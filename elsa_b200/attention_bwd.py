@@ -79,7 +79,7 @@ def _row_stats(q_c, k_c, meta, is_causal):
         ws = torch.empty((max(int(nbytes), 256),), device=q_c.device, dtype=torch.uint8)
         rc = lib.elsa_row_stats(q_c.data_ptr(), k_c.data_ptr(), *meta.c_args(), row_m.data_ptr(), row_z.data_ptr(),
                                 ws.data_ptr(), ws.numel(), dt, batch, heads, seq_len, head_dim,
-                                int(bool(is_causal)), torch.cuda.current_stream(q_c.device).cuda_stream)
+                                int(bool(is_causal)), _lib.raw_stream(q_c.device))
     _lib.check(rc, "elsa_row_stats")
     return row_m, row_z
 
@@ -133,7 +133,7 @@ def _backward_impl(q, k, v, out, grad_out, *, bias, is_causal, row_m, row_z, wan
         raise ValueError("elsa_b200: unsupported problem size for the backward")
     with _DeviceScope(q.device):
         ws = torch.empty((max(int(nbytes), 256),), device=q.device, dtype=torch.uint8)
-        stream = torch.cuda.current_stream(q.device).cuda_stream
+        stream = _lib.raw_stream(q.device)
         if strided:
             rc = lib.elsa_twopass_backward_strided(
                 q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), out_c.data_ptr(), go_c.data_ptr(),
