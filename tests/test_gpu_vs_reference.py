@@ -144,6 +144,11 @@ CASES = {
     "tc_f16_n1000_causal": (1, 4, 1000, 64, F16, True, None, 1.0, {}, True),
     "tc_bf16_n1000": (1, 4, 1000, 64, BF16, False, None, 1.0, {}, True),
     "tc_bf16_n640_causal": (1, 4, 640, 64, BF16, True, None, 1.0, {}, True),
+    # 65 to 511 tokens with enough rows for the tensor-core kernels (ViT at 224 x 224: 197 tokens)
+    "tc_vit224_f16": (64, 3, 197, 64, F16, False, None, 1.0, {}, True),
+    "tc_vit224_bf16_causal": (32, 3, 197, 64, BF16, True, None, 1.0, {}, True),
+    "tc_vit224_f32": (32, 3, 197, 64, F32, False, None, 1.0, {}, True),
+    "tc_bias_f16_n128_d32": (64, 3, 128, 32, F16, False, "h", 1.0, {}, True),
     # benchmark configurations
     "cfg_fp32_1k": (1, 8, 1024, 64, F32, False, None, 1.0, {}, True),
     "cfg_vit_f16_4097": (8, 3, 4097, 64, F16, False, None, 1.0, {}, True),
