@@ -276,7 +276,7 @@ static bool tcw_backward_ok(int dtype, int head_dim, int n_ctx, int bh, bool has
 extern "C" int elsa_uses_tensor_cores_for(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward,
                                           int batch, int heads) {
   if (batch < 1 || heads < 1) return 0;
-  // sequences of at most 64 tokens, 16-bit, not causal: two per tensor-core tile, forward and backward (win_tc.cu)
+  // sequences of at most 64 tokens, 16-bit: two per tensor-core tile, forward and backward (win_tc.cu)
   if (n_ctx >= 1 && n_ctx <= 64 && win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) return 1;
   const int bh = static_cast<int>(std::min<int64_t>(static_cast<int64_t>(batch) * heads, 1 << 30));
   if (backward)
@@ -448,7 +448,7 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
       const float sl2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(head_dim))) * 1.4426950408889634);
       return win_tc_fwd(q, qs ? *qs : cs0, k, ks ? *ks : cs0, v, vs ? *vs : cs0, bias, bias_stride_b, bias_stride_h,
                         bias_stride_q, bias_stride_k, out, os ? *os : cs0, row_m, row_z, dtype, summary_dtype, batch, heads,
-                        n_ctx, head_dim, sl2, st);
+                        n_ctx, head_dim, sl2, is_causal, st);
     }
     return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, nullptr, nullptr,
                            nullptr, dtype, summary_dtype, batch, heads, n_ctx, head_dim, 0, n_ctx, pl.part_width, 1,

@@ -80,7 +80,7 @@ bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal);
 int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void* v, Strides vs, const float* bias,
                int64_t bsb, int64_t bsh, int64_t bsq, int64_t bsk, void* out, Strides os, float* row_m, float* row_z,
                int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, float scale_log2,
-               cudaStream_t st);
+               int is_causal, cudaStream_t st);
 int win_tc_bwd(const BwdParams& p, int dtype, cudaStream_t st);
 // tcgen05 fold for fp16 / bf16 inputs with 64 < head dim <= 128 (fold_tcw.cu)
 bool fold_tcw_supported(int dtype, int head_dim, bool has_bias);

@@ -1,5 +1,5 @@
 // Short sequences (49-token Swin windows and anything else of at most 64 tokens) on the 5th-generation tensor cores,
-// fp16 / bf16, head dim <= 64 (multiples of 8), optional additive bias, not causal: ONE launch, no partition summaries.
+// fp16 / bf16, head dim <= 64 (multiples of 8), optional additive bias, causal or not: ONE launch, no partition summaries.
 //
 // A 128-row tcgen05 tile holds TWO sequences of the same head: one 4-D TMA box (64 columns x 64 rows x 1 head x 2
 // batch entries) lands both in shared memory, each zero-padded to 64 rows and 64 columns by the box, as one 128 x 64
@@ -63,7 +63,7 @@ struct WinParams {
   void* out; Strides os;
   float* row_m; float* row_z;                   // [B*H, N] row state (log2 domain), or null
   const float* bias; int64_t bsb, bsh, bsq, bsk;
-  int batch, heads, n_ctx, head_dim, summary_dtype;
+  int batch, heads, n_ctx, head_dim, summary_dtype, causal;
   float scale_log2;
   int* status;
 };
@@ -163,7 +163,7 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
 #pragma unroll
       for (int i = 0; i < 64; ++i)
-        if (i >= N) sv[i] = -CUDART_INF_F;
+        if (i >= N || (prm.causal && i > qi)) sv[i] = -CUDART_INF_F;
       float mx[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
       for (int i = 4; i < 64; i += 4) {
@@ -262,7 +262,7 @@ struct WinBwdParams {
   const float* bias; int64_t bsb, bsh, bsq, bsk;
   float* dbias; int64_t dsb, dsh, dsq, dsk; int dbias_atomic;
   void* dq; void* dk; void* dv; Strides dqs, dks, dvs;
-  int batch, heads, n_ctx, head_dim;
+  int batch, heads, n_ctx, head_dim, causal;
   float scale, scale_log2;
   int* status;
 };
@@ -456,7 +456,7 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             float a = nlse;
             if (bp && kk < N) a = fmaf(bp[kk], 1.4426950408889634f, nlse);
             float p = fast_exp2(fmaf(__uint_as_float(rs[kk]), c, a));
-            if (kk >= N) p = 0.f;
+            if (kk >= N || (prm.causal && kk > ri)) p = 0.f;
             dsv[e] = p * (__uint_as_float(rp[kk]) + nd);
           }
           dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
@@ -529,7 +529,7 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             float a = nl[qq];                                // -inf for queries that do not exist
             if (bc && qq < N) a = fmaf(bc[qq * kBiasStride], 1.4426950408889634f, a);
             float p = fast_exp2(fmaf(__uint_as_float(rs[qq]), c, a));
-            if (!row_ok) p = 0.f;                            // a key that does not exist
+            if (!row_ok || (prm.causal && ri > qq)) p = 0.f;  // a key that does not exist, or one after the query
             pv[e] = p;
             dv2[e] = p * (__uint_as_float(rp[qq]) + ndp[qq]);
             if (dbc && qq < N) {
@@ -575,8 +575,9 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 }  // namespace
 
 bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal) {
+  (void)is_causal;   // both forms are covered
   return (dtype == ELSA_F16 || dtype == ELSA_BF16) && head_dim >= 8 && head_dim <= 64 && head_dim % 8 == 0 && n_ctx >= 1 &&
-         n_ctx <= 64 && !is_causal && fold_tc_supported(dtype, 64, false);
+         n_ctx <= 64 && fold_tc_supported(dtype, 64, false);
 }
 
 // q, k, v, out: [B, H, N <= 64, D <= 64] views with element strides; bias (fp32, may be null) with its four strides;
@@ -584,8 +585,8 @@ bool win_tc_supported(int dtype, int head_dim, int n_ctx, bool is_causal) {
 int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void* v, Strides vs, const float* bias,
                int64_t bsb, int64_t bsh, int64_t bsq, int64_t bsk, void* out, Strides os, float* row_m, float* row_z,
                int dtype, int summary_dtype, int batch, int heads, int n_ctx, int head_dim, float scale_log2,
-               cudaStream_t st) {
-  if (!win_tc_supported(dtype, head_dim, n_ctx, false)) return ELSA_ERR_UNSUPPORTED;
+               int is_causal, cudaStream_t st) {
+  if (!win_tc_supported(dtype, head_dim, n_ctx, is_causal != 0)) return ELSA_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
   int rc;
   // one box = 64 columns x 64 rows x 1 head x 2 batch entries: two sequences, each padded to 64 x 64 by the fill
@@ -596,6 +597,7 @@ int win_tc_fwd(const void* q, Strides qs, const void* k, Strides ks, const void*
   prm.out = out; prm.os = os; prm.row_m = row_m; prm.row_z = row_z;
   prm.bias = bias; prm.bsb = bsb; prm.bsh = bsh; prm.bsq = bsq; prm.bsk = bsk;
   prm.batch = batch; prm.heads = heads; prm.n_ctx = n_ctx; prm.head_dim = head_dim; prm.summary_dtype = summary_dtype;
+  prm.causal = is_causal ? 1 : 0;
   prm.scale_log2 = scale_log2;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   const dim3 grid(static_cast<unsigned>((batch + 1) / 2), static_cast<unsigned>(heads));
@@ -628,7 +630,7 @@ int win_tc_bwd(const BwdParams& p, int dtype, cudaStream_t st) {
   prm.bias = p.bias; prm.bsb = p.bsb; prm.bsh = p.bsh; prm.bsq = p.bsq; prm.bsk = p.bsk;
   prm.dbias = p.dbias; prm.dsb = p.dsb; prm.dsh = p.dsh; prm.dsq = p.dsq; prm.dsk = p.dsk; prm.dbias_atomic = p.dbias_atomic;
   prm.dq = p.dq; prm.dk = p.dk; prm.dv = p.dv; prm.dqs = p.dqs; prm.dks = p.dks; prm.dvs = p.dvs;
-  prm.batch = batch; prm.heads = p.heads; prm.n_ctx = p.n_ctx; prm.head_dim = p.head_dim;
+  prm.batch = batch; prm.heads = p.heads; prm.n_ctx = p.n_ctx; prm.head_dim = p.head_dim; prm.causal = p.is_causal ? 1 : 0;
   prm.scale = p.scale; prm.scale_log2 = p.scale_log2;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   // persistent: one CTA per SM at most, a multiple of the head count (a CTA stays with one head)

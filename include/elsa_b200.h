@@ -84,7 +84,7 @@ int64_t elsa_kernel_launches(void);
 /* 1 when the tcgen05 (tensor-core) kernels cover this problem, 0 when the FP32-FMA kernels run.  Covered, from 512
  * tokens on (see elsa_uses_tensor_cores_for for shorter sequences), with or without a bias (and its gradient): fp16 and bf16 inputs with a head dim that is a multiple of 8 up
  * to 128; fp32 inputs with a head dim that is a multiple of 8 up to 64.  Also covered: fp16 and bf16 sequences of at
- * most 64 tokens (attention windows) with a head dim that is a multiple of 8 up to 64, not causal, with or without a bias
+ * most 64 tokens (attention windows) with a head dim that is a multiple of 8 up to 64, causal or not, with or without a bias
  * (and its gradient), two sequences per 128-row tile. */
 int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward);
 /* The same question for a given batch size.  Sequences of 65 to 511 tokens also run on the tensor-core kernels when the

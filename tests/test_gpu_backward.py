@@ -98,6 +98,8 @@ CASES = [
     (2, 2, 7, 24, F16, False, None),
     (1, 1, 1, 8, BF16, False, None),
     (7, 2, 33, 40, F16, False, "nn"),
+    (5, 2, 49, 32, F16, True, None),          # causal windows
+    (4, 3, 64, 64, BF16, True, "1hnn"),
 ]
 
 

@@ -155,6 +155,10 @@ CASES = [
     (12, 3, 197, 64, F16, False, "1hnn", 256, None),
     (40, 2, 70, 64, BF16, True, None, 128, None),
     (12, 3, 197, 48, F32, False, "hnn", None, None),
+    # causal sequences of at most 64 tokens on the window kernels
+    (5, 2, 49, 32, F16, True, None, 64, 49),
+    (4, 3, 64, 64, BF16, True, "1hnn", 64, 64),
+    (3, 2, 17, 24, F16, True, "nn", 64, 17),
 ]
 
 
