@@ -221,6 +221,91 @@ class _TwopassAttentionAutograd(torch.autograd.Function):
         return dq, dk, dv, dbias, None, None, None
 
 
+# ---- packed projection output: the model hooks' path, kept short on the host ------------------------------------
+# Everything that depends only on the problem's shape (stride arrays for the C ABI, workspace sizes, dtype codes) is
+# built once per shape; a call then allocates its outputs, takes pointers and goes through ctypes.
+_PACKED_PLANS: dict = {}
+
+
+class _PackedPlan:
+    __slots__ = ("dt", "esize", "hd", "qkv_strides", "out_strides", "fwd_ws", "bwd_ws", "bwd_strides")
+
+    def __init__(self, qkv, has_bias, is_causal, summary_dtype, part_width, q_chunk):
+        batch, seq_len, _, heads, head_dim = map(int, qkv.shape)
+        self.dt = _lib.dtype_code(qkv.dtype)
+        self.esize = qkv.element_size()
+        self.hd = heads * head_dim
+        # (batch, head, row) element strides of the q / k / v views of [B, N, 3, H, D] and of out as [B, N, H, D]
+        packed = (seq_len * 3 * self.hd, head_dim, 3 * self.hd)
+        plain = (seq_len * self.hd, head_dim, self.hd)
+        self.qkv_strides = _i64x(packed)
+        self.out_strides = _i64x(plain)
+        self.fwd_ws = _cached_bytes("elsa_forward_workspace_bytes", self.dt, _lib.dtype_code(summary_dtype), batch, heads,
+                                    seq_len, head_dim, int(has_bias), int(is_causal), part_width, q_chunk, 0)
+        self.bwd_ws = _cached_bytes("elsa_backward_workspace_bytes", self.dt, batch, heads, seq_len, head_dim,
+                                    int(has_bias), int(is_causal), 0)
+        self.bwd_strides = {}                    # keyed by grad_out's strides: q, k, v, out, dout, dq, dk, dv
+
+    def backward_strides(self, gs):
+        arr = self.bwd_strides.get(gs)
+        if arr is None:
+            q = tuple(self.qkv_strides)
+            o = tuple(self.out_strides)
+            arr = self.bwd_strides[gs] = _i64x(q, q, q, o, gs, q, q, q)
+        return arr
+
+
+def _packed_plan(qkv, has_bias, is_causal, summary_dtype, part_width, q_chunk):
+    key = (tuple(qkv.shape), qkv.dtype, has_bias, is_causal, summary_dtype, part_width, q_chunk)
+    plan = _PACKED_PLANS.get(key)
+    if plan is None:
+        plan = _PACKED_PLANS[key] = _PackedPlan(qkv, has_bias, is_causal, summary_dtype, part_width, q_chunk)
+    return plan
+
+
+def _packed_fast_ok(qkv) -> bool:
+    """The short path reads q, k, v as three pointers into one contiguous [B, N, 3, H, D] buffer."""
+    return (qkv.device.type == "cuda" and qkv.is_contiguous() and int(qkv.shape[-1]) % 8 == 0 and 0 < int(qkv.shape[-1]) <= 128 and int(qkv.shape[1]) > 0
+            and qkv.data_ptr() % 16 == 0 and qkv.dtype in (torch.float16, torch.bfloat16, torch.float32))
+
+
+def _packed_forward_fast(qkv, bias32, is_causal, fwd_kwargs, want_state):
+    """The forward on a contiguous packed qkv: (out as [B, N, H, D], state or None, bias meta, plan).  `state` holds
+    row_m and row_z in one allocation, the second at a 256-byte boundary like a tensor of its own."""
+    batch, seq_len, _, heads, head_dim = map(int, qkv.shape)
+    kw = dict(fwd_kwargs)
+    kw.pop("reference_rounding", None)
+    summary_dtype, part_width, q_chunk = _resolve_common(
+        qkv, algorithm=kw.pop("algorithm", "auto"), input_precision=kw.pop("input_precision", "auto"),
+        summary_dtype=kw.pop("summary_dtype", None), block_m=kw.pop("block_m", None), block_n=kw.pop("block_n", None),
+        q_chunk_size=kw.pop("q_chunk_size", None), phase1_warps=kw.pop("phase1_warps", None),
+        phase2_warps=kw.pop("phase2_warps", None), phase1_stages=kw.pop("phase1_stages", None),
+        phase2_stages=kw.pop("phase2_stages", None))
+    if kw:
+        raise TypeError(f"unexpected keyword arguments: {sorted(kw)}")
+    meta = _canonical_bias(bias32, batch=batch, heads=heads, seq_len=seq_len, device=qkv.device)
+    plan = _packed_plan(qkv, meta.has_bias, bool(is_causal), summary_dtype, part_width, q_chunk)
+    if plan.fwd_ws < 0 or plan.bwd_ws < 0:
+        raise ValueError("elsa_b200: unsupported problem size")
+    out = torch.empty((batch, seq_len, heads, head_dim), device=qkv.device, dtype=qkv.dtype)
+    state = rm_p = rz_p = None
+    if want_state:
+        pad = (batch * heads * seq_len + 63) // 64 * 64
+        state = torch.empty((2 * pad,), device=qkv.device, dtype=torch.float32)
+        rm_p = state.data_ptr()
+        rz_p = rm_p + 4 * pad
+    base, step = qkv.data_ptr(), plan.hd * plan.esize
+    with _DeviceScope(qkv.device):
+        ws = torch.empty((max(plan.fwd_ws, 256),), device=qkv.device, dtype=torch.uint8)
+        rc = _lib.load().elsa_twopass_forward_strided(
+            base, base + step, base + 2 * step, plan.qkv_strides, plan.qkv_strides, plan.qkv_strides,
+            *meta.c_args(), out.data_ptr(), plan.out_strides, rm_p, rz_p, ws.data_ptr(), ws.numel(), plan.dt,
+            _lib.dtype_code(summary_dtype), batch, heads, seq_len, head_dim, int(bool(is_causal)), part_width, q_chunk,
+            0, _lib.raw_stream(qkv.device))
+    _lib.check(rc, "elsa_twopass_forward")
+    return out, state, meta, plan
+
+
 class _PackedQkvAttentionAutograd(torch.autograd.Function):
     """Attention on a packed projection output qkv [B, N, 3, H, D] (what `nn.Linear(dim, 3*dim)` produces, viewed):
     q, k, v are read in place, the output is written as [B, N, H, D] memory, and the backward writes dq, dk, dv
@@ -228,25 +313,74 @@ class _PackedQkvAttentionAutograd(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, bias, is_causal, fwd_kwargs):
-        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)           # three [B, H, N, D] views
         # the kernels read the bias in fp32: convert once, and let the backward reuse the converted tensor
         bias32 = None
         if bias is not None:
             bias32 = bias.detach()
             if bias32.dtype != torch.float32:
                 bias32 = bias32.to(torch.float32)
-        out, row_m, row_z, q_s, k_s, v_s = twopass_attention_with_state(
-            q, k, v, bias=bias32, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
         has_bias = bias is not None
-        ctx.save_for_backward(qkv, out, bias32 if has_bias else qkv.new_empty(1, dtype=torch.float32), row_m, row_z)
         ctx.has_bias = has_bias
         ctx.bias_requires_grad = bool(has_bias and bias.requires_grad)
         ctx.bias_dtype = bias.dtype if has_bias else None
+        ctx.bias_shape = tuple(bias.shape) if has_bias else None
         ctx.is_causal = bool(is_causal)
+        ctx.fast = not fwd_kwargs.get("reference_rounding", False) and _packed_fast_ok(qkv)
+        if ctx.fast:
+            out, state, meta, plan = _packed_forward_fast(qkv, bias32, ctx.is_causal, fwd_kwargs, want_state=True)
+            ctx.plan = plan
+            if has_bias:
+                ctx.save_for_backward(qkv, out, state, meta.tensor)
+            else:
+                ctx.save_for_backward(qkv, out, state)
+            return out.permute(0, 2, 1, 3)
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)           # three [B, H, N, D] views
+        out, row_m, row_z, q_s, k_s, v_s = twopass_attention_with_state(
+            q, k, v, bias=bias32, is_causal=is_causal, return_contiguous_inputs=True, **fwd_kwargs)
+        ctx.save_for_backward(qkv, out, bias32 if has_bias else qkv.new_empty(1, dtype=torch.float32), row_m, row_z)
         return out
 
     @staticmethod
+    def _fast_backward(ctx, grad_out):
+        saved = ctx.saved_tensors
+        qkv, out, state = saved[0], saved[1], saved[2]
+        bias32 = saved[3] if ctx.has_bias else None
+        plan = ctx.plan
+        batch, seq_len, _, heads, head_dim = map(int, qkv.shape)
+        if grad_out.dtype != qkv.dtype:
+            grad_out = grad_out.to(qkv.dtype)
+        gs = _bhnd_strides(grad_out)
+        if gs is None:
+            grad_out = _aligned(grad_out)
+            gs = _bhnd_strides(grad_out)
+        dqkv = torch.empty_like(qkv)
+        meta = _canonical_bias(bias32, batch=batch, heads=heads, seq_len=seq_len, device=qkv.device)
+        dbias = None
+        dargs = (None, 0, 0, 0, 0)
+        if ctx.bias_requires_grad:
+            dbias = torch.zeros_like(meta.tensor)
+            dargs = (dbias.data_ptr(), meta.stride_b, meta.stride_h, meta.stride_q, meta.stride_k)
+        base, dbase, step = qkv.data_ptr(), dqkv.data_ptr(), plan.hd * plan.esize
+        with _DeviceScope(qkv.device):
+            ws = torch.empty((max(plan.bwd_ws, 256),), device=qkv.device, dtype=torch.uint8)
+            rc = _lib.load().elsa_twopass_backward_strided(
+                base, base + step, base + 2 * step, out.data_ptr(), grad_out.data_ptr(), plan.backward_strides(gs),
+                state.data_ptr(), state.data_ptr() + 2 * state.numel(), *meta.c_args(),
+                dbase, dbase + step, dbase + 2 * step, *dargs, ws.data_ptr(), ws.numel(), plan.dt, batch, heads, seq_len,
+                head_dim, int(ctx.is_causal), 0, _lib.raw_stream(qkv.device))
+        _lib.check(rc, "elsa_twopass_backward")
+        return dqkv, dbias
+
+    @staticmethod
     def backward(ctx, grad_out):
+        if ctx.fast:
+            dqkv, dbias = _PackedQkvAttentionAutograd._fast_backward(ctx, grad_out)
+            if dbias is not None:
+                # (the saved fp32 bias has the [B|1, H|1, N, N] form: back to the caller's shape and dtype)
+                dbias = dbias.view(ctx.bias_shape)
+                if dbias.dtype != ctx.bias_dtype:
+                    dbias = dbias.to(ctx.bias_dtype)
+            return dqkv, dbias, None, None
         qkv, out, saved_bias, row_m, row_z = ctx.saved_tensors
         bias = saved_bias if ctx.has_bias else None
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
@@ -284,6 +418,13 @@ def twopass_attention_qkvpacked(qkv: torch.Tensor, *, bias: Optional[torch.Tenso
         _validate_warps("num_warps", fwd_kwargs["bwd_num_warps"])
     fwd_kwargs = {name: val for name, val in fwd_kwargs.items() if not name.startswith("bwd_")}
     if not train:
+        if not fwd_kwargs.get("reference_rounding", False) and _packed_fast_ok(qkv):
+            bias32 = None
+            if bias is not None:
+                bias32 = bias.detach()
+                if bias32.dtype != torch.float32:
+                    bias32 = bias32.to(torch.float32)
+            return _packed_forward_fast(qkv, bias32, is_causal, fwd_kwargs, want_state=False)[0].permute(0, 2, 1, 3)
         from .attention import twopass_attention
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
         return twopass_attention(q, k, v, bias=bias, is_causal=is_causal, **fwd_kwargs)
