@@ -439,32 +439,37 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
       tc_fence_after();
       {
-        uint32_t rs[64], rp[64];
-        tmem_ld32(tS + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
-        tmem_ld32(tS + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
-        tmem_ld32(tdP + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
-        tmem_ld32(tdP + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
-        tmem_wait_ld();
+        // Four chunks of 16 keys in a loop that is NOT unrolled: the fold code of a pair then fits the instruction
+        // cache (fully unrolled, the two sides' straight-line code was refetched for every pair and the warps spent more
+        // time waiting for instructions than for data).  dS goes over S columns that were read in this or an earlier
+        // step (first sequence: ascending; second: its own S columns lie elsewhere), the zeros after the last step.
         const float* bp = (prm.bias && row_ok) ? sb_seq + ri * kBiasStride : nullptr;
-        uint32_t dsk[32], zero[32];
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          uint32_t rs[16], rp[16], dsk[8];
+          tmem_ld16(tS + lane_off + 64 * seq + 16 * j, rs);
+          tmem_ld16(tdP + lane_off + 64 * seq + 16 * j, rp);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          float dsv[2];
+          for (int i = 0; i < 16; i += 2) {
+            float dsv[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kk = i + e;
-            float a = nlse;
-            if (bp && kk < N) a = fmaf(bp[kk], 1.4426950408889634f, nlse);
-            float p = fast_exp2(fmaf(__uint_as_float(rs[kk]), c, a));
-            if (kk >= N || (prm.causal && kk > ri)) p = 0.f;
-            dsv[e] = p * (__uint_as_float(rp[kk]) + nd);
+            for (int e = 0; e < 2; ++e) {
+              const int kk = 16 * j + i + e;
+              float a = nlse;
+              if (bp && kk < N) a = fmaf(bp[kk], 1.4426950408889634f, nlse);
+              float p = fast_exp2(fmaf(__uint_as_float(rs[i + e]), c, a));
+              if (kk >= N || (prm.causal && kk > ri)) p = 0.f;
+              dsv[e] = p * (__uint_as_float(rp[i + e]) + nd);
+            }
+            dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
           }
-          dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
+          tmem_st8(tS + lane_off + 32 * seq + 8 * j, dsk);
         }
+        uint32_t zero[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) zero[i] = 0u;
         // dS of this query row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other's
-        tmem_st32(tS + lane_off + 32 * seq, dsk);
         tmem_st32(tS + lane_off + 32 * (1 - seq), zero);
         tmem_wait_st();
       }
@@ -507,45 +512,50 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
       tc_fence_after();
       {
-        uint32_t rs[64], rp[64];
-        tmem_ld32(tST + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
-        tmem_ld32(tST + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
-        tmem_ld32(tdPT + lane_off + 64 * seq, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
-        tmem_ld32(tdPT + lane_off + 64 * seq + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
-        tmem_wait_ld();
         // bias[query, key] and dbias[query, key] of this key column: the lanes of a warp hold consecutive keys of one
         // query, so that every store or reduction of a warp is one coalesced access
         const float* bc = (prm.bias && row_ok) ? sb_seq + ri : nullptr;
         float* dbc = (prm.dbias && row_ok) ? prm.dbias + static_cast<int64_t>(b) * prm.dsb + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk : nullptr;
         const float* nl = nlse_s[ph] + 64 * seq;
         const float* ndp = nd_s[ph] + 64 * seq;
-        uint32_t pk[32], dsk[32], zero[32];
+        // Four chunks of 16 queries, not unrolled (see the query side).  P^T and dS^T go over S^T columns: the first
+        // sequence walks its chunks upwards and writes behind itself, the second walks downwards because its dS^T
+        // columns [96, 128) are the upper half of the S^T columns it reads; the zeros follow the last step.
+#pragma unroll 1
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = seq ? 3 - jj : jj;
+          uint32_t rs[16], rp[16], pk[8], dsk[8];
+          tmem_ld16(tST + lane_off + 64 * seq + 16 * j, rs);
+          tmem_ld16(tdPT + lane_off + 64 * seq + 16 * j, rp);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          float pv[2], dv2[2];
+          for (int i = 0; i < 16; i += 2) {
+            float pv[2], dv2[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qq = i + e;                            // query index within the sequence
-            float a = nl[qq];                                // -inf for queries that do not exist
-            if (bc && qq < N) a = fmaf(bc[qq * kBiasStride], 1.4426950408889634f, a);
-            float p = fast_exp2(fmaf(__uint_as_float(rs[qq]), c, a));
-            if (!row_ok || (prm.causal && ri > qq)) p = 0.f;  // a key that does not exist, or one after the query
-            pv[e] = p;
-            dv2[e] = p * (__uint_as_float(rp[qq]) + ndp[qq]);
-            if (dbc && qq < N) {
-              if (dbias_local) dacc[qq * kBiasStride] += dv2[e];
-              else if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]);
-              else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
+            for (int e = 0; e < 2; ++e) {
+              const int qq = 16 * j + i + e;                   // query index within the sequence
+              float a = nl[qq];                                // -inf for queries that do not exist
+              if (bc && qq < N) a = fmaf(bc[qq * kBiasStride], 1.4426950408889634f, a);
+              float p = fast_exp2(fmaf(__uint_as_float(rs[i + e]), c, a));
+              if (!row_ok || (prm.causal && ri > qq)) p = 0.f;  // a key that does not exist, or one after the query
+              pv[e] = p;
+              dv2[e] = p * (__uint_as_float(rp[i + e]) + ndp[qq]);
+              if (dbc && qq < N) {
+                if (dbias_local) dacc[qq * kBiasStride] += dv2[e];
+                else if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]);
+                else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
+              }
             }
+            pk[i >> 1] = pack2<T>(pv[0], pv[1]);
+            dsk[i >> 1] = pack2<T>(dv2[0], dv2[1]);
           }
-          pk[i >> 1] = pack2<T>(pv[0], pv[1]);
-          dsk[i >> 1] = pack2<T>(dv2[0], dv2[1]);
+          tmem_st8(tST + lane_off + 32 * seq + 8 * j, pk);               // P^T over the tile's 128 queries
+          tmem_st8(tST + 64 + lane_off + 32 * seq + 8 * j, dsk);         // dS^T
         }
+        uint32_t zero[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) zero[i] = 0u;
-        tmem_st32(tST + lane_off + 32 * seq, pk);                  // P^T over the tile's 128 queries
         tmem_st32(tST + lane_off + 32 * (1 - seq), zero);
-        tmem_st32(tST + 64 + lane_off + 32 * seq, dsk);            // dS^T
         tmem_st32(tST + 64 + lane_off + 32 * (1 - seq), zero);
         tmem_wait_st();
       }
