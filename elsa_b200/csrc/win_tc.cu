@@ -252,7 +252,7 @@ constexpr int kBwdStageBytes = 5 * kTileBytes;       // Q, K, V, dO, out of one 
 constexpr int kBiasTile = 64 * kBiasStride;          // floats of one staged bias (or dbias) tile
 // two stages, three tiles (bias of the two sequences; or one bias tile and a dbias sum per sequence), alignment slack
 constexpr int kWinBwdSmem = 2 * kBwdStageBytes + 3 * kBiasTile * 4 + 1024;
-constexpr int kBwdThreads = 288;                     // 4 query-side warps, 4 key-side warps, 1 issuing warp
+constexpr int kBwdThreads = 544;                     // 8 query-side warps, 8 key-side warps (two threads per row), 1 issuing warp
 
 enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PHQ = 77, BAR_PHK = 78, BAR_R2Q = 79, BAR_R2K = 80, BAR_EPI = 81, BAR_PUB = 82, BAR_BIAS = 83 };
 
@@ -267,22 +267,22 @@ struct WinBwdParams {
   int* status;
 };
 
-// one accumulator row (64 fp32 columns at `src`) scaled by f and stored as d elements of T
+// half an accumulator row (32 fp32 columns at `src`) scaled by f and stored as up to 32 elements of T (n = how many of
+// them exist: the head dim minus the half's first column)
 template <typename T>
-__device__ __forceinline__ void store_acc_row(uint32_t src, T* dst, int d, float f) {
-  uint32_t r0[32], r1[32];
-  tmem_ld32(src, r0);
-  tmem_ld32(src + 32, r1);
+__device__ __forceinline__ void store_acc_half(uint32_t src, T* dst, int n, float f) {
+  uint32_t r[32];
+  tmem_ld32(src, r);
   tmem_wait_ld();
   if (!dst) return;
 #pragma unroll
-  for (int i = 0; i < 64; i += 8) {
-    if (i >= d) continue;
-    float o[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(i + e < 32 ? r0[(i + e) & 31] : r1[(i + e) & 31]) * f;
+  for (int i = 0; i < 32; i += 8) {
+    if (i >= n) continue;
     uint4 t;
-    t.x = pack2<T>(o[0], o[1]); t.y = pack2<T>(o[2], o[3]); t.z = pack2<T>(o[4], o[5]); t.w = pack2<T>(o[6], o[7]);
+    t.x = pack2<T>(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
+    t.y = pack2<T>(__uint_as_float(r[i + 2]) * f, __uint_as_float(r[i + 3]) * f);
+    t.z = pack2<T>(__uint_as_float(r[i + 4]) * f, __uint_as_float(r[i + 5]) * f);
+    t.w = pack2<T>(__uint_as_float(r[i + 6]) * f, __uint_as_float(r[i + 7]) * f);
     *reinterpret_cast<uint4*>(dst + i) = t;
   }
 }
@@ -309,7 +309,7 @@ __device__ __forceinline__ float neg_row_dot(const uint8_t* t_out, const uint8_t
 // heads).  The five tiles of the next pair are in flight while this one is computed (two stages of shared memory); a
 // bias that does not depend on the batch index is staged once.
 template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1)     // (registers are granted as for 12 warps: 168 per thread)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                   const __grid_constant__ CUtensorMap tmap_o, const WinBwdParams prm) {
@@ -334,11 +334,11 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (tid == 0) {
     abort_flag = 0;
-    mbar_init(bar_load, 1); mbar_init(bar_load + 8, 1); mbar_init(bar_r1, 1); mbar_init(bar_phq, 4); mbar_init(bar_phk, 4);
-    mbar_init(bar_r2q, 1); mbar_init(bar_r2k, 1); mbar_init(bar_epi, 8); mbar_init(bar_pub, 4); mbar_init(bar_bias, 4);
+    mbar_init(bar_load, 1); mbar_init(bar_load + 8, 1); mbar_init(bar_r1, 1); mbar_init(bar_phq, 8); mbar_init(bar_phk, 8);
+    mbar_init(bar_r2q, 1); mbar_init(bar_r2k, 1); mbar_init(bar_epi, 16); mbar_init(bar_pub, 4); mbar_init(bar_bias, 8);
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(smem_u32(&tmem_base_slot), 512);
     tmem_relinquish();
   }
@@ -348,16 +348,19 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tS = tmem_base, tdP = tmem_base + 128, tST = tmem_base + 256, tdPT = tmem_base + 384;
 
-  // row of the tile this thread owns (a query for warps 0-3, a key for warps 4-7) == its TMEM lane
-  const int row = (warp & 3) * 32 + lane;
+  // Fold warps 0-7 are the query side, 8-15 the key side.  Two threads share a row of the tile (= a TMEM lane): warp w
+  // works on lane quadrant w % 4 and on half (w / 4) % 2 of the row's 64 columns.
+  const int wq = warp & 3, half = (warp >> 2) & 1;
+  const int row = wq * 32 + lane;
   const int seq = row >> 6, ri = row & 63;                // which of the two sequences, and the row's index in it
-  const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const uint32_t lane_off = static_cast<uint32_t>(wq * 32) << 16;
+  const int pair_bar = 2 + (warp >> 3) * 4 + wq;          // named barrier of the two warps that share this quadrant
   const float c = prm.scale_log2;
   float* sb = reinterpret_cast<float*>(smem_al + 2 * kBwdStageBytes);
   const bool bias_per_batch = prm.bias && prm.bsb != 0;   // else one tile serves every pair of this head
   const float* sb_seq = sb + (bias_per_batch ? seq * kBiasTile : 0);
 
-  if (warp == 8) {
+  if (warp == 16) {
     if (lane == 0 && pair0 < n_pairs) {
       // ---------------- loads and MMAs ----------------
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_o);
@@ -408,12 +411,12 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         mma_commit(bar_r2k);
       }
     }
-  } else if (warp < 4) {
-    // ---------------- query-side warps: thread = query row ----------------
+  } else if (warp < 8) {
+    // ---------------- query-side warps: thread = (query row, half of its keys) ----------------
     auto load_state = [&](int pair, float& m, float& z) {
       const int bb = 2 * pair + seq;
       m = -CUDART_INF_F; z = 0.f;
-      if (pair < n_pairs && bb < prm.batch && ri < N) {
+      if (half == 0 && pair < n_pairs && bb < prm.batch && ri < N) {
         const int64_t ro = (static_cast<int64_t>(bb) * prm.heads + hi) * N + ri;
         m = prm.row_m[ro]; z = prm.row_z[ro];
       }
@@ -427,58 +430,75 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int b = 2 * pair + seq;
       const bool row_ok = b < prm.batch && ri < N;
       const uint8_t* tiles = smem_al + stage * kBwdStageBytes;
-      // -LSE and -D of this row, published for the key-side warps
-      float nlse = -CUDART_INF_F;
-      if (z_next > 0.f && m_next > -CUDART_INF_F) nlse = -(m_next + log2f(z_next));   // (a row whose keys are all masked keeps P = 0)
-      load_state(pair + pair_step, m_next, z_next);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_load + 8 * stage, (it >> 1) & 1, &abort_flag, prm.status, BAR_BLOAD))) break;
-      const float nd = neg_row_dot<T>(tiles + 4 * kTileBytes, tiles + 3 * kTileBytes, row, d);
-      nlse_s[ph][row] = nlse; nd_s[ph][row] = nd;
-      mbar_arrive_warp(bar_pub, lane);
+      if (half == 0) {
+        // -LSE and -D of this row, published for the row's other thread and for the key-side warps
+        float nl0 = -CUDART_INF_F;
+        if (z_next > 0.f && m_next > -CUDART_INF_F) nl0 = -(m_next + log2f(z_next));   // (a row whose keys are all masked keeps P = 0)
+        load_state(pair + pair_step, m_next, z_next);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_load + 8 * stage, (it >> 1) & 1, &abort_flag, prm.status, BAR_BLOAD))) break;
+        nlse_s[ph][row] = nl0;
+        nd_s[ph][row] = neg_row_dot<T>(tiles + 4 * kTileBytes, tiles + 3 * kTileBytes, row, d);
+        mbar_arrive_warp(bar_pub, lane);
+      }
       if (prm.bias && !__all_sync(0xffffffffu, mbar_wait(bar_bias, ph, &abort_flag, prm.status, BAR_BIAS))) break;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_pub, ph, &abort_flag, prm.status, BAR_PUB))) break;
       tc_fence_after();
       {
-        // Four chunks of 16 keys in a loop that is NOT unrolled: the fold code of a pair then fits the instruction
-        // cache (fully unrolled, the two sides' straight-line code was refetched for every pair and the warps spent more
-        // time waiting for instructions than for data).  dS goes over S columns that were read in this or an earlier
-        // step (first sequence: ascending; second: its own S columns lie elsewhere), the zeros after the last step.
-        const float* bp = (prm.bias && row_ok) ? sb_seq + ri * kBiasStride : nullptr;
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          uint32_t rs[16], rp[16], dsk[8];
-          tmem_ld16(tS + lane_off + 64 * seq + 16 * j, rs);
-          tmem_ld16(tdP + lane_off + 64 * seq + 16 * j, rp);
-          tmem_wait_ld();
+        const float nlse = nlse_s[ph][row], nd = nd_s[ph][row];
+        // this thread's 32 keys of the row's own sequence
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_off + 64 * seq + 32 * half, rs);
+        tmem_ld32(tdP + lane_off + 64 * seq + 32 * half, rp);
+        tmem_wait_ld();
+        // dS goes over S columns that the row's other thread reads: both have their scores in registers from here on
+        named_barrier_sync(pair_bar, 64);
+        // The loops below are free of branches, so that the 32 independent chains (scale, exponential, mask, product)
+        // overlap; with a conditional bias load inside, every element was a basic block of its own and ran in ~100 cycles.
+        float t[32];                                        // s c + bias log2(e) - LSE
+        if (prm.bias) {                                     // (uniform; every load is inside the staged tile, a select drops what is not bias)
+          const float* bp = sb_seq + (row_ok ? ri : 0) * kBiasStride + 32 * half;
+          const int n_b = row_ok ? N - 32 * half : 0;
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
+          for (int i = 0; i < 32; ++i) {
+            float bv = bp[i];
+            bv = (i < n_b) ? bv : 0.f;
+            t[i] = fmaf(__uint_as_float(rs[i]), c, fmaf(bv, 1.4426950408889634f, nlse));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[i] = fmaf(__uint_as_float(rs[i]), c, nlse);
+        }
+        const int k_lim = prm.causal ? min(N, ri + 1) : N;  // keys kk < k_lim take part
+        uint32_t zero[16];
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {                 // (stored as soon as eight are packed: fewer live registers)
+          uint32_t dsk[8];
+#pragma unroll
+          for (int i = 16 * sub; i < 16 * sub + 16; i += 2) {
             float dsv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int kk = 16 * j + i + e;
-              float a = nlse;
-              if (bp && kk < N) a = fmaf(bp[kk], 1.4426950408889634f, nlse);
-              float p = fast_exp2(fmaf(__uint_as_float(rs[i + e]), c, a));
-              if (kk >= N || (prm.causal && kk > ri)) p = 0.f;
+              float p = fast_exp2(t[i + e]);
+              p = (32 * half + i + e < k_lim) ? p : 0.f;
               dsv[e] = p * (__uint_as_float(rp[i + e]) + nd);
             }
-            dsk[i >> 1] = pack2<T>(dsv[0], dsv[1]);
+            dsk[(i >> 1) & 7] = pack2<T>(dsv[0], dsv[1]);
           }
-          tmem_st8(tS + lane_off + 32 * seq + 8 * j, dsk);
+          // dS of this query row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other's
+          tmem_st8(tS + lane_off + 32 * seq + 16 * half + 8 * sub, dsk);
         }
-        uint32_t zero[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) zero[i] = 0u;
-        // dS of this query row over the 128 keys of the tile: its own sequence's 64 keys, zeros for the other's
-        tmem_st32(tS + lane_off + 32 * (1 - seq), zero);
+        for (int i = 0; i < 16; ++i) zero[i] = 0u;
+        tmem_st16(tS + lane_off + 32 * (1 - seq) + 16 * half, zero);
         tmem_wait_st();
       }
       tc_fence_before();
       mbar_arrive_warp(bar_phq, lane);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r2q, ph, &abort_flag, prm.status, BAR_R2Q))) break;
       tc_fence_after();
-      T* dst = row_ok ? static_cast<T*>(prm.dq) + static_cast<int64_t>(b) * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(ri) * prm.dqs.r : nullptr;
-      store_acc_row<T>(tdP + lane_off, dst, d, prm.scale);
+      T* dst = row_ok ? static_cast<T*>(prm.dq) + static_cast<int64_t>(b) * prm.dqs.b + hi * prm.dqs.h + static_cast<int64_t>(ri) * prm.dqs.r + 32 * half : nullptr;
+      store_acc_half<T>(tdP + lane_off + 32 * half, dst, d - 32 * half, prm.scale);
       tc_fence_before();
       mbar_arrive_warp(bar_epi, lane);
       // the key side has consumed this pair's -LSE / -D (and the barrier phase that published them) before the next
@@ -486,14 +506,14 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r2k, ph, &abort_flag, prm.status, BAR_R2K))) break;
     }
   } else {
-    // ---------------- key-side warps: thread = key row ----------------
+    // ---------------- key-side warps: thread = (key row, half of the queries) ----------------
     // A bias gradient shared by the batch (with a bias that is, so that two tiles of the bias buffer are free) is summed
     // over all the CTA's pairs in shared memory, one tile per sequence of the pair and every element by one thread only,
     // and added to global memory once, at the end.
     const bool dbias_local = prm.dbias && prm.dbias_atomic && prm.dsb == 0 && !bias_per_batch;
-    float* dacc = sb + (1 + seq) * kBiasTile + ri;         // this thread's column of its sequence's tile
+    float* dacc = sb + (1 + seq) * kBiasTile + ri + 32 * half * kBiasStride;   // this thread's half column of its sequence's tile
     if (dbias_local) {
-      for (int qq = 0; qq < 64; ++qq) dacc[qq * kBiasStride] = 0.f;
+      for (int qq = 0; qq < 32; ++qq) dacc[qq * kBiasStride] = 0.f;
     }
     bool completed = true;
     int it = 0;
@@ -504,82 +524,104 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const bool row_ok = b < prm.batch && ri < N;
       if (prm.bias) {
         // (the query side has finished with the tiles of the previous pair: its dS was an input of that pair's last MMAs)
-        if (bias_per_batch) stage_bias(sb, prm.bias, prm.bsb, prm.bsh, prm.bsq, prm.bsk, 2 * pair, 2, prm.batch, hi, N, warp & 3, 4, lane);
-        else if (it == 0) stage_bias(sb, prm.bias, 0, prm.bsh, prm.bsq, prm.bsk, 0, 1, prm.batch, hi, N, warp & 3, 4, lane);
+        if (bias_per_batch) stage_bias(sb, prm.bias, prm.bsb, prm.bsh, prm.bsq, prm.bsk, 2 * pair, 2, prm.batch, hi, N, warp & 7, 8, lane);
+        else if (it == 0) stage_bias(sb, prm.bias, 0, prm.bsh, prm.bsq, prm.bsk, 0, 1, prm.batch, hi, N, warp & 7, 8, lane);
         mbar_arrive_warp(bar_bias, lane);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_bias, ph, &abort_flag, prm.status, BAR_BIAS))) break;   // all eight warps' rows
       }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_pub, ph, &abort_flag, prm.status, BAR_PUB))) break;   // -LSE, -D of the 128 queries
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
       tc_fence_after();
       {
+        // this thread's 32 queries of the key's own sequence
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tST + lane_off + 64 * seq + 32 * half, rs);
+        tmem_ld32(tdPT + lane_off + 64 * seq + 32 * half, rp);
+        tmem_wait_ld();
+        // P^T and dS^T go over S^T columns that the row's other thread reads: both have them in registers from here on
+        named_barrier_sync(pair_bar, 64);
         // bias[query, key] and dbias[query, key] of this key column: the lanes of a warp hold consecutive keys of one
         // query, so that every store or reduction of a warp is one coalesced access
-        const float* bc = (prm.bias && row_ok) ? sb_seq + ri : nullptr;
-        float* dbc = (prm.dbias && row_ok) ? prm.dbias + static_cast<int64_t>(b) * prm.dsb + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk : nullptr;
-        const float* nl = nlse_s[ph] + 64 * seq;
-        const float* ndp = nd_s[ph] + 64 * seq;
-        // Four chunks of 16 queries, not unrolled (see the query side).  P^T and dS^T go over S^T columns: the first
-        // sequence walks its chunks upwards and writes behind itself, the second walks downwards because its dS^T
-        // columns [96, 128) are the upper half of the S^T columns it reads; the zeros follow the last step.
-#pragma unroll 1
-        for (int jj = 0; jj < 4; ++jj) {
-          const int j = seq ? 3 - jj : jj;
-          uint32_t rs[16], rp[16], pk[8], dsk[8];
-          tmem_ld16(tST + lane_off + 64 * seq + 16 * j, rs);
-          tmem_ld16(tdPT + lane_off + 64 * seq + 16 * j, rp);
-          tmem_wait_ld();
+        float* dbc = (prm.dbias && row_ok) ? prm.dbias + static_cast<int64_t>(b) * prm.dsb + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk + static_cast<int64_t>(32 * half) * prm.dsq : nullptr;
+        const float* nl = nlse_s[ph] + 64 * seq + 32 * half;
+        const float* ndp = nd_s[ph] + 64 * seq + 32 * half;
+        // branch-free loops (see the query side): P^T into pv, dS^T into dsv, then the bias gradient, then the packing
+        float pv[32], dsv[32];
+        if (prm.bias) {                                     // (uniform; loads inside the staged tile, see the query side)
+          const float* bc = sb_seq + (row_ok ? ri : 0) + 32 * half * kBiasStride;
+          const int n_b = row_ok ? N - 32 * half : 0;
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float pv[2], dv2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int qq = 16 * j + i + e;                   // query index within the sequence
-              float a = nl[qq];                                // -inf for queries that do not exist
-              if (bc && qq < N) a = fmaf(bc[qq * kBiasStride], 1.4426950408889634f, a);
-              float p = fast_exp2(fmaf(__uint_as_float(rs[i + e]), c, a));
-              if (!row_ok || (prm.causal && ri > qq)) p = 0.f;  // a key that does not exist, or one after the query
-              pv[e] = p;
-              dv2[e] = p * (__uint_as_float(rp[i + e]) + ndp[qq]);
-              if (dbc && qq < N) {
-                if (dbias_local) dacc[qq * kBiasStride] += dv2[e];
-                else if (prm.dbias_atomic) atomicAdd(dbc + static_cast<int64_t>(qq) * prm.dsq, dv2[e]);
-                else dbc[static_cast<int64_t>(qq) * prm.dsq] = dv2[e];
-              }
-            }
-            pk[i >> 1] = pack2<T>(pv[0], pv[1]);
-            dsk[i >> 1] = pack2<T>(dv2[0], dv2[1]);
+          for (int i = 0; i < 32; ++i) {
+            float bv = bc[i * kBiasStride];
+            bv = (i < n_b) ? bv : 0.f;
+            pv[i] = fmaf(__uint_as_float(rs[i]), c, fmaf(bv, 1.4426950408889634f, nl[i]));   // (-inf for queries that do not exist)
           }
-          tmem_st8(tST + lane_off + 32 * seq + 8 * j, pk);               // P^T over the tile's 128 queries
-          tmem_st8(tST + 64 + lane_off + 32 * seq + 8 * j, dsk);         // dS^T
-        }
-        uint32_t zero[32];
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) zero[i] = 0u;
-        tmem_st32(tST + lane_off + 32 * (1 - seq), zero);
-        tmem_st32(tST + 64 + lane_off + 32 * (1 - seq), zero);
+          for (int i = 0; i < 32; ++i) pv[i] = fmaf(__uint_as_float(rs[i]), c, nl[i]);
+        }
+        const int q_min = !row_ok ? 64 : (prm.causal ? ri : 0);   // queries qq >= q_min see this key (none when it does not exist)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float p = fast_exp2(pv[i]);
+          p = (32 * half + i >= q_min) ? p : 0.f;
+          pv[i] = p;
+          dsv[i] = p * (__uint_as_float(rp[i]) + ndp[i]);
+        }
+        if (dbc) {
+          const int n_q = min(32, N - 32 * half);             // this thread's queries that exist
+          if (dbias_local) {                                 // (all 32 rows of the half column exist in the tile)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dacc[i * kBiasStride] += (i < n_q) ? dsv[i] : 0.f;
+          } else if (prm.dbias_atomic) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < n_q) atomicAdd(dbc + static_cast<int64_t>(i) * prm.dsq, dsv[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < n_q) dbc[static_cast<int64_t>(i) * prm.dsq] = dsv[i];
+          }
+        }
+        uint32_t zero[16];
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          uint32_t pk[8], dsk[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            pk[i] = pack2<T>(pv[16 * sub + 2 * i], pv[16 * sub + 2 * i + 1]);
+            dsk[i] = pack2<T>(dsv[16 * sub + 2 * i], dsv[16 * sub + 2 * i + 1]);
+          }
+          tmem_st8(tST + lane_off + 32 * seq + 16 * half + 8 * sub, pk);             // P^T over the tile's 128 queries
+          tmem_st8(tST + 64 + lane_off + 32 * seq + 16 * half + 8 * sub, dsk);       // dS^T
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) zero[i] = 0u;
+        tmem_st16(tST + lane_off + 32 * (1 - seq) + 16 * half, zero);
+        tmem_st16(tST + 64 + lane_off + 32 * (1 - seq) + 16 * half, zero);
         tmem_wait_st();
       }
       tc_fence_before();
       mbar_arrive_warp(bar_phk, lane);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_r2k, ph, &abort_flag, prm.status, BAR_R2K))) break;
       tc_fence_after();
-      T* dvp = row_ok ? static_cast<T*>(prm.dv) + static_cast<int64_t>(b) * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(ri) * prm.dvs.r : nullptr;
-      T* dkp = row_ok ? static_cast<T*>(prm.dk) + static_cast<int64_t>(b) * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(ri) * prm.dks.r : nullptr;
-      store_acc_row<T>(tdPT + lane_off, dvp, d, 1.f);
-      store_acc_row<T>(tdPT + 64 + lane_off, dkp, d, prm.scale);
+      T* dvp = row_ok ? static_cast<T*>(prm.dv) + static_cast<int64_t>(b) * prm.dvs.b + hi * prm.dvs.h + static_cast<int64_t>(ri) * prm.dvs.r + 32 * half : nullptr;
+      T* dkp = row_ok ? static_cast<T*>(prm.dk) + static_cast<int64_t>(b) * prm.dks.b + hi * prm.dks.h + static_cast<int64_t>(ri) * prm.dks.r + 32 * half : nullptr;
+      store_acc_half<T>(tdPT + lane_off + 32 * half, dvp, d - 32 * half, 1.f);
+      store_acc_half<T>(tdPT + 64 + lane_off + 32 * half, dkp, d - 32 * half, prm.scale);
       tc_fence_before();
       mbar_arrive_warp(bar_epi, lane);
       completed = true;
     }
     if (dbias_local && completed && ri < N) {                // (nothing is added after a wait that gave up)
-      float* dst = prm.dbias + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk;
-      for (int qq = 0; qq < N; ++qq) atomicAdd(dst + static_cast<int64_t>(qq) * prm.dsq, dacc[qq * kBiasStride]);
+      float* dst = prm.dbias + hi * prm.dsh + static_cast<int64_t>(ri) * prm.dsk + static_cast<int64_t>(32 * half) * prm.dsq;
+      for (int qq = 0; qq < 32 && 32 * half + qq < N; ++qq) atomicAdd(dst + static_cast<int64_t>(qq) * prm.dsq, dacc[qq * kBiasStride]);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_base, 512);
+  if (warp == 16) tmem_dealloc(tmem_base, 512);
 }
 
 }  // namespace
