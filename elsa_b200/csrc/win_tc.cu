@@ -155,11 +155,15 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
         for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(r0[i]) * c; sv[32 + i] = __uint_as_float(r1[i]) * c; }
       }
-      if (prm.bias && row_ok) {
-        const float* bp = sb + ((prm.bsb != 0 ? seq * 64 : 0) + qi) * kBiasStride;   // (one tile when the bias ignores the batch index)
+      if (prm.bias) {                                        // (uniform; every load is inside the staged tile, a select drops what is not bias)
+        const float* bp = sb + ((prm.bsb != 0 ? seq * 64 : 0) + (row_ok ? qi : 0)) * kBiasStride;   // (one tile when the bias ignores the batch index)
+        const int n_b = row_ok ? N : 0;
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i < N) sv[i] = fmaf(bp[i], 1.4426950408889634f, sv[i]);
+        for (int i = 0; i < 64; ++i) {
+          float bv = bp[i];
+          bv = (i < n_b) ? bv : 0.f;
+          sv[i] = fmaf(bv, 1.4426950408889634f, sv[i]);
+        }
       }
 #pragma unroll
       for (int i = 0; i < 64; ++i)
@@ -234,7 +238,8 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // ------------------------------------------------------------------------------------------------------------------
 // Backward of the same problems, one launch: dQ, dK, dV (and dbias) of two sequences of one head per CTA.
 //
-//   round 1 (issuer)   S = Q K^T, dP = dO V^T, S^T = K Q^T, dP^T = V dO^T          four 128 x 128 tiles = all 512 TMEM columns
+//   round 1 (issuer)   S^T = K Q^T, dP^T = V dO^T (the key side starts), S = Q K^T, dP = dO V^T (the query side starts):
+//                      four 128 x 128 tiles = all 512 TMEM columns
 //   query side (warps 0-3, thread = query row)   -LSE and -D of the row, published in shared memory;
 //                      P = 2^(S c + bias - LSE), dS = P (dP - D) over the row's own sequence; dS (16-bit) written over
 //                      the row's S columns
@@ -254,7 +259,7 @@ constexpr int kBiasTile = 64 * kBiasStride;          // floats of one staged bia
 constexpr int kWinBwdSmem = 2 * kBwdStageBytes + 3 * kBiasTile * 4 + 1024;
 constexpr int kBwdThreads = 544;                     // 8 query-side warps, 8 key-side warps (two threads per row), 1 issuing warp
 
-enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PHQ = 77, BAR_PHK = 78, BAR_R2Q = 79, BAR_R2K = 80, BAR_EPI = 81, BAR_PUB = 82, BAR_BIAS = 83 };
+enum BwdBarId { BAR_BLOAD = 75, BAR_R1 = 76, BAR_PHQ = 77, BAR_PHK = 78, BAR_R2Q = 79, BAR_R2K = 80, BAR_EPI = 81, BAR_PUB = 82, BAR_BIAS = 83, BAR_R1K = 84 };
 
 struct WinBwdParams {
   const void* out; Strides os; const void* dout; Strides gs;
@@ -314,7 +319,7 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                   const __grid_constant__ CUtensorMap tmap_o, const WinBwdParams prm) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[10];
+  __shared__ __align__(8) uint64_t bars[11];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ float nlse_s[2][128], nd_s[2][128];   // -LSE and -D of the tile's 128 query rows, per iteration parity
@@ -330,12 +335,12 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   // stage s: Q, K, V, dO, out at smem_base + s * kBwdStageBytes + {0..4} * kTileBytes
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_load = bar0 /* [2] */, bar_r1 = bar0 + 16, bar_phq = bar0 + 24, bar_phk = bar0 + 32, bar_r2q = bar0 + 40,
-                 bar_r2k = bar0 + 48, bar_epi = bar0 + 56, bar_pub = bar0 + 64, bar_bias = bar0 + 72;
+                 bar_r2k = bar0 + 48, bar_epi = bar0 + 56, bar_pub = bar0 + 64, bar_bias = bar0 + 72, bar_r1k = bar0 + 80;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_load, 1); mbar_init(bar_load + 8, 1); mbar_init(bar_r1, 1); mbar_init(bar_phq, 8); mbar_init(bar_phk, 8);
-    mbar_init(bar_r2q, 1); mbar_init(bar_r2k, 1); mbar_init(bar_epi, 16); mbar_init(bar_pub, 4); mbar_init(bar_bias, 8);
+    mbar_init(bar_r2q, 1); mbar_init(bar_r2k, 1); mbar_init(bar_epi, 16); mbar_init(bar_pub, 4); mbar_init(bar_bias, 8); mbar_init(bar_r1k, 1);
     fence_mbar_init();
   }
   if (warp == 16) {
@@ -389,10 +394,12 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_after();
         const uint64_t dq = make_sdesc(sQ, 16, 1024), dk = make_sdesc(sK, 16, 1024);
         const uint64_t dv = make_sdesc(sV, 16, 1024), ddo = make_sdesc(sDO, 16, 1024);
-        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tS, dq + 2 * ks, dk + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
-        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdP, ddo + 2 * ks, dv + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        // the key side has the longer way to go (two products, two gradients): its inputs first
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tST, dk + 2 * ks, dq + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdPT, dv + 2 * ks, ddo + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        mma_commit(bar_r1k);
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tS, dq + 2 * ks, dk + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < ksteps; ++ks) mma_ss(tdP, ddo + 2 * ks, dv + 2 * ks, idesc_s, ks > 0 ? 1u : 0u);
         mma_commit(bar_r1);
         if (pair + pair_step < n_pairs) issue_loads(pair + pair_step, stage ^ 1);
         const uint64_t k_mn = make_sdesc(sK, 128 * 128, 1024), q_mn = make_sdesc(sQ, 128 * 128, 1024);
@@ -530,7 +537,7 @@ win_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (!__all_sync(0xffffffffu, mbar_wait(bar_bias, ph, &abort_flag, prm.status, BAR_BIAS))) break;   // all eight warps' rows
       }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_pub, ph, &abort_flag, prm.status, BAR_PUB))) break;   // -LSE, -D of the 128 queries
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_r1, ph, &abort_flag, prm.status, BAR_R1))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_r1k, ph, &abort_flag, prm.status, BAR_R1K))) break;
       tc_fence_after();
       {
         // this thread's 32 queries of the key's own sequence
