@@ -65,7 +65,8 @@ FP32_TC_MMAS = 3.0   # 16-bit products per fp32 product: x = h0 + h1 in fp16, a*
 FP32_TC_PEAK_NOTE = ("measured bf16 dense (sustained) / 3: an fp32 product on the tensor cores is three fp16 products "
                      "(two fp16 planes per operand); the backward also runs seven contractions per tile pair for the "
                      "five counted, so its ceiling in these units is 5/7 of this figure")
-NCU_TRAFFIC_BYTES = {"headline": 101780992 + 19949824}
+NCU_TRAFFIC_BYTES = {"headline": 101780992 + 19949824,
+                     "swin_s1": 24829952}     # win_tc_bwd_kernel: dram read + write (the 14.5 MB written stay in L2)
 
 
 def peaks():
@@ -264,6 +265,13 @@ def measure_fma_peak(lib, dev):
         ms = timed(lambda i: lib.elsa_debug_fma_rate(sink.data_ptr(), blocks, iters, packed, stream), 2)
         best["packed_f32x2" if packed else "scalar"] = blocks * 256 * iters * 32 / (ms * 1e-3) / 1e12
     return {"tflops": max(best.values()), "forms": best, "how": "register-resident FMA chains, 148*8 CTAs x 256 threads, ~0.25 s per launch, CUDA events"}
+
+
+def window_bytes(b, h, n, d, esize):
+    """Algorithmic HBM bytes of the one-launch kernels for sequences of at most 64 tokens: the forward reads q, k, v and
+    writes out and the row state; the backward reads q, k, v, out, dout and the row state and writes dq, dk, dv."""
+    rows = b * h * n
+    return rows * (4 * d * esize + 8), rows * (8 * d * esize + 8)
 
 
 def measure_phase2(lib, dev, hbm_gbs):
@@ -741,6 +749,12 @@ def main():
                                     "bound": "tensor" if tc else "fp32-fma",
                                     "peak": peak, "frac": (tf / peak) if peak else None,
                                     "peak_source": (FP32_TC_PEAK_NOTE if split3 else "measured bf16 dense, sustained") if tc else "FMA chain measured in this run"}
+                    if tc and w2.n <= 64:
+                        # the window kernels move a few KB per sequence and use a few percent of the tensor pipe
+                        fb, bb = window_bytes(w2.b, w2.h, w2.n, w2.d, 2)
+                        gbs = (fb + bb) / (ms2 * 1e-3) / 1e9
+                        others[name].update({"bound": "hbm", "achieved_gbs": gbs, "peak": pk["hbm_gbs"], "frac": gbs / pk["hbm_gbs"],
+                                             "peak_source": "measured copy bandwidth; algorithmic bytes of forward + backward over the step time"})
                     del w2
                 except Exception as exc:  # noqa: BLE001
                     others[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
@@ -777,6 +791,14 @@ def main():
                     "forward": {"achieved": fwd_f / (fwd_sus * 1e-3) / 1e12, "ms": fwd_sus,
                                 "frac": (fwd_f / (fwd_sus * 1e-3) / 1e12 / peak) if peak else None},
                     "split_note": "forward / backward shares from a separate event-instrumented pass, scaled to the sustained step time"}
+        if uses_tc and n <= 64:
+            # window kernels: a few KB per sequence, a few percent of the tensor pipe: the bound is HBM (and latency)
+            fb, bb = window_bytes(b, h, n, d, 2)
+            roofline.update({"kernel": "win_tc_bwd_kernel (dQ, dK, dV, dbias of sequences of at most 64 tokens, one launch)",
+                             "bound": "hbm", "achieved": bb / (bwd_sus * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "peak_source": pk["source"] + " copy bandwidth", "peak_burst": None, "frac_of_burst": None})
+            roofline["frac"] = roofline["achieved"] / roofline["peak"]
+            roofline["forward"] = {"achieved": fb / (fwd_sus * 1e-3) / 1e9, "ms": fwd_sus, "frac": fb / (fwd_sus * 1e-3) / 1e9 / pk["hbm_gbs"]}
         if "phase2" in extras:
             roofline["phase2"] = extras.pop("phase2")
         cpu = None
