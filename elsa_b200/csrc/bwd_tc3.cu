@@ -629,6 +629,17 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const float4* nd4 = nl4 + 16;
         const bool masked = cta_tail || (prm.is_causal && q_tile0 < kseq0 + 128);   // only the diagonal tiles / the last key tile
         const int qc = q_tile0 + 16 * cq;                                           // first query of this thread's columns
+        // The bias of this thread's 16 (query, key) pairs, fetched by unconditional loads (the query clamped into the
+        // sequence) ahead of a branch-free element loop: with a conditional load inside, every element was a basic
+        // block of its own and its chain of dependent instructions overlapped with nobody's.
+        float bb[16];
+        if constexpr (BIAS) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float bv = bias_col[static_cast<int64_t>(min(qc + i, N - 1)) * prm.bsq];
+            bb[i] = (key_ok && qc + i < N) ? bv * 1.4426950408889634f : 0.f;
+          }
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const float4 nl = nl4[g], nd = nd4[g];            // -LSE, -D of 4 queries (warp-wide broadcast reads)
@@ -637,9 +648,7 @@ bwd3_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int e = 0; e < 4; ++e) {
             const int i = 4 * g + e;
             float a = nle[e] + kLog2Unit;
-            if constexpr (BIAS) {
-              if (key_ok && qc + i < N) a = fmaf(bias_col[static_cast<int64_t>(qc + i) * prm.bsq], 1.4426950408889634f, a);
-            }
+            if constexpr (BIAS) a += bb[i];
             float pv = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a));
             if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) pv = 0.f;
             p[i] = pv;

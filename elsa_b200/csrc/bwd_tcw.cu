@@ -245,6 +245,15 @@ bwdw_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     bool alive = n_t > 0;
 
     for (int j = 0; alive && j < n_t; ++j) {
+      if constexpr (BIAS) {
+        // this thread's 128 bytes of the bias row for the NEXT key tile: on their way into L2 while this tile is worked on
+        const int kn = (j + 1) * 128 + 32 * cq;
+        if (kn + 32 <= NK) {
+          const float* bn = bias_row + static_cast<int64_t>(kn + koff) * prm.bsk;
+          prefetch_l2(bn);
+          prefetch_l2(bn + 31 * prm.bsk);
+        }
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, j & 1, &abort_flag, prm.status, BAR_SDP))) { alive = false; break; }
       tc_fence_after();
       uint32_t pk[16];
@@ -511,6 +520,12 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     for (int it = 0; it < n_it; ++it) {
       const int q_tile0 = (it_begin + it) * 64;
+      if constexpr (BIAS) {
+        // the bias of the NEXT query tile (16 rows of this thread's column quarter, one 128-byte line per row and warp)
+        // on its way into L2 while this tile is worked on
+        const int qn = q_tile0 + 64 + 16 * cq + (lane & 15);
+        if (it + 1 < n_it && qn < N) prefetch_l2(bias_col + static_cast<int64_t>(qn) * prm.bsq);
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, it & 1, &abort_flag, prm.status, BAR_SDP))) { alive = false; break; }
       // the tile's row statistics were written by the bulk copies that complete on its first slot's barrier: observe
       // that barrier directly (it completed before the MMAs behind bar_sdp were issued, so this never spins)
@@ -531,6 +546,17 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const float4* nd4 = nl4 + 16;
         const bool masked = cta_tail || (prm.is_causal && q_tile0 < kseq0 + 128);   // only the diagonal tiles / the last key tile
         const int qc = q_tile0 + 16 * cq;                                           // first query of this thread's columns
+        // The bias of this thread's 16 (query, key) pairs, fetched by unconditional loads (the query clamped into the
+        // sequence) ahead of a branch-free element loop: with a conditional load inside, every element was a basic
+        // block of its own and its chain of dependent instructions overlapped with nobody's.
+        float bb[16];
+        if constexpr (BIAS) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float bv = bias_col[static_cast<int64_t>(min(qc + i, N - 1)) * prm.bsq];
+            bb[i] = (key_ok && qc + i < N) ? bv * 1.4426950408889634f : 0.f;
+          }
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const float4 nl = nl4[g], nd = nd4[g];            // -LSE, -D of 4 queries (warp-wide broadcast reads)
@@ -540,9 +566,7 @@ bwdw_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int e = 0; e < 4; ++e) {
             const int i = 4 * g + e;
             float a = nle[e];
-            if constexpr (BIAS) {
-              if (key_ok && qc + i < N) a = fmaf(bias_col[static_cast<int64_t>(qc + i) * prm.bsq], 1.4426950408889634f, a);
-            }
+            if constexpr (BIAS) a += bb[i];
             float x = fast_exp2(fmaf(__uint_as_float(rs[i]), c, a));
             if (masked && !(key_ok && (!prm.is_causal || qc + i >= key_seq))) x = 0.f;
             pv[e] = x;

@@ -239,6 +239,15 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     };
 
     for (int j = 0; j < n_t; ++j) {
+      if constexpr (BIAS) {
+        // this thread's 128 bytes of the bias row for the NEXT key tile: on their way into L2 while this tile is folded
+        const int kn = k_begin + (j + 1) * 128 + 32 * cq;
+        if (kn + 32 <= k_end) {
+          const float* bn = bias_row + static_cast<int64_t>(kn + koff) * prm.bsk;
+          prefetch_l2(bn);
+          prefetch_l2(bn + 31 * prm.bsk);
+        }
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, &abort_flag, prm.status, BAR_S))) { alive = false; break; }
       tc_fence_after();
       float sv[32];

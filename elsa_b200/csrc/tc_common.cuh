@@ -89,6 +89,10 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(row), "r"(h), "r"(b)
       : "memory");
 }
+// the cache line at p into L2 (a hint: no register, nothing to wait for)
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 // 4-D tiled prefetch global -> L2 (no shared-memory destination, no completion to wait for)
 __device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* m, int x, int row, int h, int b) {
   asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
