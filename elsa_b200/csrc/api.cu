@@ -124,20 +124,39 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
   if (part_width_in > 0) {
     pl->part_width = static_cast<int>(align_up(part_width_in, pl->tile_n));
   } else {
-    // Every extra partition is one more summary to write and merge, so take the smallest partition
-    // count whose CTA count fills the SMs in whole waves to >= 92 % (or the best seen).
+    // Every extra partition is one more summary to write and merge.  FP32-FMA kernels: the smallest partition count
+    // whose CTA count fills the SMs in whole waves to >= 92 % (or the best seen).
     const int64_t q_ctas = cdiv64(n_ctx, pl->tile_m) * bh;
     const int64_t slots = static_cast<int64_t>(sm_count()) * (pl->tensor_cores ? 1 : 3);
     const int max_parts = static_cast<int>(std::min<int64_t>(tiles_n, pl->tensor_cores ? 8 : 16));
     int best = 1;
-    double best_eff = 0.0;
-    for (int cand = 1; cand <= max_parts; ++cand) {
-      const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, cand));
-      const int64_t real_parts = cdiv64(tiles_n, tiles_per_part);
-      const int64_t ctas = q_ctas * real_parts;
-      const double eff = static_cast<double>(ctas) / static_cast<double>(cdiv64(ctas, slots) * slots);
-      if (eff > best_eff + 1e-9) { best_eff = eff; best = cand; }
-      if (eff >= 0.92) { best = cand; break; }
+    if (pl->tensor_cores) {
+      // Tensor-core kernels (one CTA per SM): time ~ waves x (key tiles per partition + fixed cost of a CTA) + the merge
+      // pass over the partition summaries, in units of one key-tile step.  The fixed cost (barrier and TMEM set-up,
+      // the first loads, the summary store) is about three steps; a step of the 256-row kernels takes ~1.8 us, so one
+      // HBM pass over a summary set is bytes / 6.5 TB/s / 1.8 us steps.  (Measured at (8,3,4097,64): five partitions
+      // fill the waves to 98 % but take 239 + 16 us; one partition fills them to 92 % and takes 190 us.)
+      const double fixed_steps = 3.0;
+      const double merge_steps_per_part = static_cast<double>(bh) * n_ctx * (head_dim * dtype_size(summary_dtype) + 8) / 6.5e6 / 1.8;
+      double best_cost = 0.0;
+      for (int cand = 1; cand <= max_parts; ++cand) {
+        const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, cand));
+        const int64_t real_parts = cdiv64(tiles_n, tiles_per_part);
+        if (real_parts != cand && cand > 1) continue;       // (the same split as a smaller candidate)
+        const int64_t waves = cdiv64(q_ctas * real_parts, slots);
+        const double cost = static_cast<double>(waves) * (tiles_per_part + fixed_steps) + merge_steps_per_part * static_cast<double>(real_parts);
+        if (cand == 1 || cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
+      }
+    } else {
+      double best_eff = 0.0;
+      for (int cand = 1; cand <= max_parts; ++cand) {
+        const int tiles_per_part = static_cast<int>(cdiv64(tiles_n, cand));
+        const int64_t real_parts = cdiv64(tiles_n, tiles_per_part);
+        const int64_t ctas = q_ctas * real_parts;
+        const double eff = static_cast<double>(ctas) / static_cast<double>(cdiv64(ctas, slots) * slots);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = cand; }
+        if (eff >= 0.92) { best = cand; break; }
+      }
     }
     pl->part_width = static_cast<int>(cdiv64(tiles_n, best)) * pl->tile_n;
   }
