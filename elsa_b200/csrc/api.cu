@@ -473,6 +473,14 @@ static int forward_impl(const void* q, const void* k, const void* v, const Strid
                            nullptr, dtype, summary_dtype, batch, heads, n_ctx, head_dim, 0, n_ctx, pl.part_width, 1,
                            is_causal, flags, st, -1, 0, ref_round, qs, ks, vs, out, os, row_m, row_z);
   }
+  // One partition and one query chunk on the 16-bit d <= 64 tensor-core fold: the summary is the row's final state, so
+  // the fold writes out and the row state itself (same rounding points as the merge pass) and no merge pass runs.
+  if (pl.n_parts == 1 && pl.q_chunk >= n_ctx && !ref_round && !(flags & (ELSA_FLAG_SCAN_STEPS | ELSA_FLAG_TREE_MERGE)) &&
+      pl.part_width % 128 == 0 && tc_forward_ok(dtype, head_dim, n_ctx, batch * heads, bias != nullptr, flags)) {
+    return phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, nullptr, nullptr,
+                           nullptr, dtype, summary_dtype, batch, heads, n_ctx, head_dim, 0, n_ctx, pl.part_width, 1,
+                           is_causal, flags, st, -1, 0, false, qs, ks, vs, out, os, row_m, row_z);
+  }
   for (int q_start = 0; q_start < n_ctx; q_start += pl.q_chunk) {
     const int q_len = std::min(pl.q_chunk, n_ctx - q_start);
     rc = phase1_dispatch(q, k, v, bias, bias_stride_b, bias_stride_h, bias_stride_q, bias_stride_k, m_a, z_a, s_a, dtype,

@@ -58,6 +58,11 @@ struct FoldTcParams {
   int n_keys, key_offset, head_dim;
   float scale_log2;
   int* status;   // the device's status word (mapped host memory)
+  // direct != 0 (one partition, the whole query range in one launch): the partition summary is the row's final state,
+  // so the kernel writes out = s / z (s rounded to the summary type first, as the merge pass would read it) through
+  // `os` and, when row_m is not null, the row state -- no summary travels through memory and no merge pass runs
+  int direct;
+  void* out; Strides os; float* row_m; float* row_z;
 };
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -343,7 +348,25 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tmem_wait_ld();
         const float f = (m_true == -CUDART_INF_F) ? 0.f : fast_exp2(m_ref - m_true);
         const float zo = zsum * f;
-        if (row_ok) {
+        if (row_ok && prm.direct) {
+          const int r_seq = prm.q_start + r_chunk;
+          const float inv = zo > 0.f ? 1.0f / zo : 0.f;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            float x = zo > 0.f ? ov[i] * f : 0.f;
+            if (prm.summary_dtype == ELSA_F16) x = round_to<__half>(x);
+            else if (prm.summary_dtype == ELSA_BF16) x = round_to<__nv_bfloat16>(x);
+            ov[i] = zo > 0.f ? x * inv : 0.f;
+          }
+          T* dst = static_cast<T*>(prm.out) + static_cast<int64_t>(bh / prm.heads) * prm.os.b + static_cast<int64_t>(bh % prm.heads) * prm.os.h +
+                   static_cast<int64_t>(r_seq) * prm.os.r;
+          store_row64<T>(dst, ov, prm.head_dim);
+          if (prm.row_m) {
+            const int64_t ro = static_cast<int64_t>(bh) * prm.n_ctx + r_seq;
+            prm.row_m[ro] = zo > 0.f ? m_true : -CUDART_INF_F;
+            prm.row_z[ro] = zo;
+          }
+        } else if (row_ok) {
           const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
           prm.m[ro] = zo > 0.f ? m_true : -CUDART_INF_F;
           prm.z[ro] = zo;
@@ -353,6 +376,20 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           else if (prm.summary_dtype == ELSA_F16) store_row64<__half>(static_cast<__half*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
           else store_row64<__nv_bfloat16>(static_cast<__nv_bfloat16*>(prm.s) + ro * prm.head_dim, ov, prm.head_dim);
         }
+      }
+    } else if (row_ok && prm.direct) {
+      // nothing admissible for this tile at all: zeros and the empty state
+      const int r_seq = prm.q_start + r_chunk;
+      float ov[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) ov[i] = 0.f;
+      T* dst = static_cast<T*>(prm.out) + static_cast<int64_t>(bh / prm.heads) * prm.os.b + static_cast<int64_t>(bh % prm.heads) * prm.os.h +
+               static_cast<int64_t>(r_seq) * prm.os.r;
+      store_row64<T>(dst, ov, prm.head_dim);
+      if (prm.row_m) {
+        const int64_t ro = static_cast<int64_t>(bh) * prm.n_ctx + r_seq;
+        prm.row_m[ro] = -CUDART_INF_F;
+        prm.row_z[ro] = 0.f;
       }
     } else if (row_ok) {
       // nothing admissible in this partition for this tile: the identity
@@ -482,6 +519,8 @@ int fold_tc(const FoldParams& p, int dtype, cudaStream_t st) {
   FoldTcParams prm;
   prm.n_keys = p.n_keys; prm.key_offset = p.key_offset; prm.head_dim = p.head_dim;
   prm.m = p.m; prm.z = p.z; prm.s = p.s;
+  prm.direct = p.direct; prm.out = p.out; prm.os = p.os; prm.row_m = p.row_m; prm.row_z = p.row_z;
+  if (p.direct && (p.n_parts != 1 || !p.out)) return ELSA_ERR_INVALID_ARGUMENT;
   if ((rc = device_status_word(&prm.status, nullptr)) != ELSA_OK) return rc;
   prm.n_ctx = p.n_ctx; prm.q_start = p.q_start; prm.q_len = p.q_len; prm.part_width = p.part_width;
   prm.n_parts = p.n_parts; prm.bh = p.bh; prm.heads = p.heads; prm.is_causal = p.is_causal; prm.summary_dtype = p.summary_dtype;
