@@ -238,14 +238,14 @@ win_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // ------------------------------------------------------------------------------------------------------------------
 // Backward of the same problems, one launch: dQ, dK, dV (and dbias) of two sequences of one head per CTA.
 //
-//   round 1 (issuer)   S^T = K Q^T, dP^T = V dO^T (the key side starts), S = Q K^T, dP = dO V^T (the query side starts):
+//   first MMAs (issuer)   S^T = K Q^T, dP^T = V dO^T (the key side starts), S = Q K^T, dP = dO V^T (the query side starts):
 //                      four 128 x 128 tiles = all 512 TMEM columns
 //   query side (warps 0-3, thread = query row)   -LSE and -D of the row, published in shared memory;
 //                      P = 2^(S c + bias - LSE), dS = P (dP - D) over the row's own sequence; dS (16-bit) written over
 //                      the row's S columns
 //   key side (warps 4-7, thread = key row, at the same time)   P^T, dS^T from S^T, dP^T with the queries' -LSE / -D;
 //                      written over the S^T columns; dbias += dS^T (the lanes of a warp hold consecutive keys: coalesced)
-//   round 2 (issuer)   dQ = dS K -> the dP columns as soon as the query side is done; dV = P^T dO, dK = dS^T Q -> the
+//   second MMAs (issuer)  dQ = dS K -> the dP columns as soon as the query side is done; dV = P^T dO, dK = dS^T Q -> the
 //                      dP^T columns as soon as the key side is done
 //   epilogue           the query side stores dQ, the key side dV and dK
 //
