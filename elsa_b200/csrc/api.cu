@@ -144,7 +144,16 @@ static int plan_forward(int dtype, int summary_dtype, int batch, int heads, int 
         const int64_t real_parts = cdiv64(tiles_n, tiles_per_part);
         if (real_parts != cand && cand > 1) continue;       // (the same split as a smaller candidate)
         const int64_t waves = cdiv64(q_ctas * real_parts, slots);
-        const double cost = static_cast<double>(waves) * (tiles_per_part + fixed_steps) + merge_steps_per_part * static_cast<double>(real_parts);
+        double cost = static_cast<double>(waves) * (tiles_per_part + fixed_steps) + merge_steps_per_part * static_cast<double>(real_parts);
+        if (is_causal) {
+          // causal: a CTA's work grows with its first row (long CTAs are handed out first), half of the tile pairs are
+          // skipped and (P - 1) / 2P of the (query tile, partition) pairs are empty: total work over the slots plus a
+          // tail of a quarter of the longest CTA.  (Measured: (1,8,8192,64) one partition 0.156 ms, two 0.138.)
+          const double p = static_cast<double>(real_parts);
+          const double work = static_cast<double>(q_ctas) * (0.5 * tiles_n + 0.5 * pl->tile_m / pl->tile_n);
+          const double ctas = static_cast<double>(q_ctas) * p * (p + 1.0) / (2.0 * p);
+          cost = (work + ctas * (fixed_steps + 1.0)) / static_cast<double>(slots) + 0.25 * tiles_per_part + merge_steps_per_part * p;
+        }
         if (cand == 1 || cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
       }
     } else {

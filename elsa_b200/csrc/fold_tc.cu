@@ -102,7 +102,10 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.z, part = blockIdx.y;
   const int bi = bh / prm.heads, hi = bh - bi * prm.heads;  // tensor-map coordinates of this (batch*head)
-  const int q0 = prm.q_start + blockIdx.x * 256;           // first query row of tile 0
+  // causal: a tile's work grows with its first row, so the tiles are handed out from the last one down -- the long
+  // ones first, the short ones fill the end of the last wave
+  const int bx = prm.is_causal ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int q0 = prm.q_start + bx * 256;           // first query row of tile 0
   const int q_end = prm.q_start + prm.q_len;
   const int k_begin = part * prm.part_width;
   const int k_end = min(prm.n_keys, k_begin + prm.part_width);   // local key indices
@@ -331,7 +334,7 @@ fold_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
 
     // epilogue: renormalise to the true max and write the summary row
-    const int r_chunk = blockIdx.x * 256 + t * 128 + row;   // row within the query chunk
+    const int r_chunk = bx * 256 + t * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     if (n_t[t] > 0) {
       if (alive && !__all_sync(0xffffffffu, mbar_wait(bar_o(t), 0, &abort_flag, prm.status, BAR_O))) alive = false;

@@ -92,7 +92,10 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.z, part = blockIdx.y;
   const int bi = bh / prm.heads, hi = bh - bi * prm.heads;  // tensor-map coordinates of this (batch*head)
-  const int q0 = prm.q_start + blockIdx.x * 128;
+  // causal: a tile's work grows with its first row, so the tiles are handed out from the last one down -- the long
+  // ones first, the short ones fill the end of the last wave
+  const int bx = prm.is_causal ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int q0 = prm.q_start + bx * 128;
   const int q_end = prm.q_start + prm.q_len;
   const int k_begin = part * prm.part_width;
   const int k_end = min(prm.n_keys, k_begin + prm.part_width);   // local key indices
@@ -341,7 +344,7 @@ fold_tcw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
 
     // epilogue: the last key tile's O, the row sum over the four quarters, renormalisation to the true max, the summary row
-    const int r_chunk = blockIdx.x * 128 + row;   // row within the query chunk
+    const int r_chunk = bx * 128 + row;   // row within the query chunk
     const bool row_ok = r_chunk < prm.q_len;
     const int64_t ro = (static_cast<int64_t>(part) * prm.bh + bh) * prm.q_len + r_chunk;
     float m_out = -CUDART_INF_F, z_out = 0.f;
