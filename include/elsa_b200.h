@@ -88,7 +88,8 @@ int64_t elsa_kernel_launches(void);
  * (and its gradient), two sequences per 128-row tile. */
 int elsa_uses_tensor_cores(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward);
 /* The same question for a given batch size.  Sequences of 65 to 511 tokens also run on the tensor-core kernels when the
- * problem has at least 4096 rows in total (batch * heads * n_ctx): from there on 128-row tiles fill the machine.
+ * problem has at least 4096 rows in total (batch * heads * n_ctx): from there on 128-row tiles fill the machine; the
+ * fp16 / bf16 backward runs there from 65 tokens on at every batch size.
  * elsa_uses_tensor_cores answers for batch = heads = 1, i.e. what holds whatever the batch size. */
 int elsa_uses_tensor_cores_for(int dtype, int head_dim, int n_ctx, int has_bias, int is_causal, int backward, int batch,
                                int heads);
