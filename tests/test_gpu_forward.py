@@ -366,3 +366,23 @@ def test_routing_of_small_head_dims_and_fp32():
             assert lib.elsa_uses_tensor_cores_for(dt, 64, 200, 0, 0, backward, 1, 3) == small
             assert lib.elsa_uses_tensor_cores_for(dt, 64, 200, 0, 0, backward, 8, 3) == 1   # 4800 rows in total
             assert lib.elsa_uses_tensor_cores_for(dt, 64, 640, 0, 0, backward, 1, 1) == 1
+
+
+def test_default_plan_of_the_tensor_core_fold():
+    """The partition count comes from a cost model (waves x (key tiles per partition + a CTA's fixed cost) + the merge
+    pass), not from wave fill alone: the ragged ViT length keeps one partition (five fill the waves better and ran a
+    third slower), the headline shape two; causal problems split finer than non-causal ones of the same size."""
+    import ctypes
+    from elsa_b200 import _lib
+    lib = _lib.load()
+
+    def parts(dt, b, h, n, d, causal):
+        n_parts = ctypes.c_int()
+        assert lib.elsa_forward_plan(dt, dt, b, h, n, d, 0, causal, 0, 0, 0, None, ctypes.byref(n_parts), None) == 0
+        return n_parts.value
+
+    assert parts(1, 8, 3, 4097, 64, 0) == 1
+    assert parts(1, 1, 8, 16384, 64, 0) == 2
+    assert parts(2, 1, 8, 16384, 64, 1) == 2
+    assert parts(1, 1, 8, 8192, 64, 0) == 1 and parts(1, 1, 8, 8192, 64, 1) == 2
+    assert parts(1, 64, 3, 197, 64, 0) == 1
