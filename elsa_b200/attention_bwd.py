@@ -273,14 +273,17 @@ def _packed_forward_fast(qkv, bias32, is_causal, fwd_kwargs, want_state):
     """The forward on a contiguous packed qkv: (out as [B, N, H, D], state or None, bias meta, plan).  `state` holds
     row_m and row_z in one allocation, the second at a 256-byte boundary like a tensor of its own."""
     batch, seq_len, _, heads, head_dim = map(int, qkv.shape)
-    kw = dict(fwd_kwargs)
-    kw.pop("reference_rounding", None)
-    summary_dtype, part_width, q_chunk = _resolve_common(
-        qkv, algorithm=kw.pop("algorithm", "auto"), input_precision=kw.pop("input_precision", "auto"),
-        summary_dtype=kw.pop("summary_dtype", None), block_m=kw.pop("block_m", None), block_n=kw.pop("block_n", None),
-        q_chunk_size=kw.pop("q_chunk_size", None), phase1_warps=kw.pop("phase1_warps", None),
-        phase2_warps=kw.pop("phase2_warps", None), phase1_stages=kw.pop("phase1_stages", None),
-        phase2_stages=kw.pop("phase2_stages", None))
+    if not fwd_kwargs:                                     # (the ViT hooks' call: nothing to validate or resolve)
+        summary_dtype, part_width, q_chunk, kw = qkv.dtype, 0, 0, None
+    else:
+        kw = dict(fwd_kwargs)
+        kw.pop("reference_rounding", None)
+        summary_dtype, part_width, q_chunk = _resolve_common(
+            qkv, algorithm=kw.pop("algorithm", "auto"), input_precision=kw.pop("input_precision", "auto"),
+            summary_dtype=kw.pop("summary_dtype", None), block_m=kw.pop("block_m", None), block_n=kw.pop("block_n", None),
+            q_chunk_size=kw.pop("q_chunk_size", None), phase1_warps=kw.pop("phase1_warps", None),
+            phase2_warps=kw.pop("phase2_warps", None), phase1_stages=kw.pop("phase1_stages", None),
+            phase2_stages=kw.pop("phase2_stages", None))
     if kw:
         raise TypeError(f"unexpected keyword arguments: {sorted(kw)}")
     meta = _canonical_bias(bias32, batch=batch, heads=heads, seq_len=seq_len, device=qkv.device)
