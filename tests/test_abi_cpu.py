@@ -107,3 +107,23 @@ def test_patch_report_and_detectors():
     rep = patch_timm_attention(model)
     assert (rep.vit_attention, rep.swin_window_attention, rep.total) == (1, 1, 2)
     assert sorted(n for n, _ in model.named_parameters()) == names_before
+
+
+def test_packed_plan_strides_match_the_views():
+    """The packed-qkv path hands the C ABI strides computed from the shape alone: they must be the strides of the q / k / v
+    views of a contiguous [B, N, 3, H, D] tensor and of the [B, H, N, D] view of the [B, N, H, D] output."""
+    from elsa_b200.attention import _bhnd_strides
+    from elsa_b200.attention_bwd import _PackedPlan
+    b, n, h, d = 3, 49, 4, 32
+    qkv = torch.zeros(b, n, 3, h, d, dtype=torch.float16)
+    plan = _PackedPlan(qkv, False, False, torch.float16, 0, 0)
+    q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+    for t in (q, k, v):
+        assert tuple(plan.qkv_strides) == _bhnd_strides(t)
+    out = torch.zeros(b, n, h, d, dtype=torch.float16).permute(0, 2, 1, 3)
+    assert tuple(plan.out_strides) == _bhnd_strides(out)
+    assert plan.hd * plan.esize == (k.data_ptr() - q.data_ptr()) == (v.data_ptr() - k.data_ptr())
+    gs = _bhnd_strides(out)
+    arr = tuple(plan.backward_strides(gs))
+    assert arr[:9] == tuple(plan.qkv_strides) * 3 and arr[9:12] == tuple(plan.out_strides) and arr[12:15] == gs
+    assert arr[15:] == tuple(plan.qkv_strides) * 3 and plan.fwd_ws >= 0 and plan.bwd_ws >= 0
